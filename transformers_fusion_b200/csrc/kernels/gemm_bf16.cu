@@ -1,0 +1,397 @@
+// bf16 GEMM for sm_100a: C[M,N] = epilogue(A * B), fp32 accumulation in tensor memory.
+//
+// Design (one persistent CTA per SM, 192 threads, warp-specialised):
+//   warp 0      TMA producer  : cp.async.bulk.tensor tiles of A and B into a 4-stage shared-memory ring
+//   warp 1      MMA issuer    : one thread issues tcgen05.mma (128 x BN x 16) per 32 bytes of K and
+//                               commits stage-release / accumulator-ready mbarriers
+//   warps 2..5  epilogue      : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread),
+//                               apply alpha / bias / activation / residual, store bf16 or fp32
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Either operand may be K-major (reduction dim contiguous) or MN-major
+// (output dim contiguous): the forward, data-gradient and weight-gradient GEMMs of a linear layer
+// all run without a transpose copy.  Small-output / long-K problems (weight gradients) are split
+// along K across CTAs and reduced with vector fp32 atomics into the fp32 gradient buffer.
+//
+// This replaces the reference's scalar one-thread-per-output kernels
+// (src/backend/gpu_compute_cuda.cpp:68 gemm_kernel; src/kernel/kernel_gemm.cpp:26 scalar_gemm_bt).
+#include "tfb_host.h"
+#include "tfb_ptx.cuh"
+
+namespace tfb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ldr] or null (bf16 output mode only)
+  long long ldr;
+  float alpha;
+  int act;       // 0 none, 1 relu, 2 gelu(tanh), 3 silu
+  int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 atomic accumulate
+  int splits, kb_per_split, tiles_m, tiles_n;
+  int* status;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // + barriers + alignment slack
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case 1: return fmaxf(v, 0.f);
+    case 2: return gelu_tanh(v);
+    case 3: return silu(v);
+    default: return v;
+  }
+}
+
+template <bool A_MN, bool B_MN, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + b * 8, 1);
+      mbar_init(bar_tempty + b * 8, 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int num_work = p.tiles_m * p.tiles_n * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w - tile * p.splits;
+        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = bar_full + stage * 8;
+          mbar_expect_tx(fb, L::STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + L::A_BYTES;
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tma_a, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, fb, m0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tma_b, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, fb, n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: give copies already issued a bounded time to land before shared memory goes away.
+        const uint64_t t0 = globaltimer_ns();
+        for (int s = 0; s < STAGES; ++s) {
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1);
+          while (!mbar_try_wait(bar_full + s * 8, par)) {
+            if (globaltimer_ns() - t0 > 2000000ull) { report(p.status, ST_TIMEOUT_DRAIN); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(FMT_BF16, FMT_BF16, A_MN, B_MN, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int abuf = 0;
+      uint32_t aphase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w - tile * p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        if (!mbar_wait(bar_tempty + abuf * 8, aphase ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + abuf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, p.status, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc(sa + k * 2048, 8192, 1024)
+                                        : umma_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024)
+                                        : umma_smem_desc(sb + k * 32, 16, 1024);
+            umma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + stage * 8);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + abuf * 8);
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int abuf = 0;
+    uint32_t aphase = 0;
+    const bool vec_ok_bf16 = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool vec_ok_f32 = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool vec_ok_res =
+        p.residual && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+    for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
+      const int tile = w / p.splits;
+      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      if (!mbar_wait(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr0 = tmem_base + abuf * BN + (uint32_t(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr0 + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row >= p.M || col0 >= p.N) continue;
+        const bool full = col0 + 32 <= p.N;
+        if (p.out_mode == 0) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+          if (p.act) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+          }
+          if (p.residual) {
+            const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
+            if (full && vec_ok_res) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = *reinterpret_cast<const uint4*>(rp + q * 8);
+                const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  const float2 f = unpack_bf16(uu[h]);
+                  v[q * 8 + h * 2] += f.x;
+                  v[q * 8 + h * 2 + 1] += f.y;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+            }
+          }
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+          if (full && vec_ok_bf16) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
+              u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+              u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+              u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(cp + q * 8) = u;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
+          }
+        } else {
+          float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+          if (p.out_mode == 1) {
+            if (full && vec_ok_f32) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 f = make_float4(__uint_as_float(r[q * 4]) * p.alpha, __uint_as_float(r[q * 4 + 1]) * p.alpha,
+                                       __uint_as_float(r[q * 4 + 2]) * p.alpha, __uint_as_float(r[q * 4 + 3]) * p.alpha);
+                *reinterpret_cast<float4*>(cp + q * 4) = f;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) cp[j] = __uint_as_float(r[j]) * p.alpha;
+            }
+          } else {
+            if (full && vec_ok_f32) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + q * 4),
+                             "f"(__uint_as_float(r[q * 4]) * p.alpha), "f"(__uint_as_float(r[q * 4 + 1]) * p.alpha),
+                             "f"(__uint_as_float(r[q * 4 + 2]) * p.alpha), "f"(__uint_as_float(r[q * 4 + 3]) * p.alpha)
+                             : "memory");
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) atomicAdd(cp + j, __uint_as_float(r[j]) * p.alpha);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + abuf * 8);
+      abuf ^= 1;
+      if (abuf == 0) aphase ^= 1;
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------------
+// host launcher
+// -------------------------------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, int BN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, BN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace tfb
+
+// C[M,N] (ldc) = act(alpha * A.B + bias) + residual.
+//   a_mn = 0: A is [M,K] with K contiguous (row pitch lda elements); a_mn = 1: A is stored [K,M], M contiguous.
+//   b_mn = 0: B is [N,K] with K contiguous (weight layout [out,in]);  b_mn = 1: B is stored [K,N], N contiguous.
+//   out_mode 0: bf16 store; 1: fp32 store; 2: fp32 atomic accumulate (C += ...), the only mode that allows split-K.
+//   max_ctas > 0 limits the persistent grid (leaves SMs free for a concurrent communication kernel).
+TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
+                          long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
+                          float alpha, int act, int out_mode, int max_ctas, int* status, void* stream) {
+  using namespace tfb;
+  if (M <= 0 || N <= 0 || K <= 0) return TFB_ERR_ARG;
+  if (out_mode != 0 && (bias || residual || act)) return TFB_ERR_ARG;
+  const int BN = (N > 128) ? 256 : 128;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, BM);
+  else rc = make_tmap_2d(&ta, A, 2, M, K, lda * 2, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_tmap_2d(&tb, B, 2, K, N, ldb * 2, BK, BN);
+  else rc = make_tmap_2d(&tb, B, 2, N, K, ldb * 2, 64, BK);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.alpha = alpha; p.act = act; p.out_mode = out_mode;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.status = status;
+  const int total_kb = (K + BK - 1) / BK;
+  int sms = sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  const int tiles = p.tiles_m * p.tiles_n;
+  int splits = 1;
+  if (out_mode == 2 && tiles < sms) {
+    splits = (sms + tiles - 1) / tiles;
+    const int max_splits = (total_kb + 7) / 8;  // keep at least 8 k-blocks (512 of K) per split
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+  }
+  p.kb_per_split = (total_kb + splits - 1) / splits;
+  p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+  const long long work = (long long)tiles * p.splits;
+  const int grid = int(work < sms ? work : sms);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (BN == 256) {
+    switch (key) {
+      case 0: return launch<false, false, 256>(ta, tb, p, grid, st);
+      case 1: return launch<false, true, 256>(ta, tb, p, grid, st);
+      case 2: return launch<true, false, 256>(ta, tb, p, grid, st);
+      default: return launch<true, true, 256>(ta, tb, p, grid, st);
+    }
+  } else {
+    switch (key) {
+      case 0: return launch<false, false, 128>(ta, tb, p, grid, st);
+      case 1: return launch<false, true, 128>(ta, tb, p, grid, st);
+      case 2: return launch<true, false, 128>(ta, tb, p, grid, st);
+      default: return launch<true, true, 128>(ta, tb, p, grid, st);
+    }
+  }
+}

@@ -1,0 +1,31 @@
+// Host-side helpers shared by the kernel translation units: error return convention,
+// TMA tensor-map creation (driver entry point looked up at run time, so the library has no
+// link-time dependency on libcuda) and a small descriptor cache.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TFB_API extern "C" __attribute__((visibility("default")))
+
+// All exported entry points return 0 on success, a negative tfb error or a positive cudaError_t.
+enum {
+  TFB_OK = 0,
+  TFB_ERR_ARG = -1,       // shape / alignment not supported by the kernel
+  TFB_ERR_DRIVER = -2,    // driver entry point or tensor-map encode failed
+  TFB_ERR_LIMIT = -3,     // size beyond a documented fixed limit
+};
+
+namespace tfb {
+
+// 2-D bf16/fp8 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld_bytes`.
+// Box = box_inner x box_outer elements, 128-byte swizzle, zero fill outside the tensor.
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                 uint64_t ld_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle128 = 1);
+// 3-D variant (inner, mid, outer) with byte strides for mid and outer.
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t d2,
+                 uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, int swizzle128 = 1);
+
+int sm_count();
+
+}  // namespace tfb

@@ -1,0 +1,132 @@
+"""ctypes binding to ``lib/libtfb_kernels.so`` (the sm_100a kernels).
+
+The library exposes a plain C ABI: every entry point takes raw device pointers, sizes and the CUDA
+stream handle, and returns 0 on success.  Python passes ``tensor.data_ptr()`` and the current torch
+stream, so launches are ordered with the surrounding PyTorch work and can be captured in CUDA
+graphs.  On a machine with a GPU a missing library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
+_lib = None
+_status = {}
+
+c_p = C.c_void_p
+c_i = C.c_int
+c_ll = C.c_longlong
+c_f = C.c_float
+
+_SIGS = {
+    "tfb_sm_count": [],
+    "tfb_gemm_bf16": [c_p, c_ll, c_i, c_p, c_ll, c_i, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_ll, c_f, c_i, c_i, c_i, c_p, c_p],
+    "tfb_rmsnorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_p],
+    "tfb_rmsnorm_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_p],
+    "tfb_layernorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_p],
+    "tfb_layernorm_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_p],
+    "tfb_rope": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_ll, c_i, c_p],
+    "tfb_glu_fwd": [c_p, c_p, c_ll, c_i, c_i, c_p],
+    "tfb_glu_bwd": [c_p, c_p, c_p, c_ll, c_i, c_i, c_p],
+    "tfb_act_fwd": [c_p, c_p, c_ll, c_i, c_p],
+    "tfb_act_bwd": [c_p, c_p, c_p, c_ll, c_i, c_p],
+    "tfb_embedding_fwd": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p],
+    "tfb_embedding_bwd": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p],
+    "tfb_add_bf16": [c_p, c_p, c_p, c_ll, c_p],
+    "tfb_cross_entropy": [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_ll, c_f, c_f, c_p],
+    "tfb_sumsq_f32": [c_p, c_ll, c_p, c_p],
+    "tfb_clip_factor": [c_p, c_f, c_f, c_p, c_p, c_p, c_p],
+    "tfb_adamw": [c_p, c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_i, c_p, c_i, c_p],
+    "tfb_lion_sgd": [c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_i, c_p, c_i, c_p],
+    "tfb_cast_f32_bf16": [c_p, c_p, c_ll, c_p],
+    "tfb_cast_bf16_f32": [c_p, c_p, c_ll, c_p],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_DIR / "libtfb_kernels.so"
+
+
+def available() -> bool:
+    return lib_path().exists()
+
+
+def lib():
+    """Load (once) and return the kernel library; build it first if the shared object is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    p = lib_path()
+    if not p.exists():
+        if os.environ.get("TFB_NO_AUTOBUILD"):
+            raise KernelError(f"{p} is missing; run `python -m transformers_fusion_b200.build`")
+        from .. import build as _build
+        _build.build_kernels()
+    _lib = C.CDLL(str(p))
+    for name, sig in _SIGS.items():
+        try:
+            fn = getattr(_lib, name)
+        except AttributeError:
+            continue
+        fn.argtypes = sig
+        fn.restype = c_i
+    return _lib
+
+
+def register(name: str, sig):
+    """Declare the signature of an entry point defined by another module (attention, comm, quant)."""
+    _SIGS[name] = sig
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = sig
+        fn.restype = c_i
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        if rc > 0:
+            raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no gpu'})")
+        raise KernelError(f"{what}: tfb error {rc} (-1 bad shape/alignment, -2 driver entry point, -3 size limit)")
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits write a code into when a wait runs out."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(8, dtype=torch.int32, device=torch.device("cuda", key))
+        _status[key] = t
+    return t
+
+
+_STATUS_NAMES = {
+    1: "operand stage never arrived (TMA)", 2: "stage never released (MMA)", 3: "accumulator never committed",
+    4: "accumulator never drained", 5: "copies still in flight at exit", 6: "peer flag never set", 7: "bad argument",
+}
+
+
+def check_status(device=None, reset=True):
+    """Synchronising read of the status word; raises if any kernel reported a wait that ran out."""
+    t = status_word(device)
+    code = int(t[0].item())
+    if code:
+        if reset:
+            t.zero_()
+        raise KernelError(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
