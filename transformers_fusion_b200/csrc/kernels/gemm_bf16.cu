@@ -203,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
       const int tile = w / p.splits;
       const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-      if (!mbar_wait(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      if (!mbar_wait_warp(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr0 = tmem_base + abuf * BN + (uint32_t(quad * 32) << 16);

@@ -158,7 +158,9 @@ struct AdamArgs {
 __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p_lp,
                                                     long long n, AdamArgs a, const float* __restrict__ gscale_ptr,
-                                                    int zero_grad) {
+                                                    int zero_grad, const float* __restrict__ hyper) {
+  // hyper (optional, device): {lr, 1 - beta1^t, 1 - beta2^t}; lets a captured CUDA graph see per-step values
+  if (hyper) { a.lr = hyper[0]; a.bc1 = hyper[1]; a.bc2 = hyper[2]; }
   const float gs = gscale_ptr ? *gscale_ptr : 1.f;
   if (gs == 0.f && gscale_ptr) {  // skipped step (overflow): only clear the gradients
     if (zero_grad)
@@ -275,14 +277,14 @@ TFB_API int tfb_clip_factor(const float* sumsq, float inv_scale, float max_norm,
 
 TFB_API int tfb_adamw(float* p, float* g, float* m, float* v, void* p_lp, long long n, float lr, float beta1,
                       float beta2, float eps, float wd, int step, const float* gscale_ptr, int zero_grad,
-                      void* stream) {
+                      const float* hyper, void* stream) {
   if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
        reinterpret_cast<uintptr_t>(v)) & 15)
     return TFB_ERR_ARG;
   if (p_lp && (reinterpret_cast<uintptr_t>(p_lp) & 7)) return TFB_ERR_ARG;
   AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, float(step)), 1.f - powf(beta2, float(step))};
   adamw_kernel<<<grid_cap(n / 4 + 1, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      p, g, m, v, static_cast<__nv_bfloat16*>(p_lp), n, a, gscale_ptr, zero_grad);
+      p, g, m, v, static_cast<__nv_bfloat16*>(p_lp), n, a, gscale_ptr, zero_grad, hyper);
   return int(cudaGetLastError());
 }
 

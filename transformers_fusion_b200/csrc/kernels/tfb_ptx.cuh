@@ -89,6 +89,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-collective form for warps that go on to execute .sync.aligned instructions (tcgen05.ld/st):
+// every lane polls, then the warp votes, so all 32 lanes take the same branch even when a wait runs out.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (no cluster fan-out anywhere: every CTA fetches its own tiles)
 // ---------------------------------------------------------------------------------------------

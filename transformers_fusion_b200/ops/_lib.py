@@ -40,7 +40,7 @@ _SIGS = {
     "tfb_cross_entropy": [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_ll, c_f, c_f, c_p],
     "tfb_sumsq_f32": [c_p, c_ll, c_p, c_p],
     "tfb_clip_factor": [c_p, c_f, c_f, c_p, c_p, c_p, c_p],
-    "tfb_adamw": [c_p, c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_i, c_p, c_i, c_p],
+    "tfb_adamw": [c_p, c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_i, c_p, c_i, c_p, c_p],
     "tfb_lion_sgd": [c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_i, c_p, c_i, c_p],
     "tfb_cast_f32_bf16": [c_p, c_p, c_ll, c_p],
     "tfb_cast_bf16_f32": [c_p, c_p, c_ll, c_p],

@@ -32,7 +32,7 @@ def _act_ref(x, act):
 # ---------------------------------------------------------------------------------------------
 # GEMM
 # ---------------------------------------------------------------------------------------------
-def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bias=None, residual=None, act=None,
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, bias=None, residual=None, act=None,
          alpha=1.0, accumulate=False, max_ctas=0):
     """C = act(alpha * A @ B + bias) + residual.
 
@@ -45,6 +45,8 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, bi
     N = b.shape[1] if b_mn else b.shape[0]
     Kb = b.shape[0] if b_mn else b.shape[1]
     assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    if out_dtype is None:
+        out_dtype = a.dtype
     if accumulate:
         assert out is not None and out.dtype == torch.float32
         out_dtype = torch.float32
@@ -360,9 +362,13 @@ def clip_factor(sumsq_t, inv_scale, max_norm, norm_out, clip_out, found_inf=None
                                      clip_out.data_ptr(), ptr(found_inf), stream()), "clip_factor")
 
 
-def adamw_(p, g, m, v, p_lp, lr, beta1, beta2, eps, wd, step, gscale=None, zero_grad=True):
+def adamw_(p, g, m, v, p_lp, lr, beta1, beta2, eps, wd, step, gscale=None, zero_grad=True, hyper=None):
     """Fused AdamW over flat fp32 state; refreshes the bf16 copy ``p_lp`` and zeroes ``g``."""
     if not p.is_cuda:
+        if hyper is not None:
+            lr, bc1, bc2 = (float(x) for x in hyper[:3])
+        else:
+            bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
         gs = gscale.float() if gscale is not None else torch.ones(())
         if gscale is not None and float(gs) == 0.0:
             if zero_grad:
@@ -371,8 +377,8 @@ def adamw_(p, g, m, v, p_lp, lr, beta1, beta2, eps, wd, step, gscale=None, zero_
         gr = g * gs
         m.mul_(beta1).add_(gr, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(gr, gr, value=1 - beta2)
-        mh = m / (1 - beta1 ** step)
-        vh = v / (1 - beta2 ** step)
+        mh = m / bc1
+        vh = v / bc2
         p.sub_(lr * (mh / (vh.sqrt() + eps) + wd * p))
         if zero_grad:
             g.zero_()
@@ -381,4 +387,86 @@ def adamw_(p, g, m, v, p_lp, lr, beta1, beta2, eps, wd, step, gscale=None, zero_
         return
     check(_lib.lib().tfb_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), ptr(p_lp), p.numel(), float(lr),
                                float(beta1), float(beta2), float(eps), float(wd), int(step), ptr(gscale),
-                               int(zero_grad), stream()), "adamw")
+                               int(zero_grad), ptr(hyper), stream()), "adamw")
+
+
+# ---------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------
+_lib.register("tfb_attn_fwd", [_lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll,
+                               _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_p, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i,
+                               _lib.c_i, _lib.c_f, _lib.c_i, _lib.c_p, _lib.c_p])
+
+
+def _split_heads(buf, col0, n_heads, D, B, S):
+    return buf[:, col0: col0 + n_heads * D].reshape(B, S, n_heads, D).permute(0, 2, 1, 3).float()
+
+
+def attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0=0, k_col0=0, v_col0=0):
+    """fp32 reference: returns (o [B*S, Hq*D], lse [B, Hq, S], probabilities)."""
+    Q = _split_heads(q, q_col0, Hq, D, B, S)
+    K = _split_heads(k, k_col0, Hkv, D, B, S).repeat_interleave(Hq // Hkv, 1)
+    V = _split_heads(v, v_col0, Hkv, D, B, S).repeat_interleave(Hq // Hkv, 1)
+    s = (Q @ K.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=s.device).triu(1), float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    P = torch.exp(s - lse[..., None])
+    o = (P @ V).permute(0, 2, 1, 3).reshape(B * S, Hq * D)
+    return o, lse, P
+
+
+def attn_fwd(q, k, v, B, S, Hq, Hkv, D, scale=None, causal=True, q_col0=0, k_col0=0, v_col0=0):
+    """q/k/v: [B*S, ld] bf16 buffers (may be one fused projection output; see column offsets).
+    Returns (o [B*S, Hq*D] bf16, lse [B, Hq, S] fp32)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        o, lse, _ = attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0, k_col0, v_col0)
+        return o.to(q.dtype), lse
+    o = torch.empty((B * S, Hq * D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    check(_lib.lib().tfb_attn_fwd(q.data_ptr(), q.stride(0), q_col0, k.data_ptr(), k.stride(0), k_col0, v.data_ptr(),
+                                  v.stride(0), v_col0, o.data_ptr(), o.stride(0), lse.data_ptr(), B, S, Hq, Hkv, D,
+                                  float(scale), int(causal), _lib.status_word(q.device).data_ptr(), stream()),
+          "attn_fwd")
+    return o, lse
+
+
+_lib.register("tfb_attn_bwd", [_lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll,
+                               _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_p, _lib.c_ll, _lib.c_p, _lib.c_p,
+                               _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll,
+                               _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_f, _lib.c_i,
+                               _lib.c_p, _lib.c_p])
+
+
+def attn_bwd(q, k, v, o, dout, lse, dqkv, B, S, Hq, Hkv, D, scale=None, causal=True, q_col0=0, k_col0=0, v_col0=0,
+             dq_col0=None, dk_col0=None, dv_col0=None):
+    """Writes dq / dk / dv into ``dqkv`` ([B*S, ld] bf16) at the given column offsets (defaults: the
+    same offsets as q / k / v, i.e. ``dqkv`` mirrors a fused projection output)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    dq_col0 = q_col0 if dq_col0 is None else dq_col0
+    dk_col0 = k_col0 if dk_col0 is None else dk_col0
+    dv_col0 = v_col0 if dv_col0 is None else dv_col0
+    if not q.is_cuda:
+        Q = _split_heads(q, q_col0, Hq, D, B, S).requires_grad_(True)
+        K = _split_heads(k, k_col0, Hkv, D, B, S).requires_grad_(True)
+        V = _split_heads(v, v_col0, Hkv, D, B, S).requires_grad_(True)
+        with torch.enable_grad():
+            G = Hq // Hkv
+            s = (Q @ K.repeat_interleave(G, 1).transpose(-1, -2)) * scale
+            if causal:
+                s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+            out = (torch.softmax(s, -1) @ V.repeat_interleave(G, 1)).permute(0, 2, 1, 3).reshape(B * S, Hq * D)
+            gq, gk, gv = torch.autograd.grad(out, (Q, K, V), dout.float())
+        dqkv[:, dq_col0: dq_col0 + Hq * D] = gq.permute(0, 2, 1, 3).reshape(B * S, Hq * D).to(dqkv.dtype)
+        dqkv[:, dk_col0: dk_col0 + Hkv * D] = gk.permute(0, 2, 1, 3).reshape(B * S, Hkv * D).to(dqkv.dtype)
+        dqkv[:, dv_col0: dv_col0 + Hkv * D] = gv.permute(0, 2, 1, 3).reshape(B * S, Hkv * D).to(dqkv.dtype)
+        return dqkv
+    delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    dp, ldd = dqkv.data_ptr(), dqkv.stride(0)
+    check(_lib.lib().tfb_attn_bwd(q.data_ptr(), q.stride(0), q_col0, k.data_ptr(), k.stride(0), k_col0, v.data_ptr(),
+                                  v.stride(0), v_col0, o.data_ptr(), o.stride(0), dout.data_ptr(), dout.stride(0),
+                                  lse.data_ptr(), delta.data_ptr(), dp, ldd, dq_col0, dp, ldd, dk_col0, dp, ldd,
+                                  dv_col0, B, S, Hq, Hkv, D, float(scale), int(causal),
+                                  _lib.status_word(q.device).data_ptr(), stream()), "attn_bwd")
+    return dqkv
