@@ -38,7 +38,9 @@ class FlatBuffers:
 
     ALIGN = 128
 
-    def __init__(self, module: nn.Module, dtype=torch.bfloat16, pad_to: int = 1):
+    def __init__(self, module: nn.Module, dtype=torch.bfloat16, pad_to: int = 1, allocator=None):
+        """``allocator(numel, dtype)`` returns an object with ``.view(dtype, numel)`` (the symmetric
+        heap's ``alloc``) when the buffers must be visible to peer GPUs; default: plain torch tensors."""
         seen, params = set(), []
         for p in module.parameters():
             if id(p) not in seen:
@@ -53,8 +55,17 @@ class FlatBuffers:
         dev = params[0].device if params else torch.device("cpu")
         self.numel = n
         self.offsets = offs
-        self.params = torch.zeros(n, dtype=dtype, device=dev)
-        self.grads = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.symm_params = self.symm_grads = None
+        if allocator is not None:
+            self.symm_params = allocator(n, dtype)
+            self.symm_grads = allocator(n, torch.float32)
+            self.params = self.symm_params.view(dtype, n)
+            self.grads = self.symm_grads.view(torch.float32, n)
+            self.params.zero_()
+            self.grads.zero_()
+        else:
+            self.params = torch.zeros(n, dtype=dtype, device=dev)
+            self.grads = torch.zeros(n, dtype=torch.float32, device=dev)
         for p, o in zip(params, offs):
             view = self.params[o: o + p.numel()].view(p.shape)
             view.copy_(p.data.to(dtype))

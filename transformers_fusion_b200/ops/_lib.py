@@ -90,7 +90,11 @@ def register(name: str, sig):
         fn.restype = c_i
 
 
-def check(rc: int, what: str):
+LAUNCHES = [0]  # kernels launched through this binding (graph replays are counted by the engine)
+
+
+def check(rc: int, what: str, n: int = 1):
+    LAUNCHES[0] += n
     if rc != 0:
         if rc > 0:
             raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no gpu'})")

@@ -56,6 +56,7 @@ class TrainEngine:
         self._graph = None
         self._static = None
         self._micro = 0
+        self.launches_per_step = 0   # kernels inside the captured graph (0 while running eagerly)
         self.fused = None
         if self.comm == "fused":
             from ..parallel.zero_fused import FusedZero
@@ -106,15 +107,26 @@ class TrainEngine:
         if self._graph is None:
             self.opt.stage_hyper(lr)
             self._static = (ids.clone(), labels.clone())
-            # warm-up on a side stream (allocator pools, lazy kernel attribute calls), then capture
+            # warm-up on a side stream (allocator pools, lazy kernel attribute calls), then capture; the
+            # warm-up is a real step, so the training state is put back afterwards
+            opt = self.opt
+            snap = [t.clone() for t in (self.flat.params, opt.master, opt.m, opt.v)]
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 self._step_impl(*self._static)
             torch.cuda.current_stream().wait_stream(s)
+            for dst, src in zip((self.flat.params, opt.master, opt.m, opt.v), snap):
+                dst.copy_(src)
+            self.flat.grads.zero_()
+            opt.step_count -= 1   # the warm-up step did not count
+            del snap
+            from ..ops import _lib
             self._graph = torch.cuda.CUDAGraph()
+            n0 = _lib.LAUNCHES[0]
             with torch.cuda.graph(self._graph):
                 self._static_loss = self._step_impl(*self._static)
+            self.launches_per_step = _lib.LAUNCHES[0] - n0
         self.opt.stage_hyper(lr)
         self._static[0].copy_(ids, non_blocking=True)
         self._static[1].copy_(labels, non_blocking=True)
