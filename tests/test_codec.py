@@ -1,0 +1,108 @@
+"""Block codec / registry / container: budget contract and round trips for all 105 formats, golden
+vectors produced by the reference's own codec for the wire-exact families, container round trip."""
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from transformers_fusion_b200.quant import codec
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "block_codec_reference.bin")
+
+
+def test_registry_names_and_bpw():
+    fm = codec.all_formats()
+    assert len(fm) == 105
+    assert fm[0][1:] == ("Q_1", 1.0) and fm[9][1:] == ("Q_32", 32.0) and fm[5][1] == "Q_8"
+    assert fm[38][1:] == ("Q_G_2", 2.625) and fm[98][1:] == ("Q_G_MX_3_5", 3.78125) and fm[104][1] == "Q_G_MX_24_5"
+    assert fm[20][1] == "Q_4_K_M" and fm[77][1:] == ("Q_6_5", 6.4375)
+    for i, name, _ in fm:
+        assert codec.parse_format(name) == i
+    assert codec.parse_format("q8") == 5 and codec.parse_format("qg4") == 40 and codec.parse_format("Q4_K_M") == 20
+    assert codec.parse_format("nonsense") == -1
+
+
+@pytest.mark.parametrize("n", [256, 1000, 37, 5])
+def test_budget_contract_and_roundtrip_all_formats(n):
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal(n) * 0.05).astype(np.float32)
+    for fmt, name, bpw in codec.all_formats():
+        payload = codec.quantize_block(fmt, w)
+        claimed = codec.claimed_bytes(fmt, n)
+        if name.startswith("Q_16") or name.startswith("Q_1") and bpw == 1.0:
+            assert len(payload) >= claimed or len(payload) == claimed
+        else:
+            assert len(payload) == claimed, (name, len(payload), claimed)
+        out = codec.dequantize_block(fmt, payload, n)
+        assert np.isfinite(out).all(), name
+        if fmt == 9:
+            assert np.array_equal(out, w)
+        if n >= 256:
+            nmse = float(((out - w) ** 2).sum() / (w ** 2).sum())
+            cap = 1.3 if bpw <= 1.5 else 0.5 if bpw < 3 else 0.12 if bpw < 4 else 0.03 if bpw < 6 else 4e-3 if bpw < 8 else 4e-4
+            assert nmse < cap, (name, nmse)
+
+
+def test_golden_vectors_from_reference_codec():
+    data = open(GOLD, "rb").read()
+    (count,) = struct.unpack_from("<I", data, 0)
+    off = 4
+    checked = 0
+    for _ in range(count):
+        fmt, n, ib, cb = struct.unpack_from("<4I", data, off)
+        off += 16
+        w = np.frombuffer(data, np.float32, n, off); off += 4 * n
+        idx = data[off:off + ib]; off += ib + cb
+        ref = np.frombuffer(data, np.float32, n, off); off += 4 * n
+        if not codec.is_wire_exact(fmt):
+            continue
+        out = codec.dequantize_block(fmt, idx, n)
+        assert np.array_equal(out.view(np.uint32), ref.view(np.uint32)), (codec.format_name(fmt), n)
+        # our encoder emits a stream of the same size whose decode is at least as close as the reference's
+        mine = codec.quantize_block(fmt, w)
+        assert len(mine) == len(idx), (codec.format_name(fmt), n, len(mine), len(idx))
+        e_ref = float(((ref - w) ** 2).sum()); e_me = float(((codec.dequantize_block(fmt, mine, n) - w) ** 2).sum())
+        assert e_me <= e_ref * 1.25 + 1e-12, (codec.format_name(fmt), n, e_me, e_ref)
+        checked += 1
+    assert checked >= 60
+
+
+def test_sha256_known_answers():
+    assert codec.sha256(b"abc").hex() == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+    assert codec.sha256(b"").hex() == "e3b0c44298fc1c149afbf4c8996fb92427ae41e4649b934ca495991b7852b855"
+    assert codec.sha256(b"a" * 1000).hex() == "41edece42d63e8d9bf515a9ba6932e1c20cbc9f5a5d134645adb5db1b9737ea3"
+
+
+def test_container_roundtrip_and_corruption(tmp_path):
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    cfg = TransformerConfig(vocab_size=300, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, ffn_hidden_size=96,
+                            max_seq_len=64)
+    m = DenseModel(cfg, dtype=torch.float32, seed=3)
+    p = tmp_path / "m.quant"
+    codec.save_model(m, p)
+    raw = open(p, "rb").read()
+    assert raw[:4] == b"QUA1" and struct.unpack_from("<I", raw, 12)[0] == 128
+    assert (tmp_path / "m.quant.idx").read_bytes()[:22] == b"TransFormers-FusionIDX"
+    m2 = codec.load_model(p)
+    for (n1, a), (n2, b) in zip(m.named_tensors(), m2.named_tensors()):
+        assert n1 == n2 and torch.equal(a, b)
+    # quantised save: 2-D tensors at 8 bits, norms exact
+    q = tmp_path / "m8.quant"
+    codec.save_model(m, q, "q8")
+    m3 = codec.load_model(q)
+    for (n1, a), (_, b) in zip(m.named_tensors(), m3.named_tensors()):
+        if a.dim() == 1:
+            assert torch.equal(a, b)
+        else:
+            assert (a - b).norm() / a.norm() < 0.03, n1
+    assert os.path.getsize(q) < 0.3 * os.path.getsize(p)
+    # truncated and corrupted files are rejected, not read out of bounds
+    (tmp_path / "bad.quant").write_bytes(raw[: len(raw) // 2])
+    with pytest.raises(ValueError):
+        codec.QuantReader(tmp_path / "bad.quant")
+    (tmp_path / "bad2.quant").write_bytes(b"QUA2" + raw[4:])
+    with pytest.raises(ValueError):
+        codec.QuantReader(tmp_path / "bad2.quant")

@@ -35,8 +35,43 @@ struct GemmParams {
   int act;       // 0 none, 1 relu, 2 gelu(tanh), 3 silu
   int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 atomic accumulate
   int splits, kb_per_split, tiles_m, tiles_n;
+  // grouped (mixture-of-experts) modes; expert segments are padded to multiples of 128 rows
+  //   1: rows of A / C grouped by expert, B = [E, ...] picked per 128-row tile (forward, data gradient)
+  //   2: reduction dimension grouped by expert, C = [E, M, N] (weight gradient of every expert in one launch)
+  int group_mode, num_experts;
+  const int* expert_of_mtile;   // mode 1: expert of every 128-row tile (-1 = padding, skipped)
+  const int* seg_start;         // mode 2: [E + 1] first row of every expert segment
+  long long c_expert_stride;    // mode 2: elements between the C matrices of consecutive experts
   int* status;
 };
+
+// Decodes work item w into tile coordinates / k-block range / expert.  Returns false when there is nothing to do.
+struct WorkItem {
+  int m0, n0, kb0, kb1, expert;  // n0 is the tile index along N (the kernel scales it by its BN)
+};
+__device__ __forceinline__ bool decode_work(const GemmParams& p, int w, int total_kb, WorkItem& it) {
+  if (p.group_mode == 2) {
+    const int tiles = p.tiles_m * p.tiles_n;
+    it.expert = w / tiles;
+    const int tile = w - it.expert * tiles;
+    it.m0 = (tile / p.tiles_n) * BM;
+    it.kb0 = p.seg_start[it.expert] / BK;
+    it.kb1 = p.seg_start[it.expert + 1] / BK;
+    it.n0 = tile % p.tiles_n;
+    return it.kb1 > it.kb0;
+  }
+  const int tile = w / p.splits, split = w - tile * p.splits;
+  it.m0 = (tile / p.tiles_n) * BM;
+  it.n0 = tile % p.tiles_n;
+  it.kb0 = split * p.kb_per_split;
+  it.kb1 = min(total_kb, it.kb0 + p.kb_per_split);
+  it.expert = 0;
+  if (p.group_mode == 1) {
+    it.expert = p.expert_of_mtile[tile / p.tiles_n];
+    if (it.expert < 0) return false;
+  }
+  return true;
+}
 
 template <int BN>
 struct SmemLayout {
@@ -101,7 +136,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   const int total_kb = (p.K + BK - 1) / BK;
-  const int num_work = p.tiles_m * p.tiles_n * p.splits;
+  const int num_work = p.tiles_m * p.tiles_n * (p.group_mode == 2 ? p.num_experts : p.splits);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -110,10 +145,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int tile = w / p.splits, split = w - tile * p.splits;
-        const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        WorkItem it;
+        if (!decode_work(p, w, total_kb, it)) continue;
+        const int m0 = it.m0, n0 = it.n0 * BN, kb0 = it.kb0, kb1 = it.kb1;
+        const int bz = p.group_mode == 1 ? it.expert : 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -131,10 +166,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, fb, m0 + j * 64, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tma_b, fb, k0, n0);
+            tma_load_3d(sb, &tma_b, fb, k0, n0, bz);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, fb, n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * 8192, &tma_b, fb, n0 + j * 64, k0, bz);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -160,9 +195,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t aphase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int tile = w / p.splits, split = w - tile * p.splits;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+        WorkItem it;
+        if (!decode_work(p, w, total_kb, it)) continue;
+        const int kb0 = it.kb0, kb1 = it.kb1;
         if (!mbar_wait(bar_tempty + abuf * 8, aphase ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + abuf * BN;
@@ -201,8 +236,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const bool vec_ok_res =
         p.residual && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
     for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
-      const int tile = w / p.splits;
-      const int m0 = (tile / p.tiles_n) * BM, n0 = (tile % p.tiles_n) * BN;
+      WorkItem it;
+      if (!decode_work(p, w, total_kb, it)) continue;
+      const int m0 = it.m0, n0 = it.n0 * BN;
+      const long long c_off = p.group_mode == 2 ? (long long)it.expert * p.c_expert_stride : 0;
       if (!mbar_wait_warp(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
@@ -265,7 +302,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
           }
         } else {
-          float* cp = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+          float* cp = reinterpret_cast<float*>(p.C) + c_off + (long long)row * p.ldc + col0;
           if (p.out_mode == 1) {
             if (full && vec_ok_f32) {
 #pragma unroll
@@ -331,25 +368,43 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
 
 }  // namespace tfb
 
-// C[M,N] (ldc) = act(alpha * A.B + bias) + residual.
-//   a_mn = 0: A is [M,K] with K contiguous (row pitch lda elements); a_mn = 1: A is stored [K,M], M contiguous.
-//   b_mn = 0: B is [N,K] with K contiguous (weight layout [out,in]);  b_mn = 1: B is stored [K,N], N contiguous.
-//   out_mode 0: bf16 store; 1: fp32 store; 2: fp32 atomic accumulate (C += ...), the only mode that allows split-K.
-//   max_ctas > 0 limits the persistent grid (leaves SMs free for a concurrent communication kernel).
-TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
-                          long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
-                          float alpha, int act, int out_mode, int max_ctas, int* status, void* stream) {
+struct TfbGemmGroup {
+  int mode;                    // 0 dense, 1 rows grouped (B has a leading expert dim), 2 reduction grouped (C has one)
+  int num_experts;
+  const int* expert_of_mtile;  // mode 1 (device)
+  const int* seg_start;        // mode 2 (device, [E + 1])
+  long long b_expert_stride;   // mode 1: elements between consecutive experts' B matrices
+  long long c_expert_stride;   // mode 2: elements between consecutive experts' C matrices
+};
+
+static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
+                     long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
+                     float alpha, int act, int out_mode, int max_ctas, const TfbGemmGroup* grp, int* status,
+                     void* stream) {
   using namespace tfb;
   if (M <= 0 || N <= 0 || K <= 0) return TFB_ERR_ARG;
   if (out_mode != 0 && (bias || residual || act)) return TFB_ERR_ARG;
-  const int BN = (N > 128) ? 256 : 128;
+  const int gmode = grp ? grp->mode : 0;
+  const int E = (gmode != 0) ? grp->num_experts : 1;
+  if (gmode == 2 && out_mode == 0) return TFB_ERR_ARG;
+  int BN = (N > 128) ? 256 : 128;
+  int sms = sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  {
+    // prefer the narrower tile when it fills the machine better (fewer idle CTAs in the last wave)
+    const long long tm = (M + BM - 1) / BM;
+    const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
+    if (BN == 256 && gmode != 2 && out_mode != 2 && t256 < sms && t128 > t256) BN = 128;
+  }
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, BM);
   else rc = make_tmap_2d(&ta, A, 2, M, K, lda * 2, 64, BK);
   if (rc) return rc;
-  if (!b_mn) rc = make_tmap_2d(&tb, B, 2, K, N, ldb * 2, BK, BN);
-  else rc = make_tmap_2d(&tb, B, 2, N, K, ldb * 2, 64, BK);
+  const int EB = gmode == 1 ? E : 1;
+  const unsigned long long bes = gmode == 1 ? (unsigned long long)grp->b_expert_stride * 2 : (unsigned long long)ldb * 2 * (b_mn ? K : N);
+  if (!b_mn) rc = make_tmap_3d(&tb, B, 2, K, N, EB, ldb * 2, bes, BK, BN, 1);
+  else rc = make_tmap_3d(&tb, B, 2, N, K, EB, ldb * 2, bes, 64, BK, 1);
   if (rc) return rc;
 
   GemmParams p;
@@ -362,12 +417,14 @@ TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  p.group_mode = gmode; p.num_experts = E;
+  p.expert_of_mtile = grp ? grp->expert_of_mtile : nullptr;
+  p.seg_start = grp ? grp->seg_start : nullptr;
+  p.c_expert_stride = grp ? grp->c_expert_stride : 0;
   const int total_kb = (K + BK - 1) / BK;
-  int sms = sm_count();
-  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   const int tiles = p.tiles_m * p.tiles_n;
   int splits = 1;
-  if (out_mode == 2 && tiles < sms) {
+  if (out_mode == 2 && gmode == 0 && tiles < sms) {
     splits = (sms + tiles - 1) / tiles;
     const int max_splits = (total_kb + 7) / 8;  // keep at least 8 k-blocks (512 of K) per split
     if (splits > max_splits) splits = max_splits;
@@ -375,7 +432,7 @@ TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
   }
   p.kb_per_split = (total_kb + splits - 1) / splits;
   p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
-  const long long work = (long long)tiles * p.splits;
+  const long long work = (long long)tiles * (gmode == 2 ? E : p.splits);
   const int grid = int(work < sms ? work : sms);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
@@ -394,4 +451,26 @@ TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B,
       default: return launch<true, true, 128>(ta, tb, p, grid, st);
     }
   }
+}
+
+// C[M,N] (ldc) = act(alpha * A.B + bias) + residual.
+//   a_mn = 0: A is [M,K] with K contiguous (row pitch lda elements); a_mn = 1: A is stored [K,M], M contiguous.
+//   b_mn = 0: B is [N,K] with K contiguous (weight layout [out,in]);  b_mn = 1: B is stored [K,N], N contiguous.
+//   out_mode 0: bf16 store; 1: fp32 store; 2: fp32 atomic accumulate (C += ...), the only mode that allows split-K.
+//   max_ctas > 0 limits the persistent grid (leaves SMs free for a concurrent communication kernel).
+TFB_API int tfb_gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
+                          long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
+                          float alpha, int act, int out_mode, int max_ctas, int* status, void* stream) {
+  return gemm_impl(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, bias, residual, ldr, alpha, act, out_mode, max_ctas,
+                   nullptr, status, stream);
+}
+
+// Grouped (mixture-of-experts) form; see TfbGemmGroup.  Mode 1: M counts the padded rows of all experts, B is
+// [E, N, K] (or [E, K, N] with b_mn).  Mode 2: K counts the padded rows, C is [E, M, N] fp32 (out_mode 1 or 2).
+TFB_API int tfb_gemm_bf16_grouped(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
+                                  void* C, long long ldc, int M, int N, int K, float alpha, int out_mode,
+                                  const TfbGemmGroup* grp, int* status, void* stream) {
+  if (!grp || grp->mode < 1 || grp->mode > 2 || grp->num_experts < 1) return TFB_ERR_ARG;
+  return gemm_impl(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, nullptr, nullptr, 0, alpha, 0, out_mode, 0, grp,
+                   status, stream);
 }

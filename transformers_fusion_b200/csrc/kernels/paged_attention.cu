@@ -1,0 +1,376 @@
+// Paged KV cache (16-token pages) with bf16 / fp8-e4m3 / 4-bit storage, and decode attention that
+// dequantises K and V on the fly.
+//
+// Storage per layer, per K or V ("pool"):
+//   KV_BF16 : [pages, 16, Hkv, D] bf16
+//   KV_FP8  : [pages, 16, Hkv, D] e4m3 bytes + scale fp32 [pages, 16, Hkv]       (amax / 448 per head row)
+//   KV_Q4   : [pages, 16, Hkv, D/2] bytes (low nibble = even element) + scale fp16 [pages, 16, Hkv, D/32]
+//             value = (nibble - 8) * scale, scale = amax / 7 per 32-element block
+//
+// kv_append   : quantise and scatter the K/V rows of new tokens into their page slots
+// paged_decode: one CTA per (sequence, kv head, split of the context).  The G = Hq / Hkv query heads
+//               that share the kv head are processed together.  Per 128-token tile: each thread scores
+//               one token against all G queries (K row dequantised in registers, queries in shared
+//               memory), the block updates the running max / sum, then each thread owns output
+//               dimensions and accumulates p * V over the tile with coalesced V reads.
+// paged_combine: merges the per-split partial results.
+//
+// Reference counterparts: PagedAttention::forward (src/inference/inference_paging.cpp:24-117, no length
+// mask), Q4KVCache 4-bit blocks (src/model/kv_cache_quant4.cpp:207-362), flash_decoding
+// (src/inference/inference_kv.cpp:141-205).
+#include <cuda_fp16.h>
+
+#include "tfb_host.h"
+#include "tfb_ptx.cuh"
+
+namespace tfb {
+
+enum { KV_BF16 = 0, KV_FP8 = 1, KV_Q4 = 2 };
+constexpr int PAGE = 16;
+
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  __half2_raw h2;
+  asm("{\n\t.reg .b16 t;\n\tmov.b16 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(*reinterpret_cast<uint32_t*>(&h2)) : "h"(uint16_t(b)));
+  return __half2float(__half(__half_raw{h2.x}));
+}
+__device__ __forceinline__ uint8_t f32_to_e4m3_sat(float x) {
+  uint16_t r;
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %1, %2;\n\tmov.b16 %0, t;\n\t}" : "=h"(r) : "f"(0.f), "f"(x));
+  return uint8_t(r & 0xff);
+}
+
+struct KvPool {
+  void* data;     // packed values
+  void* scale;    // fp32 (fp8) or fp16 (q4) scales, null for bf16
+};
+
+// ------------------------------------------------------------------------------------------------
+// append: src rows are [T, ld] bf16 with K head h at column k_col0 + h*D, V at v_col0 + h*D
+// one warp per (token, kv head); slot_mapping[t] = page * 16 + slot (negative = skip)
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__device__ __forceinline__ void store_row(KvPool pool, long long slot, int h, int Hkv, int D, const float* v, int n,
+                                          int lane) {
+  // each lane holds n = D/32 consecutive elements starting at lane * n
+  const long long row = slot * Hkv + h;
+  if (MODE == KV_BF16) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(pool.data) + row * D + lane * n;
+    for (int i = 0; i < n; ++i) dst[i] = __float2bfloat16(v[i]);
+  } else if (MODE == KV_FP8) {
+    float amax = 0.f;
+    for (int i = 0; i < n; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = amax > 0.f ? amax / 448.f : 1.f;
+    if (lane == 0) static_cast<float*>(pool.scale)[row] = s;
+    uint8_t* dst = static_cast<uint8_t*>(pool.data) + row * D + lane * n;
+    for (int i = 0; i < n; ++i) dst[i] = f32_to_e4m3_sat(v[i] / s);
+  } else {
+    // 32-element blocks: the lanes that share a block are 32 / n consecutive lanes
+    const int lanes_per_block = 32 / n;
+    float amax = 0.f;
+    for (int i = 0; i < n; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    for (int o = lanes_per_block >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = amax > 0.f ? amax / 7.f : 1.f;
+    const float sh = __half2float(__float2half(s));  // the decoder sees the fp16-rounded scale
+    if ((lane % lanes_per_block) == 0)
+      static_cast<__half*>(pool.scale)[row * (D / 32) + (lane * n) / 32] = __float2half(s);
+    uint8_t* dst = static_cast<uint8_t*>(pool.data) + row * (D / 2) + (lane * n) / 2;
+    for (int i = 0; i < n; i += 2) {
+      int a = __float2int_rn(v[i] / sh) + 8, b = __float2int_rn(v[i + 1] / sh) + 8;
+      a = min(max(a, 0), 15);
+      b = min(max(b, 0), 15);
+      dst[i / 2] = uint8_t(a | (b << 4));
+    }
+  }
+}
+
+template <int MODE>
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ src, long long ld, int k_col0, int v_col0,
+                                 const long long* __restrict__ slot_mapping, KvPool kpool, KvPool vpool, int T,
+                                 int Hkv, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (w >= (long long)T * Hkv) return;
+  const int h = int(w % Hkv);
+  const long long t = w / Hkv;
+  const long long slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int n = D / 32;  // 2 (D=64) or 4 (D=128)
+  float kv[4], vv[4];
+  const __nv_bfloat16* kp = src + t * ld + k_col0 + h * D + lane * n;
+  const __nv_bfloat16* vp = src + t * ld + v_col0 + h * D + lane * n;
+  for (int i = 0; i < n; ++i) {
+    kv[i] = __bfloat162float(kp[i]);
+    vv[i] = __bfloat162float(vp[i]);
+  }
+  store_row<MODE>(kpool, slot, h, Hkv, D, kv, n, lane);
+  store_row<MODE>(vpool, slot, h, Hkv, D, vv, n, lane);
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode
+// ------------------------------------------------------------------------------------------------
+template <int MODE, int D>
+__device__ __forceinline__ void load_row(const KvPool& pool, long long row, float* out) {
+  // whole row (D values) into registers of one thread
+  if (MODE == KV_BF16) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(pool.data) + row * D);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const uint4 u = p[i];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(w[j]);
+        out[i * 8 + 2 * j] = f.x;
+        out[i * 8 + 2 * j + 1] = f.y;
+      }
+    }
+  } else if (MODE == KV_FP8) {
+    const float s = static_cast<const float*>(pool.scale)[row];
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * D);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      const uint4 u = p[i];
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) out[i * 16 + j] = e4m3_to_f32(b[j]) * s;
+    }
+  } else {
+    const __half* sp = static_cast<const __half*>(pool.scale) + row * (D / 32);
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * (D / 2));
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const float s = __half2float(sp[i]);
+      const uint4 u = p[i];
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        out[i * 32 + 2 * j] = float(int(b[j] & 15) - 8) * s;
+        out[i * 32 + 2 * j + 1] = float(int(b[j] >> 4) - 8) * s;
+      }
+    }
+  }
+}
+
+template <int MODE, int D>
+__device__ __forceinline__ float load_elem(const KvPool& pool, long long row, int d) {
+  if (MODE == KV_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(pool.data)[row * D + d]);
+  if (MODE == KV_FP8)
+    return e4m3_to_f32(static_cast<const uint8_t*>(pool.data)[row * D + d]) * static_cast<const float*>(pool.scale)[row];
+  const uint8_t b = static_cast<const uint8_t*>(pool.data)[row * (D / 2) + d / 2];
+  const float s = __half2float(static_cast<const __half*>(pool.scale)[row * (D / 32) + d / 32]);
+  return float(int((d & 1) ? (b >> 4) : (b & 15)) - 8) * s;
+}
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_TILE = 128;
+constexpr int MAX_G = 8;
+
+// partial outputs: acc [B, Hq, splits, D] fp32 (unnormalised), ml [B, Hq, splits, 2] (max, sum)
+template <int MODE, int D, int G>
+__global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, long long ldq, KvPool kpool, KvPool vpool,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, float* __restrict__ acc_out,
+    float* __restrict__ ml_out, int Hq, int Hkv, int splits, float scale) {
+  __shared__ float sq[G][D];
+  __shared__ float sp[G][DEC_TILE];
+  __shared__ float red[G][DEC_THREADS / 32];
+  const int b = blockIdx.x, hk = blockIdx.y, sp_idx = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int len = seq_lens[b];
+  const int per = ((len + splits - 1) / splits + PAGE - 1) / PAGE * PAGE;
+  const int t_begin = sp_idx * per, t_end = min(len, t_begin + per);
+  for (int i = tid; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    sq[g][d] = __bfloat162float(q[(long long)b * ldq + (hk * G + g) * D + d]) * scale;
+  }
+  __syncthreads();
+  float m[G], l[G];
+  constexpr int DPT = (D + DEC_THREADS - 1) / DEC_THREADS;  // output dims per thread (1 for D <= 128)
+  float acc[G][DPT];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < DPT; ++j) acc[g][j] = 0.f;
+  }
+  const int* bt = block_table + (long long)b * max_pages;
+  for (int t0 = t_begin; t0 < t_end; t0 += DEC_TILE) {
+    // ---- scores: thread tid <-> token t0 + tid ----
+    const int t = t0 + tid;
+    float s[G];
+    if (t < t_end) {
+      const long long row = ((long long)bt[t / PAGE] * PAGE + (t % PAGE)) * Hkv + hk;
+      float kr[D];
+      load_row<MODE, D>(kpool, row, kr);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float a = 0.f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) a = fmaf(kr[d], sq[g][d], a);
+        s[g] = a;
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < G; ++g) s[g] = -INFINITY;
+    }
+    // ---- block max per head ----
+    float tile_m[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float v = s[g];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      if (lane == 0) red[g][warp] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float v = red[g][0];
+#pragma unroll
+      for (int w2 = 1; w2 < DEC_THREADS / 32; ++w2) v = fmaxf(v, red[g][w2]);
+      tile_m[g] = fmaxf(m[g], v);
+    }
+    __syncthreads();
+    float alpha[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float p = (t < t_end) ? __expf(s[g] - tile_m[g]) : 0.f;
+      sp[g][tid] = p;
+      alpha[g] = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - tile_m[g]);
+      float v = p;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) red[g][warp] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float v = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < DEC_THREADS / 32; ++w2) v += red[g][w2];
+      l[g] = l[g] * alpha[g] + v;
+      m[g] = tile_m[g];
+#pragma unroll
+      for (int j = 0; j < DPT; ++j) acc[g][j] *= alpha[g];
+    }
+    // ---- P.V: thread tid <-> output dims tid + j * DEC_THREADS ----
+    const int nt = min(DEC_TILE, t_end - t0);
+    for (int tt = 0; tt < nt; ++tt) {
+      const int tk = t0 + tt;
+      const long long row = ((long long)bt[tk / PAGE] * PAGE + (tk % PAGE)) * Hkv + hk;
+#pragma unroll
+      for (int j = 0; j < DPT; ++j) {
+        const int d = tid + j * DEC_THREADS;
+        if (d < D) {
+          const float v = load_elem<MODE, D>(vpool, row, d);
+#pragma unroll
+          for (int g = 0; g < G; ++g) acc[g][j] = fmaf(sp[g][tt], v, acc[g][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
+#pragma unroll
+    for (int j = 0; j < DPT; ++j) {
+      const int d = tid + j * DEC_THREADS;
+      if (d < D) acc_out[base * D + d] = acc[g][j];
+    }
+    if (tid == 0) {
+      ml_out[base * 2] = m[g];
+      ml_out[base * 2 + 1] = l[g];
+    }
+  }
+}
+
+// o[b, h, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
+__global__ void paged_combine_kernel(const float* __restrict__ acc, const float* __restrict__ ml,
+                                     __nv_bfloat16* __restrict__ o, long long ldo, int Hq, int D, int splits) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const long long base = ((long long)b * Hq + h) * splits;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[(base + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = ml[(base + s) * 2];
+    if (ms != -INFINITY) L += ml[(base + s) * 2 + 1] * __expf(ms - M);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = ml[(base + s) * 2];
+      if (ms != -INFINITY) v += acc[(base + s) * D + d] * __expf(ms - M);
+    }
+    o[(long long)b * ldo + h * D + d] = __float2bfloat16(L > 0.f ? v / L : 0.f);
+  }
+}
+
+template <int MODE, int D>
+static int launch_decode_g(int G, dim3 grid, cudaStream_t st, const __nv_bfloat16* q, long long ldq, KvPool k, KvPool v,
+                           const int* bt, int max_pages, const int* lens, float* acc, float* ml, int Hq, int Hkv,
+                           int splits, float scale) {
+#define TFB_CASE(GG)                                                                                              \
+  case GG:                                                                                                        \
+    paged_decode_kernel<MODE, D, GG><<<grid, DEC_THREADS, 0, st>>>(q, ldq, k, v, bt, max_pages, lens, acc, ml, Hq, \
+                                                                   Hkv, splits, scale);                           \
+    break;
+  switch (G) {
+    TFB_CASE(1) TFB_CASE(2) TFB_CASE(4) TFB_CASE(8)
+    default: return TFB_ERR_ARG;
+  }
+#undef TFB_CASE
+  return int(cudaGetLastError());
+}
+
+}  // namespace tfb
+
+using namespace tfb;
+
+TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0, const long long* slot_mapping,
+                          void* k_data, void* k_scale, void* v_data, void* v_scale, int T, int Hkv, int D, int mode,
+                          void* stream) {
+  if (D != 64 && D != 128) return TFB_ERR_ARG;
+  KvPool kp{k_data, k_scale}, vp{v_data, v_scale};
+  const long long warps = (long long)T * Hkv;
+  const unsigned blocks = unsigned((warps * 32 + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto s = static_cast<const __nv_bfloat16*>(src);
+  if (mode == KV_BF16) kv_append_kernel<KV_BF16><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  else if (mode == KV_FP8) kv_append_kernel<KV_FP8><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  else if (mode == KV_Q4) kv_append_kernel<KV_Q4><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  else return TFB_ERR_ARG;
+  return int(cudaGetLastError());
+}
+
+// q: [B, ldq] bf16 (query head h at column h*D).  acc_ws: fp32 [B*Hq*splits*D], ml_ws: fp32 [B*Hq*splits*2].
+TFB_API int tfb_paged_decode(const void* q, long long ldq, void* k_data, void* k_scale, void* v_data, void* v_scale,
+                             const int* block_table, int max_pages, const int* seq_lens, void* o, long long ldo,
+                             float* acc_ws, float* ml_ws, int B, int Hq, int Hkv, int D, int splits, int mode,
+                             float scale, void* stream) {
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || splits < 1) return TFB_ERR_ARG;
+  const int G = Hq / Hkv;
+  KvPool kp{k_data, k_scale}, vp{v_data, v_scale};
+  dim3 grid(B, Hkv, splits);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto Q = static_cast<const __nv_bfloat16*>(q);
+  int rc;
+#define TFB_GO(MODE)                                                                                                  \
+  rc = (D == 64) ? launch_decode_g<MODE, 64>(G, grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,   \
+                                             ml_ws, Hq, Hkv, splits, scale)                                           \
+                 : launch_decode_g<MODE, 128>(G, grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,  \
+                                              ml_ws, Hq, Hkv, splits, scale)
+  if (mode == KV_BF16) { TFB_GO(KV_BF16); }
+  else if (mode == KV_FP8) { TFB_GO(KV_FP8); }
+  else if (mode == KV_Q4) { TFB_GO(KV_Q4); }
+  else return TFB_ERR_ARG;
+#undef TFB_GO
+  if (rc) return rc;
+  paged_combine_kernel<<<dim3(B, Hq), 128, 0, st>>>(acc_ws, ml_ws, static_cast<__nv_bfloat16*>(o), ldo, Hq, D, splits);
+  return int(cudaGetLastError());
+}

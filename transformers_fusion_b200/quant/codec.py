@@ -1,0 +1,223 @@
+"""Python binding of ``libtfb_codec`` (format registry, block codec, ``.quant`` container, ``.opt``).
+
+``Format`` ids, names and wire bits-per-weight follow the reference enum (include/quant/types.h:22-277).
+``save_model`` / ``load_model`` use the reference's tensor names and block sizes (32768-weight Q_32
+blocks for full-precision saves, 256-weight blocks for quantised ones: src/model/model.cpp:168-331)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import torch
+
+_LIB = None
+FORMAT_COUNT = 105
+Q_32 = 9
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        p = Path(__file__).resolve().parent.parent / "lib" / "libtfb_codec.so"
+        if not p.exists():
+            from .. import build
+            build.build_host_lib("tfb_codec", "codec")
+        L = C.CDLL(str(p))
+        L.tfb_format_name.restype = C.c_char_p
+        L.tfb_format_name.argtypes = [C.c_int]
+        L.tfb_format_parse.argtypes = [C.c_char_p]
+        L.tfb_format_bpw.restype = C.c_double
+        L.tfb_format_bpw.argtypes = [C.c_int]
+        L.tfb_block_claimed_bytes.restype = C.c_size_t
+        L.tfb_block_claimed_bytes.argtypes = [C.c_int, C.c_uint32]
+        L.tfb_quantize_block.restype = C.c_long
+        L.tfb_quantize_block.argtypes = [C.c_int, C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t]
+        L.tfb_dequantize_block.restype = None
+        L.tfb_dequantize_block.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p]
+        L.tfb_sha256.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        L.tfb_reader_open.restype = C.c_void_p
+        L.tfb_reader_open.argtypes = [C.c_char_p]
+        for n in ("tfb_reader_valid", "tfb_reader_version", "tfb_reader_flags", "tfb_reader_num_tensors",
+                  "tfb_reader_num_blocks"):
+            getattr(L, n).argtypes = [C.c_void_p]
+        L.tfb_reader_close.argtypes = [C.c_void_p]
+        L.tfb_reader_config.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32]
+        L.tfb_reader_tensor_name.restype = C.c_char_p
+        L.tfb_reader_tensor_name.argtypes = [C.c_void_p, C.c_uint32]
+        L.tfb_reader_tensor_numel.restype = C.c_longlong
+        L.tfb_reader_tensor_numel.argtypes = [C.c_void_p, C.c_char_p]
+        L.tfb_reader_tensor_format.argtypes = [C.c_void_p, C.c_char_p]
+        L.tfb_reader_read_tensor.restype = C.c_longlong
+        L.tfb_reader_read_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong]
+        L.tfb_writer_open.restype = C.c_void_p
+        L.tfb_writer_open.argtypes = [C.c_char_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32]
+        L.tfb_writer_add_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong, C.c_int, C.c_uint32]
+        L.tfb_writer_close.argtypes = [C.c_void_p, C.c_int]
+        _LIB = L
+    return _LIB
+
+
+# ---------------------------------------------------------------------------------------------- registry
+def format_name(fmt: int) -> str:
+    n = lib().tfb_format_name(fmt)
+    return n.decode() if n else "unknown"
+
+
+def parse_format(name: str) -> int:
+    return lib().tfb_format_parse(name.encode())
+
+
+def format_bpw(fmt: int) -> float:
+    return lib().tfb_format_bpw(fmt)
+
+
+def is_wire_exact(fmt: int) -> bool:
+    return bool(lib().tfb_format_is_wire_exact(fmt))
+
+
+def claimed_bytes(fmt: int, n: int) -> int:
+    return lib().tfb_block_claimed_bytes(fmt, n)
+
+
+def all_formats():
+    return [(i, format_name(i), format_bpw(i)) for i in range(FORMAT_COUNT)]
+
+
+# ---------------------------------------------------------------------------------------------- blocks
+def quantize_block(fmt: int, w) -> bytes:
+    a = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
+    cap = max(claimed_bytes(fmt, a.size), a.size * 4) + 16
+    buf = (C.c_uint8 * cap)()
+    got = lib().tfb_quantize_block(fmt, a.ctypes.data, a.size, buf, cap)
+    if got < 0:
+        raise ValueError(f"quantize_block({format_name(fmt)}, n={a.size}) failed")
+    return bytes(buf[:got])
+
+
+def dequantize_block(fmt: int, payload: bytes, n: int) -> np.ndarray:
+    out = np.zeros(n, dtype=np.float32)
+    b = (C.c_uint8 * max(1, len(payload))).from_buffer_copy(payload or b"\0")
+    lib().tfb_dequantize_block(fmt, b, len(payload), None, 0, n, out.ctypes.data)
+    return out
+
+
+def sha256(data: bytes) -> bytes:
+    out = (C.c_uint8 * 32)()
+    lib().tfb_sha256(data, len(data), out)
+    return bytes(out)
+
+
+# ---------------------------------------------------------------------------------------------- container
+class QuantReader:
+    def __init__(self, path):
+        self._h = lib().tfb_reader_open(str(path).encode())
+        if not self._h or not lib().tfb_reader_valid(self._h):
+            if self._h:
+                lib().tfb_reader_close(self._h)
+                self._h = None
+            raise ValueError(f"{path}: not a valid .quant container")
+
+    def close(self):
+        if self._h:
+            lib().tfb_reader_close(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def version(self):
+        return lib().tfb_reader_version(self._h)
+
+    def config_bytes(self) -> bytes:
+        n = lib().tfb_reader_config(self._h, None, 0)
+        buf = (C.c_uint8 * max(1, n))()
+        lib().tfb_reader_config(self._h, buf, n)
+        return bytes(buf[:n])
+
+    def tensor_names(self):
+        return [lib().tfb_reader_tensor_name(self._h, i).decode() for i in range(lib().tfb_reader_num_tensors(self._h))]
+
+    def num_blocks(self):
+        return lib().tfb_reader_num_blocks(self._h)
+
+    def tensor_format(self, name) -> int:
+        return lib().tfb_reader_tensor_format(self._h, name.encode())
+
+    def read_tensor(self, name) -> torch.Tensor:
+        n = lib().tfb_reader_tensor_numel(self._h, name.encode())
+        if n < 0:
+            raise KeyError(name)
+        out = np.empty(n, dtype=np.float32)
+        got = lib().tfb_reader_read_tensor(self._h, name.encode(), out.ctypes.data, n)
+        if got != n:
+            raise ValueError(f"{name}: corrupt blocks")
+        return torch.from_numpy(out)
+
+
+class QuantWriter:
+    def __init__(self, path, config: bytes = b"", version: int = 1, flags: int = 0):
+        self._h = lib().tfb_writer_open(str(path).encode(), version, flags, config, len(config))
+
+    def add_tensor(self, name: str, t: torch.Tensor, fmt: int = Q_32, block: int | None = None):
+        a = t.detach().float().cpu().contiguous().numpy().reshape(-1)
+        if block is None:
+            block = 32768 if fmt == Q_32 else 256
+        if lib().tfb_writer_add_tensor(self._h, name.encode(), a.ctypes.data, a.size, fmt, block) != 0:
+            raise ValueError(f"add_tensor({name}) failed")
+
+    def close(self, write_idx=True):
+        h, self._h = self._h, None
+        if h and lib().tfb_writer_close(h, int(write_idx)) != 0:
+            raise IOError("writing .quant failed")
+
+
+def save_model(model, path, fmt: int | str = Q_32, per_layer: dict | None = None):
+    """DenseModel / MoEModel -> .quant with the reference tensor names.  ``per_layer`` maps a name
+    substring to a format (the ``--per-layer name=fmt`` rule of quant_quantize)."""
+    if isinstance(fmt, str):
+        fmt = parse_format(fmt)
+    w = QuantWriter(path, model.cfg.to_bytes())
+    for name, t in model.named_tensors():
+        f = fmt
+        for key, pf in (per_layer or {}).items():
+            if key in name:
+                f = parse_format(pf) if isinstance(pf, str) else pf
+        if t.dim() < 2 and f != Q_32:
+            f = Q_32   # norms and biases stay exact
+        w.add_tensor(name, t, f)
+    w.close()
+
+
+def load_state(path):
+    """(config bytes, {name: fp32 tensor}) of a .quant file."""
+    with QuantReader(path) as r:
+        return r.config_bytes(), {n: r.read_tensor(n) for n in r.tensor_names()}
+
+
+def load_model(path, device="cpu", dtype=torch.float32, model_cls=None, strict=True, **cfg_extra):
+    """Rebuild a DenseModel from a .quant file (shapes come from the config; names must match)."""
+    from ..models.config import TransformerConfig
+    from ..models.dense import DenseModel
+    raw, tensors = load_state(path)
+    cfg = TransformerConfig.from_bytes(raw, **cfg_extra)
+    if "lm_head.weight" not in tensors:
+        cfg.tie_embeddings = True
+    model = (model_cls or DenseModel)(cfg, device=device, dtype=dtype, seed=None)
+    with torch.no_grad():
+        for name, dst in model.named_tensors():
+            if name not in tensors:
+                if strict:
+                    raise KeyError(f"{path}: tensor {name} missing")
+                continue
+            src = tensors[name]
+            if src.numel() != dst.numel():
+                raise ValueError(f"{name}: {src.numel()} weights in file, {dst.numel()} expected")
+            dst.copy_(src.view(dst.shape).to(dst.dtype))
+    return model
