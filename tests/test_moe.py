@@ -61,8 +61,8 @@ def test_moe_gpu_matches_cpu():
     g = torch.randn(T, H).bfloat16()
     outs = []
     for dev in ("cpu", "cuda"):
-        xx = x.to(dev).requires_grad_(True)
-        ll = logits.to(dev).requires_grad_(True)
+        xx = x.detach().clone().to(dev).requires_grad_(True)
+        ll = logits.detach().clone().to(dev).requires_grad_(True)
         gup, dnp = torch.nn.Parameter(gu.to(dev)), torch.nn.Parameter(dn.to(dev))
         y, aux, idx = moe.moe_ffn(xx, ll, gup, dnp, k, True, "silu", 0.01, 0.001)
         ((y.float() * g.to(dev).float()).sum() + aux).backward()

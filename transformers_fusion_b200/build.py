@@ -91,7 +91,7 @@ def build_host_lib(name: str, subdir: str, force=False, extra_libs=()) -> Path |
     hdrs = list(d.glob("*.h")) + list(d.glob("*.hpp"))
     OBJ.mkdir(parents=True, exist_ok=True)
     jobs, objs = [], []
-    cxx = os.environ.get("CXX", "g++")
+    cxx = os.environ.get("TFB_CXX", "g++")  # not $CXX: a toolchain with a static libstdc++ would clash with torch's
     for s in srcs:
         o = OBJ / f"{subdir}_{s.stem}.o"
         objs.append(o)
@@ -112,7 +112,7 @@ def build_tools(force=False):
         return out
     bind = LIB / "bin"
     bind.mkdir(parents=True, exist_ok=True)
-    cxx = os.environ.get("CXX", "g++")
+    cxx = os.environ.get("TFB_CXX", "g++")  # not $CXX: a toolchain with a static libstdc++ would clash with torch's
     for s in sorted(d.glob("*.cpp")):
         exe = bind / s.stem
         deps = [s] + list((CSRC / "codec").glob("*.h")) + list((CSRC / "serve").glob("*.h")) + \

@@ -1,0 +1,370 @@
+"""Inference engine: paged KV cache, continuous batching, prefix reuse, priority scheduling, streaming.
+
+One ``step()`` = admit waiting requests while pages are available (prefill each prompt with the
+tcgen05 flash-attention kernel and scatter its K/V into pages, quantised on the way), then ONE decode
+token for every running sequence in a single batched pass (GEMMs with M = batch, RoPE at per-sequence
+positions, append to pages, paged decode attention with fused KV dequantisation, sampling kernel).
+Finished sequences release their pages; a prefix cache lets requests that share a prompt prefix (whole
+pages) reuse the pages instead of recomputing them.
+
+Reference counterparts: ContinuousBatching / RequestScheduler (priority desc, deadline asc) /
+PrefixCache / PagedAttention (src/inference/inference_paging.cpp:24-285, inference_kv.cpp:20-205),
+Generator / StreamingGenerator events START / TOKEN / COMPLETE / STOP (src/inference/generator.cpp),
+engine::InferenceEngine generate / generate_with_stats / generate_stream / generate_batch
+(engines/inference/inference.h).
+"""
+from __future__ import annotations
+
+import heapq
+import itertools
+import math
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..models.dense import _norm_fwd
+from ..ops import functional as F
+from .kv_cache import PAGE, PagedKVCache
+from .sampler import SamplerConfig, sample
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 64
+    num_pages: int = 4096
+    kv_mode: str = "bf16"          # bf16 | fp8 | q4
+    max_seq_len: int = 0           # 0 -> model config
+    enable_prefix_cache: bool = True
+    seed: int = 42
+
+
+@dataclass
+class Request:
+    tokens: List[int]
+    max_tokens: int = 64
+    sampling: SamplerConfig = field(default_factory=SamplerConfig)
+    id: int = 0
+    priority: int = 0
+    deadline: float = float("inf")
+    stop_ids: tuple = ()
+    on_token: Optional[Callable[[int], None]] = None
+    # runtime state
+    out: List[int] = field(default_factory=list)
+    pages: List[int] = field(default_factory=list)
+    pos: int = 0
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+    finished: bool = False
+
+
+@dataclass
+class InferenceStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    ttft_ms: float = 0.0
+    tokens_per_sec: float = 0.0
+    prefix_hit_tokens: int = 0
+
+
+class PrefixCache:
+    """Maps the hash of every whole-page token prefix to the page that holds its K/V."""
+
+    def __init__(self, allocator):
+        self.alloc = allocator
+        self.table: Dict[int, int] = {}
+
+    @staticmethod
+    def _key(tokens, n):
+        return hash(tuple(tokens[:n]))
+
+    def lookup(self, tokens):
+        pages = []
+        n = PAGE
+        while n <= len(tokens) - 1:   # at least one token must remain to produce logits
+            p = self.table.get(self._key(tokens, n))
+            if p is None or self.alloc.refs[p] == 0:
+                break
+            pages.append(p)
+            n += PAGE
+        for p in pages:
+            self.alloc.share(p)
+        return pages
+
+    def insert(self, tokens, pages):
+        for i, p in enumerate(pages):
+            n = (i + 1) * PAGE
+            if n > len(tokens):
+                break
+            k = self._key(tokens, n)
+            if k not in self.table:
+                self.table[k] = p
+                self.alloc.share(p)    # the cache holds its own reference
+
+    def evict_all(self):
+        for p in self.table.values():
+            self.alloc.release(p)
+        self.table.clear()
+
+
+class InferenceEngine:
+    def __init__(self, model, tokenizer=None, cfg: EngineConfig = EngineConfig()):
+        self.model, self.tok, self.cfg = model, tokenizer, cfg
+        mc = model.cfg
+        self.device = model.tok_embeddings.device
+        self.max_len = cfg.max_seq_len or mc.max_seq_len
+        self.cache = PagedKVCache(mc.num_layers, cfg.num_pages, mc.num_kv_heads, mc.head_dim, cfg.kv_mode, self.device)
+        self.prefix = PrefixCache(self.cache.allocator) if cfg.enable_prefix_cache else None
+        self.waiting: list = []
+        self.running: List[Request] = []
+        self._ids = itertools.count(1)
+        self._step = 0
+        self.stats = InferenceStats()
+        self.max_pages = (self.max_len + PAGE - 1) // PAGE
+
+    # ------------------------------------------------------------------ request management
+    def add_request(self, tokens, max_tokens=64, sampling: Optional[SamplerConfig] = None, priority=0,
+                    deadline=float("inf"), stop_ids=(), on_token=None) -> Request:
+        r = Request(list(tokens), max_tokens, sampling or SamplerConfig(), next(self._ids), priority, deadline,
+                    tuple(stop_ids), on_token)
+        r.t_submit = time.perf_counter()
+        heapq.heappush(self.waiting, (-priority, deadline, r.id, r))   # priority desc, deadline asc, FIFO
+        return r
+
+    def has_pending(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _release(self, r: Request):
+        for p in r.pages:
+            self.cache.allocator.release(p)
+        r.pages = []
+
+    # ------------------------------------------------------------------ model passes
+    def _layers_prefill(self, ids, pos0, r: Request):
+        """Prompt tokens ids[pos0:] of one sequence; K/V of all of them go to the pages.  Returns the
+        hidden state of the last token.  (Prefix pages already hold positions < pos0.)"""
+        m, mc = self.model, self.model.cfg
+        dev = self.device
+        Hq, Hkv, D = mc.num_heads, mc.num_kv_heads, mc.head_dim
+        S = len(ids) - pos0
+        t = torch.tensor(ids[pos0:], dtype=torch.int64, device=dev)
+        h = F.embedding_fwd(t, m.tok_embeddings.data, None, 0)
+        if m.pos_embeddings is not None:
+            h = h + m.pos_embeddings.data[pos0:pos0 + S]
+        rope = m.rope(dev)
+        positions = torch.arange(pos0, pos0 + S, dtype=torch.int32, device=dev)
+        slots = torch.tensor([r.pages[p // PAGE] * PAGE + p % PAGE for p in range(pos0, pos0 + S)], dtype=torch.int64,
+                             device=dev)
+        for li, w in enumerate(m.layers):
+            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
+            qkv = F.gemm(a, w.qkv.data, bias=w.qkv_bias)
+            if rope is not None:
+                F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S, positions=positions)
+            self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
+            if pos0 == 0:
+                o, _ = F.attn_fwd(qkv, qkv, qkv, 1, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
+            else:
+                # suffix after a cached prefix: every new token attends over the pages (prefix + the
+                # rows just appended), one decode-style query per token
+                bt = torch.tensor([r.pages + [0] * (self.max_pages - len(r.pages))], dtype=torch.int32,
+                                  device=dev).repeat(S, 1)
+                lens = (positions + 1).to(torch.int32)
+                o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), bt, lens, Hq)
+            if mc.use_parallel_residual:
+                attn = F.gemm(o, w.o.data, bias=w.o_bias)
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                base = h
+            else:
+                base = F.gemm(o, w.o.data, bias=w.o_bias, residual=h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
+            gu = F.gemm(f, w.gate_up.data, bias=w.gate_up_bias)
+            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
+            h = F.gemm(act, w.down.data, bias=w.down_bias, residual=base)
+            if mc.use_parallel_residual:
+                h = h + attn
+        return h[-1:]
+
+    def _layers_decode(self, tokens, positions, block_table, slots):
+        m, mc = self.model, self.model.cfg
+        Hq, Hkv, D = mc.num_heads, mc.num_kv_heads, mc.head_dim
+        B = tokens.shape[0]
+        h = F.embedding_fwd(tokens, m.tok_embeddings.data, None, 0)
+        if m.pos_embeddings is not None:
+            h = h + m.pos_embeddings.data[positions.long()]
+        rope = m.rope(self.device)
+        lens = (positions + 1).to(torch.int32)
+        for li, w in enumerate(m.layers):
+            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
+            qkv = F.gemm(a, w.qkv.data, bias=w.qkv_bias)
+            if rope is not None:
+                F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, 1, positions=positions)
+            self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
+            o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), block_table, lens, Hq)
+            if mc.use_parallel_residual:
+                attn = F.gemm(o, w.o.data, bias=w.o_bias)
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                base = h
+            else:
+                base = F.gemm(o, w.o.data, bias=w.o_bias, residual=h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
+            gu = F.gemm(f, w.gate_up.data, bias=w.gate_up_bias)
+            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
+            h = F.gemm(act, w.down.data, bias=w.down_bias, residual=base)
+            if mc.use_parallel_residual:
+                h = h + attn
+        return h
+
+    def _logits(self, h):
+        m = self.model
+        f, _ = _norm_fwd(m.cfg, h, m.norm, m.norm_bias)
+        return F.gemm(f, m.lm_head.data)
+
+    def _sample(self, logits, reqs):
+        dev = logits.device
+        t = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
+        k = torch.tensor([0 if (r.sampling.reference_rule and r.sampling.top_p < 1) else r.sampling.top_k for r in reqs],
+                         dtype=torch.int32, device=dev)
+        p = torch.tensor([r.sampling.top_p for r in reqs], dtype=torch.float32, device=dev)
+        rp = torch.tensor([r.sampling.repetition_penalty for r in reqs], dtype=torch.float32, device=dev)
+        hist = None
+        if any(r.sampling.repetition_penalty != 1.0 for r in reqs):
+            n = max(len(r.tokens) + len(r.out) for r in reqs)
+            hist = torch.full((len(reqs), n), -1, dtype=torch.int32)
+            for i, r in enumerate(reqs):
+                seq = r.tokens + r.out
+                hist[i, :len(seq)] = torch.tensor(seq, dtype=torch.int32)
+            hist = hist.to(dev)
+        self._step += 1
+        return sample(logits, t, k, p, rp, hist, self.cfg.seed, self._step).tolist()
+
+    # ------------------------------------------------------------------ scheduling
+    @torch.no_grad()
+    def step(self) -> List[Request]:
+        """Admit + prefill what fits, then one decode token for every running sequence.  Returns the
+        requests that finished during this step."""
+        finished: List[Request] = []
+        alloc = self.cache.allocator
+        # ---- admission / prefill ----
+        while self.waiting and len(self.running) < self.cfg.max_batch:
+            r = self.waiting[0][3]
+            n = min(len(r.tokens), self.max_len - 1)
+            r.tokens = r.tokens[:n]
+            shared = self.prefix.lookup(r.tokens) if self.prefix else []
+            need = (n + r.max_tokens + PAGE - 1) // PAGE - len(shared)
+            if need > alloc.num_free:
+                if self.prefix and self.prefix.table and not self.running:
+                    for p in shared:
+                        alloc.release(p)
+                    self.prefix.evict_all()
+                    continue
+                for p in shared:
+                    alloc.release(p)
+                break
+            heapq.heappop(self.waiting)
+            r.pages = shared + [alloc.alloc() for _ in range((n + PAGE - 1) // PAGE - len(shared))]
+            pos0 = len(shared) * PAGE
+            t0 = time.perf_counter()
+            h = self._layers_prefill(r.tokens, pos0, r)
+            tok = self._sample(self._logits(h), [r])[0]
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self.stats.prefill_ms += (time.perf_counter() - t0) * 1e3
+            self.stats.prompt_tokens += n
+            self.stats.prefix_hit_tokens += pos0
+            if self.prefix:
+                self.prefix.insert(r.tokens, r.pages)
+            r.pos = n
+            r.t_first = time.perf_counter()
+            self._emit(r, tok, finished)
+            if not r.finished:
+                self.running.append(r)
+        # ---- one decode token for everything that is running ----
+        if self.running:
+            t0 = time.perf_counter()
+            reqs = self.running
+            for r in reqs:
+                if r.pos // PAGE >= len(r.pages):
+                    r.pages.append(alloc.alloc())
+            dev = self.device
+            tokens = torch.tensor([r.out[-1] for r in reqs], dtype=torch.int64, device=dev)
+            positions = torch.tensor([r.pos for r in reqs], dtype=torch.int32, device=dev)
+            bt = torch.zeros((len(reqs), self.max_pages), dtype=torch.int32)
+            for i, r in enumerate(reqs):
+                bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+            bt = bt.to(dev)
+            slots = torch.tensor([r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs], dtype=torch.int64, device=dev)
+            h = self._layers_decode(tokens, positions, bt, slots)
+            toks = self._sample(self._logits(h), reqs)
+            self.stats.decode_ms += (time.perf_counter() - t0) * 1e3
+            still = []
+            for r, tok in zip(reqs, toks):
+                r.pos += 1
+                self._emit(r, tok, finished)
+                if not r.finished:
+                    still.append(r)
+            self.running = still
+        return finished
+
+    def _emit(self, r: Request, tok: int, finished: list):
+        r.out.append(tok)
+        self.stats.generated_tokens += 1
+        if r.on_token:
+            r.on_token(tok)
+        eos = self.tok.eos_id if self.tok is not None else -1
+        if tok == eos or tok in r.stop_ids or len(r.out) >= r.max_tokens or r.pos + 1 >= self.max_len:
+            r.finished = True
+            r.t_done = time.perf_counter()
+            self._release(r)
+            finished.append(r)
+
+    # ------------------------------------------------------------------ convenience API
+    def generate_batch(self, prompts: List[List[int]], max_tokens=64, sampling: Optional[SamplerConfig] = None):
+        reqs = [self.add_request(p, max_tokens, sampling) for p in prompts]
+        while self.has_pending():
+            self.step()
+        return [r.out for r in reqs]
+
+    def generate(self, prompt: str, max_tokens=64, sampling: Optional[SamplerConfig] = None) -> str:
+        ids = self.tok.encode(prompt)
+        out = self.generate_batch([ids], max_tokens, sampling)[0]
+        eos = self.tok.eos_id
+        return self.tok.decode([t for t in out if t != eos])
+
+    def generate_stream(self, prompt: str, on_text: Callable[[str], None], max_tokens=64,
+                        sampling: Optional[SamplerConfig] = None):
+        ids = self.tok.encode(prompt)
+        acc: List[int] = []
+        sent = [""]
+
+        def on_tok(t):
+            if t == self.tok.eos_id:
+                return
+            acc.append(t)
+            text = self.tok.decode(acc)
+            if not text.endswith("�"):       # hold back incomplete UTF-8 sequences
+                on_text(text[len(sent[0]):])
+                sent[0] = text
+        r = self.add_request(ids, max_tokens, sampling, on_token=on_tok)
+        while not r.finished:
+            self.step()
+        return r
+
+    def generate_with_stats(self, prompt: str, max_tokens=64, sampling: Optional[SamplerConfig] = None):
+        t0 = time.perf_counter()
+        before = self.stats.generated_tokens
+        text = self.generate(prompt, max_tokens, sampling)
+        dt = time.perf_counter() - t0
+        st = InferenceStats(**self.stats.__dict__)
+        st.tokens_per_sec = (self.stats.generated_tokens - before) / max(dt, 1e-9)
+        return text, st
+
+    def reset_context(self):
+        for r in self.running:
+            self._release(r)
+        self.running, self.waiting = [], []
+        if self.prefix:
+            self.prefix.evict_all()
