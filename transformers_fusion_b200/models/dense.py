@@ -346,10 +346,12 @@ class DenseModel(nn.Module):
     # ------------------------------------------------------------------ fused training step
     @torch.no_grad()
     def forward_backward(self, ids, labels, loss_scale: float = 1.0, ignore_index: int = -100,
-                         label_smoothing: float = 0.0):
+                         label_smoothing: Optional[float] = None):
         """Forward + backward of the next-token loss.  ``labels`` are already aligned with ``ids``
         (labels[b, s] is the target for position s).  Returns the mean loss as a device scalar."""
         assert self.flat is not None, "call model.flatten() before training"
+        if label_smoothing is None:
+            label_smoothing = getattr(self, "loss_label_smoothing", 0.0)
         cfg = self.cfg
         B, S = ids.shape
         T = B * S

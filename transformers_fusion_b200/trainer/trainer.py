@@ -1,0 +1,443 @@
+"""Trainer / UnifiedTrainer / DataLoader: the public training API.
+
+Field-for-field counterpart of the reference's ``TrainConfig`` (include/quant/trainer.h:24-69) and the
+``Trainer`` surface (``compile``, ``fit``, ``micro_step``, ``train_step``, ``clip_gradients``,
+``eval_loss``, ``save_checkpoint`` / ``load_checkpoint``, log / epoch / step callbacks, ``metrics``,
+EMA, dynamic loss scale, gradient noise, label smoothing: include/quant/trainer.h:240-342,
+src/trainer/trainer_core.cpp:201-1069).  Checkpoints are the reference's pair: ``<path>`` (.quant
+container, Q_32 blocks) and ``<path>.opt`` ({step, lr, n, per parameter m and v}); ``--resume`` state
+(step, loader offset, RNG) goes to ``<path>.state.json``.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from dataclasses import asdict, dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+
+from ..quant import codec
+from .fused_optim import FlatAdamW
+from .optimizers import FlatOptimizer, build_optimizer
+from .schedulers import schedule_lr
+
+
+@dataclass
+class TrainConfig:
+    batch_size: int = 8
+    seq_length: int = 512
+    epochs: int = 3
+    max_steps: int = 10000
+    learning_rate: float = 3e-4
+    weight_decay: float = 1e-2
+    warmup_steps: int = 100
+    log_interval: int = 10
+    save_interval: int = 1000
+    val_interval: int = 500
+    max_grad_norm: float = 1.0
+    grad_accum_steps: int = 1
+    lr_schedule: str = "WARMUP_COSINE"
+    loss_scale: float = 128.0
+    loss_scale_interval: int = 2000
+    dynamic_loss_scale: bool = False
+    label_smoothing: float = 0.0
+    rdrop_alpha: float = 0.0
+    grad_noise_eta: float = 0.0
+    grad_noise_gamma: float = 0.55
+    ema_decay: float = 0.0
+    qat_bits: int = 0
+    qat_symmetric: bool = True
+    moe_lb_weight: float = 0.01
+    moe_z_weight: float = 0.001
+    mtp_loss_weight: float = 0.0
+    optimizer: str = "adamw"
+    seed: int = 42
+    checkpoint_path: str = "model.quant"
+    activation_checkpointing: bool = False
+    zero_stage: int = 2
+    cuda_graph: bool = False
+
+
+@dataclass
+class TrainMetrics:
+    loss: float = 0.0
+    perplexity: float = 0.0
+    val_loss: float = 0.0
+    learning_rate: float = 0.0
+    grad_norm: float = 0.0
+    tokens_per_sec: float = 0.0
+    step: int = 0
+    epoch: int = 0
+
+
+class DataLoader:
+    """Token stream -> (ids, labels) batches of [batch, seq]; labels are ids shifted left by one.
+    Source: a text file tokenised with ``tokenizer`` (reference DataLoader, include/quant/trainer.h:78-159),
+    a 1-D tensor of token ids, or ``synthetic=(vocab, seed)``."""
+
+    def __init__(self, tokenizer=None, path: Optional[str] = None, batch_size=8, seq_length=512, tokens=None,
+                 synthetic=None, device="cpu", rank=0, world=1, pin=False):
+        self.B, self.S, self.device, self.rank, self.world = batch_size, seq_length, device, rank, world
+        self.offset = 0
+        self.synthetic = synthetic
+        self.pin = pin
+        if synthetic is not None:
+            self.tokens = None
+            self._gen = torch.Generator().manual_seed(synthetic[1] * 9973 + rank)
+        elif tokens is not None:
+            self.tokens = tokens.long()
+        else:
+            text = open(path, "r", encoding="utf-8", errors="ignore").read()
+            self.tokens = torch.tensor(tokenizer.encode(text), dtype=torch.long)
+
+    def __len__(self):
+        if self.tokens is None:
+            return 1 << 30
+        return max(0, (self.tokens.numel() - 1) // (self.B * self.S * self.world))
+
+    def reset(self):
+        self.offset = 0
+
+    def next_batch(self):
+        B, S = self.B, self.S
+        if self.tokens is None:
+            ids = torch.randint(0, self.synthetic[0], (B, S + 1), generator=self._gen)
+        else:
+            n = B * S
+            start = (self.offset * self.world + self.rank) * n
+            if start + n + 1 > self.tokens.numel():
+                self.offset = 0
+                start = self.rank * n
+                if start + n + 1 > self.tokens.numel():
+                    raise ValueError("dataset is smaller than one batch")
+            chunk = self.tokens[start:start + n + 1]
+            self.offset += 1
+            return self._ship(chunk[:-1].view(B, S).contiguous()), self._ship(chunk[1:].view(B, S).contiguous())
+        self.offset += 1
+        return self._ship(ids[:, :-1].contiguous()), self._ship(ids[:, 1:].contiguous())
+
+    def _ship(self, t):
+        if self.pin and torch.cuda.is_available():
+            t = t.pin_memory()
+        return t.to(self.device, non_blocking=True)
+
+    def __iter__(self):
+        for _ in range(len(self)):
+            yield self.next_batch()
+
+
+class ModelEMA:
+    def __init__(self, flat, decay):
+        self.flat, self.decay = flat, decay
+        self.shadow = flat.params.float().clone()
+
+    def step(self):
+        self.shadow.mul_(self.decay).add_(self.flat.params.float(), alpha=1 - self.decay)
+
+    def swap(self):
+        cur = self.flat.params.float().clone()
+        self.flat.params.copy_(self.shadow.to(self.flat.params.dtype))
+        self.shadow = cur
+
+    apply = swap
+
+
+class Trainer:
+    def __init__(self, model, tokenizer=None):
+        self.model, self.tok = model, tokenizer
+        self.cfg = TrainConfig()
+        self.opt = None
+        self.engine = None
+        self._metrics = TrainMetrics()
+        self.log_cb: Optional[Callable[[TrainMetrics], None]] = None
+        self.epoch_cb = self.step_cb = None
+        self.ema: Optional[ModelEMA] = None
+        self.loss_scale = 1.0
+        self._good_steps = 0
+        self.global_step = 0
+
+    # ------------------------------------------------------------------ configuration
+    def compile(self, optimizer=None, cfg: Optional[TrainConfig] = None, symm=None):
+        """``optimizer``: None / a name ("adamw", "adafactor", ...) / a FlatOptimizer instance."""
+        from .engine import TrainEngine
+        self.cfg = cfg or self.cfg
+        c = self.cfg
+        self.model.activation_checkpointing = c.activation_checkpointing
+        name = optimizer if isinstance(optimizer, str) else (c.optimizer if optimizer is None else None)
+        fused = name == "adamw"
+        self.engine = TrainEngine(self.model, lr=c.learning_rate, weight_decay=c.weight_decay, betas=(0.9, 0.999),
+                                  max_grad_norm=c.max_grad_norm, zero_stage=c.zero_stage, cuda_graph=c.cuda_graph and fused,
+                                  comm="fused" if symm is not None else "nccl", symm=symm,
+                                  grad_accum_steps=c.grad_accum_steps)
+        if fused:
+            self.opt = self.engine.opt
+        else:
+            self.opt = optimizer if isinstance(optimizer, FlatOptimizer) else build_optimizer(
+                name, self.model.flat, lr=c.learning_rate, weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm,
+                shard=self.engine.shard if self.engine.zero_stage else None)
+            self.engine.opt = self.opt if hasattr(self.opt, "stage_hyper") else self.engine.opt
+        if c.ema_decay > 0:
+            self.ema = ModelEMA(self.model.flat, c.ema_decay)
+        self.loss_scale = c.loss_scale if c.dynamic_loss_scale else 1.0
+        return self
+
+    def set_log_callback(self, cb): self.log_cb = cb
+    def set_epoch_callback(self, cb): self.epoch_cb = cb
+    def set_step_callback(self, cb): self.step_cb = cb
+    def metrics(self) -> TrainMetrics: return self._metrics
+
+    def lr_at(self, step):
+        c = self.cfg
+        return schedule_lr(c.lr_schedule, c.learning_rate, step, c.max_steps, c.warmup_steps)
+
+    # ------------------------------------------------------------------ steps
+    def micro_step(self, ids, labels, loss_scale: float = 1.0):
+        """Forward + backward of one micro-batch (gradients accumulate in main_grad).  Returns the loss tensor."""
+        return self.model.forward_backward(ids, labels, loss_scale=loss_scale / max(1, self.cfg.grad_accum_steps),
+                                           label_smoothing=self.cfg.label_smoothing)
+
+    def clip_gradients(self, max_norm: float) -> float:
+        g = self.model.flat.grads
+        n = float(g.norm())
+        if max_norm > 0 and n > max_norm:
+            g.mul_(max_norm / (n + 1e-6))
+        return n
+
+    def inject_gradient_noise(self, step, eta, gamma):
+        std = math.sqrt(eta / (1 + step) ** gamma)
+        self.model.flat.grads.add_(torch.randn_like(self.model.flat.grads) * std)
+
+    def train_step(self, ids, labels) -> float:
+        """One optimizer step (with gradient accumulation over ``grad_accum_steps`` equal slices)."""
+        c = self.cfg
+        lr = self.lr_at(self.global_step)
+        fused = isinstance(self.opt, FlatAdamW)
+        if fused and c.grad_accum_steps == 1 and not c.dynamic_loss_scale and c.grad_noise_eta == 0:
+            self.model.loss_label_smoothing = c.label_smoothing
+            loss = self.engine.step(ids, labels, lr)
+        else:
+            chunks = zip(ids.chunk(c.grad_accum_steps), labels.chunk(c.grad_accum_steps))
+            loss = sum(self.micro_step(i, l, self.loss_scale) for i, l in chunks) / c.grad_accum_steps
+            if c.grad_noise_eta > 0:
+                self.inject_gradient_noise(self.global_step, c.grad_noise_eta, c.grad_noise_gamma)
+            if self.loss_scale != 1.0:
+                self.model.flat.grads.mul_(1.0 / self.loss_scale)
+            overflow = c.dynamic_loss_scale and not bool(torch.isfinite(self.model.flat.grads).all())
+            if overflow:
+                self.loss_scale = max(1.0, self.loss_scale / 2)
+                self._good_steps = 0
+                self.model.flat.grads.zero_()
+            else:
+                self.opt.step(lr)
+                if c.dynamic_loss_scale:
+                    self._good_steps += 1
+                    if self._good_steps >= c.loss_scale_interval:
+                        self.loss_scale = min(65536.0, self.loss_scale * 2)
+                        self._good_steps = 0
+        if self.ema:
+            self.ema.step()
+        self.global_step += 1
+        lv = float(loss)
+        m = self._metrics
+        m.loss, m.perplexity, m.learning_rate, m.step = lv, math.exp(min(lv, 30.0)), lr, self.global_step
+        m.grad_norm = float(self.opt.grad_norm.reshape(-1)[0]) if hasattr(self.opt, "grad_norm") else 0.0
+        return lv
+
+    @torch.no_grad()
+    def eval_loss(self, val_dl, max_batches=20) -> float:
+        tot, n = 0.0, 0
+        for _ in range(min(max_batches, max(1, len(val_dl)))):
+            ids, labels = val_dl.next_batch()
+            logits = self.model(ids).float()
+            tot += float(torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1)))
+            n += 1
+        self._metrics.val_loss = tot / max(1, n)
+        return self._metrics.val_loss
+
+    def fit(self, dl, cfg: Optional[TrainConfig] = None, val_dl=None):
+        if cfg is not None or self.engine is None:
+            self.compile(None, cfg or self.cfg)
+        c = self.cfg
+        dev = self.model.tok_embeddings.device
+        for epoch in range(c.epochs):
+            dl.reset()
+            t0, toks = time.perf_counter(), 0
+            for _ in range(len(dl)):
+                if self.global_step >= c.max_steps:
+                    break
+                ids, labels = dl.next_batch()
+                self.train_step(ids.to(dev), labels.to(dev))
+                toks += ids.numel()
+                m = self._metrics
+                m.epoch = epoch
+                if self.global_step % c.log_interval == 0:
+                    m.tokens_per_sec = toks / max(1e-9, time.perf_counter() - t0)
+                    if self.log_cb:
+                        self.log_cb(m)
+                if self.step_cb:
+                    self.step_cb(m)
+                if val_dl is not None and c.val_interval and self.global_step % c.val_interval == 0:
+                    self.eval_loss(val_dl)
+                if c.save_interval and self.global_step % c.save_interval == 0:
+                    self.save_checkpoint(c.checkpoint_path, dl)
+            if self.epoch_cb:
+                self.epoch_cb(self._metrics)
+            if self.global_step >= c.max_steps:
+                break
+        self.save_checkpoint(c.checkpoint_path, dl)
+        return self._metrics
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, path, dl=None):
+        codec.save_model(self.model, path)
+        self._save_opt(path + ".opt")
+        state = {"step": self.global_step, "loader_offset": dl.offset if dl is not None else 0,
+                 "loss_scale": self.loss_scale, "rng": torch.get_rng_state().tolist(), "config": asdict(self.cfg)}
+        with open(path + ".state.json", "w") as f:
+            json.dump(state, f)
+
+    def load_checkpoint(self, path, dl=None, resume=True):
+        from ..quant.codec import load_state
+        _, tensors = load_state(path)
+        with torch.no_grad():
+            for name, dst in self.model.named_tensors():
+                dst.copy_(tensors[name].view(dst.shape).to(dst.dtype))
+        if self.opt is not None:
+            if hasattr(self.opt, "master"):
+                lo, hi = getattr(self.opt, "lo", 0), getattr(self.opt, "hi", self.model.flat.numel)
+                self.opt.master.copy_(self.model.flat.params[lo:hi].float())
+            if os.path.exists(path + ".opt"):
+                self._load_opt(path + ".opt")
+        sp = path + ".state.json"
+        if resume and os.path.exists(sp):
+            st = json.load(open(sp))
+            self.global_step = st["step"]
+            self.loss_scale = st.get("loss_scale", self.loss_scale)
+            if dl is not None:
+                dl.offset = st.get("loader_offset", 0)
+            torch.set_rng_state(torch.tensor(st["rng"], dtype=torch.uint8))
+
+    def _param_slices(self):
+        flat = self.model.flat
+        lo, hi = getattr(self.opt, "lo", 0), getattr(self.opt, "hi", flat.numel)
+        for p, off in zip(flat.params_list, flat.offsets):
+            a, b = max(off, lo), min(off + p.numel(), hi)
+            if a < b:
+                yield a - lo, b - lo
+
+    def _save_opt(self, path):
+        """{i32 step, f32 lr, i32 n, per parameter: i64 n_m, m floats, i64 n_v, v floats} (little endian)."""
+        import struct
+        m = getattr(self.opt, "m", None)
+        v = getattr(self.opt, "v", None)
+        if m is None:
+            m = self.opt.state.get("m") if hasattr(self.opt, "state") else None
+            v = self.opt.state.get("v") if hasattr(self.opt, "state") else None
+        slices = list(self._param_slices())
+        with open(path, "wb") as f:
+            f.write(struct.pack("<ifi", int(getattr(self.opt, "step_count", self.global_step)), float(self.cfg.learning_rate),
+                                len(slices) if m is not None else 0))
+            if m is None:
+                return
+            mc, vc = m.detach().float().cpu(), (v if v is not None else torch.zeros_like(m)).detach().float().cpu()
+            for a, b in slices:
+                f.write(struct.pack("<q", b - a)); f.write(mc[a:b].numpy().tobytes())
+                f.write(struct.pack("<q", b - a)); f.write(vc[a:b].numpy().tobytes())
+
+    def _load_opt(self, path):
+        import struct
+
+        import numpy as np
+        data = open(path, "rb").read()
+        step, lr, n = struct.unpack_from("<ifi", data, 0)
+        if hasattr(self.opt, "step_count"):
+            self.opt.step_count = step
+        m = getattr(self.opt, "m", None)
+        v = getattr(self.opt, "v", None)
+        slices = list(self._param_slices())
+        if m is None or n != len(slices):
+            return
+        off = 12
+        for a, b in slices:
+            (cnt,) = struct.unpack_from("<q", data, off); off += 8
+            if cnt != b - a:
+                raise ValueError(f"{path}: parameter size mismatch")
+            m[a:b].copy_(torch.from_numpy(np.frombuffer(data, np.float32, cnt, off).copy())); off += 4 * cnt
+            off += 8
+            v[a:b].copy_(torch.from_numpy(np.frombuffer(data, np.float32, cnt, off).copy())); off += 4 * cnt
+
+    # ---- EMA (reference ema_init / ema_step / ema_apply / ema_swap)
+    def ema_init(self, decay=0.999): self.ema = ModelEMA(self.model.flat, decay)
+    def ema_step(self): self.ema and self.ema.step()
+    def ema_swap(self): self.ema and self.ema.swap()
+    ema_apply = ema_swap
+
+
+KINDS = {"dense": "dense", "pretrain": "dense", "finetune": "finetune", "fine_tune": "finetune", "ft": "finetune",
+         "moe": "moe", "native": "native"}
+
+
+def unified_trainer_parse_kind(s: str) -> Optional[str]:
+    return KINDS.get(s.lower())
+
+
+@dataclass
+class UnifiedTrainArgs:
+    kind: str = "dense"
+    data: str = ""
+    optimizer: str = "adafactor"
+    batch_size: int = 8
+    seq_length: int = 512
+    epochs: int = 3
+    lr: float = 3e-4
+    log_interval: int = 10
+    save_interval: int = 1000
+    output: str = "model.quant"
+    max_steps: int = 10000
+    seed: int = 42
+
+
+class UnifiedTrainer:
+    """Single entry for the CLIs (reference UnifiedTrainer: configure / run / train_step_once /
+    save_checkpoint / load_checkpoint / metrics, src/trainer/trainer_core.cpp:1190-1327)."""
+
+    def __init__(self, model, tokenizer=None):
+        self.model, self.tok = model, tokenizer
+        self.trainer: Optional[Trainer] = None
+        self.args: Optional[UnifiedTrainArgs] = None
+
+    def configure(self, args: UnifiedTrainArgs):
+        if unified_trainer_parse_kind(args.kind) is None:
+            raise ValueError(f"unknown trainer kind '{args.kind}'")
+        if args.optimizer.lower() not in ("adafactor", "adamw") and args.optimizer.lower() not in __import__(
+                "transformers_fusion_b200.trainer.optimizers", fromlist=["OPTIMIZERS"]).OPTIMIZERS:
+            raise ValueError(f"unknown optimizer '{args.optimizer}'")
+        self.args = args
+        cfg = TrainConfig(batch_size=args.batch_size, seq_length=args.seq_length, epochs=args.epochs, learning_rate=args.lr,
+                          log_interval=args.log_interval, save_interval=args.save_interval, optimizer=args.optimizer.lower(),
+                          checkpoint_path=args.output, max_steps=args.max_steps, seed=args.seed, zero_stage=0)
+        if unified_trainer_parse_kind(args.kind) == "moe":
+            from .moe_trainer import MoETrainer
+            self.trainer = MoETrainer(self.model, self.tok)
+        else:
+            self.trainer = Trainer(self.model, self.tok)
+        self.trainer.compile(None, cfg)
+        return self
+
+    def run(self, log_cb=None):
+        a = self.args
+        dev = self.model.tok_embeddings.device
+        dl = DataLoader(self.tok, a.data, a.batch_size, a.seq_length, device=dev)
+        if log_cb:
+            self.trainer.set_log_callback(log_cb)
+        return self.trainer.fit(dl)
+
+    def train_step_once(self, ids, labels) -> float:
+        return self.trainer.train_step(ids, labels)
+
+    def save_checkpoint(self, path): self.trainer.save_checkpoint(path)
+    def load_checkpoint(self, path): self.trainer.load_checkpoint(path)
+    def metrics(self): return self.trainer.metrics()
