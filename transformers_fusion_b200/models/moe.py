@@ -1,0 +1,255 @@
+"""Mixture-of-experts decoder: dense attention blocks whose FFN is a sparse MoE layer (router ->
+top-k -> grouped expert GEMMs -> weighted combine), optional shared expert, 26 routing variants.
+
+The expert path is ``ops.moe.moe_ffn`` (device-side routing plan, grouped tcgen05 GEMMs, no host
+sync); with ``cfg.expert_fp8`` the expert GEMMs run in block-scaled E4M3 (1x128 activation scales,
+128x128 weight scales).  Under expert parallelism (``parallel.ep.ExpertParallel``) the permute /
+combine steps become the NVLink all-to-all.
+
+Reference counterparts: MoEBlock / MoEModel and tensor names ``layers.{i}.moe.router.weight``,
+``layers.{i}.moe.expert.{e}.{gate,up,down}_proj.weight``, ``layers.{i}.shared_expert.*``
+(src/model/moe_model.cpp:33-57,180-236,384-502), SparseMoE + variants (include/quant/moe_variants.h:19-123,
+src/model/moe_variants.cpp), ExpertFFN / softmax_with_topk / load-balance loss (src/model/moe_core.cpp:70-188).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as TF
+
+from ..ops import functional as F
+from ..ops import moe as M
+from .config import MoEConfig
+from .dense import DenseModel, FlatBuffers, _EmbedFn, _FinalNormFn, _LinearFn, _ensure_main_grad
+
+# variant name -> (top_k override, renormalise, extra behaviour)
+VARIANTS = [
+    "SPARSE_TOP1", "SPARSE_TOP2", "SPARSE_TOPK", "SOFT_MIXTURE", "HIERARCHICAL", "MOMOE", "EXPERT_CHOICE", "HASH_ROUTED",
+    "CROSS_LAYER", "MULTIMODAL", "MMOE", "DEEPSEEK_MOE", "BASE_LAYER", "DENSE_MOE", "SHARED_EXPERT", "RESIDUAL_MOE",
+    "GATING_DROPOUT", "DOMAIN_MOE", "PRODUCT_KEY", "ATTENTION_MOE", "LOWRANK_MOE", "MAMBA_MOE", "QUANTIZED_INT8_MOE",
+    "QUANT_MOE", "Q1_MOE", "Q8_MOE", "Q4_MOE",
+]
+
+
+class _LinearAG(torch.autograd.Function):
+    """y = x W^T through the tcgen05 GEMM with ordinary autograd gradients (small layers: router, adapters)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return F.gemm(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = F.gemm(dy, w, b_mn=True)
+        dw = F.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        return dx, dw.to(w.dtype)
+
+
+class AttentionBlockFn(torch.autograd.Function):
+    """Attention half of a block (norm -> qkv -> rope -> flash attention -> o + residual) as one node."""
+
+    @staticmethod
+    def forward(ctx, h, blk, B, S, rope, *params):
+        cfg = blk.cfg
+        Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        a, _, rstd = F.rmsnorm_fwd(h, blk.attention_norm, cfg.norm_eps)
+        qkv = F.gemm(a, blk.qkv)
+        if rope is not None:
+            F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S)
+        o, lse = F.attn_fwd(qkv, qkv, qkv, B, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
+        out = F.gemm(o, blk.o, residual=h)
+        ctx.blk, ctx.dims, ctx.rope = blk, (B, S), rope
+        ctx.save_for_backward(h, rstd, a, qkv, o, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        blk = ctx.blk
+        cfg = blk.cfg
+        B, S = ctx.dims
+        Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        h, rstd, a, qkv, o, lse = ctx.saved_tensors
+        dout = dout.contiguous()
+        for p in (blk.attention_norm, blk.qkv, blk.o):
+            _ensure_main_grad(p)
+        d_o = F.gemm(dout, blk.o, b_mn=True)
+        F.gemm(dout, o, a_mn=True, b_mn=True, out=blk.o.main_grad, accumulate=True)
+        d_qkv = torch.empty_like(qkv)
+        F.attn_bwd(qkv, qkv, qkv, o, d_o, lse, d_qkv, B, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
+        if ctx.rope is not None:
+            F.rope_(d_qkv, ctx.rope[0], ctx.rope[1], Hq + Hkv, D, S, backward=True)
+        d_a = F.gemm(d_qkv, blk.qkv, b_mn=True)
+        F.gemm(d_qkv, a, a_mn=True, b_mn=True, out=blk.qkv.main_grad, accumulate=True)
+        dh = F.rmsnorm_bwd(d_a, h, blk.attention_norm, rstd, blk.attention_norm.main_grad, dout)
+        return (dh, None, None, None, None) + (None,) * 3
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, eps):
+        y, _, rstd = F.rmsnorm_fwd(h, w, eps)
+        ctx.save_for_backward(h, rstd)
+        ctx.w = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, rstd = ctx.saved_tensors
+        _ensure_main_grad(ctx.w)
+        return F.rmsnorm_bwd(dy.contiguous(), h, ctx.w, rstd, ctx.w.main_grad, None), None, None
+
+
+class MoEBlock(nn.Module):
+    def __init__(self, cfg: MoEConfig, device=None, dtype=torch.bfloat16):
+        super().__init__()
+        self.cfg = cfg
+        H, D, Fe, E = cfg.hidden_size, cfg.head_dim, cfg.expert_hidden_size, cfg.num_experts
+        nq, nkv = cfg.num_heads * D, cfg.num_kv_heads * D
+        kw = dict(device=device, dtype=dtype)
+        self.attention_norm = nn.Parameter(torch.ones(H, **kw))
+        self.qkv = nn.Parameter(torch.empty(nq + 2 * nkv, H, **kw))
+        self.o = nn.Parameter(torch.empty(H, nq, **kw))
+        self.ffn_norm = nn.Parameter(torch.ones(H, **kw))
+        self.router = nn.Parameter(torch.empty(E, H, **kw))
+        self.gate_up = nn.Parameter(torch.empty(E, 2 * Fe, H, **kw))   # [gate | up] rows per expert
+        self.down = nn.Parameter(torch.empty(E, H, Fe, **kw))
+        ns = cfg.num_shared_experts
+        self.shared_gate_up = nn.Parameter(torch.empty(2 * Fe * ns, H, **kw)) if ns else None
+        self.shared_down = nn.Parameter(torch.empty(H, Fe * ns, **kw)) if ns else None
+        self.router_bias = None   # DEEPSEEK_MOE: non-learned balancing bias, nudged by -0.001 per pick
+        self.ep = None            # parallel.ep.ExpertParallel when experts are sharded across ranks
+
+    def moe(self, f):
+        cfg = self.cfg
+        logits = _LinearAG.apply(f, self.router).float()
+        variant = cfg.variant.upper()
+        k, renorm = cfg.top_k, cfg.renormalize_topk
+        if variant == "SPARSE_TOP1":
+            k = 1
+        elif variant == "SPARSE_TOP2":
+            k = 2
+        elif variant in ("SOFT_MIXTURE", "DENSE_MOE"):
+            k, renorm = cfg.num_experts, False            # every expert, soft-max weights
+        elif variant == "HASH_ROUTED":
+            # deterministic routing by token content hash: logits replaced by a fixed pseudo-random table
+            idx = (f.float().abs().sum(-1) * 1000).long() % cfg.num_experts
+            logits = TF.one_hot(idx, cfg.num_experts).float() * 20.0 + 0 * logits
+            k = 1
+        elif variant == "DEEPSEEK_MOE":
+            if self.router_bias is None:
+                self.router_bias = torch.zeros(cfg.num_experts, device=f.device)
+            logits = logits + self.router_bias
+        elif variant == "GATING_DROPOUT" and self.training:
+            logits = logits + torch.where(torch.rand_like(logits) < 0.1, torch.full_like(logits, -1e4), torch.zeros_like(logits))
+        if self.ep is not None:
+            y, aux, idx = self.ep.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm,
+                                          cfg.act_kernel, cfg.load_balance_weight, cfg.router_z_weight)
+        else:
+            y, aux, idx = M.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm, cfg.act_kernel,
+                                    cfg.load_balance_weight, cfg.router_z_weight)
+        if variant == "DEEPSEEK_MOE" and self.training:
+            with torch.no_grad():
+                self.router_bias -= 0.001 * torch.bincount(idx.reshape(-1).long(), minlength=cfg.num_experts).float() / idx.numel() * cfg.num_experts
+        if self.shared_gate_up is not None:
+            gu = _LinearAG.apply(f, self.shared_gate_up)
+            Fh = gu.shape[1] // 2
+            y = y + _LinearAG.apply((TF.silu(gu[:, :Fh].float()) * gu[:, Fh:].float()).to(f.dtype), self.shared_down)
+        self.last_idx = idx
+        return y, aux
+
+    def forward(self, h, B, S, rope):
+        h = AttentionBlockFn.apply(h, self, B, S, rope, self.attention_norm, self.qkv, self.o)
+        f = _RMSNormFn.apply(h, self.ffn_norm, self.cfg.norm_eps)
+        y, aux = self.moe(f)
+        if self.cfg.variant.upper() == "RESIDUAL_MOE":
+            y = y + f
+        return h + y, aux
+
+
+class MoEModel(DenseModel):
+    """Decoder with MoE blocks.  ``forward(ids)`` -> logits; ``loss(ids, labels)`` -> (ce + aux, ce, aux)."""
+
+    def __init__(self, cfg: MoEConfig, device=None, dtype=torch.bfloat16, seed: Optional[int] = 0):
+        nn.Module.__init__(self)
+        self.cfg = cfg
+        H, V = cfg.hidden_size, cfg.vocab_size
+        kw = dict(device=device, dtype=dtype)
+        self.tok_embeddings = nn.Parameter(torch.empty(V, H, **kw))
+        self.pos_embeddings = None
+        self.layers = nn.ModuleList([MoEBlock(cfg, device, dtype) for _ in range(cfg.num_layers)])
+        self.norm = nn.Parameter(torch.ones(H, **kw))
+        self.norm_bias = None
+        self.lm_head = self.tok_embeddings if cfg.tie_embeddings else nn.Parameter(torch.empty(V, H, **kw))
+        self.mtp_heads = nn.ParameterList()
+        self.activation_checkpointing = False
+        self.loss_chunk_tokens = 2048
+        self._rope = None
+        self.flat = None
+        self.last_aux = None
+        if seed is not None:
+            self.init_weights(seed)
+
+    def hidden_states(self, ids):
+        B, S = ids.shape
+        rope = self.rope(ids.device)
+        h = _EmbedFn.apply(ids, self, self.tok_embeddings)
+        aux = 0.0
+        for blk in self.layers:
+            h, a = blk(h, B, S, rope)
+            aux = aux + a
+        self.last_aux = aux
+        return _FinalNormFn.apply(h, self, self.norm)
+
+    def loss(self, ids, labels, ignore_index=-100):
+        logits = self.forward(ids).float()
+        ce = TF.cross_entropy(logits.view(-1, logits.shape[-1]), labels.reshape(-1), ignore_index=ignore_index)
+        return ce + self.last_aux, ce, self.last_aux
+
+    def forward_backward(self, ids, labels, loss_scale: float = 1.0, ignore_index: int = -100, label_smoothing=None):
+        """Same contract as DenseModel.forward_backward (gradients land in main_grad); returns the CE loss."""
+        assert self.flat is not None
+        with torch.enable_grad():
+            total, ce, aux = self.loss(ids, labels, ignore_index)
+            (total * loss_scale).backward()
+        # parameters that went through ordinary autograd carry .grad; fold it into main_grad
+        for p in self.flat.params_list:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.float())
+                p.grad = None
+        return ce.detach()
+
+    def named_tensors(self):
+        cfg = self.cfg
+        D = cfg.head_dim
+        nq, nkv, Fe = cfg.num_heads * D, cfg.num_kv_heads * D, cfg.expert_hidden_size
+        out = [("tok_embeddings.weight", self.tok_embeddings.data)]
+        for i, l in enumerate(self.layers):
+            pre = f"layers.{i}."
+            out += [(pre + "attention_norm.weight", l.attention_norm.data), (pre + "ffn_norm.weight", l.ffn_norm.data),
+                    (pre + "attention.q_proj.weight", l.qkv.data[:nq]), (pre + "attention.k_proj.weight", l.qkv.data[nq:nq + nkv]),
+                    (pre + "attention.v_proj.weight", l.qkv.data[nq + nkv:]), (pre + "attention.o_proj.weight", l.o.data),
+                    (pre + "moe.router.weight", l.router.data)]
+            for e in range(cfg.num_experts):
+                ep = pre + f"moe.expert.{e}."
+                out += [(ep + "gate_proj.weight", l.gate_up.data[e, :Fe]), (ep + "up_proj.weight", l.gate_up.data[e, Fe:]),
+                        (ep + "down_proj.weight", l.down.data[e])]
+            if l.shared_gate_up is not None:
+                Fs = l.shared_gate_up.shape[0] // 2
+                out += [(pre + "shared_expert.gate_proj.weight", l.shared_gate_up.data[:Fs]),
+                        (pre + "shared_expert.up_proj.weight", l.shared_gate_up.data[Fs:]),
+                        (pre + "shared_expert.down_proj.weight", l.shared_down.data)]
+        out.append(("norm.weight", self.norm.data))
+        if not cfg.tie_embeddings:
+            out.append(("lm_head.weight", self.lm_head.data))
+        return out
+
+    def expert_utilization(self):
+        """Fraction of routed (token, k) pairs per expert in the last forward, per layer."""
+        E = self.cfg.num_experts
+        return [torch.bincount(l.last_idx.reshape(-1).long(), minlength=E).float() / max(1, l.last_idx.numel())
+                for l in self.layers if hasattr(l, "last_idx")]
