@@ -104,7 +104,11 @@ class PagedKVCache:
     """KV pools of every layer of one model shard."""
 
     def __init__(self, num_layers, num_pages, Hkv, D, mode="bf16", device="cuda"):
-        assert D in (64, 128) and mode in MODES
+        assert mode in MODES
+        if torch.device(device).type == "cuda":
+            assert D in (64, 128), "the paged-attention kernels are built for head_dim 64 and 128"
+        else:
+            assert D % 32 == 0 or mode != "q4", "4-bit KV blocks hold 32 elements"
         self.L, self.num_pages, self.Hkv, self.D, self.mode = num_layers, num_pages, Hkv, D, mode
         self.device = torch.device(device)
         self.k = [_Pool(num_pages, Hkv, D, mode, device) for _ in range(num_layers)]
