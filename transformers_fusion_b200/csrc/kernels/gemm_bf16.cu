@@ -42,6 +42,17 @@ struct GemmParams {
   const int* expert_of_mtile;   // mode 1: expert of every 128-row tile (-1 = padding, skipped)
   const int* seg_start;         // mode 2: [E + 1] first row of every expert segment
   long long c_expert_stride;    // mode 2: elements between the C matrices of consecutive experts
+  // tensor-parallel fusion with the collective that precedes / follows the GEMM (see tp_fused.cu)
+  //   1: all-gather -> GEMM.  A is the gathered [M, K] buffer in symmetric memory; this rank's rows are in
+  //      place, the last `copy_ctas` CTAs of the grid pull the other ranks' rows over NVLink in 128-row blocks
+  //      and raise ready[block] = epoch; the TMA producer waits for a block's flag before loading from it.
+  //   2: GEMM -> reduce-scatter.  Output rows of shard d are stored straight into rank d's staging buffer
+  //      [world, rows_per_shard, N] at slot `rank` (peer stores from the epilogue); remote shards first.
+  int tp_mode, tp_rank, tp_world, tp_rows_per_shard, tp_copy_ctas, tp_epoch;
+  int* tp_ready;
+  const __nv_bfloat16* const* tp_peer_a;
+  long long tp_lda;
+  __nv_bfloat16* const* tp_peer_c;
   int* status;
 };
 
@@ -70,7 +81,58 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, int tota
     it.expert = p.expert_of_mtile[tile / p.tiles_n];
     if (it.expert < 0) return false;
   }
+  if (p.tp_mode) {
+    // rotate the row-block order: mode 1 starts with the local shard (already in place), mode 2 ends with it
+    const int bps = p.tp_rows_per_shard / BM;
+    const int shift = (p.tp_mode == 1 ? p.tp_rank : p.tp_rank + 1) * bps;
+    it.m0 = ((it.m0 / BM + shift) % p.tiles_m) * BM;
+  }
   return true;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Copy role of the all-gather -> GEMM fusion: pulls 128-row blocks of the peers' shards into the local
+// gathered buffer and publishes each block with a release store.
+__device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int ncopy) {
+  const int W = p.tp_world, bps = p.tp_rows_per_shard / BM;
+  const long long row_chunks = (long long)p.K / 8;  // 16-byte chunks per row
+  __nv_bfloat16* dst_base = const_cast<__nv_bfloat16*>(p.tp_peer_a[p.tp_rank]);
+  for (int idx = cta; idx < (W - 1) * bps; idx += ncopy) {
+    const int peer = (p.tp_rank + 1 + idx / bps) % W;
+    const int blk = peer * bps + idx % bps;  // global 128-row block index
+    const __nv_bfloat16* src = p.tp_peer_a[peer] + (long long)blk * BM * p.tp_lda;
+    __nv_bfloat16* dst = dst_base + (long long)blk * BM * p.tp_lda;
+    const long long total = (long long)BM * row_chunks;
+    for (long long c = threadIdx.x; c < total; c += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long cc = c + (long long)u * blockDim.x;
+        if (cc < total) {
+          const long long r = cc / row_chunks, k = cc % row_chunks;
+          v[u] = *reinterpret_cast<const uint4*>(src + r * p.tp_lda + k * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long cc = c + (long long)u * blockDim.x;
+        if (cc < total) {
+          const long long r = cc / row_chunks, k = cc % row_chunks;
+          *reinterpret_cast<uint4*>(dst + r * p.tp_lda + k * 8) = v[u];
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.tp_ready + blk), "r"(p.tp_epoch) : "memory");
+    }
+  }
 }
 
 template <int BN>
@@ -111,6 +173,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  // copy CTAs take the lowest block indices so that they are scheduled first: a GEMM CTA may wait for a copy
+  // CTA, never the other way round
+  const int ncopy = p.tp_mode == 1 ? p.tp_copy_ctas : 0;
+  const int nctas = int(gridDim.x) - ncopy;  // CTAs that run GEMM tiles
+  const int cta = int(blockIdx.x) - ncopy;
+  if (cta < 0) {
+    tp_copy_role(p, int(blockIdx.x), ncopy);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -144,11 +215,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      for (int w = cta; w < num_work && ok; w += nctas) {
         WorkItem it;
         if (!decode_work(p, w, total_kb, it)) continue;
         const int m0 = it.m0, n0 = it.n0 * BN, kb0 = it.kb0, kb1 = it.kb1;
         const int bz = p.group_mode == 1 ? it.expert : 0;
+        if (p.tp_mode == 1) {
+          const int blk = m0 / BM;
+          if (blk / (p.tp_rows_per_shard / BM) != p.tp_rank) {  // rows owned by a peer: wait until they have landed
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(p.tp_ready + blk) < p.tp_epoch) {
+              if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - t0 > TFB_WAIT_NS)) {
+                report(p.status, ST_TIMEOUT_FLAG);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes -> visible to the TMA reads below
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -194,7 +282,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int abuf = 0;
       uint32_t aphase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      for (int w = cta; w < num_work && ok; w += nctas) {
         WorkItem it;
         if (!decode_work(p, w, total_kb, it)) continue;
         const int kb0 = it.kb0, kb1 = it.kb1;
@@ -235,7 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const bool vec_ok_f32 = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const bool vec_ok_res =
         p.residual && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
-    for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
+    for (int w = cta; w < num_work; w += nctas) {
       WorkItem it;
       if (!decode_work(p, w, total_kb, it)) continue;
       const int m0 = it.m0, n0 = it.n0 * BN;
@@ -286,6 +374,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
           __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+          if (p.tp_mode == 2) {  // row belongs to shard d: store into rank d's staging slot for this rank
+            const int d = row / p.tp_rows_per_shard;
+            cp = p.tp_peer_c[d] + ((long long)p.tp_rank * p.tp_rows_per_shard + (row - d * p.tp_rows_per_shard)) * p.ldc + col0;
+          }
           if (full && vec_ok_bf16) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -377,10 +469,20 @@ struct TfbGemmGroup {
   long long c_expert_stride;   // mode 2: elements between consecutive experts' C matrices
 };
 
+struct TfbGemmTp {
+  int mode;               // 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter
+  int rank, world;
+  int copy_ctas;          // mode 1
+  int epoch;              // mode 1: value of a ready flag once its block has landed
+  int* ready;             // mode 1: local int[M / 128]
+  const void* peer_a;     // mode 1: device array [world] of gathered-A base pointers
+  const void* peer_c;     // mode 2: device array [world] of staging-buffer base pointers
+};
+
 static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
                      long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
                      float alpha, int act, int out_mode, int max_ctas, const TfbGemmGroup* grp, int* status,
-                     void* stream) {
+                     void* stream, const TfbGemmTp* tp = nullptr) {
   using namespace tfb;
   if (M <= 0 || N <= 0 || K <= 0) return TFB_ERR_ARG;
   if (out_mode != 0 && (bias || residual || act)) return TFB_ERR_ARG;
@@ -421,6 +523,17 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   p.expert_of_mtile = grp ? grp->expert_of_mtile : nullptr;
   p.seg_start = grp ? grp->seg_start : nullptr;
   p.c_expert_stride = grp ? grp->c_expert_stride : 0;
+  p.tp_mode = 0; p.tp_rank = 0; p.tp_world = 1; p.tp_rows_per_shard = M; p.tp_copy_ctas = 0; p.tp_epoch = 0;
+  p.tp_ready = nullptr; p.tp_peer_a = nullptr; p.tp_lda = lda; p.tp_peer_c = nullptr;
+  if (tp) {
+    if (tp->world < 1 || M % (tp->world * BM) || a_mn || out_mode != 0 || gmode != 0) return TFB_ERR_ARG;
+    if (tp->mode == 1 && (K % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms)) return TFB_ERR_ARG;
+    p.tp_mode = tp->mode; p.tp_rank = tp->rank; p.tp_world = tp->world; p.tp_rows_per_shard = M / tp->world;
+    p.tp_copy_ctas = tp->mode == 1 ? tp->copy_ctas : 0; p.tp_epoch = tp->epoch; p.tp_ready = tp->ready;
+    p.tp_peer_a = static_cast<const __nv_bfloat16* const*>(tp->peer_a);
+    p.tp_peer_c = static_cast<__nv_bfloat16* const*>(tp->peer_c);
+    if (tp->mode == 1) sms -= tp->copy_ctas;
+  }
   const int total_kb = (K + BK - 1) / BK;
   const int tiles = p.tiles_m * p.tiles_n;
   int splits = 1;
@@ -433,7 +546,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   p.kb_per_split = (total_kb + splits - 1) / splits;
   p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
   const long long work = (long long)tiles * (gmode == 2 ? E : p.splits);
-  const int grid = int(work < sms ? work : sms);
+  const int grid = int(work < sms ? work : sms) + p.tp_copy_ctas;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (BN == 256) {
@@ -473,4 +586,14 @@ TFB_API int tfb_gemm_bf16_grouped(const void* A, long long lda, int a_mn, const 
   if (!grp || grp->mode < 1 || grp->mode > 2 || grp->num_experts < 1) return TFB_ERR_ARG;
   return gemm_impl(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, nullptr, nullptr, 0, alpha, 0, out_mode, 0, grp,
                    status, stream);
+}
+
+// Tensor-parallel fused forms (see TfbGemmTp and tp_fused.cu).  Mode 1: C[M, N] = gathered A [M, K] . B^T where
+// A's row shards live on the W ranks.  Mode 2: C is ignored; partial products go to the peers' staging buffers
+// (row pitch ldc) and are summed by tfb_tp_reduce.
+TFB_API int tfb_gemm_bf16_tp(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* C,
+                             long long ldc, int M, int N, int K, const TfbGemmTp* tp, int* status, void* stream) {
+  if (!tp || tp->mode < 1 || tp->mode > 2) return TFB_ERR_ARG;
+  return gemm_impl(A, lda, 0, B, ldb, b_mn, C, ldc, M, N, K, nullptr, nullptr, 0, 1.0f, 0, 0, 0, nullptr, status,
+                   stream, tp);
 }

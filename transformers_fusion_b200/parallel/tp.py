@@ -1,0 +1,162 @@
+"""Tensor parallelism with sequence parallelism (Megatron layout) on the fused kernels.
+
+``ColumnParallelLinear``  y[M, N/W]   = all_gather_rows(x_shard[M/W, K]) @ W_local[N/W, K]^T   (all-gather -> GEMM)
+``RowParallelLinear``     y_shard[M/W, N] = reduce_scatter_rows(x[M, K/W] @ W_local[N, K/W]^T)  (GEMM -> reduce-scatter)
+
+With ``comm="fused"`` both run as ONE tcgen05 GEMM launch whose CTAs also move the data over NVLink
+(see csrc/comm/tp_fused.cu); ``comm="nccl"`` is the library baseline (all_gather_into_tensor /
+reduce_scatter_tensor around the same GEMM).  Helper functions mirror the reference's
+TensorParallelManager: ``column_parallel_split``, ``row_parallel_split``, ``partition_heads``,
+``reconstruct_weight``, ``communication_volume`` (include/quant/tensor_parallelism.h:16-173,
+src/trainer/tensor_parallelism.cpp:26-508)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib, functional as F
+from ..ops._lib import c_i, c_ll, c_p, check, stream
+
+
+class _Tp(C.Structure):
+    _fields_ = [("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int), ("epoch", C.c_int),
+                ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p)]
+
+
+def _fn():
+    fn = _lib.lib().tfb_gemm_bf16_tp
+    fn.argtypes = [c_p, c_ll, c_p, c_ll, c_i, c_p, c_ll, c_i, c_i, c_i, C.POINTER(_Tp), c_p, c_p]
+    fn.restype = c_i
+    _lib.lib().tfb_tp_reduce.argtypes = [c_p, c_p, c_p, c_ll, c_i, c_i, c_p]
+    _lib.lib().tfb_tp_reduce.restype = c_i
+    return fn
+
+
+# ---------------------------------------------------------------------------------------------- splits
+def column_parallel_split(w, world, rank):
+    """Rows (output features) in ceil chunks, like the reference (tensor_parallelism.cpp:26-35)."""
+    per = (w.shape[0] + world - 1) // world
+    return w[rank * per: min(w.shape[0], (rank + 1) * per)].contiguous()
+
+
+def row_parallel_split(w, world, rank):
+    per = (w.shape[1] + world - 1) // world
+    return w[:, rank * per: min(w.shape[1], (rank + 1) * per)].contiguous()
+
+
+def partition_heads(num_heads, world, rank):
+    per = (num_heads + world - 1) // world
+    return list(range(rank * per, min(num_heads, (rank + 1) * per)))
+
+
+def reconstruct_weight(shards, column=True):
+    return torch.cat(shards, 0 if column else 1)
+
+
+def communication_volume(M, K, N, world, dtype_bytes=2):
+    """Bytes each rank moves per column-parallel + row-parallel pair with sequence parallelism."""
+    ag = (world - 1) * (M // world) * K * dtype_bytes
+    rs = (world - 1) * (M // world) * N * dtype_bytes
+    return {"all_gather": ag, "reduce_scatter": rs, "total": ag + rs}
+
+
+# ---------------------------------------------------------------------------------------------- fused ops
+class TpContext:
+    """Symmetric buffers shared by the fused TP ops of one model shard (double-buffered gather / staging)."""
+
+    def __init__(self, symm, rank, world, max_rows, max_k, max_n, copy_ctas=16):
+        self.symm, self.rank, self.world, self.copy_ctas = symm, rank, world, copy_ctas
+        dev = symm.device
+        self.gather = [symm.alloc(max_rows * max_k, torch.bfloat16) for _ in range(2)]
+        self.stage = [symm.alloc(world * (max_rows // world) * max_n, torch.bfloat16) for _ in range(2)]
+        self.ready = torch.zeros(max_rows // 128 + 1, dtype=torch.int32, device=dev)
+        self.epoch = 0
+        self.parity = 0
+
+    def all_gather_gemm(self, x_shard, w, out=None):
+        """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K]."""
+        Ms, K = x_shard.shape
+        M, N = Ms * self.world, w.shape[0]
+        buf = self.gather[self.parity]
+        xg = buf.view(torch.bfloat16, M * K).view(M, K)
+        xg[self.rank * Ms:(self.rank + 1) * Ms].copy_(x_shard)      # producer kernels may write here directly
+        self.symm.barrier()                                           # every rank's shard is in place
+        self.epoch += 1
+        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x_shard.device)
+        tp = _Tp(1, self.rank, self.world, self.copy_ctas, self.epoch, self.ready.data_ptr(), buf.ptrs.data_ptr(), None)
+        check(_fn()(xg.data_ptr(), K, w.data_ptr(), w.stride(0), 0, y.data_ptr(), y.stride(0), M, N, K, C.byref(tp),
+                    _lib.status_word(x_shard.device).data_ptr(), stream()), "all_gather_gemm")
+        self.parity ^= 1
+        return y, xg
+
+    def gemm_reduce_scatter(self, x, w, residual=None):
+        """x [M, K_local], ``w`` [N, K_local] -> y_shard [M/W, N] = sum over ranks of the partial products."""
+        M, K = x.shape
+        N = w.shape[0]
+        Ms = M // self.world
+        buf = self.stage[self.parity]
+        tp = _Tp(2, self.rank, self.world, 0, 0, None, None, buf.ptrs.data_ptr())
+        check(_fn()(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), 0, None, N, M, N, K, C.byref(tp),
+                    _lib.status_word(x.device).data_ptr(), stream()), "gemm_reduce_scatter")
+        self.symm.barrier()                                           # all partial tiles have arrived
+        out = torch.empty((Ms, N), dtype=torch.bfloat16, device=x.device)
+        stage = buf.view(torch.bfloat16, self.world * Ms * N)
+        check(_lib.lib().tfb_tp_reduce(stage.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                       out.data_ptr(), Ms, N, self.world, stream()), "tp_reduce")
+        self.parity ^= 1
+        return out
+
+
+class ColumnParallelLinear(torch.nn.Module):
+    def __init__(self, weight_full, rank, world, ctx: TpContext = None, group=None):
+        super().__init__()
+        self.weight = torch.nn.Parameter(column_parallel_split(weight_full, world, rank))
+        self.rank, self.world, self.ctx, self.group = rank, world, ctx, group
+
+    def forward(self, x_shard):
+        if self.world == 1:
+            return F.gemm(x_shard, self.weight.data)
+        if self.ctx is not None and x_shard.is_cuda:
+            return self.ctx.all_gather_gemm(x_shard, self.weight.data)[0]
+        xs = [torch.empty_like(x_shard) for _ in range(self.world)]
+        dist.all_gather(xs, x_shard.contiguous(), group=self.group)
+        return F.gemm(torch.cat(xs, 0), self.weight.data)
+
+
+class RowParallelLinear(torch.nn.Module):
+    def __init__(self, weight_full, rank, world, ctx: TpContext = None, group=None):
+        super().__init__()
+        self.weight = torch.nn.Parameter(row_parallel_split(weight_full, world, rank))
+        self.rank, self.world, self.ctx, self.group = rank, world, ctx, group
+
+    def forward(self, x, residual_shard=None):
+        if self.world == 1:
+            return F.gemm(x, self.weight.data, residual=residual_shard)
+        if self.ctx is not None and x.is_cuda:
+            return self.ctx.gemm_reduce_scatter(x, self.weight.data, residual_shard)
+        y = F.gemm(x, self.weight.data, out_dtype=torch.float32)
+        dist.all_reduce(y, group=self.group)
+        Ms = y.shape[0] // self.world
+        out = y[self.rank * Ms:(self.rank + 1) * Ms]
+        if residual_shard is not None:
+            out = out + residual_shard.float()
+        return out.to(x.dtype)
+
+
+class SequenceParallel:
+    """scatter / gather along the sequence (row) dimension around the TP region."""
+
+    def __init__(self, rank, world, group=None):
+        self.rank, self.world, self.group = rank, world, group
+
+    def scatter(self, x, dim=0):
+        return x.chunk(self.world, dim)[self.rank].contiguous()
+
+    def gather(self, x_shard, dim=0):
+        if self.world == 1:
+            return x_shard
+        xs = [torch.empty_like(x_shard) for _ in range(self.world)]
+        dist.all_gather(xs, x_shard.contiguous(), group=self.group)
+        return torch.cat(xs, dim)
