@@ -1,0 +1,66 @@
+"""Worker for the expert-parallel test: fused dispatch / combine across ranks against the single-rank
+MoE layer on the same tokens and weights.  argv: <out_dir>."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from transformers_fusion_b200.ops import _lib, moe  # noqa: E402
+from transformers_fusion_b200.parallel.ep import ExpertParallel  # noqa: E402
+from transformers_fusion_b200.parallel.symm import SymmetricHeap  # noqa: E402
+
+
+def main():
+    out_dir = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    symm = SymmetricHeap(rank, world, dev)
+    T, H, Fh, E, k = 384, 256, 384, 4 * world, 2
+    El = E // world
+    g = torch.Generator().manual_seed(3)
+    X = (torch.randn(world, T, H, generator=g) * 0.5).bfloat16()
+    L = torch.randn(world, T, E, generator=g)
+    GU = (torch.randn(E, 2 * Fh, H, generator=g) * 0.05).bfloat16()
+    DN = (torch.randn(E, H, Fh, generator=g) * 0.05).bfloat16()
+    DY = torch.randn(world, T, H, generator=g).bfloat16()
+    ep = ExpertParallel(symm, rank, world, E, H, T, k)
+    res = {}
+    for rep in range(2):
+        x = X[rank].to(dev).requires_grad_(True)
+        lg = L[rank].to(dev).requires_grad_(True)
+        gu = torch.nn.Parameter(GU[rank * El:(rank + 1) * El].to(dev))
+        dn = torch.nn.Parameter(DN[rank * El:(rank + 1) * El].to(dev))
+        y, aux, idx = ep.moe_ffn(x, lg, gu, dn, k, True, "silu", 0.0, 0.0)
+        (y.float() * DY[rank].to(dev).float()).sum().backward()
+        torch.cuda.synchronize()
+        # reference: every rank's tokens through the full expert set on one device (CPU statement of the op)
+        gu_f, dn_f = torch.nn.Parameter(GU.clone()), torch.nn.Parameter(DN.clone())
+        ys, dxs, dls = [], [], []
+        for r in range(world):
+            xr = X[r].clone().requires_grad_(True)
+            lr = L[r].clone().requires_grad_(True)
+            yr, _, _ = moe.moe_ffn(xr, lr, gu_f, dn_f, k, True, "silu", 0.0, 0.0)
+            (yr.float() * DY[r].float()).sum().backward()
+            ys.append(yr.detach()); dxs.append(xr.grad); dls.append(lr.grad)
+
+        def rel(a, b):
+            return (a.float().cpu() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-9)
+        res[f"y_{rep}"] = rel(y, ys[rank])
+        res[f"dx_{rep}"] = rel(x.grad, dxs[rank])
+        res[f"dlogits_{rep}"] = rel(lg.grad, dls[rank])
+        res[f"dgate_up_{rep}"] = rel(gu.main_grad, gu_f.main_grad[rank * El:(rank + 1) * El])
+        res[f"ddown_{rep}"] = rel(dn.main_grad, dn_f.main_grad[rank * El:(rank + 1) * El])
+    res["status"] = int(_lib.status_word(dev)[0].item())
+    json.dump(res, open(os.path.join(out_dir, f"rank{rank}.json"), "w"))
+    dist.barrier()
+    symm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

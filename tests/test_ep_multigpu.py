@@ -1,0 +1,34 @@
+"""Expert parallelism with the fused dispatch / combine kernels on >= 2 GPUs."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_expert_parallel_matches_single_rank(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n = 2 if torch.cuda.device_count() < 4 else 4
+    port = 29700 + (os.getpid() % 90)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_mp_ep_worker.py"), str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    for i in range(n):
+        res = json.load(open(os.path.join(tmp_path, f"rank{i}.json")))
+        assert res["status"] == 0, res
+        for key, v in res.items():
+            if key != "status":
+                assert v < 4e-2, (key, v, res)
+
+
+def test_assign_experts_contiguous():
+    from transformers_fusion_b200.parallel.ep import assign_experts
+    assert assign_experts(8, 4) == [[0, 1], [2, 3], [4, 5], [6, 7]]
