@@ -1,0 +1,72 @@
+"""FormatPlanner / FormatRegistry: budgets are hard, importance decides who gets the precise tier."""
+import numpy as np
+import pytest
+import torch
+
+from transformers_fusion_b200.quant import codec
+from transformers_fusion_b200.quant.planner import FormatPlanner, FormatRegistry, ImportanceMetric
+
+
+@pytest.mark.parametrize("bpw", [1.0, 1.5, 2.5, 3.3, 4.0, 5.0, 7.1, 9.0, 20.0, 32.0])
+def test_plan_meets_budget(bpw):
+    plan = FormatPlanner(bpw).plan_for_model(256 * 200 + 77)
+    assert plan.achieved_bpw <= max(bpw, 1.0) + 1e-3
+    if bpw >= 2:
+        assert plan.achieved_bpw > 0.7 * bpw
+    assert len(plan.blocks) == 201 and plan.blocks[-1].num_weights == 77
+
+
+def test_importance_orders_tiers():
+    torch.manual_seed(0)
+    w = torch.randn(64 * 256)
+    w[: 8 * 256] *= 20
+    p = FormatPlanner(5.0)
+    s = p.score_importance(w)
+    assert s.shape == (64,) and s[:8].min() > s[8:].max()
+    plan = p.allocate(64)
+    fm = plan.formats()
+    hi = max(set(fm.tolist()), key=codec.format_bpw)
+    assert plan.uses_mix and (fm[:8] == hi).all()
+    g = torch.zeros_like(w)
+    g[-256:] = 5.0
+    s2 = p.score_importance(w, g, metric=ImportanceMetric.FISHER_DIAG)
+    assert int(np.argmax(s2)) == 63
+
+
+def test_mix_allocation_budget_and_quality():
+    rng = np.random.default_rng(0)
+    d = rng.standard_normal(256 * 64).astype(np.float32)
+    d[: 256 * 4] *= 30
+    for mix in (FormatRegistry.get_twi_mix(3.5), FormatRegistry.get_four_mix(4.0)):
+        fm = FormatRegistry.allocate_mix_blocks(mix, d)
+        by = sum(codec.claimed_bytes(int(f), 256) for f in fm)
+        assert by <= int(np.ceil(mix.effective_bpw * d.size / 8))
+        best = max(mix.tiers, key=codec.format_bpw)
+        assert (fm[:4] == best).all()          # the loud blocks are promoted first
+    # measured selection never exceeds the target
+    f = FormatRegistry.select_best_format(4.6, d)
+    assert f.bpw <= 4.6 + 1e-6
+    m = FormatRegistry.select_best_mix(4.6, d)
+    assert m.effective_bpw <= 4.6 + 1e-6
+
+
+def test_table_and_parse():
+    t = FormatRegistry.get_format_table()
+    assert "Q_4" in t and "Q_G_8_K_M" in t and t.count("\n") > 105
+    assert FormatRegistry.parse_format_name("q8").name == "Q_8"
+    assert FormatRegistry.parse_format_name("nonsense") is None
+    mix = FormatPlanner.compute_format_mix(100, 5.0)
+    assert mix == {6: 50, 4: 50}
+
+
+def test_mixed_tensor_roundtrip(tmp_path):
+    torch.manual_seed(1)
+    w = torch.randn(256 * 10 + 5)
+    plan = FormatPlanner(6.0).plan_for_model(w.numel())
+    wr = codec.QuantWriter(tmp_path / "m.quant")
+    wr.add_tensor_mixed("w", w, plan.formats())
+    wr.close()
+    r = codec.QuantReader(tmp_path / "m.quant")
+    assert (r.block_formats("w") == plan.formats()).all()
+    back = r.read_tensor("w")
+    assert back.shape == w.shape and (back - w).abs().max() < 0.3

@@ -1,0 +1,187 @@
+"""quant_bench: ``--kernel <name> --size N`` times one device kernel; ``--inference --model m.quant --prompt p``
+times generation (tools/bench.cpp:20-185).  Kernel timing: CUDA events on the launching stream, warm-up, an
+L2-sized write between timed launches, best and median of ``--iters`` launches; rates are also printed as a
+fraction of the copy / GEMM peaks when ``--peaks <json>`` (keys hbm_gbs, bf16_tflops) is given.
+
+Kernels: gemm, gemm_nt_wgrad, gemm_fp8, attention_fwd, attention_bwd, rmsnorm, rmsnorm_bwd, swiglu, rope,
+cross_entropy, adamw, paged_decode, sampling, moe_ffn."""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import time
+
+from .common import add_int
+
+KERNELS = ("gemm", "gemm_wgrad", "gemm_fp8", "attention_fwd", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "swiglu", "rope",
+           "cross_entropy", "adamw", "paged_decode", "sampling", "moe_ffn")
+
+
+def _build(kernel, n, dev, heads=0):
+    """Returns (callable, flops, bytes) for one launch of ``kernel`` at problem size ``n``."""
+    import torch
+
+    from ..ops import functional as F
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * scale).to(dtype)
+    if kernel == "gemm":
+        a, b = rnd(n, n), rnd(n, n)
+        out = torch.empty((n, n), dtype=bf, device=dev)
+        return (lambda: F.gemm(a, b, out=out)), 2.0 * n ** 3, 3 * n * n * 2
+    if kernel == "gemm_wgrad":
+        a, b = rnd(n, n), rnd(n, n)
+        out = torch.zeros((n, n), dtype=torch.float32, device=dev)
+        return (lambda: F.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)), 2.0 * n ** 3, 2 * n * n * 2 + n * n * 8
+    if kernel == "gemm_fp8":
+        from ..quant import fp8
+        qa, sa = fp8.quant_act_1x128(rnd(n, n))
+        qb, sb = fp8.quant_weight_128x128(rnd(n, n))
+        out = torch.empty((n, n), dtype=bf, device=dev)
+        return (lambda: fp8.gemm_fp8(qa, sa, qb, sb, out=out)), 2.0 * n ** 3, 2 * n * n + n * n * 2
+    if kernel in ("attention_fwd", "attention_bwd"):
+        D, S = 64, n
+        H = heads or 8
+        B = max(1, (1 << 16) // S)
+        qkv = rnd(B * S, 3 * H * D)
+        fl = 4.0 * B * H * S * S * D / 2     # causal
+        if kernel == "attention_fwd":
+            return (lambda: F.attn_fwd(qkv, qkv, qkv, B, S, H, H, D, q_col0=0, k_col0=H * D, v_col0=2 * H * D)), fl, 4 * B * S * H * D * 2
+        o, lse = F.attn_fwd(qkv, qkv, qkv, B, S, H, H, D, q_col0=0, k_col0=H * D, v_col0=2 * H * D)
+        do, dqkv = rnd(B * S, H * D), torch.empty_like(qkv)
+        return (lambda: F.attn_bwd(qkv, qkv, qkv, o, do, lse, dqkv, B, S, H, H, D, q_col0=0, k_col0=H * D, v_col0=2 * H * D)), 2.5 * fl, 8 * B * S * H * D * 2
+    if kernel in ("rmsnorm", "rmsnorm_bwd"):
+        T, Hd = n * 64, 1024
+        x, w = rnd(T, Hd), rnd(Hd)
+        if kernel == "rmsnorm":
+            return (lambda: F.rmsnorm_fwd(x, w, 1e-5)), 0.0, 2 * T * Hd * 2
+        y, rstd, h = F.rmsnorm_fwd(x, w, 1e-5)
+        dw = torch.zeros(Hd, dtype=torch.float32, device=dev)
+        return (lambda: F.rmsnorm_bwd(x, x, w, rstd, dw)), 0.0, 3 * T * Hd * 2
+    if kernel == "swiglu":
+        T, Fh = n * 64, 2048
+        x = rnd(T, 2 * Fh)
+        return (lambda: F.glu_fwd(x, "silu")), 0.0, 3 * T * Fh * 2
+    if kernel == "rope":
+        S, H, D = 1024, 8, 64
+        B = max(1, n * 64 // S)
+        x = rnd(B * S, H * D)
+        cos, sin = F.rope_tables(D, S, device=dev)
+        return (lambda: F.rope_(x, cos, sin, H, D, S)), 0.0, 2 * B * S * H * D * 2
+    if kernel == "cross_entropy":
+        T, V = n * 16, 32000
+        logits = rnd(T, V)
+        labels = torch.randint(0, V, (T,), device=dev)
+        return (lambda: F.cross_entropy_fwd_bwd(logits, labels)), 0.0, 2 * T * V * 2
+    if kernel == "adamw":
+        N = n * n * 16
+        p, gr = torch.randn(N, device=dev), torch.randn(N, device=dev)
+        m, v, lp = torch.zeros(N, device=dev), torch.zeros(N, device=dev), torch.empty(N, dtype=bf, device=dev)
+        return (lambda: F.adamw_(p, gr, m, v, lp, 1e-3, 0.9, 0.95, 1e-8, 0.01, 1)), 0.0, N * (4 * 4 + 3 * 4 + 2)
+    if kernel == "paged_decode":
+        from ..inference.kv_cache import PAGE, PagedKVCache
+        B, Hq, Hkv, D, Lctx = 64, 32, 8, 128, n
+        pages = B * (Lctx // PAGE)
+        kv = PagedKVCache(1, pages, Hkv, D, "bf16", dev)
+        kv.k[0].data.normal_()
+        kv.v[0].data.normal_()
+        bt = torch.arange(pages, device=dev, dtype=torch.int32).view(B, -1)
+        sl = torch.full((B,), Lctx, dtype=torch.int32, device=dev)
+        q = rnd(B, Hq * D)
+        return (lambda: kv.decode(0, q, bt, sl, Hq)), 4.0 * B * Hq * Lctx * D, 2 * B * Lctx * Hkv * D * 2
+    if kernel == "sampling":
+        from ..inference.sampler import sample
+        B, V = max(1, n // 64), 128256
+        logits = rnd(B, V, dtype=torch.float32)
+        t = torch.full((B,), 0.8, device=dev)
+        tk = torch.full((B,), 40, dtype=torch.int32, device=dev)
+        tp = torch.full((B,), 0.95, device=dev)
+        return (lambda: sample(logits, t, tk, tp, seed=1, step=1)), 0.0, B * V * 4
+    if kernel == "moe_ffn":
+        from ..ops import moe as M
+        T, Hd, Fh, E, k = n * 8, 1024, 512, 16, 2
+        x, wr = rnd(T, Hd), rnd(E, Hd, scale=0.1)
+        gu, dn = rnd(E, 2 * Fh, Hd, scale=0.05), rnd(E, Hd, Fh, scale=0.05)
+
+        def run():
+            with torch.no_grad():
+                return M.moe_ffn(x, F.gemm(x, wr, out_dtype=torch.float32), gu, dn, k, True, "silu", 0.0, 0.0)
+        return run, 2.0 * T * k * 3 * Hd * Fh, (gu.numel() + dn.numel()) * 2 + 4 * T * Hd * 2
+    raise SystemExit(f"Error: unknown kernel '{kernel}' (choices: {', '.join(KERNELS)})")
+
+
+def time_kernel(fn, iters=20, warmup=5, flush=True):
+    """Per-launch milliseconds (list) measured with CUDA events; a 256 MiB write evicts L2 between launches."""
+    import torch
+    scrub = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="quant_bench", description="Usage: quant_bench [--kernel <name> --size N] [--inference --model m.quant --prompt p]")
+    ap.add_argument("--kernel", default="")
+    add_int(ap, "--size", 1024)
+    ap.add_argument("--inference", action="store_true")
+    ap.add_argument("--model", default="")
+    ap.add_argument("--prompt", default="test")
+    add_int(ap, "--iters", 20)
+    add_int(ap, "--warmup", 5)
+    add_int(ap, "--heads", 0)
+    ap.add_argument("--peaks", default="")
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args(argv)
+    if a.size <= 0 or a.size > 16384:
+        print("Error: --size needs 1..16384", file=sys.stderr)
+        return 2
+    import torch
+    if a.kernel:
+        if not torch.cuda.is_available():
+            print("Error: kernel benchmarks need a CUDA device", file=sys.stderr)
+            return 1
+        names = KERNELS if a.kernel == "all" else [a.kernel]
+        peaks = json.load(open(a.peaks)) if a.peaks else {}
+        for name in names:
+            fn, flops, nbytes = _build(name, a.size, torch.device("cuda"), a.heads)
+            ms = time_kernel(fn, a.iters, a.warmup)
+            best, med = min(ms), statistics.median(ms)
+            rec = {"kernel": name, "size": a.size, "ms_best": round(best, 5), "ms_median": round(med, 5),
+                   "gbs": round(nbytes / best / 1e6, 1), "tflops": round(flops / best / 1e9, 2)}
+            if peaks:
+                rec["frac_hbm_of_measured"] = round(rec["gbs"] / peaks["hbm_gbs"], 3)
+                if flops:
+                    rec["frac_bf16_of_measured"] = round(rec["tflops"] / peaks["bf16_tflops"], 3)
+            print(json.dumps(rec) if a.json else "  ".join(f"{k}={v}" for k, v in rec.items()), flush=True)
+    if a.inference:
+        from ..inference.engine import EngineConfig, InferenceEngine
+        from ..inference.sampler import SamplerConfig
+        from ..quant import codec
+        from .common import load_tokenizer, model_dtype, pick_device
+        dev = pick_device()
+        model = codec.load_model(a.model, device=dev, dtype=model_dtype(dev))
+        eng = InferenceEngine(model, load_tokenizer(a.model), EngineConfig(num_pages=1024))
+        t0 = time.perf_counter()
+        text, st = eng.generate_with_stats(a.prompt, min(64, model.cfg.max_seq_len - 8), SamplerConfig(0.0))
+        dt = time.perf_counter() - t0
+        print(f"inference: {st.generated_tokens} tokens in {dt * 1e3:.1f} ms ({st.generated_tokens / max(dt, 1e-9):.1f} tok/s, ttft {st.ttft_ms:.2f} ms)")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

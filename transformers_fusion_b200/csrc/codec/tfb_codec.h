@@ -60,11 +60,17 @@ long long tfb_reader_read_tensor(const tfb_reader*, const char* name, float* out
 // format byte of the first block of a tensor (-1 when absent)
 int tfb_reader_tensor_format(const tfb_reader*, const char* name);
 
+// format bytes of every block of a tensor; returns the block count (or -1), writes at most cap entries
+long tfb_reader_tensor_block_formats(const tfb_reader*, const char* name, uint8_t* out, long cap);
+
 // ---- container writer -----------------------------------------------------------------------
 typedef struct tfb_writer tfb_writer;
 tfb_writer* tfb_writer_open(const char* path, uint32_t version, uint32_t flags, const uint8_t* config, uint32_t config_size);
 // queue a tensor: quantised per `block` weights (reference: 32768 for Q_32 saves, 256 for quantised ones)
 int tfb_writer_add_tensor(tfb_writer*, const char* name, const float* data, long long numel, int fmt, uint32_t block);
+// per-block formats (a planner's mix): fmts[i] encodes weights [i * block, (i + 1) * block)
+int tfb_writer_add_tensor_mixed(tfb_writer*, const char* name, const float* data, long long numel, const uint8_t* fmts,
+                                uint32_t nfmts, uint32_t block);
 // writes header | tables | blocks in the order the reference reader expects, plus "<path>.idx"; returns 0 on success
 int tfb_writer_close(tfb_writer*, int write_idx);
 

@@ -173,6 +173,14 @@ TFB_EXPORT int tfb_reader_tensor_format(const tfb_reader* r, const char* name) {
   if (!r->valid || it == r->by_name.end() || r->tensors[it->second].count == 0) return -1;
   return r->fmts[r->tensors[it->second].start].fmt;
 }
+// Format bytes of every block of a tensor; returns the block count (or -1), writes at most cap entries.
+TFB_EXPORT long tfb_reader_tensor_block_formats(const tfb_reader* r, const char* name, uint8_t* out, long cap) {
+  auto it = r->by_name.find(name);
+  if (!r->valid || it == r->by_name.end()) return -1;
+  const auto& t = r->tensors[it->second];
+  for (uint32_t b = 0; b < t.count && long(b) < cap; ++b) out[b] = r->fmts[t.start + b].fmt;
+  return long(t.count);
+}
 TFB_EXPORT long long tfb_reader_read_tensor(const tfb_reader* r, const char* name, float* out, long long cap) {
   const long long numel = tfb_reader_tensor_numel(r, name);
   if (numel < 0 || numel > cap) return -1;
@@ -222,6 +230,30 @@ TFB_EXPORT int tfb_writer_add_tensor(tfb_writer* w, const char* name, const floa
   tfb_writer::Ten t{name, uint32_t(w->blocks.size()), 0};
   for (long long off = 0; off < numel; off += block) {
     const uint32_t n = uint32_t(std::min<long long>(block, numel - off));
+    tfb_writer::Block b;
+    b.fmt = uint8_t(fmt);
+    b.nw = n;
+    b.idx.resize(std::max<size_t>(tfb_block_claimed_bytes(fmt, n), size_t(n) * 4 * (fmt == TFB_FMT_Q32)) + 8 + size_t(n) * 2);
+    const long got = tfb_quantize_block(fmt, data + off, n, b.idx.data(), b.idx.size());
+    if (got < 0) return -1;
+    b.idx.resize(size_t(got));
+    w->blocks.push_back(std::move(b));
+    ++t.count;
+  }
+  w->tensors.push_back(std::move(t));
+  return 0;
+}
+// Per-block formats (a planner's mix): fmts[i] encodes weights [i * block, (i + 1) * block).
+TFB_EXPORT int tfb_writer_add_tensor_mixed(tfb_writer* w, const char* name, const float* data, long long numel,
+                                           const uint8_t* fmts, uint32_t nfmts, uint32_t block) {
+  if (!w || !name || !data || !fmts || numel <= 0 || block == 0) return -1;
+  if ((numel + block - 1) / block != (long long)nfmts) return -1;
+  tfb_writer::Ten t{name, uint32_t(w->blocks.size()), 0};
+  for (uint32_t i = 0; i < nfmts; ++i) {
+    const long long off = (long long)i * block;
+    const uint32_t n = uint32_t(std::min<long long>(block, numel - off));
+    const int fmt = fmts[i];
+    if (fmt >= TFB_FORMAT_COUNT) return -1;
     tfb_writer::Block b;
     b.fmt = uint8_t(fmt);
     b.nw = n;

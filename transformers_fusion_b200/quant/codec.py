@@ -54,6 +54,10 @@ def lib():
         L.tfb_writer_open.argtypes = [C.c_char_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32]
         L.tfb_writer_add_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong, C.c_int, C.c_uint32]
         L.tfb_writer_close.argtypes = [C.c_void_p, C.c_int]
+        L.tfb_writer_add_tensor_mixed.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_uint32,
+                                                  C.c_uint32]
+        L.tfb_reader_tensor_block_formats.restype = C.c_long
+        L.tfb_reader_tensor_block_formats.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_long]
         _LIB = L
     return _LIB
 
@@ -150,6 +154,15 @@ class QuantReader:
     def tensor_format(self, name) -> int:
         return lib().tfb_reader_tensor_format(self._h, name.encode())
 
+    def block_formats(self, name):
+        """Format id of every block of a tensor."""
+        n = lib().tfb_reader_tensor_block_formats(self._h, name.encode(), None, 0)
+        if n < 0:
+            raise KeyError(name)
+        out = np.empty(max(1, n), dtype=np.uint8)
+        lib().tfb_reader_tensor_block_formats(self._h, name.encode(), out.ctypes.data, n)
+        return out[:n]
+
     def read_tensor(self, name) -> torch.Tensor:
         n = lib().tfb_reader_tensor_numel(self._h, name.encode())
         if n < 0:
@@ -171,6 +184,13 @@ class QuantWriter:
             block = 32768 if fmt == Q_32 else 256
         if lib().tfb_writer_add_tensor(self._h, name.encode(), a.ctypes.data, a.size, fmt, block) != 0:
             raise ValueError(f"add_tensor({name}) failed")
+
+    def add_tensor_mixed(self, name: str, t: torch.Tensor, fmts, block: int = 256):
+        """One format per ``block`` weights (a FormatPlan's assignment)."""
+        a = t.detach().float().cpu().contiguous().numpy().reshape(-1)
+        f = np.ascontiguousarray(np.asarray(fmts, dtype=np.uint8))
+        if lib().tfb_writer_add_tensor_mixed(self._h, name.encode(), a.ctypes.data, a.size, f.ctypes.data, f.size, block) != 0:
+            raise ValueError(f"add_tensor_mixed({name}) failed")
 
     def close(self, write_idx=True):
         h, self._h = self._h, None
