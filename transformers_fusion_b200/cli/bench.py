@@ -19,7 +19,7 @@ KERNELS = ("gemm", "gemm_wgrad", "gemm_fp8", "attention_fwd", "attention_bwd", "
            "cross_entropy", "adamw", "paged_decode", "sampling", "moe_ffn")
 
 
-def _build(kernel, n, dev, heads=0):
+def _build(kernel, n, dev, heads=0, shape=None):
     """Returns (callable, flops, bytes) for one launch of ``kernel`` at problem size ``n``."""
     import torch
 
@@ -29,6 +29,18 @@ def _build(kernel, n, dev, heads=0):
 
     def rnd(*shape, dtype=bf, scale=1.0):
         return (torch.randn(*shape, device=dev, generator=g) * scale).to(dtype)
+    if kernel == "gemm" and shape:
+        # shape = (M, N, K, layout): nt = activations x weight^T (forward), nn = dgrad (weight stored [K, N]),
+        # tn = wgrad (both operands stored reduction-major, fp32 accumulate)
+        M, N, K, lay = shape
+        if lay == "nt":
+            a, b, out = rnd(M, K), rnd(N, K), torch.empty((M, N), dtype=bf, device=dev)
+            return (lambda: F.gemm(a, b, out=out)), 2.0 * M * N * K, (M * K + N * K + M * N) * 2
+        if lay == "nn":
+            a, b, out = rnd(M, K), rnd(K, N), torch.empty((M, N), dtype=bf, device=dev)
+            return (lambda: F.gemm(a, b, b_mn=True, out=out)), 2.0 * M * N * K, (M * K + N * K + M * N) * 2
+        a, b, out = rnd(K, M), rnd(K, N), torch.zeros((M, N), dtype=torch.float32, device=dev)
+        return (lambda: F.gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)), 2.0 * M * N * K, (M * K + N * K) * 2 + M * N * 8
     if kernel == "gemm":
         a, b = rnd(n, n), rnd(n, n)
         out = torch.empty((n, n), dtype=bf, device=dev)
@@ -59,7 +71,7 @@ def _build(kernel, n, dev, heads=0):
         x, w = rnd(T, Hd), rnd(Hd)
         if kernel == "rmsnorm":
             return (lambda: F.rmsnorm_fwd(x, w, 1e-5)), 0.0, 2 * T * Hd * 2
-        y, rstd, h = F.rmsnorm_fwd(x, w, 1e-5)
+        y, h, rstd = F.rmsnorm_fwd(x, w, 1e-5)
         dw = torch.zeros(Hd, dtype=torch.float32, device=dev)
         return (lambda: F.rmsnorm_bwd(x, x, w, rstd, dw)), 0.0, 3 * T * Hd * 2
     if kernel == "swiglu":
@@ -144,6 +156,7 @@ def main(argv=None):
     add_int(ap, "--iters", 20)
     add_int(ap, "--warmup", 5)
     add_int(ap, "--heads", 0)
+    ap.add_argument("--shape", default="", help="gemm only: MxNxK[:nt|nn|tn]")
     ap.add_argument("--peaks", default="")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args(argv)
@@ -158,10 +171,14 @@ def main(argv=None):
         names = KERNELS if a.kernel == "all" else [a.kernel]
         peaks = json.load(open(a.peaks)) if a.peaks else {}
         for name in names:
-            fn, flops, nbytes = _build(name, a.size, torch.device("cuda"), a.heads)
+            shape = None
+            if a.shape:
+                dims, _, lay = a.shape.partition(":")
+                shape = tuple(int(x) for x in dims.lower().split("x")) + (lay or "nt",)
+            fn, flops, nbytes = _build(name, a.size, torch.device("cuda"), a.heads, shape)
             ms = time_kernel(fn, a.iters, a.warmup)
             best, med = min(ms), statistics.median(ms)
-            rec = {"kernel": name, "size": a.size, "ms_best": round(best, 5), "ms_median": round(med, 5),
+            rec = {"kernel": name, "size": a.shape or a.size, "ms_best": round(best, 5), "ms_median": round(med, 5),
                    "gbs": round(nbytes / best / 1e6, 1), "tflops": round(flops / best / 1e9, 2)}
             if peaks:
                 rec["frac_hbm_of_measured"] = round(rec["gbs"] / peaks["hbm_gbs"], 3)

@@ -1,14 +1,19 @@
 // Flash attention forward for sm_100a (causal or full, grouped-query heads, head_dim 64 or 128).
 //
-// One CTA per (batch, query head, 128-query block); 192 threads:
-//   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys) through a shared-memory ring
-//   warp 1      MMA issuer:   S_j = Q K_j^T  (tcgen05.mma, both operands in shared memory, fp32 in TMEM)
-//                             O_j = P_j V_j  (A operand = bf16 probabilities read from TMEM, B = V_j MN-major)
-//   warps 2..5  softmax:      one query row per thread - tcgen05.ld the score row, online max / sum,
-//                             exp2, write P_j (bf16 pairs) back over the score columns with tcgen05.st,
-//                             accumulate O in registers with the running rescale
-// S and O_j are double-buffered in tensor memory so the MMAs of block j+1 overlap the softmax of
-// block j.  Nothing but Q, K, V is read and nothing but O and the log-sum-exp row is written.
+// One CTA per (batch, query head, 256-query block), handled as two 128-query tiles that share every K / V tile;
+// 320 threads:
+//   warp 0        TMA producer: both Q tiles once, then K_j / V_j tiles (128 keys) through a shared-memory ring
+//   warp 1        MMA issuer:   S_t = Q_t K_j^T  (tcgen05.mma, both operands in shared memory, fp32 in TMEM)
+//                               O_t = P_t V_j    (A operand = bf16 probabilities read from TMEM, B = V_j MN-major)
+//   warps 2..5    softmax of tile 0, warps 6..9 softmax of tile 1: one query row per thread - tcgen05.ld the score
+//                 row, online max / sum, exp2, write P (bf16 pairs) back over the score columns with tcgen05.st,
+//                 accumulate O in registers with the running rescale
+// The two tiles ping-pong: while one softmax group works, the tensor core computes the other tile's scores, and each
+// scheduler always has two softmax warps to issue from.  Tensor memory: S/P of tile t at columns [128 t, 128 t + 128),
+// O of tile t at 256 + t * D.  P overwrites S, so S_t(j+1) is issued after P_t(j) V_j (the tensor core runs them in
+// issue order); the commit that announces S_t(j+1) therefore also covers O_t(j), which the softmax warps fold into
+// their registers before they release P_t(j+1).  Nothing but Q, K, V is read and nothing but O and the log-sum-exp
+// row is written.
 //
 // Reference counterparts: attention_kernel (src/backend/gpu_compute_cuda.cpp:296, one thread per
 // query, three passes, non-causal), CPU flash attention (src/kernel/flash_attention.cpp:38-225).
@@ -17,9 +22,9 @@
 
 namespace tfb {
 
-constexpr int ATT_THREADS = 192;
-constexpr int ATT_BM = 128;  // queries per CTA
-constexpr int ATT_BN = 128;  // keys per step
+constexpr int ATT_THREADS = 320;
+constexpr int ATT_BM = 128;   // queries per tile (two tiles per CTA)
+constexpr int ATT_BN = 128;   // keys per step
 constexpr int BOX_BYTES = 128 * 64 * 2;
 
 struct AttnFwdParams {
@@ -37,12 +42,79 @@ template <int D>
 struct AttnSmem {
   static constexpr int NB = D / 64;  // 64-column boxes per tile
   static constexpr int TILE = NB * BOX_BYTES;
-  static constexpr int STAGES = (D == 64) ? 3 : 2;
+  static constexpr int STAGES = (D == 64) ? 4 : 2;
   static constexpr int Q_OFF = 0;
-  static constexpr int KV_OFF = TILE;
+  static constexpr int KV_OFF = 2 * TILE;
   static constexpr int BAR_OFF = KV_OFF + STAGES * 2 * TILE;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Row maximum of 128 scores held in tensor memory (one row per thread).  MASK: keys after k_lim do not count.
+// Four independent chains of three-input max keep the dependent-issue latency off the critical path.
+template <bool MASK>
+__device__ __forceinline__ float row_max(uint32_t tS, float m, int k0, int k_lim) {
+  float mx0 = m, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(tS + c * 32, v);
+    tmem_ld_wait();
+    if (MASK) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (k0 + c * 32 + i > k_lim) v[i] = 0xff800000u;  // -inf
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      mx0 = fmax3(mx0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      mx1 = fmax3(mx1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      mx2 = fmax3(mx2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+      mx3 = fmax3(mx3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+    }
+  }
+  return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
+// p = 2^(s * sl2 - mb) for the 128 scores of this thread's row, written back over the score columns as bf16 pairs;
+// returns the row sum (fp32, four partial sums).
+template <bool MASK>
+__device__ __forceinline__ float row_probs(uint32_t tS, float sl2, float mb, int k0, int k_lim) {
+  float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(tS + c * 32, v);
+    tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sl2, -mb));
+      float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, -mb));
+      float p2 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 2]), sl2, -mb));
+      float p3 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 3]), sl2, -mb));
+      if (MASK) {
+        if (k0 + c * 32 + 2 * i > k_lim) p0 = 0.f;
+        if (k0 + c * 32 + 2 * i + 1 > k_lim) p1 = 0.f;
+        if (k0 + c * 32 + 2 * i + 2 > k_lim) p2 = 0.f;
+        if (k0 + c * 32 + 2 * i + 3 > k_lim) p3 = 0.f;
+      }
+      rs0 += p0;
+      rs1 += p1;
+      rs2 += p2;
+      rs3 += p3;
+      pk[i] = pack_bf16(p0, p1);
+      pk[i + 1] = pack_bf16(p2, p3);
+    }
+    tmem_st_32x16(tS + c * 16, pk);
+  }
+  return (rs0 + rs1) + (rs2 + rs3);
+}
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -66,13 +138,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
+  const int npair = (p.S + 2 * ATT_BM - 1) / (2 * ATT_BM);
+  const int nkb = (p.S + ATT_BN - 1) / ATT_BN;
   const int bh = p.B * p.Hq;
-  const int qb = nqb - 1 - int(blockIdx.x) / bh;  // longest (latest) query blocks are scheduled first
+  const int pair = npair - 1 - int(blockIdx.x) / bh;  // longest (latest) query blocks are scheduled first
   const int rem = int(blockIdx.x) % bh;
   const int b = rem / p.Hq, h = rem % p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
-  const int n_kv = p.causal ? min(qb + 1, (p.S + ATT_BN - 1) / ATT_BN) : (p.S + ATT_BN - 1) / ATT_BN;
+  // number of key blocks each tile visits (0: the tile lies past the end of the sequence)
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qb = pair * 2 + t;
+    n_t[t] = qb * ATT_BM >= p.S ? 0 : (p.causal ? min(qb + 1, nkb) : nkb);
+  }
+  const int n_kv = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
@@ -99,15 +179,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: S/P buffers at [0,128) and [128,256); O_j buffers at 256 + i*D.
   const uint32_t tS0 = tmem_base, tO0 = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(bar_q, L::TILE);
+      mbar_expect_tx(bar_q, 2 * L::TILE);
 #pragma unroll
-      for (int i = 0; i < NB; ++i)
-        tma_load_3d(sQ + i * BOX_BYTES, &tq, bar_q, p.q_col0 + h * D + i * 64, qb * ATT_BM, b);
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int i = 0; i < NB; ++i)
+          tma_load_3d(sQ + t * L::TILE + i * BOX_BYTES, &tq, bar_q, p.q_col0 + h * D + i * 64, (pair * 2 + t) * ATT_BM, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % ST;
         if (!mbar_wait(bar_kv_empty + st * 8, ((j / ST) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
@@ -129,143 +210,111 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(FMT_BF16, FMT_BF16, false, false, ATT_BM, ATT_BN);
       constexpr uint32_t idesc_o = umma_idesc(FMT_BF16, FMT_BF16, false, true, ATT_BM, D);
-      auto issue_s = [&](int j) {
-        const int st = j % ST;
-        const uint32_t sK = sbase + L::KV_OFF + st * 2 * L::TILE;
-        const uint32_t tS = tS0 + (j & 1) * 128;
+      auto issue_s = [&](int t, int j) {
+        const uint32_t sK = sbase + L::KV_OFF + (j % ST) * 2 * L::TILE;
+        const uint32_t sQt = sQ + t * L::TILE;
+        const uint32_t tS = tS0 + t * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * BOX_BYTES + (k & 3) * 32;
-          umma_f16_ss(tS, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k > 0);
+          umma_f16_ss(tS, umma_smem_desc(sQt + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024), idesc_s, k > 0);
         }
-        umma_commit(bar_s_full + (j & 1) * 8);
+        umma_commit(bar_s_full + t * 8);
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, ST_TIMEOUT_FULL) &&
-                mbar_wait(bar_kv_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
-      if (ok) {
+                (n_kv == 0 || mbar_wait(bar_kv_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL));
+      if (ok && n_kv > 0) {
         tc_fence_after();
-        issue_s(0);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (n_t[t] > 0) issue_s(t, 0);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int st1 = (j + 1) % ST;
           if (!mbar_wait(bar_kv_full + st1 * 8, ((j + 1) / ST) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
           tc_fence_after();
-          issue_s(j + 1);
         }
-        if (!mbar_wait(bar_p_ready + (j & 1) * 8, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
-        tc_fence_after();
         const int st = j % ST;
         const uint32_t sV = sbase + L::KV_OFF + st * 2 * L::TILE + L::TILE;
-        const uint32_t tP = tS0 + (j & 1) * 128;
-        const uint32_t tO = tO0 + (j & 1) * D;
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k) {
-          // V_j tile is [key rows][64-col boxes]: MN-major B; 16 keys = 2048 B further, next 64 columns one box on
-          umma_f16_ts(tO, tP + k * 8, umma_smem_desc(sV + k * 2048, BOX_BYTES, 1024), idesc_o, k > 0);
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || j >= n_t[t]) continue;
+          if (!mbar_wait(bar_p_ready + t * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) {
+            ok = false;
+            continue;
+          }
+          tc_fence_after();
+          const uint32_t tP = tS0 + t * 128;
+          const uint32_t tO = tO0 + t * D;
+#pragma unroll
+          for (int k = 0; k < ATT_BN / 16; ++k) {
+            // V_j tile is [key rows][64-col boxes]: MN-major B; 16 keys = 2048 B further, next 64 columns one box on
+            umma_f16_ts(tO, tP + k * 8, umma_smem_desc(sV + k * 2048, BOX_BYTES, 1024), idesc_o, k > 0);
+          }
+          if (j + 1 < n_t[t]) issue_s(t, j + 1);              // its commit also covers the P V product above
+          else umma_commit(bar_o_full + t * 8);
         }
-        umma_commit(bar_o_full + (j & 1) * 8);
-        umma_commit(bar_kv_empty + st * 8);
+        if (ok) umma_commit(bar_kv_empty + st * 8);
       }
     }
   } else {
+    const int t = (warp - 2) >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
+    const int qb = pair * 2 + t;
     const int q_idx = qb * ATT_BM + r;
+    const int n_mine = t ? n_t[1] : n_t[0];
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tS0 + t * 128 + lane_off;
+    const uint32_t tO = tO0 + t * D + lane_off;
     const float sl2 = p.scale * 1.4426950408889634f;
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
     float o[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait_warp(bar_s_full + (j & 1) * 8, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+    for (int j = 0; j < n_mine; ++j) {
+      if (!mbar_wait_warp(bar_s_full + t * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t tS = tS0 + (j & 1) * 128 + lane_off;
       const int k0 = j * ATT_BN;
       const bool need_mask = (p.causal && k0 + ATT_BN - 1 > qb * ATT_BM) || (k0 + ATT_BN > p.S);
       const int k_lim = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);  // last visible key index for this row
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      const float mx = need_mask ? row_max<true>(tS, m, k0, k_lim) : row_max<false>(tS, m, k0, k_lim);
+      if (j > 0) {  // O_t(j-1) is complete: the commit behind S_t(j) was issued after it
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + c * 32 + i <= k_lim) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tO + c * 32, v);
+          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
       }
       const float m_new = mx;
       const float mb = (m_new == -INFINITY) ? 0.f : m_new * sl2;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m * sl2 - mb);
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(__uint_as_float(v[2 * i]) * sl2 - mb);
-          float p1 = exp2f(__uint_as_float(v[2 * i + 1]) * sl2 - mb);
-          if (need_mask) {
-            if (k0 + c * 32 + 2 * i > k_lim) p0 = 0.f;
-            if (k0 + c * 32 + 2 * i + 1 > k_lim) p1 = 0.f;
-          }
-          // the row sum uses the bf16-rounded probabilities that the tensor core will see
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          const float2 pf = __bfloat1622float2(pb);
-          rs += pf.x + pf.y;
-          pk[i] = *reinterpret_cast<const uint32_t*>(&pb);
-        }
-        tmem_st_32x16(tS + c * 16, pk);
-      }
-      l = l * alpha + rs;
+      const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m * sl2 - mb);
+      const float rs = need_mask ? row_probs<true>(tS, sl2, mb, k0, k_lim) : row_probs<false>(tS, sl2, mb, k0, k_lim);
+      l = fmaf(l, alpha, rs);
       m = m_new;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_p_ready + (j & 1) * 8);
-      if (j > 0) {
-        const int jj = j - 1;
-        if (!mbar_wait_warp(bar_o_full + (jj & 1) * 8, (jj >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t tO = tO0 + (jj & 1) * D + lane_off;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tO + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-        }
-      }
+      mbar_arrive(bar_p_ready + t * 8);
       alpha_prev = alpha;
     }
-    if (ok && n_kv > 0) {
-      const int jj = n_kv - 1;
-      if (mbar_wait_warp(bar_o_full + (jj & 1) * 8, (jj >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+    if (ok && n_mine > 0) {
+      if (mbar_wait_warp(bar_o_full + t * 8, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
         tc_fence_after();
-        const uint32_t tO = tO0 + (jj & 1) * D + lane_off;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tO + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
         }
         if (q_idx < p.S) {
           const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -304,8 +353,8 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  const int nqb = (p.S + ATT_BM - 1) / ATT_BM;
-  kern<<<nqb * p.B * p.Hq, ATT_THREADS, L::TOTAL, st>>>(tq, tk, tv, p);
+  const int npair = (p.S + 2 * ATT_BM - 1) / (2 * ATT_BM);
+  kern<<<npair * p.B * p.Hq, ATT_THREADS, L::TOTAL, st>>>(tq, tk, tv, p);
   return int(cudaGetLastError());
 }
 

@@ -248,7 +248,7 @@ class DenseModel(nn.Module):
         self.lm_head = self.tok_embeddings if cfg.tie_embeddings else nn.Parameter(torch.empty(V, H, **kw))
         self.mtp_heads = nn.ParameterList([nn.Parameter(torch.empty(V, H, **kw)) for _ in range(cfg.mtp_num_heads)])
         self.activation_checkpointing = False
-        self.loss_chunk_tokens = 2048
+        self.loss_chunk_tokens = 4736   # 37 row tiles x 4 column tiles (H=512, 128-wide) = one wave of 148 SMs in the dgrad GEMM
         self._rope = None
         self.flat: Optional[FlatBuffers] = None
         if seed is not None:
@@ -365,7 +365,7 @@ class DenseModel(nn.Module):
             h, c = block_forward(cfg, blk, h, B, S, rope, save=not ckpt)
             ctxs.append(c)
         f, st = _norm_fwd(cfg, h, self.norm, self.norm_bias)
-        # ---- chunked LM head + cross entropy: logits of a chunk never leave L2-sized working sets ----
+        # ---- chunked LM head + cross entropy: only one chunk of logits exists at a time ----
         n_valid = (lab_f != ignore_index).sum().clamp(min=1).float()
         scale = (loss_scale / n_valid).reshape(1)
         d_f = torch.empty_like(f)

@@ -1,0 +1,290 @@
+"""Collective communication.
+
+* ``DistributedContext`` - rank / world bookkeeping and all_reduce / broadcast / all_gather / barrier on tensors, over
+  ``torch.distributed`` (NCCL on GPUs, gloo on CPU).  ``DistributedContext.init()`` reads the torchrun environment.
+* ``SymmCollectives``    - the same collectives as single fused kernels over symmetric peer memory (one-shot and
+  two-shot all-reduce, reduce-scatter, all-gather, broadcast; bf16 / fp32; sum / avg / max / min), for the
+  latency-bound sizes of tensor-parallel decode.  Bounded waits; errors surface through the status word.
+* ``RingAllReduce``      - the reference's API (allreduce with ops, chunked variant, reduce_scatter, allgather, scatter,
+  gather, hierarchical_allreduce).  There is no ring on NVSwitch: calls map onto SymmCollectives when a symmetric heap
+  is attached and onto torch.distributed otherwise.
+* ``ParameterServer``    - sharded key/value store of tensors with versioning and stale-gradient damping.
+
+Reference counterparts: src/trainer/distributed.cpp (DistributedContext :21-123, RingAllReduce :288-591,
+ParameterServer :597-885)."""
+from __future__ import annotations
+
+import os
+import threading
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+OPS = {"sum": 0, "avg": 1, "max": 2, "min": 3}
+_TORCH_OPS = {"sum": dist.ReduceOp.SUM, "avg": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}
+
+
+class DistributedContext:
+    def __init__(self, rank: int = 0, world_size: int = 1, group=None):
+        self.rank, self.world_size, self.group = rank, world_size, group
+
+    @classmethod
+    def init(cls, backend: Optional[str] = None, timeout_s: float = 600.0) -> "DistributedContext":
+        """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (single process when unset)."""
+        import datetime
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        if world > 1 and not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            if backend is None:
+                backend = "nccl" if torch.cuda.is_available() else "gloo"
+            if backend == "nccl":
+                torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+            dist.init_process_group(backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+        return cls(rank, world)
+
+    @property
+    def is_distributed(self):
+        return self.world_size > 1 and dist.is_initialized()
+
+    def all_reduce(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
+        if self.is_distributed:
+            dist.all_reduce(t, op=_TORCH_OPS[op], group=self.group)
+            if op == "avg":
+                t.div_(self.world_size)
+        return t
+
+    def broadcast(self, t: torch.Tensor, root: int = 0) -> torch.Tensor:
+        if self.is_distributed:
+            dist.broadcast(t, src=root, group=self.group)
+        return t
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """Concatenation of every rank's ``t`` along dim 0."""
+        if not self.is_distributed:
+            return t.clone()
+        out = torch.empty((self.world_size * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+    def reduce_scatter(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
+        """This rank's 1/W slice (dim 0) of the reduction of ``t`` over ranks."""
+        if not self.is_distributed:
+            return t.clone()
+        n = t.shape[0] // self.world_size
+        out = torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        if dist.get_backend(self.group) == "gloo":      # gloo has no reduce_scatter: reduce, then slice
+            full = t.clone()
+            dist.all_reduce(full, op=_TORCH_OPS[op], group=self.group)
+            out.copy_(full[self.rank * n:(self.rank + 1) * n])
+        else:
+            dist.reduce_scatter_tensor(out, t.contiguous(), op=_TORCH_OPS[op], group=self.group)
+        if op == "avg":
+            out.div_(self.world_size)
+        return out
+
+    def barrier(self):
+        if self.is_distributed:
+            dist.barrier(group=self.group)
+
+    def send(self, t, dst, tag=0):
+        dist.send(t.contiguous(), dst, group=self.group, tag=tag)
+
+    def recv(self, t, src, tag=0):
+        dist.recv(t, src, group=self.group, tag=tag)
+        return t
+
+
+class SymmCollectives:
+    """Fused collectives on one staging buffer in symmetric memory (``capacity`` bytes per rank)."""
+
+    def __init__(self, symm, capacity_bytes: int = 8 << 20):
+        from ..ops import _lib
+        self._lib = _lib
+        _lib.register("tfb_collective", [_lib.c_p, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_p, _lib.c_p,
+                                         _lib.c_i, _lib.c_i, _lib.c_p, _lib.c_p, _lib.c_i, _lib.c_p])
+        self.symm, self.rank, self.world = symm, symm.rank, symm.world
+        gran = 16 * self.world
+        self.capacity = (capacity_bytes + gran - 1) // gran * gran
+        self.stage = symm.alloc_bytes(self.capacity)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=symm.device)
+        self.one_shot_max_bytes = 256 << 10
+
+    def _run(self, local, n, dtype, op, mode, root=0, max_ctas=0):
+        lib, s = self._lib, self.symm
+        lib.check(lib.lib().tfb_collective(self.stage.ptrs.data_ptr(), lib.ptr(local), n, 0 if dtype == torch.bfloat16 else 1, OPS[op],
+                                           mode, root, s.flags.ptrs.data_ptr(), s.epoch.data_ptr(), self.rank, self.world,
+                                           lib.status_word(s.device).data_ptr(), self.ticket.data_ptr(), max_ctas, lib.stream()),
+                  "collective")
+
+    def _padded(self, t):
+        assert t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous()
+        esz = t.element_size()
+        gran = 16 * self.world // esz
+        n = (t.numel() + gran - 1) // gran * gran
+        assert n * esz <= self.capacity, "message exceeds the staging buffer"
+        return n
+
+    def all_reduce(self, t: torch.Tensor, op="sum", algo="auto") -> torch.Tensor:
+        """In place on ``t``.  ``algo``: one_shot | two_shot | auto (by size)."""
+        n = self._padded(t)
+        st = self.stage.view(t.dtype, n)
+        st[: t.numel()].copy_(t.reshape(-1))
+        if n > t.numel():
+            st[t.numel():].zero_()
+        one = algo == "one_shot" or (algo == "auto" and n * t.element_size() <= self.one_shot_max_bytes)
+        if one:
+            out = torch.empty(n, dtype=t.dtype, device=t.device)
+            self._run(out, n, t.dtype, op, 0, max_ctas=8)
+            t.copy_(out[: t.numel()].view(t.shape))
+        else:
+            self._run(None, n, t.dtype, op, 1)
+            t.copy_(st[: t.numel()].view(t.shape))
+        return t
+
+    def reduce_scatter(self, t: torch.Tensor, op="sum") -> torch.Tensor:
+        n = self._padded(t)
+        assert n == t.numel(), "reduce_scatter needs numel * elem_size to be a multiple of 16 * world"
+        self.stage.view(t.dtype, n).copy_(t.reshape(-1))
+        out = torch.empty(n // self.world, dtype=t.dtype, device=t.device)
+        self._run(out, n, t.dtype, op, 2)
+        return out
+
+    def all_gather(self, shard: torch.Tensor) -> torch.Tensor:
+        n = shard.numel() * self.world
+        assert n * shard.element_size() % (16 * self.world) == 0 and n * shard.element_size() <= self.capacity
+        self._run(shard.contiguous(), n, shard.dtype, "sum", 3)
+        return self.stage.view(shard.dtype, n).clone()
+
+    def broadcast(self, t: torch.Tensor, root=0) -> torch.Tensor:
+        n = self._padded(t)
+        st = self.stage.view(t.dtype, n)
+        if self.rank == root:
+            st[: t.numel()].copy_(t.reshape(-1))
+        self._run(None, n, t.dtype, "sum", 4, root)
+        t.copy_(st[: t.numel()].view(t.shape))
+        return t
+
+
+class RingAllReduce:
+    """Reference-shaped facade (ops SUM / AVG / MAX / MIN; chunked and hierarchical variants keep their names)."""
+
+    def __init__(self, ctx: DistributedContext, symm_collectives: Optional[SymmCollectives] = None):
+        self.ctx, self.sc = ctx, symm_collectives
+
+    def _dev(self, t):
+        return self.sc is not None and t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) and \
+            t.numel() * t.element_size() <= self.sc.capacity - 16 * self.sc.world
+
+    def allreduce(self, t, op="sum"):
+        return self.sc.all_reduce(t.contiguous(), op) if self._dev(t) else self.ctx.all_reduce(t, op)
+
+    def allreduce_chunked(self, t, op="sum", chunk_elems=1 << 20):
+        flat = t.reshape(-1)
+        for o in range(0, flat.numel(), chunk_elems):
+            seg = flat[o:o + chunk_elems]
+            seg.copy_(self.allreduce(seg.clone(), op))
+        return t
+
+    allreduce_double_buffer = allreduce_chunked
+
+    def reduce_scatter(self, t, op="sum"):
+        return self.ctx.reduce_scatter(t, op)
+
+    def allgather(self, t):
+        return self.ctx.all_gather(t)
+
+    def scatter(self, t, root=0):
+        """Rank r receives slice r (dim 0) of the root's tensor."""
+        full = self.ctx.broadcast(t.clone(), root)
+        n = full.shape[0] // self.ctx.world_size
+        return full[self.ctx.rank * n:(self.ctx.rank + 1) * n].clone()
+
+    def gather(self, t, root=0):
+        full = self.ctx.all_gather(t)
+        return full if self.ctx.rank == root else None
+
+    def hierarchical_allreduce(self, t, op="sum", inter_node_fn=None):
+        """Intra-node reduction, then ``inter_node_fn(tensor)`` (e.g. an NCCL all-reduce over the node leaders' group).
+        One NVSwitch domain is flat, so without an inter-node callback this is a plain all-reduce."""
+        t = self.allreduce(t, op)
+        if inter_node_fn is not None:
+            t = inter_node_fn(t)
+        return t
+
+
+class ParameterServer:
+    """Sharded tensor store (shard = hash(key) % num_shards) with versions.  ``update_gradient`` applies
+    p -= lr * g; a gradient computed against an older version is damped (x0.5 when <= 5 versions stale, dropped
+    beyond ``max_staleness``); pending updates are queued (bounded) and applied by a worker thread in async mode."""
+
+    def __init__(self, num_shards=4, lr=0.01, max_queue=64, max_staleness=5, async_mode=False):
+        self.num_shards, self.lr, self.max_queue, self.max_staleness = num_shards, lr, max_queue, max_staleness
+        self.shards: List[Dict[str, torch.Tensor]] = [dict() for _ in range(num_shards)]
+        self.versions: Dict[str, int] = {}
+        self.lock = threading.Lock()
+        self.queue: List = []
+        self.dropped = 0
+        self.async_mode = async_mode
+        self._stop = False
+        self._worker = None
+        if async_mode:
+            self._cv = threading.Condition(self.lock)
+            self._worker = threading.Thread(target=self._loop, daemon=True)
+            self._worker.start()
+
+    def _shard(self, key):
+        import zlib
+        return self.shards[zlib.crc32(key.encode()) % self.num_shards]
+
+    def push(self, key, t):
+        with self.lock:
+            self._shard(key)[key] = t.detach().clone()
+            self.versions[key] = self.versions.get(key, 0) + 1
+
+    def pull(self, key):
+        with self.lock:
+            return self._shard(key)[key].clone(), self.versions[key]
+
+    def _apply(self, key, grad, version):
+        stale = self.versions[key] - version
+        if stale > self.max_staleness:
+            self.dropped += 1
+            return False
+        scale = 0.5 if stale > 0 else 1.0
+        self._shard(key)[key].add_(grad, alpha=-self.lr * scale)
+        self.versions[key] += 1
+        return True
+
+    def update_gradient(self, key, grad, version):
+        with self.lock:
+            if not self.async_mode:
+                return self._apply(key, grad, version)
+            if len(self.queue) >= self.max_queue:
+                self.dropped += 1
+                return False
+            self.queue.append((key, grad.detach().clone(), version))
+            self._cv.notify()
+            return True
+
+    def _loop(self):
+        while True:
+            with self._cv:
+                while not self.queue and not self._stop:
+                    self._cv.wait(0.05)
+                if self._stop and not self.queue:
+                    return
+                self._apply(*self.queue.pop(0))
+
+    def flush(self):
+        while True:
+            with self.lock:
+                if not self.queue:
+                    return
+
+    def stop(self):
+        self._stop = True
+        if self._worker:
+            self._worker.join(timeout=2)
