@@ -1,0 +1,55 @@
+"""Pipeline worker (gloo, CPU): 1F1B and GPipe over N stages must reproduce the single-process loss and gradients."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from transformers_fusion_b200.models.config import TransformerConfig  # noqa: E402
+from transformers_fusion_b200.models.dense import DenseModel  # noqa: E402
+from transformers_fusion_b200.parallel.collectives import DistributedContext  # noqa: E402
+from transformers_fusion_b200.parallel.pp import PipelineParallel  # noqa: E402
+
+
+def main():
+    out_dir = sys.argv[1]
+    ctx = DistributedContext.init("gloo")
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=4, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 64, (8, 16), generator=g)
+    labels = torch.roll(ids, -1, 1)
+    labels[0, :3] = -100
+    res = {}
+    ref = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=1)
+    ref.flatten()
+    ref_loss = float(ref.forward_backward(ids, labels))
+    for sched in ("gpipe", "1f1b"):
+        m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=1)
+        pp = PipelineParallel(m, ctx.world_size, ctx.rank, ctx, num_microbatches=4)
+        pp.set_profiling(True)
+        loss = pp.run_gpipe(ids, labels) if sched == "gpipe" else pp.run_1f1b(ids, labels)
+        if pp.last:
+            res[f"{sched}_loss_err"] = abs(float(loss) - ref_loss)
+        err = 0.0
+        for p, q in zip(pp.owned_parameters(), [dict(ref.named_parameters())[n] for n, pr in m.named_parameters()
+                                                if any(pr is o for o in pp.owned_parameters())]):
+            pass
+        name_of = {id(p): n for n, p in m.named_parameters()}
+        refp = dict(ref.named_parameters())
+        for p in pp.owned_parameters():
+            n = name_of[id(p)]
+            if n == "tok_embeddings" and cfg.tie_embeddings:
+                continue
+            err = max(err, float((p.main_grad - refp[n].main_grad).abs().max()))
+        res[f"{sched}_grad_err"] = err
+        res[f"{sched}_live"] = pp.max_live_microbatches(sched)
+        assert not pp._saved
+    json.dump(res, open(os.path.join(out_dir, f"rank{ctx.rank}.json"), "w"))
+    ctx.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -5,7 +5,10 @@
 //   warp 1      MMA issuer    : one thread issues tcgen05.mma (128 x BN x 16) per 32 bytes of K and
 //                               commits stage-release / accumulator-ready mbarriers
 //   warps 2..5  epilogue      : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread),
-//                               apply alpha / bias / activation / residual, store bf16 or fp32
+//                               apply alpha / bias / activation / residual, stage 32-row x 128-byte slabs in
+//                               shared memory (128-byte swizzle, conflict-free) and hand them to TMA: a tiled
+//                               store for bf16 / fp32 outputs, a tiled fp32 reduce-add for accumulating outputs
+//                               (weight gradients, split-K).  Ragged edges are clipped by the tensor map.
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
 // the main loop of tile i+1.  Either operand may be K-major (reduction dim contiguous) or MN-major
 // (output dim contiguous): the forward, data-gradient and weight-gradient GEMMs of a linear layer
@@ -14,6 +17,8 @@
 //
 // This replaces the reference's scalar one-thread-per-output kernels
 // (src/backend/gpu_compute_cuda.cpp:68 gemm_kernel; src/kernel/kernel_gemm.cpp:26 scalar_gemm_bt).
+#include <string.h>
+
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
@@ -53,6 +58,7 @@ struct GemmParams {
   const __nv_bfloat16* const* tp_peer_a;
   long long tp_lda;
   __nv_bfloat16* const* tp_peer_c;
+  int c_tma;     // 1: the epilogue goes through shared memory and the C tensor map (aligned, dense C)
   int* status;
 };
 
@@ -140,7 +146,9 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES;   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int STG_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // + barriers + alignment slack
 };
 
@@ -156,7 +164,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -196,6 +204,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     mbar_fence_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -323,6 +332,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const bool vec_ok_f32 = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const bool vec_ok_res =
         p.residual && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+    const uint32_t stg_u32 = smem_base + L::STG_OFF + (warp - 2) * 8192;
+    int sbuf = 0;
     for (int w = cta; w < num_work; w += nctas) {
       WorkItem it;
       if (!decode_work(p, w, total_kb, it)) continue;
@@ -332,6 +343,107 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr0 = tmem_base + abuf * BN + (uint32_t(quad * 32) << 16);
+      if (p.c_tma) {
+        // ---- staged epilogue: registers -> swizzled shared-memory slab -> TMA store / reduce-add ----
+        const int slab_row0 = m0 + quad * 32;
+        const bool slab_live = slab_row0 < p.M;            // warp-uniform
+        const uint32_t xr = uint32_t(lane & 7);
+        if (p.out_mode == 0) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            const int col0 = n0 + c * 64;
+            if (col0 >= p.N) break;
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr0 + c * 64, r0);
+            tmem_ld_32x32(taddr0 + c * 64 + 32, r1);
+            tmem_ld_wait();
+            if (!slab_live) continue;
+            float v[64];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(r0[j]) * p.alpha;
+              v[32 + j] = __uint_as_float(r1[j]) * p.alpha;
+            }
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+            }
+            if (p.act) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] = apply_act(v[j], p.act);
+            }
+            if (p.residual && row < p.M) {
+              const __nv_bfloat16* rp = p.residual + (long long)row * p.ldr + col0;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                if (vec_ok_res && col0 + q * 8 + 8 <= p.N) {
+                  const uint4 u = *reinterpret_cast<const uint4*>(rp + q * 8);
+                  const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int h = 0; h < 4; ++h) {
+                    const float2 f = unpack_bf16(uu[h]);
+                    v[q * 8 + h * 2] += f.x;
+                    v[q * 8 + h * 2 + 1] += f.y;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (col0 + q * 8 + j < p.N) v[q * 8 + j] += __bfloat162float(rp[q * 8 + j]);
+                }
+              }
+            }
+            if (lane == 0) tma_store_wait_read<1>();   // the slab written two chunks ago has been read by its copy
+            __syncwarp();
+            const uint32_t slab = stg_u32 + sbuf * 4096 + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              st_shared_v4(slab + ((uint32_t(q) ^ xr) << 4), pack_bf16(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
+                           pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, 0);
+              tma_store_commit();
+            }
+            sbuf ^= 1;
+          }
+        } else {
+          const int cz = p.group_mode == 2 ? it.expert : 0;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col0 = n0 + c * 32;
+            if (col0 >= p.N) break;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr0 + c * 32, r);
+            tmem_ld_wait();
+            if (!slab_live) continue;
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            const uint32_t slab = stg_u32 + sbuf * 4096 + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              st_shared_v4(slab + ((uint32_t(q) ^ xr) << 4), __float_as_uint(__uint_as_float(r[q * 4]) * p.alpha),
+                           __float_as_uint(__uint_as_float(r[q * 4 + 1]) * p.alpha), __float_as_uint(__uint_as_float(r[q * 4 + 2]) * p.alpha),
+                           __float_as_uint(__uint_as_float(r[q * 4 + 3]) * p.alpha));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.out_mode == 2) tma_reduce_add_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, cz);
+              else tma_store_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, cz);
+              tma_store_commit();
+            }
+            sbuf ^= 1;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar_tempty + abuf * 8);
+        abuf ^= 1;
+        if (abuf == 0) aphase ^= 1;
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -430,6 +542,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       abuf ^= 1;
       if (abuf == 0) aphase ^= 1;
     }
+    if (p.c_tma && lane == 0) tma_store_wait<0>();   // staged slabs must be out of shared memory before the CTA ends
   }
 
   // ------------------------------ teardown ------------------------------
@@ -445,7 +558,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 // host launcher
 // -------------------------------------------------------------------------------------------------
 template <bool A_MN, bool B_MN, int BN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+                  cudaStream_t st) {
   using L = SmemLayout<BN>;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN>;
@@ -454,7 +568,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, tc, p);
   return int(cudaGetLastError());
 }
 
@@ -512,6 +626,19 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
+  // C tensor map for the staged epilogue: 32-row x 128-byte boxes.  Needs a 16-byte aligned base and row pitch.
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  p.c_tma = 0;
+  {
+    const int esz = out_mode == 0 ? 2 : 4;
+    const bool aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esz) % 16 == 0 &&
+                         (gmode != 2 || (grp->c_expert_stride * esz) % 16 == 0);
+    if (aligned && !(tp && tp->mode == 2)) {
+      const unsigned long long zs = gmode == 2 ? (unsigned long long)grp->c_expert_stride * esz : (unsigned long long)ldc * esz * M;
+      if (make_tmap_3d(&tc, C, esz, N, M, gmode == 2 ? E : 1, ldc * esz, zs, 128 / esz, 32, 1) == 0) p.c_tma = 1;
+    }
+  }
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
@@ -538,7 +665,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int tiles = p.tiles_m * p.tiles_n;
   int splits = 1;
   if (out_mode == 2 && gmode == 0 && tiles < sms) {
-    splits = (sms + tiles - 1) / tiles;
+    splits = sms / tiles;                       // round down: all work items must fit in one wave
     const int max_splits = (total_kb + 7) / 8;  // keep at least 8 k-blocks (512 of K) per split
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
@@ -551,17 +678,17 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (BN == 256) {
     switch (key) {
-      case 0: return launch<false, false, 256>(ta, tb, p, grid, st);
-      case 1: return launch<false, true, 256>(ta, tb, p, grid, st);
-      case 2: return launch<true, false, 256>(ta, tb, p, grid, st);
-      default: return launch<true, true, 256>(ta, tb, p, grid, st);
+      case 0: return launch<false, false, 256>(ta, tb, tc, p, grid, st);
+      case 1: return launch<false, true, 256>(ta, tb, tc, p, grid, st);
+      case 2: return launch<true, false, 256>(ta, tb, tc, p, grid, st);
+      default: return launch<true, true, 256>(ta, tb, tc, p, grid, st);
     }
   } else {
     switch (key) {
-      case 0: return launch<false, false, 128>(ta, tb, p, grid, st);
-      case 1: return launch<false, true, 128>(ta, tb, p, grid, st);
-      case 2: return launch<true, false, 128>(ta, tb, p, grid, st);
-      default: return launch<true, true, 128>(ta, tb, p, grid, st);
+      case 0: return launch<false, false, 128>(ta, tb, tc, p, grid, st);
+      case 1: return launch<false, true, 128>(ta, tb, tc, p, grid, st);
+      case 2: return launch<true, false, 128>(ta, tb, tc, p, grid, st);
+      default: return launch<true, true, 128>(ta, tb, tc, p, grid, st);
     }
   }
 }

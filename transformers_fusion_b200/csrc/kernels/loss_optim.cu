@@ -37,6 +37,90 @@ __device__ __forceinline__ float block_reduce_max(float v, float* sh) {
   return v;
 }
 
+// Register-resident variant for rows of at most 512 * 8 * NV elements (vocabularies up to 32768 with NV = 8): every
+// thread keeps its NV 16-byte vectors in registers, so the row is read from memory exactly once and the gradient is
+// written exactly once.  Same contract as cross_entropy_kernel below.
+template <int NV>
+__global__ void __launch_bounds__(512, 2) cross_entropy_regs_kernel(const __nv_bfloat16* logits, const long long* __restrict__ labels,
+                                                                 float* __restrict__ loss, float* __restrict__ lse_out,
+                                                                 __nv_bfloat16* dlogits, const float* __restrict__ scale_ptr, int V,
+                                                                 long long ld, long long ignore_index, float eps, float zw) {
+  __shared__ float sh[32];
+  const long long t = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(logits + t * ld);
+  const long long label = labels[t];
+  const bool ignored = (label == ignore_index);
+  const int V8 = V >> 3;
+  uint4 u[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 512;
+    if (i < V8) u[j] = row[i];
+  }
+  float mx = -INFINITY, tot = 0.f, zy = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 512;
+    if (i < V8) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&u[j]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16(p[k]);
+        mx = fmaxf(mx, fmaxf(f.x, f.y));
+        tot += f.x + f.y;
+        const int c = i * 8 + k * 2;
+        if (c == label) zy = f.x;
+        if (c + 1 == label) zy = f.y;
+      }
+    }
+  }
+  const float gmx = block_reduce_max(mx, sh);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 512;
+    if (i < V8) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&u[j]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16(p[k]);
+        sum += __expf(f.x - gmx) + __expf(f.y - gmx);
+      }
+    }
+  }
+  const float gsum = block_reduce_sum(sum, sh);
+  const float gtot = block_reduce_sum(tot, sh);
+  const float gzy = block_reduce_sum(zy, sh);     // exactly one thread holds the label's logit
+  const float lse = gmx + logf(gsum);
+  if (threadIdx.x == 0) {
+    loss[t] = ignored ? 0.f : (1.f - eps) * (lse - gzy) + eps * (lse - gtot / V) + zw * lse * lse;
+    if (lse_out) lse_out[t] = lse;
+  }
+  if (!dlogits) return;
+  uint4* drow = reinterpret_cast<uint4*>(dlogits + t * ld);
+  const float scale = ignored ? 0.f : (scale_ptr ? *scale_ptr : 1.f);
+  const float pm = scale * (1.f + 2.f * zw * lse);
+  const float sm = scale * eps / V;
+  const float hot = scale * (1.f - eps);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = threadIdx.x + j * 512;
+    if (i < V8) {
+      uint32_t* p = reinterpret_cast<uint32_t*>(&u[j]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16(p[k]);
+        const int c = i * 8 + k * 2;
+        float g0 = pm * __expf(f.x - lse) - sm, g1 = pm * __expf(f.y - lse) - sm;
+        if (c == label) g0 -= hot;
+        if (c + 1 == label) g1 -= hot;
+        p[k] = pack_bf16(g0, g1);
+      }
+      drow[i] = u[j];
+    }
+  }
+}
+
 // One CTA per token row.  loss[t] = (1-eps) * (lse - z_y) + eps * (lse - mean z) + zw * lse^2, 0 when the
 // label equals ignore_index.  When `dlogits` is non-null it receives
 // scale * (softmax * (1 + 2 zw lse) - (1-eps) onehot - eps / V); it may alias `logits`.
@@ -257,6 +341,17 @@ TFB_API int tfb_cross_entropy(const void* logits, const long long* labels, float
                               const float* scale_ptr, int T, int V, long long ld, long long ignore_index,
                               float label_smoothing, float z_weight, void* stream) {
   if (T <= 0 || V <= 0) return TFB_ERR_ARG;
+  const bool vec = (V % 8 == 0) && (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
+                   (!dlogits || (reinterpret_cast<uintptr_t>(dlogits) & 15) == 0);
+  if (vec && V <= 512 * 8 * 8) {
+    auto st = static_cast<cudaStream_t>(stream);
+    auto lg = static_cast<const __nv_bfloat16*>(logits);
+    auto dl = static_cast<__nv_bfloat16*>(dlogits);
+    if (V <= 512 * 8 * 2) cross_entropy_regs_kernel<2><<<T, 512, 0, st>>>(lg, labels, loss, lse, dl, scale_ptr, V, ld, ignore_index, label_smoothing, z_weight);
+    else if (V <= 512 * 8 * 4) cross_entropy_regs_kernel<4><<<T, 512, 0, st>>>(lg, labels, loss, lse, dl, scale_ptr, V, ld, ignore_index, label_smoothing, z_weight);
+    else cross_entropy_regs_kernel<8><<<T, 512, 0, st>>>(lg, labels, loss, lse, dl, scale_ptr, V, ld, ignore_index, label_smoothing, z_weight);
+    return int(cudaGetLastError());
+  }
   cross_entropy_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V,
       ld, ignore_index, label_smoothing, z_weight, 0, V);

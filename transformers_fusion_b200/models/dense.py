@@ -248,7 +248,7 @@ class DenseModel(nn.Module):
         self.lm_head = self.tok_embeddings if cfg.tie_embeddings else nn.Parameter(torch.empty(V, H, **kw))
         self.mtp_heads = nn.ParameterList([nn.Parameter(torch.empty(V, H, **kw)) for _ in range(cfg.mtp_num_heads)])
         self.activation_checkpointing = False
-        self.loss_chunk_tokens = 4736   # 37 row tiles x 4 column tiles (H=512, 128-wide) = one wave of 148 SMs in the dgrad GEMM
+        self.loss_chunk_tokens = 9472   # 74 row tiles x 2 column tiles (H=512, 256-wide) = one wave of 148 SMs in the dgrad GEMM
         self._rope = None
         self.flat: Optional[FlatBuffers] = None
         if seed is not None:
@@ -343,6 +343,33 @@ class DenseModel(nn.Module):
         logits = _LinearFn.apply(f, self.lm_head)
         return logits.view(B, S, -1)
 
+    @torch.no_grad()
+    def head_loss_backward(self, h, lab_f, loss_scale: float = 1.0, ignore_index: int = -100, label_smoothing: float = 0.0,
+                           n_valid=None):
+        """Final norm + chunked LM head + cross entropy on hidden states h [T, H]; accumulates the head's weight
+        gradients and returns (mean loss, d loss / d h).  ``n_valid`` overrides the token count the loss is
+        averaged over (pipeline micro-batches divide by the whole batch's count)."""
+        cfg = self.cfg
+        T = h.shape[0]
+        f, st = _norm_fwd(cfg, h, self.norm, self.norm_bias)
+        # ---- chunked LM head + cross entropy: only one chunk of logits exists at a time ----
+        if n_valid is None:
+            n_valid = (lab_f != ignore_index).sum().clamp(min=1).float()
+        scale = (loss_scale / n_valid).reshape(1)
+        d_f = torch.empty_like(f)
+        losses = torch.empty(T, dtype=torch.float32, device=f.device)
+        W = self.lm_head
+        ck = max(128, min(self.loss_chunk_tokens, T))
+        for t0 in range(0, T, ck):
+            t1 = min(T, t0 + ck)
+            logits = F.gemm(f[t0:t1], W.data)
+            losses[t0:t1] = F.cross_entropy_fwd_bwd(logits, lab_f[t0:t1], scale, ignore_index, label_smoothing)
+            F.gemm(logits, W.data, b_mn=True, out=d_f[t0:t1])
+            F.gemm(logits, f[t0:t1], a_mn=True, b_mn=True, out=W.main_grad, accumulate=True)
+        loss = losses.sum() / n_valid
+        dh = _norm_bwd(cfg, d_f, h, self.norm, self.norm_bias, st, None)
+        return loss, dh
+
     # ------------------------------------------------------------------ fused training step
     @torch.no_grad()
     def forward_backward(self, ids, labels, loss_scale: float = 1.0, ignore_index: int = -100,
@@ -364,22 +391,7 @@ class DenseModel(nn.Module):
             inputs.append(h)
             h, c = block_forward(cfg, blk, h, B, S, rope, save=not ckpt)
             ctxs.append(c)
-        f, st = _norm_fwd(cfg, h, self.norm, self.norm_bias)
-        # ---- chunked LM head + cross entropy: only one chunk of logits exists at a time ----
-        n_valid = (lab_f != ignore_index).sum().clamp(min=1).float()
-        scale = (loss_scale / n_valid).reshape(1)
-        d_f = torch.empty_like(f)
-        losses = torch.empty(T, dtype=torch.float32, device=f.device)
-        W = self.lm_head
-        ck = max(128, min(self.loss_chunk_tokens, T))
-        for t0 in range(0, T, ck):
-            t1 = min(T, t0 + ck)
-            logits = F.gemm(f[t0:t1], W.data)
-            losses[t0:t1] = F.cross_entropy_fwd_bwd(logits, lab_f[t0:t1], scale, ignore_index, label_smoothing)
-            F.gemm(logits, W.data, b_mn=True, out=d_f[t0:t1])
-            F.gemm(logits, f[t0:t1], a_mn=True, b_mn=True, out=W.main_grad, accumulate=True)
-        loss = losses.sum() / n_valid
-        dh = _norm_bwd(cfg, d_f, h, self.norm, self.norm_bias, st, None)
+        loss, dh = self.head_loss_backward(h, lab_f, loss_scale, ignore_index, label_smoothing)
         for i in range(cfg.num_layers - 1, -1, -1):
             c = ctxs[i]
             if ckpt:
