@@ -53,7 +53,12 @@ struct GemmParams {
   //      and raise ready[block] = epoch; the TMA producer waits for a block's flag before loading from it.
   //   2: GEMM -> reduce-scatter.  Output rows of shard d are stored straight into rank d's staging buffer
   //      [world, rows_per_shard, N] at slot `rank` (peer stores from the epilogue); remote shards first.
-  int tp_mode, tp_rank, tp_world, tp_rows_per_shard, tp_copy_ctas, tp_epoch;
+  //   3: weight all-gather -> GEMM (ZeRO-3 / FSDP).  B is the gathered weight in symmetric memory, sharded by rows
+  //      (128-row blocks); copy CTAs pull the peers' row blocks exactly as in mode 1 and the TMA producer waits for
+  //      the flag of every block a B tile touches.  Tiles (K-major B) or k-blocks (MN-major B) that use the local
+  //      shard come first.
+  int tp_mode, tp_rank, tp_world, tp_rows_per_shard, tp_copy_ctas, tp_epoch, tp_row_len;
+  int tp_n_shift, tp_k_shift;   // mode 3: first n tile / k block of the local shard
   int* tp_ready;
   const __nv_bfloat16* const* tp_peer_a;
   long long tp_lda;
@@ -87,7 +92,12 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, int tota
     it.expert = p.expert_of_mtile[tile / p.tiles_n];
     if (it.expert < 0) return false;
   }
-  if (p.tp_mode) {
+  if (p.tp_mode == 3) {
+    // n is the slow index and starts at the local shard's columns
+    it.m0 = (tile % p.tiles_m) * BM;
+    const int nt = tile / p.tiles_m;
+    it.n0 = (nt + p.tp_n_shift) % p.tiles_n;
+  } else if (p.tp_mode) {
     // rotate the row-block order: mode 1 starts with the local shard (already in place), mode 2 ends with it
     const int bps = p.tp_rows_per_shard / BM;
     const int shift = (p.tp_mode == 1 ? p.tp_rank : p.tp_rank + 1) * bps;
@@ -106,7 +116,7 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 // gathered buffer and publishes each block with a release store.
 __device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int ncopy) {
   const int W = p.tp_world, bps = p.tp_rows_per_shard / BM;
-  const long long row_chunks = (long long)p.K / 8;  // 16-byte chunks per row
+  const long long row_chunks = (long long)p.tp_row_len / 8;  // 16-byte chunks per row
   __nv_bfloat16* dst_base = const_cast<__nv_bfloat16*>(p.tp_peer_a[p.tp_rank]);
   for (int idx = cta; idx < (W - 1) * bps; idx += ncopy) {
     const int peer = (p.tp_rank + 1 + idx / bps) % W;
@@ -183,7 +193,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   constexpr uint32_t TMEM_COLS = 2 * BN;
   // copy CTAs take the lowest block indices so that they are scheduled first: a GEMM CTA may wait for a copy
   // CTA, never the other way round
-  const int ncopy = p.tp_mode == 1 ? p.tp_copy_ctas : 0;
+  const int ncopy = (p.tp_mode == 1 || p.tp_mode == 3) ? p.tp_copy_ctas : 0;
   const int nctas = int(gridDim.x) - ncopy;  // CTAs that run GEMM tiles
   const int cta = int(blockIdx.x) - ncopy;
   if (cta < 0) {
@@ -246,7 +256,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes -> visible to the TMA reads below
           }
         }
+        auto wait_block = [&](int blk) -> bool {   // rows of block `blk` owned by a peer must have landed locally
+          if (blk / (p.tp_rows_per_shard / BM) == p.tp_rank) return true;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(p.tp_ready + blk) < p.tp_epoch) {
+            if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - t0 > TFB_WAIT_NS)) {
+              report(p.status, ST_TIMEOUT_FLAG);
+              *abort_flag = 1;
+              return false;
+            }
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+          return true;
+        };
+        if (p.tp_mode == 3 && !B_MN) {
+          for (int r0 = n0; r0 < n0 + BN && r0 < p.N && ok; r0 += BM) ok = wait_block(r0 / BM);
+          if (!ok) break;
+        }
+        int last_blk = -1;
         for (int kb = kb0; kb < kb1; ++kb) {
+          const int kbr = (p.tp_mode == 3 && B_MN) ? (kb + p.tp_k_shift) % total_kb : kb;   // local shard's rows first
+          if (p.tp_mode == 3 && B_MN) {
+            const int blk = kbr * BK / BM;
+            if (blk != last_blk) {
+              if (!wait_block(blk)) { ok = false; break; }
+              last_blk = blk;
+            }
+          }
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -255,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           mbar_expect_tx(fb, L::STAGE_BYTES);
           const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
           const uint32_t sb = sa + L::A_BYTES;
-          const int k0 = kb * BK;
+          const int k0 = kbr * BK;
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tma_a, fb, k0, m0);
           } else {
@@ -612,6 +649,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
     const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
     if (BN == 256 && gmode != 2 && out_mode != 2 && t256 < sms && t128 > t256) BN = 128;
   }
+  if (tp && tp->mode == 3 && !b_mn) BN = 128;   // one ready flag per B tile; tiles stay aligned with the row shards
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, BM);
@@ -651,15 +689,32 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   p.seg_start = grp ? grp->seg_start : nullptr;
   p.c_expert_stride = grp ? grp->c_expert_stride : 0;
   p.tp_mode = 0; p.tp_rank = 0; p.tp_world = 1; p.tp_rows_per_shard = M; p.tp_copy_ctas = 0; p.tp_epoch = 0;
+  p.tp_row_len = K; p.tp_n_shift = 0; p.tp_k_shift = 0;
   p.tp_ready = nullptr; p.tp_peer_a = nullptr; p.tp_lda = lda; p.tp_peer_c = nullptr;
   if (tp) {
-    if (tp->world < 1 || M % (tp->world * BM) || a_mn || out_mode != 0 || gmode != 0) return TFB_ERR_ARG;
-    if (tp->mode == 1 && (K % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms)) return TFB_ERR_ARG;
-    p.tp_mode = tp->mode; p.tp_rank = tp->rank; p.tp_world = tp->world; p.tp_rows_per_shard = M / tp->world;
-    p.tp_copy_ctas = tp->mode == 1 ? tp->copy_ctas : 0; p.tp_epoch = tp->epoch; p.tp_ready = tp->ready;
+    if (tp->world < 1 || gmode != 0) return TFB_ERR_ARG;
+    if (tp->mode == 3) {
+      // gathered B: rows = N (K-major B) or K (MN-major B), sharded in 128-row blocks
+      const int rows = b_mn ? K : N, row_len = b_mn ? N : K;
+      if (rows % (tp->world * BM) || row_len % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms || out_mode == 2) return TFB_ERR_ARG;
+      p.tp_rows_per_shard = rows / tp->world;
+      p.tp_row_len = row_len;
+      p.tp_lda = ldb;
+      if (!b_mn) {
+        p.tp_n_shift = tp->rank * (p.tp_rows_per_shard / BN);
+      } else {
+        p.tp_k_shift = tp->rank * (p.tp_rows_per_shard / BK);
+      }
+    } else {
+      if (M % (tp->world * BM) || a_mn || out_mode != 0) return TFB_ERR_ARG;
+      if (tp->mode == 1 && (K % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms)) return TFB_ERR_ARG;
+      p.tp_rows_per_shard = M / tp->world;
+    }
+    p.tp_mode = tp->mode; p.tp_rank = tp->rank; p.tp_world = tp->world;
+    p.tp_copy_ctas = (tp->mode == 1 || tp->mode == 3) ? tp->copy_ctas : 0; p.tp_epoch = tp->epoch; p.tp_ready = tp->ready;
     p.tp_peer_a = static_cast<const __nv_bfloat16* const*>(tp->peer_a);
     p.tp_peer_c = static_cast<__nv_bfloat16* const*>(tp->peer_c);
-    if (tp->mode == 1) sms -= tp->copy_ctas;
+    if (tp->mode == 1 || tp->mode == 3) sms -= tp->copy_ctas;
   }
   const int total_kb = (K + BK - 1) / BK;
   const int tiles = p.tiles_m * p.tiles_n;
@@ -717,10 +772,11 @@ TFB_API int tfb_gemm_bf16_grouped(const void* A, long long lda, int a_mn, const 
 
 // Tensor-parallel fused forms (see TfbGemmTp and tp_fused.cu).  Mode 1: C[M, N] = gathered A [M, K] . B^T where
 // A's row shards live on the W ranks.  Mode 2: C is ignored; partial products go to the peers' staging buffers
-// (row pitch ldc) and are summed by tfb_tp_reduce.
+// (row pitch ldc) and are summed by tfb_tp_reduce.  Mode 3: B is the gathered weight (tp->peer_a holds the W base
+// addresses of the gather buffers, row-sharded); the peers' shards are pulled while the tiles of the local shard run.
 TFB_API int tfb_gemm_bf16_tp(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* C,
                              long long ldc, int M, int N, int K, const TfbGemmTp* tp, int* status, void* stream) {
-  if (!tp || tp->mode < 1 || tp->mode > 2) return TFB_ERR_ARG;
+  if (!tp || tp->mode < 1 || tp->mode > 3) return TFB_ERR_ARG;
   return gemm_impl(A, lda, 0, B, ldb, b_mn, C, ldc, M, N, K, nullptr, nullptr, 0, 1.0f, 0, 0, 0, nullptr, status,
                    stream, tp);
 }
