@@ -22,6 +22,12 @@ constexpr int AB_THREADS = 192;
 constexpr int AB_BOX = 128 * 64 * 2;
 constexpr float LOG2E = 1.4426950408889634f;
 
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnBwdParams {
   int B, S, Hq, Hkv;
   float scale;
@@ -181,18 +187,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    // per-query statistics of iteration `it` (pre-scaled log-sum-exp and delta); loaded one iteration ahead so that
+    // the global-memory latency hides behind the previous block's arithmetic
+    auto load_stats = [&](int it, float& l2, float& dl) {
       const int h = hk * G + it / n_i, i = i0 + it % n_i;
+      const int qi = i * 128 + r;
+      const long long o = ((long long)b * p.Hq + h) * p.S + qi;
+      l2 = qi < p.S ? p.lse[o] * LOG2E : INFINITY;  // +inf => probability 0 for padded queries
+      dl = qi < p.S ? p.delta[o] : 0.f;
+    };
+    float nxt_l2 = 0.f, nxt_dl = 0.f;
+    if (n_it > 0) load_stats(0, nxt_l2, nxt_dl);
+    for (int it = 0; it < n_it; ++it) {
+      const int i = i0 + it % n_i;
       const uint32_t ph = it & 1;
       float* s_lse = stats + (it & 1) * 256;
       float* s_dl = s_lse + 128;
-      {
-        const int qi = i * 128 + r;
-        const long long o = ((long long)b * p.Hq + h) * p.S + qi;
-        s_lse[r] = qi < p.S ? p.lse[o] * LOG2E : INFINITY;  // +inf => probability 0 for padded queries
-        s_dl[r] = qi < p.S ? p.delta[o] : 0.f;
-      }
+      s_lse[r] = nxt_l2;
+      s_dl[r] = nxt_dl;
       mbar_arrive(bar_stat);
+      if (it + 1 < n_it) load_stats(it + 1, nxt_l2, nxt_dl);
       if (!mbar_wait_warp(bar_stat, ph, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; break; }
       if (!mbar_wait_warp(bar_s, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -204,15 +218,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tmem_ld_32x32(tS + lane_off + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int q0 = c * 32 + 2 * e;
-          float p0 = exp2f(__uint_as_float(v[2 * e]) * sl2 - s_lse[q0]);
-          float p1 = exp2f(__uint_as_float(v[2 * e + 1]) * sl2 - s_lse[q0 + 1]);
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c * 32 + e4 * 4);   // same address in every lane: broadcast
+          const int q0 = c * 32 + e4 * 4;
+          float p0 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 0]), sl2, -l4.x));
+          float p1 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 1]), sl2, -l4.y));
+          float p2 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 2]), sl2, -l4.z));
+          float p3 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 3]), sl2, -l4.w));
           if (diag) {
             if (q0 < r) p0 = 0.f;
             if (q0 + 1 < r) p1 = 0.f;
+            if (q0 + 2 < r) p2 = 0.f;
+            if (q0 + 3 < r) p3 = 0.f;
           }
-          pk[c * 16 + e] = pack_bf16(p0, p1);
+          pk[c * 16 + e4 * 2] = pack_bf16(p0, p1);
+          pk[c * 16 + e4 * 2 + 1] = pack_bf16(p2, p3);
         }
         uint32_t (&chunk)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[c * 16]);
         tmem_st_32x16(tS + lane_off + c * 16, chunk);
@@ -229,11 +249,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tmem_ld_wait();
         uint32_t ds[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int q0 = c * 32 + 2 * e;
-          const float2 pf = unpack_bf16(pk[c * 16 + e]);
-          ds[e] = pack_bf16(pf.x * (__uint_as_float(v[2 * e]) - s_dl[q0]) * p.scale,
-                            pf.y * (__uint_as_float(v[2 * e + 1]) - s_dl[q0 + 1]) * p.scale);
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(s_dl + c * 32 + e4 * 4);
+          const float2 pa = unpack_bf16(pk[c * 16 + e4 * 2]), pb = unpack_bf16(pk[c * 16 + e4 * 2 + 1]);
+          // the softmax scale is applied once to dK when it is written out
+          ds[e4 * 2] = pack_bf16(pa.x * (__uint_as_float(v[e4 * 4 + 0]) - d4.x), pa.y * (__uint_as_float(v[e4 * 4 + 1]) - d4.y));
+          ds[e4 * 2 + 1] = pack_bf16(pb.x * (__uint_as_float(v[e4 * 4 + 2]) - d4.z), pb.y * (__uint_as_float(v[e4 * 4 + 3]) - d4.w));
         }
         tmem_st_32x16(tDP + lane_off + c * 16, ds);
       }
@@ -263,10 +284,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
             u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
             u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
             *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = u;
-            u.x = pack_bf16(__uint_as_float(u2[q * 8 + 0]), __uint_as_float(u2[q * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(u2[q * 8 + 2]), __uint_as_float(u2[q * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(u2[q * 8 + 4]), __uint_as_float(u2[q * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(u2[q * 8 + 6]), __uint_as_float(u2[q * 8 + 7]));
+            const float sc = p.scale;
+            u.x = pack_bf16(__uint_as_float(u2[q * 8 + 0]) * sc, __uint_as_float(u2[q * 8 + 1]) * sc);
+            u.y = pack_bf16(__uint_as_float(u2[q * 8 + 2]) * sc, __uint_as_float(u2[q * 8 + 3]) * sc);
+            u.z = pack_bf16(__uint_as_float(u2[q * 8 + 4]) * sc, __uint_as_float(u2[q * 8 + 5]) * sc);
+            u.w = pack_bf16(__uint_as_float(u2[q * 8 + 6]) * sc, __uint_as_float(u2[q * 8 + 7]) * sc);
             *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = u;
           }
         }
@@ -278,6 +300,31 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dS = P * (dP - delta) for one query row (128 keys): reads S and dP from tensor memory, writes dS (bf16 pairs) over
+// the dP columns.  The softmax scale is folded into the final dQ store.
+template <bool MASK>
+__device__ __forceinline__ void dq_block(uint32_t tS, uint32_t tDP, float sl2, float lse2, float dl, int k0, int k_lim) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t s[32], dp[32];
+    tmem_ld_32x32(tS + c * 32, s);
+    tmem_ld_32x32(tDP + c * 32, dp);
+    tmem_ld_wait();
+    uint32_t ds[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      float p0 = bwd_exp2(fmaf(__uint_as_float(s[2 * e]), sl2, -lse2));
+      float p1 = bwd_exp2(fmaf(__uint_as_float(s[2 * e + 1]), sl2, -lse2));
+      if (MASK) {
+        if (k0 + c * 32 + 2 * e > k_lim) p0 = 0.f;
+        if (k0 + c * 32 + 2 * e + 1 > k_lim) p1 = 0.f;
+      }
+      ds[e] = pack_bf16(p0 * (__uint_as_float(dp[2 * e]) - dl), p1 * (__uint_as_float(dp[2 * e + 1]) - dl));
+    }
+    tmem_st_32x16(tDP + c * 16, ds);
   }
 }
 
@@ -407,26 +454,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const int k0 = j * 128;
       const bool need_mask = (p.causal && j == qb) || (k0 + 128 > p.S);
       const int k_lim = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32(tS + lane_off + c * 32, s);
-        tmem_ld_32x32(tDP + lane_off + c * 32, dp);
-        tmem_ld_wait();
-        uint32_t ds[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float p0 = exp2f(__uint_as_float(s[2 * e]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(s[2 * e + 1]) * sl2 - lse2);
-          if (need_mask) {
-            if (k0 + c * 32 + 2 * e > k_lim) p0 = 0.f;
-            if (k0 + c * 32 + 2 * e + 1 > k_lim) p1 = 0.f;
-          }
-          ds[e] = pack_bf16(p0 * (__uint_as_float(dp[2 * e]) - dl) * p.scale,
-                            p1 * (__uint_as_float(dp[2 * e + 1]) - dl) * p.scale);
-        }
-        tmem_st_32x16(tDP + lane_off + c * 16, ds);
-      }
+      if (need_mask) dq_block<true>(tS + lane_off, tDP + lane_off, sl2, lse2, dl, k0, k_lim);
+      else dq_block<false>(tS + lane_off, tDP + lane_off, sl2, lse2, dl, k0, k_lim);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar_ds);
@@ -443,10 +472,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+            const float sc = p.scale;
+            u.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * sc, __uint_as_float(v[q * 8 + 1]) * sc);
+            u.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * sc, __uint_as_float(v[q * 8 + 3]) * sc);
+            u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * sc, __uint_as_float(v[q * 8 + 5]) * sc);
+            u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * sc, __uint_as_float(v[q * 8 + 7]) * sc);
             *reinterpret_cast<uint4*>(dqp + c * 32 + q * 8) = u;
           }
         }

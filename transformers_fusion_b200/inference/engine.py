@@ -144,9 +144,10 @@ class InferenceEngine:
         r.pages = []
 
     # ------------------------------------------------------------------ model passes
-    def _layers_prefill(self, ids, pos0, r: Request):
+    def _layers_prefill(self, ids, pos0, r: Request, all_positions: bool = False):
         """Prompt tokens ids[pos0:] of one sequence; K/V of all of them go to the pages.  Returns the
-        hidden state of the last token.  (Prefix pages already hold positions < pos0.)"""
+        hidden state of the last token (of every new token with ``all_positions``).  (Prefix pages already hold
+        positions < pos0.)"""
         m, mc = self.model, self.model.cfg
         dev = self.device
         Hq, Hkv, D = mc.num_heads, mc.num_kv_heads, mc.head_dim
@@ -186,7 +187,7 @@ class InferenceEngine:
             h = F.gemm(act, w.down.data, bias=w.down_bias, residual=base)
             if mc.use_parallel_residual:
                 h = h + attn
-        return h[-1:]
+        return h if all_positions else h[-1:]
 
     def _layers_decode(self, tokens, positions, block_table, slots):
         m, mc = self.model, self.model.cfg
