@@ -1,14 +1,19 @@
 // Flash attention backward for sm_100a: exact gradients, probabilities recomputed from the saved
-// log-sum-exp (nothing of size S x S is ever stored).  Two tcgen05 kernels, no atomics:
+// log-sum-exp (nothing of size S x S is ever stored).  Two tcgen05 kernels, no atomics; each runs two compute
+// warpgroups that work on the two halves of a 128 x 128 score block, so that the tensor core computes one half while
+// the other half's exponentials and products are in flight, and every scheduler has two compute warps to issue from.
 //
-//   attn_bwd_dkdv : one CTA per (batch, kv head, 128-key block); loops over the query heads of the
-//                   group and the query blocks that see these keys.  Per step
-//                     S^T = K Q^T, dP^T = V dO^T            (shared-memory operands)
-//                     P^T = exp(S^T - lse), dS^T = P^T * (dP^T - delta) * scale   (one key row per thread)
-//                     dV += P^T dO, dK += dS^T Q            (A operand from TMEM, B MN-major), accumulated in TMEM
-//   attn_bwd_dq   : one CTA per (batch, query head, 128-query block); loops over key blocks:
-//                     S = Q K^T, dP = dO V^T, dS = P * (dP - delta) * scale, dQ += dS K
+//   attn_bwd_dkdv : one CTA per (batch, kv head, 128-key block); loops over the query heads of the group and the
+//                   query blocks that see these keys.  Per step and per half w (64 queries):
+//                     S^T_w = K Q_w^T, dP^T_w = V dO_w^T                       (shared-memory operands, 128 x 64)
+//                     P^T_w = exp(S^T_w - lse), dS^T_w = P^T_w * (dP^T_w - delta)    (one key row per thread)
+//                     dV += P^T_w dO_w, dK += dS^T_w Q_w     (A operand from TMEM, B MN-major), accumulated in TMEM
+//   attn_bwd_dq   : one CTA per (batch, query head, 128-query block); loops over key blocks, half w = 64 keys:
+//                     S_w = Q K_w^T, dP_w = dO V_w^T, dS_w = P_w * (dP_w - delta), dQ += dS_w K_w
 //   attn_delta    : delta[b,h,s] = sum_d dO * O
+// The softmax scale multiplies dK and dQ once, when they are written out.
+// Tensor memory: half w owns columns [128 w, 128 w + 64) for S / P and [128 w + 64, 128 w + 128) for dP / dS; the
+// accumulators start at column 256.
 //
 // The reference's memory-efficient attention backward is approximate
 // (src/trainer/zero_optimizer_mem.cpp:496-574); its autograd attention op (src/model/autograd_functions.cpp:17-226)
@@ -18,8 +23,9 @@
 
 namespace tfb {
 
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 half 0, warps 6-9 half 1
 constexpr int AB_BOX = 128 * 64 * 2;
+constexpr int AB_HALF = 64 * 128;  // byte offset of row 64 inside a 128-row, 128-byte-pitch box
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float bwd_exp2(float x) {
@@ -47,11 +53,23 @@ struct BwdSmem {
   static constexpr int TILE = NB * AB_BOX;
   static constexpr int RES_OFF = 0;              // two resident tiles
   static constexpr int RING_OFF = 2 * TILE;      // 2 stages x 2 tiles
-  static constexpr int STAT_OFF = RING_OFF + 4 * TILE;  // [2][2][128] floats
+  static constexpr int STAT_OFF = RING_OFF + 4 * TILE;  // [2 stages][2 halves][64 lse | 64 delta] floats
   static constexpr int BAR_OFF = STAT_OFF + 2 * 2 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+// 16 output rows x 128 bf16 columns of an accumulator, written by one thread (its row)
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (&v)[32], float sc) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 u;
+    u.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * sc, __uint_as_float(v[q * 8 + 1]) * sc);
+    u.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * sc, __uint_as_float(v[q * 8 + 3]) * sc);
+    u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * sc, __uint_as_float(v[q * 8 + 5]) * sc);
+    u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * sc, __uint_as_float(v[q * 8 + 7]) * sc);
+    *reinterpret_cast<uint4*>(dst + q * 8) = u;
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // dK / dV
@@ -70,15 +88,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   float* stats = reinterpret_cast<float*>(smem + L::STAT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   const uint32_t bar_kv = smem_u32(bars);
-  const uint32_t bar_full = bar_kv + 8;        // [2]
-  const uint32_t bar_empty = bar_full + 16;    // [2]
-  const uint32_t bar_s = bar_empty + 16;       // S^T ready
-  const uint32_t bar_dp = bar_s + 8;           // dP^T ready
-  const uint32_t bar_p = bar_dp + 8;           // P^T written (128 arrivals)
-  const uint32_t bar_ds = bar_p + 8;           // dS^T written (128 arrivals)
-  const uint32_t bar_acc = bar_ds + 8;         // all accumulation done
-  const uint32_t bar_stat = bar_acc + 8;       // per-step lse / delta staged in shared memory (128 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  const uint32_t bar_full = bar_kv + 8;        // [2] Q / dO stage loaded
+  const uint32_t bar_empty = bar_full + 16;    // [2] stage consumed
+  const uint32_t bar_s = bar_empty + 16;       // [2] S^T_w and dP^T_w ready
+  const uint32_t bar_pds = bar_s + 16;         // [2] P^T_w and dS^T_w written (128 arrivals)
+  const uint32_t bar_stat = bar_pds + 16;      // [2] per-step statistics of half w staged (128 arrivals)
+  const uint32_t bar_acc = bar_stat + 16;      // all accumulation done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -97,13 +113,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_full + s * 8, 1);
       mbar_init(bar_empty + s * 8, 1);
+      mbar_init(bar_s + s * 8, 1);
+      mbar_init(bar_pds + s * 8, 128);
+      mbar_init(bar_stat + s * 8, 128);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_dp, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_ds, 128);
     mbar_init(bar_acc, 1);
-    mbar_init(bar_stat, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -115,7 +129,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 256 + D;
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 256 + D;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -145,153 +159,136 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(FMT_BF16, FMT_BF16, false, false, 128, 128);
+      constexpr uint32_t idesc_s = umma_idesc(FMT_BF16, FMT_BF16, false, false, 128, 64);
       constexpr uint32_t idesc_acc = umma_idesc(FMT_BF16, FMT_BF16, false, true, 128, D);
-      bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = it & 1;  // single-buffered barriers flip every iteration
-        if (!mbar_wait(bar_full + st * 8, (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
-        tc_fence_after();
-        const uint32_t sQ = sbase + L::RING_OFF + st * 2 * L::TILE, sDO = sQ + L::TILE;
+      // scores of half w for the step whose Q / dO tiles sit in stage st
+      auto issue_scores = [&](int w, int st) {
+        const uint32_t sQ = sbase + L::RING_OFF + st * 2 * L::TILE + w * AB_HALF, sDO = sQ + L::TILE;
+        const uint32_t tS = tmem_base + w * 128, tDP = tS + 64;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * AB_BOX + (k & 3) * 32;
           umma_f16_ss(tS, umma_smem_desc(sK + off, 16, 1024), umma_smem_desc(sQ + off, 16, 1024), idesc_s, k > 0);
         }
-        umma_commit(bar_s);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * AB_BOX + (k & 3) * 32;
           umma_f16_ss(tDP, umma_smem_desc(sV + off, 16, 1024), umma_smem_desc(sDO + off, 16, 1024), idesc_s, k > 0);
         }
-        umma_commit(bar_dp);
-        if (!mbar_wait(bar_p, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        umma_commit(bar_s + w * 8);
+      };
+      bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, ST_TIMEOUT_FULL) &&
+                (n_it == 0 || mbar_wait(bar_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL));
+      if (ok && n_it > 0) {
         tc_fence_after();
+        issue_scores(0, 0);
+        issue_scores(1, 0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        if (it + 1 < n_it) {
+          if (!mbar_wait(bar_full + ((it + 1) & 1) * 8, ((it + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
+          tc_fence_after();
+        }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16_ts(tDV, tS + k * 8, umma_smem_desc(sDO + k * 2048, AB_BOX, 1024), idesc_acc, (it > 0 || k > 0));
-        if (!mbar_wait(bar_ds, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
-        tc_fence_after();
+        for (int w = 0; w < 2; ++w) {
+          if (!ok) continue;
+          if (!mbar_wait(bar_pds + w * 8, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; continue; }
+          tc_fence_after();
+          const uint32_t sQ = sbase + L::RING_OFF + st * 2 * L::TILE + w * AB_HALF, sDO = sQ + L::TILE;
+          const uint32_t tS = tmem_base + w * 128, tDP = tS + 64;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16_ts(tDK, tDP + k * 8, umma_smem_desc(sQ + k * 2048, AB_BOX, 1024), idesc_acc, (it > 0 || k > 0));
-        umma_commit(bar_empty + st * 8);
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ts(tDV, tS + k * 8, umma_smem_desc(sDO + k * 2048, AB_BOX, 1024), idesc_acc, (it > 0 || w > 0 || k > 0));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ts(tDK, tDP + k * 8, umma_smem_desc(sQ + k * 2048, AB_BOX, 1024), idesc_acc, (it > 0 || w > 0 || k > 0));
+          if (it + 1 < n_it) issue_scores(w, (it + 1) & 1);
+        }
+        if (ok) umma_commit(bar_empty + st * 8);
       }
       umma_commit(bar_acc);
     }
   } else {
+    const int w = (warp - 2) >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int key_idx = jb * 128 + r;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tmem_base + w * 128 + lane_off, tDP = tS + 64;
     const float sl2 = p.scale * LOG2E;
     bool ok = true;
-    // per-query statistics of iteration `it` (pre-scaled log-sum-exp and delta); loaded one iteration ahead so that
-    // the global-memory latency hides behind the previous block's arithmetic
-    auto load_stats = [&](int it, float& l2, float& dl) {
+    // thread r stages one statistic of this half's 64 queries: r < 64 the pre-scaled log-sum-exp of query r, else the
+    // delta of query r - 64.  Loaded one step ahead so that the global-memory latency hides behind the arithmetic.
+    auto load_stat = [&](int it) -> float {
       const int h = hk * G + it / n_i, i = i0 + it % n_i;
-      const int qi = i * 128 + r;
+      const int qi = i * 128 + w * 64 + (r & 63);
       const long long o = ((long long)b * p.Hq + h) * p.S + qi;
-      l2 = qi < p.S ? p.lse[o] * LOG2E : INFINITY;  // +inf => probability 0 for padded queries
-      dl = qi < p.S ? p.delta[o] : 0.f;
+      if (r < 64) return qi < p.S ? p.lse[o] * LOG2E : INFINITY;   // +inf => probability 0 for padded queries
+      return qi < p.S ? p.delta[o] : 0.f;
     };
-    float nxt_l2 = 0.f, nxt_dl = 0.f;
-    if (n_it > 0) load_stats(0, nxt_l2, nxt_dl);
+    float nxt = n_it > 0 ? load_stat(0) : 0.f;
     for (int it = 0; it < n_it; ++it) {
       const int i = i0 + it % n_i;
       const uint32_t ph = it & 1;
-      float* s_lse = stats + (it & 1) * 256;
-      float* s_dl = s_lse + 128;
-      s_lse[r] = nxt_l2;
-      s_dl[r] = nxt_dl;
-      mbar_arrive(bar_stat);
-      if (it + 1 < n_it) load_stats(it + 1, nxt_l2, nxt_dl);
-      if (!mbar_wait_warp(bar_stat, ph, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; break; }
-      if (!mbar_wait_warp(bar_s, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      float* s_lse = stats + ((it & 1) * 2 + w) * 128;
+      float* s_dl = s_lse + 64;
+      s_lse[r] = nxt;
+      mbar_arrive(bar_stat + w * 8);
+      if (it + 1 < n_it) nxt = load_stat(it + 1);
+      if (!mbar_wait_warp(bar_stat + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_s + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && (i == jb);
-      uint32_t pk[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + lane_off + c * 32, v);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tS + c * 32, sv);
+        tmem_ld_32x32(tDP + c * 32, dv);
         tmem_ld_wait();
+        uint32_t pk[16], ds[16];
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
           const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c * 32 + e4 * 4);   // same address in every lane: broadcast
-          const int q0 = c * 32 + e4 * 4;
-          float p0 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 0]), sl2, -l4.x));
-          float p1 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 1]), sl2, -l4.y));
-          float p2 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 2]), sl2, -l4.z));
-          float p3 = bwd_exp2(fmaf(__uint_as_float(v[e4 * 4 + 3]), sl2, -l4.w));
+          const float4 d4 = *reinterpret_cast<const float4*>(s_dl + c * 32 + e4 * 4);
+          const int q0 = w * 64 + c * 32 + e4 * 4;      // query index inside the 128-query block
+          float p0 = bwd_exp2(fmaf(__uint_as_float(sv[e4 * 4 + 0]), sl2, -l4.x));
+          float p1 = bwd_exp2(fmaf(__uint_as_float(sv[e4 * 4 + 1]), sl2, -l4.y));
+          float p2 = bwd_exp2(fmaf(__uint_as_float(sv[e4 * 4 + 2]), sl2, -l4.z));
+          float p3 = bwd_exp2(fmaf(__uint_as_float(sv[e4 * 4 + 3]), sl2, -l4.w));
           if (diag) {
             if (q0 < r) p0 = 0.f;
             if (q0 + 1 < r) p1 = 0.f;
             if (q0 + 2 < r) p2 = 0.f;
             if (q0 + 3 < r) p3 = 0.f;
           }
-          pk[c * 16 + e4 * 2] = pack_bf16(p0, p1);
-          pk[c * 16 + e4 * 2 + 1] = pack_bf16(p2, p3);
+          pk[e4 * 2] = pack_bf16(p0, p1);
+          pk[e4 * 2 + 1] = pack_bf16(p2, p3);
+          ds[e4 * 2] = pack_bf16(p0 * (__uint_as_float(dv[e4 * 4 + 0]) - d4.x), p1 * (__uint_as_float(dv[e4 * 4 + 1]) - d4.y));
+          ds[e4 * 2 + 1] = pack_bf16(p2 * (__uint_as_float(dv[e4 * 4 + 2]) - d4.z), p3 * (__uint_as_float(dv[e4 * 4 + 3]) - d4.w));
         }
-        uint32_t (&chunk)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[c * 16]);
-        tmem_st_32x16(tS + lane_off + c * 16, chunk);
+        tmem_st_32x16(tS + c * 16, pk);
+        tmem_st_32x16(tDP + c * 16, ds);
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_p);
-      if (!mbar_wait_warp(bar_dp, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tDP + lane_off + c * 32, v);
-        tmem_ld_wait();
-        uint32_t ds[16];
-#pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(s_dl + c * 32 + e4 * 4);
-          const float2 pa = unpack_bf16(pk[c * 16 + e4 * 2]), pb = unpack_bf16(pk[c * 16 + e4 * 2 + 1]);
-          // the softmax scale is applied once to dK when it is written out
-          ds[e4 * 2] = pack_bf16(pa.x * (__uint_as_float(v[e4 * 4 + 0]) - d4.x), pa.y * (__uint_as_float(v[e4 * 4 + 1]) - d4.y));
-          ds[e4 * 2 + 1] = pack_bf16(pb.x * (__uint_as_float(v[e4 * 4 + 2]) - d4.z), pb.y * (__uint_as_float(v[e4 * 4 + 3]) - d4.w));
-        }
-        tmem_st_32x16(tDP + lane_off + c * 16, ds);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(bar_ds);
+      mbar_arrive(bar_pds + w * 8);
     }
     if (ok && mbar_wait_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool valid = key_idx < p.S;
       const long long row = (long long)b * p.S + (valid ? key_idx : 0);
-      __nv_bfloat16* dvp = p.dv + row * p.lddv + p.dv_col0 + hk * D;
-      __nv_bfloat16* dkp = p.dk + row * p.lddk + p.dk_col0 + hk * D;
-      // the tensor-memory loads are warp-collective: every lane executes them, only the stores are predicated
+      // half 0 writes dV, half 1 writes dK (scaled).  The tensor-memory loads are warp-collective: every lane executes
+      // them, only the stores are predicated.
+      __nv_bfloat16* dst = w == 0 ? p.dv + row * p.lddv + p.dv_col0 + hk * D : p.dk + row * p.lddk + p.dk_col0 + hk * D;
+      const uint32_t tA = (w == 0 ? tDV : tDK) + lane_off;
+      const float sc = w == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32], u2[32];
-        tmem_ld_32x32(tDV + lane_off + c * 32, v);
-        tmem_ld_32x32(tDK + lane_off + c * 32, u2);
+        uint32_t v[32];
+        tmem_ld_32x32(tA + c * 32, v);
         tmem_ld_wait();
-        if (valid) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-            *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = u;
-            const float sc = p.scale;
-            u.x = pack_bf16(__uint_as_float(u2[q * 8 + 0]) * sc, __uint_as_float(u2[q * 8 + 1]) * sc);
-            u.y = pack_bf16(__uint_as_float(u2[q * 8 + 2]) * sc, __uint_as_float(u2[q * 8 + 3]) * sc);
-            u.z = pack_bf16(__uint_as_float(u2[q * 8 + 4]) * sc, __uint_as_float(u2[q * 8 + 5]) * sc);
-            u.w = pack_bf16(__uint_as_float(u2[q * 8 + 6]) * sc, __uint_as_float(u2[q * 8 + 7]) * sc);
-            *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = u;
-          }
-        }
+        if (valid) store_row32(dst + c * 32, v, sc);
       }
     }
   }
@@ -303,12 +300,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   }
 }
 
-// dS = P * (dP - delta) for one query row (128 keys): reads S and dP from tensor memory, writes dS (bf16 pairs) over
-// the dP columns.  The softmax scale is folded into the final dQ store.
+// ------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------
+// dS = P * (dP - delta) for one query row and one half block (64 keys): reads S and dP from tensor memory, writes dS
+// (bf16 pairs) over the dP columns.
 template <bool MASK>
-__device__ __forceinline__ void dq_block(uint32_t tS, uint32_t tDP, float sl2, float lse2, float dl, int k0, int k_lim) {
-#pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+__device__ __forceinline__ void dq_half_block(uint32_t tS, uint32_t tDP, float sl2, float lse2, float dl, int k0, int k_lim) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
     uint32_t s[32], dp[32];
     tmem_ld_32x32(tS + c * 32, s);
     tmem_ld_32x32(tDP + c * 32, dp);
@@ -328,9 +328,6 @@ __device__ __forceinline__ void dq_block(uint32_t tS, uint32_t tDP, float sl2, f
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// dQ
-// ------------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -344,11 +341,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   const uint32_t sQ = sbase, sDO = sbase + L::TILE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   const uint32_t bar_q = smem_u32(bars);
-  const uint32_t bar_full = bar_q + 8;
+  const uint32_t bar_full = bar_q + 8;     // [2]
   const uint32_t bar_empty = bar_full + 16;
-  const uint32_t bar_s = bar_empty + 16;  // S and dP ready
-  const uint32_t bar_ds = bar_s + 8;      // dS written (128 arrivals)
-  const uint32_t bar_acc = bar_ds + 8;
+  const uint32_t bar_s = bar_empty + 16;   // [2] S_w and dP_w ready
+  const uint32_t bar_ds = bar_s + 16;      // [2] dS_w written (128 arrivals)
+  const uint32_t bar_acc = bar_ds + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -366,9 +363,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_full + s * 8, 1);
       mbar_init(bar_empty + s * 8, 1);
+      mbar_init(bar_s + s * 8, 1);
+      mbar_init(bar_ds + s * 8, 128);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_ds, 128);
     mbar_init(bar_acc, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -381,7 +378,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+  const uint32_t tDQ = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -410,14 +407,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(FMT_BF16, FMT_BF16, false, false, 128, 128);
+      constexpr uint32_t idesc_s = umma_idesc(FMT_BF16, FMT_BF16, false, false, 128, 64);
       constexpr uint32_t idesc_acc = umma_idesc(FMT_BF16, FMT_BF16, false, true, 128, D);
-      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(bar_full + st * 8, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
-        tc_fence_after();
-        const uint32_t sK = sbase + L::RING_OFF + st * 2 * L::TILE, sV = sK + L::TILE;
+      auto issue_scores = [&](int w, int st) {
+        const uint32_t sK = sbase + L::RING_OFF + st * 2 * L::TILE + w * AB_HALF, sV = sK + L::TILE;
+        const uint32_t tS = tmem_base + w * 128, tDP = tS + 64;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * AB_BOX + (k & 3) * 32;
@@ -428,58 +422,71 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
           const uint32_t off = (k >> 2) * AB_BOX + (k & 3) * 32;
           umma_f16_ss(tDP, umma_smem_desc(sDO + off, 16, 1024), umma_smem_desc(sV + off, 16, 1024), idesc_s, k > 0);
         }
-        umma_commit(bar_s);
-        if (!mbar_wait(bar_ds, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        umma_commit(bar_s + w * 8);
+      };
+      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, ST_TIMEOUT_FULL) &&
+                (n_kv == 0 || mbar_wait(bar_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL));
+      if (ok && n_kv > 0) {
         tc_fence_after();
+        issue_scores(0, 0);
+        issue_scores(1, 0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_kv) {
+          if (!mbar_wait(bar_full + ((j + 1) & 1) * 8, ((j + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
+          tc_fence_after();
+        }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16_ts(tDQ, tDP + k * 8, umma_smem_desc(sK + k * 2048, AB_BOX, 1024), idesc_acc, (j > 0 || k > 0));
-        umma_commit(bar_empty + st * 8);
+        for (int w = 0; w < 2; ++w) {
+          if (!ok) continue;
+          if (!mbar_wait(bar_ds + w * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; continue; }
+          tc_fence_after();
+          const uint32_t sK = sbase + L::RING_OFF + st * 2 * L::TILE + w * AB_HALF;
+          const uint32_t tDP = tmem_base + w * 128 + 64;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ts(tDQ, tDP + k * 8, umma_smem_desc(sK + k * 2048, AB_BOX, 1024), idesc_acc, (j > 0 || w > 0 || k > 0));
+          if (j + 1 < n_kv) issue_scores(w, (j + 1) & 1);
+        }
+        if (ok) umma_commit(bar_empty + st * 8);
       }
       umma_commit(bar_acc);
     }
   } else {
+    const int w = (warp - 2) >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int q_idx = qb * 128 + r;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tmem_base + w * 128 + lane_off, tDP = tS + 64;
     const float sl2 = p.scale * LOG2E;
     const long long so = ((long long)b * p.Hq + h) * p.S + q_idx;
     const float lse2 = q_idx < p.S ? p.lse[so] * LOG2E : INFINITY;
     const float dl = q_idx < p.S ? p.delta[so] : 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait_warp(bar_s, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_s + w * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = j * 128;
-      const bool need_mask = (p.causal && j == qb) || (k0 + 128 > p.S);
+      const int k0 = j * 128 + w * 64;
+      const bool need_mask = (p.causal && j == qb) || (k0 + 64 > p.S);
       const int k_lim = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
-      if (need_mask) dq_block<true>(tS + lane_off, tDP + lane_off, sl2, lse2, dl, k0, k_lim);
-      else dq_block<false>(tS + lane_off, tDP + lane_off, sl2, lse2, dl, k0, k_lim);
+      if (need_mask) dq_half_block<true>(tS, tDP, sl2, lse2, dl, k0, k_lim);
+      else dq_half_block<false>(tS, tDP, sl2, lse2, dl, k0, k_lim);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_ds);
+      mbar_arrive(bar_ds + w * 8);
     }
     if (ok && mbar_wait_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
-      __nv_bfloat16* dqp = p.dq + ((long long)b * p.S + q_idx) * p.lddq + p.dq_col0 + h * D;
+      // each half writes D / 2 columns of the row
+      __nv_bfloat16* dqp = p.dq + ((long long)b * p.S + q_idx) * p.lddq + p.dq_col0 + h * D + w * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(tDQ + lane_off + c * 32, v);
+        tmem_ld_32x32(tDQ + lane_off + w * (D / 2) + c * 32, v);
         tmem_ld_wait();
-        if (q_idx < p.S) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            const float sc = p.scale;
-            u.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * sc, __uint_as_float(v[q * 8 + 1]) * sc);
-            u.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * sc, __uint_as_float(v[q * 8 + 3]) * sc);
-            u.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * sc, __uint_as_float(v[q * 8 + 5]) * sc);
-            u.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * sc, __uint_as_float(v[q * 8 + 7]) * sc);
-            *reinterpret_cast<uint4*>(dqp + c * 32 + q * 8) = u;
-          }
-        }
+        if (q_idx < p.S) store_row32(dqp + c * 32, v, p.scale);
       }
     }
   }
