@@ -1,0 +1,100 @@
+import math
+
+import pytest
+import torch
+
+from transformers_fusion_b200.trainer import continual as C
+from transformers_fusion_b200.trainer import hpo_nas as H
+
+
+def objective(c, budget=1.0):
+    # best at lr = 1e-3, weight_decay = 1e-2; more budget = less noise
+    return -((math.log10(c.lr) + 3) ** 2 + 0.3 * (math.log10(c.weight_decay) + 2) ** 2)
+
+
+def test_hpo_methods(tmp_path):
+    for method, n in (("random", 40), ("bayes", 25), ("pbt", 40), ("sha", 27)):
+        e = H.HPOEngine(objective, seed=1)
+        best = e.optimize(n, method)
+        assert abs(math.log10(best.lr) + 3) < 1.0, (method, best.lr)
+        assert e.get_top_k(3)[0].id == best.id and len(e.get_eval_history()) >= min(n, 20)
+    assert e.save_best_configs(str(tmp_path / "b.json"), 3)
+    loaded = H.HPOEngine.load_configs(str(tmp_path / "b.json"))
+    assert len(loaded) == 3 and loaded[0].lr == e.get_top_k(1)[0].lr
+    plan = H.HPOEngine().setup_successive_halving(27, 5)
+    assert plan.configs_per_rung == [27, 9, 3, 1] and plan.budget_per_rung == [1.0, 3.0, 9.0, 27.0]
+    # the surrogate interpolates what it has seen
+    e = H.HPOEngine(objective, seed=2)
+    cs = e.random_search(15)
+    assert abs(e.surrogate_predict(cs[0]) - cs[0].score) < 0.2
+
+
+def test_nas_respects_constraints():
+    hw = H.HardwareConstraints(max_params=60_000_000, enabled=True)
+    nas = H.NASEngine(lambda a: math.log10(a.param_count), H.NASConfig(population=12, generations=8), hw, seed=3)
+    best = nas.search()
+    assert best.param_count <= 1.3 * hw.max_params and best.param_count > 5_000_000     # grows up to the limit, not past it
+    a = nas.random_architecture()
+    b = nas.mutate(a, H.NASMutateOp.ADD_LAYER)
+    assert b.num_layers == a.num_layers + 1 and b.param_count > a.param_count and b.id != a.id
+    c = nas.mutate(a, H.NASMutateOp.CHANGE_HEADS)
+    assert c.hidden_size % c.num_heads == 0
+    cfg = nas.to_transformer_config(best)
+    assert cfg.hidden_size == best.hidden_size and cfg.num_layers == best.num_layers
+
+
+def test_replay_and_ecc():
+    buf = C.CompressedReplayBuffer(capacity=10, spill_threshold=0.5)
+    for i in range(12):
+        buf.insert(torch.full((8,), float(i)), torch.arange(8.0), task_id=i % 2, fisher_importance=float(i + 1))
+    assert buf.size() <= 10 and min(e.fisher_importance for e in buf.entries) >= 6     # low-importance entries were dropped
+    ins, tgs, ws = buf.sample_batch(4)
+    assert len(ins) == 4 and torch.allclose(tgs[0], torch.arange(8.0), atol=0.02) and abs(sum(ws) / 4 - 1) < 1e-6
+    assert buf.compression_ratio() > 1.3           # 8-element samples: the 32-byte entry header dominates; long samples approach 4x
+    ecc = C.ECCState()
+    ecc.initialize(4)
+    ecc.update_anchor(torch.zeros(4))
+    ecc.update_fisher(torch.tensor([1.0, 0.0, 2.0, 0.0]), 1.0)
+    w = torch.ones(4)
+    assert ecc.regularize(w, 2.0) == pytest.approx(5.0) and ecc.penalty_grad(w, 2.0).tolist() == [2.0, 0.0, 8.0, 0.0]
+
+
+def test_engine_lr_governor_and_metrics():
+    eng = C.ContinualEngine(C.ContinualEngineConfig(forgetting_threshold=0.1))
+    w = torch.zeros(6)
+    assert eng.on_step(torch.ones(6), w, 1e-3, 0) == 1e-3
+    eng.on_task_boundary(1, w, baseline_loss=1.0, untrained_loss=3.0)
+    eng.register_eval(0, 1.5)                                  # task 0 got worse by 0.5 > threshold
+    assert eng.effective_lr(1e-3) == pytest.approx(5e-4)
+    m = eng.forgetting_metrics()
+    assert m.avg_forgetting == pytest.approx(0.5) and m.backward_transfer == pytest.approx(-0.5) and m.forward_transfer == pytest.approx(2.0)
+    eng.register_eval(0, 1.0)
+    assert eng.effective_lr(1e-3) == pytest.approx(2e-3)       # nothing forgotten: more plasticity
+    g = eng.regularized_grads(torch.zeros(6), torch.ones(6))
+    assert float(g.sum()) > 0
+
+
+def test_projection_watchdog_entropy():
+    w = torch.tensor([1.0, 0.0, 0.0])
+    u = torch.tensor([0.5, 0.2, -0.1])
+    C.apply_orthogonal_projection(u, w)
+    assert abs(float(u @ w)) < 1e-7 and u[1] == pytest.approx(0.2)
+    wd = C.DistributionWatchdog(2.0)
+    layer = torch.nn.Parameter(torch.randn(1000))
+    wd.track_layer(0, layer)
+    good = layer.detach().clone()
+    layer.data.mul_(5.0)
+    wd.track_layer(0, layer)
+    assert not wd.check_health()[0].is_healthy
+    wd.rollback(0, layer)
+    assert torch.equal(layer.data, good)
+    x = torch.zeros(100)
+    assert not C.apply_entropy_floor(2.0, x, torch.rand(100))
+    x = torch.randn(100)
+    y = x.clone()
+    assert C.apply_entropy_floor(0.1, y, torch.arange(100.0), generator=torch.Generator().manual_seed(0))
+    assert (y != x).sum() > 30 and torch.equal(y[60:], x[60:])
+    rb = C.ExperienceReplayBuffer(3, 2)
+    for i in range(5):
+        rb.add(i, -i)
+    assert rb.size() == 3 and rb.should_replay(4) and not rb.should_replay(3) and len(rb.sample_batch(2)[0]) == 2
