@@ -1,0 +1,79 @@
+import pytest
+import torch
+
+from transformers_fusion_b200.quant import engines as E
+
+
+def test_codebook_train_and_serialize():
+    torch.manual_seed(0)
+    x = torch.randn(50000) * 0.3
+    errs = []
+    for bits in (3, 4, 6, 8):
+        cb = E.Codebook(bits)
+        e0 = E.quant_error(x, cb.dequantize(cb.quantize(x)))
+        cb.train(x)
+        e1 = E.quant_error(x, cb.dequantize(cb.quantize(x)))
+        assert e1 < e0 and cb.centroids.numel() == 1 << bits and bool((cb.centroids[1:] >= cb.centroids[:-1]).all())
+        errs.append(e1)
+        cb2 = E.Codebook.deserialize(cb.serialize())
+        assert len(cb.serialize()) == cb.serialized_size()
+        assert torch.allclose(cb2.centroids, cb.centroids, atol=2e-3 if bits < 8 else 0)
+    assert errs == sorted(errs, reverse=True)          # more bits, less error
+    cb = E.CodebookQ4().train(x)
+    before = cb.centroids.clone()
+    cb.ema_update(x + 0.5, cb.quantize(x), 0.5)
+    assert float((cb.centroids - before).mean()) == pytest.approx(0.25, abs=0.02)
+
+
+def test_vector_quantizer():
+    torch.manual_seed(1)
+    centers = torch.randn(8, 4) * 3
+    x = centers[torch.randint(0, 8, (2000,))] + 0.05 * torch.randn(2000, 4)
+    vq = E.VectorQuantizer(8, 4).train(x)
+    q, idx, loss = vq.forward(x.clone().requires_grad_())
+    assert float(loss.detach()) < 0.1 and idx.shape == (2000,) and q.requires_grad
+    q.sum().backward()                                   # straight-through
+
+
+def test_engines_roundtrip_and_snr():
+    torch.manual_seed(2)
+    w = torch.randn(1000, 70) * 0.05
+    snr = {}
+    for name, eng in (("q8", E.Q8Engine()), ("q4", E.Q4Engine()), ("q2", E.Q2Engine())):
+        eng.train_codebook_per_block(w)
+        snr[name] = E.quant_snr(w, eng.roundtrip(w))
+    assert snr["q8"] > 30 and snr["q8"] > snr["q4"] > snr["q2"] > 3
+    st = E.Q4Engine(stochastic=True).train_codebook_per_block(w)
+    avg = torch.stack([st.roundtrip(w[:64]) for _ in range(200)]).mean(0)
+    det = E.Q4Engine().train_codebook_per_block(w).roundtrip(w[:64])
+    assert E.quant_error(w[:64], avg) < 0.5 * E.quant_error(w[:64], det)       # stochastic rounding is unbiased
+    t = E.QuantEngine()
+    p, s = t.quantize(w)
+    d = t.dequantize(p, s, w.numel()).view(w.shape)
+    assert p.numel() == ((w.numel() + 127) // 128 * 128) // 4 and set(torch.unique(torch.round(d.reshape(-1)[:128] / s[0])).tolist()) <= {-1.0, 0.0, 1.0}
+    a = torch.randn(3, 70)
+    assert torch.allclose(t.quant_gemm(a, p, s, 3, 1000, 70), a @ d.t(), atol=1e-5)
+    q, sc = t.quantize_per_channel(w, 0)
+    assert q.shape == w.shape and sc.shape == (1000,) and t.dequantize_per_channel(q, sc, 0).shape == w.shape
+    b, sc1 = E.Q1Engine().quantize(w)
+    d1 = E.Q1Engine().dequantize(b, sc1, w.numel())
+    assert torch.equal(torch.sign(d1), torch.where(w.view(-1) >= 0, 1.0, -1.0)) and E.quant_snr(w, d1.view(w.shape)) > 2
+    assert E.Q32Engine().dequantize(E.Q32Engine().quantize(w)).equal(w)
+    assert E.quant_snr(w, E.Q16Engine().dequantize(E.Q16Engine().quantize(w))) > 60
+
+
+def test_fp8_and_quant8():
+    torch.manual_seed(3)
+    x = torch.randn(64, 32) * 10
+    for kind, tol in (("e4m3", 0.07), ("e5m2", 0.13)):
+        q, s = E.fp8_quantize(x, kind)
+        assert float((E.fp8_dequantize(q, s) - x).abs().max() / x.abs().max()) < tol
+    q, s = E.fp8_quantize(x, "e4m3", per_channel_dim=0)
+    assert s.shape == (64, 1) and float(q.float().abs().max()) <= 448
+    big, _ = E.fp8_quantize(torch.tensor([1e9, -1e9, 1.0]), "e4m3")
+    assert torch.isfinite(big.float()).all()                # e4m3 has no infinities: saturates at 448
+    a, b = torch.randn(8, 32), torch.randn(5, 32)
+    assert float((E.fp8_quant_gemm(a, b) - a @ b.t()).abs().max()) < 0.8
+    for sym in (False, True):
+        q, s, zp = E.quant8_quantize_tensor(x, sym)
+        assert float((E.quant8_dequantize_tensor(q, s, zp) - x).abs().max()) <= s * 0.51 + 1e-6

@@ -1,0 +1,342 @@
+"""Codebooks and per-width quantisation engines (tensor level, on the tensor's own device).
+
+* ``Codebook(bits)``        - scalar codebook with 2^bits fp32 centroids: Lloyd training (quantile init), nearest-centroid
+  ``quantize``, ``dequantize``, EMA update from assignments, (de)serialisation.  ``CodebookQ3/Q4/Q6/Q8/Q12`` fix the width.
+* ``VectorQuantizer``       - k-means codebook over d-dimensional sub-vectors with straight-through forward.
+* ``Q8Engine / Q4Engine / Q2Engine`` - codebook + per-block scale with optional stochastic rounding between neighbours.
+* ``QuantEngine``           - ternary {-1, 0, +1} x per-block (128) scale, 2-bit packed, ``quant_gemm``.
+* ``Q1Engine``              - sign x mean |w|.   ``Q16Engine / Q32Engine`` - fp16 round trip / identity.
+* fp8: ``fp8_quantize(x, "e4m3" | "e5m2")`` (max 448, no infinities / max 57344), per-channel variants, ``fp8_quant_gemm``.
+* ``quant_error`` (MSE) and ``quant_snr`` (dB).
+* ``quant8_quantize_tensor`` - the engines/quant facade: asymmetric uint8 affine or symmetric absmax.
+
+Reference counterparts: src/codec/codebook.cpp, vector_quantizer.cpp, quant_engines_{core,fp,quant,quant1,quant2,quant4,quant8}.cpp,
+include/quant/quant_engines.h, engines/quant/quantize.cpp."""
+from __future__ import annotations
+
+import math
+import struct
+from typing import Optional, Tuple
+
+import torch
+
+
+def quant_error(a, b) -> float:
+    return float(((a.float() - b.float()) ** 2).mean())
+
+
+def quant_snr(a, b) -> float:
+    n = float(((a.float() - b.float()) ** 2).sum())
+    return float("inf") if n == 0 else 10.0 * math.log10(float((a.float() ** 2).sum()) / n)
+
+
+class Codebook:
+    def __init__(self, bits: int, device="cpu"):
+        self.bits, self.K = bits, 1 << bits
+        p = (torch.arange(self.K, dtype=torch.float64) + 0.5) / self.K
+        c = torch.erfinv(2 * p - 1) * math.sqrt(2.0)
+        self.centroids = (c / c.abs().max()).float().to(device)
+
+    def train(self, data: torch.Tensor, iters: int = 30, max_samples: int = 1 << 20):
+        """Lloyd's algorithm from a quantile initialisation."""
+        x = data.detach().float().reshape(-1)
+        if x.numel() > max_samples:
+            x = x[torch.randint(0, x.numel(), (max_samples,), device=x.device)]
+        q = (torch.arange(self.K, device=x.device, dtype=torch.float32) + 0.5) / self.K
+        c = torch.quantile(x[: min(x.numel(), 1 << 18)], q)
+        cur = torch.sort(self.centroids.to(x.device)).values
+
+        def mse(cc):
+            return float(((cc[torch.bucketize(x, (cc[1:] + cc[:-1]) / 2)] - x) ** 2).mean())
+        if mse(cur) < mse(c):             # Lloyd only ever lowers the error, so start from the better of the two
+            c = cur
+        for _ in range(iters):
+            idx = torch.bucketize(x, (c[1:] + c[:-1]) / 2)
+            s = torch.zeros(self.K, device=x.device).index_add_(0, idx, x)
+            n = torch.zeros(self.K, device=x.device).index_add_(0, idx, torch.ones_like(x))
+            new = torch.where(n > 0, s / n.clamp(min=1), c)
+            new, _ = torch.sort(new)
+            if float((new - c).abs().max()) < 1e-7:
+                c = new
+                break
+            c = new
+        self.centroids = c
+        return self
+
+    def quantize(self, x: torch.Tensor) -> torch.Tensor:
+        c = self.centroids.to(x.device)
+        idx = torch.bucketize(x.float().contiguous(), (c[1:] + c[:-1]) / 2)
+        return idx.to(torch.uint8 if self.bits <= 8 else torch.int16)
+
+    def dequantize(self, idx: torch.Tensor) -> torch.Tensor:
+        return self.centroids.to(idx.device)[idx.long()]
+
+    def ema_update(self, data: torch.Tensor, assign: torch.Tensor, lr: float):
+        """Move every centroid towards the mean of the values assigned to it."""
+        x, a = data.float().reshape(-1), assign.long().reshape(-1)
+        s = torch.zeros(self.K, device=x.device).index_add_(0, a, x)
+        n = torch.zeros(self.K, device=x.device).index_add_(0, a, torch.ones_like(x))
+        c = self.centroids.to(x.device)
+        self.centroids = torch.where(n > 0, (1 - lr) * c + lr * s / n.clamp(min=1), c)
+
+    def serialize(self) -> bytes:
+        fmt = "<f" if self.bits >= 8 else "<e"
+        body = b"".join(struct.pack(fmt, float(v)) for v in self.centroids.cpu())
+        return struct.pack("<BI", self.bits, self.K) + body
+
+    @classmethod
+    def deserialize(cls, raw: bytes):
+        bits, K = struct.unpack_from("<BI", raw, 0)
+        cb = cls(bits)
+        fmt, sz = ("<f", 4) if bits >= 8 else ("<e", 2)
+        cb.centroids = torch.tensor([struct.unpack_from(fmt, raw, 5 + i * sz)[0] for i in range(K)])
+        return cb
+
+    def serialized_size(self):
+        return 5 + self.K * (4 if self.bits >= 8 else 2)
+
+
+def CodebookQ3(device="cpu"): return Codebook(3, device)
+def CodebookQ4(device="cpu"): return Codebook(4, device)
+def CodebookQ6(device="cpu"): return Codebook(6, device)
+def CodebookQ8(device="cpu"): return Codebook(8, device)
+def CodebookQ12(device="cpu"): return Codebook(12, device)
+
+
+class VectorQuantizer:
+    def __init__(self, num_codes: int, dim: int, device="cpu", seed=0):
+        g = torch.Generator().manual_seed(seed)
+        self.codes = torch.randn(num_codes, dim, generator=g).to(device)
+        self.dim = dim
+
+    def train(self, data: torch.Tensor, iters=20):
+        x = data.detach().float().reshape(-1, self.dim)
+        K = self.codes.shape[0]
+        # farthest-first initialisation: every new code is the sample farthest from the codes chosen so far
+        sub = x[: min(x.shape[0], 1 << 16)]
+        codes = [sub[0]]
+        dmin = ((sub - codes[0]) ** 2).sum(1)
+        for _ in range(K - 1):
+            codes.append(sub[int(dmin.argmax())])
+            dmin = torch.minimum(dmin, ((sub - codes[-1]) ** 2).sum(1))
+        self.codes = torch.stack(codes).clone()
+        for _ in range(iters):
+            idx = torch.cdist(x, self.codes).argmin(1)
+            s = torch.zeros_like(self.codes).index_add_(0, idx, x)
+            n = torch.zeros(K, device=x.device).index_add_(0, idx, torch.ones(x.shape[0], device=x.device))
+            self.codes = torch.where(n[:, None] > 0, s / n[:, None].clamp(min=1), self.codes)
+        return self
+
+    def encode(self, x):
+        return torch.cdist(x.float().reshape(-1, self.dim), self.codes.to(x.device)).argmin(1)
+
+    def decode(self, idx, shape=None):
+        y = self.codes.to(idx.device)[idx]
+        return y.reshape(shape) if shape is not None else y
+
+    def forward(self, x):
+        """(quantised with straight-through gradient, indices, commitment loss)."""
+        idx = self.encode(x)
+        q = self.decode(idx, x.shape).to(x.dtype)
+        return x + (q - x).detach(), idx, ((q.detach() - x) ** 2).mean()
+
+
+class _CodebookEngine:
+    bits = 8
+
+    def __init__(self, block_size: int = 256, stochastic: bool = False, seed: int = 0):
+        self.cb = Codebook(self.bits)
+        self.block, self.stochastic = block_size, stochastic
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def train_codebook(self, data):
+        x = data.detach().float().reshape(-1)
+        self.cb.train(x / x.abs().max().clamp(min=1e-30))
+        return self
+
+    def train_codebook_per_block(self, data, block_size=None, lloyd_iters=30):
+        bs = block_size or self.block
+        x = data.detach().float().reshape(-1)
+        n = x.numel() // bs * bs
+        blk = x[:n].view(-1, bs)
+        self.cb.train((blk / blk.abs().amax(1, keepdim=True).clamp(min=1e-30)).reshape(-1), lloyd_iters)
+        return self
+
+    def quantize(self, w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(indices uint8 [n], per-block scales [nblocks])."""
+        x = w.detach().float().reshape(-1)
+        nb = (x.numel() + self.block - 1) // self.block
+        pad = torch.zeros(nb * self.block, device=x.device)
+        pad[: x.numel()] = x
+        blk = pad.view(nb, self.block)
+        s = blk.abs().amax(1).clamp(min=1e-30)
+        u = blk / s[:, None]
+        c = self.cb.centroids.to(x.device)
+        idx = torch.bucketize(u.contiguous(), (c[1:] + c[:-1]) / 2)
+        if self.stochastic:
+            lo = torch.where(c[idx] > u, (idx - 1).clamp(min=0), idx)
+            hi = (lo + 1).clamp(max=self.cb.K - 1)
+            span = (c[hi] - c[lo]).clamp(min=1e-12)
+            p_hi = ((u - c[lo]) / span).clamp(0, 1)
+            r = torch.rand(u.shape, generator=self.gen).to(x.device)
+            idx = torch.where(r < p_hi, hi, lo)
+        return idx.view(-1)[: x.numel()].to(torch.uint8), s
+
+    def dequantize(self, idx, scales, n=None):
+        n = n or idx.numel()
+        nb = scales.numel()
+        pad = torch.zeros(nb * self.block, dtype=torch.long, device=idx.device)
+        pad[: idx.numel()] = idx.long()
+        v = self.cb.centroids.to(idx.device)[pad].view(nb, self.block) * scales[:, None]
+        return v.view(-1)[:n]
+
+    def roundtrip(self, w):
+        i, s = self.quantize(w)
+        return self.dequantize(i, s, w.numel()).view(w.shape)
+
+
+class Q8Engine(_CodebookEngine):
+    bits = 8
+
+
+class Q4Engine(_CodebookEngine):
+    bits = 4
+
+
+class Q2Engine(_CodebookEngine):
+    bits = 2
+
+
+class QuantEngine:
+    """Ternary weights: per block of 128, scale = mean |w|, code = sign(w) where |w| > scale / 2 else 0; 2 bits packed."""
+
+    def __init__(self, block_size=128):
+        self.block = block_size
+
+    def quantize(self, w) -> Tuple[torch.Tensor, torch.Tensor]:
+        x = w.detach().float().reshape(-1)
+        nb = (x.numel() + self.block - 1) // self.block
+        pad = torch.zeros(nb * self.block, device=x.device)
+        pad[: x.numel()] = x
+        blk = pad.view(nb, self.block)
+        s = blk.abs().mean(1).clamp(min=1e-30)
+        t = torch.where(blk > 0.5 * s[:, None], 2, torch.where(blk < -0.5 * s[:, None], 0, 1)).to(torch.uint8).view(-1)
+        t = torch.nn.functional.pad(t, (0, (-t.numel()) % 4))
+        packed = t[0::4] | (t[1::4] << 2) | (t[2::4] << 4) | (t[3::4] << 6)
+        return packed, s
+
+    def dequantize(self, packed, scales, n):
+        t = torch.stack([packed & 3, (packed >> 2) & 3, (packed >> 4) & 3, packed >> 6], -1).reshape(-1).float() - 1
+        nb = scales.numel()
+        return (t[: nb * self.block].view(nb, self.block) * scales[:, None]).view(-1)[:n]
+
+    quantize_batch = quantize
+
+    def dequantize_batch(self, q):
+        return self.dequantize(q[0], q[1], q[0].numel() * 4)
+
+    def quant_gemm(self, a, b_packed, b_scales, M, N, K):
+        """a [M, K] @ dequant(b)[N, K]^T."""
+        b = self.dequantize(b_packed, b_scales, N * K).view(N, K)
+        return a.float().view(M, K) @ b.t()
+
+    def quantize_per_channel(self, t, channel_dim=0):
+        x = t.detach().float().transpose(0, channel_dim).contiguous()
+        s = x.reshape(x.shape[0], -1).abs().mean(1).clamp(min=1e-30)
+        shp = [-1] + [1] * (x.dim() - 1)
+        q = torch.where(x > 0.5 * s.view(shp), 1, torch.where(x < -0.5 * s.view(shp), -1, 0)).to(torch.int8)
+        return q.transpose(0, channel_dim), s
+
+    def dequantize_per_channel(self, q, scales, channel_dim=0):
+        shp = [1] * q.dim()
+        shp[channel_dim] = -1
+        return q.float() * scales.view(shp)
+
+    quant_error = staticmethod(quant_error)
+    quant_snr = staticmethod(quant_snr)
+
+
+class Q1Engine:
+    """One bit per weight: sign, with one scale (mean |w|) per tensor or per channel; 8 signs per byte."""
+
+    def quantize(self, w):
+        x = w.detach().float().reshape(-1)
+        scale = float(x.abs().mean())
+        bits = (x >= 0).to(torch.uint8)
+        bits = torch.nn.functional.pad(bits, (0, (-bits.numel()) % 8)).view(-1, 8)
+        packed = (bits << torch.arange(8, device=x.device, dtype=torch.uint8)).sum(1).to(torch.uint8)
+        return packed, scale
+
+    def dequantize(self, packed, scale, n):
+        bits = ((packed[:, None] >> torch.arange(8, device=packed.device, dtype=torch.uint8)) & 1).reshape(-1)[:n]
+        return (bits.float() * 2 - 1) * scale
+
+    def quant_gemm(self, a, b_packed, b_scale, M, N, K):
+        return a.float().view(M, K) @ self.dequantize(b_packed, b_scale, N * K).view(N, K).t()
+
+    def quantize_per_channel(self, t, channel_dim=0):
+        x = t.detach().float().transpose(0, channel_dim)
+        s = x.reshape(x.shape[0], -1).abs().mean(1)
+        return torch.where(x >= 0, 1, -1).to(torch.int8).transpose(0, channel_dim), s
+
+    quant_error = staticmethod(quant_error)
+    quant_snr = staticmethod(quant_snr)
+
+
+class Q16Engine:
+    def quantize(self, w):
+        return w.detach().to(torch.float16)
+
+    def dequantize(self, q):
+        return q.float()
+
+
+class Q32Engine:
+    def quantize(self, w):
+        return w.detach().float().clone()
+
+    def dequantize(self, q):
+        return q
+
+
+_FP8 = {"e4m3": (torch.float8_e4m3fn, 448.0), "e5m2": (torch.float8_e5m2, 57344.0)}
+
+
+def fp8_quantize(x: torch.Tensor, kind="e4m3", per_channel_dim: Optional[int] = None):
+    """(fp8 tensor, scale): x ~ fp8 * scale with the scale mapping the (per-channel) absmax onto the format's maximum."""
+    dt, mx = _FP8[kind]
+    f = x.detach().float()
+    if per_channel_dim is None:
+        s = f.abs().max().clamp(min=1e-30) / mx
+    else:
+        dims = [d for d in range(f.dim()) if d != per_channel_dim]
+        s = f.abs().amax(dims, keepdim=True).clamp(min=1e-30) / mx
+    return (f / s).clamp(-mx, mx).to(dt), s
+
+
+def fp8_dequantize(q, scale):
+    return q.float() * scale
+
+
+def fp8_quant_gemm(a, b, kind="e4m3"):
+    """a [M, K] @ b [N, K]^T with both operands rounded to fp8 (per-tensor scales); the block-scaled tensor-core version
+    lives in quant/fp8.py."""
+    qa, sa = fp8_quantize(a, kind)
+    qb, sb = fp8_quantize(b, kind)
+    return (qa.float() @ qb.float().t()) * (sa * sb)
+
+
+def quant8_quantize_tensor(t: torch.Tensor, symmetric=False):
+    """uint8 affine (scale, zero point) or int8 absmax quantisation of a whole tensor: (q, scale, zero_point)."""
+    f = t.detach().float()
+    if symmetric:
+        s = float(f.abs().max()) / 127.0 or 1.0
+        return torch.clamp(torch.round(f / s), -127, 127).to(torch.int8), s, 0
+    lo, hi = float(f.min()), float(f.max())
+    s = (hi - lo) / 255.0 or 1.0
+    zp = int(round(-lo / s))
+    return torch.clamp(torch.round(f / s) + zp, 0, 255).to(torch.uint8), s, zp
+
+
+def quant8_dequantize_tensor(q, scale, zero_point=0):
+    return (q.float() - zero_point) * scale
