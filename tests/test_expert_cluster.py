@@ -1,0 +1,93 @@
+import time
+
+import pytest
+import torch
+
+from transformers_fusion_b200.parallel import expert_cluster as X
+from transformers_fusion_b200.parallel.fault import ClusterConfig
+
+
+def test_dispatch_roundtrip_matches_dense_mixture():
+    torch.manual_seed(0)
+    T, H, E, k = 40, 8, 6, 2
+    d = X.ExpertDispatcher(E, num_nodes=3, node_id=1, top_k=k, hidden=H)
+    assert d.assignment == [[0, 1], [2, 3], [4, 5]]
+    x, logits = torch.randn(T, H), torch.randn(T, E)
+    W = torch.randn(E, H, H)
+    r = d.route_tokens(logits)
+    assert torch.allclose(r.expert_weights.sum(-1), torch.ones(T)) and int(r.tokens_per_expert.sum()) == T * k
+    assert int(r.tokens_per_node.sum()) == T * k
+    disp = d.dispatch_tokens(x, r)
+    outs = {n: torch.stack([rows[i] @ W[int(e)] for i, e in enumerate(eids)]) if len(eids) else torch.zeros(0, H)
+            for n, (rows, eids, _) in disp.items()}
+    y = d.gather_results(outs, disp, r, T)
+    ref = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            ref[t] += r.expert_weights[t, j] * (x[t] @ W[int(r.expert_indices[t, j])])
+    assert torch.allclose(y, ref, atol=1e-5)
+    plan = d.plan_all_to_all(r, [[0, 3, 0], r.tokens_per_node.tolist(), [0, 5, 0]])
+    assert plan.send_counts == r.tokens_per_node.tolist() and plan.recv_counts == [3, int(r.tokens_per_node[1]), 5]
+    assert plan.total_bytes == (plan.send_counts[0] + plan.send_counts[2]) * H * 4
+    lb, z = d.compute_load_balance(r)
+    assert lb > 0.9 and z > 0
+    d.redistribute_expert(5, 0)
+    assert d.assignment[0] == [0, 1, 5] and int(d.owner[5]) == 0
+
+
+def test_load_metrics():
+    even = X.LoadBalanceMetrics.compute([10, 10, 10, 10])
+    skew = X.LoadBalanceMetrics.compute([40, 0, 0, 0])
+    assert even.cv == 0 and abs(even.gini) < 1e-9 and even.entropy == pytest.approx(1.3862943, rel=1e-5)
+    assert skew.cv > 1.5 and skew.gini == pytest.approx(0.75) and skew.entropy == 0
+    h = X.RoutingHistogram(4)
+    h.update(torch.tensor([[0, 1], [0, 2]]))
+    assert h.counts.tolist() == [2, 1, 1, 0] and h.utilization() == 0.75
+
+
+def test_cluster_join_heartbeat_failure_and_grad_sync(tmp_path):
+    cfg = ClusterConfig(heartbeat_interval_ms=50, fault_timeout_ms=2000)
+    a, b = X.ExpertParallelManager(cfg, 8), X.ExpertParallelManager(cfg, 8)
+    pa = a.init_cluster(0)
+    pb = b.init_cluster(1)
+    try:
+        assert b.join_cluster("127.0.0.1", pa) and a.join_cluster("127.0.0.1", pb)
+        a.process_messages(0.3), b.process_messages(0.3)
+        assert a.assignment == {0: [0, 1, 2, 3], 1: [4, 5, 6, 7]} and b.local_experts() == [4, 5, 6, 7]
+        b.send_heartbeats()
+        assert a.process_messages(0.3) >= 1 and a.check_failures() == []
+        # gradient averaging over the control plane
+        import threading
+        res = {}
+        t = threading.Thread(target=lambda: res.setdefault("b", b.sync_gradients(torch.full((4,), 3.0))))
+        t.start()
+        ga = a.sync_gradients(torch.full((4,), 1.0))
+        t.join()
+        assert torch.allclose(ga, torch.full((4,), 2.0)) and torch.allclose(res["b"], torch.full((4,), 2.0))
+        # node 1 goes silent (host-side fault): after the timeout its experts move to node 0
+        dead = a.check_failures(now=time.time() + 5.0)
+        assert dead == [1] and a.assignment == {0: list(range(8))} and all(src is None for _, src, _ in a.last_moves)
+        a.checkpoint_experts(str(tmp_path / "e.pt"), {0: {"w": torch.ones(2)}})
+        c = X.ExpertParallelManager(cfg, 8)
+        ex = c.restore_experts(str(tmp_path / "e.pt"))
+        assert c.assignment == {0: list(range(8))} and torch.equal(ex[0]["w"], torch.ones(2)) and c.ft.failed == [1]
+        # the node comes back
+        b.send_heartbeats()
+        a.process_messages(0.3)
+        assert a.ft.failed == [] and a.assignment[1] == [4, 5, 6, 7]
+    finally:
+        a.comm.close(), b.comm.close()
+
+
+def test_tcp_backend_rejects_foreign_bytes():
+    s = X.TCPCommBackend(0, timeout_s=0.5)
+    port = s.listen()
+    import socket
+    c = socket.create_connection(("127.0.0.1", port))
+    c.sendall(b"GET / HTTP/1.1\r\n" + b"x" * 80)
+    c.close()
+    good = X.TCPCommBackend(1, timeout_s=0.5)
+    assert good.send(("127.0.0.1", port), X.MSG_TOKEN_DATA, b"z" * 200000)
+    m = s.recv(X.MSG_TOKEN_DATA, 2.0)
+    assert m is not None and m[1] == 1 and len(m[3]) == 200000 and s.recv(None, 0.1) is None
+    s.close(), good.close()
