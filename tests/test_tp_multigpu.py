@@ -38,3 +38,23 @@ def test_split_helpers():
     assert tp.partition_heads(8, 4, 3) == [6, 7] and tp.partition_heads(5, 4, 3) == []
     v = tp.communication_volume(4096, 4096, 4096, 2)
     assert v["all_gather"] == 2048 * 4096 * 2 and v["total"] == 2 * v["all_gather"]
+
+
+def test_tensor_parallel_manager_api():
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.parallel import tp
+    cfg = TransformerConfig(vocab_size=64, hidden_size=64, num_layers=1, num_heads=4, num_kv_heads=2, ffn_hidden_size=128, max_seq_len=16)
+    m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0)
+    shards = [tp.TensorParallelManager(m, 2, r).parallelize_model() for r in range(2)]
+    assert torch.equal(torch.cat([shards[r][0]["q"] for r in range(2)], 0), m.layers[0].qkv.data[:64])
+    assert torch.equal(torch.cat([shards[r][0]["o"] for r in range(2)], 1), m.layers[0].o.data)
+    assert torch.equal(torch.cat([shards[r]["lm_head"] for r in range(2)], 0), m.lm_head.data)
+    mgr = tp.TensorParallelManager(m, 1, 0)
+    x = torch.randn(4, 64)
+    assert torch.allclose(mgr.column_parallel_linear(x, m.layers[0].o.data), x @ m.layers[0].o.data.t(), atol=1e-5)
+    assert torch.allclose(mgr.row_parallel_linear(x, m.layers[0].o.data), x @ m.layers[0].o.data.t(), atol=1e-5)
+    assert tp.TensorParallelManager.select_strategy(cfg, 1) == "none"
+    assert tp.TensorParallelManager.select_strategy(TransformerConfig(hidden_size=4096, num_heads=32, num_layers=2), 8, 8192) == "tp+sp"
+    assert tp.HeadPartitioner(8, 2, 4).kv_heads(3) == [1] and tp.HeadPartitioner(8, 2, 4).q_heads(0) == [0, 1]
+    assert tp.SequenceParallel(1, 2).scatter(torch.arange(8).view(1, 8)).tolist() == [[4, 5, 6, 7]]

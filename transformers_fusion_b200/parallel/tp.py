@@ -160,3 +160,133 @@ class SequenceParallel:
         xs = [torch.empty_like(x_shard) for _ in range(self.world)]
         dist.all_gather(xs, x_shard.contiguous(), group=self.group)
         return torch.cat(xs, dim)
+
+
+# ---------------------------------------------------------------------------------------------- manager API
+class HeadPartitioner:
+    """Attention heads per rank (query heads and, for grouped-query attention, the kv heads they share)."""
+
+    def __init__(self, num_heads, num_kv_heads, world):
+        assert num_heads % world == 0, "query heads must divide over the ranks"
+        self.h, self.kv, self.world = num_heads, num_kv_heads, world
+
+    def q_heads(self, rank):
+        return partition_heads(self.h, self.world, rank)
+
+    def kv_heads(self, rank):
+        """kv heads used by this rank's query heads (replicated when there are fewer kv heads than ranks)."""
+        g = self.h // self.kv
+        return sorted({q // g for q in self.q_heads(rank)})
+
+
+class SequenceParallel:
+    """Scatter / gather along the sequence dimension around tensor-parallel regions."""
+
+    def __init__(self, rank, world, group=None):
+        self.rank, self.world, self.group = rank, world, group
+
+    def scatter(self, x, seq_dim=1):
+        n = x.shape[seq_dim] // self.world
+        return x.narrow(seq_dim, self.rank * n, n).contiguous()
+
+    def gather(self, x_shard, seq_dim=1):
+        if self.world == 1 or not dist.is_initialized():
+            return x_shard
+        parts = [torch.empty_like(x_shard) for _ in range(self.world)]
+        dist.all_gather(parts, x_shard.contiguous(), group=self.group)
+        return torch.cat(parts, seq_dim)
+
+    def reduce_scatter(self, x, seq_dim=1):
+        if self.world > 1 and dist.is_initialized():
+            x = x.clone()
+            dist.all_reduce(x, group=self.group)
+        return self.scatter(x, seq_dim)
+
+
+class TensorParallelManager:
+    """The reference's manager API on top of the fused kernels: weight splitting, column / row parallel products,
+    head partitioning, sequence-parallel scatter / gather, strategy selection and whole-model parallelisation."""
+
+    def __init__(self, model=None, world_size=1, rank=0, ctx: TpContext = None, group=None):
+        self.model, self.world, self.rank, self.ctx, self.group = model, world_size, rank, ctx, group
+        self.sp = SequenceParallel(rank, world_size, group)
+
+    column_parallel_split = staticmethod(column_parallel_split)
+    row_parallel_split = staticmethod(row_parallel_split)
+    reconstruct_weight = staticmethod(reconstruct_weight)
+    communication_volume = staticmethod(communication_volume)
+
+    def partition_heads(self, num_heads):
+        return partition_heads(num_heads, self.world, self.rank)
+
+    def column_parallel_linear(self, x_shard, local_w):
+        return ColumnParallelLinear.forward(_Lin(local_w, self), x_shard)
+
+    def row_parallel_linear(self, x, local_w, residual_shard=None):
+        return RowParallelLinear.forward(_Lin(local_w, self, row=True), x, residual_shard)
+
+    def sequence_parallel_scatter(self, x, seq_dim=1):
+        return self.sp.scatter(x, seq_dim)
+
+    def sequence_parallel_gather(self, x, seq_dim=1):
+        return self.sp.gather(x, seq_dim)
+
+    def allreduce_tensor(self, t):
+        if self.world > 1 and dist.is_initialized():
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def allgather_tensor(self, t, dim=0):
+        return SequenceParallel(self.rank, self.world, self.group).gather(t, dim)
+
+    def reduce_scatter_tensor(self, t, dim=0):
+        return SequenceParallel(self.rank, self.world, self.group).reduce_scatter(t, dim)
+
+    @staticmethod
+    def select_strategy(cfg, world_size, batch_tokens=8192):
+        """'none' | 'tp' | 'tp+sp': tensor parallelism pays once a layer's weights dominate its activations; sequence
+        parallelism is added when the activations between the TP regions are large enough to be worth sharding."""
+        if world_size == 1 or cfg.num_heads % world_size:
+            return "none"
+        w_bytes = 2 * cfg.hidden_size * ((cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim + cfg.hidden_size + 3 * cfg.ffn_hidden_size)
+        a_bytes = 2 * batch_tokens * cfg.hidden_size
+        if w_bytes < a_bytes // 4:
+            return "none"
+        return "tp+sp" if batch_tokens % world_size == 0 and a_bytes > (1 << 20) else "tp"
+
+    def parallelize_block(self, blk, cfg):
+        """This rank's shards of one block: q / k / v / gate / up by output rows (column parallel, by whole heads),
+        o / down by input columns (row parallel)."""
+        W, r, D = self.world, self.rank, cfg.head_dim
+        hp = HeadPartitioner(cfg.num_heads, cfg.num_kv_heads, W)
+        nq, nkv = cfg.num_heads * D, cfg.num_kv_heads * D
+        qkv = blk.qkv.data
+        q_rows = torch.cat([torch.arange(h * D, (h + 1) * D) for h in hp.q_heads(r)])
+        kv_sel = torch.cat([torch.arange(h * D, (h + 1) * D) for h in hp.kv_heads(r)])
+        out = {"q": qkv[:nq][q_rows], "k": qkv[nq:nq + nkv][kv_sel], "v": qkv[nq + nkv:][kv_sel],
+               "o": blk.o.data[:, q_rows], "down": row_parallel_split(blk.down.data, W, r)}
+        F_ = cfg.ffn_hidden_size
+        if cfg.gated:
+            out["gate"] = column_parallel_split(blk.gate_up.data[:F_], W, r)
+            out["up"] = column_parallel_split(blk.gate_up.data[F_:], W, r)
+        else:
+            out["up"] = column_parallel_split(blk.gate_up.data, W, r)
+        return out
+
+    def parallelize_model(self, model=None):
+        """{layer index: shards} plus vocabulary-parallel embedding / LM-head rows."""
+        m = model or self.model
+        out = {i: self.parallelize_block(l, m.cfg) for i, l in enumerate(m.layers)}
+        out["tok_embeddings"] = column_parallel_split(m.tok_embeddings.data, self.world, self.rank)
+        out["lm_head"] = column_parallel_split(m.lm_head.data, self.world, self.rank)
+        return out
+
+
+class _Lin:
+    """Adapter that lets the manager reuse the module forward paths with an externally owned weight."""
+
+    def __init__(self, w, mgr: TensorParallelManager, row=False):
+        self.weight = torch.nn.Parameter(w, requires_grad=False)
+        self.rank, self.world, self.ctx, self.group = mgr.rank, mgr.world, mgr.ctx, mgr.group
+
+
