@@ -1,0 +1,416 @@
+"""Serving runtime around the inference engine: ``ModelServer`` (priority queue in front of the continuous-batching loop,
+latency histograms, health / metrics JSON), ``ModelHTTPServer`` (the native HTTP front end wired to it),
+``WebSocketHandler`` (RFC 6455 server: SHA-1 / base64 handshake, text frames, token streaming), ``PluginManager``
+(shared-library and Python plugins with hot reload) and ``ModelZoo`` (named model registry with lazy loading).
+
+Reference counterparts: include/quant/production.h:21-362 (ServerMetrics, LatencyHistogram, ModelServer, ModelHTTPServer,
+WebSocketHandler, PluginManager, ModelZoo), src/server/production_core.cpp, production_api.cpp, production_gen.cpp."""
+from __future__ import annotations
+
+import base64
+import bisect
+import ctypes
+import hashlib
+import importlib.util
+import json
+import os
+import socket
+import struct
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+
+class LatencyHistogram:
+    def __init__(self, max_samples=65536):
+        self.samples: List[float] = []
+        self.max = max_samples
+        self.lock = threading.Lock()
+        self.count, self.total = 0, 0.0
+
+    def record(self, ms: float):
+        with self.lock:
+            self.count += 1
+            self.total += ms
+            bisect.insort(self.samples, ms)
+            if len(self.samples) > self.max:
+                del self.samples[:: 2]               # keep every other sample: the quantiles stay representative
+
+    def percentile(self, p: float) -> float:
+        with self.lock:
+            if not self.samples:
+                return 0.0
+            return self.samples[min(len(self.samples) - 1, int(p / 100.0 * len(self.samples)))]
+
+    def summary(self):
+        return {"count": self.count, "mean_ms": self.total / max(1, self.count), "p50_ms": self.percentile(50),
+                "p95_ms": self.percentile(95), "p99_ms": self.percentile(99)}
+
+
+@dataclass
+class ServerMetrics:
+    requests_total: int = 0
+    requests_failed: int = 0
+    tokens_generated: int = 0
+    queue_depth: int = 0
+    active: int = 0
+    started_at: float = field(default_factory=time.time)
+    latency: LatencyHistogram = field(default_factory=LatencyHistogram)
+    ttft: LatencyHistogram = field(default_factory=LatencyHistogram)
+
+    def to_json(self) -> str:
+        up = time.time() - self.started_at
+        return json.dumps({"requests_total": self.requests_total, "requests_failed": self.requests_failed,
+                           "tokens_generated": self.tokens_generated, "queue_depth": self.queue_depth, "active": self.active,
+                           "uptime_s": round(up, 3), "tokens_per_sec": self.tokens_generated / max(up, 1e-9),
+                           "latency": self.latency.summary(), "ttft": self.ttft.summary()})
+
+
+class _Ticket:
+    def __init__(self, prompt_ids, max_tokens, sampling, priority, on_token):
+        self.prompt_ids, self.max_tokens, self.sampling, self.priority, self.on_token = prompt_ids, max_tokens, sampling, priority, on_token
+        self.done = threading.Event()
+        self.tokens: List[int] = []
+        self.error: Optional[str] = None
+        self.t_submit = time.perf_counter()
+        self.t_first = 0.0
+
+
+class ModelServer:
+    """One engine loop thread; ``submit`` queues a request (higher priority first, FIFO within a priority) and returns a
+    ticket; the loop admits tickets into the engine's continuous batch and steps it."""
+
+    def __init__(self, engine, max_queue: int = 1024):
+        self.engine, self.max_queue = engine, max_queue
+        self.metrics = ServerMetrics()
+        self.cv = threading.Condition()
+        self.pending: List[_Ticket] = []
+        self.inflight: Dict[int, _Ticket] = {}
+        self.running = False
+        self.thread: Optional[threading.Thread] = None
+
+    def start(self):
+        self.running = True
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+        return self
+
+    def stop(self):
+        self.running = False
+        with self.cv:
+            self.cv.notify_all()
+        if self.thread:
+            self.thread.join(timeout=5)
+
+    def submit(self, prompt_ids, max_tokens=64, sampling=None, priority=0, on_token=None) -> _Ticket:
+        t = _Ticket(list(prompt_ids), max_tokens, sampling, priority, on_token)
+        with self.cv:
+            if len(self.pending) >= self.max_queue:
+                t.error = "queue full"
+                t.done.set()
+                self.metrics.requests_failed += 1
+                return t
+            self.pending.append(t)
+            self.pending.sort(key=lambda x: (-x.priority, x.t_submit))
+            self.metrics.queue_depth = len(self.pending)
+            self.cv.notify_all()
+        return t
+
+    def generate(self, prompt_ids, max_tokens=64, sampling=None, priority=0, timeout_s=600.0) -> List[int]:
+        t = self.submit(prompt_ids, max_tokens, sampling, priority)
+        if not t.done.wait(timeout_s):
+            raise TimeoutError("generation timed out")
+        if t.error:
+            raise RuntimeError(t.error)
+        return t.tokens
+
+    def _loop(self):
+        eng = self.engine
+        while self.running:
+            with self.cv:
+                while self.running and not self.pending and not eng.has_pending():
+                    self.cv.wait(0.05)
+                if not self.running:
+                    return
+                batch, self.pending = self.pending, []
+                self.metrics.queue_depth = 0
+            for t in batch:
+                def cb(tok, t=t):
+                    if not t.tokens:
+                        t.t_first = time.perf_counter()
+                        self.metrics.ttft.record((t.t_first - t.t_submit) * 1e3)
+                    t.tokens.append(tok)
+                    if t.on_token:
+                        t.on_token(tok)
+                try:
+                    r = eng.add_request(t.prompt_ids[-(eng.max_len - 2):] or [0], t.max_tokens, t.sampling, priority=t.priority, on_token=cb)
+                    self.inflight[r.id] = t
+                    self.metrics.requests_total += 1
+                except Exception as e:                     # a bad request must not take the loop down
+                    t.error = str(e)
+                    t.done.set()
+                    self.metrics.requests_failed += 1
+            try:
+                finished = eng.step() if eng.has_pending() else []
+            except Exception as e:
+                for t in self.inflight.values():
+                    t.error = str(e)
+                    t.done.set()
+                self.metrics.requests_failed += len(self.inflight)
+                self.inflight.clear()
+                continue
+            self.metrics.active = len(self.inflight)
+            for r in finished:
+                t = self.inflight.pop(r.id, None)
+                if t is not None:
+                    self.metrics.tokens_generated += len(t.tokens)
+                    self.metrics.latency.record((time.perf_counter() - t.t_submit) * 1e3)
+                    t.done.set()
+
+    def health_json(self) -> str:
+        return json.dumps({"status": "ok" if self.running else "stopped", "queue_depth": self.metrics.queue_depth,
+                           "active": self.metrics.active})
+
+    def metrics_json(self) -> str:
+        return self.metrics.to_json()
+
+
+class ModelHTTPServer:
+    """OpenAI-compatible HTTP endpoint (native front end) in front of a ``ModelServer``."""
+
+    def __init__(self, model_server: ModelServer, tokenizer, port=8080, model_name="model"):
+        from . import HTTPServer
+        self.ms, self.tok = model_server, tokenizer
+        self.http = HTTPServer(port)
+        self.http.set_model_name(model_name)
+        self.http.set_generate_callback(self._generate)
+
+    def _generate(self, prompt, max_tokens, temperature, top_p, top_k, stream):
+        from ..inference.sampler import SamplerConfig
+        ids = self.tok.encode(prompt)
+        out = self.ms.generate(ids, max_tokens, SamplerConfig(temperature, top_k, top_p))
+        eos = getattr(self.tok, "eos_id", -1)
+        yield self.tok.decode([t for t in out if t != eos])
+
+    def start(self):
+        self.ms.start()
+        return self.http.start()
+
+    def stop(self):
+        self.http.stop()
+        self.ms.stop()
+
+    @property
+    def port(self):
+        return self.http.port
+
+
+# ================================================================================================ WebSocket
+_WS_GUID = "258EAFA5-E914-47DA-95CA-C5AB0DC85B11"
+
+
+def websocket_accept_key(client_key: str) -> str:
+    return base64.b64encode(hashlib.sha1((client_key + _WS_GUID).encode()).digest()).decode()
+
+
+def ws_encode_frame(payload: bytes, opcode=1, mask: Optional[bytes] = None) -> bytes:
+    n = len(payload)
+    hdr = bytes([0x80 | opcode])
+    mbit = 0x80 if mask else 0
+    if n < 126:
+        hdr += bytes([mbit | n])
+    elif n < 65536:
+        hdr += bytes([mbit | 126]) + struct.pack(">H", n)
+    else:
+        hdr += bytes([mbit | 127]) + struct.pack(">Q", n)
+    if mask:
+        payload = bytes(b ^ mask[i & 3] for i, b in enumerate(payload))
+        hdr += mask
+    return hdr + payload
+
+
+def ws_decode_frame(buf: bytes):
+    """(opcode, payload, bytes consumed) or None when ``buf`` does not hold a whole frame yet."""
+    if len(buf) < 2:
+        return None
+    op, n = buf[0] & 0x0F, buf[1] & 0x7F
+    masked = bool(buf[1] & 0x80)
+    o = 2
+    if n == 126:
+        if len(buf) < 4:
+            return None
+        n, o = struct.unpack(">H", buf[2:4])[0], 4
+    elif n == 127:
+        if len(buf) < 10:
+            return None
+        n, o = struct.unpack(">Q", buf[2:10])[0], 10
+    if n > (16 << 20):
+        raise ValueError("frame too large")
+    mask = b""
+    if masked:
+        if len(buf) < o + 4:
+            return None
+        mask, o = buf[o:o + 4], o + 4
+    if len(buf) < o + n:
+        return None
+    payload = buf[o:o + n]
+    if masked:
+        payload = bytes(b ^ mask[i & 3] for i, b in enumerate(payload))
+    return op, payload, o + n
+
+
+class WebSocketHandler:
+    """Text-frame server: every received message is passed to ``on_message(text, send)``; ``send(str)`` writes a frame
+    back (call it repeatedly to stream tokens)."""
+
+    def __init__(self, port=8081, on_message: Optional[Callable] = None, host="127.0.0.1"):
+        self.port, self.host, self.on_message = port, host, on_message or (lambda text, send: send(text))
+        self.sock: Optional[socket.socket] = None
+        self._stop = False
+        self.clients = 0
+
+    def start(self):
+        self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        self.sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        self.sock.bind((self.host, self.port))
+        self.sock.listen(16)
+        self.sock.settimeout(0.2)
+        self.port = self.sock.getsockname()[1]
+        threading.Thread(target=self._accept, daemon=True).start()
+        return self.port
+
+    def stop(self):
+        self._stop = True
+        if self.sock:
+            self.sock.close()
+
+    def _accept(self):
+        while not self._stop:
+            try:
+                c, _ = self.sock.accept()
+            except (socket.timeout, OSError):
+                continue
+            threading.Thread(target=self._serve, args=(c,), daemon=True).start()
+
+    def _serve(self, c):
+        c.settimeout(30)
+        try:
+            req = b""
+            while b"\r\n\r\n" not in req:
+                part = c.recv(4096)
+                if not part or len(req) > 65536:
+                    return
+                req += part
+            head, _, rest = req.partition(b"\r\n\r\n")
+            hdrs = {}
+            for line in head.decode("latin1").split("\r\n")[1:]:
+                k, _, v = line.partition(":")
+                hdrs[k.strip().lower()] = v.strip()
+            key = hdrs.get("sec-websocket-key")
+            if hdrs.get("upgrade", "").lower() != "websocket" or not key:
+                c.sendall(b"HTTP/1.1 400 Bad Request\r\nContent-Length: 0\r\n\r\n")
+                return
+            c.sendall(("HTTP/1.1 101 Switching Protocols\r\nUpgrade: websocket\r\nConnection: Upgrade\r\n"
+                       f"Sec-WebSocket-Accept: {websocket_accept_key(key)}\r\n\r\n").encode())
+            self.clients += 1
+            send = lambda text: c.sendall(ws_encode_frame(text.encode()))
+            buf = rest
+            while not self._stop:
+                fr = ws_decode_frame(buf)
+                if fr is None:
+                    part = c.recv(65536)
+                    if not part:
+                        return
+                    buf += part
+                    continue
+                op, payload, used = fr
+                buf = buf[used:]
+                if op == 8:
+                    c.sendall(ws_encode_frame(b"", 8))
+                    return
+                if op == 9:
+                    c.sendall(ws_encode_frame(payload, 10))
+                elif op == 1:
+                    self.on_message(payload.decode("utf-8", "replace"), send)
+        except (OSError, ValueError):
+            return
+        finally:
+            c.close()
+
+
+# ================================================================================================ plugins / zoo
+class PluginManager:
+    """Plugins are Python files (a module with ``plugin_init(ctx)``) or shared libraries (``int plugin_init(void)``,
+    optional ``const char* plugin_name(void)``).  ``reload_changed`` re-imports plugins whose file changed."""
+
+    def __init__(self):
+        self.plugins: Dict[str, dict] = {}
+
+    def load(self, path: str, ctx=None) -> str:
+        name = os.path.splitext(os.path.basename(path))[0]
+        if path.endswith(".py"):
+            spec = importlib.util.spec_from_file_location(f"tfb_plugin_{name}_{int(time.time() * 1e6)}", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            res = mod.plugin_init(ctx) if hasattr(mod, "plugin_init") else None
+            self.plugins[name] = {"path": path, "mtime": os.path.getmtime(path), "module": mod, "result": res, "ctx": ctx, "kind": "python"}
+        else:
+            lib = ctypes.CDLL(path)
+            res = lib.plugin_init() if hasattr(lib, "plugin_init") else None
+            if hasattr(lib, "plugin_name"):
+                lib.plugin_name.restype = ctypes.c_char_p
+                name = lib.plugin_name().decode()
+            self.plugins[name] = {"path": path, "mtime": os.path.getmtime(path), "module": lib, "result": res, "ctx": ctx, "kind": "native"}
+        return name
+
+    def unload(self, name):
+        p = self.plugins.pop(name, None)
+        if p and p["kind"] == "python" and hasattr(p["module"], "plugin_shutdown"):
+            p["module"].plugin_shutdown()
+
+    def reload_changed(self) -> List[str]:
+        out = []
+        for name, p in list(self.plugins.items()):
+            if p["kind"] == "python" and os.path.getmtime(p["path"]) != p["mtime"]:
+                self.unload(name)
+                self.load(p["path"], p["ctx"])
+                out.append(name)
+        return out
+
+    def call(self, name, fn, *args):
+        return getattr(self.plugins[name]["module"], fn)(*args)
+
+    def names(self):
+        return sorted(self.plugins)
+
+
+class ModelZoo:
+    """name -> checkpoint path registry; models load on first use and can be evicted."""
+
+    def __init__(self, device="cpu", dtype=None):
+        self.paths: Dict[str, str] = {}
+        self.loaded: Dict[str, object] = {}
+        self.device, self.dtype = device, dtype
+
+    def register(self, name, path):
+        self.paths[name] = path
+
+    def list(self):
+        return sorted(self.paths)
+
+    def get(self, name):
+        if name not in self.loaded:
+            import torch
+            from ..quant import codec
+            self.loaded[name] = codec.load_model(self.paths[name], device=self.device, dtype=self.dtype or torch.float32)
+        return self.loaded[name]
+
+    def unload(self, name):
+        self.loaded.pop(name, None)
+
+    def scan(self, directory):
+        for f in sorted(os.listdir(directory)):
+            if f.endswith(".quant"):
+                self.register(os.path.splitext(f)[0], os.path.join(directory, f))
+        return self.list()
