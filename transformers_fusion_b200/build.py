@@ -104,6 +104,24 @@ def build_host_lib(name: str, subdir: str, force=False, extra_libs=()) -> Path |
     return so
 
 
+def build_capi(force=False) -> Path | None:
+    """csrc/capi -> lib/libtfb_capi.so, linked against the running interpreter's libpython (skipped when the
+    development headers are not installed)."""
+    import sysconfig
+    inc = sysconfig.get_paths()["include"]
+    if not (Path(inc) / "Python.h").exists():
+        return None
+    d = CSRC / "capi"
+    src, so = d / "tfb_capi.cpp", LIB / "libtfb_capi.so"
+    if force or _newer([src, d / "tfb_capi.h"], so):
+        cxx = os.environ.get("TFB_CXX", "g++")
+        libdir = sysconfig.get_config_var("LIBDIR") or "/usr/lib"
+        ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+        _run([cxx] + CXX_FLAGS + ["-shared", "-I", inc, "-I", str(d), str(src), "-o", str(so), f"-L{libdir}", f"-lpython{ver}",
+              f"-Wl,-rpath,{libdir}"])
+    return so
+
+
 def build_tools(force=False):
     """Native command-line front ends (csrc/tools/*.cpp) -> lib/bin/<name>."""
     d = CSRC / "tools"
@@ -132,6 +150,9 @@ def build_all(force=False, verbose=False):
         so = build_host_lib(name, sub, force)
         if so:
             built.append(so)
+    capi = build_capi(force)
+    if capi:
+        built.append(capi)
     built += build_tools(force)
     return built
 
