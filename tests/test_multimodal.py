@@ -1,0 +1,114 @@
+import math
+
+import pytest
+import torch
+
+from transformers_fusion_b200.models import multimodal as MM
+
+
+def small_cfg():
+    return MM.MultimodalEncoderConfig(image_patch_size=8, image_size=32, image_embed_dim=64, image_num_layers=1, image_num_heads=4,
+                                      audio_n_mels=20, audio_embed_dim=32, audio_num_layers=1, audio_num_heads=4, text_vocab_size=100,
+                                      text_embed_dim=48, text_max_len=32, text_num_layers=1, text_num_heads=4, shared_hidden=64,
+                                      shared_num_heads=4, shared_num_layers=1, modality_dropout=0.0)
+
+
+def test_towers_and_fusion_shapes_and_training():
+    torch.manual_seed(0)
+    m = MM.MultimodalCrossAttention(small_cfg())
+    img, mel, ids = torch.randn(3, 3, 32, 32), torch.randn(3, 40, 20), torch.randint(0, 100, (3, 7))
+    out = m(img, mel, ids)
+    assert out["fused"].shape == (3, 17 + 10 + 7, 64) and out["spans"] == {"image": (0, 17), "audio": (17, 27), "text": (27, 34)}
+    assert out["text_grounded"].shape == (3, 7, 64)
+    loss = out["loss_image_text"] + out["loss_audio_text"]
+    assert abs(float(out["loss_image_text"]) - math.log(3)) < 0.7
+    loss.backward()
+    assert m.vision.patch.proj.weight.grad is not None and m.text.emb.weight.grad is not None
+    only_text = m(text_ids=ids)
+    assert only_text["fused"].shape == (3, 7, 64) and "text_grounded" not in only_text
+    # the alignment head learns to pair matching rows
+    head = MM.ContrastiveAlignmentHead(16, 16, 8)
+    a = torch.randn(6, 16)
+    opt = torch.optim.Adam(head.parameters(), 1e-2)
+    l0 = float(head(a, a + 0.01 * torch.randn(6, 16)))
+    for _ in range(50):
+        opt.zero_grad()
+        l = head(a, a)
+        l.backward()
+        opt.step()
+    assert float(l) < l0 and head.similarity(a, a).argmax(1).tolist() == list(range(6))
+
+
+def test_mel_spectrogram_and_synthesis():
+    sr = 8000
+    t = torch.arange(sr).float() / sr
+    mel = MM.MelSpectrogram(sr, 40, 256, 64)
+    lo, hi = mel.compute(torch.sin(2 * math.pi * 300 * t)[None]), mel.compute(torch.sin(2 * math.pi * 2500 * t)[None])
+    assert lo.shape[0] == 1 and lo.shape[2] == 40
+    assert int(lo[0].mean(0).argmax()) < int(hi[0].mean(0).argmax())            # a higher tone lights a higher mel band
+    fb = MM.MelSpectrogram.mel_filterbank(10, 64, 8000)
+    assert fb.shape == (10, 33) and bool((fb >= 0).all()) and bool((fb.sum(1) > 0).all())
+    wav = MM.AudioSynthesizer(mel, iters=4).synthesize(lo[0])
+    assert wav.numel() > 7000 and torch.isfinite(wav).all()
+    spec = torch.fft.rfft(wav[: 4096]).abs()
+    assert abs(int(spec.argmax()) * sr / 4096 - 300) < 120                       # the reconstructed tone is where it was
+    enc = MM.AudioTransformer(MM.AudioEncoderConfig(40, 32, 4, 1))
+    assert MM.AudioFeatureExtractor(enc, mel).extract(torch.randn(2, 4000)).shape == (2, 32)
+
+
+def test_perceiver_moe_fusion_tokenizer():
+    torch.manual_seed(1)
+    p = MM.Perceiver(32, 5, 4)
+    assert p(torch.randn(2, 77, 32)).shape == (2, 5, 32)
+    moe = MM.VisionTextMoE(32, 4)
+    v, t = moe(torch.randn(2, 6, 32), torch.randn(2, 3, 32))
+    assert v.shape == (2, 6, 32) and t.shape == (2, 3, 32) and float(moe.shared.last_aux) > 0
+    am = MM.AllModalityMoE(32, 2)(image=torch.randn(1, 4, 32), audio=None, text=torch.randn(1, 2, 32))
+    assert set(am) == {"image", "text"} and am["text"].shape == (1, 2, 32)
+    for mode in ("concat", "gated", "cross_attention"):
+        f = MM.MultimodalFusion(MM.FusionConfig(32, 4, mode))
+        assert f(torch.randn(2, 5, 32), torch.randn(2, 9, 32)).shape == (2, 5, 32)
+    tk = MM.MultiModalTokenizer(image_codes=16, audio_codes=8)
+    ids = tk.encode("hi", [3, 15], [7])
+    d = tk.decode(ids)
+    assert d == {"text": "hi", "image_codes": [3, 15], "audio_codes": [7]} and max(ids) < tk.vocab_size and tk.BOI in ids
+
+
+def test_task_heads():
+    torch.manual_seed(2)
+    vit = MM.VisionTransformer(MM.ViTConfig(32, 8, 3, 32, 4, 1, 64))
+    img = torch.randn(2, 3, 32, 32)
+    clf = MM.ImageNetClassifier(vit, 10)
+    top = clf.classify(img, 3)
+    assert len(top) == 2 and len(top[0]) == 3 and abs(sum(p for _, p in clf.classify(img, 10)[0]) - 1) < 1e-4
+    assert MM.ctc_greedy_decode(torch.log(torch.tensor([[.1, .9, 0], [.1, .9, 0], [.9, .1, 0], [0, .1, .9], [0, .9, .1]]) + 1e-9)) == [1, 2, 1]
+    asr = MM.SpeechRecognizer(MM.AudioTransformer(MM.AudioEncoderConfig(20, 32, 4, 1)), 12)
+    mel = torch.randn(2, 40, 20)
+    l = asr.loss(mel, torch.randint(1, 12, (2, 4)), torch.tensor([4, 3]))
+    l.backward()
+    assert torch.isfinite(l) and len(asr.transcribe(mel)) == 2
+    ocr = MM.OCREngine(vit, 128)
+    boxes = ocr.recognize(img)
+    assert len(boxes) == 2 and boxes[0].w == 32 and isinstance(boxes[0].text, str)
+    vid = MM.VideoUnderstanding(MM.VideoEncoder(vit, 1), 5)
+    assert vid(torch.randn(2, 3, 3, 32, 32)).shape == (2, 5)
+    cap = MM.ImageCaptioning(vit, 50, 32, 1, 4, 16)
+    assert cap(img, torch.randint(0, 50, (2, 6))).shape == (2, 6, 50) and cap.caption(img, max_tokens=4).shape[1] <= 5
+    txt = MM.TextEncoder(50, 32, 1, 4, 16)
+    assert MM.VisualQA(vit, txt, 7, 32)(img, torch.randint(0, 50, (2, 5))).shape == (2, 7)
+    t2i = MM.TextToImage(txt, num_codes=16, grid=2, dim=32, layers=1, heads=4, patch=4)
+    assert t2i.generate(torch.randint(0, 50, (2, 5))).shape == (2, 3, 8, 8)
+    assert MM.TextDecoder(50, 32, 1, 4, 16)(torch.randint(0, 50, (2, 5))).shape == (2, 5, 50)
+
+
+def test_containers(tmp_path):
+    im = MM.Image(torch.rand(3, 20, 30))
+    assert im.resize(10, 12).data.shape == (3, 10, 12) and im.center_crop(16).data.shape == (3, 16, 16) and im.to_grayscale().data.shape == (1, 20, 30)
+    im.save_ppm(str(tmp_path / "a.ppm"))
+    back = MM.Image.load_ppm(str(tmp_path / "a.ppm"))
+    assert back.data.shape == (3, 20, 30) and float((back.data - im.data).abs().max()) < 1 / 255 + 1e-6
+    v = MM.Video(torch.rand(30, 3, 8, 8), 30.0)
+    assert v.sample_uniform(5).frames.shape[0] == 5 and v.duration() == 1.0
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    se = MM.SentenceEmbedder(MM.TextEncoder(259, 32, 1, 4, 64), ByteTokenizer())
+    assert se.embed(["a", "bb"]).shape == (2, 32) and se.similarity("same", "same") == pytest.approx(1.0, abs=1e-5)
