@@ -1,0 +1,167 @@
+import math
+import threading
+
+import pytest
+import torch
+
+from transformers_fusion_b200 import agi
+from transformers_fusion_b200.agi.core import KnowledgeDistillation
+from transformers_fusion_b200.utils.inferno import InfernoCounter, TaskQueue, inferno_metric
+
+
+def echo(prompt):
+    if "Critique" in prompt:
+        return "approve: no issues"
+    if "numbered steps" in prompt:
+        return "1. gather data\n2. train model (after 1)\n3. evaluate (after 2)\n4. write report (after 2, 3)"
+    return "result for " + prompt[:30]
+
+
+def test_monitor_reflector_metacognition():
+    mon = agi.SelfMonitor(logits=lambda p: torch.tensor([5.0, 0.0, 0.0, 0.0]))
+    st = mon.analyze("q", "a")
+    assert st.confidence > 0.9 and 0 <= st.uncertainty < 0.2
+    flat, peaked = torch.zeros(1, 8), torch.tensor([[9.0] + [0.0] * 7])
+    assert mon.distribution_shift(flat, flat) < 1e-9 and mon.detect_drift(peaked, flat) and mon.get_recent_alerts()[0].source == "drift"
+    r = agi.SelfReflector(echo)
+    assert r.refine("x", "No issues found") == "x" and r.consistency_check("a b c", "a b d") == 0.5
+    assert r.ece_calibration([0.9, 0.9, 0.1, 0.1], [True, True, False, False]) == pytest.approx(0.1)
+    assert r.identify_errors("p", "", "x y") == ["empty output", "missing: x y"]
+    mc = agi.MetaCognition()
+    ens = torch.stack([torch.tensor([4.0, 0, 0]), torch.tensor([0, 4.0, 0])])
+    assert mc.epistemic_uncertainty(ens) > 0.3 and mc.epistemic_uncertainty(ens[0]) < 1e-6
+    assert mc.reasoning_quality(["add the numbers", "the numbers sum to five"]) > 0.7 and mc.reasoning_quality([]) == 0
+    mc.self_model_update("q", 0.9, True)
+    mc.self_model_update("q", 0.9, False)
+    assert mc.self_model_accuracy == 0.5
+
+
+def test_guardrails_sandbox_verifier():
+    g = agi.SafetyGuardrails()
+    assert g.check_input("please summarise this") and not g.check_output("run rm -rf / now")
+    assert not g.check_modification("guardrail rules", "relax") and g.check_modification("learning rate", "halve it")
+    g.set_invariant("positive", lambda: 3 > 2)
+    assert g.check_invariant("positive") and not g.check_invariant("missing")
+    g.set_kill_switch(True)
+    assert not g.check_input("anything") and g.is_killed() and len(g.get_audit_log()) >= 6
+    sb = agi.Sandbox()
+    assert sb.static_analysis("import os\nopen('x')") == ["import of 'os' is not allowed", "call to 'open' is not allowed"]
+    assert "syntax error" in sb.static_analysis("def (")[0] and sb.static_analysis("while True:\n    pass") == ["unbounded 'while True' loop"]
+    r = sb.compile_and_test("def sq(x):\n    return x * x\n", ["sq(3) == 9", "sq(-2) == 4", "sq(2) == 5"])
+    assert r.compiled and r.tests_passed == 2 and r.tests_total == 3
+    assert not sb.compile_and_test("import socket", ["True"]).compiled
+    slow = sb._run("x = 0\nwhile x < 10**12:\n    x += 1\n", 0.5)
+    assert slow.timed_out or slow.exit_code != 0                       # bounded: never runs away
+    v = agi.SelfVerifier(sb)
+    assert v.verify_arithmetic("2 * (3 + 4)", 14) and not v.verify_arithmetic("__import__('os')", 0)
+    assert v.verify_code("def f(x):\n    return x + 1\n", ["f(1) == 2"])
+
+
+def test_agents_planning_flywheel():
+    co = agi.MultiAgentCoordinator(echo)
+    out = co.run_task("sort a list")
+    assert out.startswith("result for [Synthesizer]") and co.is_converged() and co.get_round() == 1
+    assert co.get_message_queue(co.IMPLEMENTER)[0].sender == co.ANALYST and len(co.get_agent_history(co.CRITIC)) == 1
+    pe = agi.PlanningEngine(echo)
+    plan = pe.plan("ship a model")
+    assert [s.id for s in plan] == [1, 2, 3, 4] and plan[3].depends_on == [2, 3] and pe.execute(plan) and len(pe.execution_history) == 4
+    with pytest.raises(ValueError):
+        pe.topological_sort([agi.PlanStep(1, "a", [2]), agi.PlanStep(2, "b", [1])])
+    fail = agi.PlanningEngine(None, executor=lambda s: s.id != 2)
+    p2 = fail.plan("a then b then c")
+    assert not fail.execute(p2)
+    rp = fail.replan(p2, "b failed")
+    assert rp[0].done and rp[1].description == "resolve: b failed" and rp[2].depends_on == [rp[1].id]
+    # flywheel: the "model" improves when the improver teaches it the failing cases
+    known = {}
+    h = agi.EvaluationHarness(lambda p: known.get(p, "?"))
+    fw = agi.Flywheel(h, lambda fails: known.update({p: e for p, _, e in fails}))
+    its = fw.run([("2+2", "4"), ("capital of France", "Paris")], max_iterations=3)
+    assert [i["accuracy"] for i in its] == [0.0, 1.0]
+    hitl = agi.HITL(lambda a: False)
+    assert len(agi.Flywheel(agi.EvaluationHarness(lambda p: "?"), lambda f: None, hitl=hitl).run([("a", "b")], 3)) == 1
+    imp = agi.RecursiveSelfImprover(lambda s: -abs(math.log10(s["learning_rate"]) + 3))     # best at 1e-3
+    imp.improvement_cycle(8)
+    assert 4e-4 < imp.settings["learning_rate"] < 2e-3
+
+
+def test_misc_components():
+    ex = agi.CuriosityDrivenExplorer()
+    for _ in range(10):
+        ex.observe("known", 1.0, 1.0)
+    ex.observe("surprising", 0.0, 5.0)
+    assert ex.select(["known", "surprising"]) == "surprising" and ex.select(["known", "new"]) == "new"
+    kd = KnowledgeDistillation(2.0, 0.5)
+    t = torch.randn(4, 10)
+    assert float(kd.loss(t, t)) < 1e-6 and float(kd.loss(torch.randn(4, 10), t, torch.randint(0, 10, (4,)))) > 0
+    tools = agi.ToolUse()
+    tools.register("double", lambda a: int(a) * 2)
+    assert tools.run("first double(21) then unknown(3) then double(x)") == {"double(21)": 42, "double(x)": "error: invalid literal for int() with base 10: 'x'"}
+    mem = agi.MemorySystem(2)
+    for s in ("the cat sat", "dogs bark loudly", "cats purr softly", "rain falls"):
+        mem.remember(s)
+    assert mem.recall("cat sat on", 1) == ["the cat sat"] and len(mem.long) == 2
+    chain, ans = agi.ChainOfThought(lambda p: "therefore 4" if "Step 2" in p else "add").solve("2+2", 5)
+    assert chain == ["add", "therefore 4"]
+    best, _ = agi.PromptOptimizer(lambda s: len(s)).optimize("task", ["{base}!", "Please do: {base} carefully"])
+    assert best.startswith("Please")
+    assert 0 <= agi.AlignmentSystem().value_alignment_score("I will help and explain safely") <= 1
+    assert agi.AlignmentSystem().value_alignment_score("exploit and steal") < agi.AlignmentSystem().value_alignment_score("help explain")
+
+
+def test_meta_engine_multi_agent_system_eval_world():
+    me = agi.MetaCognitionEngine(5)
+    for c, ok in [(0.9, True)] * 8 + [(0.9, False)] * 2 + [(0.3, False)] * 5:
+        me.record_confidence(c, ok)
+    assert me.expected_calibration_error() == pytest.approx((10 * 0.1 + 5 * 0.3) / 15) and me.calibrate(0.9) == pytest.approx(0.8)
+    gid, kids = me.decompose_goal("ship", ["build", "test"])
+    me.complete(kids[0])
+    assert me.progress(gid) == 0.5
+    me.complete(kids[1])
+    assert me.goals[gid].done and me.assess().goals_completed == 1.0
+    ch = me.begin_chain("g")
+    me.add_step(ch, "a", 0.9), me.add_step(ch, "b", 0.5)
+    assert ch.confidence() == pytest.approx(0.45) and me.weakest_step(ch).content == "b"
+    mas = agi.MultiAgentSystem()
+    a = mas.add_agent("worker", lambda p: "done:" + p[:12], 1.0)
+    b = mas.add_agent("worker", lambda p: "blue", 3.0)
+    t0 = mas.add_subtask("collect")
+    t1 = mas.add_subtask("analyse", [t0])
+    assert mas.run() and mas.subtasks[t1].done and mas.read(f"subtask/{t0}") is not None
+    win, tally, votes = mas.vote("colour?", ["red", "blue"])
+    assert win == "blue" and tally["blue"] == 3.0
+    mas.broadcast(a, "note", "hello")
+    assert mas.receive(b, "note").content == "hello" and mas.receive(b) is None
+    assert agi.pass_at_k(5, 0, 1) == 0 and agi.pass_at_k(5, 5, 1) == 1 and agi.pass_at_k(10, 3, 2) == pytest.approx(1 - (7 * 6) / (10 * 9))
+    suite = agi.SelfEvalSuite(lambda p: "4" if "2+2" in p.replace(" ", "").lower() else "?", lambda p, o: 0.9 if o == "4" else 0.1)
+    rep = suite.evaluate([("what is 2+2", "4"), ("capital of France", "Paris")])
+    assert rep.accuracy == 0.5 and rep.consistency == 1.0 and rep.ece == pytest.approx(0.1) and rep.pass_at_k[1] == 0.5
+    better = agi.self_eval.EvaluationReport(accuracy=0.9, consistency=1.0, robustness=1.0, tokens_per_sec=rep.tokens_per_sec)
+    assert agi.SelfEvalSuite.compare_versions(rep, better)["improved"]
+    wm = agi.WorldModel()
+    for _ in range(5):
+        wm.observe("start", "right", "mid", 0.0)
+        wm.observe("mid", "right", "goal", 10.0)
+        wm.observe("start", "left", "pit", -5.0)
+    assert wm.predict("start", "right").next_state == "mid" and wm.mpc_action("start", 3) == "right"
+    plan = wm.plan_beam("start", 2)
+    assert plan.actions == ["right", "right"] and plan.states == ["start", "mid", "goal"] and plan.expected_return == pytest.approx(9.5)
+    cf = wm.counterfactual("start", ["left"], ["right", "right"])
+    assert cf.difference == pytest.approx(14.5) and wm.uncertainty("start", "right")[0] < wm.uncertainty("nowhere", "right")[0]
+
+
+def test_inferno():
+    assert inferno_metric(1e21, 32) == pytest.approx(0.5) and inferno_metric(1e21, 4) == pytest.approx(4.0)
+    c = InfernoCounter(8.0)
+    c.start(), c.add_gemm(64, 64, 64), c.stop()
+    assert c.ops == 2 * 64 ** 3 and c.flops() > 0 and c.inferno() == pytest.approx(inferno_metric(c.flops(), 8.0))
+    gate = threading.Event()
+    q = TaskQueue(workers=1)
+    first = q.submit(gate.wait, priority=100)
+    lo, hi = q.submit(lambda: "lo", priority=1), q.submit(lambda: "hi", priority=9)
+    gate.set()
+    assert hi.result(5) == "hi" and lo.result(5) == "lo" and q.order == [100, 9, 1]
+    bad = q.submit(lambda: 1 / 0)
+    with pytest.raises(ZeroDivisionError):
+        bad.result(5)
+    q.stop()
