@@ -1,0 +1,77 @@
+import pytest
+import torch
+
+from transformers_fusion_b200.inference import kv_extras as K
+
+
+def test_page_table_levels():
+    t2, t3 = K.PageTable(2), K.PageTable(3)
+    assert t2.capacity_tokens() == 4096 * 4096 * 16 and t3.capacity_tokens() == 4096 ** 3 * 16
+    t2.set(5, 50), t2.set(4096 * 4095 + 7, 77)
+    assert t2.get(5) == 50 and t2.get(4096 * 4095 + 7) == 77 and t2.get(6) is None and t2.count == 2
+    assert t2.pop(5) == 50 and t2.get(5) is None and t2.count == 1
+    with pytest.raises(IndexError):
+        t2.set(4096 * 4096, 1)
+    t3.set(4096 * 4096 + 3, 9)
+    assert t3.get(4096 * 4096 + 3) == 9
+
+
+def test_spill_and_restore(tmp_path):
+    st = K.TieredKVStore(2, 8, resident_pages=3, path=str(tmp_path / "kv.spill"))
+    pages = {i: torch.randn(2, 16, 2, 8) for i in range(6)}
+    for i, p in pages.items():
+        st.write_page(i, p)
+    assert st.stats["evictions"] == 3 and st.on_disk == {0, 1, 2} and st.table.get(0) is None and st.table.get(5) is not None
+    st.prefetch([0])
+    assert st.ensure_resident([0, 1]) and torch.equal(st.read_page(0), pages[0]) and torch.equal(st.read_page(1), pages[1])
+    for i in range(6):                                      # everything survives being cycled through disk
+        assert torch.equal(st.read_page(i), pages[i])
+    assert st.stats["loads"] >= 3
+    # a page that is neither resident nor on disk cannot become resident: bounded wait, no hang
+    st.on_disk.add(99)
+    st.file.truncate(0)
+    st.q.put = lambda *_: None                                # the load request is lost on the way to the worker
+    assert st.ensure_resident([99], timeout_ms=100) is False
+
+
+def test_compressed_kv_and_flash_decoding():
+    torch.manual_seed(0)
+    c = K.CompressedKVCache(2, 64, 32)
+    k, v = torch.randn(10, 2, 64), torch.randn(10, 2, 64)
+    c.append(k[:6], v[:6]), c.append(k[6:], v[6:])
+    kk, vv = c.get()
+    assert kk.shape == (10, 2, 64) and c.bytes_per_token() == 2 * 2 * (16 + 4)
+    cos = torch.nn.functional.cosine_similarity(kk.reshape(-1), k.reshape(-1), dim=0)
+    assert cos > 0.75 and set(torch.unique(torch.sign(kk)).tolist()) <= {-1.0, 0.0, 1.0}
+    q = torch.randn(4, 64)
+    K_, V_ = torch.randn(50, 2, 64), torch.randn(50, 2, 64)
+    ref = torch.empty(4, 64)
+    for h in range(4):
+        s = (K_[:, h // 2] @ q[h]) * 64 ** -0.5
+        ref[h] = torch.softmax(s, 0) @ V_[:, h // 2]
+    for splits in (1, 3, 7):
+        assert torch.allclose(K.flash_decoding(q, K_, V_, splits), ref, atol=1e-5)
+
+
+def test_budget_and_facades():
+    b = K.ReasoningBudget.for_level("low")
+    assert b.budget == 256 and b.consume(255) and not b.consume(1) and b.remaining() == 0
+    from transformers_fusion_b200.inference.kv_cache import PagedKVCache
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    cache = PagedKVCache(1, 8, 2, 64, "bf16", "cpu")
+    pa = K.PagedAttention(cache)
+    blk = pa.alloc_block()
+    assert cache.allocator.num_free == 7
+    pa.free_block(blk)
+    assert cache.allocator.num_free == 8
+    m = DenseModel(TransformerConfig(vocab_size=259, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=64),
+                   device="cpu", dtype=torch.float32, seed=0)
+    cb = K.ContinuousBatching(m, ByteTokenizer(), max_batch=2, num_pages=32)
+    for i in range(3):
+        cb.add_request(K.BatchRequest([5 + i, 6, 7], 4, id=100 + i))
+    done = []
+    while cb.has_pending():
+        done += cb.step()
+    assert sorted(r.id for r in done) == [100, 101, 102] and all(len(r.tokens) <= 4 for r in done)
