@@ -92,3 +92,24 @@ def test_engine_matches_recompute_gpu():
         ref = _naive_greedy(m, p, 8)
         agree += sum(int(x == y) for x, y in zip(o, ref))
     assert agree >= 28, agree      # bf16 paths differ in rounding; near-ties may flip a token
+
+
+def test_engine_with_packed_weights_matches_dequantised_model():
+    """Serving from int8-packed weights must give the tokens of a model whose weights are the dequantised values."""
+    import torch
+    from transformers_fusion_b200.inference.engine import EngineConfig, InferenceEngine
+    from transformers_fusion_b200.inference.sampler import SamplerConfig
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.quant import wq
+    cfg = TransformerConfig(vocab_size=128, hidden_size=64, num_layers=2, num_heads=4, ffn_hidden_size=128, max_seq_len=64)
+    m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0)
+    eng = InferenceEngine(m, None, EngineConfig(num_pages=32, weight_format="int8", weight_group=32))
+    assert len(eng.packed) == 8
+    out_q = eng.generate_batch([[5, 6, 7, 8]], 8, SamplerConfig(0.0))[0]
+    m2 = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0)
+    for i, l in enumerate(m2.layers):
+        for name in ("qkv", "o", "gate_up", "down"):
+            getattr(l, name).data.copy_(wq.dequant(eng.packed[f"layers.{i}.{name}"]))
+    out_ref = InferenceEngine(m2, None, EngineConfig(num_pages=32)).generate_batch([[5, 6, 7, 8]], 8, SamplerConfig(0.0))[0]
+    assert out_q == out_ref

@@ -112,3 +112,21 @@ def test_containers(tmp_path):
     from transformers_fusion_b200.tokenizer import ByteTokenizer
     se = MM.SentenceEmbedder(MM.TextEncoder(259, 32, 1, 4, 64), ByteTokenizer())
     assert se.embed(["a", "bb"]).shape == (2, 32) and se.similarity("same", "same") == pytest.approx(1.0, abs=1e-5)
+
+
+@pytest.mark.gpu
+def test_towers_on_device_kernels_match_torch_path():
+    """bf16 on CUDA without autograd takes the GEMM / flash-attention kernels; with autograd it takes the torch path."""
+    torch.manual_seed(0)
+    vit = MM.VisionTransformer(MM.ViTConfig(32, 8, 3, 128, 2, 2, 256)).cuda().to(torch.bfloat16)
+    img = torch.randn(2, 3, 32, 32, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        fast = vit(img, return_tokens=True).float()
+    slow = vit(img.requires_grad_(), return_tokens=True).float().detach()
+    assert (fast - slow).abs().max() / slow.abs().max() < 0.05
+    txt = MM.TextEncoder(100, 128, 1, 2, 64).cuda().to(torch.bfloat16)
+    ids = torch.randint(0, 100, (2, 33), device="cuda")
+    with torch.no_grad():
+        a = txt(ids).float()
+    b = txt.emb.weight.requires_grad_() is not None and txt(ids).float().detach()
+    assert (a - b).abs().max() / b.abs().max() < 0.05

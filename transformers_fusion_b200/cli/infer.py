@@ -17,6 +17,8 @@ def main(argv=None):
     add_int(ap, "--seed", 0)
     add_int(ap, "--max-tokens", 512)
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "q4"])
+    ap.add_argument("--weights", default="", choices=["", "int8", "int4", "mxfp8", "fp4", "ternary"],
+                    help="serve the block matrices from this low-bit format with the fused-dequant GEMM")
     ap.add_argument("--device", default="auto")
     a = ap.parse_args(argv)
     from ..inference.engine import EngineConfig, InferenceEngine
@@ -29,7 +31,7 @@ def main(argv=None):
         print(f"Error: {e}", file=sys.stderr)
         return 1
     tok = load_tokenizer(a.model, a.model_dir)
-    eng = InferenceEngine(model, tok, EngineConfig(kv_mode=a.kv, seed=resolve_base_seed(a.seed), num_pages=1024))
+    eng = InferenceEngine(model, tok, EngineConfig(kv_mode=a.kv, seed=resolve_base_seed(a.seed), num_pages=1024, weight_format=a.weights))
     t0 = time.perf_counter()
     n0 = eng.stats.generated_tokens
     text = eng.generate(a.prompt, min(a.max_tokens, model.cfg.max_seq_len - 1), SamplerConfig(0.7, 40, 0.9))

@@ -84,6 +84,7 @@ def main(argv=None):
     add_float(ap, "--top-p", 0.9)
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "q4"])
     ap.add_argument("--auth-token", default="")
+    ap.add_argument("--weights", default="", choices=["", "int8", "int4", "mxfp8", "fp4", "ternary"])
     ap.add_argument("--device", default="auto")
     a = ap.parse_args(argv)
     from ..inference.engine import EngineConfig, InferenceEngine
@@ -92,7 +93,7 @@ def main(argv=None):
     dev = pick_device(a.device)
     model = codec.load_model(a.model, device=dev, dtype=model_dtype(dev))
     tok = load_tokenizer(a.model, a.model_dir)
-    eng = InferenceEngine(model, tok, EngineConfig(max_batch=a.batch_size, kv_mode=a.kv, num_pages=4096))
+    eng = InferenceEngine(model, tok, EngineConfig(max_batch=a.batch_size, kv_mode=a.kv, num_pages=4096, weight_format=a.weights))
     svc = EngineService(eng, {"max_tokens": a.max_tokens})
     srv = HTTPServer(a.port)
     srv.set_thread_pool_size(max(a.workers, a.batch_size))

@@ -38,6 +38,8 @@ class EngineConfig:
     max_seq_len: int = 0           # 0 -> model config
     enable_prefix_cache: bool = True
     seed: int = 42
+    weight_format: str = ""        # "" = bf16 weights; int8 | int4 | mxfp8 | fp4 | ternary: fused-dequant GEMM (quant/wq.py)
+    weight_group: int = 32
 
 
 @dataclass
@@ -125,6 +127,19 @@ class InferenceEngine:
         self._step = 0
         self.stats = InferenceStats()
         self.max_pages = (self.max_len + PAGE - 1) // PAGE
+        self.packed = {}
+        if cfg.weight_format:
+            from ..quant import wq
+            self._wq = wq
+            self.packed = wq.quantize_model_linears(model, cfg.weight_format, cfg.weight_group, min_numel=0)
+
+    def _lin(self, x, li, name, w, bias=None, residual=None):
+        """x @ W^T (+ bias) (+ residual) with W either the bf16 parameter or its packed low-bit form."""
+        pw = self.packed.get(f"layers.{li}.{name}")
+        if pw is None:
+            return F.gemm(x, w.data, bias=bias, residual=residual)
+        y = self._wq.gemm_wq(x, pw, bias)
+        return y if residual is None else y + residual
 
     # ------------------------------------------------------------------ request management
     def add_request(self, tokens, max_tokens=64, sampling: Optional[SamplerConfig] = None, priority=0,
@@ -162,7 +177,7 @@ class InferenceEngine:
                              device=dev)
         for li, w in enumerate(m.layers):
             a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
-            qkv = F.gemm(a, w.qkv.data, bias=w.qkv_bias)
+            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
@@ -176,15 +191,15 @@ class InferenceEngine:
                 lens = (positions + 1).to(torch.int32)
                 o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), bt, lens, Hq)
             if mc.use_parallel_residual:
-                attn = F.gemm(o, w.o.data, bias=w.o_bias)
+                attn = self._lin(o, li, "o", w.o, w.o_bias)
                 f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
                 base = h
             else:
-                base = F.gemm(o, w.o.data, bias=w.o_bias, residual=h)
+                base = self._lin(o, li, "o", w.o, w.o_bias, h)
                 f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
-            gu = F.gemm(f, w.gate_up.data, bias=w.gate_up_bias)
+            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
             act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
-            h = F.gemm(act, w.down.data, bias=w.down_bias, residual=base)
+            h = self._lin(act, li, "down", w.down, w.down_bias, base)
             if mc.use_parallel_residual:
                 h = h + attn
         return h if all_positions else h[-1:]
@@ -200,21 +215,21 @@ class InferenceEngine:
         lens = (positions + 1).to(torch.int32)
         for li, w in enumerate(m.layers):
             a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
-            qkv = F.gemm(a, w.qkv.data, bias=w.qkv_bias)
+            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, 1, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
             o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), block_table, lens, Hq)
             if mc.use_parallel_residual:
-                attn = F.gemm(o, w.o.data, bias=w.o_bias)
+                attn = self._lin(o, li, "o", w.o, w.o_bias)
                 f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
                 base = h
             else:
-                base = F.gemm(o, w.o.data, bias=w.o_bias, residual=h)
+                base = self._lin(o, li, "o", w.o, w.o_bias, h)
                 f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
-            gu = F.gemm(f, w.gate_up.data, bias=w.gate_up_bias)
+            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
             act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
-            h = F.gemm(act, w.down.data, bias=w.down_bias, residual=base)
+            h = self._lin(act, li, "down", w.down, w.down_bias, base)
             if mc.use_parallel_residual:
                 h = h + attn
         return h
