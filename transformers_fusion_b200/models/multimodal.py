@@ -123,7 +123,7 @@ class VisionTransformer(nn.Module):
         x = torch.cat([self.cls.to(x.dtype).expand(x.shape[0], -1, -1), x], 1) + self.pos.to(x.dtype)[:, : x.shape[1] + 1]
         for b in self.blocks:
             x = b(x)
-        x = self.norm(x.float()).to(x.dtype)
+        x = self.norm(x)
         return x if return_tokens else x[:, 0]
 
 

@@ -92,7 +92,8 @@ def pack_weight(w: torch.Tensor, fmt="int8", group: int = 64, pow2_scales: Optio
         codes = codes[:, 0::4] | (codes[:, 1::4] << 2) | (codes[:, 2::4] << 4) | (codes[:, 3::4] << 6)
     rb = codes.shape[1] * 64 // Kp                       # bytes per row per k-block
     NB, KB = Np // 128, Kp // 64
-    ct = codes.view(NB, 128, KB, rb).permute(0, 2, 1, 3).contiguous()
+    U = min(16, rb // 2)                                 # unit-major inside a tile: unit u of row r at (u * 128 + r) * U
+    ct = codes.view(NB, 128, KB, rb // U, U).permute(0, 2, 3, 1, 4).contiguous()
     st = scales.view(NB, 128, KB, 64 // group).permute(0, 2, 1, 3).contiguous().to(torch.bfloat16)
     return PackedWeight(ct.view(-1), st.view(-1), f, group, N, K, Np, Kp)
 
@@ -101,7 +102,8 @@ def dequant(pw: PackedWeight) -> torch.Tensor:
     """fp32 [N, K] image of a packed weight (the oracle of the kernel)."""
     NB, KB = pw.Np // 128, pw.Kp // 64
     rb = {0: 64, 1: 32, 2: 64, 3: 32, 4: 16}[pw.fmt]
-    c = pw.codes.view(NB, KB, 128, rb).permute(0, 2, 1, 3).reshape(pw.Np, KB * rb)
+    U = min(16, rb // 2)
+    c = pw.codes.view(NB, KB, rb // U, 128, U).permute(0, 3, 1, 2, 4).reshape(pw.Np, KB * rb)
     s = pw.scales.view(NB, KB, 128, 64 // pw.group).permute(0, 2, 1, 3).reshape(pw.Np, pw.Kp // pw.group).float()
     if pw.fmt in (1, 3):
         c = torch.stack([c & 15, c >> 4], -1).reshape(pw.Np, pw.Kp)
