@@ -113,3 +113,23 @@ def test_engine_with_packed_weights_matches_dequantised_model():
             getattr(l, name).data.copy_(wq.dequant(eng.packed[f"layers.{i}.{name}"]))
     out_ref = InferenceEngine(m2, None, EngineConfig(num_pages=32)).generate_batch([[5, 6, 7, 8]], 8, SamplerConfig(0.0))[0]
     assert out_q == out_ref
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("weights", ["", "int8"])
+def test_decode_graph_replay_matches_eager(weights):
+    """Captured decode steps (batch buckets 1, 2, 4 as requests finish at different lengths) give the eager tokens."""
+    m = _model("cuda", torch.bfloat16, hidden_size=256, num_heads=4, num_kv_heads=2)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(3, 200, (n,), generator=g).tolist() for n in (9, 33, 70)]
+    outs = []
+    for graph in (False, True):
+        eng = InferenceEngine(m, None, EngineConfig(max_batch=8, num_pages=128, cuda_graph=graph, weight_format=weights,
+                                                    enable_prefix_cache=False))
+        reqs = [eng.add_request(p, max_tokens=mt, sampling=GREEDY) for p, mt in zip(prompts, (4, 9, 14))]
+        while eng.has_pending():
+            eng.step()
+        outs.append([r.out for r in reqs])
+        if graph:
+            assert sorted(eng._graphs) == [1, 2, 4]
+    assert outs[0] == outs[1]

@@ -31,7 +31,7 @@ def test_device_format_choice():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt,group", [("int8", 64), ("int8", 32), ("int4", 32), ("mxfp8", 32), ("fp4", 64), ("ternary", 32)])
-@pytest.mark.parametrize("M", [1, 8, 200])
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 200, 2176])
 def test_gemm_wq_gpu(fmt, group, M):
     torch.manual_seed(1)
     N, K = 384, 1024
@@ -58,3 +58,15 @@ def test_quant_linear_module():
     assert y.shape == (2, 3, 256) and "bits/weight" in repr(lin)
     ref = x.float().view(-1, 512) @ wq.dequant(lin.pw).t()
     assert (y.float().view(-1, 256) - ref).abs().max() / ref.abs().max() < 1.5e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,group", [("int8", 64), ("int4", 32), ("mxfp8", 32), ("fp4", 32), ("ternary", 64)])
+def test_dequant_bf16_image_is_exact(fmt, group):
+    """The device image equals the fp32 oracle rounded to bf16, bit for bit."""
+    torch.manual_seed(3)
+    pw = wq.pack_weight(torch.randn(256, 320).cuda() * 0.07, fmt, group)
+    img = wq.dequant_bf16(pw)
+    ref = torch.zeros(pw.Np, pw.Kp, device="cuda")
+    ref[: pw.N, : pw.K] = wq.dequant(pw)
+    assert torch.equal(img.float(), ref.bfloat16().float())

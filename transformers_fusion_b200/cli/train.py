@@ -1,7 +1,8 @@
 """quant_train: dense pre-training from a text file.  Flags and log line follow tools/train.cpp:36-192
 (``--model --data --config --batch-size --seq-length --epochs --lr --vocab-size --hidden-size
 --num-layers --num-heads --log-interval --save-interval --optimizer adafactor|adamw --seed``); new:
-``--dp/--zero-stage/--resume/--device/--max-steps`` and an honoured ``--config`` JSON."""
+``--zero-stage/--resume/--device/--max-steps``, an honoured ``--config`` JSON, and the mesh flags ``--dp --tp --pp --ep``
+for jobs started with ``python -m torch.distributed.run`` (one process per GPU; see parallel/launch.py)."""
 from __future__ import annotations
 
 import argparse
@@ -34,6 +35,10 @@ def build_parser():
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--device", default="auto")
     ap.add_argument("--kind", default="dense")
+    add_int(ap, "--dp", 0, "Data-parallel degree (0 = world size / (tp x pp))")
+    add_int(ap, "--tp", 1, "Tensor-parallel degree (sequence parallel between the TP regions)")
+    add_int(ap, "--pp", 1, "Pipeline stages (1F1B)")
+    add_int(ap, "--ep", 1, "Expert-parallel degree (MoE models)")
     return ap
 
 
@@ -48,15 +53,23 @@ def main(argv=None):
     from ..models.dense import DenseModel
     from ..tokenizer import BPETokenizer
     from ..trainer.trainer import DataLoader, TrainConfig, Trainer
+    from ..parallel.launch import fit_parallel, init_parallel, shutdown
     seed = resolve_base_seed(args.seed)
     os.environ["QUANT_SEED"] = str(seed)
     torch.manual_seed(seed)
     over = json.load(open(args.config)) if args.config and os.path.exists(args.config) else {}
-    dev = pick_device(args.device)
-    # tokenizer: BPE trained on the first <= 64 MiB of the corpus (tools/train.cpp:119-156)
+    try:
+        st = init_parallel(args.dp, args.tp, args.pp, args.ep, args.device)
+    except ValueError as e:
+        print(f"Error: {e}", file=sys.stderr)
+        return 2
+    dev = st.device if st.world > 1 else pick_device(args.device)
+    # tokenizer: BPE trained on the first <= 64 MiB of the corpus (tools/train.cpp:119-156); deterministic, so every
+    # rank trains the same vocabulary and only rank 0 writes it
     text = open(args.data, "r", encoding="utf-8", errors="ignore").read(64 << 20)
     tok = BPETokenizer().train([text], args.vocab_size)
-    tok.save(args.model + ".vocab")
+    if st.is_main:
+        tok.save(args.model + ".vocab")
     heads = over.get("num_heads", args.num_heads)
     cfg = TransformerConfig(vocab_size=max(tok.vocab_size, 8), hidden_size=over.get("hidden_size", args.hidden_size),
                             num_layers=over.get("num_layers", args.num_layers), num_heads=heads,
@@ -66,15 +79,24 @@ def main(argv=None):
     tcfg = TrainConfig(batch_size=args.batch_size, seq_length=args.seq_length, epochs=args.epochs, learning_rate=args.lr,
                        log_interval=args.log_interval, save_interval=args.save_interval, optimizer=args.optimizer.lower(),
                        checkpoint_path=args.model, max_steps=args.max_steps, seed=seed, zero_stage=args.zero_stage)
-    tr = Trainer(model, tok).compile(None, tcfg)
-    tr.set_log_callback(lambda m: print(f"Step {m.step} | loss: {m.loss:.6g} | ppl: {m.perplexity:.6g} | lr: {m.learning_rate:.6g}"
-                                        f" | tok/s: {m.tokens_per_sec:.6g}", flush=True))
-    print(f"Using {'AdamW' if args.optimizer.lower() == 'adamw' else args.optimizer.capitalize()} optimizer via UnifiedTrainer ({args.kind}).")
-    dl = DataLoader(tok, args.data, args.batch_size, args.seq_length, device=dev)
-    if args.resume and os.path.exists(args.model):
-        tr.load_checkpoint(args.model, dl)
-    tr.fit(dl)
-    print(f"Training complete. Model saved to {args.model}")
+    line = lambda step, loss, ppl, lr, tps: print(f"Step {step} | loss: {loss:.6g} | ppl: {ppl:.6g} | lr: {lr:.6g} | tok/s: {tps:.6g}",
+                                                  flush=True)
+    if st.is_main:
+        print(f"Using {'AdamW' if args.optimizer.lower() == 'adamw' else args.optimizer.capitalize()} optimizer via UnifiedTrainer ({args.kind}).")
+    if st.world > 1:
+        if st.is_main:
+            print(f"Parallel mesh: dp={st.dp} tp={st.tp} pp={st.pp} ep={st.ep} on {st.world} ranks")
+        fit_parallel(model, tok, args.data, tcfg, st, line, args.resume)
+        shutdown(st)
+    else:
+        tr = Trainer(model, tok).compile(None, tcfg)
+        tr.set_log_callback(lambda m: line(m.step, m.loss, m.perplexity, m.learning_rate, m.tokens_per_sec))
+        dl = DataLoader(tok, args.data, args.batch_size, args.seq_length, device=dev)
+        if args.resume and os.path.exists(args.model):
+            tr.load_checkpoint(args.model, dl)
+        tr.fit(dl)
+    if st.is_main:
+        print(f"Training complete. Model saved to {args.model}")
     return 0
 
 

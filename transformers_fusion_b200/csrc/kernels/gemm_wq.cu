@@ -12,14 +12,21 @@
 // U = min(16, row_bytes / 2) bytes and stored unit-major: unit u of row r at ((u * 128) + r) * U, so that the 32 lanes of a
 // warp (32 consecutive rows) read consecutive addresses of shared memory.  Scales: [(nb * KB + kb) * 128 + r][64 / group].
 //
-// One persistent CTA per SM, 480 threads:
-//   warp 0       TMA producer of the activation tiles (128 rows x 64 k, zero-filled past M), 3-stage ring with the B tiles
+// One persistent CTA per SM, 768 threads:
+//   warp 0       TMA producer of the activation tiles (128 rows x 64 k, zero-filled past M), 4-stage ring with the B tiles
 //   warp 1       MMA issuer (tcgen05.mma 128 x 128 x 16, accumulator in TMEM, double-buffered)
-//   warps 2-9    dequantisers: thread (row r, half h) turns 32 codes of one weight row into bf16 and stores them into the
-//                B tile in the 128-byte-swizzled K-major layout the MMA descriptor expects, then fence.proxy.async + arrive
-//   warps 10-13  epilogue: TMEM -> registers -> bf16 store (+ bias), or fp32 atomic accumulation for split-K
-//   warp 14      bulk-copy producer of the packed codes and scales (one contiguous blob per tile), 8-stage ring: the
+//   warp 2       bulk-copy producer of the packed codes and scales (one contiguous blob per tile), 8-stage ring: the
 //                weight stream stays ~68 KB per SM deep in flight, independent of the pace of the dequantisers
+//   warps 4-7    epilogue: TMEM -> registers -> bf16 store (+ bias), or fp32 vector atomics for split-K
+//   Every role but the MMA issuer waits with mbar_wait_sleep: a polling warp takes issue slots from the warps that share
+//   its scheduler, and the converters need those slots (they are the instruction-issue bound of this kernel).
+//   warps 8-23   dequantisers in two groups of eight warps; group g takes the k-blocks with (index & 1) == g, so two
+//                k-blocks are decoded at once and the latency of one (shared-memory round trips, proxy fence, barrier)
+//                hides behind the other.  Thread (row r, half h) of a group turns 32 codes of one weight row into bf16
+//                and stores them into the B tile in the 128-byte-swizzled K-major layout the MMA descriptor expects.
+// Inside a 32-bit word of 4-bit codes, nibble j holds element 2j and nibble j + 4 element 2j + 1 (j < 4), so that
+// (word >> 4j) & 0x000F000F is the bf16x2-aligned pair (2j, 2j + 1); 2-bit codes likewise: field j = element 2j, field
+// j + 8 = element 2j + 1 (j < 8).
 // Small-M (decode) problems are weight-bandwidth bound; split-K spreads the few N tiles over all SMs.
 //
 // Reference counterparts: the CPU quantised matmul kernels (src/kernel/kernel_quant8.cpp, kernel_quant4.cpp, kernel_tl.cpp
@@ -29,12 +36,22 @@
 
 namespace tfb {
 
-constexpr int WQ_BM = 128, WQ_BN = 128, WQ_BK = 64, WQ_STAGES = 3, WQ_RAW_STAGES = 8, WQ_THREADS = 480, WQ_DQ_THREADS = 256;
-constexpr int WQ_A_BYTES = WQ_BM * WQ_BK * 2, WQ_B_BYTES = WQ_BN * WQ_BK * 2, WQ_STAGE = WQ_A_BYTES + WQ_B_BYTES;
+constexpr int WQ_BM = 128, WQ_BN = 128, WQ_BK = 64, WQ_RAW_STAGES = 8, WQ_THREADS = 768, WQ_DQ_THREADS = 256;
+constexpr int WQ_B_BYTES = WQ_BN * WQ_BK * 2;
 constexpr int WQ_RAW_CODES = 128 * 64, WQ_RAW_STAGE = WQ_RAW_CODES + 128 * 2 * 2;     // codes (<= 8 KB) + scales (<= 512 B)
-constexpr int WQ_RAW_OFF = WQ_STAGES * WQ_STAGE;
-constexpr int WQ_BAR_OFF = WQ_RAW_OFF + WQ_RAW_STAGES * WQ_RAW_STAGE;
-constexpr int WQ_SMEM = WQ_BAR_OFF + 512 + 1024;
+// Shared-memory plan for an activation tile of AROWS real rows.  The MMA always multiplies 128 rows; with AROWS = 16
+// (decode batches) only the first two 8-row swizzle groups of the A tile are loaded and the instruction reads on into the
+// B tile behind them: rows are independent in D = A * B, and accumulator rows past M are never stored.  The small A tile
+// doubles the ring depth, which is what covers the commit -> refill round trip when the MMAs themselves are short.
+template <int AROWS>
+struct WqPlan {
+  static constexpr int STAGES = AROWS == 16 ? 8 : 4;
+  static constexpr int A_BYTES = AROWS * WQ_BK * 2;
+  static constexpr int STAGE = A_BYTES + WQ_B_BYTES;
+  static constexpr int RAW_OFF = STAGES * STAGE;
+  static constexpr int BAR_OFF = RAW_OFF + WQ_RAW_STAGES * WQ_RAW_STAGE;
+  static constexpr int SMEM = BAR_OFF + 512 + 1024;
+};
 
 struct WqParams {
   int M, N, K;
@@ -123,11 +140,8 @@ __device__ __forceinline__ void wq_convert(const uint32_t (&w)[8], uint32_t sbit
   } else if (FMT == 1) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;   // even / odd k, one code per byte
-      o[4 * i + 0] = bf2((__byte_perm(lo, hi, 0x0400) & 0x00FF00FFu) | 0x43004300u, 0x43084308u);
-      o[4 * i + 1] = bf2((__byte_perm(lo, hi, 0x0501) & 0x00FF00FFu) | 0x43004300u, 0x43084308u);
-      o[4 * i + 2] = bf2((__byte_perm(lo, hi, 0x0602) & 0x00FF00FFu) | 0x43004300u, 0x43084308u);
-      o[4 * i + 3] = bf2((__byte_perm(lo, hi, 0x0703) & 0x00FF00FFu) | 0x43004300u, 0x43084308u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[4 * i + j] = bf2(((w[i] >> (4 * j)) & 0x000F000Fu) | 0x43004300u, 0x43084308u);
     }
   } else if (FMT == 2) {
 #pragma unroll
@@ -144,8 +158,7 @@ __device__ __forceinline__ void wq_convert(const uint32_t (&w)[8], uint32_t sbit
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t t = w[i] >> (8 * j);
-        const uint32_t y = (t & 0xFu) | ((t & 0xF0u) << 12);                     // nibbles at bits 0-3 and 16-19
+        const uint32_t y = (w[i] >> (4 * j)) & 0x000F000Fu;
         const uint32_t h2 = ((y & 0x00070007u) << 9) | ((y & 0x00080008u) << 12);
         const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
         o[4 * i + j] = pack_bf16(f.x * s14, f.y * s14);
@@ -154,20 +167,16 @@ __device__ __forceinline__ void wq_convert(const uint32_t (&w)[8], uint32_t sbit
   } else {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      // stream m holds the codes k = 4 * byte + m, one per byte
-      const uint32_t c0 = w[i] & 0x03030303u, c1 = (w[i] >> 2) & 0x03030303u, c2 = (w[i] >> 4) & 0x03030303u, c3 = (w[i] >> 6) & 0x03030303u;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t sel = uint32_t(((4 + j) << 8) | j);
-        o[8 * i + 2 * j] = bf2((__byte_perm(c0, c1, sel) & 0x00FF00FFu) | 0x43004300u, 0x43014301u);
-        o[8 * i + 2 * j + 1] = bf2((__byte_perm(c2, c3, sel) & 0x00FF00FFu) | 0x43004300u, 0x43014301u);
-      }
+      for (int j = 0; j < 8; ++j) o[8 * i + j] = bf2(((w[i] >> (2 * j)) & 0x00030003u) | 0x43004300u, 0x43014301u);
     }
   }
 }
 
-template <int FMT>
+template <int FMT, int AROWS>
 __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ CUtensorMap tma_a, const WqParams p) {
+  using PL = WqPlan<AROWS>;
+  constexpr int WQ_STAGES = PL::STAGES, WQ_A_BYTES = PL::A_BYTES, WQ_STAGE = PL::STAGE, WQ_RAW_OFF = PL::RAW_OFF, WQ_BAR_OFF = PL::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -235,7 +244,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         int m0, nb, kb0, kb1;
         decode(w, m0, nb, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait_sleep(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 32)) { ok = false; break; }
           const uint32_t fb = bar_full + stage * 8;
           mbar_expect_tx(fb, WQ_A_BYTES);
           tma_load_2d(smem_base + stage * WQ_STAGE, &tma_a, fb, kb * WQ_BK, m0);
@@ -244,7 +253,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
       }
       if (!ok) drain();
     }
-  } else if (warp == 14) {
+  } else if (warp == 2) {
     if (lane == 0) {
       int rs = 0;
       uint32_t rphase = 0;
@@ -253,7 +262,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         int m0, nb, kb0, kb1;
         decode(w, m0, nb, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_rempty + rs * 8, rphase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait_sleep(bar_rempty + rs * 8, rphase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 32)) { ok = false; break; }
           const long long tile = (long long)nb * KB + kb;
           const uint32_t rb_ = bar_rfull + rs * 8, dst = smem_base + WQ_RAW_OFF + rs * WQ_RAW_STAGE;
           mbar_expect_tx(rb_, code_bytes + scale_bytes);
@@ -293,29 +302,30 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         if (abuf == 0) aphase ^= 1;
       }
     }
-  } else if (warp < 10) {
-    // ------------------------------ dequantisers: 32 k of one weight row per thread ------------------------------
-    const int t = threadIdx.x - 64, r = t & 127, h = t >> 7;
+  } else if (warp >= 8) {
+    // ------------------------------ dequantisers: 32 k of one weight row per thread, two groups on alternate k-blocks ------
+    const int t = threadIdx.x - 256, g = t >> 8, r = t & 127, h = (t >> 7) & 1;
     const uint32_t scale_off = WQ_RAW_CODES + (p.group == 32 ? (r * 2 + h) * 2 : r * 2);
     const uint32_t xr = uint32_t(r & 7);
-    int stage = 0, rs = 0;
-    uint32_t phase = 0, rphase = 0;
+    int it = 0;
     bool ok = true;
     for (int w = cta; w < num_work && ok; w += nctas) {
       int m0, nb, kb0, kb1;
       decode(w, m0, nb, kb0, kb1);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_warp(bar_rfull + rs * 8, rphase, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if ((it & 1) != g) continue;
+        const int rs = it & (WQ_RAW_STAGES - 1), stage = it & (WQ_STAGES - 1);
+        const uint32_t rphase = (it / WQ_RAW_STAGES) & 1, phase = (it / WQ_STAGES) & 1;
+        if (!mbar_wait_sleep_warp(bar_rfull + rs * 8, rphase, abort_flag, p.status, ST_TIMEOUT_FULL, 40)) { ok = false; break; }
         const uint32_t raw = smem_base + WQ_RAW_OFF + rs * WQ_RAW_STAGE;
         uint32_t wd[8];
         wq_load_codes<FMT>(raw, r, h, wd);
         const uint32_t sbits = ld_shared_u16(raw + scale_off);
         __syncwarp();                                        // every lane holds its codes: one arrival per warp
         if (lane == 0) mbar_arrive(bar_rempty + rs * 8);
-        if (++rs == WQ_RAW_STAGES) { rs = 0; rphase ^= 1; }
         uint32_t o[16];
         wq_convert<FMT>(wd, sbits, o);
-        if (!mbar_wait_warp(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+        if (!mbar_wait_sleep_warp(bar_empty + stage * 8, phase ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 40)) { ok = false; break; }
         const uint32_t row_smem = smem_base + stage * WQ_STAGE + WQ_A_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -323,10 +333,9 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full + stage * 8);
-        if (++stage == WQ_STAGES) { stage = 0; phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------ epilogue ------------------------------
     const int quad = warp & 3;
     int abuf = 0;
@@ -335,35 +344,35 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
       int m0, nb, kb0, kb1;
       decode(w, m0, nb, kb0, kb1);
       if (kb1 <= kb0) continue;
-      if (!mbar_wait_warp(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      if (!mbar_wait_sleep_warp(bar_tfull + abuf * 8, aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 400)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr0 = tmem_base + abuf * WQ_BN + (uint32_t(quad * 32) << 16);
       // rows past M hold zeros: a warp whose 32 rows are all past M only releases the accumulator
       if (m0 + quad * 32 < p.M) {
 #pragma unroll 1
-        for (int c = 0; c < WQ_BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr0 + c * 32, v);
+        for (int c = 0; c < WQ_BN / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x16(taddr0 + c * 16, v);
           tmem_ld_wait();
-          const int col0 = nb * WQ_BN + c * 32;
-          if (row >= p.M || col0 >= p.N) continue;
-          // N is a multiple of 128 and ldc of 8 (the packer pads), so every 32-column run is whole and 16-byte aligned
-          float f[32];
+          const int col0 = nb * WQ_BN + c * 16;
+          if (row >= p.M) continue;
+          // N is a multiple of 128 and ldc of 8 (the packer pads), so every 16-column run is whole and 16-byte aligned
+          float f[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
           if (p.bias && kb0 == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] += __bfloat162float(p.bias[col0 + j]);
+            for (int j = 0; j < 16; ++j) f[j] += __bfloat162float(p.bias[col0 + j]);
           }
           if (p.splits > 1) {
             float4* cp = reinterpret_cast<float4*>(static_cast<float*>(p.C) + (long long)row * p.ldc + col0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) atomicAdd(cp + j, make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]));
+            for (int j = 0; j < 4; ++j) atomicAdd(cp + j, make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]));
           } else {
             uint4* cp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 2; ++j)
               cp[j] = make_uint4(pack_bf16(f[8 * j], f[8 * j + 1]), pack_bf16(f[8 * j + 2], f[8 * j + 3]), pack_bf16(f[8 * j + 4], f[8 * j + 5]),
                                  pack_bf16(f[8 * j + 6], f[8 * j + 7]));
           }
@@ -383,7 +392,56 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
   }
 }
 
+// Whole-matrix dequantisation to row-major bf16 (large-M products run as a plain bf16 GEMM on this image; the image lives in
+// a scratch buffer the caller reuses, so the weights stay packed in HBM between calls).  One CTA per tile, thread (r, h).
+template <int FMT>
+__global__ void __launch_bounds__(256) wq_dequant_kernel(const uint8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scales, int group,
+                                                          __nv_bfloat16* __restrict__ out, long long ld, int KB) {
+  constexpr int RB = wq_row_bytes(FMT);
+  const int kb = blockIdx.x, nb = blockIdx.y, r = threadIdx.x & 127, h = threadIdx.x >> 7;
+  const long long tile = (long long)nb * KB + kb;
+  const uint8_t* raw = wq + tile * (128 * RB);
+  uint32_t w[8];
+  if (FMT == 0 || FMT == 2) {
+    const uint4 a = *reinterpret_cast<const uint4*>(raw + ((2 * h) * 128 + r) * 16), b = *reinterpret_cast<const uint4*>(raw + ((2 * h + 1) * 128 + r) * 16);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  } else if (FMT == 1 || FMT == 3) {
+    const uint4 a = *reinterpret_cast<const uint4*>(raw + (h * 128 + r) * 16);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+  } else {
+    const uint2 a = *reinterpret_cast<const uint2*>(raw + (h * 128 + r) * 8);
+    w[0] = a.x; w[1] = a.y;
+  }
+  const int spr = WQ_BK / group;
+  const uint16_t sb = reinterpret_cast<const uint16_t*>(scales)[(tile * 128 + r) * spr + (group == 32 ? h : 0)];
+  uint32_t o[16];
+  wq_convert<FMT>(w, uint32_t(sb), o);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)(nb * 128 + r) * ld + kb * 64 + h * 32);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) dst[c] = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+}
+
 }  // namespace tfb
+
+// out [N, ld] bf16 row-major (ld % 8 == 0) = dequant(wq); N % 128 == 0, K % 64 == 0.
+TFB_API int tfb_wq_dequant(const void* wq, const void* scales, int fmt, int group, void* out, long long ld, int N, int K, void* stream) {
+  using namespace tfb;
+  if (N <= 0 || K <= 0 || K % WQ_BK || N % WQ_BN || fmt < 0 || fmt > 4 || (group != 32 && group != 64) || ld % 8) return TFB_ERR_ARG;
+  const dim3 grid(K / WQ_BK, N / WQ_BN);
+  const auto* c = static_cast<const uint8_t*>(wq);
+  const auto* sc = static_cast<const __nv_bfloat16*>(scales);
+  auto* o = static_cast<__nv_bfloat16*>(out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (fmt) {
+    case 0: wq_dequant_kernel<0><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+    case 1: wq_dequant_kernel<1><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+    case 2: wq_dequant_kernel<2><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+    case 3: wq_dequant_kernel<3><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+    default: wq_dequant_kernel<4><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+  }
+  const int rc = int(cudaGetLastError());
+  return rc ? -1000 - rc : 0;
+}
 
 // A [M, lda] bf16 (K % 64 == 0, N % 128 == 0: the packer pads).  wq / scales in the tile-major layout described at the top.
 // splits == 1: C bf16 [M, ldc]; splits > 1: C fp32 [M, ldc], accumulated into (zero it first).  splits == 0 picks a value
@@ -393,7 +451,8 @@ TFB_API int tfb_gemm_wq(const void* A, long long lda, const void* wq, const void
   using namespace tfb;
   if (M <= 0 || N <= 0 || K <= 0 || K % WQ_BK || N % WQ_BN || ldc % 8 || fmt < 0 || fmt > 4 || (group != 32 && group != 64)) return TFB_ERR_ARG;
   CUtensorMap ta;
-  if (int rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, WQ_BK, WQ_BM)) return rc;
+  const int arows = M <= 16 ? 16 : 128;
+  if (int rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, WQ_BK, arows)) return rc;
   WqParams p;
   p.M = M; p.N = N; p.K = K;
   p.wq = static_cast<const uint8_t*>(wq);
@@ -413,18 +472,23 @@ TFB_API int tfb_gemm_wq(const void* A, long long lda, const void* wq, const void
   p.kb_per_split = (KB + splits - 1) / splits;
   p.splits = (KB + p.kb_per_split - 1) / p.kb_per_split;
   using Kern = void (*)(const CUtensorMap, const WqParams);
-  static const Kern kerns[5] = {gemm_wq_kernel<0>, gemm_wq_kernel<1>, gemm_wq_kernel<2>, gemm_wq_kernel<3>, gemm_wq_kernel<4>};
+  static const Kern kerns[2][5] = {
+      {gemm_wq_kernel<0, 16>, gemm_wq_kernel<1, 16>, gemm_wq_kernel<2, 16>, gemm_wq_kernel<3, 16>, gemm_wq_kernel<4, 16>},
+      {gemm_wq_kernel<0, 128>, gemm_wq_kernel<1, 128>, gemm_wq_kernel<2, 128>, gemm_wq_kernel<3, 128>, gemm_wq_kernel<4, 128>}};
+  static const int smem_of[2] = {WqPlan<16>::SMEM, WqPlan<128>::SMEM};
   static bool configured = false;
   if (!configured) {
-    for (Kern k : kerns) {
-      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM);
-      if (e != cudaSuccess) return int(e);
-    }
+    for (int a = 0; a < 2; ++a)
+      for (Kern k : kerns[a]) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of[a]);
+        if (e != cudaSuccess) return int(e);
+      }
     configured = true;
   }
   const long long work = (long long)tiles * p.splits;
   const int grid = int(work < sms ? work : sms);
-  kerns[fmt]<<<grid, WQ_THREADS, WQ_SMEM, static_cast<cudaStream_t>(stream)>>>(ta, p);
+  const int ai = arows == 16 ? 0 : 1;
+  kerns[ai][fmt]<<<grid, WQ_THREADS, smem_of[ai], static_cast<cudaStream_t>(stream)>>>(ta, p);
   const int rc = int(cudaGetLastError());
   return rc ? -1000 - rc : p.splits;
 }

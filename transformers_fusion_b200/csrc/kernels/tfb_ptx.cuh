@@ -89,6 +89,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait that sleeps between polls.  A warp that polls in a tight loop takes issue slots from the other warps of
+// its scheduler; the single-thread roles of a warp-specialised kernel (TMA producer, MMA issuer) then run several times
+// slower than their instruction count suggests.  Roles that wait long (an epilogue waiting for a whole K loop, converters
+// waiting for a ring slot) use this form; `sleep_ns` bounds the extra wake-up latency.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > TFB_WAIT_NS) {
+        report(status, code);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_sleep_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                     uint32_t sleep_ns) {
+  const bool ok = mbar_wait_sleep(bar, parity, abort_flag, status, code, sleep_ns);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Warp-collective form for warps that go on to execute .sync.aligned instructions (tcgen05.ld/st):
 // every lane polls, then the warp votes, so all 32 lanes take the same branch even when a wait runs out.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,

@@ -40,6 +40,7 @@ class EngineConfig:
     seed: int = 42
     weight_format: str = ""        # "" = bf16 weights; int8 | int4 | mxfp8 | fp4 | ternary: fused-dequant GEMM (quant/wq.py)
     weight_group: int = 32
+    cuda_graph: bool = True        # decode steps replay a captured graph per batch-size bucket (CUDA only)
 
 
 @dataclass
@@ -113,6 +114,43 @@ class PrefixCache:
         self.table.clear()
 
 
+class _DecodeGraph:
+    """One captured decode step (all layers + final norm + LM head) for a fixed batch-size bucket.  Inputs live in static
+    device buffers that the scheduler fills before each replay; rows past the live batch carry slot -1 (no KV write)
+    and attend to one token of page 0, and their logits are ignored."""
+
+    def __init__(self, eng, bucket: int):
+        dev = eng.device
+        self.bucket = bucket
+        self.tokens = torch.zeros(bucket, dtype=torch.int64, device=dev)
+        self.positions = torch.zeros(bucket, dtype=torch.int32, device=dev)
+        self.bt = torch.zeros((bucket, eng.max_pages), dtype=torch.int32, device=dev)
+        self.slots = torch.full((bucket,), -1, dtype=torch.int64, device=dev)
+        run = lambda: eng._logits(eng._layers_decode(self.tokens, self.positions, self.bt, self.slots))
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                  # warm-up outside capture: workspaces, status words, lazy tables
+            for _ in range(2):
+                run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = run()
+
+    def replay(self, tokens, positions, bt, slots):
+        n = tokens.shape[0]
+        self.tokens[:n].copy_(tokens, non_blocking=True)
+        self.positions[:n].copy_(positions, non_blocking=True)
+        self.bt[:n].copy_(bt, non_blocking=True)
+        self.slots[:n].copy_(slots, non_blocking=True)
+        if n < self.bucket:
+            self.positions[n:].zero_()
+            self.slots[n:].fill_(-1)
+        self.graph.replay()
+        return self.logits[:n]
+
+
 class InferenceEngine:
     def __init__(self, model, tokenizer=None, cfg: EngineConfig = EngineConfig()):
         self.model, self.tok, self.cfg = model, tokenizer, cfg
@@ -125,6 +163,7 @@ class InferenceEngine:
         self.running: List[Request] = []
         self._ids = itertools.count(1)
         self._step = 0
+        self._graphs = {}
         self.stats = InferenceStats()
         self.max_pages = (self.max_len + PAGE - 1) // PAGE
         self.packed = {}
@@ -313,8 +352,17 @@ class InferenceEngine:
                 bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
             bt = bt.to(dev)
             slots = torch.tensor([r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs], dtype=torch.int64, device=dev)
-            h = self._layers_decode(tokens, positions, bt, slots)
-            toks = self._sample(self._logits(h), reqs)
+            if self.cfg.cuda_graph and dev.type == "cuda":
+                bucket = 1
+                while bucket < len(reqs):
+                    bucket *= 2
+                g = self._graphs.get(bucket)
+                if g is None:
+                    g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+                logits = g.replay(tokens, positions, bt, slots)
+            else:
+                logits = self._logits(self._layers_decode(tokens, positions, bt, slots))
+            toks = self._sample(logits, reqs)
             self.stats.decode_ms += (time.perf_counter() - t0) * 1e3
             still = []
             for r, tok in zip(reqs, toks):

@@ -39,8 +39,10 @@ def split_model(num_layers: int, num_stages: int, balance_weights: Optional[Sequ
 
 class PipelineParallel:
     def __init__(self, model, num_stages: int, stage_id: int, ctx: Optional[DistributedContext] = None,
-                 num_microbatches: int = 4, balance_weights=None):
+                 num_microbatches: int = 4, balance_weights=None, stage_ranks: Optional[Sequence[int]] = None):
         self.model, self.S, self.sid = model, num_stages, stage_id
+        # global rank of every stage of this pipeline (identity unless the pipeline is one slice of a larger job)
+        self.stage_ranks = list(stage_ranks) if stage_ranks is not None else list(range(num_stages))
         self.ctx = ctx or DistributedContext(stage_id, num_stages)
         self.num_microbatches = num_microbatches
         self.balance = balance_weights
@@ -78,7 +80,7 @@ class PipelineParallel:
         # non-blocking: in 1F1B neighbouring stages send to each other at the same time, and a blocking send on both
         # sides would wait for a receive that is never posted
         t = t.contiguous()
-        self._inflight.append((dist.isend(t, dst, group=self.ctx.group), t))
+        self._inflight.append((dist.isend(t, self.stage_ranks[dst], group=self.ctx.group), t))
 
     def _drain(self):
         for h, _ in self._inflight:
@@ -87,7 +89,7 @@ class PipelineParallel:
 
     def _recv(self, shape, dtype, src, device):
         t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, src, group=self.ctx.group)
+        dist.recv(t, self.stage_ranks[src], group=self.ctx.group)
         return t
 
     # ---- one micro-batch

@@ -75,10 +75,10 @@ class TpContext:
         self.epoch = 0
         self.parity = 0
 
-    def all_gather_gemm(self, x_shard, w, out=None):
-        """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K]."""
+    def all_gather_gemm(self, x_shard, w, out=None, b_mn=False):
+        """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K], or [K, N_local] with ``b_mn``."""
         Ms, K = x_shard.shape
-        M, N = Ms * self.world, w.shape[0]
+        M, N = Ms * self.world, (w.shape[1] if b_mn else w.shape[0])
         buf = self.gather[self.parity]
         xg = buf.view(torch.bfloat16, M * K).view(M, K)
         xg[self.rank * Ms:(self.rank + 1) * Ms].copy_(x_shard)      # producer kernels may write here directly
@@ -86,19 +86,20 @@ class TpContext:
         self.epoch += 1
         y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x_shard.device)
         tp = _Tp(1, self.rank, self.world, self.copy_ctas, self.epoch, self.ready.data_ptr(), buf.ptrs.data_ptr(), None)
-        check(_fn()(xg.data_ptr(), K, w.data_ptr(), w.stride(0), 0, y.data_ptr(), y.stride(0), M, N, K, C.byref(tp),
+        check(_fn()(xg.data_ptr(), K, w.data_ptr(), w.stride(0), int(b_mn), y.data_ptr(), y.stride(0), M, N, K, C.byref(tp),
                     _lib.status_word(x_shard.device).data_ptr(), stream()), "all_gather_gemm")
         self.parity ^= 1
         return y, xg
 
-    def gemm_reduce_scatter(self, x, w, residual=None):
-        """x [M, K_local], ``w`` [N, K_local] -> y_shard [M/W, N] = sum over ranks of the partial products."""
+    def gemm_reduce_scatter(self, x, w, residual=None, b_mn=False):
+        """x [M, K_local], ``w`` [N, K_local] (or [K_local, N] with ``b_mn``) -> y_shard [M/W, N] = sum over ranks of the
+        partial products."""
         M, K = x.shape
-        N = w.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
         Ms = M // self.world
         buf = self.stage[self.parity]
         tp = _Tp(2, self.rank, self.world, 0, 0, None, None, buf.ptrs.data_ptr())
-        check(_fn()(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), 0, None, N, M, N, K, C.byref(tp),
+        check(_fn()(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn), None, N, M, N, K, C.byref(tp),
                     _lib.status_word(x.device).data_ptr(), stream()), "gemm_reduce_scatter")
         self.symm.barrier()                                           # all partial tiles have arrived
         out = torch.empty((Ms, N), dtype=torch.bfloat16, device=x.device)
@@ -143,23 +144,6 @@ class RowParallelLinear(torch.nn.Module):
         if residual_shard is not None:
             out = out + residual_shard.float()
         return out.to(x.dtype)
-
-
-class SequenceParallel:
-    """scatter / gather along the sequence (row) dimension around the TP region."""
-
-    def __init__(self, rank, world, group=None):
-        self.rank, self.world, self.group = rank, world, group
-
-    def scatter(self, x, dim=0):
-        return x.chunk(self.world, dim)[self.rank].contiguous()
-
-    def gather(self, x_shard, dim=0):
-        if self.world == 1:
-            return x_shard
-        xs = [torch.empty_like(x_shard) for _ in range(self.world)]
-        dist.all_gather(xs, x_shard.contiguous(), group=self.group)
-        return torch.cat(xs, dim)
 
 
 # ---------------------------------------------------------------------------------------------- manager API

@@ -23,6 +23,7 @@ BITS = {0: 8, 1: 4, 2: 8, 3: 4, 4: 2}
 _E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
 
 _lib.register("tfb_gemm_wq", [c_p, c_ll, c_p, c_p, c_i, c_i, c_p, c_ll, c_i, c_i, c_i, c_p, c_i, c_i, c_p, c_p])
+_lib.register("tfb_wq_dequant", [c_p, c_p, c_i, c_i, c_p, c_ll, c_i, c_i, c_p])
 
 
 @dataclass
@@ -86,10 +87,16 @@ def pack_weight(w: torch.Tensor, fmt="int8", group: int = 64, pow2_scales: Optio
     wp[:N, :K] = w.float()
     codes, scales, _ = _quantise(wp, f, group, pow2_scales)
     # pack codes along k
+    # order inside a 32-bit word (see gemm_wq.cu): 4-bit: nibble j = element 2j, nibble j + 4 = element 2j + 1 (j < 4);
+    # 2-bit: field j = element 2j, field j + 8 = element 2j + 1 (j < 8)
     if f in (1, 3):
-        codes = codes[:, 0::2] | (codes[:, 1::2] << 4)
+        c = codes.view(Np, Kp // 8, 8)
+        e = lambda i: c[..., i]
+        codes = torch.stack([e(0) | (e(2) << 4), e(4) | (e(6) << 4), e(1) | (e(3) << 4), e(5) | (e(7) << 4)], -1).reshape(Np, Kp // 2)
     elif f == 4:
-        codes = codes[:, 0::4] | (codes[:, 1::4] << 2) | (codes[:, 2::4] << 4) | (codes[:, 3::4] << 6)
+        c = codes.view(Np, Kp // 16, 16)
+        byte = lambda a: c[..., a[0]] | (c[..., a[1]] << 2) | (c[..., a[2]] << 4) | (c[..., a[3]] << 6)
+        codes = torch.stack([byte((0, 2, 4, 6)), byte((8, 10, 12, 14)), byte((1, 3, 5, 7)), byte((9, 11, 13, 15))], -1).reshape(Np, Kp // 4)
     rb = codes.shape[1] * 64 // Kp                       # bytes per row per k-block
     NB, KB = Np // 128, Kp // 64
     U = min(16, rb // 2)                                 # unit-major inside a tile: unit u of row r at (u * 128 + r) * U
@@ -106,9 +113,15 @@ def dequant(pw: PackedWeight) -> torch.Tensor:
     c = pw.codes.view(NB, KB, rb // U, 128, U).permute(0, 3, 1, 2, 4).reshape(pw.Np, KB * rb)
     s = pw.scales.view(NB, KB, 128, 64 // pw.group).permute(0, 2, 1, 3).reshape(pw.Np, pw.Kp // pw.group).float()
     if pw.fmt in (1, 3):
-        c = torch.stack([c & 15, c >> 4], -1).reshape(pw.Np, pw.Kp)
+        b = c.view(pw.Np, pw.Kp // 8, 4)
+        lo, hi = b & 15, b >> 4                       # nibbles 0, 2, 4, 6 / 1, 3, 5, 7 of the word
+        nib = torch.stack([lo, hi], -1).reshape(pw.Np, pw.Kp // 8, 8)          # nibble order 0..7
+        c = torch.stack([nib[..., 0], nib[..., 4], nib[..., 1], nib[..., 5], nib[..., 2], nib[..., 6], nib[..., 3], nib[..., 7]],
+                        -1).reshape(pw.Np, pw.Kp)
     elif pw.fmt == 4:
-        c = torch.stack([c & 3, (c >> 2) & 3, (c >> 4) & 3, c >> 6], -1).reshape(pw.Np, pw.Kp)
+        b = c.view(pw.Np, pw.Kp // 16, 4)
+        fld = torch.stack([b & 3, (b >> 2) & 3, (b >> 4) & 3, b >> 6], -1).reshape(pw.Np, pw.Kp // 16, 16)   # field order 0..15
+        c = torch.stack([fld[..., j // 2 + 8 * (j % 2)] for j in range(16)], -1).reshape(pw.Np, pw.Kp)
     if pw.fmt == 0:
         v = c.view(torch.int8).float()
     elif pw.fmt == 1:
@@ -122,13 +135,43 @@ def dequant(pw: PackedWeight) -> torch.Tensor:
     return (v.view(pw.Np, pw.Kp // pw.group, pw.group) * s.unsqueeze(-1)).view(pw.Np, pw.Kp)[: pw.N, : pw.K]
 
 
+_SCRATCH = {}
+LARGE_M = 2048    # from here on a bf16 image in scratch + the plain bf16 GEMM beats dequantising every tile once per M-tile
+
+
+def dequant_bf16(pw: PackedWeight) -> torch.Tensor:
+    """Row-major bf16 image [Np, Kp] of a packed weight in a per-device scratch buffer shared by all weights of that
+    size or smaller (overwritten by the next call)."""
+    dev = pw.codes.device
+    n = pw.Np * pw.Kp
+    buf = _SCRATCH.get(dev)
+    if buf is None or buf.numel() < n:
+        buf = _SCRATCH[dev] = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    out = buf[:n].view(pw.Np, pw.Kp)
+    check(_lib.lib().tfb_wq_dequant(pw.codes.data_ptr(), pw.scales.data_ptr(), pw.fmt, pw.group, out.data_ptr(), pw.Kp, pw.Np, pw.Kp,
+                                    stream()), "wq_dequant")
+    return out
+
+
 def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
-    """y [M, N] = x [M, K] @ dequant(pw)^T (+ bias).  bf16 in / out; small M uses split-K with fp32 accumulation."""
+    """y [M, N] = x [M, K] @ dequant(pw)^T (+ bias).  bf16 in / out.  M <= 16 (decode): fused-dequant kernel with the deep
+    ring and split-K; M < 2048: fused-dequant kernel with 128-row tiles; larger: bf16 image in scratch + bf16 GEMM."""
     M, K = x.shape
     if not x.is_cuda:
         y = x.float() @ dequant(pw).t()
         return (y + (bias.float() if bias is not None else 0)).to(x.dtype)
     assert x.dtype == torch.bfloat16
+    if M >= LARGE_M and splits == 0:
+        from ..ops import functional as F
+        if K != pw.Kp:
+            xp = torch.zeros((M, pw.Kp), dtype=x.dtype, device=x.device)
+            xp[:, :K] = x
+            x = xp
+        bp = None
+        if bias is not None:
+            bp = torch.zeros(pw.Np, dtype=torch.bfloat16, device=x.device)
+            bp[: pw.N] = bias
+        return F.gemm(x.contiguous(), dequant_bf16(pw), bias=bp)[:, : pw.N]
     if K != pw.Kp:
         xp = torch.zeros((M, pw.Kp), dtype=x.dtype, device=x.device)
         xp[:, :K] = x
