@@ -1,0 +1,139 @@
+"""Core value types, thread-safety helpers, ranking metrics, speculative-decoding extras, tiled long-context attention."""
+import math
+import threading
+
+import pytest
+import torch
+
+from transformers_fusion_b200.inference import speculative_extras as SX
+from transformers_fusion_b200.inference.kv_cache import PageAllocator
+from transformers_fusion_b200.utils import core as C, metrics as MX
+
+
+def test_types():
+    s = C.Shape(2, 3, 4)
+    assert s.rank == 3 and s.numel() == 24 and s.strides() == (12, 4, 1) and C.Shape([5]).numel() == 5
+    with pytest.raises(ValueError):
+        C.Shape(*range(9))
+    assert C.DType.U4.bits == 4 and C.DType.BF16.torch() == torch.bfloat16
+    assert C.Status.OK() and not C.Status.error("x") and C.Status.error("bad").message == "bad"
+    assert C.Config().seed == 42
+    with pytest.raises(RuntimeError):
+        C.quant_check(False, "boom")
+
+
+def test_spsc_queue_between_threads():
+    q = C.SPSCQueue(8)
+    assert q.capacity == 8 and q.empty() and q.pop() is None
+    got, N = [], 2000
+
+    def consumer():
+        while len(got) < N:
+            v = q.pop()
+            if v is not None:
+                got.append(v)
+    t = threading.Thread(target=consumer)
+    t.start()
+    i = 0
+    while i < N:
+        if q.push(i):
+            i += 1
+    t.join(10)
+    assert got == list(range(N))
+    for j in range(8):
+        assert q.push(j)
+    assert not q.push(99) and len(q) == 8
+
+
+def test_shared_mutex_atomic_float_spinlock_counter():
+    mu, state, seen = C.SharedMutex(), {"v": 0}, []
+
+    def writer():
+        for _ in range(200):
+            with mu.unique():
+                a = state["v"]
+                state["v"] = a + 1
+
+    def reader():
+        for _ in range(200):
+            with mu.shared():
+                seen.append(state["v"])
+    ts = [threading.Thread(target=f) for f in (writer, writer, reader, reader)]
+    [t.start() for t in ts]
+    [t.join(10) for t in ts]
+    assert state["v"] == 400 and len(seen) == 400
+    af, lock, total = C.AtomicFloat(), C.SpinLock(), {"n": 0}
+    cnt = C.ThreadSafeCounter()
+
+    def work():
+        for _ in range(500):
+            af.fetch_add(0.5)
+            with lock:
+                total["n"] += 1
+            cnt.increment("steps")
+    ts = [threading.Thread(target=work) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join(10) for t in ts]
+    assert af.load() == 1000.0 and total["n"] == 2000 and cnt.get("steps") == 2000
+    assert af.compare_exchange(1000.0, 1.0) and not af.compare_exchange(5.0, 2.0) and af.fetch_max(3.0) == 1.0 and af.load() == 3.0
+    assert lock.try_lock() and not lock.try_lock()
+    lock.unlock()
+    cnt.reset("steps")
+    assert cnt.snapshot() == {}
+
+
+def test_ranking_metrics():
+    assert MX.average_precision([0.9, 0.8, 0.7, 0.6], [1, 0, 1, 0]) == pytest.approx((1 + 2 / 3) / 2)
+    assert MX.mean_average_precision([[0.9, 0.1], [0.2, 0.8], [0.5, 0.4]], [[1, 0], [1, 0], [0, 0]]) == pytest.approx((1 + 0.5) / 2)
+    lg = torch.tensor([[0.1, 0.9, 0.5], [0.8, 0.1, 0.3]])
+    assert MX.topk_accuracy(lg, [2, 2], 1) == 0.0 and MX.topk_accuracy(lg, [2, 2], 2) == 1.0
+
+
+def test_speculation_plan_and_verifier():
+    p = SX.SpeculationPlan.compute(0.8, 0.1)
+    assert p.optimal_k == round(math.sqrt(2 / 0.2)) and p.speedup == pytest.approx((1 + 3 * 0.8) / (1 + 3 * 0.1))
+    assert SX.Theorem13Result.compute(0.05, 0.1).speedup == 1.0
+    d = torch.tensor([[0., 1], [1, 0], [0, 1], [1, 0]])
+    t = torch.tensor([[0., 2], [3, 0], [5, 1], [1, 0]])
+    r = SX.SmallBatchVerifier(8).verify(d, t)
+    assert r.accepted == [True, True, False, False] and r.first_rejection_pos == 2 and r.total_accepted == 2
+    assert SX.SmallBatchVerifier(1).verify(d, t).accepted == [True]
+
+
+def test_kv_checkpoint_rewind_and_pool():
+    alloc = PageAllocator(8)
+    pages = [alloc.alloc() for _ in range(2)]              # 20 tokens -> 2 pages
+    ck = SX.checkpoint_kv(pages, 20)
+    pages += [alloc.alloc(), alloc.alloc()]                # drafting grew the sequence to 50 tokens
+    assert alloc.num_free == 4
+    assert SX.rewind_kv(alloc, pages, ck, 23) == 23        # 3 draft tokens accepted
+    assert len(pages) == 2 and alloc.num_free == 6
+    with pytest.raises(ValueError):
+        SX.rewind_kv(alloc, pages, SX.KVCheckpoint(), 5)
+    pool = SX.InferenceMemoryPool(1000)
+    assert pool.reserve("a", 600) and not pool.reserve("b", 500) and pool.reserve("b", 400)
+    assert pool.utilization() == 1.0 and pool.release("a") == 600 and pool.available() == 600 and pool.owners() == 1 and pool.peak == 1000
+
+
+def test_tiled_attention_matches_dense_and_window():
+    torch.manual_seed(0)
+    H, S, d = 2, 150, 16
+    q, k, v = (torch.randn(H, S, d) for _ in range(3))
+    att = SX.MemoryEfficientAttention(32, 32)
+    s = q @ k.transpose(-1, -2) / math.sqrt(d)
+    causal = torch.tril(torch.ones(S, S, dtype=torch.bool))
+    ref = torch.softmax(s.masked_fill(~causal, -float("inf")), -1) @ v
+    assert torch.allclose(att.forward(q, k, v), ref, atol=1e-5)
+    ref_full = torch.softmax(s, -1) @ v
+    assert torch.allclose(att.forward(q, k, v, causal=False), ref_full, atol=1e-5)
+    W, G = 40, 4
+    i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    band = causal & ((j > i - W) | (j < G))
+    ref_w = torch.softmax(s.masked_fill(~band, -float("inf")), -1) @ v
+    assert torch.allclose(att.forward_block_sparse(q, k, v, W, G), ref_w, atol=1e-5)
+    mem = att.memory_bytes(1 << 16, 8, 64)
+    assert mem["tiled"] < mem["naive"] / 100
+    with pytest.raises(ValueError):
+        SX.MemoryEfficientAttention(max_context_tokens=100).forward(q, k, v)
+    mg = SX.MultiGPUManager()
+    assert mg.device_count() == len(mg.detect()) and mg.allocate_on(0, (2, 3)).shape == (2, 3)

@@ -115,3 +115,35 @@ def test_adamw_and_clip():
         F.adamw_(P, G2, M, V, PL, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, c1)
         assert G2.abs().max().item() == 0
     close(P, p, 1e-4); close(M, m, 1e-4); close(V, v, 1e-4); close(PL, plp, 1e-2)
+
+
+@pytest.mark.gpu
+def test_bounds_check_build_reports_first_bad_index():
+    """The -DTFB_BOUNDS_CHECK library records an out-of-range token id and label (the accesses themselves stay clamped /
+    skipped, so nothing faults); the release library ignores them silently.  Runs in a child process because the library
+    variant is chosen at load time."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from transformers_fusion_b200.ops import _lib, functional as F
+assert _lib.lib_path().name == "libtfb_kernels_check.so"
+W = torch.randn(32, 64, device="cuda").bfloat16()
+ids = torch.tensor([1, 2, 99, 3], device="cuda")
+out = F.embedding_fwd(ids, W, None, 0)
+logits = torch.randn(4, 32, device="cuda").bfloat16()
+labels = torch.tensor([1, -100, 77, 5], device="cuda")
+F.cross_entropy_fwd_bwd(logits, labels, want_grad=False)
+torch.cuda.synchronize()
+rep = _lib.bounds_report()
+assert rep["elementwise"][:4] == (1, 1, 99, 32), rep
+assert rep["loss_optim"][0] == 1 and rep["loss_optim"][1:] == (3, 77, 32), rep
+assert _lib.bounds_report()["elementwise"][0] == 0
+assert torch.equal(out[2], W[0])
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, cwd=root,
+                       env=dict(os.environ, TFB_BOUNDS_CHECK="1"))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]

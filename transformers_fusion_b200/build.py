@@ -59,24 +59,26 @@ def _compile_many(jobs, workers):
                 print(out)
 
 
-def build_kernels(force=False, verbose=False) -> Path:
-    """All .cu files under csrc/kernels and csrc/comm -> lib/libtfb_kernels.so."""
+def build_kernels(force=False, verbose=False, bounds_check=False) -> Path:
+    """All .cu files under csrc/kernels and csrc/comm -> lib/libtfb_kernels.so.  ``bounds_check`` builds the variant
+    with -DTFB_BOUNDS_CHECK into lib/libtfb_kernels_check.so (loaded when the environment has TFB_BOUNDS_CHECK=1)."""
     nvcc = _nvcc()
     OBJ.mkdir(parents=True, exist_ok=True)
+    suffix, extra = ("_check", ["-DTFB_BOUNDS_CHECK"]) if bounds_check else ("", [])
     srcs = sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
     hdrs = list((CSRC / "kernels").glob("*.cuh")) + list((CSRC / "kernels").glob("*.h")) + \
         list((CSRC / "comm").glob("*.cuh")) + list((CSRC / "comm").glob("*.h"))
     jobs, objs = [], []
     for s in srcs:
-        o = OBJ / (s.stem + ".o")
+        o = OBJ / (s.stem + suffix + ".o")
         objs.append(o)
         if force or _newer([s] + hdrs, o):
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", str(CSRC / "kernels"), "-I", str(CSRC / "comm"), "-c", str(s), "-o", str(o)]
+            cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", str(CSRC / "kernels"), "-I", str(CSRC / "comm"), "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd += ["-Xptxas", "-v"]
             jobs.append(cmd)
     _compile_many(jobs, workers=min(8, os.cpu_count() or 4))
-    so = LIB / "libtfb_kernels.so"
+    so = LIB / f"libtfb_kernels{suffix}.so"
     if force or jobs or not so.exists():
         _run([nvcc, "-shared", "-o", str(so)] + [str(o) for o in objs] + ["-cudart", "static"])
     return so
@@ -143,9 +145,11 @@ def build_tools(force=False):
     return out
 
 
-def build_all(force=False, verbose=False):
+def build_all(force=False, verbose=False, bounds_check=True):
     LIB.mkdir(exist_ok=True)
     built = [build_kernels(force, verbose)]
+    if bounds_check:
+        built.append(build_kernels(force, False, bounds_check=True))
     for name, sub in (("tfb_codec", "codec"), ("tfb_tokenizer", "tokenizer"), ("tfb_serve", "serve")):
         so = build_host_lib(name, sub, force)
         if so:
@@ -161,8 +165,9 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="pass -Xptxas -v (set TFB_BUILD_VERBOSE=1 to print)")
+    ap.add_argument("--no-bounds-check", action="store_true", help="skip the -DTFB_BOUNDS_CHECK variant of the kernel library")
     a = ap.parse_args(argv)
-    for p in build_all(a.force, a.verbose):
+    for p in build_all(a.force, a.verbose, not a.no_bounds_check):
         print("built", p)
 
 

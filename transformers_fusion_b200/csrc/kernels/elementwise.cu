@@ -9,6 +9,8 @@
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
+TFB_BOUNDS_DEFINE(elementwise)
+
 namespace tfb {
 
 // ------------------------------------------------------------------------------------------------
@@ -173,6 +175,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __
        i += (long long)gridDim.x * blockDim.x) {
     const int t = int(i / vec), c = int(i % vec) * 8;
     long long id = ids[t];
+    TFB_BOUNDS(id >= 0 && id < V, 1, id, V);
     if (id < 0 || id >= V) id = 0;
     uint4 u = *reinterpret_cast<const uint4*>(W + id * H + c);
     if (P) {
@@ -197,6 +200,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __
        i += (long long)gridDim.x * blockDim.x) {
     const int t = int(i / vec), c = int(i % vec) * 4;
     const long long id = ids[t];
+    TFB_BOUNDS(id >= 0 && id < V, 2, id, V);
     if (id < 0 || id >= V) continue;
     const uint2 u = *reinterpret_cast<const uint2*>(dout + (long long)t * H + c);
     const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);

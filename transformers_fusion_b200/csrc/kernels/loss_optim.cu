@@ -10,6 +10,8 @@
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
+TFB_BOUNDS_DEFINE(loss_optim)
+
 namespace tfb {
 
 __device__ __forceinline__ float block_reduce_sum(float v, float* sh) {
@@ -50,6 +52,7 @@ __global__ void __launch_bounds__(512, 2) cross_entropy_regs_kernel(const __nv_b
   const uint4* row = reinterpret_cast<const uint4*>(logits + t * ld);
   const long long label = labels[t];
   const bool ignored = (label == ignore_index);
+  if (threadIdx.x == 0) TFB_BOUNDS(ignored || (label >= 0 && label < V), 3, label, V);
   const int V8 = V >> 3;
   uint4 u[NV];
 #pragma unroll
@@ -135,6 +138,7 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
   const __nv_bfloat16* row = logits + t * ld;
   const long long label = labels[t];
   const bool ignored = (label == ignore_index);
+  if (threadIdx.x == 0) TFB_BOUNDS(ignored || (label >= 0 && label < V), 3, label, V);
   // read before any thread starts overwriting the row with gradients (dlogits may alias logits)
   const float zy = (!ignored && label >= 0 && label < V) ? __bfloat162float(row[label]) : 0.f;
   const bool vec = ((ld & 7) == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);

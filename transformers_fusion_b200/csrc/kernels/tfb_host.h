@@ -29,3 +29,34 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0
 int sm_count();
 
 }  // namespace tfb
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Bounds-check build (-DTFB_BOUNDS_CHECK, `python -m transformers_fusion_b200.build --bounds-check`, loaded when the
+// environment has TFB_BOUNDS_CHECK=1).  Index-driven accesses (token ids, labels, page slots, block tables, expert ids)
+// are always kept inside their tables; this build additionally records the first offender of each translation unit:
+// {count, site, index, limit}, read and cleared by tfb_bounds_report_<unit>().  A release build compiles the checks out.
+// Reference counterpart: the QUANT_CHECK / bounds-checked debug build of the C++ kernels (include/quant/tensor.h).
+#ifdef TFB_BOUNDS_CHECK
+#define TFB_BOUNDS_DEFINE(unit)                                                                                    \
+  static __device__ unsigned long long g_tfb_bounds[4];                                                            \
+  TFB_API int tfb_bounds_report_##unit(unsigned long long* out4, int reset) {                                      \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, g_tfb_bounds, sizeof(unsigned long long) * 4);                      \
+    if (e == cudaSuccess && reset) {                                                                               \
+      const unsigned long long z[4] = {0, 0, 0, 0};                                                                \
+      e = cudaMemcpyToSymbol(g_tfb_bounds, z, sizeof(z));                                                          \
+    }                                                                                                              \
+    return int(e);                                                                                                 \
+  }
+#define TFB_BOUNDS(ok, site, idx, lim)                                                                             \
+  do {                                                                                                             \
+    if (!(ok) && atomicAdd(&g_tfb_bounds[0], 1ull) == 0ull) {                                                      \
+      g_tfb_bounds[1] = (unsigned long long)(site);                                                                \
+      g_tfb_bounds[2] = (unsigned long long)(long long)(idx);                                                      \
+      g_tfb_bounds[3] = (unsigned long long)(long long)(lim);                                                      \
+    }                                                                                                              \
+  } while (0)
+#else
+#define TFB_BOUNDS_DEFINE(unit)
+#define TFB_BOUNDS(ok, site, idx, lim) do {} while (0)
+#endif
+

@@ -51,8 +51,28 @@ class KernelError(RuntimeError):
     pass
 
 
+def bounds_check_build() -> bool:
+    return os.environ.get("TFB_BOUNDS_CHECK", "") not in ("", "0")
+
+
 def lib_path() -> Path:
-    return _LIB_DIR / "libtfb_kernels.so"
+    return _LIB_DIR / ("libtfb_kernels_check.so" if bounds_check_build() else "libtfb_kernels.so")
+
+
+def bounds_report(reset: bool = True) -> dict:
+    """Bounds-check build only: {unit: (count, site, index, limit)} of the first out-of-range index each unit saw
+    (sites: 1 embedding id, 2 embedding-gradient id, 3 cross-entropy label)."""
+    out = {}
+    if not bounds_check_build():
+        return out
+    for unit in ("elementwise", "loss_optim"):
+        fn = getattr(lib(), f"tfb_bounds_report_{unit}")
+        fn.argtypes, fn.restype = [c_p, c_i], c_i
+        buf = (C.c_ulonglong * 4)()
+        check(fn(C.addressof(buf), int(reset)), f"bounds_report_{unit}")
+        idx = buf[2] - (1 << 64) if buf[2] >= (1 << 63) else buf[2]
+        out[unit] = (int(buf[0]), int(buf[1]), int(idx), int(buf[3]))
+    return out
 
 
 def available() -> bool:
@@ -69,7 +89,7 @@ def lib():
         if os.environ.get("TFB_NO_AUTOBUILD"):
             raise KernelError(f"{p} is missing; run `python -m transformers_fusion_b200.build`")
         from .. import build as _build
-        _build.build_kernels()
+        _build.build_kernels(bounds_check=bounds_check_build())
     _lib = C.CDLL(str(p))
     for name, sig in _SIGS.items():
         try:

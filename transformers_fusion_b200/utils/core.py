@@ -1,0 +1,260 @@
+"""Core value types and thread-safety helpers.
+
+Types: DType (element kinds of the codec and the kernels), Shape (rank <= 8), Status (ok / message), Config (process-wide
+defaults), quant_check.  Thread-safety: single-producer single-consumer ring, readers-writer mutex, atomic float
+accumulator, spin lock, named counters.  Python threads share the GIL, so these exist for API parity and for code that
+hands work between the server's worker threads; the device side has its own (mbarrier, flag) primitives.
+
+Reference counterparts: include/quant/types.h:289-314 (DType, Shape, Status, Config, QUANT_CHECK),
+include/quant/thread_safety.h:28-255 (SPSCQueue, SharedMutex, AtomicFloat, SpinLock, ThreadSafeCounter)."""
+from __future__ import annotations
+
+import enum
+import threading
+from dataclasses import dataclass
+from typing import Generic, List, Optional, Tuple, TypeVar
+
+T = TypeVar("T")
+
+
+class DType(enum.IntEnum):
+    I64 = 0
+    I32 = 1
+    U8 = 2
+    U4 = 3
+    U16 = 4
+    F16 = 5
+    F32 = 6
+    BF16 = 7       # additions of this framework: the compute type and the two 8-bit float storage types
+    E4M3 = 8
+    E5M2 = 9
+
+    @property
+    def bits(self) -> int:
+        return {0: 64, 1: 32, 2: 8, 3: 4, 4: 16, 5: 16, 6: 32, 7: 16, 8: 8, 9: 8}[int(self)]
+
+    def torch(self):
+        import torch
+        return {0: torch.int64, 1: torch.int32, 2: torch.uint8, 3: torch.uint8, 4: torch.int16, 5: torch.float16, 6: torch.float32,
+                7: torch.bfloat16, 8: torch.float8_e4m3fn, 9: torch.float8_e5m2}[int(self)]
+
+
+class Shape(tuple):
+    """Immutable dimension list of rank <= 8."""
+    MAX_RANK = 8
+
+    def __new__(cls, *dims):
+        if len(dims) == 1 and isinstance(dims[0], (tuple, list)):
+            dims = tuple(dims[0])
+        if len(dims) > cls.MAX_RANK:
+            raise ValueError(f"rank {len(dims)} exceeds {cls.MAX_RANK}")
+        if any(int(d) < 0 for d in dims):
+            raise ValueError("negative dimension")
+        return super().__new__(cls, (int(d) for d in dims))
+
+    @property
+    def rank(self) -> int: return len(self)
+
+    def numel(self) -> int:
+        n = 1
+        for d in self:
+            n *= d
+        return n
+
+    def strides(self) -> Tuple[int, ...]:
+        out, s = [], 1
+        for d in reversed(self):
+            out.append(s)
+            s *= d
+        return tuple(reversed(out))
+
+
+@dataclass(frozen=True)
+class Status:
+    ok: bool = True
+    message: str = ""
+
+    @staticmethod
+    def OK() -> "Status": return Status(True, "")
+
+    @staticmethod
+    def error(msg: str) -> "Status": return Status(False, msg)
+
+    def __bool__(self) -> bool: return self.ok
+
+
+@dataclass
+class Config:
+    num_threads: int = 0          # 0 = all cores
+    seed: int = 42
+    pool_bytes: int = 64 << 20
+
+
+def quant_check(cond, msg: str = "check failed"):
+    if not cond:
+        raise RuntimeError(f"QUANT_CHECK: {msg}")
+
+
+# ------------------------------------------------------------------------------------------------ thread safety
+class SPSCQueue(Generic[T]):
+    """Bounded ring for one producer thread and one consumer thread.  ``push`` / ``pop`` never block: they report
+    full / empty.  Head and tail are only written by their own side."""
+
+    def __init__(self, capacity: int):
+        if capacity < 1:
+            raise ValueError("capacity must be positive")
+        self._buf: List[Optional[T]] = [None] * (capacity + 1)
+        self._head = 0          # next slot to pop   (consumer)
+        self._tail = 0          # next slot to push  (producer)
+
+    def push(self, item: T) -> bool:
+        nxt = (self._tail + 1) % len(self._buf)
+        if nxt == self._head:
+            return False
+        self._buf[self._tail] = item
+        self._tail = nxt
+        return True
+
+    def pop(self) -> Optional[T]:
+        if self._head == self._tail:
+            return None
+        item, self._buf[self._head] = self._buf[self._head], None
+        self._head = (self._head + 1) % len(self._buf)
+        return item
+
+    def __len__(self) -> int:
+        return (self._tail - self._head) % len(self._buf)
+
+    @property
+    def capacity(self) -> int: return len(self._buf) - 1
+    def empty(self) -> bool: return self._head == self._tail
+
+
+class SharedMutex:
+    """Readers-writer lock: any number of shared holders or one exclusive holder; waiting writers block new readers."""
+
+    def __init__(self):
+        self._cv = threading.Condition()
+        self._readers, self._writer, self._waiting_writers = 0, False, 0
+
+    def lock_shared(self):
+        with self._cv:
+            while self._writer or self._waiting_writers:
+                self._cv.wait()
+            self._readers += 1
+
+    def unlock_shared(self):
+        with self._cv:
+            self._readers -= 1
+            if self._readers == 0:
+                self._cv.notify_all()
+
+    def lock(self):
+        with self._cv:
+            self._waiting_writers += 1
+            while self._writer or self._readers:
+                self._cv.wait()
+            self._waiting_writers -= 1
+            self._writer = True
+
+    def unlock(self):
+        with self._cv:
+            self._writer = False
+            self._cv.notify_all()
+
+    def shared(self):
+        return _Guard(self.lock_shared, self.unlock_shared)
+
+    def unique(self):
+        return _Guard(self.lock, self.unlock)
+
+
+class _Guard:
+    def __init__(self, acquire, release):
+        self._a, self._r = acquire, release
+
+    def __enter__(self):
+        self._a()
+        return self
+
+    def __exit__(self, *exc):
+        self._r()
+        return False
+
+
+class AtomicFloat:
+    def __init__(self, value: float = 0.0):
+        self._v, self._l = float(value), threading.Lock()
+
+    def load(self) -> float:
+        with self._l:
+            return self._v
+
+    def store(self, v: float):
+        with self._l:
+            self._v = float(v)
+
+    def fetch_add(self, d: float) -> float:
+        with self._l:
+            old = self._v
+            self._v += d
+            return old
+
+    def fetch_max(self, v: float) -> float:
+        with self._l:
+            old = self._v
+            self._v = max(self._v, v)
+            return old
+
+    def compare_exchange(self, expected: float, desired: float) -> bool:
+        with self._l:
+            if self._v == expected:
+                self._v = float(desired)
+                return True
+            return False
+
+
+class SpinLock:
+    """Non-blocking acquire in a loop (short critical sections only)."""
+
+    def __init__(self):
+        self._l = threading.Lock()
+
+    def lock(self):
+        while not self._l.acquire(blocking=False):
+            pass
+
+    def try_lock(self) -> bool: return self._l.acquire(blocking=False)
+    def unlock(self): self._l.release()
+    def __enter__(self):
+        self.lock()
+        return self
+
+    def __exit__(self, *exc):
+        self.unlock()
+        return False
+
+
+class ThreadSafeCounter:
+    def __init__(self):
+        self._c, self._l = {}, threading.Lock()
+
+    def increment(self, name: str = "", by: int = 1) -> int:
+        with self._l:
+            self._c[name] = self._c.get(name, 0) + by
+            return self._c[name]
+
+    def get(self, name: str = "") -> int:
+        with self._l:
+            return self._c.get(name, 0)
+
+    def reset(self, name: Optional[str] = None):
+        with self._l:
+            if name is None:
+                self._c.clear()
+            else:
+                self._c.pop(name, None)
+
+    def snapshot(self) -> dict:
+        with self._l:
+            return dict(self._c)

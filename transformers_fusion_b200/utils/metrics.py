@@ -21,6 +21,32 @@ def accuracy(pred: Sequence[int], target: Sequence[int]) -> float:
     return sum(int(a == b) for a, b in zip(pred, target)) / n if n else 0.0
 
 
+def topk_accuracy(logits: torch.Tensor, target: Sequence[int], k: int = 1) -> float:
+    """Fraction of rows whose target is among the k largest logits."""
+    t = torch.as_tensor(target, device=logits.device).long()
+    if t.numel() == 0:
+        return 0.0
+    top = logits.float().topk(min(k, logits.shape[-1]), -1).indices
+    return float((top == t[:, None]).any(-1).float().mean())
+
+
+def average_precision(scores: Sequence[float], relevant: Sequence[int]) -> float:
+    """Area under the precision-recall steps of one ranked list (ties keep input order)."""
+    order = sorted(range(len(scores)), key=lambda i: -scores[i])
+    hits, ap = 0, 0.0
+    for rank, i in enumerate(order, 1):
+        if relevant[i]:
+            hits += 1
+            ap += hits / rank
+    return ap / hits if hits else 0.0
+
+
+def mean_average_precision(score_lists: Sequence[Sequence[float]], relevant_lists: Sequence[Sequence[int]]) -> float:
+    """Mean of the per-query (or per-class) average precision; queries without a relevant item are skipped."""
+    aps = [average_precision(s, r) for s, r in zip(score_lists, relevant_lists) if any(r)]
+    return sum(aps) / len(aps) if aps else 0.0
+
+
 def perplexity(mean_nll: float) -> float:
     return math.exp(min(mean_nll, 80.0))
 
