@@ -142,7 +142,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
         const int h = hk * G + it / n_i, i = i0 + it % n_i;
-        if (!mbar_wait_sleep(bar_empty + st * 8, ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 32)) break;
+        if (!mbar_wait(bar_empty + st * 8, ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
         const uint32_t fb = bar_full + st * 8;
         mbar_expect_tx(fb, 2 * L::TILE);
         const uint32_t sQ = sbase + L::RING_OFF + st * 2 * L::TILE, sDO = sQ + L::TILE;
@@ -236,8 +236,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       s_lse[r] = nxt;
       mbar_arrive(bar_stat + w * 8);
       if (it + 1 < n_it) nxt = load_stat(it + 1);
-      if (!mbar_wait_sleep_warp(bar_stat + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_FLAG, 20)) { ok = false; break; }
-      if (!mbar_wait_sleep_warp(bar_s + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_stat + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_s + w * 8, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && (i == jb);
 #pragma unroll
@@ -274,7 +274,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       tc_fence_before();
       mbar_arrive(bar_pds + w * 8);
     }
-    if (ok && mbar_wait_sleep_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) {
+    if (ok && mbar_wait_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool valid = key_idx < p.S;
       const long long row = (long long)b * p.S + (valid ? key_idx : 0);
@@ -390,7 +390,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       }
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
-        if (!mbar_wait_sleep(bar_empty + st * 8, ((j >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 32)) break;
+        if (!mbar_wait(bar_empty + st * 8, ((j >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
         const uint32_t fb = bar_full + st * 8;
         mbar_expect_tx(fb, 2 * L::TILE);
         const uint32_t sK = sbase + L::RING_OFF + st * 2 * L::TILE, sV = sK + L::TILE;
@@ -466,7 +466,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const float dl = q_idx < p.S ? p.delta[so] : 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait_sleep_warp(bar_s + w * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_s + w * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int k0 = j * 128 + w * 64;
       const bool need_mask = (p.causal && j == qb) || (k0 + 64 > p.S);
@@ -477,7 +477,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tc_fence_before();
       mbar_arrive(bar_ds + w * 8);
     }
-    if (ok && mbar_wait_sleep_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) {
+    if (ok && mbar_wait_warp(bar_acc, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       // each half writes D / 2 columns of the row
       __nv_bfloat16* dqp = p.dq + ((long long)b * p.S + q_idx) * p.lddq + p.dq_col0 + h * D + w * (D / 2);

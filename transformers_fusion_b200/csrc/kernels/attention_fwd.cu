@@ -191,7 +191,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           tma_load_3d(sQ + t * L::TILE + i * BOX_BYTES, &tq, bar_q, p.q_col0 + h * D + i * 64, (pair * 2 + t) * ATT_BM, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % ST;
-        if (!mbar_wait_sleep(bar_kv_empty + st * 8, ((j / ST) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 32)) break;
+        if (!mbar_wait(bar_kv_empty + st * 8, ((j / ST) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
         const uint32_t fb = bar_kv_full + st * 8;
         mbar_expect_tx(fb, 2 * L::TILE);
         const uint32_t sK = sbase + L::KV_OFF + st * 2 * L::TILE, sV = sK + L::TILE;
@@ -275,7 +275,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_mine; ++j) {
-      if (!mbar_wait_sleep_warp(bar_s_full + t * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) {
+      if (!mbar_wait_warp(bar_s_full + t * 8, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
         ok = false;
         break;
       }
@@ -306,7 +306,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       alpha_prev = alpha;
     }
     if (ok && n_mine > 0) {
-      if (mbar_wait_sleep_warp(bar_o_full + t * 8, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, 20)) {
+      if (mbar_wait_warp(bar_o_full + t * 8, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
