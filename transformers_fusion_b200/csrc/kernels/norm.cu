@@ -291,7 +291,9 @@ static int launch_bwd(const void* dy, const void* h, const void* w, const float*
   auto DX = static_cast<__nv_bfloat16*>(dx);
   const size_t sm = size_t(H) * 4;
   if (H <= 1024) {
-    const int blocks = min((rows + 7) / 8, sm_count() * 2);
+    // 64 registers per thread: four resident blocks per SM; fewer leaves the loads of a row unhidden (94 -> 70 us at
+    // 65536 x 512), more only adds atomics on dw
+    const int blocks = min((rows + 7) / 8, sm_count() * 4);
     if (H <= 512) norm_bwd_kernel<2, LN, true><<<blocks, 256, sm, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
     else norm_bwd_kernel<4, LN, true><<<blocks, 256, sm, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
   } else {
