@@ -498,27 +498,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   }
 }
 
-// delta[b,h,s] = sum_d dO[t, h*D + d] * O[t, h*D + d]; one warp per (token, head)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
-                                  const __nv_bfloat16* __restrict__ dout, long long lddo, float* __restrict__ delta,
-                                  int B, int S, int Hq, int D) {
-  const int lane = threadIdx.x & 31;
-  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const long long total = (long long)B * S * Hq;
-  if (w >= total) return;
-  const int h = int(w % Hq);
-  const long long t = w / Hq;
+// delta[b,h,s] = sum_d dO[t, h*D + d] * O[t, h*D + d].  One thread per 8 consecutive elements of a token row (16-byte
+// loads, consecutive lanes on consecutive addresses); the D / 8 lanes of a head reduce with shuffles.
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
+                                                         const __nv_bfloat16* __restrict__ dout, long long lddo,
+                                                         float* __restrict__ delta, int B, int S, int Hq, int D) {
+  const int per_row = Hq * D / 8;                       // threads per token row
+  const long long total = (long long)B * S * per_row;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const bool live = i < total;
+  const long long t = live ? i / per_row : 0;
+  const int c = live ? int(i - t * per_row) * 8 : 0;    // first column of this thread
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(o + t * ldo + h * D + d));
-    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + t * lddo + h * D + d));
-    acc += a.x * g.x + a.y * g.y;
-  }
+  if (live) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + t * ldo + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(dout + t * lddo + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
-    const long long bb = t / S, s = t % S;
-    delta[(bb * Hq + h) * S + s] = acc;
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(aw[j]), y = unpack_bf16(gw[j]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+  const int group = D / 8;                              // 8 or 16 lanes per head, aligned inside the warp
+  for (int off = group >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (live && (threadIdx.x & (group - 1)) == 0) {
+    const int h = c / D;
+    const long long bb = t / S, s_ = t % S;
+    delta[(bb * Hq + h) * S + s_] = acc;
   }
 }
 
@@ -559,10 +566,11 @@ TFB_API int tfb_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
   if ((lddq | lddk | lddv) & 7) return TFB_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15)
     return TFB_ERR_ARG;
+  if (((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout)) & 15) || (ldo & 7) || (lddo & 7)) return TFB_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   {
-    const long long warps = (long long)B * S * Hq;
-    const int blocks = int((warps * 32 + 255) / 256);
+    const long long threads = (long long)B * S * Hq * D / 8;
+    const int blocks = int((threads + 255) / 256);
     attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), ldo,
                                               static_cast<const __nv_bfloat16*>(dout), lddo, delta, B, S, Hq, D);
   }

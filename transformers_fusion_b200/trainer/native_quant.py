@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Optional
+from typing import List, Optional
 
 import torch
 
@@ -304,3 +304,117 @@ class NativeQUANTTrainer:
             self._push()
         else:
             self.flat.params.copy_(self.master.to(self.flat.params.dtype))
+
+
+# ----------------------------------------------------------------------------------------------- MoE in native low-bit form
+@dataclass
+class NativeMoEConfig:
+    hidden_size: int = 512
+    num_heads: int = 8
+    ffn_hidden: int = 1024
+    num_layers: int = 4
+    num_experts: int = 8
+    top_k: int = 2
+    load_balance_coef: float = 0.01
+    z_loss_coef: float = 0.001
+    block_size: int = 128
+    frac_quant8: float = 0.01
+    frac_quant: float = 0.95
+    vocab_size: int = 256
+    max_seq_len: int = 128
+
+
+@dataclass
+class NativeMoEMetrics:
+    loss: float = 0.0
+    lb_loss: float = 0.0
+    z_loss: float = 0.0
+    grad_norm: float = 0.0
+    frozen_pct: float = 0.0
+    quant8: int = 0
+    quant: int = 0
+    quant1: int = 0
+    total_params: int = 0
+    active_params: int = 0
+
+
+class NativeQUANTMoEModel:
+    """MoE language model whose large tensors (embedding, LM head, every expert's gate/up and down matrices) live in
+    NativeQWeightStore form and are updated there; attention, norms and routers stay in floating point with plain SGD.
+    Before each step the stores are expanded into the model's parameters, after backward they take the gradients.
+
+    Reference counterpart: NativeQUANTMoEModel (include/quant/native_quant_moe.h:11-76, src/model/native_quant_moe.cpp)."""
+
+    def __init__(self, cfg: Optional[NativeMoEConfig] = None, device="cpu", seed: int = 0):
+        from ..models.config import MoEConfig
+        from ..models.moe import MoEModel
+        self.cfg = cfg = cfg or NativeMoEConfig()
+        mc = MoEConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_layers=cfg.num_layers, num_heads=cfg.num_heads,
+                       ffn_hidden_size=cfg.ffn_hidden, max_seq_len=cfg.max_seq_len, num_experts=cfg.num_experts, top_k=cfg.top_k,
+                       load_balance_weight=cfg.load_balance_coef, router_z_weight=cfg.z_loss_coef, init_std=0.05)
+        dev = torch.device(device)
+        self.model = MoEModel(mc, device=dev, dtype=torch.float32 if dev.type == "cpu" else torch.bfloat16, seed=seed)
+        self.model.flatten()
+        self.stores: List[tuple] = []           # (parameter, store)
+        self.total_params_ = sum(p.numel() for p in self.model.parameters())
+
+    def _stored_tensors(self):
+        m = self.model
+        out = [m.tok_embeddings]
+        if m.lm_head is not m.tok_embeddings:
+            out.append(m.lm_head)
+        for blk in m.layers:
+            out += [blk.gate_up, blk.down]
+        return out
+
+    def init_from_fp32(self):
+        c = self.cfg
+        self.stores = []
+        for p in self._stored_tensors():
+            st = NativeQWeightStore(p.numel(), c.block_size, p.device)
+            st.initialize(p.data.float().reshape(-1), None, c.frac_quant8, c.frac_quant)
+            self.stores.append((p, st))
+        self.push_weights()
+
+    def push_weights(self):
+        for p, st in self.stores:
+            p.data.copy_(st.dequantize().view(p.shape).to(p.dtype))
+
+    def total_params(self) -> int: return self.total_params_
+
+    def forward(self, ids):
+        return self.model(ids)
+
+    def step(self, ids, labels, lr_s: float, lr_w: float) -> NativeMoEMetrics:
+        if not self.stores:
+            self.init_from_fp32()
+        m = self.model
+        m.flat.zero_grad()
+        loss = float(m.forward_backward(ids, labels))
+        met = NativeMoEMetrics(loss=loss, total_params=self.total_params_)
+        met.lb_loss = float(m.last_aux) if m.last_aux is not None else 0.0
+        met.grad_norm = float(m.flat.grads.norm())
+        stored = {id(p) for p, _ in self.stores}
+        frozen = []
+        for p, st in self.stores:
+            frozen.append(st.apply_quant_update(p.main_grad.reshape(-1).float(), lr_s, lr_w))
+            cnt = st.counts()
+            met.quant8 += cnt[Q8]
+            met.quant1 += cnt[Q1]
+            met.quant += cnt[Q4]
+        with torch.no_grad():
+            for p in m.parameters():
+                if id(p) not in stored and getattr(p, "main_grad", None) is not None:
+                    p.data.add_(p.main_grad.to(p.dtype), alpha=-lr_w)
+        self.push_weights()
+        met.frozen_pct = 100.0 * sum(frozen) / max(1, len(frozen))
+        per_expert = (m.layers[0].gate_up.numel() + m.layers[0].down.numel()) // self.cfg.num_experts
+        met.active_params = self.total_params_ - self.cfg.num_layers * (self.cfg.num_experts - self.cfg.top_k) * per_expert
+        return met
+
+    def memory_report(self) -> dict:
+        bits = sum(st.bits_per_weight() * st.size() for _, st in self.stores)
+        n = sum(st.size() for _, st in self.stores)
+        rest = self.total_params_ - n
+        return {"stored_params": n, "stored_bits_per_weight": bits / max(1, n), "float_params": rest,
+                "bytes": bits / 8 + rest * 4, "fp32_bytes": self.total_params_ * 4}
