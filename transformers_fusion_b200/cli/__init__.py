@@ -1,7 +1,7 @@
 """Command-line tools.  ``python -m transformers_fusion_b200.cli <tool> [args]`` or the launchers under
 ``bin/`` (one per tool, same names as the reference binaries: quant_train, quant_finetune, quant_quantize,
 quant_convert, quant_infer, quant_serve, quant_server, quant_evaluate, quant_info, quant_bench,
-quant_format_list, gle_report, train_64m, bench_speed)."""
+quant_format_list, gle_report, train_64m, bench_speed, probe_mi_extraction, generate_comparison_visuals)."""
 import importlib
 import sys
 
@@ -9,7 +9,8 @@ TOOLS = {
     "quant_train": "train", "quant_finetune": "finetune", "quant_quantize": "quantize", "quant_convert": "convert",
     "quant_infer": "infer", "quant_serve": "serve", "quant_server": "serve", "quant_evaluate": "evaluate",
     "quant_info": "info", "quant_bench": "bench", "quant_format_list": "format_list", "gle_report": "gle_report",
-    "train_64m": "train_64m", "bench_speed": "train_64m",
+    "train_64m": "train_64m", "bench_speed": "train_64m", "probe_mi_extraction": "probe_mi_extraction",
+    "generate_comparison_visuals": "generate_comparison_visuals",
 }
 
 
