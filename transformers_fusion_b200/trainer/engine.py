@@ -27,6 +27,23 @@ import torch.distributed as dist
 from .fused_optim import FlatAdamW
 
 
+class PendingLoss:
+    """Loss of an enqueued step: a pinned host slot plus the event recorded after its device-to-host copy.  The slot is
+    reused four steps later, so read the value before enqueuing the fourth step after this one."""
+
+    def __init__(self, slot, event, value):
+        self._slot, self._event, self._value = slot, event, value
+
+    def ready(self) -> bool:
+        return self._event is None or self._event.query()
+
+    def value(self) -> float:
+        if self._value is None:
+            self._event.synchronize()
+            self._value = float(self._slot[0])
+        return self._value
+
+
 class TrainEngine:
     def __init__(self, model, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0,
                  zero_stage=2, comm="fused", group=None, cuda_graph=False, grad_accum_steps=1, symm=None):
@@ -134,9 +151,25 @@ class TrainEngine:
         return self._static_loss
 
     def train_step(self, ids_cpu, labels_cpu, lr=None) -> float:
-        """End-to-end step: pinned host batch -> device -> step -> loss on the host."""
+        """End-to-end step: pinned host batch -> device -> step -> loss on the host (waits for the step)."""
+        return self.train_step_async(ids_cpu, labels_cpu, lr).value()
+
+    def train_step_async(self, ids_cpu, labels_cpu, lr=None) -> "PendingLoss":
+        """End-to-end step without stalling the host: the batch is copied from (pinned) host memory, the step is enqueued
+        and the loss is copied back into a pinned slot behind an event.  ``value()`` on the returned handle waits for that
+        event only, so a loop that reads the loss of step i after enqueuing step i + 1 keeps the device busy while still
+        reading every step's loss."""
         dev = self.flat.params.device
         ids = ids_cpu.to(dev, non_blocking=True)
         labels = labels_cpu.to(dev, non_blocking=True)
         loss = self.step(ids, labels, lr)
-        return float(loss.item())
+        if not loss.is_cuda:
+            return PendingLoss(None, None, float(loss))
+        if getattr(self, "_loss_ring", None) is None:
+            self._loss_ring = [(torch.empty(1, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+            self._loss_slot = 0
+        slot, ev = self._loss_ring[self._loss_slot]
+        self._loss_slot = (self._loss_slot + 1) % len(self._loss_ring)
+        slot.copy_(loss.detach().reshape(1).float(), non_blocking=True)
+        ev.record()
+        return PendingLoss(slot, ev, None)
