@@ -146,11 +146,62 @@ def time_kernel(fn, iters=20, warmup=5, flush=True):
     return out
 
 
+def serve_bench(a):
+    """Continuous-batching engine on a random-init preset: B requests of ``prompt_len`` random tokens, ``gen`` new tokens
+    each, greedy.  Reports output tokens/s over the whole run, the median time to first token, and the mean decode step."""
+    import statistics
+
+    import torch
+
+    from ..inference.engine import EngineConfig, InferenceEngine
+    from ..inference.sampler import SamplerConfig
+    from ..models.config import preset
+    from ..models.dense import DenseModel
+    dev = torch.device("cuda", 0)
+    cfg = preset(a.preset)
+    model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
+    g = torch.Generator().manual_seed(0)
+    for B in [int(x) for x in a.batch.split(",")]:
+        pages = (a.prompt_len + a.gen + 31) // 16 * B + 64
+        eng = InferenceEngine(model, None, EngineConfig(max_batch=B, num_pages=pages, kv_mode=a.kv, weight_format=a.weights,
+                                                        cuda_graph=not a.no_graph, enable_prefix_cache=False,
+                                                        max_seq_len=min(cfg.max_seq_len, a.prompt_len + a.gen + 16)))
+        greedy = SamplerConfig(temperature=0.0, top_k=0, top_p=1.0)
+        for rep in range(2):                       # the first pass builds graphs and workspaces
+            prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(B)]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            reqs = [eng.add_request(p, max_tokens=a.gen, sampling=greedy) for p in prompts]
+            d0 = eng.stats.decode_ms
+            steps = 0
+            while eng.has_pending():
+                eng.step()
+                steps += 1
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        out_tokens = sum(len(r.out) for r in reqs)
+        rec = {"bench": "serve", "preset": a.preset, "batch": B, "prompt_len": a.prompt_len, "gen": a.gen, "weights": a.weights or "bf16",
+               "kv": a.kv, "cuda_graph": not a.no_graph, "out_tok_s": round(out_tokens / dt, 1),
+               "ttft_ms_p50": round(statistics.median((r.t_first - r.t_submit) * 1e3 for r in reqs), 2),
+               "decode_ms_per_step": round((eng.stats.decode_ms - d0) / max(1, steps), 3), "total_ms": round(dt * 1e3, 1)}
+        print(json.dumps(rec), flush=True)
+        del eng
+        torch.cuda.empty_cache()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="quant_bench", description="Usage: quant_bench [--kernel <name> --size N] [--inference --model m.quant --prompt p]")
     ap.add_argument("--kernel", default="")
     add_int(ap, "--size", 1024)
     ap.add_argument("--inference", action="store_true")
+    ap.add_argument("--serve", action="store_true", help="serving throughput of a random-init preset: out tok/s, TTFT, decode ms/step")
+    ap.add_argument("--preset", default="llama-50m")
+    ap.add_argument("--batch", default="1,8,64")
+    ap.add_argument("--prompt-len", type=int, default=128)
+    ap.add_argument("--gen", type=int, default=64)
+    ap.add_argument("--weights", default="", help="packed weight format for --serve: int8 | int4 | mxfp8 | fp4 | ternary")
+    ap.add_argument("--kv", default="bf16", help="KV cache storage for --serve: bf16 | fp8 | q4")
+    ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--model", default="")
     ap.add_argument("--prompt", default="test")
     add_int(ap, "--iters", 20)
@@ -185,6 +236,8 @@ def main(argv=None):
                 if flops:
                     rec["frac_bf16_of_measured"] = round(rec["tflops"] / peaks["bf16_tflops"], 3)
             print(json.dumps(rec) if a.json else "  ".join(f"{k}={v}" for k, v in rec.items()), flush=True)
+    if a.serve:
+        serve_bench(a)
     if a.inference:
         from ..inference.engine import EngineConfig, InferenceEngine
         from ..inference.sampler import SamplerConfig

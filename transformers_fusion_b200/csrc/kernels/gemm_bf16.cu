@@ -19,6 +19,7 @@
 // (src/backend/gpu_compute_cuda.cpp:68 gemm_kernel; src/kernel/kernel_gemm.cpp:26 scalar_gemm_bt).
 #include <string.h>
 
+#include <mutex>
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
@@ -630,6 +631,61 @@ struct TfbGemmTp {
   const void* peer_c;     // mode 2: device array [world] of staging-buffer base pointers
 };
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Small-M path (decode batches): a product with few output tiles cannot fill the machine, and split-K needs an fp32
+// accumulation target.  The partial products go into a per-device fp32 workspace with TMA reduce-add, and a finalize
+// kernel applies bias / activation / residual and writes the requested type.  The workspace is allocated once
+// (256 MB: up to 256 rows x 262144 columns); a shape that needs more takes the single-wave path instead.
+constexpr long long SPLITK_WS_ELEMS = 64ll << 20;
+
+// One workspace per device, allocated at the first small-M product outside a stream capture (an allocation inside a
+// capture would invalidate it: a product that arrives first during capture takes the ordinary single-wave path).
+// Products of one device are expected to be issued from one stream at a time, as the inference engine does; two streams
+// running small-M products concurrently on the same device would share the buffer.
+static float* splitk_workspace(cudaStream_t stream) {
+  static float* ws[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ws[dev]) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    void* q = nullptr;
+    if (cudaMalloc(&q, SPLITK_WS_ELEMS * sizeof(float)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    ws[dev] = static_cast<float*>(q);
+  }
+  return ws[dev];
+}
+
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(const float* __restrict__ ws, long long ldw, void* __restrict__ C, long long ldc,
+                                                              const __nv_bfloat16* __restrict__ bias,
+                                                              const __nv_bfloat16* __restrict__ residual, long long ldr, int M, int N,
+                                                              int act, int out_fp32) {
+  const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;      // 4 consecutive columns
+  if (i >= (long long)M * ldw) return;
+  const int m = int(i / ldw), n = int(i % ldw);
+  if (n >= N) return;
+  const float4 a = *reinterpret_cast<const float4*>(ws + i);
+  float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (n + j < N) {
+      if (bias) v[j] += __bfloat162float(bias[n + j]);
+      v[j] = tfb::apply_act(v[j], act);
+      if (residual) v[j] += __bfloat162float(residual[(long long)m * ldr + n + j]);
+      if (out_fp32) static_cast<float*>(C)[(long long)m * ldc + n + j] = v[j];
+      else static_cast<__nv_bfloat16*>(C)[(long long)m * ldc + n + j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+
 static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
                      long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
                      float alpha, int act, int out_mode, int max_ctas, const TfbGemmGroup* grp, int* status,
@@ -640,6 +696,27 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int gmode = grp ? grp->mode : 0;
   const int E = (gmode != 0) ? grp->num_experts : 1;
   if (gmode == 2 && out_mode == 0) return TFB_ERR_ARG;
+  if (gmode == 0 && !tp && out_mode != 2 && M <= 256 && K >= 16 * BK) {
+    // few output tiles: accumulate split-K partials in fp32 and finish in a second kernel
+    const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    const long long ldw = (N + 3) / 4 * 4;
+    const int all_sms = (max_ctas > 0 && max_ctas < sm_count()) ? max_ctas : sm_count();
+    if (tiles128 * 2 <= all_sms && (long long)M * ldw <= SPLITK_WS_ELEMS) {
+      cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+      if (float* ws = splitk_workspace(st0)) {
+        cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(float) * M * ldw, st0);
+        if (e != cudaSuccess) return int(e);
+        if (int rc0 = gemm_impl(A, lda, a_mn, B, ldb, b_mn, ws, ldw, M, N, K, nullptr, nullptr, 0, alpha, 0, 2, max_ctas, nullptr, status,
+                                stream, nullptr))
+          return rc0;
+        const long long quads = (long long)M * ldw / 4;
+        splitk_finalize_kernel<<<int((quads + 255) / 256), 256, 0, st0>>>(ws, ldw, C, ldc, static_cast<const __nv_bfloat16*>(bias),
+                                                                          static_cast<const __nv_bfloat16*>(residual), ldr, M, N, act,
+                                                                          out_mode == 1);
+        return int(cudaGetLastError());
+      }
+    }
+  }
   int BN = (N > 128) ? 256 : 128;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;

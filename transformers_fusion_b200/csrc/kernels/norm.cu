@@ -259,6 +259,97 @@ __global__ void __launch_bounds__(256) norm_dw_kernel(const __nv_bfloat16* __res
   }
 }
 
+// Few rows (decode batches): one CTA per row, so that a 4096-wide row is two 16-byte loads per thread instead of sixteen
+// dependent round trips in one warp; the warp-per-row kernel above relies on many resident rows to hide that latency.
+template <int NCH, bool LAYERNORM>
+__global__ void __launch_bounds__(256) norm_fwd_rowblock_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                                                const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                                                                __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+                                                                float* __restrict__ rstd_out, float* __restrict__ mean_out, int rows, int H,
+                                                                float eps) {
+  __shared__ float red[2][8];
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long off = (long long)row * H;
+  float v[NCH][8], wv[NCH][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (c * 256 + threadIdx.x) * 8;
+    if (col < H) {
+      load8(x + off + col, v[c]);
+      load8(w + col, wv[c]);
+    }
+  }
+  if (res) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 256 + threadIdx.x) * 8;
+      if (col < H) {
+        float r[8];
+        load8(res + off + col, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += r[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (c * 256 + threadIdx.x) * 8;
+    if (col < H) {
+      if (h_out) {
+        store8(h_out + off + col, v[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] = __bfloat162float(__float2bfloat16(v[c][i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s += v[c][i];
+        ss += v[c][i] * v[c][i];
+      }
+    }
+  }
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  if (lane == 0) {
+    red[0][warp] = s;
+    red[1][warp] = ss;
+  }
+  __syncthreads();
+  s = ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    s += red[0][i];
+    ss += red[1][i];
+  }
+  float mean = 0.f, rstd;
+  if (LAYERNORM) {
+    mean = s / H;
+    rstd = rsqrtf(fmaxf(ss / H - mean * mean, 0.f) + eps);
+  } else {
+    rstd = rsqrtf(ss / H + eps);
+  }
+  if (threadIdx.x == 0) {
+    if (rstd_out) rstd_out[row] = rstd;
+    if (LAYERNORM && mean_out) mean_out[row] = mean;
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (c * 256 + threadIdx.x) * 8;
+    if (col < H) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mean) * rstd * wv[c][i];
+      if (LAYERNORM && b) {
+        float bv[8];
+        load8(b + col, bv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += bv[i];
+      }
+      store8(y + off + col, o);
+    }
+  }
+}
+
 template <bool LN>
 static int launch_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* h_out, float* rstd,
                       float* mean, int rows, int H, float eps, cudaStream_t st) {
@@ -270,6 +361,11 @@ static int launch_fwd(const void* x, const void* res, const void* w, const void*
   auto B = static_cast<const __nv_bfloat16*>(b);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto Ho = static_cast<__nv_bfloat16*>(h_out);
+  if (H >= 2048 && rows <= 4 * sm_count()) {
+    if (H <= 4096) norm_fwd_rowblock_kernel<2, LN><<<rows, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
+    else norm_fwd_rowblock_kernel<4, LN><<<rows, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
+    return int(cudaGetLastError());
+  }
 #define TFB_GO(NC) norm_fwd_kernel<NC, LN><<<blocks, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps)
   if (H <= 512) TFB_GO(2);
   else if (H <= 1024) TFB_GO(4);

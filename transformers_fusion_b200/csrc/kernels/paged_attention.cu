@@ -188,14 +188,17 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
   }
   __syncthreads();
   float m[G], l[G];
-  constexpr int DPT = (D + DEC_THREADS - 1) / DEC_THREADS;  // output dims per thread (1 for D <= 128)
-  float acc[G][DPT];
+  // P.V: warp w takes the tokens w, w + 4, ... of a tile, lane l the DL consecutive output dims starting at l * DL; the
+  // four partial sums meet in shared memory after the last tile
+  constexpr int DL = D / 32;
+  constexpr int NW = DEC_THREADS / 32;
+  float acc[G][DL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
-    for (int j = 0; j < DPT; ++j) acc[g][j] = 0.f;
+    for (int j = 0; j < DL; ++j) acc[g][j] = 0.f;
   }
   const int* bt = block_table + (long long)b * max_pages;
   for (int t0 = t_begin; t0 < t_end; t0 += DEC_TILE) {
@@ -255,34 +258,69 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
       l[g] = l[g] * alpha[g] + v;
       m[g] = tile_m[g];
 #pragma unroll
-      for (int j = 0; j < DPT; ++j) acc[g][j] *= alpha[g];
+      for (int j = 0; j < DL; ++j) acc[g][j] *= alpha[g];
     }
     // ---- P.V: thread tid <-> output dims tid + j * DEC_THREADS ----
     const int nt = min(DEC_TILE, t_end - t0);
-    for (int tt = 0; tt < nt; ++tt) {
-      const int tk = t0 + tt;
-      const long long row = ((long long)bt[tk / PAGE] * PAGE + (tk % PAGE)) * Hkv + hk;
+    __syncthreads();                                   // sp[][] of this tile is complete
+    // four tokens of this warp per step: their V loads are independent and in flight together
+    constexpr int VU = 4;
+    for (int tt0 = warp; tt0 < nt; tt0 += NW * VU) {
+      float vv[VU][DL];
 #pragma unroll
-      for (int j = 0; j < DPT; ++j) {
-        const int d = tid + j * DEC_THREADS;
-        if (d < D) {
-          const float v = load_elem<MODE, D>(vpool, row, d);
+      for (int u = 0; u < VU; ++u) {
+        const int tt = min(tt0 + u * NW, nt - 1);
+        const int tk = t0 + tt;
+        const long long row = ((long long)bt[tk / PAGE] * PAGE + (tk % PAGE)) * Hkv + hk;
+        if (MODE == KV_BF16) {
+          const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(vpool.data) + row * D + lane * DL;
+          if (DL == 4) {
+            const uint2 w2 = *reinterpret_cast<const uint2*>(src);
+            const float2 a = unpack_bf16(w2.x), c = unpack_bf16(w2.y);
+            vv[u][0] = a.x; vv[u][1] = a.y; vv[u][DL - 2] = c.x; vv[u][DL - 1] = c.y;
+          } else {
+            const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(src));
+            vv[u][0] = a.x; vv[u][DL - 1] = a.y;
+          }
+        } else {
 #pragma unroll
-          for (int g = 0; g < G; ++g) acc[g][j] = fmaf(sp[g][tt], v, acc[g][j]);
+          for (int j = 0; j < DL; ++j) vv[u][j] = load_elem<MODE, D>(vpool, row, lane * DL + j);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < VU; ++u) {
+        const int tt = tt0 + u * NW;
+        if (tt < nt) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pw = sp[g][tt];
+#pragma unroll
+            for (int j = 0; j < DL; ++j) acc[g][j] = fmaf(pw, vv[u][j], acc[g][j]);
+          }
         }
       }
     }
     __syncthreads();
   }
+  // cross-warp sum of the partial outputs
+  __shared__ float part[NW][G][D];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int j = 0; j < DL; ++j) part[warp][g][lane * DL + j] = acc[g][j];
+  __syncthreads();
+  for (int i = tid; i < G * D; i += DEC_THREADS) {
+    const int g = i / D, d = i % D;
+    float v = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < NW; ++w2) v += part[w2][g][d];
+    const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
+    acc_out[base * D + d] = v;
+  }
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
-#pragma unroll
-    for (int j = 0; j < DPT; ++j) {
-      const int d = tid + j * DEC_THREADS;
-      if (d < D) acc_out[base * D + d] = acc[g][j];
-    }
-    if (tid == 0) {
+    if (tid == g) {
+      const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
       ml_out[base * 2] = m[g];
       ml_out[base * 2 + 1] = l[g];
     }
