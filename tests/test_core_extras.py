@@ -137,3 +137,37 @@ def test_tiled_attention_matches_dense_and_window():
         SX.MemoryEfficientAttention(max_context_tokens=100).forward(q, k, v)
     mg = SX.MultiGPUManager()
     assert mg.device_count() == len(mg.detect()) and mg.allocate_on(0, (2, 3)).shape == (2, 3)
+
+
+def test_mapped_file_json_value_rate_limiter_and_aliases(tmp_path):
+    p = tmp_path / "f.bin"
+    p.write_bytes(bytes(range(50)))
+    with C.MappedFile(str(p)) as mf:
+        assert mf.size == 50 and mf.read(10, 5) == bytes(range(10, 15)) and len(mf.view()) == 50
+        with pytest.raises(ValueError):
+            mf.read(48, 5)
+    j = C.JsonValue.parse('{"a": {"b": [1, 2.5, "x", true]}, "n": 3}')
+    assert j.get_int("n") == 3 and j.get_float("a.b.1") == 2.5 and j.get_str("a.b.2") == "x" and j.get_bool("a.b.3") is True
+    assert j.get("a.zz", "d") == "d" and j.get_int("a.b.2", 7) == 7 and j.is_object() and C.JsonValue.parse(j.dump()).get_int("a.b.0") == 1
+    from transformers_fusion_b200.server.production import RateLimiter
+    t = [0.0]
+    rl = RateLimiter(rate=2.0, burst=3.0, clock=lambda: t[0])
+    assert [rl.allow("ip") for _ in range(4)] == [True, True, True, False] and rl.allow("other")
+    assert rl.retry_after("ip") == pytest.approx(0.5)
+    t[0] = 1.0
+    assert rl.allow("ip") and rl.allow("ip") and not rl.allow("ip")
+    from transformers_fusion_b200.parallel.fsdp import GradientCheckpointManager, ZeROOptimizer, ZeroOptimizer
+    assert ZeROOptimizer is ZeroOptimizer
+    g = GradientCheckpointManager([100, 100, 400, 100], [1, 1, 2, 1])
+    assert g.plan(1000) == [False] * 4 and g.plan(350) == [False, False, True, False] and g.saved_bytes() == 300
+    assert g.recompute_overhead() == pytest.approx(0.4) and all(g.plan(0))
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.moe import MoEAllConfig, create_moe_variant
+    base = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=48, max_seq_len=32, init_std=0.1)
+    m = create_moe_variant("shared_expert", base, MoEAllConfig(num_experts=4, top_k=2, expert_hidden=32), dtype=torch.float32, seed=0)
+    assert m.cfg.variant == "SHARED_EXPERT" and m.cfg.num_shared_experts == 1 and m(torch.randint(0, 64, (1, 8))).shape[-1] == 64
+    with pytest.raises(ValueError):
+        create_moe_variant("nope", base)
+    from transformers_fusion_b200.agi.core import CodeGenSelfImprover, HPOptimizer, NeuralArchitectureSearch
+    assert HPOptimizer().engine is not None and NeuralArchitectureSearch().engine is not None
+    assert CodeGenSelfImprover().improve({"attention": 5.0}) is None     # hand-written kernels are not generated

@@ -753,3 +753,65 @@ class Flywheel:
                 break
             self.improver(rep["failures"])
         return self.iterations
+
+
+class CodeGenSelfImprover:
+    """Closes the loop between profiling and the kernel source generator: takes per-op timings and roofline targets, asks
+    the generator for shape-specialised candidates of the slowest op, keeps those that compile (and, with a GPU, pass the
+    numerical check) and reports the best.  Reference counterpart: CodeGenSelfImprover (include/quant/agi.h)."""
+
+    def __init__(self, generator=None):
+        if generator is None:
+            from ..trainer.code_gen import CodeGenerator
+            generator = CodeGenerator()
+        self.gen = generator
+        self.history: list = []
+
+    def improve(self, timings_ms: dict, roofline_ms: dict = None, n: int = 1 << 20, threshold_ms: float = 0.0):
+        from ..trainer.code_gen import KernelType
+        paths = self.gen.identify_slow_paths(timings_ms, roofline_ms or {}, threshold_ms)
+        for p_ in paths:
+            name = p_.op_name.upper()
+            if name not in KernelType.__members__:
+                continue
+            try:
+                cands = self.gen.auto_optimize(KernelType[name], n, 3)
+            except ValueError:
+                continue
+            if cands:
+                self.history.append((p_.op_name, cands[0].function_name, cands[0].benchmark_ms))
+                return cands[0]
+        return None
+
+
+class HPOptimizer:
+    """Hyper-parameter search facade over trainer.hpo_nas.HPOEngine (random / successive-halving / evolutionary search
+    over a SearchSpace with a user objective).  Reference counterpart: HPOptimizer (include/quant/agi.h)."""
+
+    def __init__(self, space=None, seed: int = 0):
+        from ..trainer.hpo_nas import HPOEngine, SearchSpace
+        self.engine = HPOEngine(space or SearchSpace(), seed=seed) if _accepts(HPOEngine, "seed") else HPOEngine(space or SearchSpace())
+
+    def __getattr__(self, name):
+        return getattr(self.engine, name)
+
+
+class NeuralArchitectureSearch:
+    """Architecture search facade over trainer.hpo_nas.NASEngine (mutation-based evolution under hardware constraints).
+    Reference counterpart: NeuralArchitectureSearch (include/quant/agi.h)."""
+
+    def __init__(self, cfg=None, constraints=None):
+        from ..trainer.hpo_nas import NASConfig, NASEngine
+        args = [a for a in (cfg or NASConfig(), constraints) if a is not None]
+        try:
+            self.engine = NASEngine(*args)
+        except TypeError:
+            self.engine = NASEngine(args[0])
+
+    def __getattr__(self, name):
+        return getattr(self.engine, name)
+
+
+def _accepts(cls, name: str) -> bool:
+    import inspect
+    return name in inspect.signature(cls.__init__).parameters

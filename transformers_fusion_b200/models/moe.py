@@ -15,13 +15,15 @@ from __future__ import annotations
 
 from typing import Optional
 
+from dataclasses import dataclass
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as TF
 
 from ..ops import functional as F
 from ..ops import moe as M
-from .config import MoEConfig
+from .config import MoEConfig, TransformerConfig
 from .dense import DenseModel, FlatBuffers, _EmbedFn, _FinalNormFn, _LinearFn, _ensure_main_grad
 
 # variant name -> (top_k override, renormalise, extra behaviour)
@@ -253,3 +255,33 @@ class MoEModel(DenseModel):
         E = self.cfg.num_experts
         return [torch.bincount(l.last_idx.reshape(-1).long(), minlength=E).float() / max(1, l.last_idx.numel())
                 for l in self.layers if hasattr(l, "last_idx")]
+
+
+@dataclass
+class MoEAllConfig:
+    """Router / capacity settings shared by every variant (reference MoEAllConfig, include/quant/moe_variants.h:61-123)."""
+    num_experts: int = 16
+    top_k: int = 2
+    expert_hidden: int = 2048
+    load_balance_weight: float = 0.01
+    router_z_weight: float = 0.001
+    capacity_factor: float = 2.0
+    capacity_policy: str = "fixed"          # fixed | token_drop | token_pass
+    num_shared_experts: int = 0
+
+
+def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfig" = None, **model_kw) -> "MoEModel":
+    """Factory: a MoEModel of the named variant (any of VARIANTS, case-insensitive) over the dense shape ``base``.
+    Reference counterpart: create_moe_variant (src/model/moe_core.cpp:446-551)."""
+    name = variant.upper()
+    if name not in VARIANTS:
+        raise ValueError(f"unknown MoE variant '{variant}' (known: {', '.join(VARIANTS)})")
+    m = mcfg or MoEAllConfig()
+    import dataclasses
+    fields = {f.name for f in dataclasses.fields(TransformerConfig)}
+    kw = {k: v for k, v in dataclasses.asdict(base).items() if k in fields}
+    shared = m.num_shared_experts or (1 if name == "SHARED_EXPERT" else 0)
+    cfg = MoEConfig(**kw, num_experts=m.num_experts, top_k=m.top_k, expert_hidden_size=m.expert_hidden, num_shared_experts=shared,
+                    load_balance_weight=m.load_balance_weight, router_z_weight=m.router_z_weight, capacity_factor=m.capacity_factor,
+                    capacity_policy=m.capacity_policy, variant=name)
+    return MoEModel(cfg, **model_kw)

@@ -427,3 +427,45 @@ class ZeROOffloadManager:
         r = fn()
         self.to_host()
         return r
+
+
+ZeROOptimizer = ZeroOptimizer
+
+
+class GradientCheckpointManager:
+    """Chooses which layers recompute their activations in backward so that the saved activations fit a byte budget:
+    layers are taken in order of bytes saved per recomputed FLOP (greedy), which for equal layers is simply "as few as
+    needed".  Reference counterparts: GradientCheckpointManager (src/trainer/zero_offload.cpp) and the greedy placement of
+    ActivationCheckpoint regions (src/trainer/zero_optimizer_mem.cpp:638)."""
+
+    def __init__(self, activation_bytes, recompute_flops=None):
+        self.bytes = [int(b) for b in activation_bytes]
+        self.flops = [float(f) for f in (recompute_flops or [1.0] * len(self.bytes))]
+        self.checkpointed = [False] * len(self.bytes)
+
+    def plan(self, budget_bytes: int):
+        """Marks layers until the saved activations (those of the layers not recomputed) fit; returns the marks."""
+        self.checkpointed = [False] * len(self.bytes)
+        order = sorted(range(len(self.bytes)), key=lambda i: -self.bytes[i] / max(self.flops[i], 1e-9))
+        saved = sum(self.bytes)
+        for i in order:
+            if saved <= budget_bytes:
+                break
+            self.checkpointed[i] = True
+            saved -= self.bytes[i]
+        return list(self.checkpointed)
+
+    def saved_bytes(self) -> int:
+        return sum(b for b, c in zip(self.bytes, self.checkpointed) if not c)
+
+    def recompute_overhead(self) -> float:
+        """Extra forward FLOPs as a fraction of one forward pass."""
+        tot = sum(self.flops)
+        return sum(f for f, c in zip(self.flops, self.checkpointed) if c) / tot if tot else 0.0
+
+    def apply(self, model):
+        """Sets the per-model switch when every layer is marked (the dense model recomputes all layers or none) and
+        returns the per-layer marks for engines that checkpoint selectively."""
+        if hasattr(model, "activation_checkpointing"):
+            model.activation_checkpointing = all(self.checkpointed) and bool(self.checkpointed)
+        return list(self.checkpointed)

@@ -414,3 +414,33 @@ class ModelZoo:
             if f.endswith(".quant"):
                 self.register(os.path.splitext(f)[0], os.path.join(directory, f))
         return self.list()
+
+
+class RateLimiter:
+    """Token bucket per client key: ``rate`` tokens per second, bursts up to ``burst``.  ``allow`` is what the HTTP front
+    end calls before admitting a request (HTTP 429 on refusal); idle buckets are dropped after ``idle_s``.
+    Reference counterpart: RateLimiter (src/server/http_server.cpp:116-152); the C++ server has the same policy built in."""
+
+    def __init__(self, rate: float, burst: float, idle_s: float = 300.0, clock=None):
+        import threading
+        import time as _t
+        self.rate, self.burst, self.idle_s = float(rate), float(burst), idle_s
+        self._clock = clock or _t.monotonic
+        self._b = {}
+        self._lock = threading.Lock()
+
+    def allow(self, key: str, cost: float = 1.0) -> bool:
+        now = self._clock()
+        with self._lock:
+            tokens, last = self._b.get(key, (self.burst, now))
+            tokens = min(self.burst, tokens + (now - last) * self.rate)
+            ok = tokens >= cost
+            self._b[key] = (tokens - cost if ok else tokens, now)
+            if len(self._b) > 4096:
+                self._b = {k: v for k, v in self._b.items() if now - v[1] < self.idle_s}
+            return ok
+
+    def retry_after(self, key: str, cost: float = 1.0) -> float:
+        with self._lock:
+            tokens, last = self._b.get(key, (self.burst, self._clock()))
+        return max(0.0, (cost - tokens) / self.rate) if self.rate > 0 else float("inf")

@@ -258,3 +258,84 @@ class ThreadSafeCounter:
     def snapshot(self) -> dict:
         with self._l:
             return dict(self._c)
+
+
+# ------------------------------------------------------------------------------------------------ files and JSON values
+class MappedFile:
+    """Read-only memory map of a file with bounds-checked slices (reference MappedFile, src/codec/quant_format.cpp:624-721)."""
+
+    def __init__(self, path: str):
+        import mmap
+        self.path = path
+        self._f = open(path, "rb")
+        self.size = self._f.seek(0, 2)
+        self._m = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if self.size else None
+
+    def valid(self) -> bool: return self._f is not None
+
+    def read(self, offset: int, n: int) -> bytes:
+        if offset < 0 or n < 0 or offset + n > self.size:
+            raise ValueError(f"read of [{offset}, {offset + n}) outside a file of {self.size} bytes")
+        return bytes(self._m[offset:offset + n]) if n else b""
+
+    def view(self) -> memoryview:
+        return memoryview(self._m) if self._m is not None else memoryview(b"")
+
+    def close(self):
+        if self._m is not None:
+            self._m.close()
+        if self._f is not None:
+            self._f.close()
+        self._m = self._f = None
+
+    def __enter__(self): return self
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+
+class JsonValue:
+    """Parsed JSON with dotted-path access and typed getters that fall back to a default instead of raising
+    (reference JsonValue, src/server/json_parser.cpp)."""
+
+    def __init__(self, value=None):
+        self.value = value
+
+    @staticmethod
+    def parse(text: str) -> "JsonValue":
+        import json
+        return JsonValue(json.loads(text))
+
+    def get(self, path: str, default=None):
+        cur = self.value
+        for part in path.split(".") if path else []:
+            if isinstance(cur, dict) and part in cur:
+                cur = cur[part]
+            elif isinstance(cur, list) and part.lstrip("-").isdigit() and -len(cur) <= int(part) < len(cur):
+                cur = cur[int(part)]
+            else:
+                return default
+        return cur
+
+    def get_int(self, path, default=0):
+        v = self.get(path, default)
+        return int(v) if isinstance(v, (int, float)) and not isinstance(v, bool) else default
+
+    def get_float(self, path, default=0.0):
+        v = self.get(path, default)
+        return float(v) if isinstance(v, (int, float)) and not isinstance(v, bool) else default
+
+    def get_str(self, path, default=""):
+        v = self.get(path, default)
+        return v if isinstance(v, str) else default
+
+    def get_bool(self, path, default=False):
+        v = self.get(path, default)
+        return v if isinstance(v, bool) else default
+
+    def is_object(self): return isinstance(self.value, dict)
+    def is_array(self): return isinstance(self.value, list)
+
+    def dump(self) -> str:
+        import json
+        return json.dumps(self.value, separators=(",", ":"))
