@@ -39,10 +39,9 @@ namespace tfb {
 constexpr int WQ_BM = 128, WQ_BN = 128, WQ_BK = 64, WQ_RAW_STAGES = 8, WQ_THREADS = 768, WQ_DQ_THREADS = 256;
 constexpr int WQ_B_BYTES = WQ_BN * WQ_BK * 2;
 constexpr int WQ_RAW_CODES = 128 * 64, WQ_RAW_STAGE = WQ_RAW_CODES + 128 * 2 * 2;     // codes (<= 8 KB) + scales (<= 512 B)
-// Shared-memory plan for an activation tile of AROWS real rows.  The MMA always multiplies 128 rows; with AROWS = 16
-// (decode batches) only the first two 8-row swizzle groups of the A tile are loaded and the instruction reads on into the
-// B tile behind them: rows are independent in D = A * B, and accumulator rows past M are never stored.  The small A tile
-// doubles the ring depth, which is what covers the commit -> refill round trip when the MMAs themselves are short.
+// Shared-memory plan for an activation tile of AROWS real rows.  With AROWS = 16 (decode batches) the activation tile is two
+// 8-row swizzle groups (2 KB) and the product is issued with swapped operands (weights on the M side, batch on the N = 16
+// side).  The small tile doubles the ring depth, which covers the commit -> refill round trip when the MMAs are short.
 template <int AROWS>
 struct WqPlan {
   static constexpr int STAGES = AROWS == 16 ? 8 : 4;
@@ -275,7 +274,11 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(FMT_BF16, FMT_BF16, false, false, WQ_BM, WQ_BN);
+      // AROWS == 16 (decode): operands swapped, D^T[n, m] = W[n, :] . X[m, :]: the 128 weight rows of the tile are the M side
+      // of the instruction and the batch its N = 16 side, so an MMA costs an eighth of the 128 x 128 form and the k-block is
+      // no longer bounded below by tensor time
+      constexpr bool SWAP = AROWS == 16;
+      constexpr uint32_t idesc = umma_idesc(FMT_BF16, FMT_BF16, false, false, WQ_BM, SWAP ? 16 : WQ_BN);
       int stage = 0, abuf = 0;
       uint32_t phase = 0, aphase = 0;
       bool ok = true;
@@ -292,7 +295,8 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
           const uint32_t sa = smem_base + stage * WQ_STAGE, sb = sa + WQ_A_BYTES;
 #pragma unroll
           for (int k = 0; k < WQ_BK / 16; ++k)
-            umma_f16_ss(tmem_d, umma_smem_desc(sa + k * 32, 16, 1024), umma_smem_desc(sb + k * 32, 16, 1024), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_f16_ss(tmem_d, umma_smem_desc((SWAP ? sb : sa) + k * 32, 16, 1024), umma_smem_desc((SWAP ? sa : sb) + k * 32, 16, 1024), idesc,
+                        (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(bar_empty + stage * 8);
           if (++stage == WQ_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -348,8 +352,22 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr0 = tmem_base + abuf * WQ_BN + (uint32_t(quad * 32) << 16);
-      // rows past M hold zeros: a warp whose 32 rows are all past M only releases the accumulator
-      if (m0 + quad * 32 < p.M) {
+      if (AROWS == 16) {
+        // swapped operands: lane = weight row n of the tile, the 16 accumulator columns = batch rows m
+        uint32_t v[16];
+        tmem_ld_32x16(taddr0, v);
+        tmem_ld_wait();
+        const int n = nb * WQ_BN + quad * 32 + lane;
+        const float bv = (p.bias && kb0 == 0) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+          if (m < p.M) {
+            const float f = __uint_as_float(v[m]) + bv;
+            if (p.splits > 1) atomicAdd(static_cast<float*>(p.C) + (long long)m * p.ldc + n, f);
+            else static_cast<__nv_bfloat16*>(p.C)[(long long)m * p.ldc + n] = __float2bfloat16(f);
+          }
+        }
+      } else if (m0 + quad * 32 < p.M) {
 #pragma unroll 1
         for (int c = 0; c < WQ_BN / 16; ++c) {
           uint32_t v[16];
