@@ -55,7 +55,7 @@ class MoETrainer(Trainer):
 
     def compute_aux_loss(self) -> float:
         a = self.model.last_aux
-        return float(a) if a is not None else 0.0
+        return float(a.detach()) if a is not None else 0.0
 
     def train_step(self, ids, labels) -> float:
         loss = super().train_step(ids, labels)
