@@ -38,7 +38,7 @@ def _train(tmp_path, name, flags, nproc=2):
     return r, model
 
 
-@pytest.mark.parametrize("name,flags", [("dp", ["--zero-stage", "2"]), ("tp", ["--tp", "2"]), ("pp", ["--pp", "2"])])
+@pytest.mark.parametrize("name,flags", [("dp", ["--zero-stage", "2"]), ("tp", ["--tp", "2"]), ("pp", ["--pp", "2"]), ("fsdp", ["--zero-stage", "3"])])
 def test_train_cli_meshes(tmp_path, name, flags):
     r, model = _train(tmp_path, name, flags)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]

@@ -689,7 +689,7 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const float* __res
 static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* C,
                      long long ldc, int M, int N, int K, const void* bias, const void* residual, long long ldr,
                      float alpha, int act, int out_mode, int max_ctas, const TfbGemmGroup* grp, int* status,
-                     void* stream, const TfbGemmTp* tp = nullptr) {
+                     void* stream, const TfbGemmTp* tp = nullptr, int force_splits = 0) {
   using namespace tfb;
   if (M <= 0 || N <= 0 || K <= 0) return TFB_ERR_ARG;
   if (out_mode != 0 && (bias || residual || act)) return TFB_ERR_ARG;
@@ -697,17 +697,29 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int E = (gmode != 0) ? grp->num_experts : 1;
   if (gmode == 2 && out_mode == 0) return TFB_ERR_ARG;
   if (gmode == 0 && !tp && out_mode != 2 && M <= 256 && K >= 16 * BK) {
-    // few output tiles: accumulate split-K partials in fp32 and finish in a second kernel
-    const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    // Few rows: the product streams the weights once and is bound by how evenly the work items cover the SMs.  Pick the
+    // split count whose item count (tiles x splits) fills whole waves best, keeping at least 8 k-blocks per split;
+    // accumulate the partials in fp32 and finish in a second kernel.
+    const long long tiles_w = (long long)((M + BM - 1) / BM) * ((N + (N > 128 ? 255 : 127)) / (N > 128 ? 256 : 128));
     const long long ldw = (N + 3) / 4 * 4;
     const int all_sms = (max_ctas > 0 && max_ctas < sm_count()) ? max_ctas : sm_count();
-    if (tiles128 * 2 <= all_sms && (long long)M * ldw <= SPLITK_WS_ELEMS) {
+    const int total_kb0 = (K + BK - 1) / BK;
+    int best_s = 1;
+    double best_eff = 0.0, eff1 = 0.0;
+    for (int sp = 1; sp <= 16 && sp * 8 <= total_kb0; ++sp) {
+      const long long items = tiles_w * sp;
+      const double eff = double(items) / double((items + all_sms - 1) / all_sms * all_sms);
+      if (sp == 1) eff1 = eff;
+      if (eff > best_eff + 0.02) { best_eff = eff; best_s = sp; }
+    }
+    if (best_eff < eff1 + 0.1) best_s = 1;             // the workspace pass costs about a tenth of a weight-streaming product
+    if (best_s > 1 && (long long)M * ldw <= SPLITK_WS_ELEMS) {
       cudaStream_t st0 = static_cast<cudaStream_t>(stream);
       if (float* ws = splitk_workspace(st0)) {
         cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(float) * M * ldw, st0);
         if (e != cudaSuccess) return int(e);
         if (int rc0 = gemm_impl(A, lda, a_mn, B, ldb, b_mn, ws, ldw, M, N, K, nullptr, nullptr, 0, alpha, 0, 2, max_ctas, nullptr, status,
-                                stream, nullptr))
+                                stream, nullptr, best_s))
           return rc0;
         const long long quads = (long long)M * ldw / 4;
         splitk_finalize_kernel<<<int((quads + 255) / 256), 256, 0, st0>>>(ws, ldw, C, ldc, static_cast<const __nv_bfloat16*>(bias),
@@ -796,7 +808,9 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int total_kb = (K + BK - 1) / BK;
   const int tiles = p.tiles_m * p.tiles_n;
   int splits = 1;
-  if (out_mode == 2 && gmode == 0 && tiles < sms) {
+  if (force_splits > 0 && out_mode == 2 && gmode == 0) {
+    splits = force_splits;
+  } else if (out_mode == 2 && gmode == 0 && tiles < sms) {
     splits = sms / tiles;                       // round down: all work items must fit in one wave
     const int max_splits = (total_kb + 7) / 8;  // keep at least 8 k-blocks (512 of K) per split
     if (splits > max_splits) splits = max_splits;

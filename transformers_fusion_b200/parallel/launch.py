@@ -8,6 +8,7 @@ fastest (tensor-parallel peers exchange the most data per step), then dp, then p
 ``init_parallel`` builds the groups; ``fit_parallel`` runs the training loop that matches the factors:
   tp > 1          TPDenseModel + TPTrainer (fused all-gather->GEMM / GEMM->reduce-scatter), gradients averaged over dp
   pp > 1          PipelineParallel 1F1B over the layer ranges, AdamW on the parameters each stage owns
+  zero stage 3    FullyShardedDataParallel (weights gathered inside the consuming GEMM on CUDA)
   otherwise       the ordinary Trainer: data parallel with ZeRO stage 0 / 1 / 2 (fused reduce-scatter + AdamW)
 
 Reference counterparts: DistributedContext::init (src/distributed/distributed.cpp:21-123), FSDP / DDP / pipeline /
@@ -180,6 +181,27 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
             report(step, loss, lr_at(step), toks, t0)
         # every stage sends its owned tensors to rank 0 of its pipeline, which then holds the full model
         _collect_pipeline(model, pipe, st)
+        if st.is_main:
+            Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
+        return loss
+    if getattr(cfg, "zero_stage", 0) >= 3 and st.world > 1:
+        # ZeRO-3 / FSDP: weights, gradients and optimiser state sharded; on CUDA the weight all-gather runs inside the GEMM
+        from .collectives import DistributedContext
+        from .fsdp import FSDPConfig, FullyShardedDataParallel
+        symm = None
+        if st.device.type == "cuda":
+            from .symm import SymmetricHeap
+            symm = SymmetricHeap(st.rank, st.world, st.device)
+        fsdp = FullyShardedDataParallel(model, FSDPConfig(), DistributedContext(st.rank, st.world, None), symm)
+        for step in range(1, steps + 1):
+            ids, labels = dl.next_batch()
+            l = fsdp.train_step(ids, labels, lr_at(step))
+            lt = torch.as_tensor(float(l), device=st.device).reshape(1)
+            dist.all_reduce(lt)
+            loss = float(lt) / st.world
+            toks += ids.numel() * st.dp
+            report(step, loss, lr_at(step), toks, t0)
+        fsdp.consolidate()
         if st.is_main:
             Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
         return loss
