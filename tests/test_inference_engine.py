@@ -133,3 +133,18 @@ def test_decode_graph_replay_matches_eager(weights):
         if graph:
             assert sorted(eng._graphs) == [1, 2, 4]
     assert outs[0] == outs[1]
+
+
+def test_batched_prefill_matches_one_by_one():
+    """Prompts of different lengths prefilled together (padded) give the tokens of one-by-one prefill, and the padded rows
+    leave no trace in the cache (page accounting is identical)."""
+    m = _model()
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, 200, (n,), generator=g).tolist() for n in (5, 33, 18, 64, 7)]
+    res = []
+    for bp in (False, True):
+        eng = InferenceEngine(m, None, EngineConfig(max_batch=8, num_pages=64, batch_prefill=bp, max_prefill_tokens=150,
+                                                    enable_prefix_cache=False))
+        outs = eng.generate_batch(prompts, max_tokens=6, sampling=GREEDY)
+        res.append((outs, eng.cache.allocator.num_free, eng.stats.prompt_tokens))
+    assert res[0] == res[1]

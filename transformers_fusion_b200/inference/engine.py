@@ -41,6 +41,8 @@ class EngineConfig:
     weight_format: str = ""        # "" = bf16 weights; int8 | int4 | mxfp8 | fp4 | ternary: fused-dequant GEMM (quant/wq.py)
     weight_group: int = 32
     cuda_graph: bool = True        # decode steps replay a captured graph per batch-size bucket (CUDA only)
+    batch_prefill: bool = True     # prompts admitted in the same step (without a cached prefix) are prefilled together
+    max_prefill_tokens: int = 8192 # padded tokens per prefill batch
 
 
 @dataclass
@@ -243,6 +245,80 @@ class InferenceEngine:
                 h = h + attn
         return h if all_positions else h[-1:]
 
+    def _layers_prefill_batch(self, reqs: List[Request]):
+        """Whole prompts of several sequences in one pass: rows are [B, S_max] with the shorter prompts padded on the right
+        (causal attention keeps padding from reaching real tokens; padded rows carry slot -1 and are not cached).
+        Returns the hidden state of every sequence's last prompt token, [B, H]."""
+        m, mc = self.model, self.model.cfg
+        dev = self.device
+        Hq, Hkv, D = mc.num_heads, mc.num_kv_heads, mc.head_dim
+        B, S = len(reqs), max(len(r.tokens) for r in reqs)
+        ids = torch.zeros((B, S), dtype=torch.int64)
+        slots = torch.full((B, S), -1, dtype=torch.int64)
+        for b, r in enumerate(reqs):
+            n = len(r.tokens)
+            ids[b, :n] = torch.tensor(r.tokens, dtype=torch.int64)
+            pg = torch.tensor(r.pages, dtype=torch.int64)
+            pos = torch.arange(n)
+            slots[b, :n] = pg[pos // PAGE] * PAGE + pos % PAGE
+        ids, slots = ids.to(dev).reshape(-1), slots.to(dev).reshape(-1)
+        h = F.embedding_fwd(ids, m.tok_embeddings.data, None, 0)
+        if m.pos_embeddings is not None:
+            h = h + m.pos_embeddings.data[:S].repeat(B, 1)
+        rope = m.rope(dev)
+        positions = torch.arange(S, dtype=torch.int32, device=dev).repeat(B)
+        for li, w in enumerate(m.layers):
+            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
+            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
+            if rope is not None:
+                F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S, positions=positions)
+            self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
+            o, _ = F.attn_fwd(qkv, qkv, qkv, B, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
+            if mc.use_parallel_residual:
+                attn = self._lin(o, li, "o", w.o, w.o_bias)
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                base = h
+            else:
+                base = self._lin(o, li, "o", w.o, w.o_bias, h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
+            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
+            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
+            h = self._lin(act, li, "down", w.down, w.down_bias, base)
+            if mc.use_parallel_residual:
+                h = h + attn
+        last = torch.tensor([b * S + len(r.tokens) - 1 for b, r in enumerate(reqs)], dtype=torch.int64, device=dev)
+        return h[last]
+
+    def _prefill_fresh(self, fresh: List[Request], finished: list):
+        """Groups the newly admitted prompts (sorted by length, so padding stays small) under the padded-token budget and
+        prefills each group in one pass; then samples every sequence's first token."""
+        fresh = sorted(fresh, key=lambda r: len(r.tokens))
+        groups, cur = [], []
+        for r in fresh:
+            if cur and (len(cur) + 1) * len(r.tokens) > self.cfg.max_prefill_tokens:
+                groups.append(cur)
+                cur = []
+            cur.append(r)
+        if cur:
+            groups.append(cur)
+        for grp in groups:
+            t0 = time.perf_counter()
+            h = self._layers_prefill_batch(grp) if len(grp) > 1 else self._layers_prefill(grp[0].tokens, 0, grp[0])
+            toks = self._sample(self._logits(h), grp)
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self.stats.prefill_ms += (time.perf_counter() - t0) * 1e3
+            for r, tok in zip(grp, toks):
+                n = len(r.tokens)
+                self.stats.prompt_tokens += n
+                if self.prefix:
+                    self.prefix.insert(r.tokens, r.pages)
+                r.pos = n
+                r.t_first = time.perf_counter()
+                self._emit(r, tok, finished)
+                if not r.finished:
+                    self.running.append(r)
+
     def _layers_decode(self, tokens, positions, block_table, slots):
         m, mc = self.model, self.model.cfg
         Hq, Hkv, D = mc.num_heads, mc.num_kv_heads, mc.head_dim
@@ -304,7 +380,8 @@ class InferenceEngine:
         finished: List[Request] = []
         alloc = self.cache.allocator
         # ---- admission / prefill ----
-        while self.waiting and len(self.running) < self.cfg.max_batch:
+        fresh: List[Request] = []
+        while self.waiting and len(self.running) + len(fresh) < self.cfg.max_batch:
             r = self.waiting[0][3]
             n = min(len(r.tokens), self.max_len - 1)
             r.tokens = r.tokens[:n]
@@ -322,6 +399,9 @@ class InferenceEngine:
             heapq.heappop(self.waiting)
             r.pages = shared + [alloc.alloc() for _ in range((n + PAGE - 1) // PAGE - len(shared))]
             pos0 = len(shared) * PAGE
+            if pos0 == 0 and self.cfg.batch_prefill:
+                fresh.append(r)
+                continue
             t0 = time.perf_counter()
             h = self._layers_prefill(r.tokens, pos0, r)
             tok = self._sample(self._logits(h), [r])[0]
@@ -337,6 +417,8 @@ class InferenceEngine:
             self._emit(r, tok, finished)
             if not r.finished:
                 self.running.append(r)
+        if fresh:
+            self._prefill_fresh(fresh, finished)
         # ---- one decode token for everything that is running ----
         if self.running:
             t0 = time.perf_counter()
