@@ -137,6 +137,7 @@ class _DecodeGraph:
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
+        self._last_n = -1
         with torch.cuda.graph(self.graph):
             self.logits = run()
 
@@ -146,9 +147,10 @@ class _DecodeGraph:
         self.positions[:n].copy_(positions, non_blocking=True)
         self.bt[:n].copy_(bt, non_blocking=True)
         self.slots[:n].copy_(slots, non_blocking=True)
-        if n < self.bucket:
+        if n < self.bucket and n != self._last_n:      # rows past the live batch: reset once per batch size
             self.positions[n:].zero_()
             self.slots[n:].fill_(-1)
+        self._last_n = n
         self.graph.replay()
         return self.logits[:n]
 
@@ -166,6 +168,8 @@ class InferenceEngine:
         self._ids = itertools.count(1)
         self._step = 0
         self._graphs = {}
+        self._sample_cache = None
+        self._bt_cache = None
         self.stats = InferenceStats()
         self.max_pages = (self.max_len + PAGE - 1) // PAGE
         self.packed = {}
@@ -356,11 +360,16 @@ class InferenceEngine:
 
     def _sample(self, logits, reqs):
         dev = logits.device
-        t = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
-        k = torch.tensor([0 if (r.sampling.reference_rule and r.sampling.top_p < 1) else r.sampling.top_k for r in reqs],
-                         dtype=torch.int32, device=dev)
-        p = torch.tensor([r.sampling.top_p for r in reqs], dtype=torch.float32, device=dev)
-        rp = torch.tensor([r.sampling.repetition_penalty for r in reqs], dtype=torch.float32, device=dev)
+        # the per-row sampling parameters only change when the set of rows does: keep them on the device between steps
+        key = tuple(r.id for r in reqs)
+        cached = self._sample_cache
+        if cached is None or cached[0] != key:
+            vals = torch.tensor([[r.sampling.temperature, r.sampling.top_p, r.sampling.repetition_penalty] for r in reqs],
+                                dtype=torch.float32).t().contiguous().to(dev)
+            k = torch.tensor([0 if (r.sampling.reference_rule and r.sampling.top_p < 1) else r.sampling.top_k for r in reqs],
+                             dtype=torch.int32, device=dev)
+            cached = self._sample_cache = (key, vals[0], k, vals[1], vals[2])
+        _, t, k, p, rp = cached
         hist = None
         if any(r.sampling.repetition_penalty != 1.0 for r in reqs):
             n = max(len(r.tokens) + len(r.out) for r in reqs)
@@ -427,13 +436,18 @@ class InferenceEngine:
                 if r.pos // PAGE >= len(r.pages):
                     r.pages.append(alloc.alloc())
             dev = self.device
-            tokens = torch.tensor([r.out[-1] for r in reqs], dtype=torch.int64, device=dev)
-            positions = torch.tensor([r.pos for r in reqs], dtype=torch.int32, device=dev)
-            bt = torch.zeros((len(reqs), self.max_pages), dtype=torch.int32)
-            for i, r in enumerate(reqs):
-                bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-            bt = bt.to(dev)
-            slots = torch.tensor([r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs], dtype=torch.int64, device=dev)
+            # tokens, positions and slots travel in one small upload; the block table is re-sent only when a row changed
+            # (a new request set, or a sequence that started a new page)
+            packed = torch.tensor([[r.out[-1] for r in reqs], [r.pos for r in reqs],
+                                   [r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs]], dtype=torch.int64).to(dev)
+            tokens, positions, slots = packed[0], packed[1].to(torch.int32), packed[2]
+            bt_key = (tuple(r.id for r in reqs), tuple(len(r.pages) for r in reqs))
+            if self._bt_cache is None or self._bt_cache[0] != bt_key:
+                bt = torch.zeros((len(reqs), self.max_pages), dtype=torch.int32)
+                for i, r in enumerate(reqs):
+                    bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+                self._bt_cache = (bt_key, bt.to(dev))
+            bt = self._bt_cache[1]
             if self.cfg.cuda_graph and dev.type == "cuda":
                 bucket = 1
                 while bucket < len(reqs):
