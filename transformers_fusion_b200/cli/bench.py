@@ -157,15 +157,27 @@ def serve_bench(a):
     from ..inference.sampler import SamplerConfig
     from ..models.config import preset
     from ..models.dense import DenseModel
-    dev = torch.device("cuda", 0)
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    symm = None
+    if world > 1:                                  # tensor-parallel serving: one process per GPU (torch.distributed.run)
+        import torch.distributed as dist
+
+        from ..inference.tp_engine import TPInferenceEngine
+        from ..parallel.symm import SymmetricHeap
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        symm = SymmetricHeap(rank, world, dev)
     cfg = preset(a.preset)
     model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
     g = torch.Generator().manual_seed(0)
     for B in [int(x) for x in a.batch.split(",")]:
         pages = (a.prompt_len + a.gen + 31) // 16 * B + 64
-        eng = InferenceEngine(model, None, EngineConfig(max_batch=B, num_pages=pages, kv_mode=a.kv, weight_format=a.weights,
-                                                        cuda_graph=not a.no_graph, enable_prefix_cache=False,
-                                                        max_seq_len=min(cfg.max_seq_len, a.prompt_len + a.gen + 16)))
+        ecfg = EngineConfig(max_batch=B, num_pages=pages, kv_mode=a.kv, weight_format=a.weights, cuda_graph=not a.no_graph,
+                            enable_prefix_cache=False, max_seq_len=min(cfg.max_seq_len, a.prompt_len + a.gen + 16))
+        eng = TPInferenceEngine(model, None, ecfg, rank, world, symm) if world > 1 else InferenceEngine(model, None, ecfg)
         greedy = SamplerConfig(temperature=0.0, top_k=0, top_p=1.0)
         for rep in range(2):                       # the first pass builds graphs and workspaces
             prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(B)]
@@ -181,12 +193,17 @@ def serve_bench(a):
             dt = time.perf_counter() - t0
         out_tokens = sum(len(r.out) for r in reqs)
         rec = {"bench": "serve", "preset": a.preset, "batch": B, "prompt_len": a.prompt_len, "gen": a.gen, "weights": a.weights or "bf16",
-               "kv": a.kv, "cuda_graph": not a.no_graph, "out_tok_s": round(out_tokens / dt, 1),
+               "kv": a.kv, "tp": world, "cuda_graph": eng.cfg.cuda_graph, "out_tok_s": round(out_tokens / dt, 1),
                "ttft_ms_p50": round(statistics.median((r.t_first - r.t_submit) * 1e3 for r in reqs), 2),
                "decode_ms_per_step": round((eng.stats.decode_ms - d0) / max(1, steps), 3), "total_ms": round(dt * 1e3, 1)}
-        print(json.dumps(rec), flush=True)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
         del eng
         torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+        symm.close()
+        dist.destroy_process_group()
 
 
 def main(argv=None):
