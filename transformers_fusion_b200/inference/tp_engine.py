@@ -63,8 +63,8 @@ class TPInferenceEngine(InferenceEngine):
     def __init__(self, model: DenseModel, tokenizer=None, cfg: Optional[EngineConfig] = None, rank: int = 0, world: int = 1,
                  symm=None, group=None):
         cfg = cfg or EngineConfig()
-        if world > 1 and cfg.cuda_graph:
-            cfg = dataclasses.replace(cfg, cuda_graph=False)          # cross-rank flag kernels are launched eagerly
+        # Decode graphs are safe across ranks: every rank captures and replays the same sequence of kernels, and the
+        # all-reduce kernels keep their epoch and ticket in device memory (nothing host-side is baked into the graph).
         self.tp_rank, self.tp_world, self.tp_group = rank, world, group
         local = shard_dense_for_tp(model, rank, world) if world > 1 else model
         super().__init__(local, tokenizer, cfg)
