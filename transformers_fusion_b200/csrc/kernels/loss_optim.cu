@@ -206,6 +206,87 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
   }
 }
 
+// Three-pass form for large vocabularies with in-place gradients (row in 16-byte vectors):
+//   1  max of the row                                   (reads logits from HBM)
+//   2  p = 2^((z - max) * log2 e), sum p, store p over the row   (reads L2, one exponential per element)
+//   3  g = p * (pm / sum) - sm, label fix, store g               (reads L2, no exponential)
+// One exponential per element instead of the two of the online form, and about half its instructions; the row a CTA
+// works on (64 KB at 32k vocabulary) stays in L2 between passes, so HBM sees one read and one write.  p is rounded to
+// bf16 before the final scaling, which adds one bf16 rounding to a gradient that is stored in bf16 anyway.
+__global__ void __launch_bounds__(512) cross_entropy_3pass_kernel(const __nv_bfloat16* logits, const long long* __restrict__ labels,
+                                                                  float* __restrict__ loss, float* __restrict__ lse_out,
+                                                                  __nv_bfloat16* dlogits, const float* __restrict__ scale_ptr, int V,
+                                                                  long long ld, long long ignore_index, float eps, float zw) {
+  __shared__ float sh[32];
+  constexpr float L2E = 1.4426950408889634f;
+  const long long t = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(logits + t * ld);
+  uint4* drow = reinterpret_cast<uint4*>(dlogits + t * ld);
+  const long long label = labels[t];
+  const bool ignored = (label == ignore_index);
+  if (threadIdx.x == 0) TFB_BOUNDS(ignored || (label >= 0 && label < V), 3, label, V);
+  const bool has_label = !ignored && label >= 0 && label < V;
+  const float zy = has_label ? __bfloat162float(logits[t * ld + label]) : 0.f;   // read before the row is overwritten
+  const int V8 = V >> 3;
+  float mx = -INFINITY, tot = 0.f;
+  for (int i = threadIdx.x; i < V8; i += 512) {
+    const uint4 u = row[i];
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16(p[k]);
+      mx = fmaxf(mx, fmaxf(f.x, f.y));
+      if (eps != 0.f) tot += f.x + f.y;
+    }
+  }
+  const float gmx = block_reduce_max(mx, sh);
+  const float gtot = eps != 0.f ? block_reduce_sum(tot, sh) : 0.f;
+  const float off = -gmx * L2E;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < V8; i += 512) {
+    uint4 u = row[i];
+    uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16(p[k]);
+      const float e0 = exp2f(fmaf(f.x, L2E, off)), e1 = exp2f(fmaf(f.y, L2E, off));
+      sum += e0 + e1;
+      p[k] = pack_bf16(e0, e1);
+    }
+    drow[i] = u;
+  }
+  const float gsum = block_reduce_sum(sum, sh);           // also orders pass 2's stores before pass 3's loads (bar.sync)
+  const float lse = gmx + logf(gsum);
+  if (threadIdx.x == 0) {
+    loss[t] = ignored ? 0.f : (1.f - eps) * (lse - zy) + eps * (lse - gtot / V) + zw * lse * lse;
+    if (lse_out) lse_out[t] = lse;
+  }
+  const float scale = ignored ? 0.f : (scale_ptr ? *scale_ptr : 1.f);
+  const float pm = scale * (1.f + 2.f * zw * lse) / gsum;
+  const float sm = scale * eps / V;
+  const float hot = scale * (1.f - eps);
+  const int lab_vec = has_label ? int(label >> 3) : -1, lab_k = int(label & 7);
+  for (int i = threadIdx.x; i < V8; i += 512) {            // thread i revisits exactly the vectors it wrote in pass 2
+    uint4 u = drow[i];
+    uint32_t* p = reinterpret_cast<uint32_t*>(&u);
+    float g[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16(p[k]);
+      g[2 * k] = fmaf(f.x, pm, -sm);
+      g[2 * k + 1] = fmaf(f.y, pm, -sm);
+    }
+    if (i == lab_vec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k == lab_k) g[k] -= hot;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = pack_bf16(g[2 * k], g[2 * k + 1]);
+    drow[i] = u;
+  }
+}
+
 // sum over n of x^2, accumulated into *out (fp32).  x is fp32.
 __global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
   __shared__ float sh[32];
@@ -351,6 +432,12 @@ TFB_API int tfb_cross_entropy(const void* logits, const long long* labels, float
   // keeps four CTAs per SM in flight, measured faster than holding the row in registers (fewer resident warps).
   if (vec && V <= 512 * 8 * 2) {
     cross_entropy_regs_kernel<2><<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V, ld,
+        ignore_index, label_smoothing, z_weight);
+    return int(cudaGetLastError());
+  }
+  if (vec && dlogits == logits) {
+    cross_entropy_3pass_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V, ld,
         ignore_index, label_smoothing, z_weight);
     return int(cudaGetLastError());
