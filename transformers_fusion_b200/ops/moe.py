@@ -20,6 +20,9 @@ from . import _lib, functional as F
 from ._lib import c_f, c_i, c_ll, c_p, check, ptr, stream
 
 _lib.register("tfb_router_topk", [c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_p])
+_lib.register("tfb_router_topk2", [c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p])
+_lib.register("tfb_moe_permute2", [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+_lib.register("tfb_moe_zero_pads", [c_p, c_i, c_p, c_p, c_i, c_p, c_i, c_p])
 _lib.register("tfb_moe_plan", [c_p, c_i, c_p, c_p, c_p, c_i, c_p, c_p])
 _lib.register("tfb_moe_permute", [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p])
 _lib.register("tfb_moe_combine", [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p])
@@ -44,6 +47,12 @@ def _grouped_fn():
 # ---------------------------------------------------------------------------------------------
 def router_topk(logits, k, renormalize=True):
     """logits [T, E] -> (idx int32 [T,k], w fp32 [T,k], probs fp32 [T,E], counts int32 [E], lse fp32 [T])."""
+    return router_topk_stats(logits, k, renormalize)[:5]
+
+
+def router_topk_stats(logits, k, renormalize=True):
+    """router_topk plus the two reductions the auxiliary losses need, produced by the same kernel:
+    prob_sums fp32 [E] = sum_t probs[t, e] and lse_sq fp32 [1] = sum_t lse_t^2."""
     T, E = logits.shape
     if not logits.is_cuda:
         z = logits.float()
@@ -52,17 +61,19 @@ def router_topk(logits, k, renormalize=True):
         if renormalize:
             w = w / w.sum(-1, keepdim=True)
         counts = torch.bincount(idx.reshape(-1), minlength=E).int()
-        return idx.int(), w, probs, counts, torch.logsumexp(z, -1)
+        lse = torch.logsumexp(z, -1)
+        return idx.int(), w, probs, counts, lse, probs.sum(0), (lse * lse).sum().reshape(1)
     dev = logits.device
     idx = torch.empty((T, k), dtype=torch.int32, device=dev)
     w = torch.empty((T, k), dtype=torch.float32, device=dev)
     probs = torch.empty((T, E), dtype=torch.float32, device=dev)
-    counts = torch.zeros(E, dtype=torch.int32, device=dev)
+    red = torch.zeros(2 * E + 1, dtype=torch.float32, device=dev)        # [counts as int32 | prob_sums | lse_sq], one fill
+    counts, prob_sums, lse_sq = red[:E].view(torch.int32), red[E:2 * E], red[2 * E:]
     lse = torch.empty(T, dtype=torch.float32, device=dev)
-    check(_lib.lib().tfb_router_topk(logits.data_ptr(), int(logits.dtype == torch.float32), T, E, k, int(renormalize),
-                                     idx.data_ptr(), w.data_ptr(), probs.data_ptr(), counts.data_ptr(), None,
-                                     lse.data_ptr(), stream()), "router_topk")
-    return idx, w, probs, counts, lse
+    check(_lib.lib().tfb_router_topk2(logits.data_ptr(), int(logits.dtype == torch.float32), T, E, k, int(renormalize),
+                                      idx.data_ptr(), w.data_ptr(), probs.data_ptr(), counts.data_ptr(), prob_sums.data_ptr(),
+                                      lse.data_ptr(), lse_sq.data_ptr(), stream()), "router_topk")
+    return idx, w, probs, counts, lse, prob_sums, lse_sq
 
 
 class Plan:
@@ -72,6 +83,7 @@ class Plan:
         T, k = idx.shape
         dev = idx.device
         self.T, self.k, self.E = T, k, E
+        self.counts = counts
         self.max_rows = (T * k + 127) // 128 * 128 + 128 * E
         self.max_tiles = self.max_rows // 128
         if not idx.is_cuda:
@@ -106,16 +118,27 @@ class Plan:
               "moe_plan")
 
 
+def zero_pads(buf, plan: Plan, segments: bool):
+    """Clears the rows of an expert buffer [max_rows, H] that carry no assignment: the tail past the last segment and,
+    with ``segments``, the padding behind every expert's rows.  (Cheaper than zero-filling the whole buffer, and the
+    weight-gradient products sum over padded segments, so those rows must be zero.)"""
+    check(_lib.lib().tfb_moe_zero_pads(buf.data_ptr(), buf.shape[1], plan.seg_start.data_ptr(),
+                                       plan.counts.data_ptr() if segments else None, plan.E, plan.total.data_ptr(), buf.shape[0],
+                                       stream()), "moe_zero_pads")
+    return buf
+
+
 def permute(x, idx, plan: Plan):
     """x [T, H] -> xp [max_rows, H] with every (token, k) row placed in its expert's segment (padding rows 0)."""
     T, H = x.shape
-    xp = torch.zeros((plan.max_rows, H), dtype=x.dtype, device=x.device)
     if not x.is_cuda:
+        xp = torch.zeros((plan.max_rows, H), dtype=x.dtype, device=x.device)
         xp[plan.row_of.reshape(-1).long()] = x.repeat_interleave(plan.k, 0)
         return xp
-    check(_lib.lib().tfb_moe_permute(x.data_ptr(), idx.data_ptr(), plan.cursor.data_ptr(), plan.row_of.data_ptr(),
-                                     plan.token_of_row.data_ptr(), xp.data_ptr(), T, plan.k, H, stream()), "moe_permute")
-    return xp
+    xp = torch.empty((plan.max_rows, H), dtype=x.dtype, device=x.device)
+    check(_lib.lib().tfb_moe_permute2(x.data_ptr(), idx.data_ptr(), plan.cursor.data_ptr(), plan.row_of.data_ptr(),
+                                      plan.token_of_row.data_ptr(), xp.data_ptr(), T, plan.k, H, plan.E, stream()), "moe_permute")
+    return zero_pads(xp, plan, True)
 
 
 def permute_bwd(dxp, plan: Plan):
@@ -153,7 +176,7 @@ def combine_bwd(dy, yp, w, plan: Plan):
         dyp[rows] = (dy.float().repeat_interleave(k, 0) * w.reshape(-1, 1)).to(yp.dtype)
         dw = (dy.float().repeat_interleave(k, 0) * yp[rows].float()).sum(-1).view(T, k)
         return dyp, dw
-    dyp = torch.zeros_like(yp)
+    dyp = zero_pads(torch.empty_like(yp), plan, True) if hasattr(plan, "total") else torch.zeros_like(yp)
     dw = torch.empty((T, k), dtype=torch.float32, device=dy.device)
     check(_lib.lib().tfb_moe_combine_bwd(dy.data_ptr(), yp.data_ptr(), plan.row_of.data_ptr(), w.data_ptr(),
                                          dyp.data_ptr(), dw.data_ptr(), T, k, H, stream()), "moe_combine_bwd")
@@ -175,7 +198,12 @@ def grouped_gemm(xp, w, plan: Plan, b_mn=False):
                 W = w[e].float() if b_mn else w[e].float().t()
                 out[i * 128:(i + 1) * 128] = (xp[i * 128:(i + 1) * 128].float() @ W).to(xp.dtype)
         return out
-    out = torch.zeros((rows, N), dtype=xp.dtype, device=xp.device)
+    # tiles past the last segment are skipped by the kernel: only that tail needs clearing (padding rows inside a segment
+    # are products of zero rows)
+    if hasattr(plan, "total") and N % 8 == 0:
+        out = zero_pads(torch.empty((rows, N), dtype=xp.dtype, device=xp.device), plan, False)
+    else:
+        out = torch.zeros((rows, N), dtype=xp.dtype, device=xp.device)
     g = _Group(1, E, plan.expert_of_tile.data_ptr(), None, w.stride(0), 0)
     check(_grouped_fn()(xp.data_ptr(), xp.stride(0), 0, w.data_ptr(), w.stride(1), int(b_mn), out.data_ptr(),
                         out.stride(0), rows, N, K, 1.0, 0, C.byref(g), _lib.status_word(xp.device).data_ptr(), stream()),
@@ -216,7 +244,7 @@ class MoEFFN(torch.autograd.Function):
     def forward(ctx, x, logits, gate_up, down, k, renorm, act, lb_weight, z_weight):
         T, H = x.shape
         E = gate_up.shape[0]
-        idx, w, probs, counts, lse = router_topk(logits, k, renorm)
+        idx, w, probs, counts, lse, prob_sums, lse_sq = router_topk_stats(logits, k, renorm)
         plan = Plan(idx, counts, E)
         xp = permute(x, idx, plan)
         gu = grouped_gemm(xp, gate_up.data, plan)
@@ -224,7 +252,7 @@ class MoEFFN(torch.autograd.Function):
         yp = grouped_gemm(a, down.data, plan)
         y = combine(yp, w, plan)
         f = counts.float() / float(T * k)
-        aux = lb_weight * E * (f * probs.mean(0)).sum() + z_weight * (lse * lse).mean()
+        aux = (lb_weight * E / T) * (f * prob_sums).sum() + (z_weight / T) * lse_sq[0]
         ctx.save_for_backward(x, xp, gu, a, yp, w, probs, idx, lse, f)
         ctx.plan, ctx.gate_up, ctx.down = plan, gate_up, down
         ctx.cfg = (k, renorm, act, lb_weight, z_weight, E)
