@@ -189,7 +189,7 @@ class MoEModel(DenseModel):
         self.lm_head = self.tok_embeddings if cfg.tie_embeddings else nn.Parameter(torch.empty(V, H, **kw))
         self.mtp_heads = nn.ParameterList()
         self.activation_checkpointing = False
-        self.loss_chunk_tokens = 2048
+        self.loss_chunk_tokens = 9472
         self._rope = None
         self.flat = None
         self.last_aux = None
@@ -215,9 +215,25 @@ class MoEModel(DenseModel):
     def forward_backward(self, ids, labels, loss_scale: float = 1.0, ignore_index: int = -100, label_smoothing=None):
         """Same contract as DenseModel.forward_backward (gradients land in main_grad); returns the CE loss."""
         assert self.flat is not None
+        if label_smoothing is None:
+            label_smoothing = getattr(self, "loss_label_smoothing", 0.0)
+        B, S = ids.shape
         with torch.enable_grad():
-            total, ce, aux = self.loss(ids, labels, ignore_index)
-            (total * loss_scale).backward()
+            # blocks under autograd (block-level nodes); the head runs as in the dense model: chunked LM head with the
+            # cross entropy computed in place, so the full [T, V] logits never exist and no fp32 copy of them is made
+            rope = self.rope(ids.device)
+            h = _EmbedFn.apply(ids, self, self.tok_embeddings)
+            aux = 0.0
+            for blk in self.layers:
+                h, a = blk(h, B, S, rope)
+                aux = aux + a
+            self.last_aux = aux
+            with torch.no_grad():
+                ce, dh = self.head_loss_backward(h.detach(), labels.reshape(-1), loss_scale, ignore_index, label_smoothing)
+            if torch.is_tensor(aux) and aux.requires_grad:
+                torch.autograd.backward([h, aux * loss_scale], [dh, None])
+            else:
+                h.backward(dh)
         # parameters that went through ordinary autograd carry .grad; fold it into main_grad
         for p in self.flat.params_list:
             if p.grad is not None:
