@@ -84,8 +84,16 @@ class TPInferenceEngine(InferenceEngine):
     def _lin(self, x, li, name, w, bias=None, residual=None):
         if self.tp_world == 1 or name not in ("o", "down"):
             return super()._lin(x, li, name, w, bias, residual)
-        y = super()._lin(x, li, name, w, None, None)              # this rank's partial sum
-        y = self._all_reduce(y)
+        M, N = x.shape[0], w.shape[0]
+        st = self.coll.stage_view(x.dtype, M * N) if (self.coll is not None and not self.packed and x.is_cuda) else None
+        if st is not None:
+            # the partial product lands in the staging buffer of the all-reduce and the reduced rows are used where the
+            # kernel leaves them: no copy in, no copy out
+            F.gemm(x, w.data, out=st.view(M, N))
+            self.allreduce_calls += 1
+            y = self.coll.all_reduce_staged(M * N, x.dtype).view(M, N)
+        else:
+            y = self._all_reduce(super()._lin(x, li, name, w, None, None))   # this rank's partial sum, then the sum
         if bias is not None:
             y = y + bias
         return y if residual is None else y + residual

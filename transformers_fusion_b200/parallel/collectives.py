@@ -144,6 +144,26 @@ class SymmCollectives:
             t.copy_(st[: t.numel()].view(t.shape))
         return t
 
+    def stage_view(self, dtype, numel: int):
+        """View of this rank's staging buffer for producers that write their result there directly (saves the copy-in of
+        all_reduce); None when ``numel`` does not fit or is not a whole number of 16-byte x world granules."""
+        esz = torch.empty(0, dtype=dtype).element_size()
+        if numel * esz > self.capacity or (numel * esz) % (16 * self.world):
+            return None
+        return self.stage.view(dtype, numel)
+
+    def all_reduce_staged(self, numel: int, dtype, op="sum") -> torch.Tensor:
+        """All-reduce of data already in the staging buffer (see stage_view).  Returns a flat tensor holding the result:
+        a fresh buffer for the one-shot form, the staging buffer itself for the two-shot form (consume it before the next
+        collective)."""
+        esz = torch.empty(0, dtype=dtype).element_size()
+        if numel * esz <= self.one_shot_max_bytes:
+            out = torch.empty(numel, dtype=dtype, device=self.symm.device)
+            self._run(out, numel, dtype, op, 0, max_ctas=8)
+            return out
+        self._run(None, numel, dtype, op, 1)
+        return self.stage.view(dtype, numel)
+
     def reduce_scatter(self, t: torch.Tensor, op="sum") -> torch.Tensor:
         n = self._padded(t)
         assert n == t.numel(), "reduce_scatter needs numel * elem_size to be a multiple of 16 * world"
