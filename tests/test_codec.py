@@ -106,3 +106,37 @@ def test_container_roundtrip_and_corruption(tmp_path):
     (tmp_path / "bad2.quant").write_bytes(b"QUA2" + raw[4:])
     with pytest.raises(ValueError):
         codec.QuantReader(tmp_path / "bad2.quant")
+
+
+def test_index_sidecar_legacy_magics_and_dedup_store(tmp_path):
+    import struct
+
+    import torch
+
+    from transformers_fusion_b200.quant import codec
+    p = str(tmp_path / "m.quant")
+    w = codec.QuantWriter(p, b"cfg")
+    w.add_tensor("a.weight", torch.randn(4, 64))
+    w.add_tensor("b.weight", torch.randn(128))
+    w.close(write_idx=True)
+    ver, entries = codec.read_index(p + ".idx")
+    assert ver == 1 and [n for n, _ in entries] == ["a.weight", "b.weight"] and codec.verify_index(p)
+    body = open(p + ".idx", "rb").read()[len(codec.IDX_MAGICS[0]):]
+    for legacy in codec.IDX_MAGICS[1:]:
+        q = tmp_path / ("legacy_" + legacy.decode() + ".idx")
+        q.write_bytes(legacy + body)
+        assert codec.read_index(str(q))[1] == entries
+    (tmp_path / "bad.idx").write_bytes(b"nope" + body)
+    with pytest.raises(ValueError):
+        codec.read_index(str(tmp_path / "bad.idx"))
+    (tmp_path / "trail.idx").write_bytes(codec.IDX_MAGICS[0] + body + b"x")
+    with pytest.raises(ValueError):
+        codec.read_index(str(tmp_path / "trail.idx"))
+    st = codec.DedupStore(str(tmp_path / "blobs"))
+    t = torch.arange(10.)
+    k1, k2, k3 = st.write_tensor(t), st.write_tensor(t.clone()), st.write_dedup(b"other")
+    assert k1 == k2 != k3 and (st.writes, st.hits) == (2, 1) and st.read(k3) == b"other"
+    assert st.read(k1) == struct.pack("<10f", *range(10))
+    open(str(tmp_path / "blobs" / k3), "wb").write(b"tampered")
+    with pytest.raises(ValueError):
+        st.read(k3)

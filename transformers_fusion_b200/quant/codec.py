@@ -241,3 +241,75 @@ def load_model(path, device="cpu", dtype=torch.float32, model_cls=None, strict=T
                 raise ValueError(f"{name}: {src.numel()} weights in file, {dst.numel()} expected")
             dst.copy_(src.view(dst.shape).to(dst.dtype))
     return model
+
+
+# ------------------------------------------------------------------------------------------------ index side-car, dedup store
+IDX_MAGICS = (b"TransFormers-FusionIDX", b"TransCenderIDX", b"InNovaIDX")      # current, then the two legacy spellings
+
+
+def read_index(path: str):
+    """Parses ``<model>.quant.idx``: magic | u32 version | u32 n | per tensor {u16 len, name, sha256(name)}.  Accepts the
+    current magic and both legacy ones.  Returns (version, [(name, digest)])."""
+    import struct
+    data = open(path, "rb").read()
+    magic = next((m for m in IDX_MAGICS if data.startswith(m)), None)
+    if magic is None:
+        raise ValueError(f"{path}: not a tensor index")
+    off = len(magic)
+    ver, n = struct.unpack_from("<II", data, off)
+    off += 8
+    out = []
+    for _ in range(n):
+        (ln,) = struct.unpack_from("<H", data, off)
+        off += 2
+        name = data[off:off + ln].decode("utf-8")
+        off += ln
+        out.append((name, data[off:off + 32]))
+        off += 32
+    if off != len(data):
+        raise ValueError(f"{path}: {len(data) - off} trailing bytes")
+    return ver, out
+
+
+def verify_index(quant_path: str) -> bool:
+    """The side-car lists exactly the tensors of the container, in order, with sha256(name) digests."""
+    _, entries = read_index(quant_path + ".idx")
+    with QuantReader(quant_path) as r:
+        names = r.tensor_names()
+    return [n for n, _ in entries] == list(names) and all(sha256(n.encode()) == d for n, d in entries)
+
+
+class DedupStore:
+    """Content-addressed blob store: ``write_dedup`` keeps one copy of identical payloads (tied embeddings, repeated
+    experts after upcycling, shared codebooks) under ``<dir>/<sha256 hex>`` and returns the digest.
+    Reference counterpart: QUANTWriter::write_dedup (sha256 content addressing, src/codec/quant_format.cpp)."""
+
+    def __init__(self, directory: str):
+        import os
+        self.dir = directory
+        os.makedirs(directory, exist_ok=True)
+        self.writes = self.hits = 0
+
+    def write_dedup(self, payload: bytes) -> str:
+        import os
+        key = sha256(payload).hex()
+        p = os.path.join(self.dir, key)
+        if os.path.exists(p):
+            self.hits += 1
+        else:
+            tmp = p + ".tmp"
+            with open(tmp, "wb") as f:
+                f.write(payload)
+            os.replace(tmp, p)
+            self.writes += 1
+        return key
+
+    def read(self, key: str) -> bytes:
+        import os
+        data = open(os.path.join(self.dir, key), "rb").read()
+        if sha256(data).hex() != key:
+            raise ValueError(f"blob {key} is corrupt")
+        return data
+
+    def write_tensor(self, t: torch.Tensor) -> str:
+        return self.write_dedup(t.detach().contiguous().cpu().numpy().tobytes())
