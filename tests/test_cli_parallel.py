@@ -55,3 +55,14 @@ def test_train_cli_meshes(tmp_path, name, flags):
 def test_train_cli_rejects_bad_mesh(tmp_path):
     r, _ = _train(tmp_path, "bad", ["--tp", "3"])
     assert r.returncode != 0 and "does not divide" in (r.stdout + r.stderr)
+
+
+@pytest.mark.parametrize("name,flags", [("dp2tp2", ["--tp", "2", "--dp", "2"]), ("dp2pp2", ["--pp", "2", "--dp", "2"])])
+def test_train_cli_two_dimensional_meshes(tmp_path, name, flags):
+    """Four gloo ranks: data parallel x tensor parallel and data parallel x pipeline (the groups of mesh_groups in use)."""
+    r, model = _train(tmp_path, name, flags, nproc=4)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    steps = [l for l in r.stdout.splitlines() if l.startswith("Step ")]
+    first, last = (float(l.split("loss:")[1].split("|")[0]) for l in (steps[0], steps[-1]))
+    assert last < first and os.path.exists(model)
+    assert "dp=2" in r.stdout
