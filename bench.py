@@ -30,7 +30,7 @@ SEQ = 1024
 
 def reference_arm(args):
     """The reference is a CPU-only C++/CMake project with no Python packaging: the prescribed
-    ``pip install --target baseline/_ref /root/reference`` fails ("neither setup.py nor
+    ``pip install --target baseline/_ref <reference tree>`` fails ("neither setup.py nor
     pyproject.toml found"), and its own trainer runs ~8 tokens/s at this model size on one core, so a
     single 65,536-token step would take hours."""
     print(json.dumps({"impl": "reference",
