@@ -72,3 +72,31 @@ def test_moe_gpu_matches_cpu():
     for a, b, name in zip(outs[0], outs[1], ("y", "aux", "dx", "dlogits", "dgate_up", "ddown")):
         tol = 3e-2 * a.abs().max().item() + 1e-3
         assert (a - b).abs().max().item() < tol, (name, (a - b).abs().max().item(), a.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_router_stats_and_pad_zeroing_gpu():
+    """The router kernel's block-aggregated reductions equal the torch reductions; permute leaves every unassigned row of
+    the expert buffer zero (padding behind each segment and the tail) without a whole-buffer fill."""
+    from transformers_fusion_b200.ops import moe as M
+    torch.manual_seed(0)
+    T, E, k, H = 3000, 16, 2, 64
+    logits = torch.randn(T, E, device="cuda").bfloat16()
+    idx, w, probs, counts, lse, psum, lsq = M.router_topk_stats(logits, k, True)
+    assert int(counts.sum()) == T * k
+    assert torch.equal(counts.cpu(), torch.bincount(idx.reshape(-1).long().cpu(), minlength=E).int())
+    assert torch.allclose(psum, probs.sum(0), rtol=1e-4, atol=1e-3)
+    assert torch.allclose(lsq[0], (lse * lse).sum(), rtol=1e-4)
+    plan = M.Plan(idx, counts, E)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    xp = M.permute(x, idx, plan)
+    rows = plan.row_of.reshape(-1).long()
+    assert rows.unique().numel() == T * k                                  # every assignment has its own row
+    assert torch.equal(xp[rows], x.repeat_interleave(k, 0))
+    mask = torch.ones(plan.max_rows, dtype=torch.bool, device="cuda")
+    mask[rows] = False
+    assert float(xp[mask].abs().sum()) == 0.0
+    seg = plan.seg_start.cpu().tolist()
+    for e in range(E):                                                     # rows of expert e lie inside its segment
+        r = rows[(idx.reshape(-1) == e)]
+        assert r.numel() == int(counts[e]) and (r.numel() == 0 or (int(r.min()) >= seg[e] and int(r.max()) < seg[e] + int(counts[e])))
