@@ -186,6 +186,19 @@ class InferenceEngine:
         y = self._wq.gemm_wq(x, pw, bias)
         return y if residual is None else y + residual
 
+    def _ffn(self, li, w, f, base):
+        """Feed-forward half of a block on normed rows ``f`` with residual ``base``: the dense GLU / MLP, or - for a
+        mixture-of-experts block - router, top-k dispatch, grouped expert GEMMs and weighted combine."""
+        mc = self.model.cfg
+        if hasattr(w, "router"):
+            y, _ = w.moe(f)
+            if mc.variant.upper() == "RESIDUAL_MOE":
+                y = y + f
+            return base + y
+        gu = self._lin(f, li, "gate_up", w.gate_up, getattr(w, "gate_up_bias", None))
+        act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
+        return self._lin(act, li, "down", w.down, getattr(w, "down_bias", None), base)
+
     # ------------------------------------------------------------------ request management
     def add_request(self, tokens, max_tokens=64, sampling: Optional[SamplerConfig] = None, priority=0,
                     deadline=float("inf"), stop_ids=(), on_token=None) -> Request:
@@ -221,8 +234,8 @@ class InferenceEngine:
         slots = torch.tensor([r.pages[p // PAGE] * PAGE + p % PAGE for p in range(pos0, pos0 + S)], dtype=torch.int64,
                              device=dev)
         for li, w in enumerate(m.layers):
-            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
-            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
+            a, _ = _norm_fwd(mc, h, w.attention_norm, getattr(w, "attention_norm_bias", None))
+            qkv = self._lin(a, li, "qkv", w.qkv, getattr(w, "qkv_bias", None))
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
@@ -236,15 +249,13 @@ class InferenceEngine:
                 lens = (positions + 1).to(torch.int32)
                 o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), bt, lens, Hq)
             if mc.use_parallel_residual:
-                attn = self._lin(o, li, "o", w.o, w.o_bias)
-                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                attn = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None))
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
                 base = h
             else:
-                base = self._lin(o, li, "o", w.o, w.o_bias, h)
-                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
-            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
-            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
-            h = self._lin(act, li, "down", w.down, w.down_bias, base)
+                base = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None), h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
+            h = self._ffn(li, w, f, base)
             if mc.use_parallel_residual:
                 h = h + attn
         return h if all_positions else h[-1:]
@@ -272,22 +283,20 @@ class InferenceEngine:
         rope = m.rope(dev)
         positions = torch.arange(S, dtype=torch.int32, device=dev).repeat(B)
         for li, w in enumerate(m.layers):
-            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
-            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
+            a, _ = _norm_fwd(mc, h, w.attention_norm, getattr(w, "attention_norm_bias", None))
+            qkv = self._lin(a, li, "qkv", w.qkv, getattr(w, "qkv_bias", None))
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, S, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
             o, _ = F.attn_fwd(qkv, qkv, qkv, B, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
             if mc.use_parallel_residual:
-                attn = self._lin(o, li, "o", w.o, w.o_bias)
-                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                attn = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None))
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
                 base = h
             else:
-                base = self._lin(o, li, "o", w.o, w.o_bias, h)
-                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
-            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
-            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
-            h = self._lin(act, li, "down", w.down, w.down_bias, base)
+                base = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None), h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
+            h = self._ffn(li, w, f, base)
             if mc.use_parallel_residual:
                 h = h + attn
         last = torch.tensor([b * S + len(r.tokens) - 1 for b, r in enumerate(reqs)], dtype=torch.int64, device=dev)
@@ -333,22 +342,20 @@ class InferenceEngine:
         rope = m.rope(self.device)
         lens = (positions + 1).to(torch.int32)
         for li, w in enumerate(m.layers):
-            a, _ = _norm_fwd(mc, h, w.attention_norm, w.attention_norm_bias)
-            qkv = self._lin(a, li, "qkv", w.qkv, w.qkv_bias)
+            a, _ = _norm_fwd(mc, h, w.attention_norm, getattr(w, "attention_norm_bias", None))
+            qkv = self._lin(a, li, "qkv", w.qkv, getattr(w, "qkv_bias", None))
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, 1, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
             o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), block_table, lens, Hq)
             if mc.use_parallel_residual:
-                attn = self._lin(o, li, "o", w.o, w.o_bias)
-                f, _ = _norm_fwd(mc, h, w.ffn_norm, w.ffn_norm_bias)
+                attn = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None))
+                f, _ = _norm_fwd(mc, h, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
                 base = h
             else:
-                base = self._lin(o, li, "o", w.o, w.o_bias, h)
-                f, _ = _norm_fwd(mc, base, w.ffn_norm, w.ffn_norm_bias)
-            gu = self._lin(f, li, "gate_up", w.gate_up, w.gate_up_bias)
-            act = F.glu_fwd(gu, mc.act_kernel) if mc.gated else F.act_fwd(gu, mc.act_kernel)
-            h = self._lin(act, li, "down", w.down, w.down_bias, base)
+                base = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None), h)
+                f, _ = _norm_fwd(mc, base, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
+            h = self._ffn(li, w, f, base)
             if mc.use_parallel_residual:
                 h = h + attn
         return h
