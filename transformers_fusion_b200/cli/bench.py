@@ -171,7 +171,13 @@ def serve_bench(a):
         dist.init_process_group("nccl", device_id=dev)
         symm = SymmetricHeap(rank, world, dev)
     cfg = preset(a.preset)
-    model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
+    if a.layers > 0:
+        cfg.num_layers = a.layers
+    if hasattr(cfg, "num_experts"):
+        from ..models.moe import MoEModel
+        model = MoEModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
+    else:
+        model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
     g = torch.Generator().manual_seed(0)
     for B in [int(x) for x in a.batch.split(",")]:
         pages = (a.prompt_len + a.gen + 31) // 16 * B + 64
@@ -192,7 +198,7 @@ def serve_bench(a):
             torch.cuda.synchronize()
             dt = time.perf_counter() - t0
         out_tokens = sum(len(r.out) for r in reqs)
-        rec = {"bench": "serve", "preset": a.preset, "batch": B, "prompt_len": a.prompt_len, "gen": a.gen, "weights": a.weights or "bf16",
+        rec = {"bench": "serve", "preset": a.preset, "layers": cfg.num_layers, "batch": B, "prompt_len": a.prompt_len, "gen": a.gen, "weights": a.weights or "bf16",
                "kv": a.kv, "tp": world, "cuda_graph": eng.cfg.cuda_graph, "out_tok_s": round(out_tokens / dt, 1),
                "ttft_ms_p50": round(statistics.median((r.t_first - r.t_submit) * 1e3 for r in reqs), 2),
                "decode_ms_per_step": round((eng.stats.decode_ms - d0) / max(1, steps), 3), "total_ms": round(dt * 1e3, 1)}
@@ -219,6 +225,7 @@ def main(argv=None):
     ap.add_argument("--weights", default="", help="packed weight format for --serve: int8 | int4 | mxfp8 | fp4 | ternary")
     ap.add_argument("--kv", default="bf16", help="KV cache storage for --serve: bf16 | fp8 | q4")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="--serve: override the preset's layer count (fits big shapes on one GPU)")
     ap.add_argument("--model", default="")
     ap.add_argument("--prompt", default="test")
     add_int(ap, "--iters", 20)
