@@ -41,12 +41,16 @@ class _LinearAG(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
+        if w.shape[0] % 8:                       # rows of [T, N] must be 16-byte multiples for the TMA path (e.g. 4 experts)
+            return x @ w.t()
         return F.gemm(x, w)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
+        if w.shape[0] % 8:
+            return dy @ w, (dy.float().t() @ x.float()).to(w.dtype)
         dx = F.gemm(dy, w, b_mn=True)
         dw = F.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
         return dx, dw.to(w.dtype)

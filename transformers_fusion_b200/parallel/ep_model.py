@@ -1,0 +1,80 @@
+"""Expert-parallel training of the MoE model: every rank keeps the attention / norm / router / embedding weights
+(replicated, data parallel) and E / W of the experts of every layer; tokens travel to the experts' owners and back
+through the fused dispatch / combine kernels over NVLink peer memory (``parallel.ep.ExpertParallel``).
+
+Gradients: replicated tensors are averaged over the ranks; an expert's weights see the tokens of all ranks already, so
+their gradients are only divided by the world size (each rank's loss is the mean over its own tokens, the objective is
+the mean over ranks).
+
+Reference counterparts: ExpertParallel (round-robin experts, replicated tokens, all-reduce combine;
+src/model/moe_model.cpp:508-700), ExpertParallelManager / assign_experts_to_nodes (src/model/expert_parallel.cpp:319)."""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .ep import ExpertParallel
+
+
+def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int) -> List[nn.Parameter]:
+    """Cuts every MoE block's expert tensors down to this rank's contiguous block of experts, attaches the dispatch /
+    combine object, and rebuilds the flat parameter buffer.  Returns the expert parameters (the rest is replicated)."""
+    cfg = model.cfg
+    E = cfg.num_experts
+    if E % world:
+        raise ValueError("the number of experts must divide by the expert-parallel degree")
+    El = E // world
+    experts = []
+    for blk in model.layers:
+        if not hasattr(blk, "router"):
+            continue
+        blk.gate_up = nn.Parameter(blk.gate_up.data[rank * El:(rank + 1) * El].clone())
+        blk.down = nn.Parameter(blk.down.data[rank * El:(rank + 1) * El].clone())
+        blk.ep = ExpertParallel(symm, rank, world, E, cfg.hidden_size, max_tokens, min(cfg.top_k, 8))
+        experts += [blk.gate_up, blk.down]
+    model.flat = None
+    model.flatten()
+    return experts
+
+
+class EPTrainer:
+    """AdamW (fp32 masters) over the replicated tensors and this rank's experts."""
+
+    def __init__(self, model, expert_params: List[nn.Parameter], lr=3e-4, weight_decay=0.01, max_grad_norm=1.0, group=None):
+        from ..engines.dense import OptimSuite
+        self.model, self.group, self.max_grad_norm = model, group, max_grad_norm
+        ids = {id(p) for p in expert_params}
+        self.experts = list(expert_params)
+        self.shared = [p for p in model.parameters() if id(p) not in ids]
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.opt = OptimSuite("adamw", lr, weight_decay)
+        self.opt.add_group(self.shared, 1.0, 1.0)
+        self.opt.add_group(self.experts, 1.0, 1.0)
+        self.grad_norm = 0.0
+
+    def train_step(self, ids, labels, lr: Optional[float] = None) -> float:
+        m, W = self.model, self.world
+        m.flat.zero_grad()
+        loss = m.forward_backward(ids, labels)
+        if W > 1:
+            for p in self.shared:
+                dist.all_reduce(p.main_grad, group=self.group)
+            for p in m.parameters():
+                p.main_grad.div_(W)
+        sq_e = sum(p.main_grad.pow(2).sum() for p in self.experts).reshape(1)
+        lt = loss.detach().float().reshape(1).clone()
+        if W > 1:
+            dist.all_reduce(sq_e, group=self.group)
+            dist.all_reduce(lt, group=self.group)
+        sq = sq_e[0] + sum(p.main_grad.pow(2).sum() for p in self.shared)
+        self.grad_norm = float(sq.sqrt())
+        if self.max_grad_norm > 0 and self.grad_norm > self.max_grad_norm:
+            for p in m.parameters():
+                p.main_grad.mul_(self.max_grad_norm / (self.grad_norm + 1e-6))
+        if lr is not None:
+            self.opt.set_lr(lr)
+        self.opt.step()
+        return float(lt) / W

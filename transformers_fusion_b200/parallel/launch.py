@@ -7,6 +7,7 @@ fastest (tensor-parallel peers exchange the most data per step), then dp, then p
 
 ``init_parallel`` builds the groups; ``fit_parallel`` runs the training loop that matches the factors:
   tp > 1          TPDenseModel + TPTrainer (fused all-gather->GEMM / GEMM->reduce-scatter), gradients averaged over dp
+  ep > 1          MoE model with the experts of every layer spread over the ranks (fused dispatch / combine), EPTrainer
   pp > 1          PipelineParallel 1F1B over the layer ranges, AdamW on the parameters each stage owns
   zero stage 3    FullyShardedDataParallel (weights gathered inside the consuming GEMM on CUDA)
   otherwise       the ordinary Trainer: data parallel with ZeRO stage 0 / 1 / 2 (fused reduce-scatter + AdamW)
@@ -152,6 +153,21 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
         tpm.gather_into(model)
         if st.is_main:
             Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
+        return loss
+    if st.ep > 1:
+        # expert parallel over all ranks (which are also the data-parallel ranks of the replicated tensors)
+        if st.ep != st.world or not hasattr(model.cfg, "num_experts") or st.device.type != "cuda":
+            raise ValueError("--ep needs a mixture-of-experts model on CUDA and ep equal to the number of ranks")
+        from .ep_model import EPTrainer, attach_expert_parallel
+        from .symm import SymmetricHeap
+        symm = SymmetricHeap(st.rank, st.world, st.device)
+        experts = attach_expert_parallel(model, symm, st.rank, st.world, cfg.batch_size * cfg.seq_length)
+        tr = EPTrainer(model, experts, cfg.learning_rate, cfg.weight_decay, cfg.max_grad_norm)
+        for step in range(1, steps + 1):
+            ids, labels = dl.next_batch()
+            loss = tr.train_step(ids, labels, lr_at(step))
+            toks += ids.numel() * st.world
+            report(step, loss, lr_at(step), toks, t0)
         return loss
     if st.pp > 1:
         from ..engines.dense import OptimSuite
