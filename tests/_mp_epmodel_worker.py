@@ -47,6 +47,7 @@ def main():
     El = res["local_experts"]
     ge, gf = model.layers[0].down.main_grad, full.layers[0].down.main_grad[rank * El:(rank + 1) * El]
     res["g_down_has_remote_tokens"] = float((ge - gf).abs().max()) > 0      # the owner also sees the other rank's tokens
+    model.flat.zero_grad()                      # the optimiser step leaves the gradients zeroed; start from that state
     losses = [tr.train_step(ids, labels) for _ in range(8)]
     res["losses"] = losses
     w = model.layers[0].qkv.data.float()

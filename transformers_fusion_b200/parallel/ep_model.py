@@ -41,40 +41,38 @@ def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int) 
 
 
 class EPTrainer:
-    """AdamW (fp32 masters) over the replicated tensors and this rank's experts."""
+    """Fused AdamW (fp32 masters, one kernel over the flat buffer) over the replicated tensors and this rank's experts.
+    The clipping norm is global: the replicated part once plus every rank's expert part."""
 
     def __init__(self, model, expert_params: List[nn.Parameter], lr=3e-4, weight_decay=0.01, max_grad_norm=1.0, group=None):
-        from ..engines.dense import OptimSuite
-        self.model, self.group, self.max_grad_norm = model, group, max_grad_norm
+        from ..trainer.fused_optim import FlatAdamW
+        self.model, self.group = model, group
         ids = {id(p) for p in expert_params}
         self.experts = list(expert_params)
         self.shared = [p for p in model.parameters() if id(p) not in ids]
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.opt = OptimSuite("adamw", lr, weight_decay)
-        self.opt.add_group(self.shared, 1.0, 1.0)
-        self.opt.add_group(self.experts, 1.0, 1.0)
-        self.grad_norm = 0.0
+        self.opt = FlatAdamW(model.flat, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
+                             norm_reduce=self._norm_reduce if self.world > 1 else None)
+
+    def _norm_reduce(self, sumsq):
+        """sumsq holds this rank's total (replicated + own experts); add the other ranks' expert parts."""
+        own = torch.stack([p.main_grad.pow(2).sum() for p in self.experts]).sum().reshape(1)
+        tot = own.clone()
+        dist.all_reduce(tot, group=self.group)
+        sumsq.add_(tot - own)
+
+    @property
+    def grad_norm(self) -> float:
+        return float(self.opt.grad_norm)
 
     def train_step(self, ids, labels, lr: Optional[float] = None) -> float:
         m, W = self.model, self.world
-        m.flat.zero_grad()
         loss = m.forward_backward(ids, labels)
+        lt = loss.detach().float().reshape(1).clone()
         if W > 1:
             for p in self.shared:
                 dist.all_reduce(p.main_grad, group=self.group)
-            for p in m.parameters():
-                p.main_grad.div_(W)
-        sq_e = sum(p.main_grad.pow(2).sum() for p in self.experts).reshape(1)
-        lt = loss.detach().float().reshape(1).clone()
-        if W > 1:
-            dist.all_reduce(sq_e, group=self.group)
+            m.flat.grads.div_(W)
             dist.all_reduce(lt, group=self.group)
-        sq = sq_e[0] + sum(p.main_grad.pow(2).sum() for p in self.shared)
-        self.grad_norm = float(sq.sqrt())
-        if self.max_grad_norm > 0 and self.grad_norm > self.max_grad_norm:
-            for p in m.parameters():
-                p.main_grad.mul_(self.max_grad_norm / (self.grad_norm + 1e-6))
-        if lr is not None:
-            self.opt.set_lr(lr)
-        self.opt.step()
+        self.opt.step(lr)                                   # clips, updates, refreshes the bf16 weights, zeroes the gradients
         return float(lt) / W
