@@ -186,8 +186,9 @@ def combine_bwd(dy, yp, w, plan: Plan):
 # ---------------------------------------------------------------------------------------------
 # grouped GEMMs
 # ---------------------------------------------------------------------------------------------
-def grouped_gemm(xp, w, plan: Plan, b_mn=False):
-    """xp [rows, K] @ w[e]^T per 128-row tile.  w is [E, N, K] (b_mn False) or [E, K, N] (b_mn True)."""
+def grouped_gemm(xp, w, plan: Plan, b_mn=False, out=None):
+    """xp [rows, K] @ w[e]^T per 128-row tile.  w is [E, N, K] (b_mn False) or [E, K, N] (b_mn True).  ``out``
+    (CUDA only): a [rows, N] buffer to write into, e.g. a symmetric-memory buffer that peers read next."""
     rows, K = xp.shape
     E = w.shape[0]
     N = w.shape[2] if b_mn else w.shape[1]
@@ -200,7 +201,10 @@ def grouped_gemm(xp, w, plan: Plan, b_mn=False):
         return out
     # tiles past the last segment are skipped by the kernel: only that tail needs clearing (padding rows inside a segment
     # are products of zero rows)
-    if hasattr(plan, "total") and N % 8 == 0:
+    if out is not None:
+        assert out.shape == (rows, N) and out.dtype == xp.dtype and hasattr(plan, "total") and N % 8 == 0
+        zero_pads(out, plan, False)
+    elif hasattr(plan, "total") and N % 8 == 0:
         out = zero_pads(torch.empty((rows, N), dtype=xp.dtype, device=xp.device), plan, False)
     else:
         out = torch.zeros((rows, N), dtype=xp.dtype, device=xp.device)

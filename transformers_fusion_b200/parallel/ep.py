@@ -95,7 +95,7 @@ class _EpFFN(torch.autograd.Function):
         xp_saved = xp.clone()
         gu = M.grouped_gemm(xp_saved, gate_up.data, pl)
         a = F.glu_fwd(gu, act)
-        yp.copy_(M.grouped_gemm(a, down.data, pl))
+        M.grouped_gemm(a, down.data, pl, out=yp)        # straight into the buffer the sources read in combine
         ep.symm.barrier()                              # expert outputs are readable by the sources
         y = torch.empty((T, H), dtype=x.dtype, device=dev)
         check(lib.tfb_ep_combine(ep.yp.ptrs.data_ptr(), idx.data_ptr(), pl.row_of.data_ptr(), w.data_ptr(), y.data_ptr(),
@@ -133,7 +133,7 @@ class _EpFFN(torch.autograd.Function):
         da = M.grouped_gemm(dyp, down.data, pl, b_mn=True)
         M.grouped_wgrad(dyp, a, pl, down.main_grad)
         dgu = F.glu_bwd(gu, da, act)
-        yp_sym.copy_(M.grouped_gemm(dgu, gate_up.data, pl, b_mn=True))   # dxp, exposed through the yp buffer
+        M.grouped_gemm(dgu, gate_up.data, pl, b_mn=True, out=yp_sym)     # dxp, exposed through the yp buffer
         M.grouped_wgrad(dgu, xp_saved, pl, gate_up.main_grad)
         ep.symm.barrier()                               # dxp rows are readable by the sources
         dx = torch.empty((T, H), dtype=x.dtype, device=dev)

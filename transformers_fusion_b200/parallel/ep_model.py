@@ -51,15 +51,38 @@ class EPTrainer:
         self.experts = list(expert_params)
         self.shared = [p for p in model.parameters() if id(p) not in ids]
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._runs = None
         self.opt = FlatAdamW(model.flat, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
                              norm_reduce=self._norm_reduce if self.world > 1 else None)
 
+    def _shared_runs(self):
+        """The replicated tensors' gradients as maximal contiguous slices of the flat gradient buffer, so that the
+        all-reduce count is the number of runs between expert tensors, not the number of tensors."""
+        if self._runs is None:
+            flat = self.model.flat.grads
+            base, esz = flat.data_ptr(), flat.element_size()
+            spans = sorted(((p.main_grad.data_ptr() - base) // esz, p.main_grad.numel()) for p in self.shared)
+            taken = sorted((p.main_grad.data_ptr() - base) // esz for p in self.experts)
+            runs = []
+            for off, n in spans:
+                assert 0 <= off and off + n <= flat.numel()
+                end = runs[-1][0] + runs[-1][1] if runs else -1
+                # alignment padding between two replicated tensors is zero on every rank: the run may span it
+                if runs and off >= end and not any(end <= t < off for t in taken) and off - end < 4096:
+                    runs[-1][1] = off + n - runs[-1][0]
+                else:
+                    runs.append([off, n])
+            self._runs = [flat[o:o + n] for o, n in runs]
+        return self._runs
+
     def _norm_reduce(self, sumsq):
-        """sumsq holds this rank's total (replicated + own experts); add the other ranks' expert parts."""
+        """sumsq holds this rank's total (replicated + own experts); the result is replicated + every rank's experts.
+        Both terms come out of one all-reduce, so every rank gets the same bits and hence the same clipping factor
+        (a rank-local sum would differ in rounding and let the replicated weights drift apart)."""
         own = torch.stack([p.main_grad.pow(2).sum() for p in self.experts]).sum().reshape(1)
-        tot = own.clone()
-        dist.all_reduce(tot, group=self.group)
-        sumsq.add_(tot - own)
+        v = torch.cat([sumsq.reshape(1) - own, own])
+        dist.all_reduce(v, group=self.group)
+        sumsq.copy_((v[0] / self.world + v[1]).reshape(sumsq.shape))
 
     @property
     def grad_norm(self) -> float:
@@ -70,8 +93,8 @@ class EPTrainer:
         loss = m.forward_backward(ids, labels)
         lt = loss.detach().float().reshape(1).clone()
         if W > 1:
-            for p in self.shared:
-                dist.all_reduce(p.main_grad, group=self.group)
+            for g in self._shared_runs():
+                dist.all_reduce(g, group=self.group)
             m.flat.grads.div_(W)
             dist.all_reduce(lt, group=self.group)
         self.opt.step(lr)                                   # clips, updates, refreshes the bf16 weights, zeroes the gradients
