@@ -16,6 +16,8 @@
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
+TFB_BOUNDS_DEFINE(moe_routing)
+
 namespace tfb {
 
 constexpr int MAX_E = 256;
@@ -188,7 +190,10 @@ __global__ void __launch_bounds__(256) moe_zero_pads_kernel(__nv_bfloat16* __res
     r0 = *total;
     r1 = max_rows;
   }
+  // grid.y is sized for a tail of many thousand rows (an expert-parallel buffer is provisioned for the worst-case
+  // imbalance); blocks beyond the range leave at once
   const long long n8 = (long long)(r1 - r0) * H / 8;
+  if (blockIdx.y * (long long)blockDim.x >= n8) return;
   uint4* p = reinterpret_cast<uint4*>(buf + (long long)r0 * H);
   for (long long i = blockIdx.y * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.y * blockDim.x)
     p[i] = make_uint4(0, 0, 0, 0);
@@ -333,7 +338,7 @@ TFB_API int tfb_moe_permute2(const void* x, const int* topk_idx, int* cursor, in
 TFB_API int tfb_moe_zero_pads(void* buf, int H, const int* seg_start, const int* counts, int E, const int* total, int max_rows,
                               void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  moe_zero_pads_kernel<<<dim3(E + 1, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(buf), H, seg_start,
+  moe_zero_pads_kernel<<<dim3(E + 1, 296), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(buf), H, seg_start,
                                                                                       counts, E, total, max_rows);
   return int(cudaGetLastError());
 }

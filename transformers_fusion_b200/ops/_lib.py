@@ -61,11 +61,11 @@ def lib_path() -> Path:
 
 def bounds_report(reset: bool = True) -> dict:
     """Bounds-check build only: {unit: (count, site, index, limit)} of the first out-of-range index each unit saw
-    (sites: 1 embedding id, 2 embedding-gradient id, 3 cross-entropy label)."""
+    (sites: 1 embedding id, 2 embedding-gradient id, 3 cross-entropy label, 5 routed expert id)."""
     out = {}
     if not bounds_check_build():
         return out
-    for unit in ("elementwise", "loss_optim"):
+    for unit in ("elementwise", "loss_optim", "moe_routing"):
         fn = getattr(lib(), f"tfb_bounds_report_{unit}")
         fn.argtypes, fn.restype = [c_p, c_i], c_i
         buf = (C.c_ulonglong * 4)()
