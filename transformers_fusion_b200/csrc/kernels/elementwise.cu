@@ -80,9 +80,11 @@ __device__ __forceinline__ float act_grad(float g, int act) {
   }
 }
 
+// `rows_dev` (optional): a device-side row count below M, e.g. the routed rows of an expert buffer provisioned for more.
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long M,
-                               int F, int act) {
+                               int F, int act, const int* __restrict__ rows_dev) {
   const int vec = F >> 3;
+  if (rows_dev) M = min(M, (long long)max(*rows_dev, 0));
   const long long total = M * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -105,8 +107,10 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat
 
 // din [M, 2F] = [dout * up * act'(gate) | dout * act(gate)]
 __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
-                               __nv_bfloat16* __restrict__ din, long long M, int F, int act) {
+                               __nv_bfloat16* __restrict__ din, long long M, int F, int act,
+                               const int* __restrict__ rows_dev) {
   const int vec = F >> 3;
+  if (rows_dev) M = min(M, (long long)max(*rows_dev, 0));
   const long long total = M * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -251,18 +255,25 @@ TFB_API int tfb_rope(void* x, const float* cos_t, const float* sin_t, const int*
   return int(cudaGetLastError());
 }
 
-TFB_API int tfb_glu_fwd(const void* in, void* out, long long M, int F, int act, void* stream) {
+TFB_API int tfb_glu_fwd_rows(const void* in, void* out, long long M, int F, int act, const int* rows_dev, void* stream) {
   if (F % 8) return TFB_ERR_ARG;
   glu_fwd_kernel<<<grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), M, F, act);
+      static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), M, F, act, rows_dev);
   return int(cudaGetLastError());
 }
-TFB_API int tfb_glu_bwd(const void* in, const void* dout, void* din, long long M, int F, int act, void* stream) {
+TFB_API int tfb_glu_fwd(const void* in, void* out, long long M, int F, int act, void* stream) {
+  return tfb_glu_fwd_rows(in, out, M, F, act, nullptr, stream);
+}
+TFB_API int tfb_glu_bwd_rows(const void* in, const void* dout, void* din, long long M, int F, int act, const int* rows_dev,
+                             void* stream) {
   if (F % 8) return TFB_ERR_ARG;
   glu_bwd_kernel<<<grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(din),
-      M, F, act);
+      M, F, act, rows_dev);
   return int(cudaGetLastError());
+}
+TFB_API int tfb_glu_bwd(const void* in, const void* dout, void* din, long long M, int F, int act, void* stream) {
+  return tfb_glu_bwd_rows(in, dout, din, M, F, act, nullptr, stream);
 }
 TFB_API int tfb_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
   if (n % 8) return TFB_ERR_ARG;

@@ -32,6 +32,8 @@ _SIGS = {
     "tfb_rope": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_ll, c_i, c_p],
     "tfb_glu_fwd": [c_p, c_p, c_ll, c_i, c_i, c_p],
     "tfb_glu_bwd": [c_p, c_p, c_p, c_ll, c_i, c_i, c_p],
+    "tfb_glu_fwd_rows": [c_p, c_p, c_ll, c_i, c_i, c_p, c_p],
+    "tfb_glu_bwd_rows": [c_p, c_p, c_p, c_ll, c_i, c_i, c_p, c_p],
     "tfb_act_fwd": [c_p, c_p, c_ll, c_i, c_p],
     "tfb_act_bwd": [c_p, c_p, c_p, c_ll, c_i, c_p],
     "tfb_embedding_fwd": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p],

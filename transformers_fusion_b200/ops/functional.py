@@ -227,18 +227,20 @@ def rope_(x, cos, sin, n_heads, head_dim, seq_len, pos_offset=0, positions=None,
 # ---------------------------------------------------------------------------------------------
 # activations
 # ---------------------------------------------------------------------------------------------
-def glu_fwd(x, act="silu"):
-    """x [M, 2F] = [gate | up] -> act(gate) * up."""
+def glu_fwd(x, act="silu", rows=None):
+    """x [M, 2F] = [gate | up] -> act(gate) * up.  ``rows`` (CUDA): a 1-element int32 device tensor; only the first
+    ``rows`` rows are computed (the rest of the result is left unwritten)."""
     M, F2 = x.shape
     Fh = F2 // 2
     if not x.is_cuda:
         return (_act_ref(x[:, :Fh].float(), act) * x[:, Fh:].float()).to(x.dtype)
     out = torch.empty((M, Fh), dtype=x.dtype, device=x.device)
-    check(_lib.lib().tfb_glu_fwd(x.data_ptr(), out.data_ptr(), M, Fh, ACT[act], stream()), "glu_fwd")
+    check(_lib.lib().tfb_glu_fwd_rows(x.data_ptr(), out.data_ptr(), M, Fh, ACT[act],
+                                      rows.data_ptr() if rows is not None else None, stream()), "glu_fwd")
     return out
 
 
-def glu_bwd(x, dout, act="silu"):
+def glu_bwd(x, dout, act="silu", rows=None):
     M, F2 = x.shape
     Fh = F2 // 2
     if not x.is_cuda:
@@ -250,7 +252,8 @@ def glu_bwd(x, dout, act="silu"):
         d = dout.float()
         return torch.cat([d * u * ga, d * a.detach()], 1).to(x.dtype)
     din = torch.empty_like(x)
-    check(_lib.lib().tfb_glu_bwd(x.data_ptr(), dout.data_ptr(), din.data_ptr(), M, Fh, ACT[act], stream()), "glu_bwd")
+    check(_lib.lib().tfb_glu_bwd_rows(x.data_ptr(), dout.data_ptr(), din.data_ptr(), M, Fh, ACT[act],
+                                      rows.data_ptr() if rows is not None else None, stream()), "glu_bwd")
     return din
 
 

@@ -94,7 +94,7 @@ class _EpFFN(torch.autograd.Function):
         ep.symm.barrier()                              # every token row has reached its owner
         xp_saved = xp.clone()
         gu = M.grouped_gemm(xp_saved, gate_up.data, pl)
-        a = F.glu_fwd(gu, act)
+        a = F.glu_fwd(gu, act, rows=pl.total)          # only the routed rows; the provisioned tail is never read
         M.grouped_gemm(a, down.data, pl, out=yp)        # straight into the buffer the sources read in combine
         ep.symm.barrier()                              # expert outputs are readable by the sources
         y = torch.empty((T, H), dtype=x.dtype, device=dev)
@@ -132,7 +132,7 @@ class _EpFFN(torch.autograd.Function):
         dyp = xp_sym.clone()
         da = M.grouped_gemm(dyp, down.data, pl, b_mn=True)
         M.grouped_wgrad(dyp, a, pl, down.main_grad)
-        dgu = F.glu_bwd(gu, da, act)
+        dgu = F.glu_bwd(gu, da, act, rows=pl.total)
         M.grouped_gemm(dgu, gate_up.data, pl, b_mn=True, out=yp_sym)     # dxp, exposed through the yp buffer
         M.grouped_wgrad(dgu, xp_saved, pl, gate_up.main_grad)
         ep.symm.barrier()                               # dxp rows are readable by the sources
