@@ -98,6 +98,9 @@ def main(argv=None):
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--model", default="llama-50m")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="sequences per step over all ranks (the headline configuration is the default; other values are "
+                         "for studying one rank's share of a larger job on a single GPU)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
@@ -131,8 +134,9 @@ def main(argv=None):
             symm = SymmetricHeap(rank, world, dev)
 
     cfg = preset(args.model)
-    assert GLOBAL_BATCH % world == 0
-    local_batch = GLOBAL_BATCH // world
+    global_batch = args.global_batch
+    assert global_batch % world == 0
+    local_batch = global_batch // world
     model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
     engine = TrainEngine(model, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0, zero_stage=2,
                          comm=comm, cuda_graph=(not args.no_graph) and comm != "nccl", symm=symm)
@@ -199,7 +203,7 @@ def main(argv=None):
     clocks = sampler.stop() if rank == 0 else None
     _lib.check_status(dev)
 
-    tokens = GLOBAL_BATCH * SEQ * args.steps
+    tokens = global_batch * SEQ * args.steps
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     if rank == 0:
@@ -208,7 +212,7 @@ def main(argv=None):
             "warmup": W, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids; random-init weights)",
             "impl": "ours" if args.impl == "ours" else "ours-nccl-baseline",
-            "config": {"model": MODEL, "global_batch": GLOBAL_BATCH, "seq_len": SEQ,
+            "config": {"model": MODEL, "global_batch": global_batch, "seq_len": SEQ,
                        "parallelism": f"dp{world}-zero2" if world > 1 else "single",
                        "optimizer": "AdamW fp32 master", "comm": comm, "cuda_graph": engine.cuda_graph,
                        "l2": "per-step working set (activations + logits, several GB) exceeds the 126 MB L2; "
