@@ -28,9 +28,10 @@ def main():
     GU = (torch.randn(E, 2 * Fh, H, generator=g) * 0.05).bfloat16()
     DN = (torch.randn(E, H, Fh, generator=g) * 0.05).bfloat16()
     DY = torch.randn(world, T, H, generator=g).bfloat16()
-    ep = ExpertParallel(symm, rank, world, E, H, T, k)
+    eps = [ExpertParallel(symm, rank, world, E, H, T, k), ExpertParallel(symm, rank, world, E, H, T, k, resident=True)]
     res = {}
-    for rep in range(2):
+    for rep in range(4):                      # copy-out buffers (0, 2) and resident buffers (1, 3), each used twice
+        ep = eps[rep % 2]
         x = X[rank].to(dev).requires_grad_(True)
         lg = L[rank].to(dev).requires_grad_(True)
         gu = torch.nn.Parameter(GU[rank * El:(rank + 1) * El].to(dev))

@@ -37,7 +37,11 @@ class _EpPlan:
 
 
 class ExpertParallel:
-    def __init__(self, symm, rank, world, num_experts, hidden, max_tokens, top_k, capacity_factor=None):
+    def __init__(self, symm, rank, world, num_experts, hidden, max_tokens, top_k, capacity_factor=None, resident=False):
+        """``resident``: this object serves ONE layer and every forward is followed by its backward before the next
+        forward.  The dispatched rows and the expert outputs then stay in the symmetric buffers until the backward
+        (no copies out and back), gradients arrive in a third buffer, and a layer crosses five flag barriers instead
+        of eight.  A backward that finds the buffers overwritten by a later forward raises."""
         assert num_experts % world == 0
         self.symm, self.rank, self.world, self.E, self.H = symm, rank, world, num_experts, hidden
         self.El = num_experts // world
@@ -49,6 +53,8 @@ class ExpertParallel:
         self.xp = symm.alloc(self.max_rows * hidden, bf)     # dispatch target / dxp source
         self.yp = symm.alloc(self.max_rows * hidden, bf)     # combine source / dyp target
         self.counts_all = symm.alloc(world * num_experts, torch.int32)
+        self.resident, self.generation = resident, 0
+        self.gp = symm.alloc(self.max_rows * hidden, bf) if resident else None     # dyp target
         self.dev = dev
 
     def _t(self, buf, dtype=torch.bfloat16):
@@ -71,6 +77,9 @@ class _EpFFN(torch.autograd.Function):
         idx, w, probs, counts, lse = M.router_topk(logits, k, renorm)
         xp, yp = ep._t(ep.xp), ep._t(ep.yp)
         xp.zero_()
+        ep.generation += 1
+        if ep.resident:
+            ep._t(ep.gp).zero_()          # ordered before this forward's barriers, so peers' gradient rows land on zeros
         check(lib.tfb_ep_push_counts(counts.data_ptr(), ep.counts_all.ptrs.data_ptr(), W, E, rank, s()), "ep_push_counts")
         ep.symm.barrier()
         pl = _EpPlan()
@@ -92,7 +101,7 @@ class _EpFFN(torch.autograd.Function):
         f_glob = ca.view(W, E).float().sum(0)
         f_glob = f_glob / f_glob.sum().clamp(min=1)
         ep.symm.barrier()                              # every token row has reached its owner
-        xp_saved = xp.clone()
+        xp_saved = xp if ep.resident else xp.clone()
         gu = M.grouped_gemm(xp_saved, gate_up.data, pl)
         a = F.glu_fwd(gu, act, rows=pl.total)          # only the routed rows; the provisioned tail is never read
         M.grouped_gemm(a, down.data, pl, out=yp)        # straight into the buffer the sources read in combine
@@ -101,7 +110,11 @@ class _EpFFN(torch.autograd.Function):
         check(lib.tfb_ep_combine(ep.yp.ptrs.data_ptr(), idx.data_ptr(), pl.row_of.data_ptr(), w.data_ptr(), y.data_ptr(),
                                  T, k, H, El, s()), "ep_combine")
         aux = lb_weight * E * (f_glob * probs.mean(0)).sum() + z_weight * (lse * lse).mean()
-        ctx.save_for_backward(x, xp_saved, gu, a, yp.clone(), w, probs, idx, lse, f_glob)
+        if ep.resident:
+            ctx.save_for_backward(x, gu, a, w, probs, idx, lse, f_glob)
+        else:
+            ctx.save_for_backward(x, gu, a, w, probs, idx, lse, f_glob, xp_saved, yp.clone())
+        ctx.generation = ep.generation
         ctx.pl, ctx.ep, ctx.gate_up, ctx.down = pl, ep, gate_up, down
         ctx.cfg = (k, renorm, act, lb_weight, z_weight)
         ctx.logits_dtype = logits.dtype
@@ -111,25 +124,35 @@ class _EpFFN(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, daux, _didx):
         lib, s = _lib.lib(), stream
-        x, xp_saved, gu, a, yp_saved, w, probs, idx, lse, f_glob = ctx.saved_tensors
         pl, ep, gate_up, down = ctx.pl, ctx.ep, ctx.gate_up, ctx.down
+        if ep.resident:
+            x, gu, a, w, probs, idx, lse, f_glob = ctx.saved_tensors
+            if ctx.generation != ep.generation:
+                raise RuntimeError("resident expert-parallel buffers were overwritten by a later forward; build "
+                                   "ExpertParallel(resident=False) for schedules that run two forwards before a backward")
+        else:
+            x, gu, a, w, probs, idx, lse, f_glob, xp_saved, yp_saved = ctx.saved_tensors
         k, renorm, act, lb_weight, z_weight = ctx.cfg
         T, H = x.shape
         E, El = ep.E, ep.El
         dev = x.device
         dy = dy.contiguous()
         xp_sym, yp_sym = ep._t(ep.xp), ep._t(ep.yp)
-        yp_sym.copy_(yp_saved)                          # owners re-expose their outputs (needed for d weights)
-        xp_sym.zero_()                                  # xp buffer now receives dyp rows
-        ep.symm.barrier()
+        if ep.resident:
+            xp_saved, grad_buf, dyp_sym = xp_sym, ep.gp, ep._t(ep.gp)      # outputs still exposed, gp cleared in forward
+        else:
+            yp_sym.copy_(yp_saved)                      # owners re-expose their outputs (needed for d weights)
+            xp_sym.zero_()                              # xp buffer now receives dyp rows
+            ep.symm.barrier()
+            grad_buf, dyp_sym = ep.xp, xp_sym
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
-        check(lib.tfb_ep_combine_bwd(dy.data_ptr(), ep.yp.ptrs.data_ptr(), ep.xp.ptrs.data_ptr(), idx.data_ptr(),
+        check(lib.tfb_ep_combine_bwd(dy.data_ptr(), ep.yp.ptrs.data_ptr(), grad_buf.ptrs.data_ptr(), idx.data_ptr(),
                                      pl.row_of.data_ptr(), w.data_ptr(), dw.data_ptr(), T, k, H, El, s()), "ep_combine_bwd")
         ep.symm.barrier()                               # gradient rows have reached the owners
         for p_ in (gate_up, down):
             if not hasattr(p_, "main_grad") or p_.main_grad is None:
                 p_.main_grad = torch.zeros(p_.shape, dtype=torch.float32, device=dev)
-        dyp = xp_sym.clone()
+        dyp = dyp_sym if ep.resident else dyp_sym.clone()
         da = M.grouped_gemm(dyp, down.data, pl, b_mn=True)
         M.grouped_wgrad(dyp, a, pl, down.main_grad)
         dgu = F.glu_bwd(gu, da, act, rows=pl.total)
@@ -139,7 +162,8 @@ class _EpFFN(torch.autograd.Function):
         dx = torch.empty((T, H), dtype=x.dtype, device=dev)
         check(lib.tfb_ep_dispatch_bwd(ep.yp.ptrs.data_ptr(), idx.data_ptr(), pl.row_of.data_ptr(), dx.data_ptr(), T, k, H,
                                       El, s()), "ep_dispatch_bwd")
-        ep.symm.barrier()                               # sources are done with the owners' buffers
+        if not ep.resident:                             # resident: the next writer of these buffers is this layer's next
+            ep.symm.barrier()                           # forward, which crosses two barriers first
         # router gradient (local tokens): identical to the single-rank expression
         dprobs = torch.zeros_like(probs)
         li = idx.long()

@@ -19,9 +19,12 @@ from torch import nn
 from .ep import ExpertParallel
 
 
-def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int) -> List[nn.Parameter]:
+def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int, resident: bool = True) -> List[nn.Parameter]:
     """Cuts every MoE block's expert tensors down to this rank's contiguous block of experts, attaches the dispatch /
-    combine object, and rebuilds the flat parameter buffer.  Returns the expert parameters (the rest is replicated)."""
+    combine object, and rebuilds the flat parameter buffer.  Returns the expert parameters (the rest is replicated).
+    ``resident`` (every layer owns its buffers and each forward is followed by its backward): dispatched rows and expert
+    outputs stay in the symmetric buffers between forward and backward; pass False for schedules that run a layer's
+    forward twice before its backward (recomputation, interleaved micro-batches)."""
     cfg = model.cfg
     E = cfg.num_experts
     if E % world:
@@ -33,7 +36,7 @@ def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int) 
             continue
         blk.gate_up = nn.Parameter(blk.gate_up.data[rank * El:(rank + 1) * El].clone())
         blk.down = nn.Parameter(blk.down.data[rank * El:(rank + 1) * El].clone())
-        blk.ep = ExpertParallel(symm, rank, world, E, cfg.hidden_size, max_tokens, min(cfg.top_k, 8))
+        blk.ep = ExpertParallel(symm, rank, world, E, cfg.hidden_size, max_tokens, min(cfg.top_k, 8), resident=resident)
         experts += [blk.gate_up, blk.down]
     model.flat = None
     model.flatten()
