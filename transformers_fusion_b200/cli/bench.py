@@ -185,7 +185,7 @@ def serve_bench(a):
                             enable_prefix_cache=False, max_seq_len=min(cfg.max_seq_len, a.prompt_len + a.gen + 16))
         eng = TPInferenceEngine(model, None, ecfg, rank, world, symm) if world > 1 else InferenceEngine(model, None, ecfg)
         greedy = SamplerConfig(temperature=0.0, top_k=0, top_p=1.0)
-        for rep in range(2):                       # the first pass builds graphs and workspaces
+        for rep in range(3):                       # the first passes build graphs and workspaces and settle the allocator
             prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(B)]
             torch.cuda.synchronize()
             t0 = time.perf_counter()

@@ -659,12 +659,18 @@ static float* splitk_workspace(cudaStream_t stream) {
       (void)cudaGetLastError();
       return nullptr;
     }
+    // The workspace is all zero between products: cleared once here, and the finalize kernel clears what it has read.
+    if (cudaMemset(q, 0, SPLITK_WS_ELEMS * sizeof(float)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      (void)cudaFree(q);
+      return nullptr;
+    }
     ws[dev] = static_cast<float*>(q);
   }
   return ws[dev];
 }
 
-__global__ void __launch_bounds__(256) splitk_finalize_kernel(const float* __restrict__ ws, long long ldw, void* __restrict__ C, long long ldc,
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(float* __restrict__ ws, long long ldw, void* __restrict__ C, long long ldc,
                                                               const __nv_bfloat16* __restrict__ bias,
                                                               const __nv_bfloat16* __restrict__ residual, long long ldr, int M, int N,
                                                               int act, int out_fp32) {
@@ -673,6 +679,7 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const float* __res
   const int m = int(i / ldw), n = int(i % ldw);
   if (n >= N) return;
   const float4 a = *reinterpret_cast<const float4*>(ws + i);
+  *reinterpret_cast<float4*>(ws + i) = make_float4(0.f, 0.f, 0.f, 0.f);     // leave the workspace clear for the next product
   float v[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -716,8 +723,6 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
     if (best_s > 1 && (long long)M * ldw <= SPLITK_WS_ELEMS) {
       cudaStream_t st0 = static_cast<cudaStream_t>(stream);
       if (float* ws = splitk_workspace(st0)) {
-        cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(float) * M * ldw, st0);
-        if (e != cudaSuccess) return int(e);
         if (int rc0 = gemm_impl(A, lda, a_mn, B, ldb, b_mn, ws, ldw, M, N, K, nullptr, nullptr, 0, alpha, 0, 2, max_ctas, nullptr, status,
                                 stream, nullptr, best_s))
           return rc0;

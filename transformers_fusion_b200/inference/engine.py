@@ -347,7 +347,7 @@ class InferenceEngine:
             if rope is not None:
                 F.rope_(qkv, rope[0], rope[1], Hq + Hkv, D, 1, positions=positions)
             self.cache.append(li, qkv, Hq * D, (Hq + Hkv) * D, slots)
-            o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), block_table, lens, Hq)
+            o = self.cache.decode(li, qkv[:, :Hq * D], block_table, lens, Hq)
             if mc.use_parallel_residual:
                 attn = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None))
                 f, _ = _norm_fwd(mc, h, w.ffn_norm, getattr(w, "ffn_norm_bias", None))
