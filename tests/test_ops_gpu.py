@@ -66,6 +66,10 @@ def test_glu(act):
     d = torch.randn(M, Fh, dtype=BF)
     close(F.glu_fwd(x.cuda(), act), F.glu_fwd(x, act))
     close(F.glu_bwd(x.cuda(), d.cuda(), act), F.glu_bwd(x, d, act))
+    # device-side row count: only the first rows are computed, the rest of the output is left alone
+    rows = torch.tensor([200], dtype=torch.int32, device="cuda")
+    close(F.glu_fwd(x.cuda(), act, rows=rows)[:200], F.glu_fwd(x, act)[:200])
+    close(F.glu_bwd(x.cuda(), d.cuda(), act, rows=rows)[:200], F.glu_bwd(x, d, act)[:200])
 
 
 def test_embedding():
