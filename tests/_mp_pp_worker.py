@@ -13,6 +13,34 @@ from transformers_fusion_b200.parallel.collectives import DistributedContext  # 
 from transformers_fusion_b200.parallel.pp import PipelineParallel  # noqa: E402
 
 
+def tied_case(ctx, ids, labels):
+    """Tied embedding / LM head: both end stages must hold the summed gradient, clip on the global norm and end one
+    optimizer step with the same table as a single-process run."""
+    from transformers_fusion_b200.engines.dense import OptimSuite
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=4, num_heads=4, ffn_hidden_size=64, max_seq_len=16,
+                            tie_embeddings=True)
+    ref = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=2)
+    ref.flatten()
+    ref.forward_backward(ids, labels)
+    ro = OptimSuite("adamw", 1e-2, 0.0)
+    ro.add_group(list(ref.parameters()), 1.0, 1.0)
+    ref_norm = ro.clip(0.05)
+    ref_emb_grad = ref.tok_embeddings.main_grad.clone()
+    ro.step()
+    m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=2)
+    pp = PipelineParallel(m, ctx.world_size, ctx.rank, ctx, num_microbatches=4)
+    pp.run_1f1b(ids, labels)
+    opt = OptimSuite("adamw", 1e-2, 0.0)
+    opt.add_group(pp.owned_parameters(), 1.0, 1.0)
+    norm = pp.clip_gradients(0.05)
+    out = {"tied_norm_err": abs(norm - ref_norm) / ref_norm}
+    if pp.first or pp.last:
+        out["tied_grad_err"] = float((m.tok_embeddings.main_grad - ref_emb_grad).abs().max())
+        opt.step()
+        out["tied_param_err"] = float((m.tok_embeddings.data - ref.tok_embeddings.data).abs().max())
+    return out
+
+
 def main():
     out_dir = sys.argv[1]
     ctx = DistributedContext.init("gloo")
@@ -25,7 +53,10 @@ def main():
     ref = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=1)
     ref.flatten()
     ref_loss = float(ref.forward_backward(ids, labels))
-    for sched in ("gpipe", "1f1b"):
+    for sched in ("gpipe", "1f1b", "1f1b_tied"):
+        if sched == "1f1b_tied":
+            res.update(tied_case(ctx, ids, labels))
+            continue
         m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=1)
         pp = PipelineParallel(m, ctx.world_size, ctx.rank, ctx, num_microbatches=4)
         pp.set_profiling(True)
@@ -33,9 +64,6 @@ def main():
         if pp.last:
             res[f"{sched}_loss_err"] = abs(float(loss) - ref_loss)
         err = 0.0
-        for p, q in zip(pp.owned_parameters(), [dict(ref.named_parameters())[n] for n, pr in m.named_parameters()
-                                                if any(pr is o for o in pp.owned_parameters())]):
-            pass
         name_of = {id(p): n for n, p in m.named_parameters()}
         refp = dict(ref.named_parameters())
         for p in pp.owned_parameters():

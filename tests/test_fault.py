@@ -103,3 +103,30 @@ def test_device_wait_times_out_with_status():
     assert fault.device_wait_status(dev) == (0, "ok")
     x = torch.ones(8, device=dev) * 2                                  # the context is still usable
     assert float(x.sum()) == 16.0
+
+
+@pytest.mark.gpu
+def test_heap_reset_after_timed_out_wait():
+    """After a bounded wait ran out, SymmetricHeap.reset() clears the status, tickets and accumulators, moves the epoch
+    past anything in flight and leaves the heap usable (the failure is a flag that nothing sets; no GPU fault)."""
+    from transformers_fusion_b200.ops import _lib
+    from transformers_fusion_b200.parallel.symm import SymmetricHeap
+    dev = torch.device("cuda")
+    heap = SymmetricHeap(0, 1, dev)
+    ticket = torch.full((1,), 7, dtype=torch.int32, device=dev)        # a last-CTA counter left at a partial count
+    heap.on_reset(ticket.zero_)
+    fault.device_wait_status(dev)
+    ptrs = torch.tensor([heap.flags.local_ptr, heap.flags.local_ptr], dtype=torch.int64, device=dev)   # imaginary rank 1
+    _lib.check(_lib.lib().tfb_comm_barrier(ptrs.data_ptr(), heap.epoch.data_ptr(), 0, 2, _lib.status_word(dev).data_ptr(),
+                                           _lib.stream()), "barrier")
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.KernelError):
+        _lib.check_status(dev, reset=False)
+    e0 = int(heap.epoch.item())
+    heap.reset()
+    assert int(ticket.item()) == 0 and int(heap.epoch.item()) > e0 + 1000
+    assert fault.device_wait_status(dev) == (0, "ok")
+    heap.barrier()
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    heap.close()

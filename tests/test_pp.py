@@ -27,3 +27,6 @@ def test_pipeline_matches_single_process(tmp_path):
         assert res[1][f"{sched}_loss_err"] < 1e-4
         assert res[0][f"{sched}_grad_err"] < 1e-4 and res[1][f"{sched}_grad_err"] < 1e-4
     assert res[0]["1f1b_live"] == 2 and res[1]["1f1b_live"] == 1 and res[0]["gpipe_live"] == 4
+    for r in res:
+        assert r["tied_norm_err"] < 1e-4
+        assert r["tied_grad_err"] < 1e-5 and r["tied_param_err"] < 1e-5

@@ -100,3 +100,26 @@ def test_unified_trainer_and_ema(tmp_path):
     before = m.flat.params.clone()
     u.train_step_once(*dl.next_batch()); u.trainer.ema_step(); u.trainer.ema_swap()
     assert not torch.equal(m.flat.params, before)
+
+
+def test_engine_gradient_accumulation_matches_full_batch():
+    """Two half-batch micro-steps with grad_accum_steps=2 apply ONE update equal to a full-batch step."""
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.trainer.engine import TrainEngine
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 64, (4, 16), generator=g)
+    labels = torch.roll(ids, -1, 1)
+    a = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=5)
+    b = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=5)
+    ea = TrainEngine(a, lr=1e-2, max_grad_norm=0.0)
+    eb = TrainEngine(b, lr=1e-2, max_grad_norm=0.0, grad_accum_steps=2)
+    ea.step(ids, labels)
+    before = b.flat.params.clone()
+    eb.step(ids[:2], labels[:2])
+    assert torch.equal(b.flat.params, before) and eb.opt.step_count == 0     # window still open: no update yet
+    eb.step(ids[2:], labels[2:])
+    assert eb.opt.step_count == 1
+    assert (a.flat.params - b.flat.params).abs().max() < 1e-5

@@ -533,16 +533,11 @@ template <int D>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const AttnBwdParams& p, cudaStream_t st) {
   using L = BwdSmem<D>;
-  static bool configured = false;
+  static DeviceOnce once1, once2;   // kernel attributes are per device: set on the first launch on each one
   auto k1 = attn_bwd_dkdv_kernel<D>;
   auto k2 = attn_bwd_dq_kernel<D>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return int(e);
-    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  if (int e = ensure_dyn_smem(once1, k1, L::TOTAL)) return e;
+  if (int e = ensure_dyn_smem(once2, k2, L::TOTAL)) return e;
   const int nqb = (p.S + 127) / 128;
   k1<<<nqb * p.Hkv * p.B, AB_THREADS, L::TOTAL, st>>>(tq, tk, tv, tdo, p);
   k2<<<nqb * p.Hq * p.B, AB_THREADS, L::TOTAL, st>>>(tq, tk, tv, tdo, p);

@@ -15,8 +15,11 @@
 //   * B * Hq * S must not exceed TFB_ATTN_BWD_NOALLOC_MAX_ROWS (4 Mi rows = 16 MiB of scratch, held by
 //     every GPU that loads the library until the process exits).  Larger problems are refused with
 //     TFB_ERR_LIMIT (-3) and nothing is launched.
-//   * The first call on a device looks up the device address of the array (no allocation, but it is
-//     set-up work): make that first call before any stream capture begins on that device.
+//   * The first call on a device looks up the device address of the array and raises the kernels'
+//     shared-memory limit on that device (no allocation, but both are set-up work that a stream
+//     capture does not record): make that first call before any stream capture begins on that device.
+//   * The address table covers device indices 0..63; on a device with a higher index the call is
+//     refused with TFB_ERR_LIMIT (-3).
 //   * All calls share the one array and nothing in it needs to start at zero (every row that is read
 //     is written first by the same call).  Two calls that overlap on the GPU - different streams, or
 //     two host threads - race on it; serialise them on one stream or use tfb_attn_bwd() with separate

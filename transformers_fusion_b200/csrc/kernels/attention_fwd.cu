@@ -346,13 +346,9 @@ template <int D>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
                            cudaStream_t st) {
   using L = AttnSmem<D>;
-  static bool configured = false;
+  static DeviceOnce once;
   auto kern = attn_fwd_kernel<D>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  if (int e = ensure_dyn_smem(once, kern, L::TOTAL)) return e;
   const int npair = (p.S + 2 * ATT_BM - 1) / (2 * ATT_BM);
   kern<<<npair * p.B * p.Hq, ATT_THREADS, L::TOTAL, st>>>(tq, tk, tv, p);
   return int(cudaGetLastError());

@@ -13,7 +13,7 @@
 // the main loop of tile i+1.  Either operand may be K-major (reduction dim contiguous) or MN-major
 // (output dim contiguous): the forward, data-gradient and weight-gradient GEMMs of a linear layer
 // all run without a transpose copy.  Small-output / long-K problems (weight gradients) are split
-// along K across CTAs and reduced with vector fp32 atomics into the fp32 gradient buffer.
+// along K across CTAs and summed into the fp32 gradient buffer by TMA reduce-add from the staged epilogue.
 //
 // This replaces the reference's scalar one-thread-per-output kernels
 // (src/backend/gpu_compute_cuda.cpp:68 gemm_kernel; src/kernel/kernel_gemm.cpp:26 scalar_gemm_bt).
@@ -599,13 +599,9 @@ template <bool A_MN, bool B_MN, int BN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
                   cudaStream_t st) {
   using L = SmemLayout<BN>;
-  static bool configured = false;
+  static DeviceOnce once;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  if (int e = ensure_dyn_smem(once, kern, L::TOTAL)) return e;
   kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, tc, p);
   return int(cudaGetLastError());
 }

@@ -280,12 +280,8 @@ TFB_API int tfb_gemm_fp8_blockscaled(const void* A, const float* sa, const void*
   p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc; p.sa = sa; p.sb = sb;
   p.tiles_m = (M + F8_BM - 1) / F8_BM; p.tiles_n = (N + F8_BN - 1) / F8_BN; p.kblocks = (K + F8_BK - 1) / F8_BK;
   p.expert_of_mtile = expert_of_mtile; p.status = status;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F8Smem::TOTAL);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  static DeviceOnce once;
+  if (int e = ensure_dyn_smem(once, gemm_fp8_kernel, F8Smem::TOTAL)) return e;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_fp8_kernel<<<grid, F8_THREADS, F8Smem::TOTAL, static_cast<cudaStream_t>(stream)>>>(ta, tb, p);

@@ -494,14 +494,13 @@ TFB_API int tfb_gemm_wq(const void* A, long long lda, const void* wq, const void
       {gemm_wq_kernel<0, 16>, gemm_wq_kernel<1, 16>, gemm_wq_kernel<2, 16>, gemm_wq_kernel<3, 16>, gemm_wq_kernel<4, 16>},
       {gemm_wq_kernel<0, 128>, gemm_wq_kernel<1, 128>, gemm_wq_kernel<2, 128>, gemm_wq_kernel<3, 128>, gemm_wq_kernel<4, 128>}};
   static const int smem_of[2] = {WqPlan<16>::SMEM, WqPlan<128>::SMEM};
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce once;
+  if (once.first_use()) {
     for (int a = 0; a < 2; ++a)
       for (Kern k : kerns[a]) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of[a]);
-        if (e != cudaSuccess) return int(e);
+        if (e != cudaSuccess) { once.retry(); return int(e); }
       }
-    configured = true;
   }
   const long long work = (long long)tiles * p.splits;
   const int grid = int(work < sms ? work : sms);

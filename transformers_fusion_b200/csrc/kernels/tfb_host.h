@@ -28,6 +28,35 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0
 
 int sm_count();
 
+// One-time set-up per device.  Kernel attributes (cudaFuncSetAttribute) belong to the device that is current when
+// they are set, so a process that drives several GPUs has to repeat them on each: `first_use()` is true exactly once
+// per device (devices beyond 63 report true on every call, which only repeats an idempotent set-up).
+class DeviceOnce {
+ public:
+  bool first_use() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    const unsigned long long bit = 1ull << dev;
+    const unsigned long long old = __atomic_fetch_or(&done_, bit, __ATOMIC_ACQ_REL);
+    return (old & bit) == 0;
+  }
+  void retry() {   // set-up failed: let the next call on this device try again
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) __atomic_fetch_and(&done_, ~(1ull << dev), __ATOMIC_ACQ_REL);
+  }
+ private:
+  unsigned long long done_ = 0;
+};
+
+// Raises a kernel's dynamic shared-memory limit once per device.  Returns 0 or a cudaError_t.
+template <class Kern>
+inline int ensure_dyn_smem(DeviceOnce& once, Kern kern, int bytes) {
+  if (!once.first_use()) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) { once.retry(); return int(e); }
+  return 0;
+}
+
 }  // namespace tfb
 
 // ---------------------------------------------------------------------------------------------------------------------

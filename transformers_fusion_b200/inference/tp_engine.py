@@ -7,7 +7,7 @@ activations, so sampling with the shared seed picks the same token everywhere an
 exchanging anything else.
 
 Reference counterparts: TensorParallelManager::parallelize_model / row_parallel_linear + allreduce_tensor
-(src/distributed/tensor_parallelism.cpp:334-451) applied to the inference path; the reference has no multi-process
+(src/trainer/tensor_parallelism.cpp:334-451) applied to the inference path; the reference has no multi-process
 serving engine."""
 from __future__ import annotations
 

@@ -110,6 +110,7 @@ class SymmCollectives:
         self.capacity = (capacity_bytes + gran - 1) // gran * gran
         self.stage = symm.alloc_bytes(self.capacity)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=symm.device)
+        symm.on_reset(self.ticket.zero_)
         self.one_shot_max_bytes = 256 << 10
 
     def _run(self, local, n, dtype, op, mode, root=0, max_ctas=0):

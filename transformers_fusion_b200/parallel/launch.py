@@ -12,9 +12,9 @@ fastest (tensor-parallel peers exchange the most data per step), then dp, then p
   zero stage 3    FullyShardedDataParallel (weights gathered inside the consuming GEMM on CUDA)
   otherwise       the ordinary Trainer: data parallel with ZeRO stage 0 / 1 / 2 (fused reduce-scatter + AdamW)
 
-Reference counterparts: DistributedContext::init (src/distributed/distributed.cpp:21-123), FSDP / DDP / pipeline /
-tensor-parallel managers each taking a context and a rank (src/distributed/*.cpp); the reference has no launcher that
-composes them."""
+Reference counterparts: DistributedContext (src/trainer/distributed.cpp:21-123), FSDP / DDP / pipeline /
+tensor-parallel managers each taking a world size and a rank (src/trainer/{fsdp,ddp,pipeline,tensor_parallelism}.cpp);
+the reference has no launcher that composes them."""
 from __future__ import annotations
 
 import datetime
@@ -173,7 +173,7 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
         from ..engines.dense import OptimSuite
         from .collectives import DistributedContext
         from .pp import PipelineParallel
-        pipe = PipelineParallel(model, st.pp, st.pp_rank, DistributedContext(st.pp_rank, st.pp, None),
+        pipe = PipelineParallel(model, st.pp, st.pp_rank, DistributedContext(st.pp_rank, st.pp, st.pp_group),
                                 num_microbatches=min(4, cfg.batch_size), stage_ranks=st.pp_ranks)
         opt = OptimSuite("adamw", cfg.learning_rate, cfg.weight_decay)
         owned = pipe.owned_parameters()
@@ -189,7 +189,7 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
                     dist.all_reduce(p.main_grad, group=st.dp_group)
                     p.main_grad.div_(st.dp)
             opt.set_lr(lr_at(step))
-            opt.clip(cfg.max_grad_norm)
+            pipe.clip_gradients(cfg.max_grad_norm)      # global norm over every stage; a tied embedding counted once
             opt.step()
             pipe.clear_accumulated_gradients()
             loss = float(lt)

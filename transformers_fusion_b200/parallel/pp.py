@@ -53,7 +53,6 @@ class PipelineParallel:
         self.fwd_ns: List[int] = []
         self.bwd_ns: List[int] = []
         self._saved = {}
-        self._inflight = []
         self.loss_sum = None
 
     # ---- configuration
@@ -76,65 +75,80 @@ class PipelineParallel:
         return list(range(self.lo, self.hi))
 
     # ---- transport
-    def _send(self, t, dst):
-        # non-blocking: in 1F1B neighbouring stages send to each other at the same time, and a blocking send on both
-        # sides would wait for a receive that is never posted
-        t = t.contiguous()
-        self._inflight.append((dist.isend(t, self.stage_ranks[dst], group=self.ctx.group), t))
+    def _exchange(self, send_next=None, send_prev=None, recv_next=None, recv_prev=None):
+        """Point-to-point traffic of one schedule slot, posted as ONE batch (``dist.batch_isend_irecv``) and waited for.
 
-    def _drain(self):
-        for h, _ in self._inflight:
-            h.wait()
-        self._inflight = []
+        Pairing a slot's send with its receive matters on NCCL: neighbouring stages share one communicator, so a send
+        and a receive enqueued as separate calls run in program order, and in the steady state of 1F1B stage s wants to
+        send activations while stage s + 1 wants to send gradients; each would wait for a receive that the other has
+        queued behind its own send.  Inside one batch NCCL progresses all of the operations together.
+        ``recv_next`` / ``recv_prev`` are (shape, dtype, device) of the tensor expected from that neighbour."""
+        ops, got_next, got_prev, keep = [], None, None, []
+        nxt = self.stage_ranks[self.sid + 1] if self.sid + 1 < self.S else None
+        prv = self.stage_ranks[self.sid - 1] if self.sid > 0 else None
+        if send_prev is not None:
+            keep.append(send_prev.contiguous())
+            ops.append(dist.P2POp(dist.isend, keep[-1], prv, group=self.ctx.group))
+        if recv_prev is not None:
+            got_prev = torch.empty(recv_prev[0], dtype=recv_prev[1], device=recv_prev[2])
+            ops.append(dist.P2POp(dist.irecv, got_prev, prv, group=self.ctx.group))
+        if send_next is not None:
+            keep.append(send_next.contiguous())
+            ops.append(dist.P2POp(dist.isend, keep[-1], nxt, group=self.ctx.group))
+        if recv_next is not None:
+            got_next = torch.empty(recv_next[0], dtype=recv_next[1], device=recv_next[2])
+            ops.append(dist.P2POp(dist.irecv, got_next, nxt, group=self.ctx.group))
+        if ops:
+            for h in dist.batch_isend_irecv(ops):
+                h.wait()
+        return got_next, got_prev
 
-    def _recv(self, shape, dtype, src, device):
-        t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, self.stage_ranks[src], group=self.ctx.group)
-        return t
+    def _hidden_spec(self, ids):
+        m = self.model
+        return ((ids.shape[0] * ids.shape[1], m.cfg.hidden_size), m.tok_embeddings.dtype, m.tok_embeddings.device)
 
-    # ---- one micro-batch
+    # ---- one micro-batch (compute only; the schedules move the tensors)
     @torch.no_grad()
-    def forward_microbatch(self, mb: int, ids: torch.Tensor, labels: Optional[torch.Tensor] = None):
-        """Runs this stage's layers on micro-batch ``mb``; keeps what backward needs."""
+    def forward_microbatch(self, mb: int, ids: torch.Tensor, labels: Optional[torch.Tensor] = None, h_in=None):
+        """Runs this stage's layers on micro-batch ``mb`` (``h_in`` = hidden state received from the previous stage;
+        the first stage embeds ``ids``); keeps what backward needs and returns the stage's output."""
         t0 = time.perf_counter_ns()
         m, cfg = self.model, self.model.cfg
         B, S = ids.shape
-        dev, dt = m.tok_embeddings.device, m.tok_embeddings.dtype
-        h = m.embed(ids) if self.first else self._recv((B * S, cfg.hidden_size), dt, self.sid - 1, dev)
+        dev = m.tok_embeddings.device
+        h = m.embed(ids) if self.first else h_in
         rope = m.rope(dev)
         ctxs = []
         for i in range(self.lo, self.hi):
             h, c = block_forward(cfg, m.layers[i], h, B, S, rope, save=True)
             ctxs.append(c)
         self._saved[mb] = (ctxs, ids, labels, h if self.last else None)
-        if not self.last:
-            self._send(h, self.sid + 1)
         if self.profiling:
             self.fwd_ns.append(time.perf_counter_ns() - t0)
         return h
 
     @torch.no_grad()
-    def backward_microbatch(self, mb: int, n_valid_total=None):
+    def backward_microbatch(self, mb: int, n_valid_total=None, dh=None):
+        """Backward of micro-batch ``mb`` (``dh`` = gradient received from the next stage; the last stage starts from
+        the loss).  Returns the gradient for the previous stage (None on the first stage)."""
         t0 = time.perf_counter_ns()
         m, cfg = self.model, self.model.cfg
         ctxs, ids, labels, h_last = self._saved.pop(mb)
-        dev, dt = m.tok_embeddings.device, m.tok_embeddings.dtype
+        dev = m.tok_embeddings.device
         B, S = ids.shape
         rope = m.rope(dev)
         if self.last:
             loss, dh = m.head_loss_backward(h_last, labels.reshape(-1), n_valid=n_valid_total)
             self.loss_sum = loss if self.loss_sum is None else self.loss_sum + loss
-        else:
-            dh = self._recv((B * S, cfg.hidden_size), dt, self.sid + 1, dev)
         for i in range(self.hi - 1, self.lo - 1, -1):
             dh = block_backward(cfg, m.layers[i], ctxs[i - self.lo], dh, rope)
         if self.first:
             F.embedding_bwd(ids.reshape(-1), dh, m.tok_embeddings.main_grad,
                             m.pos_embeddings.main_grad if m.pos_embeddings is not None else None, S)
-        else:
-            self._send(dh, self.sid - 1)
+            dh = None
         if self.profiling:
             self.bwd_ns.append(time.perf_counter_ns() - t0)
+        return dh
 
     # ---- schedules
     def _split(self, ids, labels):
@@ -146,33 +160,89 @@ class PipelineParallel:
     def run_gpipe(self, ids, labels):
         """All forwards, then all backwards.  Returns the mean loss on the last stage (None elsewhere)."""
         mbs, n_valid = self._split(ids, labels)
+        spec = self._hidden_spec(mbs[0][0])
         self.loss_sum = None
         for k, (i, l) in enumerate(mbs):
-            self.forward_microbatch(k, i, l)
+            h_in = None if self.first else self._exchange(recv_prev=spec)[1]
+            h = self.forward_microbatch(k, i, l, h_in)
+            if not self.last:
+                self._exchange(send_next=h)
         for k in reversed(range(len(mbs))):
-            self.backward_microbatch(k, n_valid)
-        self._drain()
+            dh = None if self.last else self._exchange(recv_next=spec)[0]
+            d_in = self.backward_microbatch(k, n_valid, dh)
+            if not self.first:
+                self._exchange(send_prev=d_in)
+        self._finish()
         return self.loss_sum
 
     def run_1f1b(self, ids, labels):
+        """Warm-up forwards, steady one-forward-one-backward, cool-down backwards.  In the steady state the activation
+        that goes to the next stage and the gradient that comes back from it travel in one batch, and so do the
+        gradient for the previous stage and the next activation from it."""
         mbs, n_valid = self._split(ids, labels)
         M = len(mbs)
+        spec = self._hidden_spec(mbs[0][0])
         self.loss_sum = None
         warm = min(M, self.S - 1 - self.sid)
-        f = b = 0
-        for _ in range(warm):
-            self.forward_microbatch(f, *mbs[f])
-            f += 1
-        while f < M:                        # steady state
-            self.forward_microbatch(f, *mbs[f])
-            f += 1
-            self.backward_microbatch(b, n_valid)
-            b += 1
-        while b < M:                        # cool-down
-            self.backward_microbatch(b, n_valid)
-            b += 1
-        self._drain()
+        steady = M - warm
+        for k in range(warm):
+            h_in = None if self.first else self._exchange(recv_prev=spec)[1]
+            h = self.forward_microbatch(k, *mbs[k], h_in)
+            if not self.last:
+                self._exchange(send_next=h)
+        h_in = None
+        if steady > 0 and not self.first:
+            h_in = self._exchange(recv_prev=spec)[1]
+        for k in range(steady):
+            h = self.forward_microbatch(warm + k, *mbs[warm + k], h_in)
+            dh = None
+            if not self.last:
+                dh = self._exchange(send_next=h, recv_next=spec)[0]
+            d_in = self.backward_microbatch(k, n_valid, dh)
+            if not self.first:
+                more = k + 1 < steady
+                h_in = self._exchange(send_prev=d_in, recv_prev=spec if more else None)[1]
+        for k in range(steady, M):                          # cool-down
+            dh = None if self.last else self._exchange(recv_next=spec)[0]
+            d_in = self.backward_microbatch(k, n_valid, dh)
+            if not self.first:
+                self._exchange(send_prev=d_in)
+        self._finish()
         return self.loss_sum
+
+    def _finish(self):
+        """End of a schedule: a tied embedding has one copy on the first stage (embedding gradient) and one on the last
+        (LM-head gradient); both copies must see the sum, or they drift apart."""
+        if self.model.cfg.tie_embeddings and self.S > 1 and (self.first or self.last):
+            g = self.model.tok_embeddings.main_grad
+            other = self.stage_ranks[-1] if self.first else self.stage_ranks[0]
+            buf = torch.empty_like(g)
+            ops = [dist.P2POp(dist.isend, g, other, group=self.ctx.group), dist.P2POp(dist.irecv, buf, other, group=self.ctx.group)]
+            for h in dist.batch_isend_irecv(ops):
+                h.wait()
+            g.add_(buf)
+
+    def grad_norm(self) -> float:
+        """Global gradient norm over all stages (every stage returns the same value); a tied embedding counts once."""
+        skip = self.model.tok_embeddings if (self.model.cfg.tie_embeddings and self.S > 1 and self.last) else None
+        sq = torch.zeros(1, dtype=torch.float32, device=self.model.tok_embeddings.device)
+        for p in self.owned_parameters():
+            if p is not skip:
+                sq += p.main_grad.float().pow(2).sum()
+        if self.S > 1:
+            dist.all_reduce(sq, group=self.ctx.group)
+        return float(sq.sqrt())
+
+    def clip_gradients(self, max_norm: float) -> float:
+        """Scales this stage's gradients by the factor that brings the GLOBAL norm to ``max_norm``."""
+        norm = self.grad_norm()
+        if max_norm > 0 and norm > max_norm:
+            seen = set()
+            for p in self.owned_parameters():
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    p.main_grad.mul_(max_norm / (norm + 1e-6))
+        return norm
 
     forward_1f1b = run_1f1b
 
@@ -191,7 +261,7 @@ class PipelineParallel:
 
     def owned_parameters(self):
         """Parameters this stage updates (its layers, plus embedding / head on the end stages; a tied embedding is
-        updated by both end stages, whose gradients must then be summed by the caller)."""
+        updated by both end stages from the summed gradient that the schedules leave on both of them)."""
         ps = [p for i in range(self.lo, self.hi) for p in self.model.layers[i].parameters()]
         if self.first:
             ps.append(self.model.tok_embeddings)

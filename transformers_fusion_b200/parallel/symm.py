@@ -44,6 +44,7 @@ class SymmetricHeap:
     def __init__(self, rank: int, world: int, device, group=None):
         self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
         self.buffers = []
+        self._reset_hooks = []
         lib = _lib.lib()
         for name in ("tfb_symm_alloc", "tfb_symm_open", "tfb_symm_close", "tfb_symm_free"):
             getattr(lib, name).restype = C.c_int
@@ -86,6 +87,38 @@ class SymmetricHeap:
         _lib.check(_lib.lib().tfb_comm_barrier(self.flags.ptrs.data_ptr(), self.epoch.data_ptr(), self.rank,
                                                self.world, _lib.status_word(self.device).data_ptr(), _lib.stream()),
                    "comm_barrier")
+
+    def on_reset(self, fn):
+        """Register a callable that puts a user's device-side bookkeeping (completion tickets, partial accumulators)
+        back to its idle state; ``reset()`` runs all of them."""
+        self._reset_hooks.append(fn)
+
+    def reset(self):
+        """Recovery after a bounded device wait ran out (``ops._lib.check_status`` raised ``KernelError``).
+
+        A kernel that gives up returns before its last-CTA bookkeeping: completion tickets and accumulators keep partial
+        counts and the ranks' epochs are out of step, so the next collective on this heap could see a stale "done" and
+        overwrite buffers that are still in use.  Every rank of the group calls this (it is a host-side collective): the
+        device is drained, the ranks agree on a fresh epoch above anything in flight, every local flag and the local
+        epoch are set to it, the registered hooks clear tickets and accumulators, the status word is cleared, and one
+        bounded device barrier proves that the flags work again."""
+        torch.cuda.synchronize(self.device)
+        e = self.epoch.clone().to(torch.int64)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+            dist.all_reduce(e, op=dist.ReduceOp.MAX, group=self.group)
+        fresh = int(e.item()) + 1024
+        self.flags.view(torch.int32).fill_(fresh)
+        self.epoch.fill_(fresh)
+        for fn in self._reset_hooks:
+            fn()
+        _lib.status_word(self.device).zero_()
+        torch.cuda.synchronize(self.device)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+        self.barrier()
+        torch.cuda.synchronize(self.device)
+        _lib.check_status(self.device)
 
     def close(self):
         lib = _lib.lib()

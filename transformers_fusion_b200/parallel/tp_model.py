@@ -15,7 +15,7 @@ Embedding, norms and LM head are replicated; each rank computes the loss of its 
 are summed over the TP group after backward.
 
 Reference counterparts: TensorParallelManager::parallelize_model / column_parallel_linear / row_parallel_linear and the
-sequence-parallel scatter / gather (src/distributed/tensor_parallelism.cpp:53-142, 334-451)."""
+sequence-parallel scatter / gather (src/trainer/tensor_parallelism.cpp:53-142, 334-451)."""
 from __future__ import annotations
 
 from typing import List, Optional

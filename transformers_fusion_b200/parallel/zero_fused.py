@@ -41,6 +41,7 @@ class FusedZero:
         self.norm_slots = symm.alloc_bytes(4 * max(world, 32))
         self.accum = torch.zeros(4, dtype=torch.float32, device=dev)
         self.ticket = torch.zeros(4, dtype=torch.int32, device=dev)
+        symm.on_reset(lambda: (self.accum.zero_(), self.ticket.zero_()))
         lib = _lib.lib()
         for name in ("tfb_zero_reduce_scatter", "tfb_zero_adamw_allgather"):
             fn = getattr(lib, name)

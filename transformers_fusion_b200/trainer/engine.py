@@ -53,7 +53,7 @@ class TrainEngine:
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.zero_stage = zero_stage if self.world > 1 else 0
         self.comm = comm if self.world > 1 else "none"
-        self.grad_accum_steps = grad_accum_steps
+        self.grad_accum_steps = max(1, int(grad_accum_steps))
         self.cuda_graph = cuda_graph
         self.symm = symm
         pad = self.world * 1024
@@ -70,8 +70,7 @@ class TrainEngine:
         self.opt = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                              max_grad_norm=max_grad_norm, shard=self.shard,
                              norm_reduce=self._norm_reduce if self.zero_stage >= 1 else None)
-        self._graph = None
-        self._static = None
+        self._graphs = {}            # {closes the accumulation window?: (graph, static inputs, static loss)}
         self._micro = 0
         self.launches_per_step = 0   # kernels inside the captured graph (0 while running eagerly)
         self.fused = None
@@ -111,44 +110,59 @@ class TrainEngine:
         dist.all_gather_into_tensor(flat.params, flat.params[lo:hi].clone(), group=self.group)
 
     # ------------------------------------------------------------------ steps
-    def _step_impl(self, ids, labels):
-        loss = self.model.forward_backward(ids, labels)
-        self._sync_and_update()
+    def _step_impl(self, ids, labels, final=True):
+        """Forward + backward of one micro-batch (gradients scaled by 1 / grad_accum_steps and added to the flat buffer);
+        the reduction and the optimizer update follow only on the micro-batch that closes the accumulation window."""
+        loss = self.model.forward_backward(ids, labels, loss_scale=1.0 / self.grad_accum_steps)
+        if final:
+            self._sync_and_update()
         return loss
 
-    def step(self, ids, labels, lr=None):
-        """One optimizer step on a device-resident batch.  Returns the local mean loss (device scalar)."""
-        if not self.cuda_graph or not ids.is_cuda:
-            self.opt.stage_hyper(lr)
-            return self._step_impl(ids, labels)
-        if self._graph is None:
-            self.opt.stage_hyper(lr)
-            self._static = (ids.clone(), labels.clone())
-            # warm-up on a side stream (allocator pools, lazy kernel attribute calls), then capture; the
-            # warm-up is a real step, so the training state is put back afterwards
-            opt = self.opt
-            snap = [t.clone() for t in (self.flat.params, opt.master, opt.m, opt.v)]
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._step_impl(*self._static)
-            torch.cuda.current_stream().wait_stream(s)
-            for dst, src in zip((self.flat.params, opt.master, opt.m, opt.v), snap):
-                dst.copy_(src)
-            self.flat.grads.zero_()
-            opt.step_count -= 1   # the warm-up step did not count
-            del snap
-            from ..ops import _lib
-            self._graph = torch.cuda.CUDAGraph()
-            n0 = _lib.LAUNCHES[0]
-            with torch.cuda.graph(self._graph):
-                self._static_loss = self._step_impl(*self._static)
+    def _capture(self, final, ids, labels):
+        """Warm-up on a side stream (allocator pools, lazy kernel attribute calls), then capture.  The warm-up is a real
+        step, so the training state is put back afterwards."""
+        opt = self.opt
+        static = (ids.clone(), labels.clone())
+        state = (self.flat.params, opt.master, opt.m, opt.v, self.flat.grads)
+        snap = [t.clone() for t in state]
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._step_impl(*static, final=final)
+        torch.cuda.current_stream().wait_stream(s)
+        for dst, src in zip(state, snap):
+            dst.copy_(src)
+        del snap
+        from ..ops import _lib
+        graph = torch.cuda.CUDAGraph()
+        n0 = _lib.LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            loss = self._step_impl(*static, final=final)
+        if final:
             self.launches_per_step = _lib.LAUNCHES[0] - n0
-        self.opt.stage_hyper(lr)
-        self._static[0].copy_(ids, non_blocking=True)
-        self._static[1].copy_(labels, non_blocking=True)
-        self._graph.replay()
-        return self._static_loss
+        return graph, static, loss
+
+    def step(self, ids, labels, lr=None):
+        """One micro-batch on a device-resident batch; every ``grad_accum_steps``-th call reduces the accumulated
+        gradients and applies the optimizer update.  Returns the local mean loss of the micro-batch (device scalar)."""
+        self._micro += 1
+        final = self._micro % self.grad_accum_steps == 0
+        if not self.cuda_graph or not ids.is_cuda:
+            if final:
+                self.opt.stage_hyper(lr)
+            return self._step_impl(ids, labels, final)
+        if self._graphs.get(final) is None:
+            if final:
+                self.opt.stage_hyper(lr)       # the warm-up step reads staged values; it does not count as a step
+                self.opt.step_count -= 1
+            self._graphs[final] = self._capture(final, ids, labels)
+        graph, static, loss = self._graphs[final]
+        if final:
+            self.opt.stage_hyper(lr)
+        static[0].copy_(ids, non_blocking=True)
+        static[1].copy_(labels, non_blocking=True)
+        graph.replay()
+        return loss
 
     def train_step(self, ids_cpu, labels_cpu, lr=None) -> float:
         """End-to-end step: pinned host batch -> device -> step -> loss on the host (waits for the step)."""

@@ -43,17 +43,26 @@ class FlatAdamW:
         self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
         # ring of slots: the host may run many steps ahead of the asynchronous uploads
         self._hyper_host = torch.zeros(256, 4, dtype=torch.float32)
+        self._hyper_events = None
         if dev.type == "cuda":
             self._hyper_host = self._hyper_host.pin_memory()
+            self._hyper_events = [None] * 256          # per slot: recorded after the slot's upload was enqueued
 
     def stage_hyper(self, lr: Optional[float] = None):
         """Advance the step counter and upload this step's scalars (call outside a graph replay)."""
         self.step_count += 1
-        h = self._hyper_host[self.step_count % 256]
+        slot = self.step_count % 256
+        h = self._hyper_host[slot]
+        if self._hyper_events is not None and self._hyper_events[slot] is not None:
+            self._hyper_events[slot].synchronize()     # the upload that last used this slot (256 steps ago) must be done
         h[0] = self.lr if lr is None else lr
         h[1] = 1.0 - self.betas[0] ** self.step_count
         h[2] = 1.0 - self.betas[1] ** self.step_count
         self.hyper.copy_(h, non_blocking=True)
+        if self._hyper_events is not None:
+            if self._hyper_events[slot] is None:
+                self._hyper_events[slot] = torch.cuda.Event()
+            self._hyper_events[slot].record()
 
     def step(self, lr: Optional[float] = None, inv_loss_scale: float = 1.0, staged: bool = False):
         if not staged:

@@ -9,7 +9,7 @@ reads the byte ranges of the old files that overlap its slice), so a job can res
 ``consolidate`` rebuilds the single-file ``.quant`` checkpoint from the shards.
 
 Reference counterparts: FSDP::save_sharded_checkpoint / load_sharded_checkpoint (``model.rank{r}.quant`` + manifest,
-src/distributed/fsdp.cpp:560-640) and ZeroOptimizer::save_state / load_state (zero_optimizer_core.cpp)."""
+src/trainer/fsdp.cpp:560-640) and ZeroOptimizer::save_state / load_state (zero_optimizer_core.cpp)."""
 from __future__ import annotations
 
 import json
