@@ -35,6 +35,7 @@ def main():
     # reference: one process, whole batch, same AdamW
     ref = DenseModel(cfg, device=dev, dtype=dt, seed=3)
     ref_f = FullyShardedDataParallel(ref, FSDPConfig(lr=1e-2, weight_decay=0.0), DistributedContext(0, 1))
+    ref_f.engine.mesh.world_group = None
     m = DenseModel(cfg, device=dev, dtype=dt, seed=3)
     fs = FullyShardedDataParallel(m, FSDPConfig(lr=1e-2, weight_decay=0.0, copy_ctas=4), ctx, symm)
     res = {"n_sharded": len(fs.weights), "savings": fs.memory_savings_ratio()}
@@ -49,6 +50,7 @@ def main():
         ref_losses.append(float(ref_f.train_step(ids_all.to(dev), lab_all.to(dev))))
     res["losses"], res["ref_losses"] = losses, ref_losses
     fs.consolidate()
+    ref_f.consolidate()
     err = 0.0
     for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
         err = max(err, float((p.data.float() - q.data.float()).abs().max()))

@@ -20,7 +20,7 @@ def _launch(n, backend, tmp_path, env):
 
 def test_zero3_matches_single_process_gloo(tmp_path):
     for res in _launch(2, "gloo", tmp_path, {"CUDA_VISIBLE_DEVICES": ""}):
-        assert res["n_sharded"] == 8 and res["savings"] > 0.3 and res["gathers"] > 20
+        assert res["n_sharded"] >= 8 and res["savings"] > 0.3 and res["gathers"] > 20
         for a, b in zip(res["losses"], res["ref_losses"]):
             assert abs(a - b) < 2e-4, res
         assert res["param_err"] < 2e-4, res

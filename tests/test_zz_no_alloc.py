@@ -28,7 +28,22 @@ def _call(fn, qkv, o, dout, lse, dqkv, B, S, Hq, Hkv, D):
               _lib.status_word(qkv.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
+def _fp32_statement(qkv, dout, B, S, Hq, Hkv, D):
+    """Gradients of causal grouped-query attention by torch autograd in fp32 on the same bf16 inputs."""
+    x = qkv.float().detach().requires_grad_(True)
+    q = x[:, :Hq * D].view(B, S, Hq, D).transpose(1, 2)
+    k = x[:, Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D).transpose(1, 2).repeat_interleave(Hq // Hkv, 1)
+    v = x[:, (Hq + Hkv) * D:].view(B, S, Hkv, D).transpose(1, 2).repeat_interleave(Hq // Hkv, 1)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(D)
+    s = s.masked_fill(torch.ones(S, S, device=x.device, dtype=torch.bool).triu(1), float("-inf"))
+    o = (s.softmax(-1) @ v).transpose(1, 2).reshape(B * S, Hq * D)
+    o.backward(dout.float())
+    return x.grad
+
+
 def test_noalloc_matches_regular_entry_point_twice():
+    """Compared with the ordinary entry point on both calls (that one is checked against fp32 in
+    test_attention_gpu.py) and, on the first call, directly with the fp32 statement as well."""
     lib = _lib.lib()
     fn = lib.tfb_attn_bwd_noalloc
     fn.argtypes, fn.restype = SIG, c_i
@@ -49,6 +64,9 @@ def test_noalloc_matches_regular_entry_point_twice():
         scale = ref.float().abs().max().item()
         assert torch.isfinite(got.float()).all()
         assert (got.float() - ref.float()).abs().max().item() < 3e-2 * scale + 2e-2
+        if n == 0:
+            exact = _fp32_statement(qkv, dout, B, S, Hq, Hkv, D)
+            assert (got.float() - exact).abs().max().item() < 3e-2 * exact.abs().max().item() + 2e-2
 
 
 def test_noalloc_rejects_oversize():

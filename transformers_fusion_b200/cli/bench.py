@@ -4,7 +4,8 @@ L2-sized write between timed launches, best and median of ``--iters`` launches; 
 fraction of the copy / GEMM peaks when ``--peaks <json>`` (keys hbm_gbs, bf16_tflops) is given.
 
 Kernels: gemm, gemm_nt_wgrad, gemm_fp8, attention_fwd, attention_bwd, rmsnorm, rmsnorm_bwd, swiglu, rope,
-cross_entropy, adamw, paged_decode, sampling, moe_ffn."""
+cross_entropy, adamw, paged_decode, sampling, moe_ffn.  ``--comm`` (multi-GPU) times the fused compute+collective kernels
+against their NCCL forms (cli/bench_comm.py)."""
 from __future__ import annotations
 
 import argparse
@@ -234,7 +235,21 @@ def main(argv=None):
     ap.add_argument("--shape", default="", help="gemm only: MxNxK[:nt|nn|tn]")
     ap.add_argument("--peaks", default="")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--comm", action="store_true", help="fused compute+collective kernels against NCCL + plain kernels "
+                                                        "(run under torch.distributed.run; see cli/bench_comm.py)")
+    ap.add_argument("--link-gbs", type=float, default=770.0, help="--comm: NVLink bandwidth per direction per GPU, GB/s")
+    ap.add_argument("--gemm-tflops", type=float, default=1382.0, help="--comm: sustained bf16 GEMM rate for the roofline")
+    ap.add_argument("--zero-mb", type=int, default=256, help="--comm: flat fp32 gradient buffer of the ZeRO-2 step, MiB")
+    ap.add_argument("--unit-mb", type=int, default=436, help="--comm: fp32 gradients of one FSDP unit, MiB")
+    ap.add_argument("--tokens", type=int, default=8192, help="--comm: rows of the tensor-parallel products")
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--copy-ctas", type=int, default=8)
     a = ap.parse_args(argv)
+    if a.comm:
+        from .bench_comm import comm_bench
+        comm_bench(a)
+        return 0
     if a.size <= 0 or a.size > 16384:
         print("Error: --size needs 1..16384", file=sys.stderr)
         return 2

@@ -23,12 +23,27 @@
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
+TFB_BOUNDS_DEFINE(gemm_bf16)
+
 namespace tfb {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int STAGES = 4;
 constexpr int GEMM_THREADS = 192;
+
+enum : int { TP_AG = 1, TP_RS = 2, TP_WG = 4 };
+
+// Rows of one operand that live as row shards on `world` ranks and are copied into a local buffer in 128-row blocks.
+struct GatherSpec {
+  int rank, world, rows_per_shard, row_len, epoch, rows;  // rows: rows of the operand that the product touches
+  int src_is_full;   // 1: src[r] is rank r's whole gathered buffer (block b at b * 128 * ld); 0: rank r's shard only
+  int skip_local;    // 1: this rank's rows are already in place in dst
+  int* ready;        // local int[padded rows / 128]: ready[b] >= epoch once block b has landed in dst
+  const __nv_bfloat16* const* src;   // [world] base pointers (peer memory)
+  __nv_bfloat16* dst;
+  long long ld;
+};
 
 struct GemmParams {
   int M, N, K;
@@ -48,22 +63,22 @@ struct GemmParams {
   const int* expert_of_mtile;   // mode 1: expert of every 128-row tile (-1 = padding, skipped)
   const int* seg_start;         // mode 2: [E + 1] first row of every expert segment
   long long c_expert_stride;    // mode 2: elements between the C matrices of consecutive experts
-  // tensor-parallel fusion with the collective that precedes / follows the GEMM (see tp_fused.cu)
-  //   1: all-gather -> GEMM.  A is the gathered [M, K] buffer in symmetric memory; this rank's rows are in
-  //      place, the last `copy_ctas` CTAs of the grid pull the other ranks' rows over NVLink in 128-row blocks
+  // fusion with the collective that precedes / follows the GEMM (see tp_fused.cu); tp_mode is a set of bits:
+  //   TP_AG (1): all-gather -> GEMM.  A is the gathered [M, K] buffer in symmetric memory; this rank's rows are in
+  //      place, the first `copy_ctas` CTAs of the grid pull the other ranks' rows over NVLink in 128-row blocks
   //      and raise ready[block] = epoch; the TMA producer waits for a block's flag before loading from it.
-  //   2: GEMM -> reduce-scatter.  Output rows of shard d are stored straight into rank d's staging buffer
+  //   TP_RS (2): GEMM -> reduce-scatter.  Output rows of shard d are stored straight into rank d's staging buffer
   //      [world, rows_per_shard, N] at slot `rank` (peer stores from the epilogue); remote shards first.
-  //   3: weight all-gather -> GEMM (ZeRO-3 / FSDP).  B is the gathered weight in symmetric memory, sharded by rows
-  //      (128-row blocks); copy CTAs pull the peers' row blocks exactly as in mode 1 and the TMA producer waits for
-  //      the flag of every block a B tile touches.  Tiles (K-major B) or k-blocks (MN-major B) that use the local
-  //      shard come first.
-  int tp_mode, tp_rank, tp_world, tp_rows_per_shard, tp_copy_ctas, tp_epoch, tp_row_len;
-  int tp_n_shift, tp_k_shift;   // mode 3: first n tile / k block of the local shard
-  int* tp_ready;
-  const __nv_bfloat16* const* tp_peer_a;
-  long long tp_lda;
-  __nv_bfloat16* const* tp_peer_c;
+  //   TP_WG (4): weight all-gather -> GEMM (ZeRO-3 / FSDP).  Every rank of the data-parallel group keeps one row
+  //      shard of B (128-row blocks) in symmetric memory; the copy CTAs pull all shards (the local one first) into the
+  //      local gather buffer B and the TMA producer waits for the flag of every block a B tile touches.  Tiles
+  //      (K-major B) or k-blocks (MN-major B) that use the local shard come first.
+  //   TP_AG and TP_WG may be combined (column-parallel product of a sharded weight), and so may TP_RS and TP_WG.
+  int tp_mode, tp_copy_ctas;
+  GatherSpec ag, wg;
+  int wg_n_shift, wg_k_shift;   // TP_WG: first n tile / k block of the local shard
+  int rs_rank, rs_world, rs_rows_per_shard;
+  __nv_bfloat16* const* rs_peer_c;
   int c_tma;     // 1: the epilogue goes through shared memory and the C tensor map (aligned, dense C)
   int* status;
 };
@@ -92,17 +107,21 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, int tota
   if (p.group_mode == 1) {
     it.expert = p.expert_of_mtile[tile / p.tiles_n];
     if (it.expert < 0) return false;
+    TFB_BOUNDS(it.expert < p.num_experts, 12, it.expert, p.num_experts);
+    if (it.expert >= p.num_experts) return false;
   }
-  if (p.tp_mode == 3) {
-    // n is the slow index and starts at the local shard's columns
+  if ((p.tp_mode & TP_WG) && p.wg_n_shift >= 0) {
+    // K-major gathered B: n is the slow index and starts at the local shard's columns
     it.m0 = (tile % p.tiles_m) * BM;
     const int nt = tile / p.tiles_m;
-    it.n0 = (nt + p.tp_n_shift) % p.tiles_n;
-  } else if (p.tp_mode) {
-    // rotate the row-block order: mode 1 starts with the local shard (already in place), mode 2 ends with it
-    const int bps = p.tp_rows_per_shard / BM;
-    const int shift = (p.tp_mode == 1 ? p.tp_rank : p.tp_rank + 1) * bps;
-    it.m0 = ((it.m0 / BM + shift) % p.tiles_m) * BM;
+    it.n0 = (nt + p.wg_n_shift) % p.tiles_n;
+  }
+  if (p.tp_mode & TP_AG) {
+    // rotate the row-block order: start with the local shard (already in place)
+    it.m0 = ((it.m0 / BM + p.ag.rank * (p.ag.rows_per_shard / BM)) % p.tiles_m) * BM;
+  } else if (p.tp_mode & TP_RS) {
+    // ... and for the reduce-scatter end with it: remote shards are stored first
+    it.m0 = ((it.m0 / BM + (p.rs_rank + 1) * (p.rs_rows_per_shard / BM)) % p.tiles_m) * BM;
   }
   return true;
 }
@@ -113,41 +132,113 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   return v;
 }
 
-// Copy role of the all-gather -> GEMM fusion: pulls 128-row blocks of the peers' shards into the local
-// gathered buffer and publishes each block with a release store.
-__device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int ncopy) {
-  const int W = p.tp_world, bps = p.tp_rows_per_shard / BM;
-  const long long row_chunks = (long long)p.tp_row_len / 8;  // 16-byte chunks per row
-  __nv_bfloat16* dst_base = const_cast<__nv_bfloat16*>(p.tp_peer_a[p.tp_rank]);
-  for (int idx = cta; idx < (W - 1) * bps; idx += ncopy) {
-    const int peer = (p.tp_rank + 1 + idx / bps) % W;
-    const int blk = peer * bps + idx % bps;  // global 128-row block index
-    const __nv_bfloat16* src = p.tp_peer_a[peer] + (long long)blk * BM * p.tp_lda;
-    __nv_bfloat16* dst = dst_base + (long long)blk * BM * p.tp_lda;
-    const long long total = (long long)BM * row_chunks;
-    for (long long c = threadIdx.x; c < total; c += 4 * blockDim.x) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long long cc = c + (long long)u * blockDim.x;
-        if (cc < total) {
-          const long long r = cc / row_chunks, k = cc % row_chunks;
-          v[u] = *reinterpret_cast<const uint4*>(src + r * p.tp_lda + k * 8);
+// Copy role of the gather -> GEMM fusions: pulls 128-row blocks of the ranks' shards into the local gathered buffer
+// and publishes each block with a release store.  Contiguous blocks (row pitch == row length) travel as untiled bulk
+// copies through a shared-memory ring driven by one thread (16 KB chunks, four loads in flight per CTA, so a handful
+// of CTAs keeps enough bytes in flight to fill NVLink); strided rows fall back to per-thread 16-byte copies.
+constexpr int COPY_CHUNK = 16384;
+constexpr int COPY_SLOTS = 8;
+
+__device__ __forceinline__ bool copy_block_bulk(const __nv_bfloat16* src, __nv_bfloat16* dst, long long bytes, uint32_t ring,
+                                                uint32_t bars, uint32_t& seq, volatile int* abort_flag, int* status) {
+  const int nt = int((bytes + COPY_CHUNK - 1) / COPY_CHUNK);
+  const char* s8 = reinterpret_cast<const char*>(src);
+  char* d8 = reinterpret_cast<char*>(dst);
+  int nl = 0, ns = 0;
+  const uint32_t seq0 = seq;
+  while (ns < nt) {
+    while (nl < nt && nl - ns < 4) {
+      tma_store_wait_read<3>();   // the store that last used this ring slot (eight chunks ago) has read it
+      const uint32_t q = seq0 + nl, slot = q % COPY_SLOTS;
+      const uint32_t sz = uint32_t(min((long long)COPY_CHUNK, bytes - (long long)nl * COPY_CHUNK));
+      mbar_expect_tx(bars + slot * 8, sz);
+      bulk_load(ring + slot * COPY_CHUNK, s8 + (long long)nl * COPY_CHUNK, sz, bars + slot * 8);
+      ++nl;
+    }
+    const uint32_t q = seq0 + ns, slot = q % COPY_SLOTS, parity = (q / COPY_SLOTS) & 1u;
+    if (!mbar_wait(bars + slot * 8, parity, abort_flag, status, ST_TIMEOUT_FULL)) {
+      // give the loads already issued a bounded time to land before shared memory goes away
+      const uint64_t t0 = globaltimer_ns();
+      for (int j = ns; j < nl; ++j) {
+        const uint32_t qq = seq0 + j;
+        while (!mbar_try_wait(bars + (qq % COPY_SLOTS) * 8, (qq / COPY_SLOTS) & 1u)) {
+          if (globaltimer_ns() - t0 > 2000000ull) { report(status, ST_TIMEOUT_DRAIN); break; }
         }
       }
+      tma_store_wait<0>();
+      return false;
+    }
+    fence_proxy_async_smem();
+    const uint32_t sz = uint32_t(min((long long)COPY_CHUNK, bytes - (long long)ns * COPY_CHUNK));
+    bulk_store(d8 + (long long)ns * COPY_CHUNK, ring + slot * COPY_CHUNK, sz);
+    tma_store_commit();
+    ++ns;
+  }
+  seq = seq0 + nt;
+  tma_store_wait<0>();       // the block is in the gathered buffer
+  fence_proxy_async_all();   // bulk-copy writes before the flag that publishes them
+  return true;
+}
+
+__device__ __forceinline__ void copy_block_threads(const __nv_bfloat16* src, __nv_bfloat16* dst, long long ld, long long row_chunks,
+                                                   int rows) {
+  const long long total = (long long)rows * row_chunks;
+  for (long long c = threadIdx.x; c < total; c += 4 * blockDim.x) {
+    uint4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const long long cc = c + (long long)u * blockDim.x;
-        if (cc < total) {
-          const long long r = cc / row_chunks, k = cc % row_chunks;
-          *reinterpret_cast<uint4*>(dst + r * p.tp_lda + k * 8) = v[u];
-        }
+    for (int u = 0; u < 4; ++u) {
+      const long long cc = c + (long long)u * blockDim.x;
+      if (cc < total) {
+        const long long r = cc / row_chunks, k = cc % row_chunks;
+        v[u] = *reinterpret_cast<const uint4*>(src + r * ld + k * 8);
       }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.tp_ready + blk), "r"(p.tp_epoch) : "memory");
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long cc = c + (long long)u * blockDim.x;
+      if (cc < total) {
+        const long long r = cc / row_chunks, k = cc % row_chunks;
+        *reinterpret_cast<uint4*>(dst + r * ld + k * 8) = v[u];
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int ncopy, uint32_t ring, uint32_t bars,
+                                             volatile int* abort_flag) {
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < COPY_SLOTS; ++i) mbar_init(bars + i * 8, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int nA = (p.tp_mode & TP_AG) ? (p.ag.world - 1) * (p.ag.rows_per_shard / BM) : 0;
+  const int nB = (p.tp_mode & TP_WG) ? p.wg.world * (p.wg.rows_per_shard / BM) : 0;
+  uint32_t seq = 0;
+  for (int idx = cta; idx < nA + nB; idx += ncopy) {
+    const GatherSpec& g = idx < nA ? p.ag : p.wg;
+    const int j = idx < nA ? idx : idx - nA;
+    const int bps = g.rows_per_shard / BM;
+    const int peer = (g.rank + (g.skip_local ? 1 : 0) + j / bps) % g.world;
+    const int b = j % bps, blk = peer * bps + b;  // block inside the shard / inside the gathered operand
+    if (blk * BM >= g.rows) continue;             // padding rows: nothing reads them
+    TFB_BOUNDS(peer >= 0 && peer < g.world && blk >= 0, 11, blk, g.world * bps);
+    const __nv_bfloat16* src = g.src[peer] + (long long)(g.src_is_full ? blk : b) * BM * g.ld;
+    __nv_bfloat16* dst = g.dst + (long long)blk * BM * g.ld;
+    if (g.ld == g.row_len) {
+      // after a copy that ran out of time nothing more is published: the consumers' own bounded waits end the kernel
+      if (threadIdx.x == 0 && !*abort_flag &&
+          copy_block_bulk(src, dst, (long long)BM * g.row_len * 2, ring, bars, seq, abort_flag, p.status)) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(g.ready + blk), "r"(g.epoch) : "memory");
+      }
+    } else {
+      copy_block_threads(src, dst, g.ld, (long long)g.row_len / 8, BM);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(g.ready + blk), "r"(g.epoch) : "memory");
+      }
     }
   }
 }
@@ -194,11 +285,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   constexpr uint32_t TMEM_COLS = 2 * BN;
   // copy CTAs take the lowest block indices so that they are scheduled first: a GEMM CTA may wait for a copy
   // CTA, never the other way round
-  const int ncopy = (p.tp_mode == 1 || p.tp_mode == 3) ? p.tp_copy_ctas : 0;
+  const int ncopy = (p.tp_mode & (TP_AG | TP_WG)) ? p.tp_copy_ctas : 0;
   const int nctas = int(gridDim.x) - ncopy;  // CTAs that run GEMM tiles
   const int cta = int(blockIdx.x) - ncopy;
   if (cta < 0) {
-    tp_copy_role(p, int(blockIdx.x), ncopy);
+    tp_copy_role(p, int(blockIdx.x), ncopy, smem_base, bar_full, abort_flag);
     return;
   }
 
@@ -240,48 +331,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (!decode_work(p, w, total_kb, it)) continue;
         const int m0 = it.m0, n0 = it.n0 * BN, kb0 = it.kb0, kb1 = it.kb1;
         const int bz = p.group_mode == 1 ? it.expert : 0;
-        if (p.tp_mode == 1) {
-          const int blk = m0 / BM;
-          if (blk / (p.tp_rows_per_shard / BM) != p.tp_rank) {  // rows owned by a peer: wait until they have landed
-            const uint64_t t0 = globaltimer_ns();
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(p.tp_ready + blk) < p.tp_epoch) {
-              if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - t0 > TFB_WAIT_NS)) {
-                report(p.status, ST_TIMEOUT_FLAG);
-                *abort_flag = 1;
-                ok = false;
-                break;
-              }
-            }
-            if (!ok) break;
-            asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes -> visible to the TMA reads below
-          }
-        }
-        auto wait_block = [&](int blk) -> bool {   // rows of block `blk` owned by a peer must have landed locally
-          if (blk / (p.tp_rows_per_shard / BM) == p.tp_rank) return true;
+        auto wait_block = [&](const GatherSpec& g, int blk) -> bool {   // block `blk` of a gathered operand has landed locally
+          if (g.skip_local && blk / (g.rows_per_shard / BM) == g.rank) return true;
           const uint64_t t0 = globaltimer_ns();
           uint32_t spins = 0;
-          while (ld_acquire_gpu(p.tp_ready + blk) < p.tp_epoch) {
+          while (ld_acquire_gpu(g.ready + blk) < g.epoch) {
             if ((++spins & 255u) == 0u && (*abort_flag || globaltimer_ns() - t0 > TFB_WAIT_NS)) {
               report(p.status, ST_TIMEOUT_FLAG);
               *abort_flag = 1;
               return false;
             }
           }
-          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("fence.proxy.async;" ::: "memory");  // the copy CTAs' writes -> visible to the TMA reads below
           return true;
         };
-        if (p.tp_mode == 3 && !B_MN) {
-          for (int r0 = n0; r0 < n0 + BN && r0 < p.N && ok; r0 += BM) ok = wait_block(r0 / BM);
+        if (p.tp_mode & TP_AG) {
+          if (!wait_block(p.ag, m0 / BM)) { ok = false; break; }
+        }
+        if ((p.tp_mode & TP_WG) && !B_MN) {
+          for (int r0 = n0; r0 < n0 + BN && r0 < p.N && ok; r0 += BM) ok = wait_block(p.wg, r0 / BM);
           if (!ok) break;
         }
         int last_blk = -1;
         for (int kb = kb0; kb < kb1; ++kb) {
-          const int kbr = (p.tp_mode == 3 && B_MN) ? (kb + p.tp_k_shift) % total_kb : kb;   // local shard's rows first
-          if (p.tp_mode == 3 && B_MN) {
+          const int kbr = ((p.tp_mode & TP_WG) && B_MN) ? (kb + p.wg_k_shift) % total_kb : kb;   // local shard's rows first
+          if ((p.tp_mode & TP_WG) && B_MN) {
             const int blk = kbr * BK / BM;
             if (blk != last_blk) {
-              if (!wait_block(blk)) { ok = false; break; }
+              if (!wait_block(p.wg, blk)) { ok = false; break; }
               last_blk = blk;
             }
           }
@@ -524,9 +601,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
           __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-          if (p.tp_mode == 2) {  // row belongs to shard d: store into rank d's staging slot for this rank
-            const int d = row / p.tp_rows_per_shard;
-            cp = p.tp_peer_c[d] + ((long long)p.tp_rank * p.tp_rows_per_shard + (row - d * p.tp_rows_per_shard)) * p.ldc + col0;
+          if (p.tp_mode & TP_RS) {  // row belongs to shard d: store into rank d's staging slot for this rank
+            const int d = row / p.rs_rows_per_shard;
+            cp = p.rs_peer_c[d] + ((long long)p.rs_rank * p.rs_rows_per_shard + (row - d * p.rs_rows_per_shard)) * p.ldc + col0;
           }
           if (full && vec_ok_bf16) {
 #pragma unroll
@@ -618,13 +695,18 @@ struct TfbGemmGroup {
 };
 
 struct TfbGemmTp {
-  int mode;               // 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter
-  int rank, world;
-  int copy_ctas;          // mode 1
-  int epoch;              // mode 1: value of a ready flag once its block has landed
-  int* ready;             // mode 1: local int[M / 128]
-  const void* peer_a;     // mode 1: device array [world] of gathered-A base pointers
-  const void* peer_c;     // mode 2: device array [world] of staging-buffer base pointers
+  int mode;               // bits: 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter, 4 weight gather -> GEMM
+  int rank, world;        // tensor-parallel group (bits 1, 2)
+  int copy_ctas;          // bits 1, 4: CTAs that move data instead of multiplying
+  int epoch;              // bit 1: value of a ready flag once its block has landed
+  int* ready;             // bit 1: local int[M / 128]
+  const void* peer_a;     // bit 1: device array [world] of gathered-A base pointers
+  const void* peer_c;     // bit 2: device array [world] of staging-buffer base pointers
+  // bit 4: B is the local gather buffer of a weight whose row shards ([wg_rows / wg_world, ldb] each, 128-row blocks)
+  // live on the wg_world ranks of the data-parallel group
+  int wg_rank, wg_world, wg_epoch, wg_rows;   // wg_rows: padded row count, a multiple of 128 * wg_world
+  int* wg_ready;          // local int[wg_rows / 128]
+  const void* wg_src;     // device array [wg_world] of shard base pointers
 };
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -739,7 +821,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
     const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
     if (BN == 256 && gmode != 2 && out_mode != 2 && t256 < sms && t128 > t256) BN = 128;
   }
-  if (tp && tp->mode == 3 && !b_mn) BN = 128;   // one ready flag per B tile; tiles stay aligned with the row shards
+  if (tp && (tp->mode & TP_WG) && !b_mn && (tp->wg_rows / tp->wg_world) % 256) BN = 128;   // tiles stay inside one row shard
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, BM);
@@ -762,7 +844,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
     const int esz = out_mode == 0 ? 2 : 4;
     const bool aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esz) % 16 == 0 &&
                          (gmode != 2 || (grp->c_expert_stride * esz) % 16 == 0);
-    if (aligned && !(tp && tp->mode == 2)) {
+    if (aligned && !(tp && (tp->mode & TP_RS))) {
       const unsigned long long zs = gmode == 2 ? (unsigned long long)grp->c_expert_stride * esz : (unsigned long long)ldc * esz * M;
       if (make_tmap_3d(&tc, C, esz, N, M, gmode == 2 ? E : 1, ldc * esz, zs, 128 / esz, 32, 1) == 0) p.c_tma = 1;
     }
@@ -778,33 +860,50 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   p.expert_of_mtile = grp ? grp->expert_of_mtile : nullptr;
   p.seg_start = grp ? grp->seg_start : nullptr;
   p.c_expert_stride = grp ? grp->c_expert_stride : 0;
-  p.tp_mode = 0; p.tp_rank = 0; p.tp_world = 1; p.tp_rows_per_shard = M; p.tp_copy_ctas = 0; p.tp_epoch = 0;
-  p.tp_row_len = K; p.tp_n_shift = 0; p.tp_k_shift = 0;
-  p.tp_ready = nullptr; p.tp_peer_a = nullptr; p.tp_lda = lda; p.tp_peer_c = nullptr;
+  p.tp_mode = 0; p.tp_copy_ctas = 0;
+  memset(&p.ag, 0, sizeof(p.ag));
+  memset(&p.wg, 0, sizeof(p.wg));
+  p.wg_n_shift = -1; p.wg_k_shift = 0;
+  p.rs_rank = 0; p.rs_world = 1; p.rs_rows_per_shard = M; p.rs_peer_c = nullptr;
   if (tp) {
-    if (tp->world < 1 || gmode != 0) return TFB_ERR_ARG;
-    if (tp->mode == 3) {
-      // gathered B: rows = N (K-major B) or K (MN-major B), sharded in 128-row blocks
-      const int rows = b_mn ? K : N, row_len = b_mn ? N : K;
-      if (rows % (tp->world * BM) || row_len % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms || out_mode == 2) return TFB_ERR_ARG;
-      p.tp_rows_per_shard = rows / tp->world;
-      p.tp_row_len = row_len;
-      p.tp_lda = ldb;
-      if (!b_mn) {
-        p.tp_n_shift = tp->rank * (p.tp_rows_per_shard / BN);
-      } else {
-        p.tp_k_shift = tp->rank * (p.tp_rows_per_shard / BK);
-      }
-    } else {
-      if (M % (tp->world * BM) || a_mn || out_mode != 0) return TFB_ERR_ARG;
-      if (tp->mode == 1 && (K % 8 || tp->copy_ctas < 1 || tp->copy_ctas >= sms)) return TFB_ERR_ARG;
-      p.tp_rows_per_shard = M / tp->world;
+    if (gmode != 0 || tp->mode < 1 || tp->mode > 7 || (tp->mode & (TP_AG | TP_RS)) == (TP_AG | TP_RS)) return TFB_ERR_ARG;
+    if (tp->mode & (TP_AG | TP_WG)) {
+      if (tp->copy_ctas < 1 || tp->copy_ctas >= sms) return TFB_ERR_ARG;
+      p.tp_copy_ctas = tp->copy_ctas;
+      sms -= tp->copy_ctas;
     }
-    p.tp_mode = tp->mode; p.tp_rank = tp->rank; p.tp_world = tp->world;
-    p.tp_copy_ctas = (tp->mode == 1 || tp->mode == 3) ? tp->copy_ctas : 0; p.tp_epoch = tp->epoch; p.tp_ready = tp->ready;
-    p.tp_peer_a = static_cast<const __nv_bfloat16* const*>(tp->peer_a);
-    p.tp_peer_c = static_cast<__nv_bfloat16* const*>(tp->peer_c);
-    if (tp->mode == 1 || tp->mode == 3) sms -= tp->copy_ctas;
+    if (tp->mode & (TP_AG | TP_RS)) {
+      if (tp->world < 1 || M % (tp->world * BM) || a_mn || out_mode != 0) return TFB_ERR_ARG;
+    }
+    if (tp->mode & TP_AG) {
+      if (K % 8 || !tp->ready || !tp->peer_a) return TFB_ERR_ARG;
+      p.ag.rank = tp->rank; p.ag.world = tp->world; p.ag.rows_per_shard = M / tp->world; p.ag.row_len = K;
+      p.ag.epoch = tp->epoch; p.ag.rows = M; p.ag.src_is_full = 1; p.ag.skip_local = 1; p.ag.ready = tp->ready;
+      p.ag.src = static_cast<const __nv_bfloat16* const*>(tp->peer_a);
+      p.ag.dst = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(A));
+      p.ag.ld = lda;
+    }
+    if (tp->mode & TP_RS) {
+      if (!tp->peer_c) return TFB_ERR_ARG;
+      p.rs_rank = tp->rank; p.rs_world = tp->world; p.rs_rows_per_shard = M / tp->world;
+      p.rs_peer_c = static_cast<__nv_bfloat16* const*>(tp->peer_c);
+    }
+    if (tp->mode & TP_WG) {
+      // gathered B: rows = N (K-major B) or K (MN-major B), sharded in 128-row blocks over the data-parallel group
+      const int rows = b_mn ? K : N, row_len = b_mn ? N : K;
+      if (tp->wg_world < 1 || tp->wg_rows < rows || tp->wg_rows % (tp->wg_world * BM) || row_len % 8 || out_mode == 2 ||
+          !tp->wg_ready || !tp->wg_src)
+        return TFB_ERR_ARG;
+      p.wg.rank = tp->wg_rank; p.wg.world = tp->wg_world; p.wg.rows_per_shard = tp->wg_rows / tp->wg_world;
+      p.wg.row_len = row_len; p.wg.epoch = tp->wg_epoch; p.wg.rows = rows; p.wg.src_is_full = 0; p.wg.skip_local = 0;
+      p.wg.ready = tp->wg_ready;
+      p.wg.src = static_cast<const __nv_bfloat16* const*>(tp->wg_src);
+      p.wg.dst = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(B));
+      p.wg.ld = ldb;
+      if (!b_mn) p.wg_n_shift = (tp->wg_rank * (p.wg.rows_per_shard / BN)) % p.tiles_n;
+      else p.wg_k_shift = (tp->wg_rank * (p.wg.rows_per_shard / BK)) % ((K + BK - 1) / BK);
+    }
+    p.tp_mode = tp->mode;
   }
   const int total_kb = (K + BK - 1) / BK;
   const int tiles = p.tiles_m * p.tiles_n;
@@ -820,7 +919,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   p.kb_per_split = (total_kb + splits - 1) / splits;
   p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
   const long long work = (long long)tiles * (gmode == 2 ? E : p.splits);
-  const int grid = int(work < sms ? work : sms) + p.tp_copy_ctas;
+  const int grid = int(work < sms ? work : sms) + p.tp_copy_ctas;   // copy CTAs take the lowest block indices
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (BN == 256) {
@@ -862,13 +961,16 @@ TFB_API int tfb_gemm_bf16_grouped(const void* A, long long lda, int a_mn, const 
                    status, stream);
 }
 
-// Tensor-parallel fused forms (see TfbGemmTp and tp_fused.cu).  Mode 1: C[M, N] = gathered A [M, K] . B^T where
-// A's row shards live on the W ranks.  Mode 2: C is ignored; partial products go to the peers' staging buffers
-// (row pitch ldc) and are summed by tfb_tp_reduce.  Mode 3: B is the gathered weight (tp->peer_a holds the W base
-// addresses of the gather buffers, row-sharded); the peers' shards are pulled while the tiles of the local shard run.
+// Fused compute + collective forms (see TfbGemmTp and tp_fused.cu).  Bit 1: C[M, N] = gathered A [M, K] . B^T where
+// A's row shards live on the W tensor-parallel ranks.  Bit 2: C is ignored; partial products go to the peers' staging
+// buffers (row pitch ldc) and are summed by tfb_tp_reduce.  Bit 4: B is the local gather buffer of a weight whose row
+// shards live on the data-parallel ranks (tp->wg_src); the shards are pulled while the tiles of the local shard run.
+// `residual` ([M, ldr] bf16, added in the epilogue) is allowed when bit 2 is clear.
 TFB_API int tfb_gemm_bf16_tp(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* C,
-                             long long ldc, int M, int N, int K, const TfbGemmTp* tp, int* status, void* stream) {
-  if (!tp || tp->mode < 1 || tp->mode > 3) return TFB_ERR_ARG;
-  return gemm_impl(A, lda, 0, B, ldb, b_mn, C, ldc, M, N, K, nullptr, nullptr, 0, 1.0f, 0, 0, 0, nullptr, status,
+                             long long ldc, int M, int N, int K, const void* residual, long long ldr,
+                             const TfbGemmTp* tp, int* status, void* stream) {
+  if (!tp || tp->mode < 1 || tp->mode > 7) return TFB_ERR_ARG;
+  if (residual && (tp->mode & 2)) return TFB_ERR_ARG;
+  return gemm_impl(A, lda, 0, B, ldb, b_mn, C, ldc, M, N, K, nullptr, residual, ldr, 1.0f, 0, 0, 0, nullptr, status,
                    stream, tp);
 }

@@ -2,11 +2,12 @@
 
 ``FullyShardedDataParallel`` keeps 1/W of every weight matrix (contiguous 128-row blocks) plus the matching fp32 master /
 Adam state on each rank.  A forward or backward GEMM that needs the whole matrix gathers it *inside the GEMM launch*:
-the weight lives in a symmetric buffer, a few CTAs of the kernel pull the peers' row blocks over NVLink and raise a
-flag per block while the remaining CTAs already multiply the tiles of the local shard (``tfb_gemm_bf16_tp`` mode 3).
-Gradients are reduce-scattered and the local shards updated by the fused ZeRO kernels; no parameter all-gather follows
-the update, because the next step's GEMMs pull what they need.  On CPU / gloo (tests) the same schedule runs with
-``all_gather_into_tensor`` / reduce-scatter collectives.
+a few CTAs of the kernel pull the ranks' row shards over NVLink into one of two per-block gather buffers and raise a flag
+per 128-row block while the remaining CTAs already multiply the tiles of the local shard (``tfb_gemm_bf16_tp`` bit 4).
+Gradients are reduce-scattered block by block while backward continues and the local shards are updated by one fused
+AdamW; no parameter all-gather follows the update, because the next step's GEMMs pull what they need.  On CPU / gloo
+(tests) the same schedule runs with all-gather / reduce-scatter collectives.  The engine itself is
+``parallel.sharded.ShardedEngine``, which also composes this with tensor parallelism.
 
 Also here: ``ZeroOptimizer`` (stage 1/2 facade with the reference's method names), ``CPUOffloadEngine`` (pinned host
 pool + side stream for optimizer state), ``ActivationCheckpointing`` and ``profile_memory``.
@@ -16,14 +17,12 @@ Reference counterparts: include/quant/fsdp.h:18-155 + src/trainer/fsdp.cpp (forw
 :366-603, zero_offload.cpp."""
 from __future__ import annotations
 
-import ctypes as C
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 
-from ..ops import _lib, functional as F
 from .collectives import DistributedContext
 
 
@@ -51,209 +50,91 @@ class MemoryProfile:
     total: int = 0
 
 
-class ShardedWeight:
-    """One weight matrix [rows, cols] sharded by rows.  ``full`` is a [rows_padded, cols] gather buffer (symmetric on
-    GPUs); this rank's rows are always valid in place, the others only after a gather."""
-
-    def __init__(self, name, param, rank, world, symm=None):
-        self.name, self.param, self.rank, self.world = name, param, rank, world
-        rows, cols = param.shape
-        gran = 128 * world
-        self.rows, self.cols = rows, cols
-        self.rows_p = (rows + gran - 1) // gran * gran
-        self.per = self.rows_p // world
-        dev, dt = param.device, param.dtype
-        self.symm_buf = None
-        if symm is not None:
-            self.symm_buf = symm.alloc(self.rows_p * cols, dt)
-            self.full = self.symm_buf.view(dt, self.rows_p * cols).view(self.rows_p, cols)
-            self.full.zero_()
-        else:
-            self.full = torch.zeros((self.rows_p, cols), dtype=dt, device=dev)
-        self.full[:rows].copy_(param.data)
-        lo = rank * self.per
-        self.shard = self.full[lo:lo + self.per]                   # bf16 / compute-dtype shard, in place
-        self.master = self.shard.float().clone()
-        self.m = torch.zeros_like(self.master)
-        self.v = torch.zeros_like(self.master)
-        self.ready = torch.zeros(self.rows_p // 128, dtype=torch.int32, device=dev) if symm is not None else None
-        self.epoch = 0
-        param.data = self.full[:rows]                               # the model's kernels read the gather buffer
-
-    def scrub_remote(self):
-        """Forget the peers' rows (what ZeRO-3 frees between uses); used by tests to prove that gathers happen."""
-        lo = self.rank * self.per
-        self.full[:lo].zero_()
-        self.full[lo + self.per:].zero_()
-
-
 class FullyShardedDataParallel:
+    """ZeRO stage 3 over the ranks of ``ctx`` with the reference's method names; the work is done by
+    ``parallel.sharded.ShardedEngine`` (tensor-parallel degree 1 here; ``parallel.launch`` builds the dp x tp form).
+
+    ``symm``: symmetric heap over the same ranks.  With it (CUDA) the weight gather runs inside the consuming GEMM, the
+    gradient reduce-scatter is one peer-memory kernel per block overlapped with backward, and the shard update is one fused
+    AdamW; without it the same schedule uses the library collectives."""
+
     def __init__(self, model, cfg: Optional[FSDPConfig] = None, ctx: Optional[DistributedContext] = None, symm=None):
+        from .sharded import Mesh, ShardedEngine
         self.model, self.cfg = model, cfg or FSDPConfig()
         self.ctx = ctx or DistributedContext.init()
         self.rank, self.world = self.ctx.rank, self.ctx.world_size
         self.symm = symm
+        c = self.cfg
+        mesh = Mesh(self.rank, self.world, 0, 1, self.ctx.group, None, self.ctx.group)
+        fused = symm is not None and model.tok_embeddings.is_cuda and self.world > 1
+        self.engine = ShardedEngine.from_dense(model, mesh, comm="fused" if fused else "nccl", dp_heap=symm if fused else None,
+                                               lr=c.lr, betas=c.betas, eps=c.eps, weight_decay=c.weight_decay,
+                                               max_grad_norm=c.max_grad_norm, copy_ctas=c.copy_ctas)
+        self.engine.activation_checkpointing = c.activation_checkpointing
+        self.weights = list(self.engine.params.values())
         self.step_count = 0
-        model.flatten()
-        self.weights: List[ShardedWeight] = []
-        self.small: List[torch.nn.Parameter] = []     # norms, biases, embeddings: replicated, gradients all-reduced
-        for n, p in model.named_parameters():
-            if p.dim() == 2 and p.shape[0] >= 128 * self.world and n not in ("tok_embeddings", "lm_head", "pos_embeddings"):
-                self.weights.append(ShardedWeight(n, p, self.rank, self.world, symm))
-            else:
-                self.small.append(p)
-        self._by_param = {id(w.param): w for w in self.weights}
-        self.small_state = [(p.data.float().clone(), torch.zeros(p.shape, device=p.device), torch.zeros(p.shape, device=p.device))
-                            for p in self.small]
-        self._install_hooks()
-        self.gathers = 0
 
-    # ---- gather ------------------------------------------------------------------------------------------------
-    def gather(self, w: ShardedWeight):
-        """Make every row of ``w.full`` valid on this rank (library path; the fused path does this inside the GEMM)."""
-        if self.world == 1:
-            return
-        dist.all_gather_into_tensor(w.full.view(-1), w.shard.contiguous().view(-1), group=self.ctx.group)
-        self.gathers += 1
+    @property
+    def gathers(self):
+        return self.engine.gathers
 
-    def _install_hooks(self):
-        """Route the model's linear layers through gemm_gathered for sharded weights."""
-        fsdp = self
-        orig = F.gemm
-
-        def gemm(a, b, *args, **kw):
-            base = b._base if b._base is not None else b
-            w = fsdp._by_storage.get(base.data_ptr()) if hasattr(fsdp, "_by_storage") else None
-            if w is None or fsdp.world == 1 or kw.get("a_mn"):
-                return orig(a, b, *args, **kw)
-            return fsdp.gemm_gathered(a, w, b, orig, *args, **kw)
-        self._by_storage = {w.full.data_ptr(): w for w in self.weights}
-        self._gemm = gemm
-
-    def gemm_gathered(self, a, w: ShardedWeight, b_view, orig, *args, **kw):
-        fused = self.symm is not None and a.is_cuda and not kw.get("bias") is not None and kw.get("residual") is None \
-            and kw.get("act") is None and kw.get("out_dtype") in (None, torch.bfloat16) and not kw.get("accumulate") \
-            and b_view.shape[0] == w.rows_p
-        if not fused:
-            self.gather(w)
-            return orig(a, b_view, *args, **kw)
-        b_mn = bool(kw.get("b_mn"))
-        M, K = a.shape
-        N = w.cols if b_mn else w.rows_p
-        out = kw.get("out")
-        y = out if out is not None else torch.empty((M, N), dtype=a.dtype, device=a.device)
-        from .tp import _Tp, _fn
-        self.symm.barrier()                       # every rank's shard holds this step's values
-        w.epoch += 1
-        tp = _Tp(3, self.rank, self.world, self.cfg.copy_ctas, w.epoch, w.ready.data_ptr(), w.symm_buf.ptrs.data_ptr(), None)
-        _lib.check(_fn()(a.data_ptr(), a.stride(0), w.full.data_ptr(), w.full.stride(0), int(b_mn), y.data_ptr(), y.stride(0),
-                         M, N, K, C.byref(tp), _lib.status_word(a.device).data_ptr(), _lib.stream()), "gemm_weight_gather")
-        self.gathers += 1
-        return y
+    @property
+    def last_grad_norm(self):
+        return float(self.engine.last_grad_norm)
 
     # ---- step --------------------------------------------------------------------------------------------------
     def forward_backward(self, ids, labels):
-        import transformers_fusion_b200.models.dense as dense_mod
-        saved = dense_mod.F.gemm
-        dense_mod.F.gemm = self._gemm
-        try:
-            if self.cfg.activation_checkpointing:
-                self.model.activation_checkpointing = True
-            return self.model.forward_backward(ids, labels)
-        finally:
-            dense_mod.F.gemm = saved
+        """Forward + backward of the local batch; the gradient reduce-scatter of each block is issued as soon as that
+        block's backward is complete (reduce_scatter_grads of the reference, fsdp.cpp:508-543)."""
+        return self.engine.forward_backward(ids, labels)
 
     def forward(self, ids):
-        import transformers_fusion_b200.models.dense as dense_mod
-        saved = dense_mod.F.gemm
-        dense_mod.F.gemm = self._gemm
-        try:
-            with torch.no_grad():
-                return self.model.forward(ids)
-        finally:
-            dense_mod.F.gemm = saved
-
-    def reduce_scatter_grads(self):
-        """Average gradients over ranks; each rank keeps the fp32 gradient of its own row shard."""
-        W = self.world
-        out = []
-        for w in self.weights:
-            g = w.param.main_grad                                   # [rows, cols] fp32
-            gp = torch.zeros((w.rows_p, w.cols), dtype=torch.float32, device=g.device)
-            gp[: w.rows].copy_(g)
-            if W > 1:
-                out.append(self.ctx.reduce_scatter(gp, "avg"))
-            else:
-                out.append(gp)
-        for p in self.small:
-            if W > 1:
-                self.ctx.all_reduce(p.main_grad, "avg")
-        return out
-
-    def clip_gradients(self, shard_grads, max_norm: float) -> float:
-        ss = sum(float((g * g).sum()) for g in shard_grads)
-        t = torch.tensor([ss], device=self.model.tok_embeddings.device)
-        if self.world > 1:
-            self.ctx.all_reduce(t, "sum")
-        ss = float(t) + sum(float((p.main_grad * p.main_grad).sum()) for p in self.small)
-        norm = ss ** 0.5
-        self.last_grad_norm = norm
-        return min(1.0, max_norm / (norm + 1e-6)) if max_norm > 0 else 1.0
+        """Logits [B, S, V] of the current weights (gathers the whole model into ``self.model``: evaluation helper)."""
+        self.consolidate()
+        with torch.no_grad():
+            return self.model.forward(ids)
 
     def optimizer_step(self, lr: Optional[float] = None):
-        c = self.cfg
-        lr = c.lr if lr is None else lr
         self.step_count += 1
-        t = self.step_count
-        grads = self.reduce_scatter_grads()
-        clip = self.clip_gradients(grads, c.max_grad_norm)
-        b1, b2 = c.betas
-        bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
-
-        def adam(master, m, v, g, wd):
-            g = g * clip
-            m.mul_(b1).add_(g, alpha=1 - b1)
-            v.mul_(b2).addcmul_(g, g, value=1 - b2)
-            master.mul_(1 - lr * wd).addcdiv_(m / bc1, (v / bc2).sqrt().add_(c.eps), value=-lr)
-        for w, g in zip(self.weights, grads):
-            adam(w.master, w.m, w.v, g, c.weight_decay)
-            w.shard.copy_(w.master.to(w.shard.dtype))
-        for p, (master, m, v) in zip(self.small, self.small_state):
-            adam(master, m, v, p.main_grad, 0.0 if p.dim() < 2 else c.weight_decay)
-            p.data.copy_(master.to(p.dtype))
-        self.zero_grad()
+        self.engine.optimizer_step(lr)
 
     def train_step(self, ids, labels, lr=None):
         loss = self.forward_backward(ids, labels)
         self.optimizer_step(lr)
         return loss
 
+    def clip_gradients(self, max_norm: float) -> float:
+        """Sets the clip threshold used by the next optimizer_step (the norm is global over all shards)."""
+        self.engine.max_grad_norm = max_norm
+        return self.last_grad_norm
+
     def zero_grad(self):
-        self.model.flat.zero_grad()
+        self.engine.full_grad.zero_()
+        self.engine.gshard.zero_()
+        self.engine.small_grad.zero_()
 
     def scrub(self):
-        for w in self.weights:
-            w.scrub_remote()
+        """Forget every gathered weight (the engine does this itself after each optimizer step)."""
+        self.engine.invalidate_gathers()
 
     def consolidate(self):
-        """Gather every weight (for checkpointing or evaluation)."""
-        for w in self.weights:
-            self.gather(w)
+        """Gather every weight into ``self.model`` (for checkpointing or evaluation)."""
+        self.engine.export_to(self.model)
 
     def profile_memory(self) -> MemoryProfile:
-        esz = self.model.tok_embeddings.element_size()
-        sharded = sum(w.per * w.cols for w in self.weights)
-        small = sum(p.numel() for p in self.small)
+        mp_ = self.engine.memory_profile()
         mp = MemoryProfile()
-        mp.parameters = (sharded + small) * esz
-        mp.gradients = self.model.flat.numel * 4
-        mp.optimizer_state = (sharded + small) * 12
-        mp.total = mp.parameters + mp.gradients + mp.optimizer_state
+        mp.parameters = mp_["parameters"] + mp_["gather_buffers"]
+        mp.gradients = mp_["gradients"]
+        mp.optimizer_state = mp_["optimizer_state"]
+        mp.total = mp_["total"]
         return mp
 
     def memory_savings_ratio(self) -> float:
-        full = sum(w.rows * w.cols for w in self.weights) + sum(p.numel() for p in self.small)
-        mine = sum(w.per * w.cols for w in self.weights) + sum(p.numel() for p in self.small)
+        """Fraction of the parameter + optimizer-state bytes this rank does not hold."""
+        e = self.engine
+        full = sum(p.rows * p.cols for p in e.params.values()) + e.small_lp.numel()
+        mine = e.shard_numel + e.small_lp.numel()
         return 1.0 - mine / max(1, full)
 
     @staticmethod
@@ -263,24 +144,26 @@ class FullyShardedDataParallel:
 
 
 class FSDPBlock:
-    """Per-block view: gather one block's weights ahead of use (``gather_and_install``), and drop them afterwards."""
+    """Per-block view: which sharded weights belong to a layer, and their gather / gradient state."""
 
     def __init__(self, fsdp: FullyShardedDataParallel, layer_index: int):
         self.fsdp = fsdp
-        pre = f"layers.{layer_index}."
-        self.weights = [w for w in fsdp.weights if w.name.startswith(pre)]
+        self.unit = 1 + layer_index
+        self.weights = list(fsdp.engine.units[self.unit])
 
     def gather_and_install(self):
-        for w in self.weights:
-            self.fsdp.gather(w)
+        """Full matrices of the block's weights (library gather; the training path gathers inside its GEMMs)."""
+        e = self.fsdp.engine
+        return {p.name: e.gather_full(p.name) for p in self.weights}
 
     def release(self):
-        for w in self.weights:
-            w.scrub_remote()
+        for p in self.weights:
+            p.gathered = False
 
     def shard_gradients(self):
-        return [self.fsdp.ctx.reduce_scatter(torch.nn.functional.pad(w.param.main_grad, (0, 0, 0, w.rows_p - w.rows)), "avg")
-                for w in self.weights]
+        """This rank's reduced fp32 gradient shards of the block (valid after the block's backward)."""
+        e = self.fsdp.engine
+        return [e.gshard[p.shard_off:p.shard_off + p.per * p.cols].view(p.per, p.cols) for p in self.weights]
 
 
 class ActivationCheckpointing:

@@ -6,10 +6,11 @@ fastest (tensor-parallel peers exchange the most data per step), then dp, then p
     rank = (pp_idx * dp + dp_idx) * tp + tp_idx
 
 ``init_parallel`` builds the groups; ``fit_parallel`` runs the training loop that matches the factors:
-  tp > 1          TPDenseModel + TPTrainer (fused all-gather->GEMM / GEMM->reduce-scatter), gradients averaged over dp
+  tp > 1 or zero stage 3   ShardedEngine: ZeRO-3 over the dp ranks x tensor + sequence parallelism over the tp ranks
+                  (weight gather, all-gather->GEMM and GEMM->reduce-scatter inside the GEMM launches; symmetric heaps per
+                  dp group and per tp group).  Model shapes it does not cover fall back to TPDenseModel + TPTrainer.
   ep > 1          MoE model with the experts of every layer spread over the ranks (fused dispatch / combine), EPTrainer
   pp > 1          PipelineParallel 1F1B over the layer ranges, AdamW on the parameters each stage owns
-  zero stage 3    FullyShardedDataParallel (weights gathered inside the consuming GEMM on CUDA)
   otherwise       the ordinary Trainer: data parallel with ZeRO stage 0 / 1 / 2 (fused reduce-scatter + AdamW)
 
 Reference counterparts: DistributedContext (src/trainer/distributed.cpp:21-123), FSDP / DDP / pipeline /
@@ -131,18 +132,49 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
 
     import time
     t0, toks, loss = time.perf_counter(), 0, 0.0
+    sharded_ok = _sharded_supported(model.cfg, st) and st.pp == 1 and st.ep == 1
+    if sharded_ok and (st.tp > 1 or (getattr(cfg, "zero_stage", 0) >= 3 and st.world > 1)):
+        # ZeRO-3 over the dp ranks composed with tensor + sequence parallelism over the tp ranks; symmetric heaps span
+        # exactly the dp group and the tp group of this rank, so the fused kernels work on any dp x tp factoring
+        from .sharded import Mesh, ShardedEngine
+        dp_heap = tp_heap = None
+        comm = "nccl"
+        if st.device.type == "cuda" and os.environ.get("TFB_COMM", "fused") == "fused":
+            from .symm import SymmetricHeap
+            comm = "fused"
+            if st.dp > 1:
+                dp_heap = SymmetricHeap(st.dp_rank, st.dp, st.device, group=st.dp_group)
+            if st.tp > 1:
+                tp_heap = SymmetricHeap(st.tp_rank, st.tp, st.device, group=st.tp_group)
+        mesh = Mesh(st.dp_rank, st.dp, st.tp_rank, st.tp, st.dp_group, st.tp_group, None)
+        eng = ShardedEngine.from_dense(model, mesh, comm=comm, dp_heap=dp_heap, tp_heap=tp_heap, lr=cfg.learning_rate,
+                                       weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
+                                       max_tokens=cfg.batch_size * cfg.seq_length)
+        for step in range(1, steps + 1):
+            ids, labels = dl.next_batch()
+            lt = eng.train_step(ids, labels, lr_at(step)).detach().float().reshape(1).clone()
+            if st.dp > 1:
+                dist.all_reduce(lt, group=st.dp_group)
+            loss = float(lt) / st.dp
+            toks += ids.numel() * st.dp
+            report(step, loss, lr_at(step), toks, t0)
+        eng.export_to(model)
+        if st.is_main:
+            Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
+        return loss
     if st.tp > 1:
+        # model shapes the sharded engine does not cover (LayerNorm, biases, learned positions): autograd-level tensor
+        # parallelism with library collectives, gradients averaged over dp
         from .tp_model import TPDenseModel, TPGroup, TPTrainer
         ctx = None
-        if st.device.type == "cuda":
+        if st.device.type == "cuda" and os.environ.get("TFB_COMM", "fused") == "fused":
             from .symm import SymmetricHeap
             from .tp import TpContext
             c = model.cfg
             T = cfg.batch_size * cfg.seq_length
             widest = max(c.hidden_size, 2 * c.ffn_hidden_size // st.tp, (c.num_heads + 2 * c.num_kv_heads) * c.head_dim // st.tp)
-            # symmetric memory spans the ranks of the TP group only when the whole world is that group
-            if st.tp == st.world:
-                ctx = TpContext(SymmetricHeap(st.rank, st.world, st.device), st.tp_rank, st.tp, T, widest, widest, copy_ctas=8)
+            ctx = TpContext(SymmetricHeap(st.tp_rank, st.tp, st.device, group=st.tp_group), st.tp_rank, st.tp, T, widest, widest,
+                            copy_ctas=8)
         tpm = TPDenseModel(model, TPGroup(st.tp_rank, st.tp, st.tp_group, ctx))
         tr = TPTrainer(tpm, cfg.learning_rate, cfg.weight_decay, cfg.max_grad_norm, st.dp_group if st.dp > 1 else None)
         for step in range(1, steps + 1):
@@ -201,26 +233,7 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
             Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
         return loss
     if getattr(cfg, "zero_stage", 0) >= 3 and st.world > 1:
-        # ZeRO-3 / FSDP: weights, gradients and optimiser state sharded; on CUDA the weight all-gather runs inside the GEMM
-        from .collectives import DistributedContext
-        from .fsdp import FSDPConfig, FullyShardedDataParallel
-        symm = None
-        if st.device.type == "cuda":
-            from .symm import SymmetricHeap
-            symm = SymmetricHeap(st.rank, st.world, st.device)
-        fsdp = FullyShardedDataParallel(model, FSDPConfig(), DistributedContext(st.rank, st.world, None), symm)
-        for step in range(1, steps + 1):
-            ids, labels = dl.next_batch()
-            l = fsdp.train_step(ids, labels, lr_at(step))
-            lt = torch.as_tensor(float(l), device=st.device).reshape(1)
-            dist.all_reduce(lt)
-            loss = float(lt) / st.world
-            toks += ids.numel() * st.dp
-            report(step, loss, lr_at(step), toks, t0)
-        fsdp.consolidate()
-        if st.is_main:
-            Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
-        return loss
+        raise ValueError("--zero-stage 3 covers RoPE + RMSNorm models without biases; use --zero-stage 2 for this model")
     tr = Trainer(model, tok).compile(None, cfg)
     if log:
         tr.set_log_callback(lambda m: st.is_main and log(m.step, m.loss, m.perplexity, m.learning_rate, m.tokens_per_sec * st.dp))
@@ -230,6 +243,14 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
         tr.cfg.save_interval = 1 << 60                 # only rank 0 writes checkpoints
     tr.fit(dl)
     return tr.metrics().loss
+
+
+def _sharded_supported(c, st) -> bool:
+    """Model shapes parallel.sharded.ShardedEngine covers on this mesh."""
+    return (getattr(c, "norm_type", "") == "rmsnorm" and not c.use_parallel_residual and not c.attention_bias and
+            c.position_type == "rope" and not hasattr(c, "num_experts") and c.num_heads % st.tp == 0 and
+            c.num_kv_heads % st.tp == 0 and c.ffn_hidden_size % st.tp == 0 and c.vocab_size % st.tp == 0 and
+            getattr(c, "mtp_num_heads", 0) == 0)
 
 
 def _single(cfg):

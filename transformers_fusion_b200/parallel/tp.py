@@ -21,17 +21,66 @@ from ..ops._lib import c_i, c_ll, c_p, check, stream
 
 
 class _Tp(C.Structure):
+    """Mirror of TfbGemmTp (csrc/kernels/gemm_bf16.cu): ``mode`` bits 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter,
+    4 weight gather -> GEMM."""
     _fields_ = [("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int), ("epoch", C.c_int),
-                ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p)]
+                ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p),
+                ("wg_rank", C.c_int), ("wg_world", C.c_int), ("wg_epoch", C.c_int), ("wg_rows", C.c_int),
+                ("wg_ready", C.c_void_p), ("wg_src", C.c_void_p)]
 
 
 def _fn():
     fn = _lib.lib().tfb_gemm_bf16_tp
-    fn.argtypes = [c_p, c_ll, c_p, c_ll, c_i, c_p, c_ll, c_i, c_i, c_i, C.POINTER(_Tp), c_p, c_p]
+    fn.argtypes = [c_p, c_ll, c_p, c_ll, c_i, c_p, c_ll, c_i, c_i, c_i, c_p, c_ll, C.POINTER(_Tp), c_p, c_p]
     fn.restype = c_i
     _lib.lib().tfb_tp_reduce.argtypes = [c_p, c_p, c_p, c_ll, c_i, c_i, c_p]
     _lib.lib().tfb_tp_reduce.restype = c_i
     return fn
+
+
+class WeightGather:
+    """What the GEMM needs to pull a row-sharded weight (ZeRO-3 / FSDP) into its local gather buffer while it runs:
+    ``buf`` [rows_p, cols] local bf16 gather buffer, ``src`` device int64[world] with the base address of every rank's
+    shard ([rows_p / world, cols], symmetric memory), ``ready`` local int32[rows_p / 128] flags and the value ``epoch``
+    they take once a block has landed (one more than at the previous gather into the same flags)."""
+    __slots__ = ("buf", "src", "ready", "epoch", "rank", "world", "rows_p")
+
+    def __init__(self, buf, src, ready, epoch, rank, world):
+        self.buf, self.src, self.ready, self.epoch, self.rank, self.world = buf, src, ready, epoch, rank, world
+        self.rows_p = buf.shape[0]
+
+
+def fused_gemm(x, w, *, b_mn=False, n=None, k=None, out=None, residual=None, tp=None, wg: WeightGather = None, copy_ctas=8):
+    """One launch of the tcgen05 GEMM with a collective folded in: ``tp`` = (mode bit 1 or 2, rank, world, epoch, ready,
+    peer_a ptrs, peer_c ptrs) for the tensor-parallel all-gather / reduce-scatter, ``wg`` for the weight gather.
+    x [M, K]; ``w`` [N, K] (or [K, N] with ``b_mn``; for a gathered weight pass the gather buffer's view); returns y
+    [M, N] (None for the reduce-scatter form, whose partial products go to the peers' staging buffers)."""
+    M = x.shape[0]
+    K = k if k is not None else x.shape[1]
+    N = n if n is not None else (w.shape[1] if b_mn else w.shape[0])
+    d = _Tp()
+    mode = 0
+    if tp is not None:
+        mode |= tp[0]
+        d.rank, d.world, d.epoch = tp[1], tp[2], tp[3]
+        d.ready, d.peer_a, d.peer_c = tp[4], tp[5], tp[6]
+    if wg is not None:
+        mode |= 4
+        d.wg_rank, d.wg_world, d.wg_epoch, d.wg_rows = wg.rank, wg.world, wg.epoch, wg.rows_p
+        d.wg_ready, d.wg_src = wg.ready.data_ptr(), wg.src.data_ptr()
+    d.mode, d.copy_ctas = mode, copy_ctas
+    y = None
+    if not (mode & 2):
+        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ldc = y.stride(0) if y is not None else N
+    check(_fn()(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn), ptr_or_none(y), ldc, M, N, K,
+                ptr_or_none(residual), residual.stride(0) if residual is not None else 0, C.byref(d),
+                _lib.status_word(x.device).data_ptr(), stream()), "fused_gemm")
+    return y
+
+
+def ptr_or_none(t):
+    return None if t is None else t.data_ptr()
 
 
 # ---------------------------------------------------------------------------------------------- splits
@@ -75,32 +124,30 @@ class TpContext:
         self.epoch = 0
         self.parity = 0
 
-    def all_gather_gemm(self, x_shard, w, out=None, b_mn=False):
-        """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K], or [K, N_local] with ``b_mn``."""
+    def all_gather_gemm(self, x_shard, w, out=None, b_mn=False, wg: WeightGather = None, n=None, k=None):
+        """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K], or [K, N_local] with ``b_mn``.  With ``wg`` the
+        weight's row shards are gathered over the data-parallel group inside the same launch."""
         Ms, K = x_shard.shape
-        M, N = Ms * self.world, (w.shape[1] if b_mn else w.shape[0])
+        M = Ms * self.world
         buf = self.gather[self.parity]
         xg = buf.view(torch.bfloat16, M * K).view(M, K)
         xg[self.rank * Ms:(self.rank + 1) * Ms].copy_(x_shard)      # producer kernels may write here directly
         self.symm.barrier()                                           # every rank's shard is in place
         self.epoch += 1
-        y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x_shard.device)
-        tp = _Tp(1, self.rank, self.world, self.copy_ctas, self.epoch, self.ready.data_ptr(), buf.ptrs.data_ptr(), None)
-        check(_fn()(xg.data_ptr(), K, w.data_ptr(), w.stride(0), int(b_mn), y.data_ptr(), y.stride(0), M, N, K, C.byref(tp),
-                    _lib.status_word(x_shard.device).data_ptr(), stream()), "all_gather_gemm")
+        tp = (1, self.rank, self.world, self.epoch, self.ready.data_ptr(), buf.ptrs.data_ptr(), None)
+        y = fused_gemm(xg, w, b_mn=b_mn, n=n, k=k, out=out, tp=tp, wg=wg, copy_ctas=self.copy_ctas)
         self.parity ^= 1
         return y, xg
 
-    def gemm_reduce_scatter(self, x, w, residual=None, b_mn=False):
+    def gemm_reduce_scatter(self, x, w, residual=None, b_mn=False, wg: WeightGather = None, n=None, k=None):
         """x [M, K_local], ``w`` [N, K_local] (or [K_local, N] with ``b_mn``) -> y_shard [M/W, N] = sum over ranks of the
-        partial products."""
-        M, K = x.shape
-        N = w.shape[1] if b_mn else w.shape[0]
+        partial products (+ ``residual`` [M/W, N])."""
+        M = x.shape[0]
+        N = n if n is not None else (w.shape[1] if b_mn else w.shape[0])
         Ms = M // self.world
         buf = self.stage[self.parity]
-        tp = _Tp(2, self.rank, self.world, 0, 0, None, None, buf.ptrs.data_ptr())
-        check(_fn()(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn), None, N, M, N, K, C.byref(tp),
-                    _lib.status_word(x.device).data_ptr(), stream()), "gemm_reduce_scatter")
+        tp = (2, self.rank, self.world, 0, None, None, buf.ptrs.data_ptr())
+        fused_gemm(x, w, b_mn=b_mn, n=N, k=k, tp=tp, wg=wg, copy_ctas=self.copy_ctas)
         self.symm.barrier()                                           # all partial tiles have arrived
         out = torch.empty((Ms, N), dtype=torch.bfloat16, device=x.device)
         stage = buf.view(torch.bfloat16, self.world * Ms * N)
