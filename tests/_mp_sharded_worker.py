@@ -32,7 +32,9 @@ def main():
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(st.device)
     labels = torch.roll(ids, -1, 1)
-    kw = dict(lr=1e-2, betas=(0.9, 0.95), weight_decay=0.0, max_grad_norm=0.5)
+    # bf16 on GPUs: Adam turns rounding noise in near-zero gradients into full-size steps, so the weight comparison there
+    # uses a small learning rate (the losses and the gradient norm carry the check)
+    kw = dict(lr=1e-3 if cuda else 1e-2, betas=(0.9, 0.95), weight_decay=0.0, max_grad_norm=0.5)
     ref = DenseModel(cfg, device=st.device, dtype=dt, seed=3)
     src = DenseModel(cfg, device=st.device, dtype=dt, seed=3)
     dp_heap = tp_heap = None
@@ -73,6 +75,7 @@ def main():
         scale = float(refp[n].float().abs().max()) + 1e-6
         werr = max(werr, float((p.float() - refp[n].float()).abs().max()) / scale)
     res["weight_err"] = werr
+    res["losses"] = [float(x) for x in res.get("losses", [])]
     res["grad_norm"] = float(eng.last_grad_norm)
     res["ref_grad_norm"] = float(ref_eng.opt.grad_norm)
     mp = eng.memory_profile()

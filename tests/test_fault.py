@@ -111,7 +111,7 @@ def test_heap_reset_after_timed_out_wait():
     past anything in flight and leaves the heap usable (the failure is a flag that nothing sets; no GPU fault)."""
     from transformers_fusion_b200.ops import _lib
     from transformers_fusion_b200.parallel.symm import SymmetricHeap
-    dev = torch.device("cuda")
+    dev = torch.device("cuda", 0)
     heap = SymmetricHeap(0, 1, dev)
     ticket = torch.full((1,), 7, dtype=torch.int32, device=dev)        # a last-CTA counter left at a partial count
     heap.on_reset(ticket.zero_)

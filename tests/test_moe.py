@@ -100,3 +100,70 @@ def test_router_stats_and_pad_zeroing_gpu():
     for e in range(E):                                                     # rows of expert e lie inside its segment
         r = rows[(idx.reshape(-1) == e)]
         assert r.numel() == int(counts[e]) and (r.numel() == 0 or (int(r.min()) >= seg[e] and int(r.max()) < seg[e] + int(counts[e])))
+
+
+def test_routing_rules_of_the_non_topk_variants():
+    """Expert choice, hierarchical and BASE-layer selections and the three capacity policies (models/moe_routing.py)."""
+    import torch
+    from transformers_fusion_b200.models import moe_routing as R
+    g = torch.Generator().manual_seed(0)
+    T, E = 64, 8
+    logits = torch.randn(T, E, generator=g) * 2
+    # expert choice: every expert holds exactly its capacity before the per-token cap, never more after it
+    sel = R.expert_choice(logits, 2.0, E)
+    C = R.expert_choice_capacity(T, E, 2.0)
+    assert C == 16 and bool((sel.sum(0) == C).all())
+    sel2 = R.expert_choice(logits, 2.0, 2)
+    assert bool((sel2.sum(1) <= 2).all()) and bool((sel2.sum(0) <= C).all()) and bool((sel2 <= sel).all())
+    # hierarchical: 4 groups of 2, two groups per token, one expert per chosen group
+    sel = R.hierarchical(logits, 4, 2, 1)
+    assert bool((sel.sum(1) == 2).all())
+    grp = sel.view(T, 4, 2).any(-1)
+    assert bool((grp.sum(1) == 2).all())
+    score = torch.logsumexp(logits.view(T, 4, 2), -1)
+    assert bool((grp == torch.zeros_like(grp).scatter(1, score.topk(2, 1).indices, True)).all())
+    # BASE layer: balanced, one expert per token
+    sel = R.base_layer(logits)
+    assert bool((sel.sum(1) == 1).all()) and int(sel.sum(0).max()) <= 8 and int(sel.sum(0).min()) >= 8
+    # capacity policies on skewed logits: expert 0 is everybody's favourite
+    skew = logits.clone()
+    skew[:, 0] += 6.0
+    cap = R.capacity_limit(T, E, 2, 1.0)
+    for pol in ("fixed", "token_drop", "token_pass"):
+        sel, pt = R.apply_capacity(skew, 2, 1.0, pol)
+        assert int(sel.sum(0).max()) <= cap, pol
+        assert bool((sel.sum(1) <= 2).all())
+        if pol == "fixed":
+            assert float(sel.sum()) > float(R.apply_capacity(skew, 2, 1.0, "token_drop")[0].sum())   # lost pairs were re-routed
+        if pol == "token_pass":
+            assert float(pt.max()) > 0 and float(pt.max()) <= 1.0
+        else:
+            assert float(pt.abs().max()) == 0
+
+
+def test_variant_models_route_by_their_rule():
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.moe import MoEAllConfig, create_moe_variant
+    base = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(1))
+    outs = {}
+    for name, kw in (("EXPERT_CHOICE", {}), ("HIERARCHICAL", dict(num_groups=4, top_groups=2)), ("BASE_LAYER", {}),
+                     ("SPARSE_TOPK", dict(capacity_policy="token_drop", capacity_factor=0.5)), ("SPARSE_TOPK", {})):
+        m = create_moe_variant(name, base, MoEAllConfig(num_experts=8, top_k=2, expert_hidden=32, **kw), device="cpu",
+                               dtype=torch.float32, seed=0)
+        m.flatten()
+        loss, ce, aux = m.loss(ids, torch.roll(ids, -1, 1))
+        loss.backward()
+        assert torch.isfinite(loss) and m.layers[0].router.grad is not None
+        blk = m.layers[0]
+        outs[(name, tuple(kw))] = float(ce.detach())
+        if name == "EXPERT_CHOICE":
+            assert int(blk.last_sel.sum(0).max()) <= 8           # capacity 2.0 * 32 / 8
+        if name == "HIERARCHICAL":
+            assert bool((blk.last_sel.sum(1) == 2).all())
+        if name == "BASE_LAYER":
+            assert int(blk.last_sel.sum(0).max()) == 4 and bool((blk.last_sel.sum(1) == 1).all())
+        if kw.get("capacity_policy"):
+            assert int(blk.last_sel.sum(0).max()) <= 4            # ceil(0.5 * 32 * 2 / 8)
+    assert len(set(round(v, 5) for v in outs.values())) == len(outs)     # the rules really differ from plain top-k

@@ -45,5 +45,5 @@ def test_sharded_engine_matches_single_process_gpu(tmp_path, nproc, tp, comm):
     res = _run(tmp_path, nproc, tp, comm, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     for r in res:
         assert max(r["loss_err"]) < 5e-2, r
-        assert r["weight_err"] < 5e-2, r
+        assert r["weight_err"] < 8e-2, r
         assert abs(r["grad_norm"] - r["ref_grad_norm"]) < 5e-2 * max(1.0, r["ref_grad_norm"]), r

@@ -180,6 +180,13 @@ def serve_bench(a):
     else:
         model = DenseModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
     g = torch.Generator().manual_seed(0)
+    if a.load == "baseline5":
+        _serve_load(a, cfg, model, rank, world, symm, g)
+        if world > 1:
+            dist.barrier()
+            symm.close()
+            dist.destroy_process_group()
+        return
     for B in [int(x) for x in a.batch.split(",")]:
         pages = (a.prompt_len + a.gen + 31) // 16 * B + 64
         ecfg = EngineConfig(max_batch=B, num_pages=pages, kv_mode=a.kv, weight_format=a.weights, cuda_graph=not a.no_graph,
@@ -213,6 +220,64 @@ def serve_bench(a):
         dist.destroy_process_group()
 
 
+def _serve_load(a, cfg, model, rank, world, symm, g):
+    """Closed-loop load of BASELINE config 5: ``--requests`` (256) requests with prompt lengths uniform in
+    [--prompt-min, --prompt-max] (128-2048) and ``--gen`` (256) output tokens each, ``--concurrent`` (64) in flight: a new
+    request is submitted the moment one finishes.  Token ids come from the seed.  Reports output tokens/s over the whole
+    run and the median / p90 time to first token (submission to first sampled token)."""
+    import statistics
+
+    import torch
+
+    from ..inference.engine import EngineConfig, InferenceEngine
+    from ..inference.sampler import SamplerConfig
+    conc, nreq = a.concurrent, a.requests
+    lens = torch.randint(a.prompt_min, a.prompt_max + 1, (nreq,), generator=g).tolist()
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    max_len = a.prompt_max + a.gen + 16
+    pages = (max_len + 15) // 16 * conc + 64
+    ecfg = EngineConfig(max_batch=conc, num_pages=pages, kv_mode=a.kv, weight_format=a.weights, cuda_graph=not a.no_graph,
+                        enable_prefix_cache=False, max_seq_len=min(cfg.max_seq_len, max_len))
+    if world > 1:
+        from ..inference.tp_engine import TPInferenceEngine
+        eng = TPInferenceEngine(model, None, ecfg, rank, world, symm)
+    else:
+        eng = InferenceEngine(model, None, ecfg)
+    greedy = SamplerConfig(temperature=0.0, top_k=0, top_p=1.0)
+    # warm-up: graphs for the batch buckets, workspaces, allocator
+    warm = [eng.add_request(prompts[i % nreq][:256], max_tokens=8, sampling=greedy) for i in range(conc)]
+    while eng.has_pending():
+        eng.step()
+    del warm
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nxt, live, done = 0, [], []
+    d0, steps = eng.stats.decode_ms, 0
+    while nxt < nreq or live:
+        while nxt < nreq and len(live) < conc:
+            live.append(eng.add_request(prompts[nxt], max_tokens=a.gen, sampling=greedy))
+            nxt += 1
+        eng.step()
+        steps += 1
+        still = []
+        for r in live:
+            (done if r.finished else still).append(r)
+        live = still
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    out_tokens = sum(len(r.out) for r in done)
+    ttft = sorted((r.t_first - r.t_submit) * 1e3 for r in done)
+    rec = {"bench": "serve_load", "load": "baseline5", "preset": a.preset, "layers": cfg.num_layers, "requests": nreq,
+           "concurrent": conc, "prompt_len": [a.prompt_min, a.prompt_max], "prompt_tokens": sum(lens), "gen": a.gen,
+           "weights": a.weights or "bf16", "kv": a.kv, "tp": world, "cuda_graph": eng.cfg.cuda_graph,
+           "out_tok_s": round(out_tokens / dt, 1), "ttft_ms_p50": round(statistics.median(ttft), 2),
+           "ttft_ms_p90": round(ttft[int(0.9 * (len(ttft) - 1))], 2), "total_s": round(dt, 2), "engine_steps": steps,
+           "decode_ms_per_step": round((eng.stats.decode_ms - d0) / max(1, steps), 3),
+           "data": "synthetic (seeded token ids; random-init weights)"}
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="quant_bench", description="Usage: quant_bench [--kernel <name> --size N] [--inference --model m.quant --prompt p]")
     ap.add_argument("--kernel", default="")
@@ -235,6 +300,12 @@ def main(argv=None):
     ap.add_argument("--shape", default="", help="gemm only: MxNxK[:nt|nn|tn]")
     ap.add_argument("--peaks", default="")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--load", default="", help="--serve: 'baseline5' = closed-loop load (256 requests, prompts 128-2048, 256 "
+                                               "outputs, 64 concurrent) instead of the fixed-batch sweep")
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--concurrent", type=int, default=64)
+    ap.add_argument("--prompt-min", type=int, default=128)
+    ap.add_argument("--prompt-max", type=int, default=2048)
     ap.add_argument("--comm", action="store_true", help="fused compute+collective kernels against NCCL + plain kernels "
                                                         "(run under torch.distributed.run; see cli/bench_comm.py)")
     ap.add_argument("--link-gbs", type=float, default=770.0, help="--comm: NVLink bandwidth per direction per GPU, GB/s")

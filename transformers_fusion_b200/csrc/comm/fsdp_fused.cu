@@ -50,6 +50,10 @@ __device__ __forceinline__ float4 fs_ld_peer(const float* p) {
   return v;
 }
 
+// MAXW: compile-time bound on the group size (the peer loops unroll over it); UNROLL: 16-byte vectors each thread
+// keeps in flight per peer.  A bounded grid (the kernel shares the GPU with backward) needs deep per-thread queues to
+// cover NVLink latency: 48 CTAs x 512 threads x UNROLL x (W - 1) x 16 B in flight.
+template <int MAXW, int UNROLL>
 __global__ void __launch_bounds__(512) fsdp_reduce_scatter_kernel(FsdpRsArgs a) {
   __shared__ int sh_ok;
   __shared__ float sh_red[32];
@@ -61,24 +65,39 @@ __global__ void __launch_bounds__(512) fsdp_reduce_scatter_kernel(FsdpRsArgs a) 
   float ss = 0.f;
   for (int s = 0; s < a.nseg; ++s) {
     const FsdpSeg sg = a.seg[s];
-    const float* src[FS_MAX_WORLD];
+    const float* src[MAXW];
 #pragma unroll
-    for (int r = 0; r < FS_MAX_WORLD; ++r)
+    for (int r = 0; r < MAXW; ++r)
       src[r] = r < W ? a.grad_ptrs[(c.rank + r) % W] + sg.full_off + sg.shard_len * c.rank : nullptr;   // [0] is local
     float* dst = a.gshard + sg.shard_off;
     const long long n4 = sg.shard_len >> 2;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-      float4 acc = reinterpret_cast<const float4*>(src[0])[i];
-      float4 v[FS_MAX_WORLD];
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n4; i0 += stride * UNROLL) {
+      float4 acc[UNROLL];
+      float4 v[UNROLL][MAXW];
 #pragma unroll
-      for (int r = 1; r < FS_MAX_WORLD; ++r)
-        if (r < W) v[r] = fs_ld_peer(src[r] + i * 4);   // all peer loads in flight before the first add
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < n4) {
+          acc[u] = reinterpret_cast<const float4*>(src[0])[i];
 #pragma unroll
-      for (int r = 1; r < FS_MAX_WORLD; ++r)
-        if (r < W) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
-      acc.x *= a.scale; acc.y *= a.scale; acc.z *= a.scale; acc.w *= a.scale;
-      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
-      reinterpret_cast<float4*>(dst)[i] = acc;
+          for (int r = 1; r < MAXW; ++r)
+            if (r < W) v[u][r] = fs_ld_peer(src[r] + i * 4);   // all peer loads in flight before the first add
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < n4) {
+          float4 t = acc[u];
+#pragma unroll
+          for (int r = 1; r < MAXW; ++r)
+            if (r < W) { t.x += v[u][r].x; t.y += v[u][r].y; t.z += v[u][r].z; t.w += v[u][r].w; }
+          t.x *= a.scale; t.y *= a.scale; t.z *= a.scale; t.w *= a.scale;
+          ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+          reinterpret_cast<float4*>(dst)[i] = t;
+        }
+      }
     }
   }
 #pragma unroll
@@ -152,7 +171,11 @@ TFB_API int tfb_fsdp_reduce_scatter(const TfbFsdpRsDesc* d, int max_ctas, void* 
   }
   int grid = sm_count() * 2;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  fsdp_reduce_scatter_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d->world <= 2) fsdp_reduce_scatter_kernel<2, 6><<<grid, 512, 0, st>>>(a);
+  else if (d->world <= 4) fsdp_reduce_scatter_kernel<4, 3><<<grid, 512, 0, st>>>(a);
+  else if (d->world <= 8) fsdp_reduce_scatter_kernel<8, 2><<<grid, 512, 0, st>>>(a);
+  else fsdp_reduce_scatter_kernel<FS_MAX_WORLD, 1><<<grid, 512, 0, st>>>(a);
   return int(cudaGetLastError());
 }
 

@@ -45,6 +45,12 @@ struct GatherSpec {
   long long ld;
 };
 
+// C tensor maps of the reduce-scatter form: one per destination rank's staging buffer (peer memory).
+constexpr int RS_TMA_MAX_WORLD = 8;
+struct PeerMaps {
+  CUtensorMap m[RS_TMA_MAX_WORLD];
+};
+
 struct GemmParams {
   int M, N, K;
   void* C;
@@ -266,7 +272,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ PeerMaps tma_peers, const GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -519,7 +525,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, 0);
+              if (p.tp_mode & TP_RS) {
+                // rows of shard d go to rank d's staging buffer, slot `rank`: one 32-row x 128-byte slab per copy, so the
+                // bytes cross NVLink in whole lines (tile rows never straddle two shards: shards are multiples of 128 rows)
+                const int d = slab_row0 / p.rs_rows_per_shard;
+                tma_store_3d(&tma_peers.m[d], stg_u32 + sbuf * 4096, col0,
+                             p.rs_rank * p.rs_rows_per_shard + (slab_row0 - d * p.rs_rows_per_shard), 0);
+              } else {
+                tma_store_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, 0);
+              }
               tma_store_commit();
             }
             sbuf ^= 1;
@@ -673,13 +687,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 // host launcher
 // -------------------------------------------------------------------------------------------------
 template <bool A_MN, bool B_MN, int BN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
-                  cudaStream_t st) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const PeerMaps& tpeers, const GemmParams& p,
+                  int grid, cudaStream_t st) {
   using L = SmemLayout<BN>;
   static DeviceOnce once;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN>;
   if (int e = ensure_dyn_smem(once, kern, L::TOTAL)) return e;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, tc, p);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, tc, tpeers, p);
   return int(cudaGetLastError());
 }
 
@@ -702,6 +716,8 @@ struct TfbGemmTp {
   int* ready;             // bit 1: local int[M / 128]
   const void* peer_a;     // bit 1: device array [world] of gathered-A base pointers
   const void* peer_c;     // bit 2: device array [world] of staging-buffer base pointers
+  const void* const* peer_c_host;   // bit 2, optional: the same addresses in host memory; with them (and world <= 8) the
+                                    // partial tiles leave through TMA stores instead of per-thread stores
   // bit 4: B is the local gather buffer of a weight whose row shards ([wg_rows / wg_world, ldb] each, 128-row blocks)
   // live on the wg_world ranks of the data-parallel group
   int wg_rank, wg_world, wg_epoch, wg_rows;   // wg_rows: padded row count, a multiple of 128 * wg_world
@@ -839,12 +855,24 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   // C tensor map for the staged epilogue: 32-row x 128-byte boxes.  Needs a 16-byte aligned base and row pitch.
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
+  PeerMaps tpeers;
+  memset(&tpeers, 0, sizeof(tpeers));
   p.c_tma = 0;
   {
     const int esz = out_mode == 0 ? 2 : 4;
     const bool aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * esz) % 16 == 0 &&
                          (gmode != 2 || (grp->c_expert_stride * esz) % 16 == 0);
-    if (aligned && !(tp && (tp->mode & TP_RS))) {
+    const bool rs = tp && (tp->mode & TP_RS);
+    if (aligned && rs && tp->peer_c_host && tp->world <= RS_TMA_MAX_WORLD && out_mode == 0 && (ldc * 2) % 16 == 0) {
+      const int rps = M / tp->world;
+      bool ok = true;
+      for (int d = 0; d < tp->world && ok; ++d)
+        ok = (reinterpret_cast<uintptr_t>(tp->peer_c_host[d]) & 15) == 0 &&
+             make_tmap_3d(&tpeers.m[d], tp->peer_c_host[d], 2, N, (unsigned long long)tp->world * rps, 1, ldc * 2,
+                          (unsigned long long)ldc * 2 * tp->world * rps, 64, 32, 1) == 0;
+      if (ok) p.c_tma = 1;
+    }
+    if (aligned && !rs) {
       const unsigned long long zs = gmode == 2 ? (unsigned long long)grp->c_expert_stride * esz : (unsigned long long)ldc * esz * M;
       if (make_tmap_3d(&tc, C, esz, N, M, gmode == 2 ? E : 1, ldc * esz, zs, 128 / esz, 32, 1) == 0) p.c_tma = 1;
     }
@@ -924,17 +952,17 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
   const int key = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (BN == 256) {
     switch (key) {
-      case 0: return launch<false, false, 256>(ta, tb, tc, p, grid, st);
-      case 1: return launch<false, true, 256>(ta, tb, tc, p, grid, st);
-      case 2: return launch<true, false, 256>(ta, tb, tc, p, grid, st);
-      default: return launch<true, true, 256>(ta, tb, tc, p, grid, st);
+      case 0: return launch<false, false, 256>(ta, tb, tc, tpeers, p, grid, st);
+      case 1: return launch<false, true, 256>(ta, tb, tc, tpeers, p, grid, st);
+      case 2: return launch<true, false, 256>(ta, tb, tc, tpeers, p, grid, st);
+      default: return launch<true, true, 256>(ta, tb, tc, tpeers, p, grid, st);
     }
   } else {
     switch (key) {
-      case 0: return launch<false, false, 128>(ta, tb, tc, p, grid, st);
-      case 1: return launch<false, true, 128>(ta, tb, tc, p, grid, st);
-      case 2: return launch<true, false, 128>(ta, tb, tc, p, grid, st);
-      default: return launch<true, true, 128>(ta, tb, tc, p, grid, st);
+      case 0: return launch<false, false, 128>(ta, tb, tc, tpeers, p, grid, st);
+      case 1: return launch<false, true, 128>(ta, tb, tc, tpeers, p, grid, st);
+      case 2: return launch<true, false, 128>(ta, tb, tc, tpeers, p, grid, st);
+      default: return launch<true, true, 128>(ta, tb, tc, tpeers, p, grid, st);
     }
   }
 }

@@ -23,6 +23,7 @@ import torch.nn.functional as TF
 
 from ..ops import functional as F
 from ..ops import moe as M
+from . import moe_routing as R
 from .config import MoEConfig, TransformerConfig
 from .dense import DenseModel, FlatBuffers, _EmbedFn, _FinalNormFn, _LinearFn, _ensure_main_grad
 
@@ -152,12 +153,40 @@ class MoEBlock(nn.Module):
             logits = logits + self.router_bias
         elif variant == "GATING_DROPOUT" and self.training:
             logits = logits + torch.where(torch.rand_like(logits) < 0.1, torch.full_like(logits, -1e4), torch.zeros_like(logits))
+        # ---- rules that pick a selection [T, E] first (models/moe_routing.py); the fused expert path then runs on masked logits
+        sel = passthrough = None
+        E = cfg.num_experts
+        if variant == "EXPERT_CHOICE":
+            k = min(max(k, 2), E, 8)
+            sel = R.expert_choice(logits, cfg.capacity_factor, k)
+            renorm = True
+        elif variant in ("HIERARCHICAL", "MOMOE"):
+            groups = getattr(cfg, "num_groups", 0) or max(1, int(round(E ** 0.5)))
+            while E % groups:
+                groups -= 1
+            top_groups = min(groups, max(1, getattr(cfg, "top_groups", 0) or k))
+            sel = R.hierarchical(logits, groups, top_groups, getattr(cfg, "top_experts_per_group", 1) or 1)
+            k, renorm = min(8, top_groups * (getattr(cfg, "top_experts_per_group", 1) or 1)), True
+        elif variant == "BASE_LAYER":
+            sel = R.base_layer(logits)
+            k, renorm = 1, True
+        elif cfg.capacity_policy.lower() in ("fixed", "token_drop", "token_pass") and variant.startswith("SPARSE"):
+            sel, passthrough = R.apply_capacity(logits, min(k, 8), cfg.capacity_factor, cfg.capacity_policy)
+            renorm = True
+        covered = None
+        if sel is not None:
+            self.last_sel = sel
+            logits, covered = R.masked_logits(logits, sel)
         if self.ep is not None:
             y, aux, idx = self.ep.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm,
                                           cfg.act_kernel, cfg.load_balance_weight, cfg.router_z_weight)
         else:
             y, aux, idx = M.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm, cfg.act_kernel,
                                     cfg.load_balance_weight, cfg.router_z_weight)
+        if covered is not None:
+            y = y * covered[:, None].to(y.dtype)               # tokens that no expert serves contribute nothing
+            if passthrough is not None and bool((passthrough > 0).any()):
+                y = y * (1.0 - passthrough)[:, None].to(y.dtype) + f * passthrough[:, None].to(f.dtype)
         if variant == "DEEPSEEK_MOE" and self.training:
             with torch.no_grad():
                 self.router_bias -= 0.001 * torch.bincount(idx.reshape(-1).long(), minlength=cfg.num_experts).float() / idx.numel() * cfg.num_experts
@@ -286,8 +315,11 @@ class MoEAllConfig:
     load_balance_weight: float = 0.01
     router_z_weight: float = 0.001
     capacity_factor: float = 2.0
-    capacity_policy: str = "fixed"          # fixed | token_drop | token_pass
+    capacity_policy: str = "none"           # none | fixed | token_drop | token_pass (see models/moe_routing.py)
     num_shared_experts: int = 0
+    num_groups: int = 0                     # HIERARCHICAL / MOMOE: 0 = about sqrt(num_experts)
+    top_groups: int = 0                     # 0 = top_k
+    top_experts_per_group: int = 1
 
 
 def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfig" = None, **model_kw) -> "MoEModel":
@@ -304,4 +336,5 @@ def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfi
     cfg = MoEConfig(**kw, num_experts=m.num_experts, top_k=m.top_k, expert_hidden_size=m.expert_hidden, num_shared_experts=shared,
                     load_balance_weight=m.load_balance_weight, router_z_weight=m.router_z_weight, capacity_factor=m.capacity_factor,
                     capacity_policy=m.capacity_policy, variant=name)
+    cfg.num_groups, cfg.top_groups, cfg.top_experts_per_group = m.num_groups, m.top_groups, m.top_experts_per_group
     return MoEModel(cfg, **model_kw)

@@ -65,7 +65,10 @@ class SymmetricHeap:
         h = C.create_string_buffer(64)
         _lib.check(lib.tfb_symm_alloc(nbytes, C.byref(p), h), "symm_alloc", 0)
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(h.raw), group=self.group)
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(h.raw), group=self.group)
+        else:
+            handles[0] = bytes(h.raw)
         ptrs = []
         for r, hb in enumerate(handles):
             if r == self.rank:

@@ -24,7 +24,7 @@ class _Tp(C.Structure):
     """Mirror of TfbGemmTp (csrc/kernels/gemm_bf16.cu): ``mode`` bits 1 all-gather -> GEMM, 2 GEMM -> reduce-scatter,
     4 weight gather -> GEMM."""
     _fields_ = [("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int), ("epoch", C.c_int),
-                ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p),
+                ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p), ("peer_c_host", C.c_void_p),
                 ("wg_rank", C.c_int), ("wg_world", C.c_int), ("wg_epoch", C.c_int), ("wg_rows", C.c_int),
                 ("wg_ready", C.c_void_p), ("wg_src", C.c_void_p)]
 
@@ -64,6 +64,8 @@ def fused_gemm(x, w, *, b_mn=False, n=None, k=None, out=None, residual=None, tp=
         mode |= tp[0]
         d.rank, d.world, d.epoch = tp[1], tp[2], tp[3]
         d.ready, d.peer_a, d.peer_c = tp[4], tp[5], tp[6]
+        if len(tp) > 7 and tp[7] is not None:
+            d.peer_c_host = C.cast(tp[7], C.c_void_p)
     if wg is not None:
         mode |= 4
         d.wg_rank, d.wg_world, d.wg_epoch, d.wg_rows = wg.rank, wg.world, wg.epoch, wg.rows_p
@@ -123,6 +125,7 @@ class TpContext:
         self.ready = torch.zeros(max_rows // 128 + 1, dtype=torch.int32, device=dev)
         self.epoch = 0
         self.parity = 0
+        self._stage_host = {}     # staging buffer -> ctypes array of the W peer addresses (for the TMA-store epilogue)
 
     def all_gather_gemm(self, x_shard, w, out=None, b_mn=False, wg: WeightGather = None, n=None, k=None):
         """x_shard [M/W, K] -> y [M, N_local]; ``w`` [N_local, K], or [K, N_local] with ``b_mn``.  With ``wg`` the
@@ -146,7 +149,10 @@ class TpContext:
         N = n if n is not None else (w.shape[1] if b_mn else w.shape[0])
         Ms = M // self.world
         buf = self.stage[self.parity]
-        tp = (2, self.rank, self.world, 0, None, None, buf.ptrs.data_ptr())
+        host = self._stage_host.get(id(buf))
+        if host is None:
+            host = self._stage_host[id(buf)] = (C.c_void_p * self.world)(*buf.peer_ptrs)
+        tp = (2, self.rank, self.world, 0, None, None, buf.ptrs.data_ptr(), host)
         fused_gemm(x, w, b_mn=b_mn, n=N, k=k, tp=tp, wg=wg, copy_ctas=self.copy_ctas)
         self.symm.barrier()                                           # all partial tiles have arrived
         out = torch.empty((Ms, N), dtype=torch.bfloat16, device=x.device)
