@@ -140,3 +140,27 @@ def test_index_sidecar_legacy_magics_and_dedup_store(tmp_path):
     open(str(tmp_path / "blobs" / k3), "wb").write(b"tampered")
     with pytest.raises(ValueError):
         st.read(k3)
+
+
+def test_foreign_stream_of_a_non_wire_exact_format_is_refused(tmp_path):
+    """A file this library wrote in one of its own-encoder formats reads back; the same bytes with the writer's mark
+    cleared (= a file from another encoder) are refused instead of decoding to wrong weights."""
+    import struct
+    import torch
+    own = next(f for f in range(codec.FORMAT_COUNT) if not codec.is_wire_exact(f))
+    w = codec.QuantWriter(tmp_path / "a.quant")
+    t = torch.randn(1024)
+    w.add_tensor("x", t, own)
+    w.add_tensor("y", t, codec.Q_32)
+    w.close()
+    r = codec.QuantReader(tmp_path / "a.quant")
+    assert r.read_tensor("x").shape == (1024,)
+    raw = bytearray(open(tmp_path / "a.quant", "rb").read())
+    flags, = struct.unpack_from("<I", raw, 8)
+    assert flags & 0x40000000
+    struct.pack_into("<I", raw, 8, flags & ~0x40000000)
+    open(tmp_path / "b.quant", "wb").write(raw)
+    r2 = codec.QuantReader(tmp_path / "b.quant")
+    assert torch.equal(r2.read_tensor("y"), t)                      # wire-exact formats are unaffected
+    with pytest.raises(ValueError, match="another"):
+        r2.read_tensor("x")

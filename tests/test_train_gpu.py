@@ -73,3 +73,31 @@ def test_activation_checkpointing_same_grads():
     torch.cuda.synchronize()
     rel = (gs[0] - gs[1]).norm().item() / gs[0].norm().item()
     assert rel < 2e-2, rel   # split-K atomics reorder fp32 sums; nothing else differs
+
+
+@pytest.mark.gpu
+def test_fused_adafactor_matches_pytorch_statement():
+    """Multi-tensor Adafactor kernels (csrc/kernels/adafactor.cu) against the per-tensor PyTorch statement in fp32."""
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.trainer.optimizers import Adafactor
+    cfg = TransformerConfig(vocab_size=256, hidden_size=128, num_layers=2, num_heads=2, ffn_hidden_size=256, max_seq_len=64)
+    for beta1 in (0.0, 0.9):
+        a = DenseModel(cfg, device="cuda", dtype=torch.bfloat16, seed=1)
+        b = DenseModel(cfg, device="cuda", dtype=torch.bfloat16, seed=1)
+        fa, fb = a.flatten(), b.flatten()
+        oa = Adafactor(fa, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0, beta1=beta1)
+        ob = Adafactor(fb, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0, beta1=beta1)
+        ob._fused_tables = lambda: None                    # force the PyTorch statement
+        g = torch.Generator(device="cuda").manual_seed(0)
+        for step in range(3):
+            gr = torch.randn(fa.numel, device="cuda", generator=g) * 0.1
+            fa.grads.copy_(gr)
+            fb.grads.copy_(gr)
+            oa.step()
+            ob.step()
+            err = (oa.master - ob.master).abs().max().item()
+            assert err < 2e-5, (beta1, step, err)
+            assert float(fa.grads.abs().max()) == 0.0
+        assert torch.equal(fa.params, oa.master.to(torch.bfloat16))

@@ -20,6 +20,10 @@ extern "C" {
 
 #define TFB_FORMAT_COUNT 105
 #define TFB_FMT_Q32 9
+// Container header flag set by this library's writer when a file holds blocks of a format whose stream is this library's
+// own encoding (tfb_format_is_wire_exact == 0).  Readers refuse such formats in files without the flag: those were written
+// by another encoder with a different stream layout.
+#define TFB_FLAG_OWN_STREAMS 0x40000000u
 
 // ---- registry -------------------------------------------------------------------------------
 const char* tfb_format_name(int fmt);            // "Q_4", "Q_G_8_K_M", ...; null when out of range

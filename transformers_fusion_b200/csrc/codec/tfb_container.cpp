@@ -196,6 +196,10 @@ TFB_EXPORT long long tfb_reader_read_tensor(const tfb_reader* r, const char* nam
     const uint8_t* ip = cbp + cb + 4;
     int fmt = r->fmts[b].fmt;
     if (fmt >= TFB_FORMAT_COUNT || fmt == 19 + 1000) fmt = TFB_FMT_Q32;  // out-of-range wire bytes decode as raw fp32
+    // A format whose block stream this library encodes in its own way can only be decoded when this library wrote the
+    // file (the writer marks such files); the same format written by another encoder has a different stream, and
+    // decoding it here would return wrong weights without any sign of trouble.
+    if (!tfb_format_is_wire_exact(fmt) && !(r->flags & TFB_FLAG_OWN_STREAMS)) return -2;
     tfb_dequantize_block(fmt, ip, ib, cbp, cb, nw, out + pos);
     pos += nw;
   }
@@ -206,6 +210,7 @@ TFB_EXPORT long long tfb_reader_read_tensor(const tfb_reader* r, const char* nam
 // writer
 // ------------------------------------------------------------------------------------------------
 struct tfb_writer {
+  void note_format(int fmt) { if (!tfb_format_is_wire_exact(fmt)) flags |= TFB_FLAG_OWN_STREAMS; }
   std::string path;
   uint32_t version, flags;
   std::vector<uint8_t> config;
@@ -232,6 +237,7 @@ TFB_EXPORT int tfb_writer_add_tensor(tfb_writer* w, const char* name, const floa
     const uint32_t n = uint32_t(std::min<long long>(block, numel - off));
     tfb_writer::Block b;
     b.fmt = uint8_t(fmt);
+    w->note_format(fmt);
     b.nw = n;
     b.idx.resize(std::max<size_t>(tfb_block_claimed_bytes(fmt, n), size_t(n) * 4 * (fmt == TFB_FMT_Q32)) + 8 + size_t(n) * 2);
     const long got = tfb_quantize_block(fmt, data + off, n, b.idx.data(), b.idx.size());
@@ -256,6 +262,7 @@ TFB_EXPORT int tfb_writer_add_tensor_mixed(tfb_writer* w, const char* name, cons
     if (fmt >= TFB_FORMAT_COUNT) return -1;
     tfb_writer::Block b;
     b.fmt = uint8_t(fmt);
+    w->note_format(fmt);
     b.nw = n;
     b.idx.resize(std::max<size_t>(tfb_block_claimed_bytes(fmt, n), size_t(n) * 4 * (fmt == TFB_FMT_Q32)) + 8 + size_t(n) * 2);
     const long got = tfb_quantize_block(fmt, data + off, n, b.idx.data(), b.idx.size());

@@ -1,6 +1,6 @@
 // Cross-entropy (forward + in-place logit gradient), global gradient norm / clip factor, and the
 // fused multi-tensor optimizers over flat fp32 state (AdamW, Lion, SGD-momentum; Adafactor's
-// factored second moment lives in adafactor.cu).
+// factored second moment is the multi-tensor kernel set of adafactor.cu).
 //
 // Reference counterparts: cross-entropy forward/backward (src/model/autograd_functions.cpp:363,
 // src/backend/gpu_compute_vulkan.cpp:1675-1721 vk_cross_entropy(+grad)); AdamW::step

@@ -169,6 +169,10 @@ class QuantReader:
             raise KeyError(name)
         out = np.empty(n, dtype=np.float32)
         got = lib().tfb_reader_read_tensor(self._h, name.encode(), out.ctypes.data, n)
+        if got == -2:
+            raise ValueError(f"{name}: stored in format {format_name(self.tensor_format(name))}, whose block stream from another "
+                             "encoder this library cannot decode (only the formats `quant_format_list` marks wire-exact "
+                             "interchange with files written elsewhere); re-export the file in a wire-exact format")
         if got != n:
             raise ValueError(f"{name}: corrupt blocks")
         return torch.from_numpy(out)

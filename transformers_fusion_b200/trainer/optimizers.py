@@ -283,9 +283,61 @@ class NovoGrad(FlatOptimizer):
 
 class Adafactor(FlatOptimizer):
     """Factored second moments for matrices (row / column statistics), full for vectors; relative-step
-    free variant with update clipping (reference Adafactor::step, src/trainer/optimizer.cpp:338)."""
+    free variant with update clipping (reference Adafactor::step, src/trainer/optimizer.cpp:338).
+
+    On CUDA the whole step is the multi-tensor kernel set of csrc/kernels/adafactor.cu (five launches for all tensors);
+    the per-tensor PyTorch statement below is the CPU path and the oracle of its test."""
     name = "adafactor"
     per_tensor = True
+
+    def _fused_tables(self):
+        """Device table of (offset, r offset, c offset, d0, d1, first row, decay scale) per tensor plus the flat r / c /
+        scratch buffers; None when this optimizer's shard cuts through a tensor (sharded runs keep the PyTorch path)."""
+        if getattr(self, "_af", None) is not None:
+            return self._af
+        import ctypes as C
+        import numpy as np
+        rows, r_off, c_off, recs, max_d1 = 0, 0, 0, [], 1
+        for i, (p, off) in enumerate(zip(self.flat.params_list, self.flat.offsets)):
+            if off < self.lo or off + p.numel() > self.hi:
+                return None
+            d0, d1 = (p.numel() // p.shape[-1], p.shape[-1]) if p.dim() >= 2 else (1, p.numel())
+            recs.append((off - self.lo, r_off, c_off, d0, d1, rows, 1.0))
+            rows, r_off, c_off, max_d1 = rows + d0, r_off + d0, c_off + d1, max(max_d1, d1)
+        dt = np.dtype([("off", "<i8"), ("r_off", "<i8"), ("c_off", "<i8"), ("d0", "<i4"), ("d1", "<i4"), ("row0", "<i4"), ("wd", "<f4")])
+        tab = np.array(recs, dtype=dt)
+        dev = self.master.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        self._af = {"table": torch.from_numpy(tab.view(np.uint8).copy()).to(dev), "nt": len(recs), "rows": rows, "max_d1": max_d1,
+                    "r": torch.zeros(r_off, **f32), "c": torch.zeros(c_off, **f32), "csum": torch.zeros(c_off, **f32),
+                    "rmean": torch.zeros(len(recs), **f32), "usq": torch.zeros(len(recs), **f32),
+                    "m": torch.zeros_like(self.master) if self.h.get("beta1", 0.0) > 0 else None}
+        from ..ops import _lib
+        fn = _lib.lib().tfb_adafactor
+        c_p, c_i, c_f = C.c_void_p, C.c_int, C.c_float
+        fn.argtypes = [c_p, c_i, c_i, c_i] + [c_p] * 10 + [c_f] * 6 + [c_p]
+        fn.restype = c_i
+        return self._af
+
+    def step(self, lr=None):
+        af = self._fused_tables() if self.master.is_cuda and self.lo == 0 and self.hi == self.flat.numel else None
+        if af is None:
+            return super().step(lr)
+        from ..ops import _lib
+        self.step_count += 1
+        lr = self.lr if lr is None else lr
+        self.clip()
+        b2 = min(0.999, 1.0 - self.step_count ** -0.8)
+        g = self.flat.grads[self.lo:self.hi]
+        lp = self.flat.params[self.lo:self.hi]
+        _lib.check(_lib.lib().tfb_adafactor(af["table"].data_ptr(), af["nt"], af["rows"], af["max_d1"], g.data_ptr(),
+                                            self.master.data_ptr(), lp.data_ptr() if lp.dtype == torch.bfloat16 else None,
+                                            _lib.ptr(af["m"]), af["r"].data_ptr(), af["c"].data_ptr(), af["csum"].data_ptr(),
+                                            af["rmean"].data_ptr(), af["usq"].data_ptr(), None, b2, self.h.get("eps", 1e-30),
+                                            self.h.get("clip_threshold", 1.0), lr, self.wd, self.h.get("beta1", 0.0),
+                                            _lib.stream()), "adafactor", 5)
+        if lp.dtype != torch.bfloat16:
+            lp.copy_(self.master.to(lp.dtype))
 
     def update(self, p, g, lr, idx):
         b2 = min(0.999, 1.0 - self.step_count ** -0.8)
