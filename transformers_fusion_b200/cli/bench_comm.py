@@ -116,7 +116,7 @@ def comm_bench(a):
     d.grad_ptrs, d.gshard, d.sumsq, d.ticket = full.ptrs.data_ptr(), gshard.data_ptr(), sumsq.data_ptr(), ticket.data_ptr()
     d.scale, d.nseg = 1.0 / W, 1
     d.seg[0], d.seg[1], d.seg[2] = 0, 0, nfull // W
-    for ctas in (0, 48):
+    for ctas in (0, 96):
         us_f = _timed(lambda: _lib.check(lib.tfb_fsdp_reduce_scatter(C.byref(d), ctas, _lib.stream()), "fsdp_rs"), it, wu, dist, dev)
         us_l = _timed(lambda: dist.reduce_scatter_tensor(gshard, fullv, op=dist.ReduceOp.AVG), it, wu, dist, dev)
         emit(f"fsdp_reduce_scatter(ctas={ctas or 'all'})", f"{nfull * 4 >> 20} MiB fp32", us_f, us_l, (W - 1) * (nfull // W) * 4)

@@ -76,6 +76,7 @@ __device__ __forceinline__ uint4 ar_reduce(const uint4* v, int W, int dtype, int
 }
 
 __global__ void __launch_bounds__(512) collective_kernel(ArArgs a) {
+  tfb::pdl_sync();
   __shared__ int sh_ok;
   const CommCtx& c = a.c;
   const int W = c.world, rank = c.rank;
@@ -174,6 +175,6 @@ TFB_API int tfb_collective(const void* bufs, void* local, long long n, int dtype
   const long long cap = max_ctas > 0 ? max_ctas : sm_count();   // one CTA per SM at most: every CTA must be resident to poll
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
-  collective_kernel<<<unsigned(ctas), 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  tfb::launch_k(collective_kernel, unsigned(ctas), 512, 0, static_cast<cudaStream_t>(stream), a);
   return int(cudaGetLastError());
 }

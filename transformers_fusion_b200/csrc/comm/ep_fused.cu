@@ -32,6 +32,7 @@ constexpr int EP_MAX_W = 16;
 __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int W, int E, int rank, int* __restrict__ base,
                                int* __restrict__ seg_start, int* __restrict__ expert_of_tile, int max_tiles,
                                int* __restrict__ total_rows, int* __restrict__ cursor) {
+  tfb::pdl_sync();
   if (threadIdx.x != 0) return;
   const int El = E / W;
   for (int owner = 0; owner < W; ++owner) {
@@ -66,6 +67,7 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int W, int E,
 // every rank pushes its E counts into row `rank` of every peer's counts_all
 __global__ void ep_push_counts_kernel(const int* __restrict__ counts, int* const* __restrict__ peer_counts_all, int W,
                                       int E, int rank) {
+  tfb::pdl_sync();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= W * E) return;
   const int peer = i / E, e = i % E;
@@ -76,6 +78,7 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const in
                                    const int* __restrict__ base, int* __restrict__ cursor, int* __restrict__ row_of,
                                    __nv_bfloat16* const* __restrict__ peer_xp, int T, int K, int H, int El,
                                    int max_rows) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (w >= (long long)T * K) return;
@@ -97,6 +100,7 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const in
 __global__ void ep_combine_kernel(__nv_bfloat16* const* __restrict__ peer_yp, const int* __restrict__ topk_idx,
                                   const int* __restrict__ row_of, const float* __restrict__ topk_w,
                                   __nv_bfloat16* __restrict__ y, int T, int K, int H, int El) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
@@ -127,6 +131,7 @@ __global__ void ep_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, __nv
                                       __nv_bfloat16* const* __restrict__ peer_dyp, const int* __restrict__ topk_idx,
                                       const int* __restrict__ row_of, const float* __restrict__ topk_w,
                                       float* __restrict__ dw, int T, int K, int H, int El) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (w >= (long long)T * K) return;
@@ -159,6 +164,7 @@ __global__ void ep_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, __nv
 __global__ void ep_dispatch_bwd_kernel(__nv_bfloat16* const* __restrict__ peer_dxp, const int* __restrict__ topk_idx,
                                        const int* __restrict__ row_of, __nv_bfloat16* __restrict__ dx, int T, int K,
                                        int H, int El) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
@@ -190,21 +196,21 @@ static inline unsigned ep_blocks(long long warps) { return unsigned((warps * 32 
 
 TFB_API int tfb_ep_push_counts(const int* counts, const void* peer_counts_all, int W, int E, int rank, void* stream) {
   if (W > EP_MAX_W || E > EP_MAX_E || E % W) return TFB_ERR_LIMIT;
-  ep_push_counts_kernel<<<(W * E + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(ep_push_counts_kernel, (W * E + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream), 
       counts, static_cast<int* const*>(peer_counts_all), W, E, rank);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_ep_plan(const int* counts_all, int W, int E, int rank, int* base, int* seg_start, int* expert_of_tile,
                         int max_tiles, int* total_rows, int* cursor, void* stream) {
   if (W > EP_MAX_W || E > EP_MAX_E || E % W) return TFB_ERR_LIMIT;
-  ep_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts_all, W, E, rank, base, seg_start,
+  tfb::launch_k(ep_plan_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), counts_all, W, E, rank, base, seg_start,
                                                                  expert_of_tile, max_tiles, total_rows, cursor);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_ep_dispatch(const void* x, const int* topk_idx, const int* base, int* cursor, int* row_of,
                             const void* peer_xp, int T, int K, int H, int El, int max_rows, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  ep_dispatch_kernel<<<ep_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(ep_dispatch_kernel, ep_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), topk_idx, base, cursor, row_of,
       static_cast<__nv_bfloat16* const*>(peer_xp), T, K, H, El, max_rows);
   return int(cudaGetLastError());
@@ -212,7 +218,7 @@ TFB_API int tfb_ep_dispatch(const void* x, const int* topk_idx, const int* base,
 TFB_API int tfb_ep_combine(const void* peer_yp, const int* topk_idx, const int* row_of, const float* topk_w, void* y,
                            int T, int K, int H, int El, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  ep_combine_kernel<<<ep_blocks(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(ep_combine_kernel, ep_blocks(T), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16* const*>(peer_yp), topk_idx, row_of, topk_w, static_cast<__nv_bfloat16*>(y), T, K, H, El);
   return int(cudaGetLastError());
 }
@@ -220,7 +226,7 @@ TFB_API int tfb_ep_combine_bwd(const void* dy, const void* peer_yp, const void* 
                                const int* row_of, const float* topk_w, float* dw, int T, int K, int H, int El,
                                void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  ep_combine_bwd_kernel<<<ep_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(ep_combine_bwd_kernel, ep_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16* const*>(peer_yp),
       static_cast<__nv_bfloat16* const*>(peer_dyp), topk_idx, row_of, topk_w, dw, T, K, H, El);
   return int(cudaGetLastError());
@@ -228,7 +234,7 @@ TFB_API int tfb_ep_combine_bwd(const void* dy, const void* peer_yp, const void* 
 TFB_API int tfb_ep_dispatch_bwd(const void* peer_dxp, const int* topk_idx, const int* row_of, void* dx, int T, int K,
                                 int H, int El, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  ep_dispatch_bwd_kernel<<<ep_blocks(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(ep_dispatch_bwd_kernel, ep_blocks(T), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16* const*>(peer_dxp), topk_idx, row_of, static_cast<__nv_bfloat16*>(dx), T, K, H, El);
   return int(cudaGetLastError());
 }

@@ -51,10 +51,15 @@ __device__ __forceinline__ float4 fs_ld_peer(const float* p) {
 }
 
 // MAXW: compile-time bound on the group size (the peer loops unroll over it); UNROLL: 16-byte vectors each thread
-// keeps in flight per peer.  A bounded grid (the kernel shares the GPU with backward) needs deep per-thread queues to
-// cover NVLink latency: 48 CTAs x 512 threads x UNROLL x (W - 1) x 16 B in flight.
+// keeps in flight per peer.  The kernel shares the GPU with the backward pass, so its CTAs must fit beside a resident GEMM
+// CTA (192 threads x 168 registers, ~200 KB of shared memory): 256 threads x <= 128 registers and no dynamic shared
+// memory leave room for both on one SM, where a 512-thread CTA of this kernel would claim the whole register file and
+// could only start once a GEMM CTA had left, stalling the persistent GEMM that follows.  A bounded grid needs deep
+// per-thread queues to cover NVLink latency: 96 CTAs x 256 threads x UNROLL x (W - 1) x 16 B in flight.
+constexpr int FS_THREADS = 256;
 template <int MAXW, int UNROLL>
-__global__ void __launch_bounds__(512) fsdp_reduce_scatter_kernel(FsdpRsArgs a) {
+__global__ void __launch_bounds__(FS_THREADS) fsdp_reduce_scatter_kernel(FsdpRsArgs a) {
+  tfb::pdl_sync();
   __shared__ int sh_ok;
   __shared__ float sh_red[32];
   const CommCtx& c = a.c;
@@ -124,6 +129,7 @@ __global__ void __launch_bounds__(512) fsdp_reduce_scatter_kernel(FsdpRsArgs a) 
 __global__ void embedding_fwd_sharded_kernel(const long long* __restrict__ ids, const __nv_bfloat16* const* __restrict__ shard_ptrs,
                                              __nv_bfloat16* __restrict__ out, int T, int H, long long per_rows, int world,
                                              long long vocab_lo, long long vocab_n) {
+  tfb::pdl_sync();
   const int vec = H >> 3;
   const long long total = (long long)T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -169,13 +175,13 @@ TFB_API int tfb_fsdp_reduce_scatter(const TfbFsdpRsDesc* d, int max_ctas, void* 
     if (d->seg[s].shard_len % 4 || d->seg[s].full_off % 4 || d->seg[s].shard_off % 4) return TFB_ERR_ARG;
     a.seg[s] = FsdpSeg{d->seg[s].full_off, d->seg[s].shard_off, d->seg[s].shard_len};
   }
-  int grid = sm_count() * 2;
+  int grid = sm_count() * 4;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d->world <= 2) fsdp_reduce_scatter_kernel<2, 6><<<grid, 512, 0, st>>>(a);
-  else if (d->world <= 4) fsdp_reduce_scatter_kernel<4, 3><<<grid, 512, 0, st>>>(a);
-  else if (d->world <= 8) fsdp_reduce_scatter_kernel<8, 2><<<grid, 512, 0, st>>>(a);
-  else fsdp_reduce_scatter_kernel<FS_MAX_WORLD, 1><<<grid, 512, 0, st>>>(a);
+  if (d->world <= 2) tfb::launch_k(fsdp_reduce_scatter_kernel<2, 6>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 4) tfb::launch_k(fsdp_reduce_scatter_kernel<4, 3>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 8) tfb::launch_k(fsdp_reduce_scatter_kernel<8, 2>, grid, FS_THREADS, 0, st, a);
+  else tfb::launch_k(fsdp_reduce_scatter_kernel<FS_MAX_WORLD, 1>, grid, FS_THREADS, 0, st, a);
   return int(cudaGetLastError());
 }
 
@@ -186,7 +192,7 @@ TFB_API int tfb_embedding_fwd_sharded(const long long* ids, const void* shard_pt
   const long long work = (long long)T * (H / 8);
   long long g = (work + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
-  embedding_fwd_sharded_kernel<<<int(g < 1 ? 1 : g), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(embedding_fwd_sharded_kernel, int(g < 1 ? 1 : g), 256, 0, static_cast<cudaStream_t>(stream), 
       ids, static_cast<const __nv_bfloat16* const*>(shard_ptrs), static_cast<__nv_bfloat16*>(out), T, H, per_rows, world,
       vocab_lo, vocab_n);
   return int(cudaGetLastError());

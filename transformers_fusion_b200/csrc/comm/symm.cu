@@ -49,6 +49,7 @@ TFB_API int tfb_symm_free(void* ptr) { return int(cudaFree(ptr)); }
 namespace tfb {
 
 __global__ void barrier_kernel(CommCtx c) {
+  tfb::pdl_sync();
   if (threadIdx.x == 0) {
     const int e = comm_next_epoch(c);
     comm_signal_all(c, e);
@@ -62,6 +63,6 @@ __global__ void barrier_kernel(CommCtx c) {
 // bounded wait ran out and the status word says so).
 TFB_API int tfb_comm_barrier(const void* flag_ptrs, int* epoch, int rank, int world, int* status, void* stream) {
   tfb::CommCtx c{static_cast<int* const*>(flag_ptrs), epoch, rank, world, status};
-  tfb::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c);
+  tfb::launch_k(tfb::barrier_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), c);
   return int(cudaGetLastError());
 }

@@ -20,6 +20,7 @@ namespace tfb {
 // out[r, :] = sum_s stage[s, r, :] (+ residual[r, :]);  stage is [world, rows, N] bf16
 __global__ void tp_reduce_kernel(const __nv_bfloat16* __restrict__ stage, const __nv_bfloat16* __restrict__ residual,
                                  __nv_bfloat16* __restrict__ out, long long rows, int N, int world) {
+  tfb::pdl_sync();
   const long long n8 = rows * N / 8;
   const long long slot = rows * (long long)N;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
@@ -51,7 +52,7 @@ TFB_API int tfb_tp_reduce(const void* stage, const void* residual, void* out, lo
   long long blocks = (rows * N / 8 + 255) / 256;
   const long long cap = (long long)tfb::sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  tfb::tp_reduce_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(tfb::tp_reduce_kernel, unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(stage), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(out), rows, N, world);
   return int(cudaGetLastError());

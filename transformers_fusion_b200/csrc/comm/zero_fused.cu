@@ -48,6 +48,7 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
 }
 
 __global__ void __launch_bounds__(512) zero_reduce_scatter_kernel(ZeroArgs a) {
+  tfb::pdl_sync();
   __shared__ int sh_ok;
   __shared__ float sh_red[32];
   const CommCtx& c = a.c;
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(512) zero_reduce_scatter_kernel(ZeroArgs a) {
 }
 
 __global__ void __launch_bounds__(512) zero_adamw_allgather_kernel(ZeroArgs a) {
+  tfb::pdl_sync();
   __shared__ int sh_ok;
   const CommCtx& c = a.c;
   const int e0 = ld_volatile(c.epoch);
@@ -182,6 +184,7 @@ __global__ void __launch_bounds__(512) zero_adamw_allgather_kernel(ZeroArgs a) {
 }
 
 __global__ void zero_wait_kernel(CommCtx c) {
+  tfb::pdl_sync();
   if (threadIdx.x == 0) comm_wait_all(c, ld_volatile(c.epoch));
 }
 
@@ -219,7 +222,7 @@ TFB_API int tfb_zero_reduce_scatter(const TfbZeroDesc* d, int max_ctas, void* st
   if (int rc = fill(d, a)) return rc;
   int grid = sm_count() * 2;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  zero_reduce_scatter_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  tfb::launch_k(zero_reduce_scatter_kernel, grid, 512, 0, static_cast<cudaStream_t>(stream), a);
   return int(cudaGetLastError());
 }
 
@@ -229,13 +232,13 @@ TFB_API int tfb_zero_adamw_allgather(const TfbZeroDesc* d, int max_ctas, void* s
   if (int rc = fill(d, a)) return rc;
   int grid = sm_count() * 2;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  zero_adamw_allgather_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  tfb::launch_k(zero_adamw_allgather_kernel, grid, 512, 0, static_cast<cudaStream_t>(stream), a);
   return int(cudaGetLastError());
 }
 
 // Phase 3: returns once every rank's parameters have arrived in the local buffer.
 TFB_API int tfb_zero_wait(const TfbZeroDesc* d, void* stream) {
   CommCtx c{static_cast<int* const*>(d->flag_ptrs), d->epoch, d->rank, d->world, d->status};
-  zero_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c);
+  tfb::launch_k(zero_wait_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), c);
   return int(cudaGetLastError());
 }

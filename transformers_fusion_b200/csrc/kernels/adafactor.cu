@@ -56,6 +56,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 __global__ void __launch_bounds__(256) af_rows_kernel(AfArgs a) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const int nwarp = (gridDim.x * blockDim.x) >> 5;
   const float gs = a.gscale ? *a.gscale : 1.f;
@@ -73,6 +74,7 @@ __global__ void __launch_bounds__(256) af_rows_kernel(AfArgs a) {
 
 // grid.x = column blocks of 256 over the widest tensor, grid.y = 64-row chunks over all rows
 __global__ void __launch_bounds__(256) af_cols_kernel(AfArgs a) {
+  tfb::pdl_sync();
   const float gs = a.gscale ? *a.gscale : 1.f;
   for (int chunk = blockIdx.y; chunk * 64 < a.total_rows; chunk += gridDim.y) {
     int row = chunk * 64;
@@ -92,6 +94,7 @@ __global__ void __launch_bounds__(256) af_cols_kernel(AfArgs a) {
 }
 
 __global__ void __launch_bounds__(256) af_finish_kernel(AfArgs a) {
+  tfb::pdl_sync();
   __shared__ float sh[8];
   for (int ti = blockIdx.x; ti < a.nt; ti += gridDim.x) {
     const AfTensor t = a.t[ti];
@@ -118,6 +121,7 @@ __global__ void __launch_bounds__(256) af_finish_kernel(AfArgs a) {
 
 template <bool APPLY>
 __global__ void __launch_bounds__(256) af_update_kernel(AfArgs a) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const int nwarp = (gridDim.x * blockDim.x) >> 5;
   const float gs = a.gscale ? *a.gscale : 1.f;
@@ -176,11 +180,11 @@ TFB_API int tfb_adafactor(const void* tensors, int nt, int total_rows, int max_d
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int sms = sm_count();
   const int row_grid = min((total_rows + 7) / 8, sms * 8);
-  af_rows_kernel<<<row_grid, 256, 0, st>>>(a);
+  tfb::launch_k(af_rows_kernel, row_grid, 256, 0, st, a);
   dim3 cg(min((max_d1 + 255) / 256, 64), min((total_rows + 63) / 64, sms * 4));
-  af_cols_kernel<<<cg, 256, 0, st>>>(a);
-  af_finish_kernel<<<min(nt, sms), 256, 0, st>>>(a);
-  af_update_kernel<false><<<row_grid, 256, 0, st>>>(a);
-  af_update_kernel<true><<<row_grid, 256, 0, st>>>(a);
+  tfb::launch_k(af_cols_kernel, cg, 256, 0, st, a);
+  tfb::launch_k(af_finish_kernel, min(nt, sms), 256, 0, st, a);
+  tfb::launch_k(af_update_kernel<false>, row_grid, 256, 0, st, a);
+  tfb::launch_k(af_update_kernel<true>, row_grid, 256, 0, st, a);
   return int(cudaGetLastError());
 }

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                      const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                      const AttnBwdParams p) {
+  tfb::pdl_sync();
   using L = BwdSmem<D>;
   constexpr int NB = L::NB;
   extern __shared__ uint8_t smem_raw[];
@@ -333,6 +334,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                    const AttnBwdParams p) {
+  tfb::pdl_sync();
   using L = BwdSmem<D>;
   constexpr int NB = L::NB;
   extern __shared__ uint8_t smem_raw[];
@@ -503,6 +505,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
                                                          const __nv_bfloat16* __restrict__ dout, long long lddo,
                                                          float* __restrict__ delta, int B, int S, int Hq, int D) {
+  tfb::pdl_sync();
   const int per_row = Hq * D / 8;                       // threads per token row
   const long long total = (long long)B * S * per_row;
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -539,8 +542,8 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   if (int e = ensure_dyn_smem(once1, k1, L::TOTAL)) return e;
   if (int e = ensure_dyn_smem(once2, k2, L::TOTAL)) return e;
   const int nqb = (p.S + 127) / 128;
-  k1<<<nqb * p.Hkv * p.B, AB_THREADS, L::TOTAL, st>>>(tq, tk, tv, tdo, p);
-  k2<<<nqb * p.Hq * p.B, AB_THREADS, L::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  tfb::launch_k(k1, nqb * p.Hkv * p.B, AB_THREADS, L::TOTAL, st, tq, tk, tv, tdo, p);
+  tfb::launch_k(k2, nqb * p.Hq * p.B, AB_THREADS, L::TOTAL, st, tq, tk, tv, tdo, p);
   return int(cudaGetLastError());
 }
 
@@ -566,7 +569,7 @@ TFB_API int tfb_attn_bwd(const void* q, long long ldq, int q_col0, const void* k
   {
     const long long threads = (long long)B * S * Hq * D / 8;
     const int blocks = int((threads + 255) / 256);
-    attn_delta_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), ldo,
+    tfb::launch_k(attn_delta_kernel, blocks, 256, 0, st, static_cast<const __nv_bfloat16*>(o), ldo,
                                               static_cast<const __nv_bfloat16*>(dout), lddo, delta, B, S, Hq, D);
   }
   CUtensorMap tq, tk, tv, tdo;

@@ -179,6 +179,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  tfb::pdl_sync();   // set-up above touches no global memory; operands written by the previous kernel are read below
   const uint32_t tS0 = tmem_base, tO0 = tmem_base + 256;
 
   if (warp == 0) {
@@ -350,7 +351,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
   auto kern = attn_fwd_kernel<D>;
   if (int e = ensure_dyn_smem(once, kern, L::TOTAL)) return e;
   const int npair = (p.S + 2 * ATT_BM - 1) / (2 * ATT_BM);
-  kern<<<npair * p.B * p.Hq, ATT_THREADS, L::TOTAL, st>>>(tq, tk, tv, p);
+  tfb::launch_k(kern, npair * p.B * p.Hq, ATT_THREADS, L::TOTAL, st, tq, tk, tv, p);
   return int(cudaGetLastError());
 }
 

@@ -22,6 +22,7 @@ namespace tfb {
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, const int* __restrict__ positions, int T, int S,
                             int pos_offset, int n_heads, int D, long long ld, float sign) {
+  tfb::pdl_sync();
   const int half = D >> 1;
   const int vec_per_head = half >> 3;  // 8 pairs per thread
   const long long total = (long long)T * n_heads * vec_per_head;
@@ -83,6 +84,7 @@ __device__ __forceinline__ float act_grad(float g, int act) {
 // `rows_dev` (optional): a device-side row count below M, e.g. the routed rows of an expert buffer provisioned for more.
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long M,
                                int F, int act, const int* __restrict__ rows_dev) {
+  tfb::pdl_sync();
   const int vec = F >> 3;
   if (rows_dev) M = min(M, (long long)max(*rows_dev, 0));
   const long long total = M * vec;
@@ -109,6 +111,7 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat
 __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
                                __nv_bfloat16* __restrict__ din, long long M, int F, int act,
                                const int* __restrict__ rows_dev) {
+  tfb::pdl_sync();
   const int vec = F >> 3;
   if (rows_dev) M = min(M, (long long)max(*rows_dev, 0));
   const long long total = M * vec;
@@ -139,6 +142,7 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_
 // Plain activation y = act(x) and dx = dy * act'(x) over n elements (n % 8 == 0).
 __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n8,
                                int act) {
+  tfb::pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 u = reinterpret_cast<const uint4*>(x)[i];
     uint32_t* p = reinterpret_cast<uint32_t*>(&u);
@@ -152,6 +156,7 @@ __global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
 }
 __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                                __nv_bfloat16* __restrict__ dx, long long n8, int act) {
+  tfb::pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     const uint4 u = reinterpret_cast<const uint4*>(x)[i];
     uint4 d = reinterpret_cast<const uint4*>(dy)[i];
@@ -173,6 +178,7 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ W,
                                      const __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ out, int T,
                                      int S, int H, int V) {
+  tfb::pdl_sync();
   const int vec = H >> 3;
   const long long total = (long long)T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -198,6 +204,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __
 
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
                                      float* __restrict__ dW, float* __restrict__ dP, int T, int S, int H, int V) {
+  tfb::pdl_sync();
   const int vec = H >> 2;
   const long long total = (long long)T * vec;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -222,6 +229,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __
 // out = a + b (bf16), n % 8 == 0
 __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                            __nv_bfloat16* __restrict__ out, long long n8) {
+  tfb::pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     uint4 u = reinterpret_cast<const uint4*>(a)[i];
     const uint4 v = reinterpret_cast<const uint4*>(b)[i];
@@ -250,14 +258,14 @@ TFB_API int tfb_rope(void* x, const float* cos_t, const float* sin_t, const int*
                      int pos_offset, int n_heads, int D, long long ld, int backward, void* stream) {
   if (D % 16 || ld % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return TFB_ERR_ARG;
   const long long work = (long long)T * n_heads * (D / 16);
-  rope_kernel<<<grid_for(work), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(rope_kernel, grid_for(work), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(x), cos_t, sin_t, positions, T, S, pos_offset, n_heads, D, ld, backward ? -1.f : 1.f);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_glu_fwd_rows(const void* in, void* out, long long M, int F, int act, const int* rows_dev, void* stream) {
   if (F % 8) return TFB_ERR_ARG;
-  glu_fwd_kernel<<<grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(glu_fwd_kernel, grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), M, F, act, rows_dev);
   return int(cudaGetLastError());
 }
@@ -267,7 +275,7 @@ TFB_API int tfb_glu_fwd(const void* in, void* out, long long M, int F, int act, 
 TFB_API int tfb_glu_bwd_rows(const void* in, const void* dout, void* din, long long M, int F, int act, const int* rows_dev,
                              void* stream) {
   if (F % 8) return TFB_ERR_ARG;
-  glu_bwd_kernel<<<grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(glu_bwd_kernel, grid_for(M * (F / 8)), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(din),
       M, F, act, rows_dev);
   return int(cudaGetLastError());
@@ -277,13 +285,13 @@ TFB_API int tfb_glu_bwd(const void* in, const void* dout, void* din, long long M
 }
 TFB_API int tfb_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
   if (n % 8) return TFB_ERR_ARG;
-  act_fwd_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(act_fwd_kernel, grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n / 8, act);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_act_bwd(const void* x, const void* dy, void* dx, long long n, int act, void* stream) {
   if (n % 8) return TFB_ERR_ARG;
-  act_bwd_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(act_bwd_kernel, grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx),
       n / 8, act);
   return int(cudaGetLastError());
@@ -291,7 +299,7 @@ TFB_API int tfb_act_bwd(const void* x, const void* dy, void* dx, long long n, in
 TFB_API int tfb_embedding_fwd(const long long* ids, const void* W, const void* P, void* out, int T, int S, int H, int V,
                               void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  embedding_fwd_kernel<<<grid_for((long long)T * (H / 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(embedding_fwd_kernel, grid_for((long long)T * (H / 8)), 256, 0, static_cast<cudaStream_t>(stream), 
       ids, static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(P), static_cast<__nv_bfloat16*>(out),
       T, S, H, V);
   return int(cudaGetLastError());
@@ -299,13 +307,13 @@ TFB_API int tfb_embedding_fwd(const long long* ids, const void* W, const void* P
 TFB_API int tfb_embedding_bwd(const long long* ids, const void* dout, float* dW, float* dP, int T, int S, int H, int V,
                               void* stream) {
   if (H % 4) return TFB_ERR_ARG;
-  embedding_bwd_kernel<<<grid_for((long long)T * (H / 4)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(embedding_bwd_kernel, grid_for((long long)T * (H / 4)), 256, 0, static_cast<cudaStream_t>(stream), 
       ids, static_cast<const __nv_bfloat16*>(dout), dW, dP, T, S, H, V);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {
   if (n % 8) return TFB_ERR_ARG;
-  add_kernel<<<grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(add_kernel, grid_for(n / 8), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(out),
       n / 8);
   return int(cudaGetLastError());

@@ -28,6 +28,7 @@ constexpr int FQ_MAX_PER_LANE = 32;   // block <= 1024 elements
 template <typename T>
 __global__ void fake_quant_block_kernel(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ scale_out,
                                         long long n, int block, int bits, int symmetric) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -78,6 +79,7 @@ __global__ void fake_quant_block_kernel(const T* __restrict__ x, T* __restrict__
 template <typename T>
 __global__ void lsq_fwd_kernel(const T* __restrict__ x, const float* __restrict__ step, T* __restrict__ y, long long n,
                                float qn, float qp) {
+  tfb::pdl_sync();
   const float s = fmaxf(*step, 1e-12f), inv = 1.f / s;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     st_f(y + i, fminf(fmaxf(rintf(ld_f(x + i) * inv), qn), qp) * s);
@@ -87,6 +89,7 @@ template <typename T>
 __global__ void lsq_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ step,
                                T* __restrict__ dx, float* __restrict__ dstep, long long n, float qn, float qp,
                                float grad_scale) {
+  tfb::pdl_sync();
   const float s = fmaxf(*step, 1e-12f), inv = 1.f / s;
   float acc = 0.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -123,10 +126,10 @@ TFB_API int tfb_fake_quant_block(const void* x, void* y, void* scale_out, long l
   const long long nb = (n + block - 1) / block;
   auto st = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    fake_quant_block_kernel<__nv_bfloat16><<<fq_grid(nb), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
+    tfb::launch_k(fake_quant_block_kernel<__nv_bfloat16>, fq_grid(nb), 256, 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
                                                                           static_cast<float*>(scale_out), n, block, bits, symmetric);
   else
-    fake_quant_block_kernel<float><<<fq_grid(nb), 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y),
+    tfb::launch_k(fake_quant_block_kernel<float>, fq_grid(nb), 256, 0, st, static_cast<const float*>(x), static_cast<float*>(y),
                                                                 static_cast<float*>(scale_out), n, block, bits, symmetric);
   return int(cudaGetLastError());
 }
@@ -136,10 +139,10 @@ TFB_API int tfb_lsq_fwd(const void* x, const void* step, void* y, long long n, f
   auto st = static_cast<cudaStream_t>(stream);
   const int grid = int(std::min<long long>((n + 255) / 256, (long long)sm_count() * 8));
   if (dtype == 0)
-    lsq_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(step),
+    tfb::launch_k(lsq_fwd_kernel<__nv_bfloat16>, grid, 256, 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(step),
                                                         static_cast<__nv_bfloat16*>(y), n, qn, qp);
   else
-    lsq_fwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), static_cast<const float*>(step), static_cast<float*>(y), n, qn, qp);
+    tfb::launch_k(lsq_fwd_kernel<float>, grid, 256, 0, st, static_cast<const float*>(x), static_cast<const float*>(step), static_cast<float*>(y), n, qn, qp);
   return int(cudaGetLastError());
 }
 
@@ -150,11 +153,11 @@ TFB_API int tfb_lsq_bwd(const void* x, const void* dy, const void* step, void* d
   auto st = static_cast<cudaStream_t>(stream);
   const int grid = int(std::min<long long>((n + 255) / 256, (long long)sm_count() * 8));
   if (dtype == 0)
-    lsq_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
+    tfb::launch_k(lsq_bwd_kernel<__nv_bfloat16>, grid, 256, 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
                                                         static_cast<const float*>(step), static_cast<__nv_bfloat16*>(dx),
                                                         static_cast<float*>(dstep), n, qn, qp, grad_scale);
   else
-    lsq_bwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), static_cast<const float*>(dy), static_cast<const float*>(step),
+    tfb::launch_k(lsq_bwd_kernel<float>, grid, 256, 0, st, static_cast<const float*>(x), static_cast<const float*>(dy), static_cast<const float*>(step),
                                                 static_cast<float*>(dx), static_cast<float*>(dstep), n, qn, qp, grad_scale);
   return int(cudaGetLastError());
 }

@@ -295,6 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int nctas = int(gridDim.x) - ncopy;  // CTAs that run GEMM tiles
   const int cta = int(blockIdx.x) - ncopy;
   if (cta < 0) {
+    tfb::pdl_sync();
     tp_copy_role(p, int(blockIdx.x), ncopy, smem_base, bar_full, abort_flag);
     return;
   }
@@ -322,6 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  tfb::pdl_sync();   // set-up above touches no global memory; operands written by the previous kernel are read below
 
   const int total_kb = (p.K + BK - 1) / BK;
   const int num_work = p.tiles_m * p.tiles_n * (p.group_mode == 2 ? p.num_experts : p.splits);
@@ -693,7 +695,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   static DeviceOnce once;
   auto kern = gemm_bf16_kernel<A_MN, B_MN, BN>;
   if (int e = ensure_dyn_smem(once, kern, L::TOTAL)) return e;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, st>>>(ta, tb, tc, tpeers, p);
+  tfb::launch_k(kern, grid, GEMM_THREADS, L::TOTAL, st, ta, tb, tc, tpeers, p);
   return int(cudaGetLastError());
 }
 
@@ -768,6 +770,7 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(float* __restrict_
                                                               const __nv_bfloat16* __restrict__ bias,
                                                               const __nv_bfloat16* __restrict__ residual, long long ldr, int M, int N,
                                                               int act, int out_fp32) {
+  tfb::pdl_sync();
   const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;      // 4 consecutive columns
   if (i >= (long long)M * ldw) return;
   const int m = int(i / ldw), n = int(i % ldw);
@@ -821,7 +824,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
                                 stream, nullptr, best_s))
           return rc0;
         const long long quads = (long long)M * ldw / 4;
-        splitk_finalize_kernel<<<int((quads + 255) / 256), 256, 0, st0>>>(ws, ldw, C, ldc, static_cast<const __nv_bfloat16*>(bias),
+        tfb::launch_k(splitk_finalize_kernel, int((quads + 255) / 256), 256, 0, st0, ws, ldw, C, ldc, static_cast<const __nv_bfloat16*>(bias),
                                                                           static_cast<const __nv_bfloat16*>(residual), ldr, M, N, act,
                                                                           out_mode == 1);
         return int(cudaGetLastError());
@@ -837,7 +840,6 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
     const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
     if (BN == 256 && gmode != 2 && out_mode != 2 && t256 < sms && t128 > t256) BN = 128;
   }
-  if (tp && (tp->mode & TP_WG) && !b_mn && (tp->wg_rows / tp->wg_world) % 256) BN = 128;   // tiles stay inside one row shard
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_tmap_2d(&ta, A, 2, K, M, lda * 2, BK, BM);

@@ -42,6 +42,7 @@ struct F8Smem {
 
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb, const F8Params p) {
+  tfb::pdl_sync();
   using L = F8Smem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -202,6 +203,7 @@ __device__ __forceinline__ uint8_t f32_to_e4m3(float x) {
 // x [rows, K] bf16 -> q [rows, K] e4m3 + scale [rows, K/128] fp32 (amax / 448 per 1x128 block); one warp per block
 __global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                        float* __restrict__ scale, long long rows, int K) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int kblocks = (K + 127) / 128;
@@ -237,6 +239,7 @@ __global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint
 __global__ void __launch_bounds__(256) quant_fp8_128x128_kernel(const __nv_bfloat16* __restrict__ w,
                                                                 uint8_t* __restrict__ q, float* __restrict__ scale,
                                                                 int N, int K) {
+  tfb::pdl_sync();
   __shared__ float red[8];
   const int kb = blockIdx.x, nb = blockIdx.y;
   const int kblocks = gridDim.x;
@@ -284,7 +287,7 @@ TFB_API int tfb_gemm_fp8_blockscaled(const void* A, const float* sa, const void*
   if (int e = ensure_dyn_smem(once, gemm_fp8_kernel, F8Smem::TOTAL)) return e;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_fp8_kernel<<<grid, F8_THREADS, F8Smem::TOTAL, static_cast<cudaStream_t>(stream)>>>(ta, tb, p);
+  tfb::launch_k(gemm_fp8_kernel, grid, F8_THREADS, F8Smem::TOTAL, static_cast<cudaStream_t>(stream), ta, tb, p);
   return int(cudaGetLastError());
 }
 
@@ -292,14 +295,14 @@ TFB_API int tfb_quant_fp8_1x128(const void* x, void* q, float* scale, long long 
   if (K % 4) return TFB_ERR_ARG;
   const long long warps = rows * ((K + 127) / 128);
   const long long blocks = (warps * 32 + 255) / 256;
-  quant_fp8_1x128_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(quant_fp8_1x128_kernel, (unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, K);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_quant_fp8_128x128(const void* w, void* q, float* scale, int N, int K, void* stream) {
   dim3 g((K + 127) / 128, (N + 127) / 128);
-  quant_fp8_128x128_kernel<<<g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(quant_fp8_128x128_kernel, g, 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scale, N, K);
   return int(cudaGetLastError());
 }

@@ -174,6 +174,7 @@ __device__ __forceinline__ void wq_convert(const uint32_t (&w)[8], uint32_t sbit
 
 template <int FMT, int AROWS>
 __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ CUtensorMap tma_a, const WqParams p) {
+  tfb::pdl_sync();
   using PL = WqPlan<AROWS>;
   constexpr int WQ_STAGES = PL::STAGES, WQ_A_BYTES = PL::A_BYTES, WQ_STAGE = PL::STAGE, WQ_RAW_OFF = PL::RAW_OFF, WQ_BAR_OFF = PL::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
@@ -415,6 +416,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
 template <int FMT>
 __global__ void __launch_bounds__(256) wq_dequant_kernel(const uint8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scales, int group,
                                                           __nv_bfloat16* __restrict__ out, long long ld, int KB) {
+  tfb::pdl_sync();
   constexpr int RB = wq_row_bytes(FMT);
   const int kb = blockIdx.x, nb = blockIdx.y, r = threadIdx.x & 127, h = threadIdx.x >> 7;
   const long long tile = (long long)nb * KB + kb;
@@ -451,11 +453,11 @@ TFB_API int tfb_wq_dequant(const void* wq, const void* scales, int fmt, int grou
   auto* o = static_cast<__nv_bfloat16*>(out);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (fmt) {
-    case 0: wq_dequant_kernel<0><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
-    case 1: wq_dequant_kernel<1><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
-    case 2: wq_dequant_kernel<2><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
-    case 3: wq_dequant_kernel<3><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
-    default: wq_dequant_kernel<4><<<grid, 256, 0, st>>>(c, sc, group, o, ld, K / WQ_BK); break;
+    case 0: tfb::launch_k(wq_dequant_kernel<0>, grid, 256, 0, st, c, sc, group, o, ld, K / WQ_BK); break;
+    case 1: tfb::launch_k(wq_dequant_kernel<1>, grid, 256, 0, st, c, sc, group, o, ld, K / WQ_BK); break;
+    case 2: tfb::launch_k(wq_dequant_kernel<2>, grid, 256, 0, st, c, sc, group, o, ld, K / WQ_BK); break;
+    case 3: tfb::launch_k(wq_dequant_kernel<3>, grid, 256, 0, st, c, sc, group, o, ld, K / WQ_BK); break;
+    default: tfb::launch_k(wq_dequant_kernel<4>, grid, 256, 0, st, c, sc, group, o, ld, K / WQ_BK); break;
   }
   const int rc = int(cudaGetLastError());
   return rc ? -1000 - rc : 0;
@@ -505,7 +507,7 @@ TFB_API int tfb_gemm_wq(const void* A, long long lda, const void* wq, const void
   const long long work = (long long)tiles * p.splits;
   const int grid = int(work < sms ? work : sms);
   const int ai = arows == 16 ? 0 : 1;
-  kerns[ai][fmt]<<<grid, WQ_THREADS, smem_of[ai], static_cast<cudaStream_t>(stream)>>>(ta, p);
+  tfb::launch_k(kerns[ai][fmt], grid, WQ_THREADS, smem_of[ai], static_cast<cudaStream_t>(stream), ta, p);
   const int rc = int(cudaGetLastError());
   return rc ? -1000 - rc : p.splits;
 }

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(512, 2) cross_entropy_regs_kernel(const __nv_b
                                                                  float* __restrict__ loss, float* __restrict__ lse_out,
                                                                  __nv_bfloat16* dlogits, const float* __restrict__ scale_ptr, int V,
                                                                  long long ld, long long ignore_index, float eps, float zw) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   const long long t = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(logits + t * ld);
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(const __nv_bfloat16*
                                                             __nv_bfloat16* dlogits, const float* __restrict__ scale_ptr,
                                                             int V, long long ld, long long ignore_index, float eps,
                                                             float zw, int vocab_start, int vocab_total) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   const long long t = blockIdx.x;
   const __nv_bfloat16* row = logits + t * ld;
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(512) cross_entropy_3pass_kernel(const __nv_bfl
                                                                   float* __restrict__ loss, float* __restrict__ lse_out,
                                                                   __nv_bfloat16* dlogits, const float* __restrict__ scale_ptr, int V,
                                                                   long long ld, long long ignore_index, float eps, float zw) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   constexpr float L2E = 1.4426950408889634f;
   const long long t = blockIdx.x;
@@ -289,6 +292,7 @@ __global__ void __launch_bounds__(512) cross_entropy_3pass_kernel(const __nv_bfl
 
 // sum over n of x^2, accumulated into *out (fp32).  x is fp32.
 __global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   float acc = 0.f;
   const long long n4 = n >> 2;
@@ -307,6 +311,7 @@ __global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ x,
 // A non-finite norm yields clip 0 and sets *found_inf (dynamic loss scaling skips that step).
 __global__ void clip_factor_kernel(const float* __restrict__ sumsq, float inv_scale, float max_norm,
                                    float* __restrict__ norm_out, float* __restrict__ clip_out, int* found_inf) {
+  tfb::pdl_sync();
   const float nrm = sqrtf(*sumsq) * inv_scale;
   float c = inv_scale;
   if (!isfinite(nrm)) {
@@ -328,6 +333,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float
                                                     float* __restrict__ v, __nv_bfloat16* __restrict__ p_lp,
                                                     long long n, AdamArgs a, const float* __restrict__ gscale_ptr,
                                                     int zero_grad, const float* __restrict__ hyper) {
+  tfb::pdl_sync();
   // hyper (optional, device): {lr, 1 - beta1^t, 1 - beta2^t}; lets a captured CUDA graph see per-step values
   if (hyper) { a.lr = hyper[0]; a.bc1 = hyper[1]; a.bc2 = hyper[2]; }
   const float gs = gscale_ptr ? *gscale_ptr : 1.f;
@@ -383,6 +389,7 @@ __global__ void __launch_bounds__(256) lion_sgd_kernel(float* __restrict__ p, fl
                                                        float* __restrict__ m, __nv_bfloat16* __restrict__ p_lp,
                                                        long long n, float lr, float b1, float b2, float wd, int mode,
                                                        const float* __restrict__ gscale_ptr, int zero_grad) {
+  tfb::pdl_sync();
   const float gs = gscale_ptr ? *gscale_ptr : 1.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float gr = g[i] * gs;
@@ -404,10 +411,12 @@ __global__ void __launch_bounds__(256) lion_sgd_kernel(float* __restrict__ p, fl
 
 // dst(bf16) = src(fp32) and dst(fp32) = src(bf16)
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, long long n) {
+  tfb::pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     d[i] = __float2bfloat16(s[i]);
 }
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d, long long n) {
+  tfb::pdl_sync();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     d[i] = __bfloat162float(s[i]);
 }
@@ -431,31 +440,31 @@ TFB_API int tfb_cross_entropy(const void* logits, const long long* labels, float
   // Small vocabularies fit in two vectors per thread at full occupancy; for larger ones the streaming kernel, which
   // keeps four CTAs per SM in flight, measured faster than holding the row in registers (fewer resident warps).
   if (vec && V <= 512 * 8 * 2) {
-    cross_entropy_regs_kernel<2><<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+    tfb::launch_k(cross_entropy_regs_kernel<2>, T, 512, 0, static_cast<cudaStream_t>(stream), 
         static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V, ld,
         ignore_index, label_smoothing, z_weight);
     return int(cudaGetLastError());
   }
   if (vec && dlogits == logits) {
-    cross_entropy_3pass_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+    tfb::launch_k(cross_entropy_3pass_kernel, T, 512, 0, static_cast<cudaStream_t>(stream), 
         static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V, ld,
         ignore_index, label_smoothing, z_weight);
     return int(cudaGetLastError());
   }
-  cross_entropy_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(cross_entropy_kernel, T, 512, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, static_cast<__nv_bfloat16*>(dlogits), scale_ptr, V,
       ld, ignore_index, label_smoothing, z_weight, 0, V);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_sumsq_f32(const float* x, long long n, float* out, void* stream) {
-  sumsq_kernel<<<grid_cap(n / 4 + 1, 512, 2), 512, 0, static_cast<cudaStream_t>(stream)>>>(x, n, out);
+  tfb::launch_k(sumsq_kernel, grid_cap(n / 4 + 1, 512, 2), 512, 0, static_cast<cudaStream_t>(stream), x, n, out);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_clip_factor(const float* sumsq, float inv_scale, float max_norm, float* norm_out, float* clip_out,
                             int* found_inf, void* stream) {
-  clip_factor_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sumsq, inv_scale, max_norm, norm_out, clip_out,
+  tfb::launch_k(clip_factor_kernel, 1, 1, 0, static_cast<cudaStream_t>(stream), sumsq, inv_scale, max_norm, norm_out, clip_out,
                                                                     found_inf);
   return int(cudaGetLastError());
 }
@@ -468,25 +477,25 @@ TFB_API int tfb_adamw(float* p, float* g, float* m, float* v, void* p_lp, long l
     return TFB_ERR_ARG;
   if (p_lp && (reinterpret_cast<uintptr_t>(p_lp) & 7)) return TFB_ERR_ARG;
   AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, float(step)), 1.f - powf(beta2, float(step))};
-  adamw_kernel<<<grid_cap(n / 4 + 1, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(adamw_kernel, grid_cap(n / 4 + 1, 256, 8), 256, 0, static_cast<cudaStream_t>(stream), 
       p, g, m, v, static_cast<__nv_bfloat16*>(p_lp), n, a, gscale_ptr, zero_grad, hyper);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_lion_sgd(float* p, float* g, float* m, void* p_lp, long long n, float lr, float b1, float b2, float wd,
                          int mode, const float* gscale_ptr, int zero_grad, void* stream) {
-  lion_sgd_kernel<<<grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(lion_sgd_kernel, grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream), 
       p, g, m, static_cast<__nv_bfloat16*>(p_lp), n, lr, b1, b2, wd, mode, gscale_ptr, zero_grad);
   return int(cudaGetLastError());
 }
 
 TFB_API int tfb_cast_f32_bf16(const float* s, void* d, long long n, void* stream) {
-  cast_f32_bf16_kernel<<<grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(cast_f32_bf16_kernel, grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream), 
       s, static_cast<__nv_bfloat16*>(d), n);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_cast_bf16_f32(const void* s, float* d, long long n, void* stream) {
-  cast_bf16_f32_kernel<<<grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(cast_bf16_f32_kernel, grid_cap(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(s), d, n);
   return int(cudaGetLastError());
 }

@@ -48,6 +48,7 @@ __device__ __forceinline__ float vp_reduce_max(float v, float* sh) {
 __global__ void __launch_bounds__(512) ce_vp_stats_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                                                           float4* __restrict__ stats, int V, long long ld, long long vocab_lo,
                                                           long long vocab_total, long long ignore_index) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   const long long t = blockIdx.x;
   const __nv_bfloat16* row = logits + t * ld;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(512) ce_vp_stats_kernel(const __nv_bfloat16* _
 __global__ void __launch_bounds__(512) ce_vp_grad_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                                                          const float* __restrict__ lse, const float* __restrict__ scale_ptr, int V,
                                                          long long ld, long long vocab_lo, long long ignore_index) {
+  tfb::pdl_sync();
   const long long t = blockIdx.x;
   __nv_bfloat16* row = logits + t * ld;
   const long long label = labels[t];
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(512) ce_vp_grad_kernel(__nv_bfloat16* __restri
 TFB_API int tfb_ce_vp_stats(const void* logits, const long long* labels, float* stats, int T, int V, long long ld,
                             long long vocab_lo, long long vocab_total, long long ignore_index, void* stream) {
   if (T <= 0 || V <= 0 || (reinterpret_cast<uintptr_t>(stats) & 15)) return TFB_ERR_ARG;
-  tfb::ce_vp_stats_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(logits), labels,
+  tfb::launch_k(tfb::ce_vp_stats_kernel, T, 512, 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(logits), labels,
                                                                           reinterpret_cast<float4*>(stats), V, ld, vocab_lo,
                                                                           vocab_total, ignore_index);
   return int(cudaGetLastError());
@@ -133,7 +135,7 @@ TFB_API int tfb_ce_vp_stats(const void* logits, const long long* labels, float* 
 TFB_API int tfb_ce_vp_grad(void* logits, const long long* labels, const float* lse, const float* scale, int T, int V, long long ld,
                            long long vocab_lo, long long ignore_index, void* stream) {
   if (T <= 0 || V <= 0) return TFB_ERR_ARG;
-  tfb::ce_vp_grad_kernel<<<T, 512, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(logits), labels, lse, scale, V,
+  tfb::launch_k(tfb::ce_vp_grad_kernel, T, 512, 0, static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16*>(logits), labels, lse, scale, V,
                                                                          ld, vocab_lo, ignore_index);
   return int(cudaGetLastError());
 }

@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const __nv_bfloat16* _
                                                           float* __restrict__ topk_w, float* __restrict__ probs_out,
                                                           int* __restrict__ counts, float* __restrict__ prob_sums,
                                                           float* __restrict__ lse_out, float* __restrict__ lse_sq_sum) {
+  tfb::pdl_sync();
   __shared__ int s_cnt[MAX_E];
   __shared__ float s_ps[MAX_E];
   __shared__ float s_lsq;
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const __nv_bfloat16* _
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ seg_start,
                                 int* __restrict__ cursor, int* __restrict__ expert_of_tile, int max_tiles,
                                 int* __restrict__ total_rows) {
+  tfb::pdl_sync();
   if (threadIdx.x == 0) {
     int off = 0, tile = 0;
     for (int e = 0; e < E; ++e) {
@@ -141,6 +143,7 @@ constexpr int PERM_ROWS = 64;
 __global__ void __launch_bounds__(256) moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
                                                           int* __restrict__ cursor, int* __restrict__ row_of, int* __restrict__ token_of_row,
                                                           __nv_bfloat16* __restrict__ xp, int T, int K, int H, int E) {
+  tfb::pdl_sync();
   __shared__ int s_cnt[MAX_E];
   __shared__ int s_base[MAX_E];
   __shared__ int s_rank[PERM_ROWS];
@@ -180,6 +183,7 @@ __global__ void __launch_bounds__(256) moe_permute_kernel(const __nv_bfloat16* _
 __global__ void __launch_bounds__(256) moe_zero_pads_kernel(__nv_bfloat16* __restrict__ buf, int H, const int* __restrict__ seg_start,
                                                             const int* __restrict__ counts, int E, const int* __restrict__ total,
                                                             int max_rows) {
+  tfb::pdl_sync();
   const int seg = blockIdx.x;                       // 0..E-1: expert padding, E: tail
   int r0, r1;
   if (seg < E) {
@@ -203,6 +207,7 @@ __global__ void __launch_bounds__(256) moe_zero_pads_kernel(__nv_bfloat16* __res
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ row_of,
                                    const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ y,
                                    const __nv_bfloat16* __restrict__ residual, int T, int K, int H) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
@@ -240,6 +245,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const i
 __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ yp,
                                        const int* __restrict__ row_of, const float* __restrict__ topk_w,
                                        __nv_bfloat16* __restrict__ dyp, float* __restrict__ dw, int T, int K, int H) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (w >= (long long)T * K) return;
@@ -269,6 +275,7 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, con
 // backward of permute: dx[t] = sum_k dxp[row_of[t,k]]; one warp per token
 __global__ void moe_permute_bwd_kernel(const __nv_bfloat16* __restrict__ dxp, const int* __restrict__ row_of,
                                        __nv_bfloat16* __restrict__ dx, int T, int K, int H) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
@@ -310,7 +317,7 @@ TFB_API int tfb_router_topk2(const void* logits, int logits_f32, int T, int E, i
                              float* probs, int* counts, float* prob_sums, float* lse, float* lse_sq_sum, void* stream) {
   if (E > MAX_E || K > MAX_K || K < 1 || K > E) return TFB_ERR_LIMIT;
   const int blocks = int(std::min<long long>(warps_to_blocks(T), 148 * 8));
-  router_topk_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(router_topk_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), 
       logits_f32 ? nullptr : static_cast<const __nv_bfloat16*>(logits),
       logits_f32 ? static_cast<const float*>(logits) : nullptr, T, E, K, renorm, topk_idx, topk_w, probs, counts,
       prob_sums, lse, lse_sq_sum);
@@ -318,7 +325,7 @@ TFB_API int tfb_router_topk2(const void* logits, int logits_f32, int T, int E, i
 }
 TFB_API int tfb_moe_plan(const int* counts, int E, int* seg_start, int* cursor, int* expert_of_tile, int max_tiles,
                          int* total_rows, void* stream) {
-  moe_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, E, seg_start, cursor, expert_of_tile,
+  tfb::launch_k(moe_plan_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), counts, E, seg_start, cursor, expert_of_tile,
                                                                   max_tiles, total_rows);
   return int(cudaGetLastError());
 }
@@ -330,7 +337,7 @@ TFB_API int tfb_moe_permute2(const void* x, const int* topk_idx, int* cursor, in
                              int H, int E, void* stream) {
   if (H % 8 || E < 1 || E > MAX_E) return TFB_ERR_ARG;
   const long long rows = (long long)T * K;
-  moe_permute_kernel<<<int((rows + PERM_ROWS - 1) / PERM_ROWS), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(moe_permute_kernel, int((rows + PERM_ROWS - 1) / PERM_ROWS), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), topk_idx, cursor, row_of, token_of_row, static_cast<__nv_bfloat16*>(xp), T, K, H, E);
   return int(cudaGetLastError());
 }
@@ -338,14 +345,14 @@ TFB_API int tfb_moe_permute2(const void* x, const int* topk_idx, int* cursor, in
 TFB_API int tfb_moe_zero_pads(void* buf, int H, const int* seg_start, const int* counts, int E, const int* total, int max_rows,
                               void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  moe_zero_pads_kernel<<<dim3(E + 1, 296), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(buf), H, seg_start,
+  tfb::launch_k(moe_zero_pads_kernel, dim3(E + 1, 296), 256, 0, static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16*>(buf), H, seg_start,
                                                                                       counts, E, total, max_rows);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_moe_combine(const void* yp, const int* row_of, const float* topk_w, void* y, const void* residual,
                             int T, int K, int H, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  moe_combine_kernel<<<warps_to_blocks(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(moe_combine_kernel, warps_to_blocks(T), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(yp), row_of, topk_w, static_cast<__nv_bfloat16*>(y),
       static_cast<const __nv_bfloat16*>(residual), T, K, H);
   return int(cudaGetLastError());
@@ -353,14 +360,14 @@ TFB_API int tfb_moe_combine(const void* yp, const int* row_of, const float* topk
 TFB_API int tfb_moe_combine_bwd(const void* dy, const void* yp, const int* row_of, const float* topk_w, void* dyp,
                                 float* dw, int T, int K, int H, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  moe_combine_bwd_kernel<<<warps_to_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(moe_combine_bwd_kernel, warps_to_blocks((long long)T * K), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(yp), row_of, topk_w,
       static_cast<__nv_bfloat16*>(dyp), dw, T, K, H);
   return int(cudaGetLastError());
 }
 TFB_API int tfb_moe_permute_bwd(const void* dxp, const int* row_of, void* dx, int T, int K, int H, void* stream) {
   if (H % 8) return TFB_ERR_ARG;
-  moe_permute_bwd_kernel<<<warps_to_blocks(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  tfb::launch_k(moe_permute_bwd_kernel, warps_to_blocks(T), 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(dxp), row_of, static_cast<__nv_bfloat16*>(dx), T, K, H);
   return int(cudaGetLastError());
 }

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __re
                                                        __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
                                                        float* __restrict__ rstd_out, float* __restrict__ mean_out,
                                                        int rows, int H, float eps) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -134,6 +135,7 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const __nv_bfloat16* __re
                                                        const __nv_bfloat16* __restrict__ dres,
                                                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
                                                        float* __restrict__ db, int rows, int H) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -227,6 +229,7 @@ __global__ void __launch_bounds__(256) norm_dw_kernel(const __nv_bfloat16* __res
                                                       const float* __restrict__ rstd_in,
                                                       const float* __restrict__ mean_in, float* __restrict__ dw,
                                                       float* __restrict__ db, int rows, int H) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = (blockIdx.x * 32 + lane) * 8;
   float aw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -267,6 +270,7 @@ __global__ void __launch_bounds__(256) norm_fwd_rowblock_kernel(const __nv_bfloa
                                                                 __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
                                                                 float* __restrict__ rstd_out, float* __restrict__ mean_out, int rows, int H,
                                                                 float eps) {
+  tfb::pdl_sync();
   __shared__ float red[2][8];
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long off = (long long)row * H;
@@ -362,11 +366,11 @@ static int launch_fwd(const void* x, const void* res, const void* w, const void*
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto Ho = static_cast<__nv_bfloat16*>(h_out);
   if (H >= 2048 && rows <= 4 * sm_count()) {
-    if (H <= 4096) norm_fwd_rowblock_kernel<2, LN><<<rows, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
-    else norm_fwd_rowblock_kernel<4, LN><<<rows, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
+    if (H <= 4096) tfb::launch_k(norm_fwd_rowblock_kernel<2, LN>, rows, 256, 0, st, X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
+    else tfb::launch_k(norm_fwd_rowblock_kernel<4, LN>, rows, 256, 0, st, X, R, W, B, Y, Ho, rstd, mean, rows, H, eps);
     return int(cudaGetLastError());
   }
-#define TFB_GO(NC) norm_fwd_kernel<NC, LN><<<blocks, 256, 0, st>>>(X, R, W, B, Y, Ho, rstd, mean, rows, H, eps)
+#define TFB_GO(NC) tfb::launch_k(norm_fwd_kernel<NC, LN>, blocks, 256, 0, st, X, R, W, B, Y, Ho, rstd, mean, rows, H, eps)
   if (H <= 512) TFB_GO(2);
   else if (H <= 1024) TFB_GO(4);
   else if (H <= 2048) TFB_GO(8);
@@ -390,15 +394,15 @@ static int launch_bwd(const void* dy, const void* h, const void* w, const float*
     // 64 registers per thread: four resident blocks per SM; fewer leaves the loads of a row unhidden (94 -> 70 us at
     // 65536 x 512), more only adds atomics on dw
     const int blocks = min((rows + 7) / 8, sm_count() * 4);
-    if (H <= 512) norm_bwd_kernel<2, LN, true><<<blocks, 256, sm, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
-    else norm_bwd_kernel<4, LN, true><<<blocks, 256, sm, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
+    if (H <= 512) tfb::launch_k(norm_bwd_kernel<2, LN, true>, blocks, 256, sm, st, DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
+    else tfb::launch_k(norm_bwd_kernel<4, LN, true>, blocks, 256, sm, st, DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
   } else {
     const int blocks = min((rows + 7) / 8, sm_count() * 8);
-    if (H <= 2048) norm_bwd_kernel<8, LN, false><<<blocks, 256, 0, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
-    else if (H <= 4096) norm_bwd_kernel<16, LN, false><<<blocks, 256, 0, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
-    else norm_bwd_kernel<32, LN, false><<<blocks, 256, 0, st>>>(DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
+    if (H <= 2048) tfb::launch_k(norm_bwd_kernel<8, LN, false>, blocks, 256, 0, st, DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
+    else if (H <= 4096) tfb::launch_k(norm_bwd_kernel<16, LN, false>, blocks, 256, 0, st, DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
+    else tfb::launch_k(norm_bwd_kernel<32, LN, false>, blocks, 256, 0, st, DY, Hh, W, rstd, mean, DR, DX, dw, db, rows, H);
     dim3 g((H + 255) / 256, min(64, (rows + 7) / 8));
-    norm_dw_kernel<LN><<<g, 256, 0, st>>>(DY, Hh, rstd, mean, dw, db, rows, H);
+    tfb::launch_k(norm_dw_kernel<LN>, g, 256, 0, st, DY, Hh, rstd, mean, dw, db, rows, H);
   }
   return int(cudaGetLastError());
 }

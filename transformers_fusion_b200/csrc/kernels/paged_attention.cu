@@ -89,6 +89,7 @@ template <int MODE>
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ src, long long ld, int k_col0, int v_col0,
                                  const long long* __restrict__ slot_mapping, KvPool kpool, KvPool vpool, int T,
                                  int Hkv, int D) {
+  tfb::pdl_sync();
   const int lane = threadIdx.x & 31;
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   if (w >= (long long)T * Hkv) return;
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, long long ldq, KvPool kpool, KvPool vpool,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, float* __restrict__ acc_out,
     float* __restrict__ ml_out, int Hq, int Hkv, int splits, float scale) {
+  tfb::pdl_sync();
   __shared__ float sq[G][D];
   __shared__ float sp[G][DEC_TILE];
   __shared__ float red[G][DEC_THREADS / 32];
@@ -330,6 +332,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
 // o[b, h, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
 __global__ void paged_combine_kernel(const float* __restrict__ acc, const float* __restrict__ ml,
                                      __nv_bfloat16* __restrict__ o, long long ldo, int Hq, int D, int splits) {
+  tfb::pdl_sync();
   const int b = blockIdx.x, h = blockIdx.y;
   const long long base = ((long long)b * Hq + h) * splits;
   float M = -INFINITY;
@@ -355,7 +358,7 @@ static int launch_decode_g(int G, dim3 grid, cudaStream_t st, const __nv_bfloat1
                            int splits, float scale) {
 #define TFB_CASE(GG)                                                                                              \
   case GG:                                                                                                        \
-    paged_decode_kernel<MODE, D, GG><<<grid, DEC_THREADS, 0, st>>>(q, ldq, k, v, bt, max_pages, lens, acc, ml, Hq, \
+    tfb::launch_k(paged_decode_kernel<MODE, D, GG>, grid, DEC_THREADS, 0, st, q, ldq, k, v, bt, max_pages, lens, acc, ml, Hq, \
                                                                    Hkv, splits, scale);                           \
     break;
   switch (G) {
@@ -379,9 +382,9 @@ TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0,
   const unsigned blocks = unsigned((warps * 32 + 255) / 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto s = static_cast<const __nv_bfloat16*>(src);
-  if (mode == KV_BF16) kv_append_kernel<KV_BF16><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
-  else if (mode == KV_FP8) kv_append_kernel<KV_FP8><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
-  else if (mode == KV_Q4) kv_append_kernel<KV_Q4><<<blocks, 256, 0, st>>>(s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  if (mode == KV_BF16) tfb::launch_k(kv_append_kernel<KV_BF16>, blocks, 256, 0, st, s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  else if (mode == KV_FP8) tfb::launch_k(kv_append_kernel<KV_FP8>, blocks, 256, 0, st, s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
+  else if (mode == KV_Q4) tfb::launch_k(kv_append_kernel<KV_Q4>, blocks, 256, 0, st, s, ld, k_col0, v_col0, slot_mapping, kp, vp, T, Hkv, D);
   else return TFB_ERR_ARG;
   return int(cudaGetLastError());
 }
@@ -409,6 +412,6 @@ TFB_API int tfb_paged_decode(const void* q, long long ldq, void* k_data, void* k
   else return TFB_ERR_ARG;
 #undef TFB_GO
   if (rc) return rc;
-  paged_combine_kernel<<<dim3(B, Hq), 128, 0, st>>>(acc_ws, ml_ws, static_cast<__nv_bfloat16*>(o), ldo, Hq, D, splits);
+  tfb::launch_k(paged_combine_kernel, dim3(B, Hq), 128, 0, st, acc_ws, ml_ws, static_cast<__nv_bfloat16*>(o), ldo, Hq, D, splits);
   return int(cudaGetLastError());
 }

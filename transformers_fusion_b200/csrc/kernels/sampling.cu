@@ -52,6 +52,7 @@ struct SampleArgs {
 };
 
 __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleArgs a) {
+  tfb::pdl_sync();
   __shared__ float sh[32];
   __shared__ float s_thr;
   __shared__ int s_pick;
@@ -208,6 +209,6 @@ TFB_API int tfb_sample(const TfbSampleDesc* d, int B, void* stream) {
   if (B <= 0 || d->V <= 0) return TFB_ERR_ARG;
   tfb::SampleArgs a;
   memcpy(&a, d, sizeof(a));
-  tfb::sample_kernel<<<B, tfb::SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  tfb::launch_k(tfb::sample_kernel, B, tfb::SAMP_THREADS, 0, static_cast<cudaStream_t>(stream), a);
   return int(cudaGetLastError());
 }

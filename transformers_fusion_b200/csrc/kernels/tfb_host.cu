@@ -2,6 +2,8 @@
 
 #include <cudaTypedefs.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 namespace tfb {
@@ -56,6 +58,14 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0
                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? TFB_OK : TFB_ERR_DRIVER;
+}
+
+int pdl_enabled() {
+  static const int on = [] {
+    const char* e = getenv("TFB_PDL");
+    return (e && e[0] == '1') ? 1 : 0;
+  }();
+  return on;
 }
 
 int sm_count() {

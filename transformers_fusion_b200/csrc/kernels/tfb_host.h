@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #define TFB_API extern "C" __attribute__((visibility("default")))
 
 // All exported entry points return 0 on success, a negative tfb error or a positive cudaError_t.
@@ -27,6 +29,31 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0
                  uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, int swizzle128 = 1);
 
 int sm_count();
+
+// 1 when the environment has TFB_PDL=1 (read once): whether launches allow programmatic stream serialization.  Off by
+// default: measured on B200 under CUDA-graph replay it shortens a batch-1 decode step of the 8B shape by 5 % (1.45 -> 1.38
+// ms for 8 layers) but lengthens the 64-sequence training step of the 50M model by 3 % (31.1 -> 32.0 ms), where early-placed
+// CTAs of the next kernel take shared memory and registers from the tail of the running one.
+int pdl_enabled();
+
+// Launch of a kernel of this library: same meaning as kernel<<<grid, block, smem, stream>>>(args...), plus the launch
+// attribute that lets the kernel's CTAs be placed while the previous kernel of the stream drains (each kernel starts with
+// pdl_sync(), or with its own set-up followed by pdl_sync(), so nothing is read early).  Errors surface through
+// cudaGetLastError() as with the <<<>>> form.
+template <class... KArgs, class... Args>
+inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // One-time set-up per device.  Kernel attributes (cudaFuncSetAttribute) belong to the device that is current when
 // they are set, so a process that drives several GPUs has to repeat them on each: `first_use()` is true exactly once

@@ -45,6 +45,21 @@ __device__ __forceinline__ void report(int* status, int code) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------------
+// Every kernel of this library is launched with programmatic stream serialization allowed (tfb::launch_k): its CTAs may
+// be placed on SMs while the previous kernel of the stream is still draining.  `pdl_wait` blocks until that previous
+// kernel has completed and its memory is visible, so nothing before it may touch global memory a predecessor wrote;
+// `pdl_launch_dependents` lets the NEXT kernel of the stream start being placed.  Calling them in this order keeps the
+// look-ahead at one kernel: a kernel releases its successor only after its own predecessor is done.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
+// ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

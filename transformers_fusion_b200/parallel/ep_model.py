@@ -19,12 +19,15 @@ from torch import nn
 from .ep import ExpertParallel
 
 
-def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int, resident: bool = True) -> List[nn.Parameter]:
+def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int, resident: bool = True,
+                           capacity_factor: Optional[float] = None) -> List[nn.Parameter]:
     """Cuts every MoE block's expert tensors down to this rank's contiguous block of experts, attaches the dispatch /
     combine object, and rebuilds the flat parameter buffer.  Returns the expert parameters (the rest is replicated).
     ``resident`` (every layer owns its buffers and each forward is followed by its backward): dispatched rows and expert
     outputs stay in the symmetric buffers between forward and backward; pass False for schedules that run a layer's
-    forward twice before its backward (recomputation, interleaved micro-batches)."""
+    forward twice before its backward (recomputation, interleaved micro-batches).  ``capacity_factor`` sizes the
+    per-rank expert buffers as a multiple of the balanced load (max_tokens * top_k rows); the default provisions for
+    every token of every rank landing on one rank."""
     cfg = model.cfg
     E = cfg.num_experts
     if E % world:
@@ -36,7 +39,8 @@ def attach_expert_parallel(model, symm, rank: int, world: int, max_tokens: int, 
             continue
         blk.gate_up = nn.Parameter(blk.gate_up.data[rank * El:(rank + 1) * El].clone())
         blk.down = nn.Parameter(blk.down.data[rank * El:(rank + 1) * El].clone())
-        blk.ep = ExpertParallel(symm, rank, world, E, cfg.hidden_size, max_tokens, min(cfg.top_k, 8), resident=resident)
+        blk.ep = ExpertParallel(symm, rank, world, E, cfg.hidden_size, max_tokens, min(cfg.top_k, 8),
+                                capacity_factor=capacity_factor, resident=resident)
         experts += [blk.gate_up, blk.down]
     model.flat = None
     model.flatten()

@@ -92,7 +92,7 @@ class ShardedEngine:
 
     def __init__(self, cfg, mesh: Mesh, weight_of: Callable[[str], torch.Tensor], device, dtype=torch.bfloat16, comm="fused",
                  lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0, max_tokens=0, dp_heap=None,
-                 tp_heap=None, rs_ctas=48, copy_ctas=8, loss_chunk_tokens=4096):
+                 tp_heap=None, rs_ctas=96, copy_ctas=8, loss_chunk_tokens=4096):
         assert cfg.norm_type == "rmsnorm" and not cfg.use_parallel_residual and not cfg.attention_bias, \
             "the sharded engine covers the sequential RMSNorm block without biases"
         assert cfg.num_heads % mesh.tp == 0 and cfg.num_kv_heads % mesh.tp == 0 and cfg.ffn_hidden_size % mesh.tp == 0
