@@ -244,6 +244,9 @@ def main(argv=None):
     ap.add_argument("--model", default="llama-50m")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (stated in the config line)")
     ap.add_argument("--tp", type=int, default=2, help="llama3-8b-fsdp-tp2: tensor-parallel degree")
+    ap.add_argument("--gather", default="auto", choices=["auto", "prefetch", "fused"],
+                    help="llama3-8b-fsdp-tp2: ZeRO-3 weight gather by a prefetching kernel on a side stream, or inside the "
+                         "GEMM that first uses the weight")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="sequences per step over all ranks (the headline configuration is the default; other values are "
                          "for studying one rank's share of a larger job on a single GPU)")
@@ -581,7 +584,8 @@ def main_sharded(args):
             if st.tp > 1:
                 heaps[1] = SymmetricHeap(st.tp_rank, st.tp, dev, group=st.tp_group)
         e = ShardedEngine.from_config(cfg, mesh, dev, seed=0, comm=comm_, dp_heap=heaps[0], tp_heap=heaps[1], lr=3e-4,
-                                      betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0, max_tokens=T)
+                                      betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0, max_tokens=T,
+                                      gather=args.gather)
         return e, heaps
     engine, heaps = make_engine(comm)
     g = torch.Generator().manual_seed(1234 + st.dp_rank)      # the tp ranks of one dp group see the same batch

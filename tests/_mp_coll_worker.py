@@ -57,6 +57,67 @@ def main():
         res["sc_all_gather"] = float((ag.float().cpu() - torch.arange(1, world + 1).float().repeat_interleave(2048)).abs().max())
         bt = sc.broadcast(torch.full((777,), float(rank), device=dev), root=1)
         res["sc_broadcast"] = float((bt.cpu() - 1.0).abs().max())
+        # staged all-reduce with the residual added inside the kernel; eager, then replayed from a graph that was
+        # captured with an odd number of collectives, with eager collectives in between the replays
+        n = 4096
+        parts = [torch.randn(n, generator=torch.Generator().manual_seed(50 + r)).to(torch.bfloat16) for r in range(world)]
+        resid = torch.randn(n, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+        ref = (sum(v.float() for v in parts) + resid.float())
+        mine, rdev = parts[rank].to(dev), resid.to(dev)
+
+        def staged_once():
+            sc.stage_view(torch.bfloat16, n).copy_(mine)
+            return sc.all_reduce_staged(n, torch.bfloat16, residual=rdev)
+        res["sc_staged_residual"] = float((staged_once().float().cpu() - ref).abs().max() / 5e-2)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            staged_once()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        tok = sc.capture_begin()
+        with torch.cuda.graph(graph):
+            outs = [staged_once() for _ in range(3)]
+            sc.capture_end(tok)
+        worst = 0.0
+        for rep in range(4):
+            sc.before_replay(tok)
+            graph.replay()
+            worst = max(worst, max(float((o.float().cpu() - ref).abs().max()) for o in outs))
+            if rep % 2 == 0:       # an odd number of eager collectives between two replays
+                worst = max(worst, float((staged_once().float().cpu() - ref).abs().max()))
+        res["sc_staged_graph"] = worst / 5e-2
+        # flag-in-data all-reduce: every op and dtype eagerly, then (sum + residual, in place) replayed from a graph with
+        # eager calls in between; sizes from one 16-byte vector to the largest message
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 5e-2)):
+            for n_ll in (8, 4096, sc.one_shot_max_bytes // 4):
+                xs = [torch.randn(n_ll, generator=torch.Generator().manual_seed(11 * r + n_ll)).to(dtype) for r in range(world)]
+                st_ = torch.stack([v.float() for v in xs])
+                for op, want in (("sum", st_.sum(0)), ("avg", st_.mean(0)), ("max", st_.amax(0)), ("min", st_.amin(0))):
+                    for rep in range(2):
+                        y = sc.all_reduce_ll(xs[rank].to(dev), op)
+                        res[f"sc_ll_{op}_{dtype}_{n_ll}_{rep}"] = float((y.float().cpu() - want).abs().max() / tol)
+
+        def ll_once():
+            buf = mine.clone()
+            return sc.all_reduce_ll(buf, residual=rdev, out=buf)
+        res["sc_ll_residual"] = float((ll_once().float().cpu() - ref).abs().max() / 5e-2)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            ll_once()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2):
+            outs2 = [ll_once() for _ in range(3)]
+        worst = 0.0
+        for rep in range(4):
+            graph2.replay()
+            worst = max(worst, max(float((o.float().cpu() - ref).abs().max()) for o in outs2))
+            if rep % 2 == 0:
+                worst = max(worst, float((ll_once().float().cpu() - ref).abs().max()))
+        res["sc_ll_graph"] = worst / 5e-2
         torch.cuda.synchronize()
         res["status"] = int(_lib.status_word(dev)[0].item())
     json.dump(res, open(os.path.join(out_dir, f"rank{rank}.json"), "w"))

@@ -38,15 +38,16 @@ def main():
     ref = DenseModel(cfg, device=st.device, dtype=dt, seed=3)
     src = DenseModel(cfg, device=st.device, dtype=dt, seed=3)
     dp_heap = tp_heap = None
-    if comm == "fused":
+    if comm in ("fused", "fused_in_gemm"):
         from transformers_fusion_b200.parallel.symm import SymmetricHeap
         if st.dp > 1:
             dp_heap = SymmetricHeap(st.dp_rank, st.dp, st.device, group=st.dp_group)
         if st.tp > 1:
             tp_heap = SymmetricHeap(st.tp_rank, st.tp, st.device, group=st.tp_group)
     mesh = Mesh(st.dp_rank, st.dp, st.tp_rank, st.tp, st.dp_group, st.tp_group, None)
-    eng = ShardedEngine.from_dense(src, mesh, comm=comm if comm != "gloo" else "nccl", dp_heap=dp_heap, tp_heap=tp_heap,
-                                   loss_chunk_tokens=256, **kw)
+    gather = "fused" if comm == "fused_in_gemm" else "prefetch"
+    eng = ShardedEngine.from_dense(src, mesh, comm={"gloo": "nccl", "fused_in_gemm": "fused"}.get(comm, comm), dp_heap=dp_heap,
+                                   tp_heap=tp_heap, loss_chunk_tokens=256, gather=gather, **kw)
     ref_eng = TrainEngine(ref, zero_stage=0, comm="none", **kw)
     ref_eng.world, ref_eng.zero_stage = 1, 0
     per = B // st.dp

@@ -91,3 +91,28 @@ def test_tcp_backend_rejects_foreign_bytes():
     m = s.recv(X.MSG_TOKEN_DATA, 2.0)
     assert m is not None and m[1] == 1 and len(m[3]) == 200000 and s.recv(None, 0.1) is None
     s.close(), good.close()
+
+
+def test_pipeline_scheduler_chains_stages_and_micro_batches():
+    import torch
+    from transformers_fusion_b200.parallel.expert_cluster import PipelineScheduler
+    sch = PipelineScheduler(3, micro_batch_size=2)
+    calls = []
+
+    class Stage:
+        def __init__(self, k):
+            self.k = k
+
+        def forward_expert_parallel(self, x, experts):
+            calls.append((self.k, x.shape[0]))
+            return x + self.k
+    x = torch.zeros(5, 4)
+    assert sch.execute_pipeline([Stage(1), Stage(10), Stage(100)]) is None and sch.all_stages_done()
+    sch.schedule_forward(x, 0)
+    assert not sch.all_stages_done()
+    y = sch.execute_pipeline([Stage(1), Stage(10), Stage(100)])
+    assert torch.equal(y, x + 111) and sch.all_stages_done()
+    assert calls[:3] == [(1, 2), (10, 2), (100, 2)] and len(calls) == 9          # three micro-batches through three stages
+    assert torch.equal(sch.get_stage(2).output_buffer, torch.full((1, 4), 111.0))
+    sch.reset()
+    assert sch.get_stage(0).input_buffer is None and sch.current_step == 0

@@ -75,3 +75,40 @@ def test_budget_and_facades():
     while cb.has_pending():
         done += cb.step()
     assert sorted(r.id for r in done) == [100, 101, 102] and all(len(r.tokens) <= 4 for r in done)
+
+
+def test_q4_kv_cache_lloyd_max_codebooks():
+    """4-bit KV with a trained 16-entry codebook per block: round trip error, nibble order, ratio, range reads."""
+    import torch
+    from transformers_fusion_b200.inference.kv_extras import Q4KVCache
+    torch.manual_seed(0)
+    H, D, L = 4, 32, 2
+    c = Q4KVCache(L, 64, H, D, block_size=64)
+    k = torch.randn(1, H, 10, D)
+    v = torch.randn(1, H, 10, D) * 3 + 1
+    c.append(0, k, v)
+    c.append(0, k[:, :, :3], v[:, :, :3])
+    assert c.context_len() == 13
+    kk, vv = c.get_range(0, 0, 10)
+    assert kk.shape == (1, H, 10, D)
+    for a, b in ((kk, k), (vv, v)):
+        nmse = float(((a - b) ** 2).sum() / (b ** 2).sum())
+        assert nmse < 0.02, nmse                      # 16 trained levels per 64 values
+    # a uniform 16-level grid over the block range (the Lloyd-Max starting point) must be no better than the trained codebook
+    flat = k.permute(2, 1, 0, 3).reshape(-1, 64)
+    pk, cb = Q4KVCache.quantize_blocks(flat, iters=0)
+    pk2, cb2 = Q4KVCache.quantize_blocks(flat, iters=20)
+    e0 = float(((Q4KVCache.dequantize_blocks(pk, cb) - flat) ** 2).sum())
+    e1 = float(((Q4KVCache.dequantize_blocks(pk2, cb2) - flat) ** 2).sum())
+    assert e1 < e0
+    # nibble order: element 0 in the low nibble
+    one = torch.zeros(1, 64); one[0, 0] = 5.0
+    pk, cb = Q4KVCache.quantize_blocks(one)
+    assert float(cb.float()[0, int(pk[0, 0]) & 0xF]) > 4.0
+    assert abs(c.compression_ratio() - 4.0) < 1e-6      # 32 index + 32 codebook bytes per 64 fp32 values
+    k2, _ = c.get_range(0, 10, 13)
+    assert k2.shape == (1, H, 3, D) and float((k2 - k[:, :, :3]).abs().max()) < 1.0
+    c.resize(128)
+    assert c.max_seq_len() == 128 and c.get_all(0)[0].shape[2] == 13
+    c.clear()
+    assert c.context_len() == 0

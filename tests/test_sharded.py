@@ -38,7 +38,8 @@ def _gpus():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("nproc,tp,comm", [(2, 1, "fused"), (2, 2, "fused"), (4, 2, "fused"), (4, 2, "nccl")])
+@pytest.mark.parametrize("nproc,tp,comm", [(2, 1, "fused"), (2, 1, "fused_in_gemm"), (2, 2, "fused"), (4, 2, "fused"),
+                                           (4, 2, "fused_in_gemm"), (4, 2, "nccl")])
 def test_sharded_engine_matches_single_process_gpu(tmp_path, nproc, tp, comm):
     if _gpus() < nproc:
         pytest.skip(f"needs {nproc} GPUs")

@@ -308,6 +308,7 @@ def main(argv=None):
     ap.add_argument("--prompt-max", type=int, default=2048)
     ap.add_argument("--comm", action="store_true", help="fused compute+collective kernels against NCCL + plain kernels "
                                                         "(run under torch.distributed.run; see cli/bench_comm.py)")
+    ap.add_argument("--comm-ops", default="all", help="--comm: comma-separated subset of zero2, fsdp, all_reduce, tp_gemm")
     ap.add_argument("--link-gbs", type=float, default=770.0, help="--comm: NVLink bandwidth per direction per GPU, GB/s")
     ap.add_argument("--gemm-tflops", type=float, default=1382.0, help="--comm: sustained bf16 GEMM rate for the roofline")
     ap.add_argument("--zero-mb", type=int, default=256, help="--comm: flat fp32 gradient buffer of the ZeRO-2 step, MiB")
@@ -315,7 +316,7 @@ def main(argv=None):
     ap.add_argument("--tokens", type=int, default=8192, help="--comm: rows of the tensor-parallel products")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
-    ap.add_argument("--copy-ctas", type=int, default=8)
+    ap.add_argument("--copy-ctas", type=int, default=12)
     a = ap.parse_args(argv)
     if a.comm:
         from .bench_comm import comm_bench

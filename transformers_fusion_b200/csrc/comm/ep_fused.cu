@@ -20,6 +20,8 @@
 #include "tfb_comm.cuh"
 #include "tfb_host.h"
 
+TFB_BOUNDS_DEFINE(ep_fused)
+
 namespace tfb {
 
 constexpr int EP_MAX_E = 256;
@@ -87,7 +89,8 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const in
   int row = 0;
   if (lane == 0) {
     row = base[e] + atomicAdd(cursor + e, 1);
-    if (row >= max_rows) row = -1;  // beyond the buffer: dropped (cannot happen with worst-case sizing)
+    TFB_BOUNDS(row >= 0 && row < max_rows, 41, row, max_rows);
+    if (row >= max_rows || row < 0) row = -1;  // beyond the buffer: dropped (cannot happen with worst-case sizing)
     row_of[w] = row;
   }
   row = __shfl_sync(0xffffffffu, row, 0);

@@ -9,6 +9,9 @@
 //       weight of the unit: 128-bit peer loads of the W copies of this rank's row shard, sum, 1/W, store into the
 //       rank's flat fp32 shard-gradient buffer, and the squared norm of what was stored added to a device accumulator
 //       (the global gradient norm needs no separate pass).  The last CTA signals "done reading".
+//   fsdp_all_gather : one launch per unit on a side stream, one unit ahead of the compute (prefetch): every weight of
+//       the unit is assembled in the local gather buffer from the W row shards with 128-bit peer loads.  No flags: the
+//       shards only change in the optimizer step, which ends with a barrier over the group.
 //   embedding_fwd_sharded : token-embedding lookup straight from the row shards of the table: the owner of a row is
 //       id / per, so each token's row is fetched from whichever rank holds it (the all-gather of the table shrinks to
 //       the rows the batch actually uses).  Ids outside [vocab_lo, vocab_lo + vocab_n) give zero rows (vocabulary-
@@ -52,13 +55,13 @@ __device__ __forceinline__ float4 fs_ld_peer(const float* p) {
 
 // MAXW: compile-time bound on the group size (the peer loops unroll over it); UNROLL: 16-byte vectors each thread
 // keeps in flight per peer.  The kernel shares the GPU with the backward pass, so its CTAs must fit beside a resident GEMM
-// CTA (192 threads x 168 registers, ~200 KB of shared memory): 256 threads x <= 128 registers and no dynamic shared
-// memory leave room for both on one SM, where a 512-thread CTA of this kernel would claim the whole register file and
-// could only start once a GEMM CTA had left, stalling the persistent GEMM that follows.  A bounded grid needs deep
-// per-thread queues to cover NVLink latency: 96 CTAs x 256 threads x UNROLL x (W - 1) x 16 B in flight.
-constexpr int FS_THREADS = 256;
+// CTA (320 threads x 168 registers = 53,760 of the SM's 65,536 registers, ~225 KB of shared memory): 128 threads x <= 80
+// registers and a few bytes of static shared memory fit into what is left, where a larger CTA of this kernel could only
+// start once a GEMM CTA had left and would then hold up the persistent GEMM that follows.  One such CTA per SM, so the
+// per-thread queues must be deep enough to cover NVLink latency: 148 CTAs x 128 threads x UNROLL x (W - 1) x 16 B in flight.
+constexpr int FS_THREADS = 128;
 template <int MAXW, int UNROLL>
-__global__ void __launch_bounds__(FS_THREADS) fsdp_reduce_scatter_kernel(FsdpRsArgs a) {
+__global__ void __launch_bounds__(FS_THREADS, 6) fsdp_reduce_scatter_kernel(FsdpRsArgs a) {
   tfb::pdl_sync();
   __shared__ int sh_ok;
   __shared__ float sh_red[32];
@@ -126,6 +129,47 @@ __global__ void __launch_bounds__(FS_THREADS) fsdp_reduce_scatter_kernel(FsdpRsA
   }
 }
 
+struct FsdpAgSeg {
+  const uint4* const* src;   // device array [world]: every rank's shard of this weight
+  uint4* dst;                // local gathered matrix: shard r goes to dst + r * shard_vecs
+  long long shard_vecs;      // 16-byte vectors per shard
+};
+struct FsdpAgArgs {
+  int rank, world, nseg;
+  FsdpAgSeg seg[FS_MAX_SEGS];
+};
+
+// Like the reduce-scatter above, sized to sit beside a resident GEMM CTA: 128 threads, <= 80 registers, no shared memory.
+constexpr int AG_UNROLL = 8;
+__global__ void __launch_bounds__(FS_THREADS, 6) fsdp_all_gather_kernel(FsdpAgArgs a) {
+  tfb::pdl_sync();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long t0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (int s = 0; s < a.nseg; ++s) {
+    const FsdpAgSeg sg = a.seg[s];
+    for (int rr = 0; rr < a.world; ++rr) {
+      const int r = (a.rank + rr) % a.world;      // own shard first, then the peers starting at the next rank
+      const uint4* src = sg.src[r];
+      uint4* dst = sg.dst + (long long)r * sg.shard_vecs;
+      for (long long i0 = t0; i0 < sg.shard_vecs; i0 += stride * AG_UNROLL) {
+        uint4 v[AG_UNROLL];
+#pragma unroll
+        for (int u = 0; u < AG_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < sg.shard_vecs)
+            asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i) : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < AG_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < sg.shard_vecs) dst[i] = v[u];
+        }
+      }
+    }
+  }
+}
+
 __global__ void embedding_fwd_sharded_kernel(const long long* __restrict__ ids, const __nv_bfloat16* const* __restrict__ shard_ptrs,
                                              __nv_bfloat16* __restrict__ out, int T, int H, long long per_rows, int world,
                                              long long vocab_lo, long long vocab_n) {
@@ -178,10 +222,36 @@ TFB_API int tfb_fsdp_reduce_scatter(const TfbFsdpRsDesc* d, int max_ctas, void* 
   int grid = sm_count() * 4;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d->world <= 2) tfb::launch_k(fsdp_reduce_scatter_kernel<2, 6>, grid, FS_THREADS, 0, st, a);
-  else if (d->world <= 4) tfb::launch_k(fsdp_reduce_scatter_kernel<4, 3>, grid, FS_THREADS, 0, st, a);
-  else if (d->world <= 8) tfb::launch_k(fsdp_reduce_scatter_kernel<8, 2>, grid, FS_THREADS, 0, st, a);
+  if (d->world <= 2) tfb::launch_k(fsdp_reduce_scatter_kernel<2, 5>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 4) tfb::launch_k(fsdp_reduce_scatter_kernel<4, 2>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 8) tfb::launch_k(fsdp_reduce_scatter_kernel<8, 1>, grid, FS_THREADS, 0, st, a);
   else tfb::launch_k(fsdp_reduce_scatter_kernel<FS_MAX_WORLD, 1>, grid, FS_THREADS, 0, st, a);
+  return int(cudaGetLastError());
+}
+
+struct TfbFsdpAgSeg { const void* src_ptrs; void* dst; long long shard_bytes; };
+struct TfbFsdpAgDesc {
+  int rank, world, nseg, pad;
+  TfbFsdpAgSeg seg[FS_MAX_SEGS];
+};
+
+// All-gather of one unit's weights from the row shards of the W ranks into this rank's gather buffer (see the top of the
+// file).  Every segment: src_ptrs = device array [world] of shard addresses, dst = local [world * shard_bytes] matrix,
+// shard_bytes a multiple of 16.  `max_ctas` bounds the grid (0: four CTAs per SM; beside a resident GEMM CTA one fits
+// per SM and the others follow as slots free up).
+TFB_API int tfb_fsdp_all_gather(const TfbFsdpAgDesc* d, int max_ctas, void* stream) {
+  if (!d || d->world < 1 || d->world > FS_MAX_WORLD || d->nseg < 1 || d->nseg > FS_MAX_SEGS || d->rank < 0 || d->rank >= d->world)
+    return TFB_ERR_ARG;
+  FsdpAgArgs a;
+  a.rank = d->rank; a.world = d->world; a.nseg = d->nseg;
+  for (int s = 0; s < d->nseg; ++s) {
+    const TfbFsdpAgSeg& g = d->seg[s];
+    if (!g.src_ptrs || !g.dst || g.shard_bytes <= 0 || g.shard_bytes % 16 || (reinterpret_cast<uintptr_t>(g.dst) & 15)) return TFB_ERR_ARG;
+    a.seg[s] = FsdpAgSeg{static_cast<const uint4* const*>(g.src_ptrs), static_cast<uint4*>(g.dst), g.shard_bytes / 16};
+  }
+  int grid = sm_count() * 4;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  tfb::launch_k(fsdp_all_gather_kernel, grid, FS_THREADS, 0, static_cast<cudaStream_t>(stream), a);
   return int(cudaGetLastError());
 }
 

@@ -57,6 +57,33 @@ __device__ __forceinline__ bool comm_wait_all(const CommCtx& c, int e) {
   return true;
 }
 
+// block-level, one thread per peer (blockDim.x >= world): the W release stores, and the W polls, run side by side
+// instead of one after the other
+__device__ __forceinline__ void comm_signal_all_par(const CommCtx& c, int e) {
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + c.rank, e);
+  }
+}
+__device__ __forceinline__ bool comm_wait_all_block_par(const CommCtx& c, int e, int* sh_ok) {
+  if (threadIdx.x == 0) *sh_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const int* mine = c.flags[c.rank] + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (ld_acquire_sys(mine) < e) {
+      if ((++it & 255u) == 0u && globaltimer_ns() - t0 > TFB_WAIT_NS) {
+        report(c.status, ST_TIMEOUT_FLAG);
+        *sh_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *sh_ok != 0;
+}
+
 // block-level: thread 0 waits, the result is broadcast to the block
 __device__ __forceinline__ bool comm_wait_all_block(const CommCtx& c, int e, int* sh_ok) {
   if (threadIdx.x == 0) *sh_ok = comm_wait_all(c, e) ? 1 : 0;

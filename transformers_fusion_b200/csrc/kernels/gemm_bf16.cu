@@ -1,10 +1,11 @@
 // bf16 GEMM for sm_100a: C[M,N] = epilogue(A * B), fp32 accumulation in tensor memory.
 //
-// Design (one persistent CTA per SM, 192 threads, warp-specialised):
+// Design (one persistent CTA per SM, 320 threads, warp-specialised):
 //   warp 0      TMA producer  : cp.async.bulk.tensor tiles of A and B into a 4-stage shared-memory ring
 //   warp 1      MMA issuer    : one thread issues tcgen05.mma (128 x BN x 16) per 32 bytes of K and
 //                               commits stage-release / accumulator-ready mbarriers
-//   warps 2..5  epilogue      : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread),
+//   warps 2..9  epilogue      : tcgen05.ld the 128 x BN fp32 accumulator (one row per thread, two warps per TMEM lane
+//                               quadrant, each taking half of the columns),
 //                               apply alpha / bias / activation / residual, stage 32-row x 128-byte slabs in
 //                               shared memory (128-byte swizzle, conflict-free) and hand them to TMA: a tiled
 //                               store for bf16 / fp32 outputs, a tiled fp32 reduce-add for accumulating outputs
@@ -30,7 +31,8 @@ namespace tfb {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int STAGES = 4;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;   // two warps per TMEM lane quadrant, each draining half of the tile's columns
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 
 enum : int { TP_AG = 1, TP_RS = 2, TP_WG = 4 };
 
@@ -140,21 +142,24 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 
 // Copy role of the gather -> GEMM fusions: pulls 128-row blocks of the ranks' shards into the local gathered buffer
 // and publishes each block with a release store.  Contiguous blocks (row pitch == row length) travel as untiled bulk
-// copies through a shared-memory ring driven by one thread (16 KB chunks, four loads in flight per CTA, so a handful
-// of CTAs keeps enough bytes in flight to fill NVLink); strided rows fall back to per-thread 16-byte copies.
+// copies through a shared-memory ring driven by one thread: 16 KB chunks in the CTA's operand-stage memory (8 slots for
+// the 128-wide tile configuration, 12 for the 256-wide one), all but two slots' worth of loads in flight, so that about
+// a dozen CTAs keep more than a megabyte in flight, which is what a ~2 us NVLink round trip needs to run near link
+// bandwidth.  Strided rows fall back to per-thread 16-byte copies.
 constexpr int COPY_CHUNK = 16384;
-constexpr int COPY_SLOTS = 8;
+constexpr int COPY_MAX_SLOTS = 12;
 
 __device__ __forceinline__ bool copy_block_bulk(const __nv_bfloat16* src, __nv_bfloat16* dst, long long bytes, uint32_t ring,
-                                                uint32_t bars, uint32_t& seq, volatile int* abort_flag, int* status) {
+                                                uint32_t bars, uint32_t& seq, volatile int* abort_flag, int* status,
+                                                const uint32_t COPY_SLOTS) {
   const int nt = int((bytes + COPY_CHUNK - 1) / COPY_CHUNK);
   const char* s8 = reinterpret_cast<const char*>(src);
   char* d8 = reinterpret_cast<char*>(dst);
   int nl = 0, ns = 0;
   const uint32_t seq0 = seq;
   while (ns < nt) {
-    while (nl < nt && nl - ns < 4) {
-      tma_store_wait_read<3>();   // the store that last used this ring slot (eight chunks ago) has read it
+    while (nl < nt && nl - ns < int(COPY_SLOTS) - 2) {
+      tma_store_wait_read<2>();   // at most two stores still reading: the one that last used this slot is not among them
       const uint32_t q = seq0 + nl, slot = q % COPY_SLOTS;
       const uint32_t sz = uint32_t(min((long long)COPY_CHUNK, bytes - (long long)nl * COPY_CHUNK));
       mbar_expect_tx(bars + slot * 8, sz);
@@ -211,15 +216,15 @@ __device__ __forceinline__ void copy_block_threads(const __nv_bfloat16* src, __n
 }
 
 __device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int ncopy, uint32_t ring, uint32_t bars,
-                                             volatile int* abort_flag) {
+                                             volatile int* abort_flag, const uint32_t slots) {
   if (threadIdx.x == 0) {
-    for (int i = 0; i < COPY_SLOTS; ++i) mbar_init(bars + i * 8, 1);
+    for (uint32_t i = 0; i < slots; ++i) mbar_init(bars + i * 8, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
   __syncthreads();
   const int nA = (p.tp_mode & TP_AG) ? (p.ag.world - 1) * (p.ag.rows_per_shard / BM) : 0;
-  const int nB = (p.tp_mode & TP_WG) ? p.wg.world * (p.wg.rows_per_shard / BM) : 0;
+  const int nB = (p.tp_mode & TP_WG) ? (p.wg.world - (p.wg.skip_local ? 1 : 0)) * (p.wg.rows_per_shard / BM) : 0;
   uint32_t seq = 0;
   for (int idx = cta; idx < nA + nB; idx += ncopy) {
     const GatherSpec& g = idx < nA ? p.ag : p.wg;
@@ -234,7 +239,7 @@ __device__ __forceinline__ void tp_copy_role(const GemmParams& p, int cta, int n
     if (g.ld == g.row_len) {
       // after a copy that ran out of time nothing more is published: the consumers' own bounded waits end the kernel
       if (threadIdx.x == 0 && !*abort_flag &&
-          copy_block_bulk(src, dst, (long long)BM * g.row_len * 2, ring, bars, seq, abort_flag, p.status)) {
+          copy_block_bulk(src, dst, (long long)BM * g.row_len * 2, ring, bars, seq, abort_flag, p.status, slots)) {
         __threadfence();
         asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(g.ready + blk), "r"(g.epoch) : "memory");
       }
@@ -254,8 +259,11 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STG_OFF = STAGES * STAGE_BYTES;   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B)
-  static constexpr int STG_BYTES = 4 * 2 * 4096;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES;   // epilogue staging slabs follow the operand stages
+  // epilogue staging: one 32-row x 128-byte slab per epilogue warp, double-buffered where shared memory allows (the
+  // 256-wide tile leaves room for one slab per warp next to its four operand stages)
+  static constexpr int STG_BUFS = (BN == 256) ? 1 : 2;
+  static constexpr int STG_BYTES = EPI_WARPS * STG_BUFS * 4096;
   static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // + barriers + alignment slack
 };
@@ -296,7 +304,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int cta = int(blockIdx.x) - ncopy;
   if (cta < 0) {
     tfb::pdl_sync();
-    tp_copy_role(p, int(blockIdx.x), ncopy, smem_base, bar_full, abort_flag);
+    constexpr uint32_t kSlots = (STAGES * L::STAGE_BYTES / COPY_CHUNK) < COPY_MAX_SLOTS ? (STAGES * L::STAGE_BYTES / COPY_CHUNK)
+                                                                                          : COPY_MAX_SLOTS;
+    tp_copy_role(p, int(blockIdx.x), ncopy, smem_base, bar_full, abort_flag, kSlots);
     return;
   }
 
@@ -307,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + b * 8, 1);
-      mbar_init(bar_tempty + b * 8, 128);
+      mbar_init(bar_tempty + b * 8, 32 * EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -455,7 +465,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const bool vec_ok_f32 = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const bool vec_ok_res =
         p.residual && ((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
-    const uint32_t stg_u32 = smem_base + L::STG_OFF + (warp - 2) * 8192;
+    const int ew = warp - 2;           // epilogue warp 0..7
+    const int half = ew >> 2;          // which half of the tile's columns this warp drains
+    const uint32_t stg_u32 = smem_base + L::STG_OFF + ew * (L::STG_BUFS * 4096);
     int sbuf = 0;
     for (int w = cta; w < num_work; w += nctas) {
       WorkItem it;
@@ -473,7 +485,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const uint32_t xr = uint32_t(lane & 7);
         if (p.out_mode == 0) {
 #pragma unroll 1
-          for (int c = 0; c < BN / 64; ++c) {
+          for (int c = half * (BN / 128); c < (half + 1) * (BN / 128); ++c) {
             const int col0 = n0 + c * 64;
             if (col0 >= p.N) break;
             uint32_t r0[32], r1[32];
@@ -516,7 +528,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 }
               }
             }
-            if (lane == 0) tma_store_wait_read<1>();   // the slab written two chunks ago has been read by its copy
+            if (lane == 0) tma_store_wait_read<L::STG_BUFS - 1>();   // the slab about to be rewritten has been read by its copy
             __syncwarp();
             const uint32_t slab = stg_u32 + sbuf * 4096 + lane * 128;
 #pragma unroll
@@ -538,19 +550,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               }
               tma_store_commit();
             }
-            sbuf ^= 1;
+            sbuf ^= (L::STG_BUFS - 1);
           }
         } else {
           const int cz = p.group_mode == 2 ? it.expert : 0;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
             const int col0 = n0 + c * 32;
             if (col0 >= p.N) break;
             uint32_t r[32];
             tmem_ld_32x32(taddr0 + c * 32, r);
             tmem_ld_wait();
             if (!slab_live) continue;
-            if (lane == 0) tma_store_wait_read<1>();
+            if (lane == 0) tma_store_wait_read<L::STG_BUFS - 1>();
             __syncwarp();
             const uint32_t slab = stg_u32 + sbuf * 4096 + lane * 128;
 #pragma unroll
@@ -566,7 +578,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               else tma_store_3d(&tma_c, stg_u32 + sbuf * 4096, col0, slab_row0, cz);
               tma_store_commit();
             }
-            sbuf ^= 1;
+            sbuf ^= (L::STG_BUFS - 1);
           }
         }
         tc_fence_before();
@@ -576,7 +588,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr0 + c * 32, r);
         tmem_ld_wait();
@@ -725,6 +737,7 @@ struct TfbGemmTp {
   int wg_rank, wg_world, wg_epoch, wg_rows;   // wg_rows: padded row count, a multiple of 128 * wg_world
   int* wg_ready;          // local int[wg_rows / 128]
   const void* wg_src;     // device array [wg_world] of shard base pointers
+  int wg_skip_local;      // 1: the caller has already copied this rank's shard into B (the copy CTAs then move remote rows only)
 };
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -925,7 +938,7 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
           !tp->wg_ready || !tp->wg_src)
         return TFB_ERR_ARG;
       p.wg.rank = tp->wg_rank; p.wg.world = tp->wg_world; p.wg.rows_per_shard = tp->wg_rows / tp->wg_world;
-      p.wg.row_len = row_len; p.wg.epoch = tp->wg_epoch; p.wg.rows = rows; p.wg.src_is_full = 0; p.wg.skip_local = 0;
+      p.wg.row_len = row_len; p.wg.epoch = tp->wg_epoch; p.wg.rows = rows; p.wg.src_is_full = 0; p.wg.skip_local = tp->wg_skip_local ? 1 : 0;
       p.wg.ready = tp->wg_ready;
       p.wg.src = static_cast<const __nv_bfloat16* const*>(tp->wg_src);
       p.wg.dst = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(B));

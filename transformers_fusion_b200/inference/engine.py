@@ -138,8 +138,11 @@ class _DecodeGraph:
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         self._last_n = -1
+        self.eng = eng
+        self.token = eng._graph_capture_begin()
         with torch.cuda.graph(self.graph):
             self.logits = run()
+            eng._graph_capture_end(self.token)
 
     def replay(self, tokens, positions, bt, slots):
         n = tokens.shape[0]
@@ -151,6 +154,7 @@ class _DecodeGraph:
             self.positions[n:].zero_()
             self.slots[n:].fill_(-1)
         self._last_n = n
+        self.eng._graph_before_replay(self.token)
         self.graph.replay()
         return self.logits[:n]
 
@@ -177,6 +181,17 @@ class InferenceEngine:
             from ..quant import wq
             self._wq = wq
             self.packed = wq.quantize_model_linears(model, cfg.weight_format, cfg.weight_group, min_numel=0)
+
+    # hooks around decode-graph capture and replay (the tensor-parallel engine keeps its collectives' host-side state
+    # consistent with what a graph has baked in)
+    def _graph_capture_begin(self):
+        return None
+
+    def _graph_capture_end(self, token):
+        pass
+
+    def _graph_before_replay(self, token):
+        pass
 
     def _lin(self, x, li, name, w, bias=None, residual=None):
         """x @ W^T (+ bias) (+ residual) with W either the bf16 parameter or its packed low-bit form."""

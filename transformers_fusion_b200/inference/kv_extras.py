@@ -317,3 +317,124 @@ class ContinuousBatching:
             text = self.tok.decode([t for t in r.out if t != getattr(self.tok, "eos_id", -1)]) if self.tok else ""
             out.append(BatchResponse(text, self.ids.pop(r.id, r.id), list(r.out)))
         return out
+
+
+class Q4KVCache:
+    """Per-layer key / value store quantised to 4 bits with a 16-entry fp16 codebook per block, trained for every block
+    by Lloyd-Max (uniform start over the block's range, at most 20 assign / centroid rounds).  Blocks of ``block_size``
+    (32 / 64 / 128) elements run over the flattened [token][head][dim] stream of one token chunk; indices are packed two
+    per byte, low nibble first.  ``get_range`` returns fp32 [1, heads, length, dim].  The paged engine's own 4-bit mode
+    (scale per 32 elements, ``PagedKVCache(kv_mode="q4")``) is the device form; this class keeps the reference's
+    codebook form and its API.
+
+    Reference counterpart: Q4KVCache (include/quant/kv_cache_quant4.h, src/model/kv_cache_quant4.cpp:77-152 training,
+    :181-199 nibble order, :207-291 append, :293-362 get_range, :388 compression_ratio)."""
+    Q4_CODEBOOK_SIZE = 16
+
+    def __init__(self, num_layers: int, max_seq_len: int, num_heads: int, head_dim: int, block_size: int = 64, device="cpu"):
+        assert block_size in (32, 64, 128)
+        self.num_layers, self._max_seq_len, self.num_heads, self.head_dim, self._block = num_layers, max_seq_len, num_heads, head_dim, block_size
+        self.device = torch.device(device)
+        per_tok = num_heads * head_dim
+        assert per_tok % block_size == 0, "heads x dim must be a whole number of blocks"
+        self.blocks_per_token = per_tok // block_size
+        nb = max_seq_len * self.blocks_per_token
+        mk_i = lambda: torch.zeros((nb, block_size // 2), dtype=torch.uint8, device=self.device)
+        mk_c = lambda: torch.zeros((nb, 16), dtype=torch.float16, device=self.device)
+        self.k_idx, self.v_idx = [mk_i() for _ in range(num_layers)], [mk_i() for _ in range(num_layers)]
+        self.k_cb, self.v_cb = [mk_c() for _ in range(num_layers)], [mk_c() for _ in range(num_layers)]
+        self.pos = [0] * num_layers
+
+    # ---- block codec (batched over blocks)
+    @staticmethod
+    def quantize_blocks(x: torch.Tensor, iters: int = 20):
+        """x [nb, n] fp32 -> (packed indices uint8 [nb, n / 2], codebook fp16 [nb, 16])."""
+        x = x.float()
+        lo, hi = x.min(-1, keepdim=True).values, x.max(-1, keepdim=True).values
+        span = (hi - lo).clamp(min=1e-12)
+        cb = lo + span * (torch.arange(16, device=x.device, dtype=torch.float32)[None, :] + 0.5) / 16.0
+        for _ in range(iters):
+            idx = (x[:, :, None] - cb[:, None, :]).abs().argmin(-1)                      # [nb, n]
+            onehot = torch.nn.functional.one_hot(idx, 16).float()
+            cnt = onehot.sum(1)
+            new = (onehot * x[:, :, None]).sum(1) / cnt.clamp(min=1)
+            new = torch.where(cnt > 0, new, cb)                                         # empty cells keep their centre
+            if torch.allclose(new, cb, atol=0, rtol=1e-6):
+                cb = new
+                break
+            cb = new
+        cb16 = cb.to(torch.float16)
+        idx = (x[:, :, None] - cb16.float()[:, None, :]).abs().argmin(-1).to(torch.uint8)
+        packed = idx[:, 0::2] | (idx[:, 1::2] << 4)
+        return packed, cb16
+
+    @staticmethod
+    def dequantize_blocks(packed: torch.Tensor, cb16: torch.Tensor):
+        idx = torch.stack([packed & 0xF, packed >> 4], -1).reshape(packed.shape[0], -1).long()
+        return cb16.float().gather(1, idx)
+
+    quantize_block_quant4 = quantize_blocks
+    dequantize_block_quant4 = dequantize_blocks
+
+    # ---- cache API
+    def append(self, layer: int, k: torch.Tensor, v: torch.Tensor):
+        """k, v: [1, heads, t, dim] (or [heads, t, dim]) for t new tokens of ``layer``."""
+        k = k.reshape(self.num_heads, -1, self.head_dim)
+        v = v.reshape(self.num_heads, -1, self.head_dim)
+        t = k.shape[1]
+        p0 = self.pos[layer]
+        if p0 + t > self._max_seq_len:
+            raise ValueError("Q4KVCache is full")
+        for src, idx, cb in ((k, self.k_idx[layer], self.k_cb[layer]), (v, self.v_idx[layer], self.v_cb[layer])):
+            flat = src.permute(1, 0, 2).reshape(t * self.blocks_per_token, self._block).to(self.device)   # [token][head][dim]
+            pk, c16 = self.quantize_blocks(flat)
+            b0 = p0 * self.blocks_per_token
+            idx[b0:b0 + pk.shape[0]] = pk
+            cb[b0:b0 + pk.shape[0]] = c16
+        self.pos[layer] = p0 + t
+
+    def get_range(self, layer: int, start: int, end: int):
+        end = min(end, self.pos[layer])
+        n = max(0, end - start)
+        out = []
+        for idx, cb in ((self.k_idx[layer], self.k_cb[layer]), (self.v_idx[layer], self.v_cb[layer])):
+            b0, b1 = start * self.blocks_per_token, end * self.blocks_per_token
+            x = self.dequantize_blocks(idx[b0:b1], cb[b0:b1]).reshape(n, self.num_heads, self.head_dim)
+            out.append(x.permute(1, 0, 2).unsqueeze(0).contiguous())
+        return out[0], out[1]
+
+    def get_all(self, layer: int):
+        return self.get_range(layer, 0, self.pos[layer])
+
+    def context_len(self) -> int:
+        return self.pos[0] if self.pos else 0
+
+    def max_seq_len(self):
+        return self._max_seq_len
+
+    def block_size(self):
+        return self._block
+
+    def size_bytes(self) -> int:
+        used = sum(self.pos) * self.blocks_per_token
+        return 2 * used * (self._block // 2 + 32)
+
+    def size_bytes_fp32_equivalent(self) -> int:
+        return 2 * sum(self.pos) * self.num_heads * self.head_dim * 4
+
+    def compression_ratio(self) -> float:
+        return self.size_bytes_fp32_equivalent() / max(1, self.size_bytes())
+
+    def clear(self):
+        self.pos = [0] * self.num_layers
+
+    def resize(self, new_max_seq_len: int):
+        keep = min(new_max_seq_len, self._max_seq_len) * self.blocks_per_token
+        for lst, width, dt in ((self.k_idx, self._block // 2, torch.uint8), (self.v_idx, self._block // 2, torch.uint8),
+                               (self.k_cb, 16, torch.float16), (self.v_cb, 16, torch.float16)):
+            for i, t in enumerate(lst):
+                n = torch.zeros((new_max_seq_len * self.blocks_per_token, width), dtype=dt, device=self.device)
+                n[:keep] = t[:keep]
+                lst[i] = n
+        self._max_seq_len = new_max_seq_len
+        self.pos = [min(p, new_max_seq_len) for p in self.pos]

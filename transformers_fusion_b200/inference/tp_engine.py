@@ -64,7 +64,8 @@ class TPInferenceEngine(InferenceEngine):
                  symm=None, group=None):
         cfg = cfg or EngineConfig()
         # Decode graphs are safe across ranks: every rank captures and replays the same sequence of kernels, and the
-        # all-reduce kernels keep their epoch and ticket in device memory (nothing host-side is baked into the graph).
+        # all-reduce kernels keep their epoch and ticket in device memory.  The one piece of host-side state a graph bakes
+        # in - which of the two staging buffers each collective uses - is kept consistent by the capture / replay hooks.
         self.tp_rank, self.tp_world, self.tp_group = rank, world, group
         local = shard_dense_for_tp(model, rank, world) if world > 1 else model
         super().__init__(local, tokenizer, cfg)
@@ -81,17 +82,48 @@ class TPInferenceEngine(InferenceEngine):
         dist.all_reduce(y, group=self.tp_group)
         return y
 
+    def _graph_capture_begin(self):
+        return self.coll.capture_begin() if self.coll is not None else None
+
+    def _graph_capture_end(self, token):
+        if self.coll is not None:
+            self.coll.capture_end(token)
+
+    def _graph_before_replay(self, token):
+        if self.coll is not None:
+            self.coll.before_replay(token)
+
     def _lin(self, x, li, name, w, bias=None, residual=None):
         if self.tp_world == 1 or name not in ("o", "down"):
             return super()._lin(x, li, name, w, bias, residual)
         M, N = x.shape[0], w.shape[0]
-        st = self.coll.stage_view(x.dtype, M * N) if (self.coll is not None and not self.packed and x.is_cuda) else None
-        if st is not None:
-            # the partial product lands in the staging buffer of the all-reduce and the reduced rows are used where the
-            # kernel leaves them: no copy in, no copy out
-            F.gemm(x, w.data, out=st.view(M, N))
+        if self.coll is not None and x.is_cuda and M * N * x.element_size() <= self.coll.one_shot_max_bytes \
+                and (M * N * x.element_size()) % 16 == 0:
+            # decode-sized: this rank's partial product stays in local memory; the flag-in-data all-reduce pushes it to
+            # the peers, sums what arrives and adds the residual stream in the same kernel
+            y = super()._lin(x, li, name, w, None, None)
             self.allreduce_calls += 1
-            y = self.coll.all_reduce_staged(M * N, x.dtype).view(M, N)
+            fuse = bias is None and residual is not None and residual.is_contiguous() and residual.data_ptr() % 16 == 0
+            y = self.coll.all_reduce_ll(y.contiguous(), residual=residual if fuse else None, out=y if y.is_contiguous() else None)
+            if fuse:
+                return y
+            if bias is not None:
+                y = y + bias
+            return y if residual is None else y + residual
+        st = self.coll.stage_view(x.dtype, M * N) if (self.coll is not None and x.is_cuda) else None
+        if st is not None:
+            # the partial product lands in the staging buffer of the all-reduce, the residual stream is added inside the
+            # reduction and the reduced rows are used where the kernel leaves them: no copy in, no copy out, no add
+            pw = self.packed.get(f"layers.{li}.{name}")
+            if pw is None:
+                F.gemm(x, w.data, out=st.view(M, N))
+            else:
+                self._wq.gemm_wq(x, pw, None, out=st.view(M, N))
+            self.allreduce_calls += 1
+            fuse = bias is None and residual is not None
+            y = self.coll.all_reduce_staged(M * N, x.dtype, residual=residual if fuse else None).view(M, N)
+            if fuse:
+                return y
         else:
             y = self._all_reduce(super()._lin(x, li, name, w, None, None))   # this rank's partial sum, then the sum
         if bias is not None:

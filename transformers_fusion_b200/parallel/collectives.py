@@ -98,27 +98,75 @@ class DistributedContext:
 
 
 class SymmCollectives:
-    """Fused collectives on one staging buffer in symmetric memory (``capacity`` bytes per rank)."""
+    """Fused collectives on staging buffers in symmetric memory (``capacity`` bytes per rank each).
+
+    There are two staging buffers and consecutive collectives alternate between them.  That lets the one-shot all-reduce
+    run without its closing barrier: a rank leaves the opening barrier of collective n+1 only after every peer has
+    finished collective n, so by the time a buffer is refilled (collective n+2) nobody reads it.  The alternation is
+    host-side state, so a sequence that is replayed (a CUDA graph) must hold an even number of collectives and start on
+    the buffer it was captured on: capture_begin / capture_end / before_replay take care of both."""
 
     def __init__(self, symm, capacity_bytes: int = 8 << 20):
         from ..ops import _lib
         self._lib = _lib
         _lib.register("tfb_collective", [_lib.c_p, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_p, _lib.c_p,
-                                         _lib.c_i, _lib.c_i, _lib.c_p, _lib.c_p, _lib.c_i, _lib.c_p])
+                                         _lib.c_i, _lib.c_i, _lib.c_p, _lib.c_p, _lib.c_i, _lib.c_p, _lib.c_i, _lib.c_p])
         self.symm, self.rank, self.world = symm, symm.rank, symm.world
         gran = 16 * self.world
         self.capacity = (capacity_bytes + gran - 1) // gran * gran
-        self.stage = symm.alloc_bytes(self.capacity)
+        self._stages = [symm.alloc_bytes(self.capacity), symm.alloc_bytes(self.capacity)]
+        self._half = 0
+        self.count = 0                  # collectives launched (or captured) so far
         self.ticket = torch.zeros(1, dtype=torch.int32, device=symm.device)
         symm.on_reset(self.ticket.zero_)
         self.one_shot_max_bytes = 256 << 10
+        # flag-in-data all-reduce: receive area [2 parities][world senders][one_shot_max_bytes of data as 8-byte pairs]
+        _lib.register("tfb_allreduce_ll", [_lib.c_p, _lib.c_p, _lib.c_p, _lib.c_p, _lib.c_ll, _lib.c_ll, _lib.c_i, _lib.c_i, _lib.c_i,
+                                           _lib.c_i, _lib.c_p, _lib.c_p, _lib.c_p, _lib.c_i, _lib.c_p])
+        self._ll_recv = symm.alloc_bytes(2 * self.world * self.one_shot_max_bytes * 2)
+        self._ll_state = torch.zeros(2, dtype=torch.int32, device=symm.device)      # sequence number, ticket
 
-    def _run(self, local, n, dtype, op, mode, root=0, max_ctas=0):
+        def _ll_clear():
+            self._ll_recv.view(torch.int32, self._ll_recv.nbytes // 4).zero_()
+            self._ll_state.zero_()
+        _ll_clear()
+        symm.on_reset(_ll_clear)
+        symm.barrier()                  # nobody pushes into an area that its owner has not cleared yet
+
+    @property
+    def stage(self):
+        """The staging buffer the next collective works on."""
+        return self._stages[self._half]
+
+    def _run(self, local, n, dtype, op, mode, root=0, max_ctas=0, extra=None, open_ended=False):
         lib, s = self._lib, self.symm
         lib.check(lib.lib().tfb_collective(self.stage.ptrs.data_ptr(), lib.ptr(local), n, 0 if dtype == torch.bfloat16 else 1, OPS[op],
                                            mode, root, s.flags.ptrs.data_ptr(), s.epoch.data_ptr(), self.rank, self.world,
-                                           lib.status_word(s.device).data_ptr(), self.ticket.data_ptr(), max_ctas, lib.stream()),
+                                           lib.status_word(s.device).data_ptr(), self.ticket.data_ptr(), max_ctas,
+                                           lib.ptr(extra), 1 if open_ended else 0, lib.stream()),
                   "collective")
+        self._half ^= 1
+        self.count += 1
+
+    def _pad(self):
+        """One smallest collective (with its closing barrier): moves the alternation on by one."""
+        n = 16 * self.world // 4
+        self._run(torch.empty(n, dtype=torch.float32, device=self.symm.device), n, torch.float32, "sum", 0, max_ctas=1)
+
+    # A captured sequence has its staging buffers baked in.  capture_begin() notes which buffer it starts on,
+    # capture_end() (still inside the capture) makes the number of captured collectives even, so that the sequence ends
+    # on the other buffer, and before_replay() brings the host-side alternation to the captured starting point (with one
+    # small eager collective when the eager work in between left it on the other buffer).
+    def capture_begin(self):
+        return (self._half, self.count)
+
+    def capture_end(self, token):
+        if (self.count - token[1]) & 1:
+            self._pad()
+
+    def before_replay(self, token):
+        if self._half != token[0]:
+            self._pad()
 
     def _padded(self, t):
         assert t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous()
@@ -137,13 +185,41 @@ class SymmCollectives:
             st[t.numel():].zero_()
         one = algo == "one_shot" or (algo == "auto" and n * t.element_size() <= self.one_shot_max_bytes)
         if one:
-            out = torch.empty(n, dtype=t.dtype, device=t.device)
-            self._run(out, n, t.dtype, op, 0, max_ctas=8)
-            t.copy_(out[: t.numel()].view(t.shape))
+            if n == t.numel():
+                self._run(t, n, t.dtype, op, 0, max_ctas=self._one_shot_ctas(n * t.element_size()), open_ended=True)
+            else:
+                out = torch.empty(n, dtype=t.dtype, device=t.device)
+                self._run(out, n, t.dtype, op, 0, max_ctas=self._one_shot_ctas(n * t.element_size()), open_ended=True)
+                t.copy_(out[: t.numel()].view(t.shape))
         else:
             self._run(None, n, t.dtype, op, 1)
             t.copy_(st[: t.numel()].view(t.shape))
         return t
+
+    @staticmethod
+    def _one_shot_ctas(nbytes: int) -> int:
+        """One CTA up to 8 KiB (the barrier is paid once), then one per 16 KiB up to 32."""
+        return max(1, min(32, nbytes // (16 << 10)))
+
+    def all_reduce_ll(self, x: torch.Tensor, op="sum", residual: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Latency-bound all-reduce of a local tensor (any local memory; at most ``one_shot_max_bytes``, a multiple of 16
+        bytes): every rank pushes its data, tagged with a sequence number, into the peers' receive areas and reduces what
+        arrives in its own - no barrier, nothing host-side to keep in step (safe in captured graphs).  ``residual``: local
+        addend (op sum).  Result in ``out`` (default: a new tensor; may be ``x`` itself)."""
+        assert x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float32)
+        nbytes = x.numel() * x.element_size()
+        assert nbytes % 16 == 0 and nbytes <= self.one_shot_max_bytes, "message not a multiple of 16 bytes or too large"
+        if out is None:
+            out = torch.empty_like(x)
+        if residual is not None:
+            assert op == "sum" and residual.dtype == x.dtype and residual.numel() == x.numel() and residual.is_contiguous()
+        lib = self._lib
+        lib.check(lib.lib().tfb_allreduce_ll(self._ll_recv.ptrs.data_ptr(), x.data_ptr(), lib.ptr(residual), out.data_ptr(), x.numel(),
+                                             self.one_shot_max_bytes, 0 if x.dtype == torch.bfloat16 else 1, OPS[op], self.rank,
+                                             self.world, self._ll_state.data_ptr(), self._ll_state[1:].data_ptr(),
+                                             lib.status_word(self.symm.device).data_ptr(), 0, lib.stream()), "allreduce_ll")
+        return out
 
     def stage_view(self, dtype, numel: int):
         """View of this rank's staging buffer for producers that write their result there directly (saves the copy-in of
@@ -153,17 +229,26 @@ class SymmCollectives:
             return None
         return self.stage.view(dtype, numel)
 
-    def all_reduce_staged(self, numel: int, dtype, op="sum") -> torch.Tensor:
+    def all_reduce_staged(self, numel: int, dtype, op="sum", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """All-reduce of data already in the staging buffer (see stage_view).  Returns a flat tensor holding the result:
-        a fresh buffer for the one-shot form, the staging buffer itself for the two-shot form (consume it before the next
-        collective)."""
+        a fresh buffer for the one-shot form, the staging buffer itself for the two-shot form (consume it before the
+        collective after the next one).  ``residual`` (same dtype, ``numel`` elements, op sum): added to the result -
+        inside the kernel, before the one rounding, for the one-shot form."""
         esz = torch.empty(0, dtype=dtype).element_size()
+        if residual is not None:
+            assert op == "sum" and residual.dtype == dtype and residual.numel() == numel
+            residual = residual.contiguous()
         if numel * esz <= self.one_shot_max_bytes:
             out = torch.empty(numel, dtype=dtype, device=self.symm.device)
-            self._run(out, numel, dtype, op, 0, max_ctas=8)
+            fuse = residual is not None and residual.data_ptr() % 16 == 0
+            self._run(out, numel, dtype, op, 0, max_ctas=self._one_shot_ctas(numel * esz), extra=residual if fuse else None,
+                      open_ended=True)
+            if residual is not None and not fuse:
+                out += residual.view(-1)
             return out
+        st = self.stage.view(dtype, numel)
         self._run(None, numel, dtype, op, 1)
-        return self.stage.view(dtype, numel)
+        return st if residual is None else st + residual.view(-1)
 
     def reduce_scatter(self, t: torch.Tensor, op="sum") -> torch.Tensor:
         n = self._padded(t)
@@ -176,8 +261,9 @@ class SymmCollectives:
     def all_gather(self, shard: torch.Tensor) -> torch.Tensor:
         n = shard.numel() * self.world
         assert n * shard.element_size() % (16 * self.world) == 0 and n * shard.element_size() <= self.capacity
+        st = self.stage.view(shard.dtype, n)
         self._run(shard.contiguous(), n, shard.dtype, "sum", 3)
-        return self.stage.view(shard.dtype, n).clone()
+        return st.clone()
 
     def broadcast(self, t: torch.Tensor, root=0) -> torch.Tensor:
         n = self._padded(t)

@@ -384,3 +384,82 @@ class ExpertParallelManager:
             acc += torch.from_numpy(np.frombuffer(m[3], dtype=np.float32).copy()).view(acc.shape)
             got += 1
         return (acc / got).to(grads.device)
+
+
+class PipelineStage:
+    """One stage of the expert pipeline: the experts it runs, where, and its pending input / last output."""
+
+    def __init__(self, stage_id: int):
+        self.stage_id, self.expert_ids, self.node_id, self.ready = stage_id, [], -1, False
+        self.input_buffer = self.output_buffer = None
+
+
+class PipelineScheduler:
+    """Chains expert-parallel stages: stage i's output becomes stage i + 1's input; ``execute_pipeline`` runs every stage
+    that has input pending, in order, through its manager's ``forward_expert_parallel``.  ``micro_batch_size`` splits a
+    scheduled input into micro-batches that flow through the stages one after another, so stage i can work on micro-batch
+    j + 1 while stage i + 1 holds micro-batch j (the order a multi-node deployment overlaps).
+
+    Reference counterpart: PipelineScheduler / PipelineStage (include/quant/expert_parallel.h:197-228,
+    src/model/expert_parallel.cpp:975-1051)."""
+
+    def __init__(self, num_stages: int, micro_batch_size: int):
+        import threading
+        self.num_stages, self.micro_batch_size = num_stages, max(1, micro_batch_size)
+        self._stages = [PipelineStage(i) for i in range(num_stages)]
+        self._lock = threading.Lock()
+        self.current_step = 0
+
+    def schedule_forward(self, x, stage_id: int):
+        with self._lock:
+            if 0 <= stage_id < self.num_stages:
+                self._stages[stage_id].input_buffer, self._stages[stage_id].ready = x, True
+
+    def schedule_backward(self, grad_output, stage_id: int):
+        with self._lock:
+            if 0 <= stage_id < self.num_stages:
+                self._stages[stage_id].output_buffer = grad_output
+
+    def execute_pipeline(self, managers, all_experts=None):
+        """``managers[i]``: object with ``forward_expert_parallel(x, experts)`` (ExpertParallelManager) or a plain callable
+        for stage i.  Returns the last stage's output (micro-batches concatenated) or None when nothing was pending."""
+        import torch
+        with self._lock:
+            first = self._stages[0]
+            if not first.ready or first.input_buffer is None:
+                pending = [s for s in self._stages if s.ready and s.input_buffer is not None]
+                if not pending:
+                    return None
+                start, chunks = pending[0].stage_id, [pending[0].input_buffer]
+            else:
+                start, chunks = 0, list(torch.split(first.input_buffer, self.micro_batch_size, 0))
+            outs = []
+            for mb in chunks:
+                x = mb
+                for st in range(start, self.num_stages):
+                    s = self._stages[st]
+                    if st >= len(managers) or managers[st] is None:
+                        break
+                    fn = managers[st]
+                    ex = all_experts[st] if all_experts is not None and st < len(all_experts) else None
+                    y = fn.forward_expert_parallel(x, ex) if hasattr(fn, "forward_expert_parallel") else fn(x)
+                    y = getattr(y, "output", y)
+                    s.input_buffer, s.output_buffer, s.ready = x, y, False
+                    x = y
+                    self.current_step += 1
+                outs.append(x)
+            return torch.cat(outs, 0) if len(outs) > 1 else outs[0]
+
+    def get_stage(self, stage_id: int):
+        with self._lock:
+            return self._stages[stage_id] if 0 <= stage_id < self.num_stages else PipelineStage(-1)
+
+    def all_stages_done(self) -> bool:
+        with self._lock:
+            return not any(s.ready for s in self._stages)
+
+    def reset(self):
+        with self._lock:
+            for s in self._stages:
+                s.ready, s.input_buffer, s.output_buffer = False, None, None
+            self.current_step = 0

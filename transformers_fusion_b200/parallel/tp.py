@@ -26,7 +26,7 @@ class _Tp(C.Structure):
     _fields_ = [("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int), ("epoch", C.c_int),
                 ("ready", C.c_void_p), ("peer_a", C.c_void_p), ("peer_c", C.c_void_p), ("peer_c_host", C.c_void_p),
                 ("wg_rank", C.c_int), ("wg_world", C.c_int), ("wg_epoch", C.c_int), ("wg_rows", C.c_int),
-                ("wg_ready", C.c_void_p), ("wg_src", C.c_void_p)]
+                ("wg_ready", C.c_void_p), ("wg_src", C.c_void_p), ("wg_skip_local", C.c_int)]
 
 
 def _fn():
@@ -43,11 +43,13 @@ class WeightGather:
     ``buf`` [rows_p, cols] local bf16 gather buffer, ``src`` device int64[world] with the base address of every rank's
     shard ([rows_p / world, cols], symmetric memory), ``ready`` local int32[rows_p / 128] flags and the value ``epoch``
     they take once a block has landed (one more than at the previous gather into the same flags)."""
-    __slots__ = ("buf", "src", "ready", "epoch", "rank", "world", "rows_p")
+    __slots__ = ("buf", "src", "ready", "epoch", "rank", "world", "rows_p", "skip_local")
 
-    def __init__(self, buf, src, ready, epoch, rank, world):
+    def __init__(self, buf, src, ready, epoch, rank, world, skip_local=False):
+        """``skip_local``: this rank's own rows are already in ``buf`` (copied by the caller): only remote rows travel."""
         self.buf, self.src, self.ready, self.epoch, self.rank, self.world = buf, src, ready, epoch, rank, world
         self.rows_p = buf.shape[0]
+        self.skip_local = skip_local
 
 
 def fused_gemm(x, w, *, b_mn=False, n=None, k=None, out=None, residual=None, tp=None, wg: WeightGather = None, copy_ctas=8):
@@ -70,6 +72,7 @@ def fused_gemm(x, w, *, b_mn=False, n=None, k=None, out=None, residual=None, tp=
         mode |= 4
         d.wg_rank, d.wg_world, d.wg_epoch, d.wg_rows = wg.rank, wg.world, wg.epoch, wg.rows_p
         d.wg_ready, d.wg_src = wg.ready.data_ptr(), wg.src.data_ptr()
+        d.wg_skip_local = int(wg.skip_local)
     d.mode, d.copy_ctas = mode, copy_ctas
     y = None
     if not (mode & 2):

@@ -153,9 +153,19 @@ def dequant_bf16(pw: PackedWeight) -> torch.Tensor:
     return out
 
 
-def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
+def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = None, splits: int = 0,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y [M, N] = x [M, K] @ dequant(pw)^T (+ bias).  bf16 in / out.  M <= 16 (decode): fused-dequant kernel with the deep
-    ring and split-K; M < 2048: fused-dequant kernel with 128-row tiles; larger: bf16 image in scratch + bf16 GEMM."""
+    ring and split-K; M < 2048: fused-dequant kernel with 128-row tiles; larger: bf16 image in scratch + bf16 GEMM.
+    ``out`` [M, N] bf16: where the result goes (e.g. the staging buffer of a collective)."""
+    y = _gemm_wq(x, pw, bias, splits, out)
+    if out is not None and y is not out:
+        out.copy_(y)
+        return out
+    return y
+
+
+def _gemm_wq(x, pw, bias, splits, dst):
     M, K = x.shape
     if not x.is_cuda:
         y = x.float() @ dequant(pw).t()
@@ -181,6 +191,8 @@ def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = No
     use_split = splits > 1 or (splits == 0 and tiles * 2 <= 148 and pw.Kp >= 512)
     if use_split:
         out = torch.zeros((M, pw.Np), dtype=torch.float32, device=x.device)
+    elif dst is not None and pw.Np == pw.N and dst.is_contiguous() and dst.dtype == torch.bfloat16:
+        out = dst
     else:
         out = torch.empty((M, pw.Np), dtype=torch.bfloat16, device=x.device)
     bp = None
@@ -192,6 +204,11 @@ def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = No
                                 _lib.status_word(x.device).data_ptr(), stream())
     if rc < 1:
         check(rc, "gemm_wq")
+    if out.dtype == torch.bfloat16:
+        return out if out is dst else out[:, : pw.N]
+    if dst is not None:                       # the fp32 split-K sums are rounded straight into the caller's buffer
+        dst.copy_(out[:, : pw.N])
+        return dst
     return out[:, : pw.N].to(torch.bfloat16)
 
 
