@@ -30,7 +30,8 @@ def test_host_collectives_gloo(tmp_path):
 def test_fused_collectives(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    n = 2 if torch.cuda.device_count() < 4 else 4
+    g = torch.cuda.device_count()
+    n = 2 if g < 4 else (4 if g < 8 else 8)
     for res in _launch(n, "nccl", tmp_path, {"NCCL_NVLS_ENABLE": "0"}):
         assert res["status"] == 0, res
         for k, v in res.items():

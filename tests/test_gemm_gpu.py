@@ -32,6 +32,20 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert err <= 1e-2 * ref.abs().max().item() + 1e-3, err
 
 
+@pytest.mark.parametrize("M,N,K", [(640, 3504, 192), (1100, 7000, 128), (520, 3328, 64)])
+def test_gemm_grouped_raster(M, N, K):
+    """Wide outputs (more than twelve 256-column tiles, at least four row tiles) are walked in groups of eight tile columns:
+    every output tile must still be produced exactly once, including the ragged last group."""
+    for b_mn in (False, True):
+        a, b = _mk(M, N, K, False, b_mn)
+        c = F.gemm(a, b, b_mn=b_mn)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        ref = _ref(a, b, False, b_mn)
+        err = (c.float() - ref).abs().max().item()
+        assert err <= 1e-2 * ref.abs().max().item() + 1e-3, err
+
+
 def test_gemm_epilogue():
     M, N, K = 512, 768, 256
     a, b = _mk(M, N, K, False, False)

@@ -145,6 +145,18 @@ assert rep["elementwise"][0] >= 1 and rep["elementwise"][1:] == (1, 99, 32), rep
 assert rep["loss_optim"][0] == 1 and rep["loss_optim"][1:] == (3, 77, 32), rep
 assert _lib.bounds_report()["elementwise"][0] == 0
 assert torch.equal(out[2], W[0])
+# paged KV cache: a slot beyond the pool is skipped, a block-table page beyond the pool reads page 0
+from transformers_fusion_b200.inference.kv_cache import PAGE, PagedKVCache
+cache = PagedKVCache(1, 4, 2, 64, "bf16", "cuda")
+src = torch.randn(3, 2 * 2 * 64, device="cuda").bfloat16()
+cache.append(0, src, 0, 128, torch.tensor([0, 1, 4 * PAGE + 5], device="cuda"))
+q = torch.randn(1, 4 * 64, device="cuda").bfloat16()
+bt = torch.tensor([[0, 9]], dtype=torch.int32, device="cuda")
+o = cache.decode(0, q, bt, torch.tensor([PAGE + 2], dtype=torch.int32, device="cuda"), 4)
+torch.cuda.synchronize()
+rep = _lib.bounds_report()["paged_attention"]
+assert rep[0] >= 2 and rep[1] in (51, 52) and rep[3] in (4 * PAGE, 4), rep
+assert torch.isfinite(o.float()).all()
 print("ok")
 '''
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -64,6 +64,7 @@ struct GemmParams {
   int act;       // 0 none, 1 relu, 2 gelu(tanh), 3 silu
   int out_mode;  // 0 bf16 store, 1 fp32 store, 2 fp32 atomic accumulate
   int splits, kb_per_split, tiles_m, tiles_n;
+  int raster_gn;   // tile order: groups of raster_gn tile columns; inside a group n runs fastest, then m
   // grouped (mixture-of-experts) modes; expert segments are padded to multiples of 128 rows
   //   1: rows of A / C grouped by expert, B = [E, ...] picked per 128-row tile (forward, data gradient)
   //   2: reduction dimension grouped by expert, C = [E, M, N] (weight gradient of every expert in one launch)
@@ -107,22 +108,29 @@ __device__ __forceinline__ bool decode_work(const GemmParams& p, int w, int tota
     return it.kb1 > it.kb0;
   }
   const int tile = w / p.splits, split = w - tile * p.splits;
-  it.m0 = (tile / p.tiles_n) * BM;
-  it.n0 = tile % p.tiles_n;
+  // Grouped raster.  A wave of 148 tiles in plain row-major order spans every tile column, i.e. reads all of B once per
+  // wave; with a wide N (B larger than L2) that is one DRAM pass over B per wave.  In groups of raster_gn columns a wave
+  // covers a roughly square patch, the group's slice of B stays in L2 for the whole sweep over M, and A is streamed once
+  // per group.  raster_gn == tiles_n is the plain row-major order, raster_gn == 1 column-major.
+  const int per_group = p.raster_gn * p.tiles_m;
+  const int grp = tile / per_group, within = tile - grp * per_group;
+  const int gn = min(p.raster_gn, p.tiles_n - grp * p.raster_gn);
+  const int m_idx = within / gn, n_idx = grp * p.raster_gn + (within - m_idx * gn);
+  it.m0 = m_idx * BM;
+  it.n0 = n_idx;
   it.kb0 = split * p.kb_per_split;
   it.kb1 = min(total_kb, it.kb0 + p.kb_per_split);
   it.expert = 0;
   if (p.group_mode == 1) {
-    it.expert = p.expert_of_mtile[tile / p.tiles_n];
+    it.expert = p.expert_of_mtile[m_idx];
     if (it.expert < 0) return false;
     TFB_BOUNDS(it.expert < p.num_experts, 12, it.expert, p.num_experts);
     if (it.expert >= p.num_experts) return false;
   }
   if ((p.tp_mode & TP_WG) && p.wg_n_shift >= 0) {
-    // K-major gathered B: n is the slow index and starts at the local shard's columns
-    it.m0 = (tile % p.tiles_m) * BM;
-    const int nt = tile / p.tiles_m;
-    it.n0 = (nt + p.wg_n_shift) % p.tiles_n;
+    // K-major gathered B: the column groups are visited starting at the local shard's columns, in the order in which
+    // the copy CTAs deliver the peers' rows
+    it.n0 = (n_idx + p.wg_n_shift) % p.tiles_n;
   }
   if (p.tp_mode & TP_AG) {
     // rotate the row-block order: start with the local shard (already in place)
@@ -947,6 +955,18 @@ static int gemm_impl(const void* A, long long lda, int a_mn, const void* B, long
       else p.wg_k_shift = (tp->wg_rank * (p.wg.rows_per_shard / BK)) % ((K + BK - 1) / BK);
     }
     p.tp_mode = tp->mode;
+  }
+  {
+    // tile order (see decode_work): row-major unless B is wide; the activation gather / reduce-scatter orders follow the
+    // row blocks and stay row-major; a gathered K-major weight is always walked in column groups
+    static const int raster_env = [] { const char* e = getenv("TFB_GEMM_RASTER"); return e ? atoi(e) : -1; }();
+    const int wide = (BN == 256) ? 8 : 16;
+    p.raster_gn = p.tiles_n;
+    if (gmode != 2 && !(p.tp_mode & (TP_AG | TP_RS))) {
+      if ((p.tp_mode & TP_WG) && p.wg_n_shift >= 0) p.raster_gn = raster_env == 0 ? 1 : min(wide, p.tiles_n);
+      else if (raster_env != 0 && p.tiles_n > wide + wide / 2 && p.tiles_m >= 4) p.raster_gn = raster_env > 0 ? raster_env : wide;
+    }
+    if (p.raster_gn < 1) p.raster_gn = 1;
   }
   const int total_kb = (K + BK - 1) / BK;
   const int tiles = p.tiles_m * p.tiles_n;

@@ -23,6 +23,8 @@
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
+TFB_BOUNDS_DEFINE(paged_attention)
+
 namespace tfb {
 
 enum { KV_BF16 = 0, KV_FP8 = 1, KV_Q4 = 2 };
@@ -42,6 +44,7 @@ __device__ __forceinline__ uint8_t f32_to_e4m3_sat(float x) {
 struct KvPool {
   void* data;     // packed values
   void* scale;    // fp32 (fp8) or fp16 (q4) scales, null for bf16
+  long long rows; // token slots in the pool (pages x PAGE); 0 = not given.  Read by the bounds-check build only.
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -97,6 +100,10 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ src, long lon
   const long long t = w / Hkv;
   const long long slot = slot_mapping[t];
   if (slot < 0) return;
+  TFB_BOUNDS(kpool.rows == 0 || slot < kpool.rows, 51, slot, kpool.rows);
+#ifdef TFB_BOUNDS_CHECK
+  if (kpool.rows != 0 && slot >= kpool.rows) return;
+#endif
   const int n = D / 32;  // 2 (D=64) or 4 (D=128)
   float kv[4], vv[4];
   const __nv_bfloat16* kp = src + t * ld + k_col0 + h * D + lane * n;
@@ -208,7 +215,12 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const int t = t0 + tid;
     float s[G];
     if (t < t_end) {
-      const long long row = ((long long)bt[t / PAGE] * PAGE + (t % PAGE)) * Hkv + hk;
+      long long page = bt[t / PAGE];
+      TFB_BOUNDS(kpool.rows == 0 || (page >= 0 && (page + 1) * PAGE <= kpool.rows), 52, page, kpool.rows / PAGE);
+#ifdef TFB_BOUNDS_CHECK
+      if (kpool.rows != 0 && (page < 0 || (page + 1) * PAGE > kpool.rows)) page = 0;
+#endif
+      const long long row = (page * PAGE + (t % PAGE)) * Hkv + hk;
       float kr[D];
       load_row<MODE, D>(kpool, row, kr);
 #pragma unroll
@@ -273,7 +285,11 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
       for (int u = 0; u < VU; ++u) {
         const int tt = min(tt0 + u * NW, nt - 1);
         const int tk = t0 + tt;
-        const long long row = ((long long)bt[tk / PAGE] * PAGE + (tk % PAGE)) * Hkv + hk;
+        long long page = bt[tk / PAGE];
+#ifdef TFB_BOUNDS_CHECK
+        if (vpool.rows != 0 && (page < 0 || (page + 1) * PAGE > vpool.rows)) page = 0;   // reported by the score pass above
+#endif
+        const long long row = (page * PAGE + (tk % PAGE)) * Hkv + hk;
         if (MODE == KV_BF16) {
           const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(vpool.data) + row * D + lane * DL;
           if (DL == 4) {
@@ -373,11 +389,12 @@ static int launch_decode_g(int G, dim3 grid, cudaStream_t st, const __nv_bfloat1
 
 using namespace tfb;
 
+// pool_rows: token slots in each pool (pages x 16), checked by the bounds-check build; 0 = not given.
 TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0, const long long* slot_mapping,
                           void* k_data, void* k_scale, void* v_data, void* v_scale, int T, int Hkv, int D, int mode,
-                          void* stream) {
+                          long long pool_rows, void* stream) {
   if (D != 64 && D != 128) return TFB_ERR_ARG;
-  KvPool kp{k_data, k_scale}, vp{v_data, v_scale};
+  KvPool kp{k_data, k_scale, pool_rows}, vp{v_data, v_scale, pool_rows};
   const long long warps = (long long)T * Hkv;
   const unsigned blocks = unsigned((warps * 32 + 255) / 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -393,10 +410,10 @@ TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0,
 TFB_API int tfb_paged_decode(const void* q, long long ldq, void* k_data, void* k_scale, void* v_data, void* v_scale,
                              const int* block_table, int max_pages, const int* seq_lens, void* o, long long ldo,
                              float* acc_ws, float* ml_ws, int B, int Hq, int Hkv, int D, int splits, int mode,
-                             float scale, void* stream) {
+                             float scale, long long pool_rows, void* stream) {
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || splits < 1) return TFB_ERR_ARG;
   const int G = Hq / Hkv;
-  KvPool kp{k_data, k_scale}, vp{v_data, v_scale};
+  KvPool kp{k_data, k_scale, pool_rows}, vp{v_data, v_scale, pool_rows};
   dim3 grid(B, Hkv, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto Q = static_cast<const __nv_bfloat16*>(q);

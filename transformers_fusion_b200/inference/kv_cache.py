@@ -19,9 +19,9 @@ from ..ops._lib import c_f, c_i, c_ll, c_p, check, ptr, stream
 PAGE = 16
 MODES = {"bf16": 0, "fp8": 1, "q4": 2}
 
-_lib.register("tfb_kv_append", [c_p, c_ll, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+_lib.register("tfb_kv_append", [c_p, c_ll, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_p])
 _lib.register("tfb_paged_decode", [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_ll, c_p, c_p, c_i, c_i, c_i,
-                                   c_i, c_i, c_i, c_f, c_p])
+                                   c_i, c_i, c_i, c_f, c_ll, c_p])
 
 
 class PageAllocator:
@@ -132,7 +132,7 @@ class PagedKVCache:
             return
         check(_lib.lib().tfb_kv_append(src.data_ptr(), src.stride(0), k_col0, v_col0, slot_mapping.data_ptr(),
                                        kp.data.data_ptr(), ptr(kp.scale), vp.data.data_ptr(), ptr(vp.scale), T,
-                                       self.Hkv, self.D, MODES[self.mode], stream()), "kv_append")
+                                       self.Hkv, self.D, MODES[self.mode], self.num_pages * PAGE, stream()), "kv_append")
 
     def decode(self, layer, q, block_table, seq_lens, Hq, scale=None, splits=None):
         """q [B, Hq*D] bf16 -> o [B, Hq*D] attending over the first seq_lens[b] cached tokens of each sequence."""
@@ -166,5 +166,5 @@ class PagedKVCache:
                                           vp.data.data_ptr(), ptr(vp.scale), block_table.data_ptr(),
                                           block_table.shape[1], seq_lens.data_ptr(), o.data_ptr(), o.stride(0),
                                           acc.data_ptr(), ml.data_ptr(), B, Hq, Hkv, D, splits, MODES[self.mode],
-                                          float(scale), stream()), "paged_decode", 2)
+                                          float(scale), self.num_pages * PAGE, stream()), "paged_decode", 2)
         return o

@@ -65,11 +65,13 @@ def bounds_report(reset: bool = True) -> dict:
     """Bounds-check build only: {unit: (count, site, index, limit)} of the first out-of-range index each unit saw
     (sites: 1 embedding id, 2 embedding-gradient id, 3 cross-entropy label, 5 routed expert id, 11 gather block of a
     fused GEMM, 12 expert of a grouped-GEMM row tile, 21 row owner of the sharded embedding, 31 vocabulary-parallel label,
-    41 destination row of an expert-parallel dispatch)."""
+    41 destination row of an expert-parallel dispatch, 51 KV-cache slot of an append, 52 page of a paged-decode block
+    table)."""
     out = {}
     if not bounds_check_build():
         return out
-    for unit in ("elementwise", "loss_optim", "moe_routing", "gemm_bf16", "fsdp_fused", "loss_vocab_parallel", "ep_fused"):
+    for unit in ("elementwise", "loss_optim", "moe_routing", "gemm_bf16", "fsdp_fused", "loss_vocab_parallel", "ep_fused",
+                 "paged_attention"):
         fn = getattr(lib(), f"tfb_bounds_report_{unit}", None)
         if fn is None:
             continue
