@@ -244,6 +244,9 @@ def main(argv=None):
     ap.add_argument("--model", default="llama-50m")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (stated in the config line)")
     ap.add_argument("--tp", type=int, default=2, help="llama3-8b-fsdp-tp2: tensor-parallel degree")
+    ap.add_argument("--kernel-table", default="", metavar="FILE",
+                    help="llama3-8b-fsdp-tp2: after the timed steps run one more step under the PyTorch profiler and write "
+                         "rank 0's per-kernel table to FILE (shares of a step; never the source of a reported number)")
     ap.add_argument("--gather", default="auto", choices=["auto", "prefetch", "fused"],
                     help="llama3-8b-fsdp-tp2: ZeRO-3 weight gather by a prefetching kernel on a side stream, or inside the "
                          "GEMM that first uses the weight")
@@ -642,6 +645,16 @@ def main_sharded(args):
     _lib.check_status(dev)
     peak = torch.tensor([float(torch.cuda.max_memory_allocated(dev))], device=dev)
     dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            dev_step(0)
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.kernel_table, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70))
+        barrier()
     memp = engine.memory_profile()
     heap_bytes = sum(b.nbytes for h in heaps if h is not None for b in h.buffers)
     global_tokens = st.dp * T

@@ -29,6 +29,7 @@ constexpr int BOX_BYTES = 128 * 64 * 2;
 
 struct AttnFwdParams {
   int B, S, Hq, Hkv;
+  int Skv, q_off;  // keys per sequence; causal: query i sees keys <= i + q_off (q_off = Skv - S: the queries are the last S positions)
   float scale;
   int causal;
   int q_col0, k_col0, v_col0;
@@ -139,7 +140,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int npair = (p.S + 2 * ATT_BM - 1) / (2 * ATT_BM);
-  const int nkb = (p.S + ATT_BN - 1) / ATT_BN;
+  const int nkb = (p.Skv + ATT_BN - 1) / ATT_BN;
   const int bh = p.B * p.Hq;
   const int pair = npair - 1 - int(blockIdx.x) / bh;  // longest (latest) query blocks are scheduled first
   const int rem = int(blockIdx.x) % bh;
@@ -150,7 +151,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int qb = pair * 2 + t;
-    n_t[t] = qb * ATT_BM >= p.S ? 0 : (p.causal ? min(qb + 1, nkb) : nkb);
+    const int q_last = min(qb * ATT_BM + ATT_BM - 1, p.S - 1);   // last query row of the tile
+    n_t[t] = qb * ATT_BM >= p.S ? 0 : (p.causal ? min((q_last + p.q_off) / ATT_BN + 1, nkb) : nkb);
   }
   const int n_kv = max(n_t[0], n_t[1]);
 
@@ -282,8 +284,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       tc_fence_after();
       const int k0 = j * ATT_BN;
-      const bool need_mask = (p.causal && k0 + ATT_BN - 1 > qb * ATT_BM) || (k0 + ATT_BN > p.S);
-      const int k_lim = p.causal ? min(q_idx, p.S - 1) : (p.S - 1);  // last visible key index for this row
+      const bool need_mask = (p.causal && k0 + ATT_BN - 1 > qb * ATT_BM + p.q_off) || (k0 + ATT_BN > p.Skv);
+      const int k_lim = p.causal ? min(q_idx + p.q_off, p.Skv - 1) : (p.Skv - 1);  // last visible key index for this row
       const float mx = need_mask ? row_max<true>(tS, m, k0, k_lim) : row_max<false>(tS, m, k0, k_lim);
       if (j > 0) {  // O_t(j-1) is complete: the commit behind S_t(j) was issued after it
 #pragma unroll
@@ -361,19 +363,35 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 // head h of q starts at column q_col0 + h * D of its row (likewise k, v with the kv head index), so
 // the three pointers may be the same fused [T, (Hq + 2 Hkv) D] projection output.
 // o: [B*S, ldo] bf16, head h at column h * D.  lse: [B, Hq, S] fp32 (may be null).
+//
+// tfb_attn_fwd_kv: the keys / values have Skv >= S rows per sequence (k, v rows are b * Skv + s) and the S queries are the
+// last S positions: with `causal`, query i sees keys 0 .. i + (Skv - S).  This is the prefill of a prompt suffix behind a
+// cached prefix (the prefix keys come out of the paged cache, see tfb_kv_gather).
+TFB_API int tfb_attn_fwd_kv(const void* q, long long ldq, int q_col0, const void* k, long long ldk, int k_col0,
+                            const void* v, long long ldv, int v_col0, void* o, long long ldo, float* lse, int B, int S,
+                            int Skv, int Hq, int Hkv, int D, float scale, int causal, int* status, void* stream);
+
 TFB_API int tfb_attn_fwd(const void* q, long long ldq, int q_col0, const void* k, long long ldk, int k_col0,
                          const void* v, long long ldv, int v_col0, void* o, long long ldo, float* lse, int B, int S,
                          int Hq, int Hkv, int D, float scale, int causal, int* status, void* stream) {
+  return tfb_attn_fwd_kv(q, ldq, q_col0, k, ldk, k_col0, v, ldv, v_col0, o, ldo, lse, B, S, S, Hq, Hkv, D, scale, causal, status,
+                         stream);
+}
+
+TFB_API int tfb_attn_fwd_kv(const void* q, long long ldq, int q_col0, const void* k, long long ldk, int k_col0,
+                            const void* v, long long ldv, int v_col0, void* o, long long ldo, float* lse, int B, int S,
+                            int Skv, int Hq, int Hkv, int D, float scale, int causal, int* status, void* stream) {
   using namespace tfb;
-  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || B <= 0 || S <= 0) return TFB_ERR_ARG;
+  if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || B <= 0 || S <= 0 || Skv < S) return TFB_ERR_ARG;
   if ((q_col0 | k_col0 | v_col0) & 7 || (ldo & 7) || (reinterpret_cast<uintptr_t>(o) & 15)) return TFB_ERR_ARG;
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_tmap_3d(&tq, q, 2, ldq, S, B, ldq * 2, ldq * 2 * S, 64, 128, 1))) return rc;
-  if ((rc = make_tmap_3d(&tk, k, 2, ldk, S, B, ldk * 2, ldk * 2 * S, 64, 128, 1))) return rc;
-  if ((rc = make_tmap_3d(&tv, v, 2, ldv, S, B, ldv * 2, ldv * 2 * S, 64, 128, 1))) return rc;
+  if ((rc = make_tmap_3d(&tk, k, 2, ldk, Skv, B, ldk * 2, ldk * 2 * Skv, 64, 128, 1))) return rc;
+  if ((rc = make_tmap_3d(&tv, v, 2, ldv, Skv, B, ldv * 2, ldv * 2 * Skv, 64, 128, 1))) return rc;
   AttnFwdParams p;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.Skv = Skv; p.q_off = Skv - S;
   p.scale = scale; p.causal = causal;
   p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
   p.O = static_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse; p.status = status;

@@ -18,6 +18,7 @@
 // Reference counterparts: PagedAttention::forward (src/inference/inference_paging.cpp:24-117, no length
 // mask), Q4KVCache 4-bit blocks (src/model/kv_cache_quant4.cpp:207-362), flash_decoding
 // (src/inference/inference_kv.cpp:141-205).
+#include <algorithm>
 #include <cuda_fp16.h>
 
 #include "tfb_host.h"
@@ -385,9 +386,109 @@ static int launch_decode_g(int G, dim3 grid, cudaStream_t st, const __nv_bfloat1
   return int(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------------------
+// gather: the first n cached tokens of one sequence -> contiguous bf16 rows [n, Hkv * D] for K and V (dequantised), so
+// that a prompt suffix behind a cached prefix can run through the tensor-core attention kernel instead of one
+// decode-style query per token.  One thread per (token, kv head, 32-element chunk).
+// ------------------------------------------------------------------------------------------------
+template <int MODE, int D>
+__device__ __forceinline__ void load_chunk32(const KvPool& pool, long long row, int c, float* out) {
+  if (MODE == KV_BF16) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(pool.data) + row * D + c * 32);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 u = p[i];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(w[j]);
+        out[i * 8 + 2 * j] = f.x;
+        out[i * 8 + 2 * j + 1] = f.y;
+      }
+    }
+  } else if (MODE == KV_FP8) {
+    const float s = static_cast<const float*>(pool.scale)[row];
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * D + c * 32);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 u = p[i];
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&u);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) out[i * 16 + j] = e4m3_to_f32(b[j]) * s;
+    }
+  } else {
+    const float s = __half2float(static_cast<const __half*>(pool.scale)[row * (D / 32) + c]);
+    const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * (D / 2) + c * 16);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(&u);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      out[2 * j] = float(int(b[j] & 15) - 8) * s;
+      out[2 * j + 1] = float(int(b[j] >> 4) - 8) * s;
+    }
+  }
+}
+
+template <int MODE, int D>
+__global__ void __launch_bounds__(256) kv_gather_kernel(KvPool kpool, KvPool vpool, const int* __restrict__ block_table, int n,
+                                                        __nv_bfloat16* __restrict__ out_k, __nv_bfloat16* __restrict__ out_v,
+                                                        long long ld, int Hkv) {
+  tfb::pdl_sync();
+  constexpr int C = D / 32;
+  const long long total = (long long)n * Hkv * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = int(i % C);
+    const int h = int((i / C) % Hkv);
+    const int t = int(i / ((long long)C * Hkv));
+    long long page = block_table[t / PAGE];
+    TFB_BOUNDS(kpool.rows == 0 || (page >= 0 && (page + 1) * PAGE <= kpool.rows), 53, page, kpool.rows / PAGE);
+#ifdef TFB_BOUNDS_CHECK
+    if (kpool.rows != 0 && (page < 0 || (page + 1) * PAGE > kpool.rows)) page = 0;
+#endif
+    const long long row = (page * PAGE + (t % PAGE)) * Hkv + h;
+    float f[32];
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      load_chunk32<MODE, D>(which ? vpool : kpool, row, c, f);
+      uint4* dst = reinterpret_cast<uint4*>((which ? out_v : out_k) + (long long)t * ld + h * D + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u;
+        u.x = pack_bf16(f[q * 8], f[q * 8 + 1]); u.y = pack_bf16(f[q * 8 + 2], f[q * 8 + 3]);
+        u.z = pack_bf16(f[q * 8 + 4], f[q * 8 + 5]); u.w = pack_bf16(f[q * 8 + 6], f[q * 8 + 7]);
+        dst[q] = u;
+      }
+    }
+  }
+}
+
 }  // namespace tfb
 
 using namespace tfb;
+
+// The first n cached tokens of one sequence (block_table: its page list) as contiguous bf16 rows: out_k / out_v
+// [n, ld] with kv head h at column h * D (ld a multiple of 8, buffers 16-byte aligned).
+TFB_API int tfb_kv_gather(void* k_data, void* k_scale, void* v_data, void* v_scale, const int* block_table, int n, void* out_k,
+                          void* out_v, long long ld, int Hkv, int D, int mode, long long pool_rows, void* stream) {
+  if ((D != 64 && D != 128) || Hkv <= 0 || n <= 0 || (ld & 7) || ld < (long long)Hkv * D) return TFB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(out_k) | reinterpret_cast<uintptr_t>(out_v)) & 15) return TFB_ERR_ARG;
+  KvPool kp{k_data, k_scale, pool_rows}, vp{v_data, v_scale, pool_rows};
+  const long long total = (long long)n * Hkv * (D / 32);
+  const int grid = int(std::min<long long>((total + 255) / 256, 148 * 8));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto ok = static_cast<__nv_bfloat16*>(out_k);
+  auto ov = static_cast<__nv_bfloat16*>(out_v);
+#define TFB_GATHER(MODE)                                                                                            \
+  do {                                                                                                              \
+    if (D == 64) tfb::launch_k(kv_gather_kernel<MODE, 64>, grid, 256, 0, st, kp, vp, block_table, n, ok, ov, ld, Hkv);   \
+    else tfb::launch_k(kv_gather_kernel<MODE, 128>, grid, 256, 0, st, kp, vp, block_table, n, ok, ov, ld, Hkv);          \
+  } while (0)
+  if (mode == KV_BF16) TFB_GATHER(KV_BF16);
+  else if (mode == KV_FP8) TFB_GATHER(KV_FP8);
+  else if (mode == KV_Q4) TFB_GATHER(KV_Q4);
+  else return TFB_ERR_ARG;
+#undef TFB_GATHER
+  return int(cudaGetLastError());
+}
 
 // pool_rows: token slots in each pool (pages x 16), checked by the bounds-check build; 0 = not given.
 TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0, const long long* slot_mapping,

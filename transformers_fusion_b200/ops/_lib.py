@@ -66,7 +66,7 @@ def bounds_report(reset: bool = True) -> dict:
     (sites: 1 embedding id, 2 embedding-gradient id, 3 cross-entropy label, 5 routed expert id, 11 gather block of a
     fused GEMM, 12 expert of a grouped-GEMM row tile, 21 row owner of the sharded embedding, 31 vocabulary-parallel label,
     41 destination row of an expert-parallel dispatch, 51 KV-cache slot of an append, 52 page of a paged-decode block
-    table)."""
+    table, 53 page of a KV gather)."""
     out = {}
     if not bounds_check_build():
         return out
