@@ -94,6 +94,28 @@ def test_engine_matches_recompute_gpu():
     assert agree >= 28, agree      # bf16 paths differ in rounding; near-ties may flip a token
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("kv_mode", ["bf16", "fp8"])
+def test_prefix_cache_suffix_prefill_gpu(kv_mode):
+    """A prompt whose first pages are cached: the suffix runs through the KV gather + tensor-core attention path and must
+    give the tokens of an engine that prefills the whole prompt (bf16 rounding may flip a near-tie).  With an fp8 cache the
+    two engines legitimately differ - the cold one attends over the exact prompt keys, the warm one over the fp8-rounded
+    prefix - so only the first tokens are compared there."""
+    m = _model("cuda", torch.bfloat16, hidden_size=256, num_heads=4, num_kv_heads=2)
+    base = torch.randint(3, 200, (200,), generator=torch.Generator().manual_seed(1)).tolist()
+    a, b = base + [7, 8, 9], base + list(range(10, 50))
+    cold = InferenceEngine(m, None, EngineConfig(num_pages=128, enable_prefix_cache=False, kv_mode=kv_mode))
+    ref = cold.generate_batch([a, b], 8, GREEDY)
+    warm = InferenceEngine(m, None, EngineConfig(num_pages=128, enable_prefix_cache=True, max_batch=1, kv_mode=kv_mode))
+    got = warm.generate_batch([a, b], 8, GREEDY)
+    assert warm.stats.prefix_hit_tokens == 192
+    agree = sum(int(x == y) for o, r in zip(got, ref) for x, y in zip(o, r))
+    if kv_mode == "bf16":
+        assert agree >= 14, (got, ref)
+    else:
+        assert all(len(o) == 8 for o in got) and agree >= 2, (got, ref)
+
+
 def test_engine_with_packed_weights_matches_dequantised_model():
     """Serving from int8-packed weights must give the tokens of a model whose weights are the dequantised values."""
     import torch

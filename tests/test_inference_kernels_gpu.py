@@ -54,6 +54,29 @@ def test_paged_append_and_decode(mode, Hq, Hkv, D):
         assert (outs["cuda"][b] - ref).abs().max().item() < tol
 
 
+@pytest.mark.parametrize("mode", ["bf16", "fp8", "q4"])
+@pytest.mark.parametrize("Hkv,D,n", [(2, 64, 100), (1, 128, 33), (4, 128, 256)])
+def test_kv_gather_matches_host_dequant(mode, Hkv, D, n):
+    """The gather kernel returns the first n cached tokens of a sequence as contiguous bf16 rows: identical to the host
+    statement (dequantise the pool, pick the sequence's pages) after its one rounding to bf16."""
+    pages = 40
+    cache = PagedKVCache(1, pages, Hkv, D, mode, "cuda")
+    npg = (n + PAGE - 1) // PAGE
+    pg = torch.randperm(pages)[:npg].to(torch.int32)
+    pos = torch.arange(n)
+    slots = (pg[pos // PAGE].long() * PAGE + pos % PAGE).cuda()
+    src = torch.randn(n, 2 * Hkv * D, device="cuda", dtype=torch.bfloat16)
+    cache.append(0, src, 0, Hkv * D, slots)
+    k, v = cache.gather(0, pg.cuda(), n)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    K = cache.k[0].dequant()[pg.long().cuda()].reshape(-1, Hkv * D)[:n].to(torch.bfloat16)
+    V = cache.v[0].dequant()[pg.long().cuda()].reshape(-1, Hkv * D)[:n].to(torch.bfloat16)
+    assert torch.equal(k, K) and torch.equal(v, V)
+    tol = {"bf16": 0.0, "fp8": 0.3, "q4": 0.6}[mode]
+    assert (k.float() - src[:, :Hkv * D].float()).abs().max().item() <= tol
+
+
 def test_sampling_distribution_and_greedy():
     V, B = 1000, 4
     logits = torch.randn(B, V) * 2

@@ -140,30 +140,39 @@ struct FsdpAgArgs {
 };
 
 // Like the reduce-scatter above, sized to sit beside a resident GEMM CTA: 128 threads, <= 80 registers, no shared memory.
-constexpr int AG_UNROLL = 8;
+// Every thread has one 16-byte load in flight to each rank at a time (UNROLL of them per rank): all W - 1 peers are read
+// at once, which spreads the traffic over every NVLink port instead of draining one peer after the other.
+template <int MAXW, int UNROLL>
 __global__ void __launch_bounds__(FS_THREADS, 6) fsdp_all_gather_kernel(FsdpAgArgs a) {
   tfb::pdl_sync();
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long t0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int W = a.world;
   for (int s = 0; s < a.nseg; ++s) {
     const FsdpAgSeg sg = a.seg[s];
-    for (int rr = 0; rr < a.world; ++rr) {
-      const int r = (a.rank + rr) % a.world;      // own shard first, then the peers starting at the next rank
-      const uint4* src = sg.src[r];
-      uint4* dst = sg.dst + (long long)r * sg.shard_vecs;
-      for (long long i0 = t0; i0 < sg.shard_vecs; i0 += stride * AG_UNROLL) {
-        uint4 v[AG_UNROLL];
+    const uint4* src[MAXW];
 #pragma unroll
-        for (int u = 0; u < AG_UNROLL; ++u) {
-          const long long i = i0 + u * stride;
-          if (i < sg.shard_vecs)
-            asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i) : "memory");
+    for (int rr = 0; rr < MAXW; ++rr) src[rr] = rr < W ? sg.src[(a.rank + rr) % W] : nullptr;   // [0] is the local shard
+    for (long long i0 = t0; i0 < sg.shard_vecs; i0 += stride * UNROLL) {
+      uint4 v[UNROLL][MAXW];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < sg.shard_vecs) {
+#pragma unroll
+          for (int rr = 0; rr < MAXW; ++rr)
+            if (rr < W)
+              asm volatile("ld.global.relaxed.sys.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[u][rr].x), "=r"(v[u][rr].y), "=r"(v[u][rr].z), "=r"(v[u][rr].w) : "l"(src[rr] + i) : "memory");
         }
+      }
 #pragma unroll
-        for (int u = 0; u < AG_UNROLL; ++u) {
-          const long long i = i0 + u * stride;
-          if (i < sg.shard_vecs) dst[i] = v[u];
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < sg.shard_vecs) {
+#pragma unroll
+          for (int rr = 0; rr < MAXW; ++rr)
+            if (rr < W) sg.dst[(long long)((a.rank + rr) % W) * sg.shard_vecs + i] = v[u][rr];
         }
       }
     }
@@ -251,7 +260,11 @@ TFB_API int tfb_fsdp_all_gather(const TfbFsdpAgDesc* d, int max_ctas, void* stre
   }
   int grid = sm_count() * 4;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  tfb::launch_k(fsdp_all_gather_kernel, grid, FS_THREADS, 0, static_cast<cudaStream_t>(stream), a);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d->world <= 2) tfb::launch_k(fsdp_all_gather_kernel<2, 4>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 4) tfb::launch_k(fsdp_all_gather_kernel<4, 2>, grid, FS_THREADS, 0, st, a);
+  else if (d->world <= 8) tfb::launch_k(fsdp_all_gather_kernel<8, 1>, grid, FS_THREADS, 0, st, a);
+  else tfb::launch_k(fsdp_all_gather_kernel<FS_MAX_WORLD, 1>, grid, FS_THREADS, 0, st, a);
   return int(cudaGetLastError());
 }
 

@@ -248,6 +248,7 @@ class InferenceEngine:
         positions = torch.arange(pos0, pos0 + S, dtype=torch.int32, device=dev)
         slots = torch.tensor([r.pages[p // PAGE] * PAGE + p % PAGE for p in range(pos0, pos0 + S)], dtype=torch.int64,
                              device=dev)
+        pages_dev = None
         for li, w in enumerate(m.layers):
             a, _ = _norm_fwd(mc, h, w.attention_norm, getattr(w, "attention_norm_bias", None))
             qkv = self._lin(a, li, "qkv", w.qkv, getattr(w, "qkv_bias", None))
@@ -257,12 +258,13 @@ class InferenceEngine:
             if pos0 == 0:
                 o, _ = F.attn_fwd(qkv, qkv, qkv, 1, S, Hq, Hkv, D, k_col0=Hq * D, v_col0=(Hq + Hkv) * D)
             else:
-                # suffix after a cached prefix: every new token attends over the pages (prefix + the
-                # rows just appended), one decode-style query per token
-                bt = torch.tensor([r.pages + [0] * (self.max_pages - len(r.pages))], dtype=torch.int32,
-                                  device=dev).repeat(S, 1)
-                lens = (positions + 1).to(torch.int32)
-                o = self.cache.decode(li, qkv[:, :Hq * D].contiguous(), bt, lens, Hq)
+                # suffix after a cached prefix: the prefix and the rows just appended come out of the pages as contiguous
+                # bf16 rows (dequantised), and the new tokens run through the tensor-core attention kernel as the last S
+                # positions of a pos0 + S long sequence
+                if pages_dev is None:
+                    pages_dev = torch.tensor(r.pages, dtype=torch.int32, device=dev)
+                kk, vv = self.cache.gather(li, pages_dev, pos0 + S)
+                o, _ = F.attn_fwd(qkv, kk, vv, 1, S, Hq, Hkv, D, kv_len=pos0 + S)
             if mc.use_parallel_residual:
                 attn = self._lin(o, li, "o", w.o, getattr(w, "o_bias", None))
                 f, _ = _norm_fwd(mc, h, w.ffn_norm, getattr(w, "ffn_norm_bias", None))

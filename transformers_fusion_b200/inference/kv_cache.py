@@ -20,6 +20,7 @@ PAGE = 16
 MODES = {"bf16": 0, "fp8": 1, "q4": 2}
 
 _lib.register("tfb_kv_append", [c_p, c_ll, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_p])
+_lib.register("tfb_kv_gather", [c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_ll, c_i, c_i, c_i, c_ll, c_p])
 _lib.register("tfb_paged_decode", [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_ll, c_p, c_p, c_i, c_i, c_i,
                                    c_i, c_i, c_i, c_f, c_ll, c_p])
 
@@ -133,6 +134,22 @@ class PagedKVCache:
         check(_lib.lib().tfb_kv_append(src.data_ptr(), src.stride(0), k_col0, v_col0, slot_mapping.data_ptr(),
                                        kp.data.data_ptr(), ptr(kp.scale), vp.data.data_ptr(), ptr(vp.scale), T,
                                        self.Hkv, self.D, MODES[self.mode], self.num_pages * PAGE, stream()), "kv_append")
+
+    def gather(self, layer, pages, n):
+        """The first ``n`` cached tokens of one sequence (``pages``: its page list, int32 tensor) as contiguous bf16 rows
+        (k [n, Hkv*D], v [n, Hkv*D]), dequantised: the keys / values a prompt suffix attends over besides itself."""
+        kp, vp = self.k[layer], self.v[layer]
+        Hkv, D = self.Hkv, self.D
+        if not kp.data.is_cuda:
+            K, V = kp.dequant(), vp.dequant()
+            pg = pages[: (n + PAGE - 1) // PAGE].long()
+            return (K[pg].reshape(-1, Hkv * D)[:n].to(torch.bfloat16), V[pg].reshape(-1, Hkv * D)[:n].to(torch.bfloat16))
+        ok = torch.empty((n, Hkv * D), dtype=torch.bfloat16, device=kp.data.device)
+        ov = torch.empty_like(ok)
+        check(_lib.lib().tfb_kv_gather(kp.data.data_ptr(), ptr(kp.scale), vp.data.data_ptr(), ptr(vp.scale), pages.data_ptr(), n,
+                                       ok.data_ptr(), ov.data_ptr(), Hkv * D, Hkv, D, MODES[self.mode], self.num_pages * PAGE,
+                                       stream()), "kv_gather")
+        return ok, ov
 
     def decode(self, layer, q, block_table, seq_lens, Hq, scale=None, splits=None):
         """q [B, Hq*D] bf16 -> o [B, Hq*D] attending over the first seq_lens[b] cached tokens of each sequence."""

@@ -401,36 +401,46 @@ _lib.register("tfb_attn_fwd", [_lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_l
                                _lib.c_i, _lib.c_f, _lib.c_i, _lib.c_p, _lib.c_p])
 
 
+_lib.register("tfb_attn_fwd_kv", [_lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_i, _lib.c_p, _lib.c_ll,
+                                  _lib.c_i, _lib.c_p, _lib.c_ll, _lib.c_p, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i, _lib.c_i,
+                                  _lib.c_i, _lib.c_f, _lib.c_i, _lib.c_p, _lib.c_p])
+
+
 def _split_heads(buf, col0, n_heads, D, B, S):
     return buf[:, col0: col0 + n_heads * D].reshape(B, S, n_heads, D).permute(0, 2, 1, 3).float()
 
 
-def attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0=0, k_col0=0, v_col0=0):
-    """fp32 reference: returns (o [B*S, Hq*D], lse [B, Hq, S], probabilities)."""
+def attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0=0, k_col0=0, v_col0=0, kv_len=None):
+    """fp32 reference: returns (o [B*S, Hq*D], lse [B, Hq, S], probabilities).  ``kv_len`` >= S: k / v hold that many
+    rows per sequence and the queries are its last S positions."""
+    Skv = S if kv_len is None else kv_len
     Q = _split_heads(q, q_col0, Hq, D, B, S)
-    K = _split_heads(k, k_col0, Hkv, D, B, S).repeat_interleave(Hq // Hkv, 1)
-    V = _split_heads(v, v_col0, Hkv, D, B, S).repeat_interleave(Hq // Hkv, 1)
+    K = _split_heads(k, k_col0, Hkv, D, B, Skv).repeat_interleave(Hq // Hkv, 1)
+    V = _split_heads(v, v_col0, Hkv, D, B, Skv).repeat_interleave(Hq // Hkv, 1)
     s = (Q @ K.transpose(-1, -2)) * scale
     if causal:
-        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device=s.device).triu(1), float("-inf"))
+        s = s.masked_fill(torch.ones(S, Skv, dtype=torch.bool, device=s.device).triu(1 + Skv - S), float("-inf"))
     lse = torch.logsumexp(s, -1)
     P = torch.exp(s - lse[..., None])
     o = (P @ V).permute(0, 2, 1, 3).reshape(B * S, Hq * D)
     return o, lse, P
 
 
-def attn_fwd(q, k, v, B, S, Hq, Hkv, D, scale=None, causal=True, q_col0=0, k_col0=0, v_col0=0):
+def attn_fwd(q, k, v, B, S, Hq, Hkv, D, scale=None, causal=True, q_col0=0, k_col0=0, v_col0=0, kv_len=None):
     """q/k/v: [B*S, ld] bf16 buffers (may be one fused projection output; see column offsets).
-    Returns (o [B*S, Hq*D] bf16, lse [B, Hq, S] fp32)."""
+    Returns (o [B*S, Hq*D] bf16, lse [B, Hq, S] fp32).  ``kv_len`` > S: k / v are [B*kv_len, ld] and the S queries are
+    the last S positions of each sequence (a prompt suffix attending over a cached prefix and itself)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    Skv = S if kv_len is None else int(kv_len)
+    assert Skv >= S
     if not q.is_cuda:
-        o, lse, _ = attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0, k_col0, v_col0)
+        o, lse, _ = attn_ref(q, k, v, B, S, Hq, Hkv, D, scale, causal, q_col0, k_col0, v_col0, Skv)
         return o.to(q.dtype), lse
     o = torch.empty((B * S, Hq * D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
-    check(_lib.lib().tfb_attn_fwd(q.data_ptr(), q.stride(0), q_col0, k.data_ptr(), k.stride(0), k_col0, v.data_ptr(),
-                                  v.stride(0), v_col0, o.data_ptr(), o.stride(0), lse.data_ptr(), B, S, Hq, Hkv, D,
-                                  float(scale), int(causal), _lib.status_word(q.device).data_ptr(), stream()),
+    check(_lib.lib().tfb_attn_fwd_kv(q.data_ptr(), q.stride(0), q_col0, k.data_ptr(), k.stride(0), k_col0, v.data_ptr(),
+                                     v.stride(0), v_col0, o.data_ptr(), o.stride(0), lse.data_ptr(), B, S, Skv, Hq, Hkv, D,
+                                     float(scale), int(causal), _lib.status_word(q.device).data_ptr(), stream()),
           "attn_fwd")
     return o, lse
 

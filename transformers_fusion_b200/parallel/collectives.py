@@ -178,6 +178,9 @@ class SymmCollectives:
 
     def all_reduce(self, t: torch.Tensor, op="sum", algo="auto") -> torch.Tensor:
         """In place on ``t``.  ``algo``: one_shot | two_shot | auto (by size)."""
+        nb = t.numel() * t.element_size()
+        if algo == "auto" and nb <= self.one_shot_max_bytes and nb % 16 == 0 and t.data_ptr() % 16 == 0:
+            return self.all_reduce_ll(t, op, out=t)       # no staging copy, no barrier
         n = self._padded(t)
         st = self.stage.view(t.dtype, n)
         st[: t.numel()].copy_(t.reshape(-1))
