@@ -111,12 +111,13 @@ class ShardedEngine:
         # compute (peer loads by small CTAs that sit beside the GEMM's); "fused" = the copy CTAs of the GEMM that first
         # uses a weight pull it (no separate launch, but a GEMM whose every tile needs the whole weight - the input
         # gradient - then runs at the speed of its copy CTAs)
-        # "auto": inside the GEMM for a group of two (half of every weight is local and 12 copy CTAs keep up: measured
-        # 90.8 against 93.3 ms per step on the 8-layer 8B shape), the prefetch kernel for larger groups, where most of
-        # every weight is remote
+        # "auto" is the prefetch kernel: measured on the 8-layer 8B shape with a group of two, 84.9 ms per step against 90.0 ms
+        # with the gather inside the GEMM (whose wide products cannot use the grouped tile order, and whose input-gradient
+        # products wait for the whole weight); for larger groups most of every weight is remote and the copy CTAs of the
+        # GEMM fall further behind
         assert gather in ("auto", "prefetch", "fused")
         if gather == "auto":
-            gather = "fused" if mesh.dp <= 2 else "prefetch"
+            gather = "prefetch"
         self.gather_mode, self.ag_ctas = gather, ag_ctas
         self.step_count = 0
         self.dp_heap, self.tp_heap = dp_heap, tp_heap
