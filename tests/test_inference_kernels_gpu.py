@@ -13,10 +13,10 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("mode", ["bf16", "fp8", "q4"])
-@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 64), (4, 1, 128), (4, 4, 64)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 64), (4, 1, 128), (4, 4, 64), (8, 1, 128), (4, 2, 64)])
 def test_paged_append_and_decode(mode, Hq, Hkv, D):
-    B, pages = 5, 64
-    lens = torch.tensor([1, 17, 100, 255, 33], dtype=torch.int32)
+    B, pages = 6, 112
+    lens = torch.tensor([1, 17, 100, 255, 33, 700], dtype=torch.int32)
     ld = (Hq + 2 * Hkv) * D
     caches = {d: PagedKVCache(1, pages, Hkv, D, mode, d) for d in ("cpu", "cuda")}
     max_pages = (int(lens.max()) + PAGE - 1) // PAGE

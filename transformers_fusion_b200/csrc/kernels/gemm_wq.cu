@@ -31,6 +31,7 @@
 //
 // Reference counterparts: the CPU quantised matmul kernels (src/kernel/kernel_quant8.cpp, kernel_quant4.cpp, kernel_tl.cpp
 // ternary lookup, kernel_q3 / q6 / q12 / q24), INT8Inference / FP8Inference (src/inference/inference_lowprec.cpp).
+#include <algorithm>
 #include "tfb_host.h"
 #include "tfb_ptx.cuh"
 
@@ -461,6 +462,41 @@ TFB_API int tfb_wq_dequant(const void* wq, const void* scales, int fmt, int grou
   }
   const int rc = int(cudaGetLastError());
   return rc ? -1000 - rc : 0;
+}
+
+namespace tfb {
+// fp32 split-K sums -> bf16 output, and the workspace goes back to zero for its next use (one launch instead of a memset
+// before the product and a cast after it)
+__global__ void __launch_bounds__(256) wq_finalize_kernel(float* __restrict__ ws, long long ldw, __nv_bfloat16* __restrict__ C,
+                                                          long long ldc, int M, int N, int W4) {
+  tfb::pdl_sync();
+  const long long total = (long long)M * W4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / W4), c = int(i % W4) * 4;
+    float4* src = reinterpret_cast<float4*>(ws + (long long)r * ldw + c);
+    const float4 v = *src;
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < N) {
+      uint2 o;
+      o.x = pack_bf16(v.x, v.y);
+      o.y = pack_bf16(v.z, v.w);
+      *reinterpret_cast<uint2*>(C + (long long)r * ldc + c) = o;
+    }
+  }
+}
+}  // namespace tfb
+
+// C [M, ldc] bf16 <- ws [M, ldw] fp32 for the first N columns, and ws <- 0 over its first `width` columns (the padded
+// width the product accumulated into).  N, width, ldw, ldc multiples of 4; N <= width <= ldw.
+TFB_API int tfb_wq_finalize(float* ws, long long ldw, void* C, long long ldc, int M, int N, int width, void* stream) {
+  if (M <= 0 || N <= 0 || (N & 3) || (width & 3) || width < N || width > ldw || (ldw & 3) || (ldc & 3) ||
+      (reinterpret_cast<uintptr_t>(ws) & 15) || (reinterpret_cast<uintptr_t>(C) & 7))
+    return TFB_ERR_ARG;
+  const long long total = (long long)M * (width / 4);
+  const int grid = int(std::min<long long>((total + 255) / 256, 148 * 8));
+  tfb::launch_k(tfb::wq_finalize_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), ws, ldw, static_cast<__nv_bfloat16*>(C), ldc, M,
+                N, width / 4);
+  return int(cudaGetLastError());
 }
 
 // A [M, lda] bf16 (K % 64 == 0, N % 128 == 0: the packer pads).  wq / scales in the tile-major layout described at the top.

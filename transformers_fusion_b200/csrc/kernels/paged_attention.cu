@@ -19,6 +19,8 @@
 // mask), Q4KVCache 4-bit blocks (src/model/kv_cache_quant4.cpp:207-362), flash_decoding
 // (src/inference/inference_kv.cpp:141-205).
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <cuda_fp16.h>
 
 #include "tfb_host.h"
@@ -301,9 +303,24 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
             const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(src));
             vv[u][0] = a.x; vv[u][DL - 1] = a.y;
           }
-        } else {
+        } else if (MODE == KV_FP8) {
+          // the lane's DL consecutive values in one load (4 or 2 bytes) + the row's scale
+          const float sc = static_cast<const float*>(vpool.scale)[row];
+          const uint8_t* src = static_cast<const uint8_t*>(vpool.data) + row * D + lane * DL;
+          uint32_t w;
+          if (DL == 4) w = *reinterpret_cast<const uint32_t*>(src);
+          else w = *reinterpret_cast<const uint16_t*>(src);
 #pragma unroll
-          for (int j = 0; j < DL; ++j) vv[u][j] = load_elem<MODE, D>(vpool, row, lane * DL + j);
+          for (int j = 0; j < DL; ++j) vv[u][j] = e4m3_to_f32(uint8_t(w >> (8 * j))) * sc;
+        } else {
+          // 4-bit: DL values = DL / 2 bytes, all inside one 32-element scale group
+          const float sc = __half2float(static_cast<const __half*>(vpool.scale)[row * (D / 32) + (lane * DL) / 32]);
+          const uint8_t* src = static_cast<const uint8_t*>(vpool.data) + row * (D / 2) + (lane * DL) / 2;
+          uint32_t w;
+          if (DL == 4) w = *reinterpret_cast<const uint16_t*>(src);
+          else w = *src;
+#pragma unroll
+          for (int j = 0; j < DL; ++j) vv[u][j] = float(int((w >> (4 * j)) & 15u) - 8) * sc;
         }
       }
 #pragma unroll
@@ -367,6 +384,318 @@ __global__ void paged_combine_kernel(const float* __restrict__ acc, const float*
     }
     o[(long long)b * ldo + h * D + d] = __float2bfloat16(L > 0.f ? v / L : 0.f);
   }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode on the tensor cores
+//
+// The kernel above spends ~1500 thread instructions per cached token and kv head (one K row per thread: 128 loads from
+// shared memory and 512 FMAs for four query heads, then a warp walks the V rows) and ends up issue- and latency-bound at
+// 0.3 of the copy bandwidth.  Here the G query heads of a kv head are the (zero-padded) 16 rows of an mma.sync
+// m16n8k16 tile: S = Q K^T and O += P V cost 64 tensor instructions per 32 cached tokens, and what is left is moving
+// the rows.  Each of the four warps of a CTA owns every fourth 32-token chunk of the split's range: it brings the
+// chunk's K and V rows into its private shared-memory tile (cp.async for bf16 pools; load, dequantise, store for the
+// fp8 / 4-bit pools), runs the two products with ldmatrix-fed fragments, and keeps its own running max / sum / output;
+// the four partial results are merged once at the end.  Nothing is shared between the warps while they stream, so
+// there is no CTA barrier in the loop; several CTAs per SM keep enough loads in flight.
+// (mma.sync rather than tcgen05: with at most 8 query rows per kv head a 128-row UMMA tile would be 94 % padding.)
+// ------------------------------------------------------------------------------------------------
+constexpr int TC_THREADS = 128;
+constexpr int TC_CHUNK = 32;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void st_shared_u4(uint32_t dst, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// byte offset of 16-byte chunk c of row r in a [rows][D] bf16 tile with rows padded by 16 bytes: a row is one contiguous
+// piece (the target of one bulk copy), and eight consecutive rows at one chunk index fall into eight different bank groups
+// (row pitch = 17 or 9 chunks), which is what ldmatrix reads
+template <int D>
+__device__ __forceinline__ uint32_t tc_off(int r, int c) {
+  return uint32_t(r * (D * 2 + 16) + (c << 4));
+}
+
+// rows t0 .. t0 + 31 (t0 a multiple of 16: two pages) of one sequence's cache, kv head hk -> the warp's [32][D] bf16 tile;
+// rows from `nvalid` on are zero.  bf16 pools: lane r sends row r as one bulk copy that completes on the warp's mbarrier
+// (the caller has armed it with the byte count); fp8 / 4-bit pools: 16-byte loads, conversion in registers, 16-byte stores.
+template <int MODE, int D>
+__device__ __forceinline__ void tc_stage(const KvPool& pool, const int* __restrict__ bt, int t0, int nvalid, int hk, int Hkv,
+                                         uint32_t tile, int lane, uint32_t bar) {
+  auto page_of = [&](int which) -> long long {
+    long long page = bt[t0 / PAGE + which];
+    TFB_BOUNDS(pool.rows == 0 || (page >= 0 && (page + 1) * PAGE <= pool.rows), 52, page, pool.rows / PAGE);
+#ifdef TFB_BOUNDS_CHECK
+    if (pool.rows != 0 && (page < 0 || (page + 1) * PAGE > pool.rows)) page = 0;
+#endif
+    return page;
+  };
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  if (MODE == KV_BF16) {
+    const int r = lane;
+    if (r < nvalid) {
+      const long long row = (page_of(r >> 4) * PAGE + (r & 15)) * Hkv + hk;
+      bulk_load(tile + tc_off<D>(r, 0), static_cast<const __nv_bfloat16*>(pool.data) + row * D, D * 2, bar);
+    } else {
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) st_shared_u4(tile + tc_off<D>(r, c), zero);
+    }
+    return;
+  }
+  const long long pg0 = page_of(0), pg1 = nvalid > PAGE ? page_of(1) : 0;
+  auto row_of = [&](int r) -> long long { return ((r < PAGE ? pg0 : pg1) * PAGE + (r & 15)) * Hkv + hk; };
+  if (MODE == KV_FP8) {
+    constexpr int UPR = D / 16;                 // 16-byte loads (16 values) per row
+    constexpr int N = TC_CHUNK * UPR / 32;      // loads per lane
+    uint4 raw[N];
+    float sc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int id = lane + 32 * j, r = id / UPR, u = id % UPR;
+      raw[j] = zero;
+      sc[j] = 0.f;
+      if (r < nvalid) {
+        const long long row = row_of(r);
+        raw[j] = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * D + u * 16);
+        sc[j] = static_cast<const float*>(pool.scale)[row];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int id = lane + 32 * j, r = id / UPR, u = id % UPR;
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw[j]);
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) w[q] = pack_bf16(e4m3_to_f32(b[2 * q]) * sc[j], e4m3_to_f32(b[2 * q + 1]) * sc[j]);
+      st_shared_u4(tile + tc_off<D>(r, 2 * u), make_uint4(w[0], w[1], w[2], w[3]));
+      st_shared_u4(tile + tc_off<D>(r, 2 * u + 1), make_uint4(w[4], w[5], w[6], w[7]));
+    }
+  } else {
+    constexpr int UPR = D / 32;                 // 16-byte loads (32 values, one scale group) per row
+    constexpr int N = TC_CHUNK * UPR / 32;
+    uint4 raw[N];
+    float sc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int id = lane + 32 * j, r = id / UPR, u = id % UPR;
+      raw[j] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);   // code 8 = value 0
+      sc[j] = 0.f;
+      if (r < nvalid) {
+        const long long row = row_of(r);
+        raw[j] = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(pool.data) + row * (D / 2) + u * 16);
+        sc[j] = __half2float(static_cast<const __half*>(pool.scale)[row * (D / 32) + u]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const int id = lane + 32 * j, r = id / UPR, u = id % UPR;
+      const uint32_t words[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {             // one 32-bit word = eight codes = one output chunk
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          // code -> float without an integer conversion: 2^23 + code as bits, minus (2^23 + 8)
+          const float lo = __uint_as_float(0x4B000000u | ((words[c] >> (8 * q)) & 15u)) - 8388616.f;
+          const float hi = __uint_as_float(0x4B000000u | ((words[c] >> (8 * q + 4)) & 15u)) - 8388616.f;
+          w[q] = pack_bf16(lo * sc[j], hi * sc[j]);
+        }
+        st_shared_u4(tile + tc_off<D>(r, 4 * u + c), make_uint4(w[0], w[1], w[2], w[3]));
+      }
+    }
+  }
+}
+
+template <int MODE, int D>
+__global__ void __launch_bounds__(TC_THREADS) paged_decode_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, long long ldq, KvPool kpool, KvPool vpool, const int* __restrict__ block_table,
+    int max_pages, const int* __restrict__ seq_lens, float* __restrict__ acc_out, float* __restrict__ ml_out, int Hq, int Hkv,
+    int G, int splits, float scale, int* status) {
+  tfb::pdl_sync();
+  extern __shared__ __align__(128) uint8_t tc_smem[];
+  constexpr int ROWB = D * 2 + 16;                 // padded row pitch (see tc_off)
+  constexpr int TILEB = TC_CHUNK * ROWB;
+  constexpr int CPR = D / 8;
+  constexpr int KS = D / 16;       // k steps of S = Q K^T
+  constexpr int NBD = D / 8;       // n blocks of O
+  const int b = blockIdx.x, hk = blockIdx.y, sp_idx = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t sQ = smem_u32(tc_smem);
+  const uint32_t sK = sQ + 16 * ROWB + warp * 2 * TILEB, sV = sK + TILEB;
+  const uint32_t bar = sQ + 16 * ROWB + (TC_THREADS / 32) * 2 * TILEB + warp * 8;   // one mbarrier per warp (bf16 pools)
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tc_smem + 16 * ROWB + (TC_THREADS / 32) * 2 * TILEB + 64);
+  if (MODE == KV_BF16 && lane == 0) {
+    mbar_init(bar, 1);
+    if (warp == 0) *abort_flag = 0;
+    mbar_fence_init();
+  }
+  const int len = seq_lens[b];
+  const int per = ((len + splits - 1) / splits + PAGE - 1) / PAGE * PAGE;
+  const int t_begin = sp_idx * per, t_end = min(len, t_begin + per);
+  const int* bt = block_table + (long long)b * max_pages;
+
+  // the G query heads of this kv head as rows 0 .. G-1 of a 16-row tile
+  for (int i = tid; i < 16 * CPR; i += TC_THREADS) {
+    const int r = i / CPR, c = i % CPR;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < G) v = *reinterpret_cast<const uint4*>(q + (long long)b * ldq + (hk * G + r) * D + c * 8);
+    st_shared_u4(sQ + tc_off<D>(r, c), v);
+  }
+  __syncthreads();
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
+    ldsm_x4(sQ + tc_off<D>(r, c), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+  }
+  float o[NBD][4];
+#pragma unroll
+  for (int n = 0; n < NBD; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;          // of row lane / 4 (log2 units), l summed over this thread's columns
+  const float sl2 = scale * 1.4426950408889634f;
+
+  uint32_t phase = 0;
+  for (int t0 = t_begin + warp * TC_CHUNK; t0 < t_end; t0 += (TC_THREADS / 32) * TC_CHUNK) {
+    const int nvalid = min(TC_CHUNK, t_end - t0);
+    if (MODE == KV_BF16) {
+      if (lane == 0) mbar_expect_tx(bar, uint32_t(nvalid) * D * 2 * 2);
+      __syncwarp();
+    }
+    tc_stage<MODE, D>(kpool, bt, t0, nvalid, hk, Hkv, sK, lane, bar);
+    tc_stage<MODE, D>(vpool, bt, t0, nvalid, hk, Hkv, sV, lane, bar);
+    if (MODE == KV_BF16) {
+      // bounded: a copy that never lands sets the status word and the warp leaves the loop (its partial result is wrong,
+      // the host raises from the status word)
+      if (!mbar_wait_warp(bar, phase, abort_flag, status, ST_TIMEOUT_FULL)) break;
+      phase ^= 1u;
+    }
+    __syncwarp();
+    // ---- S = Q K^T: four blocks of eight tokens ----
+    float sc[TC_CHUNK / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < TC_CHUNK / 8; ++nb) {
+      sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < KS / 2; ++k2) {
+        uint32_t k0, k1, k2r, k3;
+        ldsm_x4(sK + tc_off<D>(nb * 8 + (lane & 7), k2 * 4 + (lane >> 3)), k0, k1, k2r, k3);
+        mma_bf16_16816(sc[nb], qa[2 * k2], k0, k1);
+        mma_bf16_16816(sc[nb], qa[2 * k2 + 1], k2r, k3);
+      }
+    }
+    // ---- online softmax of row lane / 4 (this thread: columns nb * 8 + (lane & 3) * 2 + {0, 1}) ----
+    float mx = m_run;
+#pragma unroll
+    for (int nb = 0; nb < TC_CHUNK / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int tok = nb * 8 + (lane & 3) * 2 + e;
+        const float v = tok < nvalid ? sc[nb][e] * sl2 : -INFINITY;
+        sc[nb][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mx);
+    m_run = mx;
+    l_run *= alpha;
+    uint32_t pa[TC_CHUNK / 16][4];
+#pragma unroll
+    for (int nb = 0; nb < TC_CHUNK / 8; ++nb) {
+      const float p0 = exp2f(sc[nb][0] - mx), p1 = exp2f(sc[nb][1] - mx);
+      l_run += p0 + p1;
+      pa[nb >> 1][(nb & 1) * 2] = pack_bf16(p0, p1);     // rows 0-7 of the A tile; rows 8-15 (padding) stay zero
+      pa[nb >> 1][(nb & 1) * 2 + 1] = 0u;
+    }
+#pragma unroll
+    for (int n = 0; n < NBD; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
+    // ---- O += P V ----
+#pragma unroll
+    for (int kk = 0; kk < TC_CHUNK / 16; ++kk) {
+#pragma unroll
+      for (int n2 = 0; n2 < NBD / 2; ++n2) {
+        uint32_t v0, v1, v2, v3;
+        ldsm_x4_t(sV + tc_off<D>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * n2 + (lane >> 4)), v0, v1, v2, v3);
+        mma_bf16_16816(o[2 * n2], pa[kk], v0, v1);
+        mma_bf16_16816(o[2 * n2 + 1], pa[kk], v2, v3);
+      }
+    }
+    __syncwarp();      // every lane is done with the tiles before they are refilled
+    if (MODE == KV_BF16) fence_proxy_async_smem();   // ... by bulk copies, which write through the async proxy
+  }
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  // ---- merge the four warps (the staging area is free now) ----
+  __syncthreads();
+  float* red_m = reinterpret_cast<float*>(tc_smem);          // [4][8]
+  float* red_l = red_m + 32;                                 // [4][8]
+  float* red_o = red_l + 32;                                 // [4][8][D]
+  const int row = lane >> 2;
+  if ((lane & 3) == 0) {
+    red_m[warp * 8 + row] = m_run;
+    red_l[warp * 8 + row] = l_run;
+  }
+#pragma unroll
+  for (int n = 0; n < NBD; ++n) {
+    float* dst = red_o + (warp * 8 + row) * D + n * 8 + (lane & 3) * 2;
+    dst[0] = o[n][0];
+    dst[1] = o[n][1];
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += TC_THREADS) {
+    const int g = i / D, d = i % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 8 + g]);
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = red_m[w * 8 + g];
+      if (mw != -INFINITY) v += red_o[(w * 8 + g) * D + d] * exp2f(mw - M);
+    }
+    const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
+    acc_out[base * D + d] = v;
+  }
+  if (tid < G) {
+    const int g = tid;
+    float M = -INFINITY, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 8 + g]);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = red_m[w * 8 + g];
+      if (mw != -INFINITY) L += red_l[w * 8 + g] * exp2f(mw - M);
+    }
+    const long long base = (((long long)b * Hq + hk * G + g) * splits + sp_idx);
+    ml_out[base * 2] = M * 0.6931471805599453f;      // back to natural-log units for the combine kernel
+    ml_out[base * 2 + 1] = L;
+  }
+}
+
+template <int MODE, int D>
+static int launch_decode_mma(dim3 grid, cudaStream_t st, const __nv_bfloat16* q, long long ldq, KvPool k, KvPool v, const int* bt,
+                             int max_pages, const int* lens, float* acc, float* ml, int Hq, int Hkv, int G, int splits, float scale,
+                             int* status) {
+  constexpr int SMEM = (16 + (TC_THREADS / 32) * 2 * TC_CHUNK) * (D * 2 + 16) + 128;   // Q tile, four K/V tile pairs, barriers
+  static_assert(SMEM >= int(sizeof(float)) * (64 + 4 * 8 * D), "the merge buffers reuse the staging area");
+  static DeviceOnce once;
+  auto kern = paged_decode_mma_kernel<MODE, D>;
+  if (int e = ensure_dyn_smem(once, kern, SMEM)) return e;
+  tfb::launch_k(kern, grid, TC_THREADS, SMEM, st, q, ldq, k, v, bt, max_pages, lens, acc, ml, Hq, Hkv, G, splits, scale, status);
+  return int(cudaGetLastError());
 }
 
 template <int MODE, int D>
@@ -508,10 +837,11 @@ TFB_API int tfb_kv_append(const void* src, long long ld, int k_col0, int v_col0,
 }
 
 // q: [B, ldq] bf16 (query head h at column h*D).  acc_ws: fp32 [B*Hq*splits*D], ml_ws: fp32 [B*Hq*splits*2].
+// status: the device status word (a bulk copy that does not land within the wait bound is reported there).
 TFB_API int tfb_paged_decode(const void* q, long long ldq, void* k_data, void* k_scale, void* v_data, void* v_scale,
                              const int* block_table, int max_pages, const int* seq_lens, void* o, long long ldo,
                              float* acc_ws, float* ml_ws, int B, int Hq, int Hkv, int D, int splits, int mode,
-                             float scale, long long pool_rows, void* stream) {
+                             float scale, long long pool_rows, int* status, void* stream) {
   if ((D != 64 && D != 128) || Hkv <= 0 || Hq % Hkv || splits < 1) return TFB_ERR_ARG;
   const int G = Hq / Hkv;
   KvPool kp{k_data, k_scale, pool_rows}, vp{v_data, v_scale, pool_rows};
@@ -519,8 +849,16 @@ TFB_API int tfb_paged_decode(const void* q, long long ldq, void* k_data, void* k
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto Q = static_cast<const __nv_bfloat16*>(q);
   int rc;
+  // tensor-core kernel by default (up to 8 query heads per kv head, q rows 16-byte aligned); TFB_PAGED_DECODE=simt
+  // selects the CUDA-core kernel
+  static const bool simt = [] { const char* e = getenv("TFB_PAGED_DECODE"); return e && !strcmp(e, "simt"); }();
+  const bool mma_ok = !simt && G <= 8 && (ldq % 8) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
 #define TFB_GO(MODE)                                                                                                  \
-  rc = (D == 64) ? launch_decode_g<MODE, 64>(G, grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,   \
+  rc = mma_ok ? ((D == 64) ? launch_decode_mma<MODE, 64>(grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws, ml_ws, \
+                                                         Hq, Hkv, G, splits, scale, status)                           \
+                           : launch_decode_mma<MODE, 128>(grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,       \
+                                                          ml_ws, Hq, Hkv, G, splits, scale, status))                  \
+     : (D == 64) ? launch_decode_g<MODE, 64>(G, grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,   \
                                              ml_ws, Hq, Hkv, splits, scale)                                           \
                  : launch_decode_g<MODE, 128>(G, grid, st, Q, ldq, kp, vp, block_table, max_pages, seq_lens, acc_ws,  \
                                               ml_ws, Hq, Hkv, splits, scale)

@@ -22,7 +22,7 @@ MODES = {"bf16": 0, "fp8": 1, "q4": 2}
 _lib.register("tfb_kv_append", [c_p, c_ll, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_p])
 _lib.register("tfb_kv_gather", [c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_ll, c_i, c_i, c_i, c_ll, c_p])
 _lib.register("tfb_paged_decode", [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_ll, c_p, c_p, c_i, c_i, c_i,
-                                   c_i, c_i, c_i, c_f, c_ll, c_p])
+                                   c_i, c_i, c_i, c_f, c_ll, c_p, c_p])
 
 
 class PageAllocator:
@@ -171,7 +171,9 @@ class PagedKVCache:
             return out.to(q.dtype)
         if splits is None:
             max_len = block_table.shape[1] * PAGE
-            splits = max(1, min(16, (2 * 148) // max(1, B * Hkv), max_len // 256))
+            # enough CTAs (128 threads each) for about eight per SM: the kernel is latency-bound per CTA (one K row per
+            # thread, then a serial walk over the tile's V rows), so parallelism across CTAs is what hides it
+            splits = max(1, min(16, (8 * 148) // max(1, B * Hkv), max_len // 128))
         key = (B, Hq, splits)
         if key not in self._ws:
             self._ws[key] = (torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device),
@@ -183,5 +185,6 @@ class PagedKVCache:
                                           vp.data.data_ptr(), ptr(vp.scale), block_table.data_ptr(),
                                           block_table.shape[1], seq_lens.data_ptr(), o.data_ptr(), o.stride(0),
                                           acc.data_ptr(), ml.data_ptr(), B, Hq, Hkv, D, splits, MODES[self.mode],
-                                          float(scale), self.num_pages * PAGE, stream()), "paged_decode", 2)
+                                          float(scale), self.num_pages * PAGE, _lib.status_word(q.device).data_ptr(),
+                                          stream()), "paged_decode", 2)
         return o

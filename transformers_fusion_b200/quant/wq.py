@@ -23,6 +23,7 @@ BITS = {0: 8, 1: 4, 2: 8, 3: 4, 4: 2}
 _E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
 
 _lib.register("tfb_gemm_wq", [c_p, c_ll, c_p, c_p, c_i, c_i, c_p, c_ll, c_i, c_i, c_i, c_p, c_i, c_i, c_p, c_p])
+_lib.register("tfb_wq_finalize", [c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_p])
 _lib.register("tfb_wq_dequant", [c_p, c_p, c_i, c_i, c_p, c_ll, c_i, c_i, c_p])
 
 
@@ -153,6 +154,9 @@ def dequant_bf16(pw: PackedWeight) -> torch.Tensor:
     return out
 
 
+_SPLIT_WS = {}
+
+
 def gemm_wq(x: torch.Tensor, pw: PackedWeight, bias: Optional[torch.Tensor] = None, splits: int = 0,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y [M, N] = x [M, K] @ dequant(pw)^T (+ bias).  bf16 in / out.  M <= 16 (decode): fused-dequant kernel with the deep
@@ -190,7 +194,11 @@ def _gemm_wq(x, pw, bias, splits, dst):
     tiles = ((M + 127) // 128) * (pw.Np // 128)
     use_split = splits > 1 or (splits == 0 and tiles * 2 <= 148 and pw.Kp >= 512)
     if use_split:
-        out = torch.zeros((M, pw.Np), dtype=torch.float32, device=x.device)
+        # the fp32 workspace of this shape is kept zeroed between uses: the finalize kernel clears what it reads
+        key = (x.device, torch.cuda.current_stream(x.device).cuda_stream, M, pw.Np)
+        out = _SPLIT_WS.get(key)
+        if out is None:
+            out = _SPLIT_WS[key] = torch.zeros((M, pw.Np), dtype=torch.float32, device=x.device)
     elif dst is not None and pw.Np == pw.N and dst.is_contiguous() and dst.dtype == torch.bfloat16:
         out = dst
     else:
@@ -206,10 +214,18 @@ def _gemm_wq(x, pw, bias, splits, dst):
         check(rc, "gemm_wq")
     if out.dtype == torch.bfloat16:
         return out if out is dst else out[:, : pw.N]
-    if dst is not None:                       # the fp32 split-K sums are rounded straight into the caller's buffer
-        dst.copy_(out[:, : pw.N])
-        return dst
-    return out[:, : pw.N].to(torch.bfloat16)
+    # the fp32 split-K sums are rounded straight into the caller's buffer (or a new one) and the workspace is cleared
+    if dst is None or dst.dtype != torch.bfloat16 or dst.stride(-1) != 1 or dst.stride(0) % 4 or dst.data_ptr() % 8 or pw.N % 4:
+        y = torch.empty((M, pw.N), dtype=torch.bfloat16, device=x.device) if pw.N % 4 == 0 else None
+        if y is None:                          # odd widths: plain cast, explicit clear
+            y = out[:, : pw.N].to(torch.bfloat16)
+            out.zero_()
+            return y
+    else:
+        y = dst
+    check(_lib.lib().tfb_wq_finalize(out.data_ptr(), out.stride(0), y.data_ptr(), y.stride(0), M, pw.N, pw.Np, stream()),
+          "wq_finalize")
+    return y
 
 
 class QuantLinear(torch.nn.Module):
