@@ -534,10 +534,12 @@ __global__ void __launch_bounds__(TC_THREADS) paged_decode_mma_kernel(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t sQ = smem_u32(tc_smem);
   const uint32_t sK = sQ + 16 * ROWB + warp * 2 * TILEB, sV = sK + TILEB;
-  const uint32_t bar = sQ + 16 * ROWB + (TC_THREADS / 32) * 2 * TILEB + warp * 8;   // one mbarrier per warp (bf16 pools)
+  // bf16 pools: two mbarriers per warp (K tile, V tile)
+  const uint32_t bar_k = sQ + 16 * ROWB + (TC_THREADS / 32) * 2 * TILEB + warp * 16, bar_v = bar_k + 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tc_smem + 16 * ROWB + (TC_THREADS / 32) * 2 * TILEB + 64);
   if (MODE == KV_BF16 && lane == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
     if (warp == 0) *abort_flag = 0;
     mbar_fence_init();
   }
@@ -566,34 +568,77 @@ __global__ void __launch_bounds__(TC_THREADS) paged_decode_mma_kernel(
   float m_run = -INFINITY, l_run = 0.f;          // of row lane / 4 (log2 units), l summed over this thread's columns
   const float sl2 = scale * 1.4426950408889634f;
 
-  uint32_t phase = 0;
-  for (int t0 = t_begin + warp * TC_CHUNK; t0 < t_end; t0 += (TC_THREADS / 32) * TC_CHUNK) {
-    const int nvalid = min(TC_CHUNK, t_end - t0);
-    if (MODE == KV_BF16) {
-      if (lane == 0) mbar_expect_tx(bar, uint32_t(nvalid) * D * 2 * 2);
-      __syncwarp();
+  // bf16 pools: lane r sends row r of a chunk as one bulk copy (`page`: the lane's page of that chunk), rows past the end
+  // are zeroed.  The K tile is refilled as soon as S is computed and the V tile as soon as O is updated, so the next
+  // chunk's rows travel while this chunk's softmax / products run, and the page indices are fetched one chunk ahead.
+  auto issue_rows = [&](const KvPool& pool, long long page, int nv, uint32_t tile, uint32_t bar) {
+    if (lane == 0) mbar_expect_tx(bar, uint32_t(nv) * D * 2);
+    __syncwarp();
+    if (lane < nv) {
+      const long long row = (page * PAGE + (lane & 15)) * Hkv + hk;
+      bulk_load(tile + tc_off<D>(lane, 0), static_cast<const __nv_bfloat16*>(pool.data) + row * D, D * 2, bar);
+    } else {
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) st_shared_u4(tile + tc_off<D>(lane, c), zero);
     }
-    tc_stage<MODE, D>(kpool, bt, t0, nvalid, hk, Hkv, sK, lane, bar);
-    tc_stage<MODE, D>(vpool, bt, t0, nvalid, hk, Hkv, sV, lane, bar);
+  };
+  auto page_for = [&](int t0c, int nv) -> long long {
+    long long page = lane < nv ? bt[t0c / PAGE + (lane >> 4)] : 0;
+    TFB_BOUNDS(kpool.rows == 0 || (page >= 0 && (page + 1) * PAGE <= kpool.rows), 52, page, kpool.rows / PAGE);
+#ifdef TFB_BOUNDS_CHECK
+    if (kpool.rows != 0 && (page < 0 || (page + 1) * PAGE > kpool.rows)) page = 0;
+#endif
+    return page;
+  };
+  // after a wait that ran out: give the copies still in flight a bounded time to land before shared memory is reused
+  auto drain = [&](uint32_t ph) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!(mbar_try_wait(bar_k, ph) && mbar_try_wait(bar_v, ph))) {
+      if (globaltimer_ns() - t0 > 2000000ull) { report(status, ST_TIMEOUT_DRAIN); break; }
+    }
+  };
+  constexpr int STEP = (TC_THREADS / 32) * TC_CHUNK;
+  uint32_t phase = 0;
+  const int t_first = t_begin + warp * TC_CHUNK;
+  if (MODE == KV_BF16 && t_first < t_end) {
+    const int nv = min(TC_CHUNK, t_end - t_first);
+    const long long pg = page_for(t_first, nv);
+    issue_rows(kpool, pg, nv, sK, bar_k);
+    issue_rows(vpool, pg, nv, sV, bar_v);
+  }
+  for (int t0 = t_first; t0 < t_end; t0 += STEP) {
+    const int nvalid = min(TC_CHUNK, t_end - t0);
+    const int nv_next = min(TC_CHUNK, t_end - (t0 + STEP));         // <= 0: this is the warp's last chunk
+    long long pg_next = 0;
     if (MODE == KV_BF16) {
+      if (nv_next > 0) pg_next = page_for(t0 + STEP, nv_next);
       // bounded: a copy that never lands sets the status word and the warp leaves the loop (its partial result is wrong,
       // the host raises from the status word)
-      if (!mbar_wait_warp(bar, phase, abort_flag, status, ST_TIMEOUT_FULL)) break;
-      phase ^= 1u;
+      if (!mbar_wait_warp(bar_k, phase, abort_flag, status, ST_TIMEOUT_FULL)) { drain(phase); break; }
+    } else {
+      tc_stage<MODE, D>(kpool, bt, t0, nvalid, hk, Hkv, sK, lane, 0u);
+      tc_stage<MODE, D>(vpool, bt, t0, nvalid, hk, Hkv, sV, lane, 0u);
     }
     __syncwarp();
-    // ---- S = Q K^T: four blocks of eight tokens ----
+    // ---- S = Q K^T: four blocks of eight tokens; the four accumulators are independent, so they are interleaved ----
     float sc[TC_CHUNK / 8][4];
 #pragma unroll
-    for (int nb = 0; nb < TC_CHUNK / 8; ++nb) {
-      sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+    for (int nb = 0; nb < TC_CHUNK / 8; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
 #pragma unroll
-      for (int k2 = 0; k2 < KS / 2; ++k2) {
+    for (int k2 = 0; k2 < KS / 2; ++k2) {
+#pragma unroll
+      for (int nb = 0; nb < TC_CHUNK / 8; ++nb) {
         uint32_t k0, k1, k2r, k3;
         ldsm_x4(sK + tc_off<D>(nb * 8 + (lane & 7), k2 * 4 + (lane >> 3)), k0, k1, k2r, k3);
         mma_bf16_16816(sc[nb], qa[2 * k2], k0, k1);
         mma_bf16_16816(sc[nb], qa[2 * k2 + 1], k2r, k3);
       }
+    }
+    if (MODE == KV_BF16 && nv_next > 0) {      // the K tile is free: fetch the next chunk's keys
+      __syncwarp();
+      fence_proxy_async_smem();
+      issue_rows(kpool, pg_next, nv_next, sK, bar_k);
     }
     // ---- online softmax of row lane / 4 (this thread: columns nb * 8 + (lane & 3) * 2 + {0, 1}) ----
     float mx = m_run;
@@ -623,6 +668,10 @@ __global__ void __launch_bounds__(TC_THREADS) paged_decode_mma_kernel(
 #pragma unroll
     for (int n = 0; n < NBD; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
     // ---- O += P V ----
+    if (MODE == KV_BF16) {
+      if (!mbar_wait_warp(bar_v, phase, abort_flag, status, ST_TIMEOUT_FULL)) { drain(phase); break; }
+      phase ^= 1u;
+    }
 #pragma unroll
     for (int kk = 0; kk < TC_CHUNK / 16; ++kk) {
 #pragma unroll
@@ -634,7 +683,10 @@ __global__ void __launch_bounds__(TC_THREADS) paged_decode_mma_kernel(
       }
     }
     __syncwarp();      // every lane is done with the tiles before they are refilled
-    if (MODE == KV_BF16) fence_proxy_async_smem();   // ... by bulk copies, which write through the async proxy
+    if (MODE == KV_BF16 && nv_next > 0) {            // ... by bulk copies, which write through the async proxy
+      fence_proxy_async_smem();
+      issue_rows(vpool, pg_next, nv_next, sV, bar_v);
+    }
   }
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
