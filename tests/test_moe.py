@@ -167,3 +167,45 @@ def test_variant_models_route_by_their_rule():
         if kw.get("capacity_policy"):
             assert int(blk.last_sel.sum(0).max()) <= 4            # ceil(0.5 * 32 * 2 / 8)
     assert len(set(round(v, 5) for v in outs.values())) == len(outs)     # the rules really differ from plain top-k
+
+
+def test_structural_and_quantised_output_variants():
+    """PRODUCT_KEY (two independently routed halves), ATTENTION_MOE (product of two projections as routing score),
+    LOWRANK_MOE (bottleneck in front of router and experts), DOMAIN_MOE (classifier-weighted expert groups) and the
+    variants that snap the mixture to fixed levels: each trains (finite loss, gradients on its own parameters and on the
+    experts of every group) and differs from plain top-k."""
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.moe import MoEAllConfig, create_moe_variant
+    base = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(1))
+    ces = {}
+    for name in ("SPARSE_TOPK", "PRODUCT_KEY", "ATTENTION_MOE", "LOWRANK_MOE", "DOMAIN_MOE", "QUANT_MOE", "Q1_MOE", "Q8_MOE",
+                 "Q4_MOE", "QUANTIZED_INT8_MOE"):
+        m = create_moe_variant(name, base, MoEAllConfig(num_experts=8, top_k=2, expert_hidden=32), device="cpu",
+                               dtype=torch.float32, seed=0)
+        m.flatten()
+        loss, ce, aux = m.loss(ids, torch.roll(ids, -1, 1))
+        loss.backward()
+        blk = m.layers[0]
+        assert torch.isfinite(loss), name
+        ces[name] = round(float(ce.detach()), 6)
+        g = blk.gate_up.main_grad.abs().sum((1, 2))
+        if name == "PRODUCT_KEY":
+            assert blk.last_idx.shape[1] == 4 and bool((blk.last_idx[:, :2] < 4).all()) and bool((blk.last_idx[:, 2:] >= 4).all())
+            assert bool((g[:4] > 0).any()) and bool((g[4:] > 0).any())
+        if name == "DOMAIN_MOE":
+            assert blk.last_idx.shape[1] == 8 and blk.domain_classifier.grad is not None and bool((g > 0).all())
+        if name == "ATTENTION_MOE":
+            assert blk.router_k.grad is not None and float(blk.router_k.grad.abs().sum()) > 0
+        if name == "LOWRANK_MOE":
+            assert blk.lowrank_down.grad is not None and blk.lowrank_up.grad is not None
+            names = [n for n, _ in m.named_tensors()]
+            assert "layers.0.moe.lowrank_down.weight" in names
+        if name in ("QUANT_MOE", "Q1_MOE", "Q8_MOE", "Q4_MOE"):
+            assert float(g.sum()) > 0            # straight-through: the experts still get gradients
+    assert ces["QUANTIZED_INT8_MOE"] == ces["SPARSE_TOPK"]          # all scales are one until calibrated
+    # the structural variants really route / mix differently from plain top-k; the level-snapping ones change the output
+    # wherever it does not already sit on a level (small mixtures may all snap to the same level at initialisation)
+    for name in ("PRODUCT_KEY", "ATTENTION_MOE", "LOWRANK_MOE", "DOMAIN_MOE", "Q1_MOE", "Q8_MOE"):
+        assert ces[name] != ces["SPARSE_TOPK"], (name, ces)

@@ -17,6 +17,8 @@ from typing import Optional
 
 from dataclasses import dataclass
 
+import math
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as TF
@@ -130,6 +132,23 @@ class MoEBlock(nn.Module):
         self.shared_down = nn.Parameter(torch.empty(H, Fe * ns, **kw)) if ns else None
         self.router_bias = None   # DEEPSEEK_MOE: non-learned balancing bias, nudged by -0.001 per pick
         self.ep = None            # parallel.ep.ExpertParallel when experts are sharded across ranks
+        # variant-specific parameters (reference: src/model/moe_variants.cpp:990-1150)
+        variant = cfg.variant.upper()
+        self.router_k = self.lowrank_down = self.lowrank_up = self.domain_classifier = None
+        if variant == "ATTENTION_MOE":            # routing score = (x Wq) * (x Wk) * sqrt(H), element-wise per expert
+            self.router_k = nn.Parameter(torch.empty(E, H, **kw))
+        elif variant == "LOWRANK_MOE":            # router and experts see x pushed through a rank-r bottleneck
+            r = max(8, min(256, H // 2) // 8 * 8)
+            self.lowrank_down = nn.Parameter(torch.empty(r, H, **kw))
+            self.lowrank_up = nn.Parameter(torch.empty(H, r, **kw))
+        elif variant == "DOMAIN_MOE":             # a domain classifier mixes per-domain expert groups
+            nd = max(1, min(getattr(cfg, "num_domains", 0) or 4, E))
+            while E % nd:
+                nd -= 1
+            self.num_domains = nd
+            self.domain_classifier = nn.Parameter(torch.empty(nd, H, **kw))
+        # quantised-output variants: fixed levels, gradients pass straight through
+        self.register_buffer("expert_scales", torch.ones(E, device=device, dtype=torch.float32), persistent=False)
 
     def moe(self, f):
         cfg = self.cfg
@@ -151,6 +170,8 @@ class MoEBlock(nn.Module):
             if self.router_bias is None:
                 self.router_bias = torch.zeros(cfg.num_experts, device=f.device)
             logits = logits + self.router_bias
+        elif variant == "ATTENTION_MOE":
+            logits = logits * _LinearAG.apply(f, self.router_k).float() * math.sqrt(cfg.hidden_size)
         elif variant == "GATING_DROPOUT" and self.training:
             logits = logits + torch.where(torch.rand_like(logits) < 0.1, torch.full_like(logits, -1e4), torch.zeros_like(logits))
         # ---- rules that pick a selection [T, E] first (models/moe_routing.py); the fused expert path then runs on masked logits
@@ -177,16 +198,68 @@ class MoEBlock(nn.Module):
         if sel is not None:
             self.last_sel = sel
             logits, covered = R.masked_logits(logits, sel)
-        if self.ep is not None:
-            y, aux, idx = self.ep.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm,
-                                          cfg.act_kernel, cfg.load_balance_weight, cfg.router_z_weight)
+        def experts(x, lg, lo, hi, kk):
+            """Fused expert path over experts lo .. hi-1 with their slice of the logits."""
+            if (lo, hi) == (0, E):
+                gu, dn = self.gate_up, self.down
+            else:
+                # views of the group's experts; their weight gradients land in the matching rows of the full main_grad
+                gu, dn = self.gate_up[lo:hi], self.down[lo:hi]
+                for full, part in ((self.gate_up, gu), (self.down, dn)):
+                    _ensure_main_grad(full)
+                    part.main_grad = full.main_grad[lo:hi]
+            if self.ep is not None:
+                assert (lo, hi) == (0, E), "grouped variants are not expert-parallel"
+                return self.ep.moe_ffn(x, lg, gu, dn, kk, renorm, cfg.act_kernel, cfg.load_balance_weight, cfg.router_z_weight)
+            return M.moe_ffn(x, lg.contiguous(), gu, dn, kk, renorm, cfg.act_kernel, cfg.load_balance_weight, cfg.router_z_weight)
+
+        if variant == "PRODUCT_KEY":
+            # two key spaces: the first and second half of the experts are routed independently (top-k in each) and the
+            # two mixtures are added
+            half = max(1, E // 2)
+            ya, aux_a, idx_a = experts(f, logits[:, :half], 0, half, min(k, half, 8))
+            if E - half > 0:
+                yb, aux_b, idx_b = experts(f, logits[:, half:], half, E, min(k, E - half, 8))
+                y, aux, idx = ya + yb, aux_a + aux_b, torch.cat([idx_a, idx_b + half], -1)
+            else:
+                y, aux, idx = ya, aux_a, idx_a
+        elif variant == "DOMAIN_MOE":
+            nd, per = self.num_domains, E // self.num_domains
+            dom = torch.softmax(_LinearAG.apply(f, self.domain_classifier).float(), -1)
+            y, aux, idxs = 0.0, 0.0, []
+            for d in range(nd):
+                yd, ad, idd = experts(f, logits[:, d * per:(d + 1) * per], d * per, (d + 1) * per, min(k, per, 8))
+                y = y + yd * dom[:, d:d + 1].to(yd.dtype)
+                aux = aux + ad / nd
+                idxs.append(idd + d * per)
+            idx = torch.cat(idxs, -1)
         else:
-            y, aux, idx = M.moe_ffn(f, logits, self.gate_up, self.down, min(k, 8), renorm, cfg.act_kernel,
-                                    cfg.load_balance_weight, cfg.router_z_weight)
+            xin = f
+            if variant == "LOWRANK_MOE":
+                xin = _LinearAG.apply(_LinearAG.apply(f, self.lowrank_down), self.lowrank_up)
+                logits = _LinearAG.apply(xin, self.router).float()
+            y, aux, idx = experts(xin, logits, 0, E, min(k, 8))
         if covered is not None:
             y = y * covered[:, None].to(y.dtype)               # tokens that no expert serves contribute nothing
             if passthrough is not None and bool((passthrough > 0).any()):
                 y = y * (1.0 - passthrough)[:, None].to(y.dtype) + f * passthrough[:, None].to(f.dtype)
+        # ---- quantised-output variants (reference: moe_variants.cpp:1190-1380): the mixture is snapped to fixed levels,
+        # gradients pass straight through
+        if variant in ("QUANT_MOE", "Q1_MOE", "Q8_MOE", "Q4_MOE", "QUANTIZED_INT8_MOE"):
+            sq = float(self.expert_scales[-1])
+            yf = y.float()
+            if variant == "QUANTIZED_INT8_MOE":
+                y = y * float(self.expert_scales.double().prod())
+            else:
+                if variant == "QUANT_MOE":
+                    q = torch.where(yf * sq > 0.1, sq, torch.where(yf * sq < -0.1, -sq, 0.0))
+                elif variant == "Q1_MOE":
+                    q = torch.where(yf * sq >= 0, sq, -sq)
+                elif variant == "Q8_MOE":
+                    q = (torch.round(yf / 0.01).clamp(-128, 127)) * 0.01
+                else:
+                    q = (torch.round(yf / 0.1).clamp(-8, 7)) * 0.1
+                y = y + (q - yf).detach().to(y.dtype)
         if variant == "DEEPSEEK_MOE" and self.training:
             with torch.no_grad():
                 self.router_bias -= 0.001 * torch.bincount(idx.reshape(-1).long(), minlength=cfg.num_experts).float() / idx.numel() * cfg.num_experts
@@ -289,6 +362,9 @@ class MoEModel(DenseModel):
                 ep = pre + f"moe.expert.{e}."
                 out += [(ep + "gate_proj.weight", l.gate_up.data[e, :Fe]), (ep + "up_proj.weight", l.gate_up.data[e, Fe:]),
                         (ep + "down_proj.weight", l.down.data[e])]
+            for nm in ("router_k", "lowrank_down", "lowrank_up", "domain_classifier"):
+                if getattr(l, nm, None) is not None:
+                    out.append((pre + f"moe.{nm}.weight", getattr(l, nm).data))
             if l.shared_gate_up is not None:
                 Fs = l.shared_gate_up.shape[0] // 2
                 out += [(pre + "shared_expert.gate_proj.weight", l.shared_gate_up.data[:Fs]),
@@ -318,6 +394,7 @@ class MoEAllConfig:
     capacity_policy: str = "none"           # none | fixed | token_drop | token_pass (see models/moe_routing.py)
     num_shared_experts: int = 0
     num_groups: int = 0                     # HIERARCHICAL / MOMOE: 0 = about sqrt(num_experts)
+    num_domains: int = 4                    # DOMAIN_MOE: expert groups mixed by the domain classifier
     top_groups: int = 0                     # 0 = top_k
     top_experts_per_group: int = 1
 
@@ -337,4 +414,5 @@ def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfi
                     load_balance_weight=m.load_balance_weight, router_z_weight=m.router_z_weight, capacity_factor=m.capacity_factor,
                     capacity_policy=m.capacity_policy, variant=name)
     cfg.num_groups, cfg.top_groups, cfg.top_experts_per_group = m.num_groups, m.top_groups, m.top_experts_per_group
+    cfg.num_domains = m.num_domains
     return MoEModel(cfg, **model_kw)
