@@ -116,6 +116,43 @@ def test_prefix_cache_suffix_prefill_gpu(kv_mode):
         assert all(len(o) == 8 for o in got) and agree >= 2, (got, ref)
 
 
+@pytest.mark.gpu
+def test_pipelined_decode_matches_synchronous_gpu():
+    """Launching a decode step before the previous step's tokens are read must not change anything the caller sees: same
+    tokens for every request, also when sequences end early on a stop token (seen one step late by the scheduler), when
+    requests are admitted while others decode, and with more requests than batch slots."""
+    m = _model("cuda", torch.bfloat16, hidden_size=256, num_heads=4, num_kv_heads=2)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 200, (n,), generator=g).tolist() for n in (5, 17, 60, 40, 9, 33, 21, 12, 50, 7)]
+
+    def run(pipeline, stops):
+        eng = InferenceEngine(m, None, EngineConfig(max_batch=4, num_pages=256, pipeline_decode=pipeline, enable_prefix_cache=False))
+        reqs = [eng.add_request(p, max_tokens=12 + (i % 3), sampling=GREEDY, stop_ids=stops.get(i, ())) for i, p in enumerate(prompts)]
+        steps = 0
+        while eng.has_pending():
+            eng.step()
+            steps += 1
+        assert eng.cache.allocator.num_free == 256, "every page must be back after the last request"
+        return [r.out for r in reqs], steps
+    def agreement(a, b):
+        same = sum(int(x == y) for o, r in zip(a, b) for x, y in zip(o, r))
+        return same / max(1, sum(min(len(o), len(r)) for o, r in zip(a, b)))
+    base, _ = run(False, {})
+    pipe, _ = run(True, {})
+    assert [len(o) for o in pipe] == [len(o) for o in base] == [12 + (i % 3) for i in range(len(prompts))]
+    assert agreement(pipe, base) >= 0.9, (pipe, base)        # split-K sums are atomic: near-ties may flip a token
+    # stop tokens taken from the outputs themselves: those sequences end early, exactly at the stop token
+    stops = {i: (o[3],) for i, o in enumerate(base) if i % 2 == 0}
+    sync, n_sync = run(False, stops)
+    pipe, n_pipe = run(True, stops)
+    for outs in (sync, pipe):
+        for i, o in enumerate(outs):
+            if i in stops and stops[i][0] in o:
+                assert o.index(stops[i][0]) == len(o) - 1, (i, o)      # nothing is emitted after the stop token
+    assert any(len(o) < 12 for o in pipe) and agreement(pipe, sync) >= 0.9
+    assert n_pipe <= n_sync + 4
+
+
 def test_engine_with_packed_weights_matches_dequantised_model():
     """Serving from int8-packed weights must give the tokens of a model whose weights are the dequantised values."""
     import torch

@@ -43,6 +43,7 @@ class EngineConfig:
     cuda_graph: bool = True        # decode steps replay a captured graph per batch-size bucket (CUDA only)
     batch_prefill: bool = True     # prompts admitted in the same step (without a cached prefix) are prefilled together
     max_prefill_tokens: int = 8192 # padded tokens per prefill batch
+    pipeline_decode: bool = True   # CUDA: a decode step is launched before the previous step's tokens are read on the host
 
 
 @dataclass
@@ -174,6 +175,8 @@ class InferenceEngine:
         self._graphs = {}
         self._sample_cache = None
         self._bt_cache = None
+        self._inflight = None          # (requests, device tokens, pinned host tokens, event) of the decode step in flight
+        self._tok_host = None
         self.stats = InferenceStats()
         self.max_pages = (self.max_len + PAGE - 1) // PAGE
         self.packed = {}
@@ -224,7 +227,7 @@ class InferenceEngine:
         return r
 
     def has_pending(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     def _release(self, r: Request):
         for p in r.pages:
@@ -382,7 +385,8 @@ class InferenceEngine:
         f, _ = _norm_fwd(m.cfg, h, m.norm, m.norm_bias)
         return F.gemm(f, m.lm_head.data)
 
-    def _sample(self, logits, reqs):
+    def _sample_dev(self, logits, reqs):
+        """Sampled token ids as a device tensor [len(reqs)] (no host synchronisation)."""
         dev = logits.device
         # the per-row sampling parameters only change when the set of rows does: keep them on the device between steps
         key = tuple(r.id for r in reqs)
@@ -403,7 +407,10 @@ class InferenceEngine:
                 hist[i, :len(seq)] = torch.tensor(seq, dtype=torch.int32)
             hist = hist.to(dev)
         self._step += 1
-        return sample(logits, t, k, p, rp, hist, self.cfg.seed, self._step).tolist()
+        return sample(logits, t, k, p, rp, hist, self.cfg.seed, self._step)
+
+    def _sample(self, logits, reqs):
+        return self._sample_dev(logits, reqs).tolist()
 
     # ------------------------------------------------------------------ scheduling
     @torch.no_grad()
@@ -453,25 +460,37 @@ class InferenceEngine:
         if fresh:
             self._prefill_fresh(fresh, finished)
         # ---- one decode token for everything that is running ----
-        if self.running:
+        # Pipelined form (CUDA, no repetition penalty): positions, slots and the block table are known on the host without
+        # the previous step's tokens, and those tokens are on the device, so the next step is launched first and the
+        # previous step's tokens are read (from a pinned buffer filled behind an event) while it runs.  End-of-sequence
+        # tokens are therefore seen one step late: such a sequence runs one step too many, whose result is dropped (its
+        # cache write lands in pages that are free or handed to a prefill enqueued later on the same stream).
+        dev = self.device
+        prev, self._inflight = self._inflight, None
+        pipelined = (self.cfg.pipeline_decode and dev.type == "cuda" and
+                     all(r.sampling.repetition_penalty == 1.0 for r in self.running))
+        if prev is not None and not pipelined:
+            self._collect(prev, finished)
+            prev = None
+        pend = {id(r): i for i, r in enumerate(prev[0])} if prev is not None else {}
+        # with its pending token counted, a sequence is decoded again only if that token does not end it by length
+        reqs = [r for r in self.running
+                if id(r) not in pend or (len(r.out) + 1 < r.max_tokens and len(r.tokens) + len(r.out) + 1 < self.max_len)]
+        if reqs:
             t0 = time.perf_counter()
-            reqs = self.running
             for r in reqs:
                 if r.pos // PAGE >= len(r.pages):
                     r.pages.append(alloc.alloc())
-            dev = self.device
-            # tokens, positions and slots travel in one small upload; the block table is re-sent only when a row changed
-            # (a new request set, or a sequence that started a new page)
-            packed = torch.tensor([[r.out[-1] for r in reqs], [r.pos for r in reqs],
-                                   [r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs]], dtype=torch.int64).to(dev)
+            # host tokens (0 where the token is still on the device), positions, slots and the row of the previous step that
+            # holds a pending token (-1: none) travel in one small upload; the block table only re-sends what changed
+            packed = torch.tensor([[0 if id(r) in pend else r.out[-1] for r in reqs], [r.pos for r in reqs],
+                                   [r.pages[r.pos // PAGE] * PAGE + r.pos % PAGE for r in reqs],
+                                   [pend.get(id(r), -1) for r in reqs]], dtype=torch.int64).to(dev)
             tokens, positions, slots = packed[0], packed[1].to(torch.int32), packed[2]
-            bt_key = (tuple(r.id for r in reqs), tuple(len(r.pages) for r in reqs))
-            if self._bt_cache is None or self._bt_cache[0] != bt_key:
-                bt = torch.zeros((len(reqs), self.max_pages), dtype=torch.int32)
-                for i, r in enumerate(reqs):
-                    bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-                self._bt_cache = (bt_key, bt.to(dev))
-            bt = self._bt_cache[1]
+            if pend:
+                src = packed[3]
+                tokens = torch.where(src >= 0, prev[1][src.clamp(min=0)], tokens)
+            bt = self._block_table(reqs)
             if self.cfg.cuda_graph and dev.type == "cuda":
                 bucket = 1
                 while bucket < len(reqs):
@@ -482,16 +501,71 @@ class InferenceEngine:
                 logits = g.replay(tokens, positions, bt, slots)
             else:
                 logits = self._logits(self._layers_decode(tokens, positions, bt, slots))
-            toks = self._sample(logits, reqs)
-            self.stats.decode_ms += (time.perf_counter() - t0) * 1e3
-            still = []
-            for r, tok in zip(reqs, toks):
+            for r in reqs:
                 r.pos += 1
-                self._emit(r, tok, finished)
-                if not r.finished:
-                    still.append(r)
-            self.running = still
+            toks_dev = self._sample_dev(logits, reqs)
+            if pipelined:
+                if self._tok_host is None:
+                    self._tok_host = [torch.empty(self.cfg.max_batch, dtype=torch.int64).pin_memory() for _ in range(2)]
+                self._tok_flip = getattr(self, "_tok_flip", 0) ^ 1     # never the buffer the previous step is still read from
+                host = self._tok_host[self._tok_flip][:len(reqs)]
+                host.copy_(toks_dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                self._inflight = (reqs, toks_dev, host, ev)
+                if prev is not None:
+                    self._collect(prev, finished)
+            else:
+                self._collect((reqs, toks_dev, None, None), finished)
+            self.stats.decode_ms += (time.perf_counter() - t0) * 1e3
+        elif prev is not None:
+            self._collect(prev, finished)
         return finished
+
+    def _collect(self, step, finished: list):
+        """Read the tokens of a launched decode step and hand them to their requests (a request that has finished in the
+        meantime - end of sequence seen one step late, or stopped from outside - drops its token)."""
+        reqs, toks_dev, host, ev = step
+        if host is not None:
+            ev.synchronize()
+            toks = host.tolist()
+        else:
+            toks = toks_dev.tolist()
+        for r, tok in zip(reqs, toks):
+            if not r.finished:
+                self._emit(r, tok, finished)
+        self.running = [r for r in self.running if not r.finished]
+
+    def _block_table(self, reqs):
+        """Device block table [len(reqs), max_pages] for the running sequences.  The table lives on the device; a step
+        uploads only what changed since the last one - the page a sequence has just started, or the whole row when a
+        different request now sits in that row - as one (index, value) list.  Entries past a sequence's last page may be
+        stale: the kernels read pages below ceil(length / 16) only."""
+        dev, mp = self.device, self.max_pages
+        if self._bt_cache is None:
+            self._bt_cache = (torch.zeros((self.cfg.max_batch, mp), dtype=torch.int32, device=dev), [])
+        table, rows = self._bt_cache
+        idx, val = [], []
+        for i, r in enumerate(reqs):
+            n = len(r.pages)
+            have = rows[i] if i < len(rows) else None
+            if have is None or have[0] != r.id or have[1] > n:
+                lo = 0
+            elif have[1] < n:
+                lo = have[1]
+            else:
+                continue
+            idx.extend(range(i * mp + lo, i * mp + n))
+            val.extend(r.pages[lo:])
+            if i < len(rows):
+                rows[i] = (r.id, n)
+            else:
+                rows.append((r.id, n))
+        del rows[len(reqs):]
+        if idx:
+            u = torch.tensor([idx, val], dtype=torch.int64).to(dev)
+            table.view(-1).index_copy_(0, u[0], u[1].to(torch.int32))
+        return table[:len(reqs)]
 
     def _emit(self, r: Request, tok: int, finished: list):
         r.out.append(tok)
@@ -499,7 +573,7 @@ class InferenceEngine:
         if r.on_token:
             r.on_token(tok)
         eos = self.tok.eos_id if self.tok is not None else -1
-        if tok == eos or tok in r.stop_ids or len(r.out) >= r.max_tokens or r.pos + 1 >= self.max_len:
+        if tok == eos or tok in r.stop_ids or len(r.out) >= r.max_tokens or len(r.tokens) + len(r.out) >= self.max_len:
             r.finished = True
             r.t_done = time.perf_counter()
             self._release(r)
