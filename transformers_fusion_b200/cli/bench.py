@@ -174,6 +174,13 @@ def serve_bench(a):
     cfg = preset(a.preset)
     if a.layers > 0:
         cfg.num_layers = a.layers
+    if a.tp_shape > 1:
+        # one rank's share of a tensor-parallel deployment, alone on this GPU: its heads, kv heads and FFN slice, the
+        # replicated embedding / head, and no all-reduce - the compute side of a rank without the peers
+        import dataclasses
+        assert world == 1 and cfg.num_heads % a.tp_shape == 0 and cfg.ffn_hidden_size % a.tp_shape == 0
+        cfg = dataclasses.replace(cfg, num_heads=cfg.num_heads // a.tp_shape, num_kv_heads=max(1, cfg.num_kv_heads // a.tp_shape),
+                                  head_dim=cfg.head_dim, ffn_hidden_size=cfg.ffn_hidden_size // a.tp_shape)
     if hasattr(cfg, "num_experts"):
         from ..models.moe import MoEModel
         model = MoEModel(cfg, device=dev, dtype=torch.bfloat16, seed=0)
@@ -269,7 +276,7 @@ def _serve_load(a, cfg, model, rank, world, symm, g):
     ttft = sorted((r.t_first - r.t_submit) * 1e3 for r in done)
     rec = {"bench": "serve_load", "load": "baseline5", "preset": a.preset, "layers": cfg.num_layers, "requests": nreq,
            "concurrent": conc, "prompt_len": [a.prompt_min, a.prompt_max], "prompt_tokens": sum(lens), "gen": a.gen,
-           "weights": a.weights or "bf16", "kv": a.kv, "tp": world, "cuda_graph": eng.cfg.cuda_graph,
+           "weights": a.weights or "bf16", "kv": a.kv, "tp": world, "tp_shape": a.tp_shape, "cuda_graph": eng.cfg.cuda_graph,
            "out_tok_s": round(out_tokens / dt, 1), "ttft_ms_p50": round(statistics.median(ttft), 2),
            "ttft_ms_p90": round(ttft[int(0.9 * (len(ttft) - 1))], 2), "total_s": round(dt, 2), "engine_steps": steps,
            "decode_ms_per_step": round((eng.stats.decode_ms - d0) / max(1, steps), 3),
@@ -292,6 +299,8 @@ def main(argv=None):
     ap.add_argument("--kv", default="bf16", help="KV cache storage for --serve: bf16 | fp8 | q4")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="--serve: override the preset's layer count (fits big shapes on one GPU)")
+    ap.add_argument("--tp-shape", type=int, default=1, help="--serve on one GPU: serve one rank's share of a TP=N deployment "
+                                                             "(heads and FFN divided by N, no collectives)")
     ap.add_argument("--model", default="")
     ap.add_argument("--prompt", default="test")
     add_int(ap, "--iters", 20)
