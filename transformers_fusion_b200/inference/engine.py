@@ -472,10 +472,17 @@ class InferenceEngine:
         if prev is not None and not pipelined:
             self._collect(prev, finished)
             prev = None
-        pend = {id(r): i for i, r in enumerate(prev[0])} if prev is not None else {}
-        # with its pending token counted, a sequence is decoded again only if that token does not end it by length
-        reqs = [r for r in self.running
-                if id(r) not in pend or (len(r.out) + 1 < r.max_tokens and len(r.tokens) + len(r.out) + 1 < self.max_len)]
+        def launch_set():
+            pend_ = {id(r): i for i, r in enumerate(prev[0])} if prev is not None else {}
+            # with its pending token counted, a sequence is decoded again only if that token does not end it by length
+            return pend_, [r for r in self.running if id(r) not in pend_ or
+                           (len(r.out) + 1 < r.max_tokens and len(r.tokens) + len(r.out) + 1 < self.max_len)]
+        pend, reqs = launch_set()
+        if prev is not None and reqs and self.cfg.cuda_graph and self._bucket(len(reqs)) not in self._graphs:
+            # a graph for this batch size has to be captured first: do that with nothing in flight
+            self._collect(prev, finished)
+            prev = None
+            pend, reqs = launch_set()
         if reqs:
             t0 = time.perf_counter()
             for r in reqs:
@@ -492,9 +499,7 @@ class InferenceEngine:
                 tokens = torch.where(src >= 0, prev[1][src.clamp(min=0)], tokens)
             bt = self._block_table(reqs)
             if self.cfg.cuda_graph and dev.type == "cuda":
-                bucket = 1
-                while bucket < len(reqs):
-                    bucket *= 2
+                bucket = self._bucket(len(reqs))
                 g = self._graphs.get(bucket)
                 if g is None:
                     g = self._graphs[bucket] = _DecodeGraph(self, bucket)
@@ -521,6 +526,13 @@ class InferenceEngine:
         elif prev is not None:
             self._collect(prev, finished)
         return finished
+
+    @staticmethod
+    def _bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
 
     def _collect(self, step, finished: list):
         """Read the tokens of a launched decode step and hand them to their requests (a request that has finished in the
