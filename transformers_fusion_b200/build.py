@@ -145,6 +145,24 @@ def build_tools(force=False):
     return out
 
 
+def build_sanitized(kind: str = "asan", force=False) -> Path:
+    """The host-side native sources (codec + container, tokenizer, HTTP server) and the harness csrc/san/san_driver.cpp as
+    one executable under a sanitizer: kind "asan" = -fsanitize=address,undefined, "tsan" = -fsanitize=thread.
+    Product: lib/bin/tfb_san_<kind> (run it with a scratch directory as its argument)."""
+    flags = {"asan": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "tsan": ["-fsanitize=thread"]}[kind]
+    bind = LIB / "bin"
+    bind.mkdir(parents=True, exist_ok=True)
+    exe = bind / f"tfb_san_{kind}"
+    srcs = [CSRC / "san" / "san_driver.cpp"] + sorted((CSRC / "codec").glob("*.cpp")) + sorted((CSRC / "tokenizer").glob("*.cpp")) + \
+        sorted((CSRC / "serve").glob("*.cpp"))
+    deps = srcs + list((CSRC / "codec").glob("*.h"))
+    if force or _newer(deps, exe):
+        cxx = os.environ.get("TFB_CXX", "g++")
+        _run([cxx, "-O1", "-g", "-fno-omit-frame-pointer", "-std=c++17", "-pthread", "-Wall", "-Wno-unused-function"] + flags +
+             ["-I", str(CSRC / "codec")] + [str(s) for s in srcs] + ["-o", str(exe)])
+    return exe
+
+
 def build_all(force=False, verbose=False, bounds_check=True):
     LIB.mkdir(exist_ok=True)
     built = [build_kernels(force, verbose)]
@@ -166,7 +184,12 @@ def main(argv=None):
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="pass -Xptxas -v (set TFB_BUILD_VERBOSE=1 to print)")
     ap.add_argument("--no-bounds-check", action="store_true", help="skip the -DTFB_BOUNDS_CHECK variant of the kernel library")
+    ap.add_argument("--sanitize", choices=["asan", "tsan"], help="only build the sanitizer harness of the host-side native code "
+                                                                "(lib/bin/tfb_san_asan: address + undefined behaviour; tfb_san_tsan: threads)")
     a = ap.parse_args(argv)
+    if a.sanitize:
+        print("built", build_sanitized(a.sanitize, a.force))
+        return
     for p in build_all(a.force, a.verbose, not a.no_bounds_check):
         print("built", p)
 

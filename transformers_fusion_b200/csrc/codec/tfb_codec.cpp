@@ -1286,17 +1286,53 @@ TFB_EXPORT int tfb_format_is_wire_exact(int fmt) {
   int bits;
   return family_of(fmt, &bits) != F_OWN;
 }
-TFB_EXPORT size_t tfb_block_claimed_bytes(int fmt, uint32_t n) {
-  if (fmt < 0 || fmt >= TFB_FORMAT_COUNT) return 0;
-  return size_t(ceil(float(registry()[fmt].bpw) * float(n) / 8.0f));
+static size_t formula_bytes(int fmt, uint32_t n) { return size_t(ceil(float(registry()[fmt].bpw) * float(n) / 8.0f)); }
+static long encode_block(int fmt, const float* w, uint32_t n, uint8_t* out, size_t cap);
+
+// Bytes an encoder of this library writes for a block of n weights.  The wire layouts of the grouped / half-step formats
+// carry whole header bytes, so at ragged block sizes a stream can be a byte longer than bpw * n / 8: the layout, not the
+// formula, is what a caller's buffer has to hold.  The length depends on (format, n) only; it is taken from a dry run on
+// a zero block and remembered per thread.
+static size_t stream_bytes(int fmt, uint32_t n) {
+  static thread_local std::vector<std::pair<uint64_t, size_t>> memo;
+  const uint64_t key = (uint64_t(uint32_t(fmt)) << 32) | n;
+  for (const auto& kv : memo)
+    if (kv.first == key) return kv.second;
+  std::vector<float> zeros(n, 0.0f);
+  std::vector<uint8_t> scratch(size_t(n) * 4 + 64);
+  const long got = encode_block(fmt, zeros.data(), n, scratch.data(), scratch.size());
+  const size_t len = got > 0 ? size_t(got) : formula_bytes(fmt, n);
+  if (memo.size() >= 256) memo.clear();
+  memo.emplace_back(key, len);
+  return len;
 }
 
+TFB_EXPORT size_t tfb_block_claimed_bytes(int fmt, uint32_t n) {
+  if (fmt < 0 || fmt >= TFB_FORMAT_COUNT) return 0;
+  const size_t f = formula_bytes(fmt, n);
+  if (n == 0 || n > (1u << 20)) return f;
+  return std::max(f, stream_bytes(fmt, n));
+}
+
+// Encodes into `out` when the stream fits into `cap` bytes; the encoders themselves always work in a scratch buffer with
+// room for any layout (4 bytes per weight + headers), so a short `cap` is an error return, never an overrun.
 TFB_EXPORT long tfb_quantize_block(int fmt, const float* w, uint32_t n, uint8_t* out, size_t cap) {
   if (fmt < 0 || fmt >= TFB_FORMAT_COUNT || !w || !out || n == 0) return -1;
+  static thread_local std::vector<uint8_t> scratch;
+  const size_t room = size_t(n) * 4 + 64;
+  if (scratch.size() < room) scratch.resize(room);
+  const long got = encode_block(fmt, w, n, scratch.data(), room);
+  if (got < 0 || size_t(got) > cap) return -1;
+  memcpy(out, scratch.data(), size_t(got));
+  if (size_t(got) < cap) memset(out + got, 0, cap - size_t(got));   // the rest of the caller's buffer reads as zeros, as before
+  return got;
+}
+
+static long encode_block(int fmt, const float* w, uint32_t n, uint8_t* out, size_t cap) {
   int bits;
   const Family fam = family_of(fmt, &bits);
   const FormatInfo& f = registry()[fmt];
-  size_t need = tfb_block_claimed_bytes(fmt, n);
+  size_t need = formula_bytes(fmt, n);
   if (fam == F_Q16) need = std::max(need, size_t(n) * 2);
   if (fam == F_Q1) need = std::max(need, size_t(n + 7) / 8);
   if (cap < need) return -1;
@@ -1374,7 +1410,7 @@ TFB_EXPORT void tfb_dequantize_block(int fmt, const uint8_t* idx, size_t idx_byt
     case F_G16:
     case F_G24: {
       const size_t plain = size_t(n) * (fam == F_G16 ? 2 : 3);
-      const size_t claimed = tfb_block_claimed_bytes(fmt, n);
+      const size_t claimed = formula_bytes(fmt, n);
       const bool tail = n % 32 == 0 && idx_bytes >= claimed && claimed > plain;
       if (fam == F_G16) dec_q16(idx, tail ? plain : idx_bytes, n, out); else dec_q24(idx, tail ? plain : idx_bytes, n, out);
       if (tail) dec_mean_tail(idx + plain, n, out);

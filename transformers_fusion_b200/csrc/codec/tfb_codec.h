@@ -5,11 +5,11 @@
 // src/codec/quant_format.cpp, src/codec/block_codec.cpp):
 //   container   header | config | u32 n_fmt | {u32 id, u8 fmt, u32 cb}* | u32 n_tensors |
 //               {u16 len, name, u32 start, u32 count}* | blocks {u32 nw, u32 cb, cb, u32 idx, idx}*
-//   exact codecs (decode is bit-identical to the reference; encode produces streams its decoder
-//   accepts): Q_32, Q_24(+K), Q_16(+K), lattice Q_8 / Q_4 / Q_2(+K), Q_G_16 / Q_G_24 residual-mean
-//   forms.  The remaining formats use this library's own encoders with the same budget contract
-//   (payload bytes == ceil(bpw * n / 8)) and the same primitive families (sign, fixed codebook,
-//   grouped affine, mixed tiers); see format_is_wire_exact().
+//   block streams: all 105 formats decode streams of the reference encoder bit-identically and encode streams of the
+//   same layout and length (raw / truncated floats, lattice Q_8 / Q_4 / Q_2, fixed quantile codebooks, grouped affine,
+//   6-bit scaled integers, compound 8 / 12-bit, four-tier mixes, the small-group fallback of short blocks).  A stream's
+//   length follows from its layout; at ragged block sizes it can exceed ceil(bpw * n / 8) by a header byte, which
+//   tfb_block_claimed_bytes accounts for.
 #pragma once
 #include <stddef.h>
 #include <stdint.h>
@@ -33,11 +33,11 @@ int tfb_format_is_grouped(int fmt);
 int tfb_format_is_mix(int fmt);
 int tfb_format_k_tier(int fmt);                  // 0 none, 1 L, 2 M, 3 H
 int tfb_format_is_wire_exact(int fmt);
-size_t tfb_block_claimed_bytes(int fmt, uint32_t n);
+size_t tfb_block_claimed_bytes(int fmt, uint32_t n);   // buffer size that holds any stream of n weights in this format
 
 // ---- block codec ----------------------------------------------------------------------------
 // Encodes n weights.  idx_out must hold tfb_block_claimed_bytes(fmt, n) bytes (cb is unused: 0 bytes).
-// Returns the number of payload bytes written, or -1.
+// Returns the number of payload bytes written, or -1 (also when idx_cap is too small: nothing is written past it).
 long tfb_quantize_block(int fmt, const float* w, uint32_t n, uint8_t* idx_out, size_t idx_cap);
 // Decodes; tolerant of short payloads (missing bits read as zero).  Unknown formats decode zeros.
 void tfb_dequantize_block(int fmt, const uint8_t* idx, size_t idx_bytes, const uint8_t* cb, size_t cb_bytes,
