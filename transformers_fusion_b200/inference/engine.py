@@ -3,9 +3,12 @@
 One ``step()`` = admit waiting requests while pages are available (prefill each prompt with the
 tcgen05 flash-attention kernel and scatter its K/V into pages, quantised on the way), then ONE decode
 token for every running sequence in a single batched pass (GEMMs with M = batch, RoPE at per-sequence
-positions, append to pages, paged decode attention with fused KV dequantisation, sampling kernel).
+positions, append to pages, paged decode attention on the tensor cores with fused KV dequantisation,
+sampling kernel).  On CUDA the step is pipelined: the sampled ids stay on the device and feed the next
+step there, which is launched before the host has read them (one step late, from a pinned buffer).
 Finished sequences release their pages; a prefix cache lets requests that share a prompt prefix (whole
-pages) reuse the pages instead of recomputing them.
+pages) reuse the pages instead of recomputing them, and the rest of such a prompt attends over the
+cached pages through a gather + the tensor-core attention kernel.
 
 Reference counterparts: ContinuousBatching / RequestScheduler (priority desc, deadline asc) /
 PrefixCache / PagedAttention (src/inference/inference_paging.cpp:24-285, inference_kv.cpp:20-205),

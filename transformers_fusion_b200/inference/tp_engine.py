@@ -1,8 +1,10 @@
 """Tensor-parallel serving: every rank runs the same continuous-batching scheduler on the same requests and holds
 1 / W of every layer (its query / kv heads, its slice of the FFN, its pages of the KV cache for those heads).  The two
-row-parallel products of a block (attention output, FFN down) produce partial sums that are added across ranks with the
-one-shot / two-shot all-reduce kernels over NVLink peer memory (decode-sized messages take the one-shot form); on CPU or
-without a symmetric heap the sum goes through torch.distributed.  The all-reduce gives every rank bit-identical
+row-parallel products of a block (attention output, FFN down) produce partial sums that are added across ranks over
+NVLink peer memory: decode-sized messages by the flag-in-data all-reduce (every rank pushes its rows, tagged with a
+sequence number, into the peers' receive areas and sums what arrives - no barrier - with the residual stream added in
+the same kernel), prefill-sized ones by the two-shot kernel on a staging buffer; on CPU or without a symmetric heap the
+sum goes through torch.distributed.  The all-reduce gives every rank bit-identical
 activations, so sampling with the shared seed picks the same token everywhere and the schedulers stay in step without
 exchanging anything else.
 

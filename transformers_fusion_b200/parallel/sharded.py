@@ -8,16 +8,18 @@ One step, per rank:
 
 * forward / backward are written by hand over the sm_100a kernels (no autograd graph).  Between the tensor-parallel
   regions the token stream is a row shard [T / tp, H] (sequence parallelism); the two collectives of a tensor-parallel
-  product ride inside its GEMM launch (all-gather -> GEMM, GEMM -> reduce-scatter), and so does the ZeRO-3 parameter
-  gather: the first GEMM that consumes a weight pulls the dp peers' row shards over NVLink into one of two per-unit gather
-  buffers while the tiles of the local shard already multiply (``tfb_gemm_bf16_tp`` bits 1 / 2 / 4).  A unit's buffer
-  is recycled two units later, so only two units' worth of full weights exist at any time.
+  product ride inside its GEMM launch (all-gather -> GEMM, GEMM -> reduce-scatter; ``tfb_gemm_bf16_tp`` bits 1 / 2).
+* the ZeRO-3 parameter gather fills one of two per-unit gather buffers (a unit's buffer is recycled two units later, so
+  only two units' worth of full weights exist at any time).  Default (``gather="prefetch"``): one all-gather kernel per
+  unit on a side stream, one unit ahead of the compute, whose small CTAs read every dp peer's row shards over NVLink
+  beside the running GEMMs.  ``gather="fused"``: the first GEMM that consumes a weight pulls the peers' shards itself
+  (bit 4 of the GEMM mode word) while the tiles of the local shard already multiply.
 * the token embedding is read straight from the shards (each row from the dp rank that owns it), the LM head and the
   cross entropy are vocabulary-parallel (the ranks exchange [T, 4] row statistics, never logits).
 * as soon as a unit's backward is complete its gradients are reduce-scattered over the dp group by one kernel on a side
   stream with a bounded grid (peer loads, 1/dp scale, squared-norm partial), overlapping the backward of the next unit.
 * after the last unit: global gradient norm (one scalar all-reduce), clip, one fused AdamW over this rank's flat shard
-  state, refreshed bf16 shards in place.  No parameter all-gather follows: the next step's GEMMs pull what they need.
+  state, refreshed bf16 shards in place.  No parameter all-gather follows: the next step gathers what it needs.
 
 ``comm="nccl"`` (and every CPU / gloo run) replaces each fused piece by the library collective plus the plain kernel and is
 the baseline the fused path is compared against.
