@@ -1,9 +1,14 @@
 #!/bin/sh
 # Builds the unmodified reference (CMake, Release, AVX2) from a scratch copy and installs its static libraries plus the
-# config-1 timing harness into baseline/_ref/ (git-ignored).  Usage: baseline/build_reference.sh [reference tree]
+# config-1 timing harness into baseline/_ref/ (git-ignored).
+# Usage: baseline/build_reference.sh <reference tree>      (or TFB_REFERENCE_SRC=<reference tree>)
 set -e
 here="$(cd "$(dirname "$0")" && pwd)"
-src="${1:-/root/reference}"
+src="${1:-$TFB_REFERENCE_SRC}"
+if [ -z "$src" ] || [ ! -d "$src" ]; then
+  echo "usage: $0 <path of the reference source tree>" >&2
+  exit 2
+fi
 work="$(mktemp -d /tmp/tfb_ref_build.XXXXXX)"
 cp -r "$src" "$work/src"
 cmake -S "$work/src" -B "$work/build" -DCMAKE_BUILD_TYPE=Release -DQUANT_AVX2=ON -DQUANT_BUILD_TESTS=OFF \
