@@ -116,6 +116,35 @@ def test_prefix_cache_suffix_prefill_gpu(kv_mode):
         assert all(len(o) == 8 for o in got) and agree >= 2, (got, ref)
 
 
+def test_pipelined_schedule_on_cpu():
+    """The pipelined schedule (launch first, read the previous step's tokens afterwards) run on the CPU, where arithmetic is
+    deterministic: token-for-token the outputs of the synchronous schedule, with more requests than batch slots, sequences
+    that end on a stop token (seen one step late), and every page returned at the end."""
+    m = _model()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 200, (n,), generator=g).tolist() for n in (5, 17, 60, 40, 9, 33, 21, 12)]
+
+    def run(pipeline, stops):
+        eng = InferenceEngine(m, None, EngineConfig(max_batch=3, num_pages=128, pipeline_decode=pipeline, enable_prefix_cache=False))
+        reqs = [eng.add_request(p, max_tokens=10 + (i % 3), sampling=GREEDY, stop_ids=stops.get(i, ())) for i, p in enumerate(prompts)]
+        steps = 0
+        while eng.has_pending():
+            eng.step()
+            steps += 1
+        assert eng.cache.allocator.num_free == 128
+        return [r.out for r in reqs], steps
+    base, n0 = run(False, {})
+    pipe, n1 = run("force", {})
+    assert pipe == base and [len(o) for o in base] == [10 + (i % 3) for i in range(len(prompts))]
+    stops = {i: (o[4],) for i, o in enumerate(base) if i % 2 == 0}
+    sync, _ = run(False, stops)
+    pipe, _ = run("force", stops)
+    assert pipe == sync and any(len(o) < 10 for o in sync)
+    for i, o in enumerate(sync):
+        if i in stops:
+            assert o.index(stops[i][0]) == len(o) - 1
+
+
 @pytest.mark.gpu
 def test_pipelined_decode_matches_synchronous_gpu():
     """Launching a decode step before the previous step's tokens are read must not change anything the caller sees: same

@@ -46,7 +46,8 @@ class EngineConfig:
     cuda_graph: bool = True        # decode steps replay a captured graph per batch-size bucket (CUDA only)
     batch_prefill: bool = True     # prompts admitted in the same step (without a cached prefix) are prefilled together
     max_prefill_tokens: int = 8192 # padded tokens per prefill batch
-    pipeline_decode: bool = True   # CUDA: a decode step is launched before the previous step's tokens are read on the host
+    pipeline_decode: object = True # CUDA: a decode step is launched before the previous step's tokens are read on the host
+                                   # ("force": the same schedule on any device, for testing the scheduler on CPU)
 
 
 @dataclass
@@ -470,7 +471,7 @@ class InferenceEngine:
         # cache write lands in pages that are free or handed to a prefill enqueued later on the same stream).
         dev = self.device
         prev, self._inflight = self._inflight, None
-        pipelined = (self.cfg.pipeline_decode and dev.type == "cuda" and
+        pipelined = (bool(self.cfg.pipeline_decode) and (dev.type == "cuda" or self.cfg.pipeline_decode == "force") and
                      all(r.sampling.repetition_penalty == 1.0 for r in self.running))
         if prev is not None and not pipelined:
             self._collect(prev, finished)
@@ -513,13 +514,15 @@ class InferenceEngine:
                 r.pos += 1
             toks_dev = self._sample_dev(logits, reqs)
             if pipelined:
-                if self._tok_host is None:
-                    self._tok_host = [torch.empty(self.cfg.max_batch, dtype=torch.int64).pin_memory() for _ in range(2)]
-                self._tok_flip = getattr(self, "_tok_flip", 0) ^ 1     # never the buffer the previous step is still read from
-                host = self._tok_host[self._tok_flip][:len(reqs)]
-                host.copy_(toks_dev, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
+                host = ev = None
+                if dev.type == "cuda":
+                    if self._tok_host is None:
+                        self._tok_host = [torch.empty(self.cfg.max_batch, dtype=torch.int64).pin_memory() for _ in range(2)]
+                    self._tok_flip = getattr(self, "_tok_flip", 0) ^ 1  # never the buffer the previous step is still read from
+                    host = self._tok_host[self._tok_flip][:len(reqs)]
+                    host.copy_(toks_dev, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record()
                 self._inflight = (reqs, toks_dev, host, ev)
                 if prev is not None:
                     self._collect(prev, finished)
