@@ -77,3 +77,44 @@ def test_fp8_and_quant8():
     for sym in (False, True):
         q, s, zp = E.quant8_quantize_tensor(x, sym)
         assert float((E.quant8_dequantize_tensor(q, s, zp) - x).abs().max()) <= s * 0.51 + 1e-6
+
+
+def test_ternary_lut_streams():
+    """TL1 / TL2 row streams: byte layout, round trip at ragged K, the lookup-table product's integer arithmetic (written
+    out here as the reference's scalar loops), and the transcode to the packed device format."""
+    torch.manual_seed(3)
+    for kind, K in ((1, 10), (1, 13), (2, 24), (2, 29)):
+        tl = E.TernaryLUT(kind)
+        t = torch.randint(-1, 2, (5, K))
+        packed = tl.pack(t)
+        assert packed.shape == (5, (K + 3) // 4 if kind == 1 else (K + 11) // 12 * 3) and packed.dtype == torch.uint8
+        assert torch.equal(tl.unpack(packed, K).long(), t)
+        # weight i of a row sits in bits 2 * (i % 4) of byte i // 4, with 00 = -1, 01 = 0, 10 = +1
+        for i in range(K):
+            assert int((packed[2, i // 4] >> (2 * (i % 4))) & 3) == int(t[2, i]) + 1
+        a = torch.randn(3, K) * 2
+        got = tl.gemm(packed, a, K)
+        want = torch.zeros(5, 3)
+        for n in range(3):
+            sc = 127.0 / max(float(a[n].abs().max()), 1e-10)
+            ai = torch.round(a[n] * sc).long()
+            for m in range(5):
+                if kind == 1:
+                    tot = 0
+                    for i in range(0, K - 1, 2):
+                        tot += max(-128, min(127, int(ai[i]) * int(t[m, i]) + int(ai[i + 1]) * int(t[m, i + 1])))
+                    if K % 2:
+                        tot += int(ai[K - 1]) * int(t[m, K - 1])
+                else:
+                    tot = int((ai * t[m]).sum())
+                want[m, n] = tot / sc
+        assert torch.allclose(got, want, atol=1e-5), (kind, K)
+        if kind == 2:          # no saturation: off the exact product only by the int8 rounding of the activations
+            assert (got - t.float() @ a.t()).abs().max() <= 0.5 * K * float(a.abs().max()) / 127 + 1e-5
+    # transcode for the fused-dequant GEMM: ternary values x per-row scale survive exactly
+    tl = E.TernaryLUT(1)
+    t = torch.randint(-1, 2, (128, 64))
+    scale = torch.rand(128) + 0.5
+    pw = tl.to_packed_weight(tl.pack(t), 64, scale)
+    from transformers_fusion_b200.quant import wq
+    assert torch.allclose(wq.dequant(pw)[:128, :64], t.float() * scale[:, None], rtol=1e-2, atol=1e-3)

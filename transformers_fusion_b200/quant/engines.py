@@ -5,12 +5,15 @@
 * ``VectorQuantizer``       - k-means codebook over d-dimensional sub-vectors with straight-through forward.
 * ``Q8Engine / Q4Engine / Q2Engine`` - codebook + per-block scale with optional stochastic rounding between neighbours.
 * ``QuantEngine``           - ternary {-1, 0, +1} x per-block (128) scale, 2-bit packed, ``quant_gemm``.
+* ``TernaryLUT``            - the reference's TL1 / TL2 row streams of ternary weights (2 bits each: 00 = -1, 01 = 0, 10 = +1;
+  rows of ceil(K / 4) bytes, or 3 bytes per 12 weights) with its lookup-table product (activations rounded to int8 per row,
+  pair sums saturating at int8 in TL1) and the transcode into the packed ternary form of the fused-dequant GEMM.
 * ``Q1Engine``              - sign x mean |w|.   ``Q16Engine / Q32Engine`` - fp16 round trip / identity.
 * fp8: ``fp8_quantize(x, "e4m3" | "e5m2")`` (max 448, no infinities / max 57344), per-channel variants, ``fp8_quant_gemm``.
 * ``quant_error`` (MSE) and ``quant_snr`` (dB).
 * ``quant8_quantize_tensor`` - the engines/quant facade: asymmetric uint8 affine or symmetric absmax.
 
-Reference counterparts: src/codec/codebook.cpp, vector_quantizer.cpp, quant_engines_{core,fp,quant,quant1,quant2,quant4,quant8}.cpp,
+Reference counterparts: src/kernel/kernel_tl.cpp (TL1 :12-89, TL2 :91-186), src/codec/codebook.cpp, vector_quantizer.cpp, quant_engines_{core,fp,quant,quant1,quant2,quant4,quant8}.cpp,
 include/quant/quant_engines.h, engines/quant/quantize.cpp."""
 from __future__ import annotations
 
@@ -254,6 +257,67 @@ class QuantEngine:
 
     quant_error = staticmethod(quant_error)
     quant_snr = staticmethod(quant_snr)
+
+
+class TernaryLUT:
+    """Row streams of ternary weights in the reference's two lookup-table layouts.
+
+    ``kind`` 1 (TL1): a row of K weights is ceil(K / 4) bytes, weight i in bits 2 (i % 4) .. of byte i / 4; the product
+    looks pairs of weights up in a 9-entry table of int8 activation sums, each entry saturated to [-128, 127].
+    ``kind`` 2 (TL2): 12 weights per 3 bytes (rows padded to whole 3-byte groups), triples looked up in 27-entry tables;
+    sums are kept in 32 bits.  Both quantise every activation row to int8 with scale 127 / max |a| and divide the integer
+    dot product by that scale."""
+
+    CODE = {-1: 0, 0: 1, 1: 2}
+
+    def __init__(self, kind: int = 1):
+        assert kind in (1, 2)
+        self.kind = kind
+
+    def row_bytes(self, K: int) -> int:
+        return (K + 3) // 4 if self.kind == 1 else (K + 11) // 12 * 3
+
+    def pack(self, t: torch.Tensor) -> torch.Tensor:
+        """t [rows, K] with values in {-1, 0, +1} -> uint8 [rows, row_bytes(K)] (padding weights are zeros: code 01)."""
+        rows, K = t.shape
+        rb = self.row_bytes(K)
+        codes = torch.ones((rows, rb * 4), dtype=torch.uint8, device=t.device)
+        codes[:, :K] = (t.to(torch.int16) + 1).to(torch.uint8)
+        c = codes.view(rows, rb, 4)
+        return c[..., 0] | (c[..., 1] << 2) | (c[..., 2] << 4) | (c[..., 3] << 6)
+
+    def unpack(self, packed: torch.Tensor, K: int) -> torch.Tensor:
+        """uint8 [rows, row_bytes(K)] -> int8 [rows, K]; the unused code 11 reads as +1, as in the reference's decoder."""
+        rows = packed.shape[0]
+        c = torch.stack([packed & 3, (packed >> 2) & 3, (packed >> 4) & 3, packed >> 6], -1).reshape(rows, -1)[:, :K]
+        return torch.where(c == 0, -1, torch.where(c == 1, 0, 1)).to(torch.int8)
+
+    def gemm(self, packed: torch.Tensor, a: torch.Tensor, K: int) -> torch.Tensor:
+        """out [rows_w, rows_a] = ternary rows x activation rows with the reference's integer arithmetic (see the class
+        docstring); ``a`` is [rows_a, K] floating point."""
+        w = self.unpack(packed, K).to(torch.int32)
+        af = a.detach().float()
+        scale = 127.0 / af.abs().amax(-1).clamp(min=1e-10)
+        ai = torch.round(af * scale[:, None]).to(torch.int32)
+        if self.kind == 2:
+            tot = w.to(torch.float64) @ ai.to(torch.float64).t()
+            return (tot / scale[None, :].double()).float()
+        Kp = K - (K % 2)
+        # pair sums saturate like the int8 table entries they stand for
+        ps = (w[:, None, 0:Kp:2] * ai[None, :, 0:Kp:2] + w[:, None, 1:Kp:2] * ai[None, :, 1:Kp:2]).clamp(-128, 127)
+        tot = ps.sum(-1)
+        if K % 2:
+            tot = tot + w[:, None, K - 1] * ai[None, :, K - 1]
+        return tot.float() / scale[None, :]
+
+    def to_packed_weight(self, packed: torch.Tensor, K: int, scale=1.0, group: int = 32):
+        """The stream as a ``quant.wq.PackedWeight`` (device ternary format: codes x one scale per group) for the
+        fused-dequant GEMM; ``scale``: a number or a per-row tensor that the ternary values are multiplied by."""
+        from . import wq
+        w = self.unpack(packed, K).float()
+        s = torch.as_tensor(scale, dtype=torch.float32, device=w.device)
+        s = s if s.dim() == 1 else s.expand(w.shape[0])
+        return wq.pack_weight(w * s[:, None], "ternary", group, row_scales=s)
 
 
 class Q1Engine:

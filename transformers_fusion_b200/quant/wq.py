@@ -43,8 +43,10 @@ class PackedWeight:
         return BITS[self.fmt] + 16.0 / self.group
 
 
-def _quantise(w: torch.Tensor, fmt: int, group: int, pow2_scales: bool):
-    """w [Np, Kp] fp32 -> (codes uint8 [Np, Kp] one code per element, scales fp32 [Np, Kp / group], dequantised fp32)."""
+def _quantise(w: torch.Tensor, fmt: int, group: int, pow2_scales: bool, given_scales=None):
+    """w [Np, Kp] fp32 -> (codes uint8 [Np, Kp] one code per element, scales fp32 [Np, Kp / group], dequantised fp32).
+    ``given_scales`` [Np, Kp / group]: use these instead of deriving them from the data (transcodes of streams that
+    carry their own scale)."""
     Np, Kp = w.shape
     g = w.view(Np, Kp // group, group)
     amax = g.abs().amax(-1, keepdim=True).clamp(min=1e-30)
@@ -52,7 +54,9 @@ def _quantise(w: torch.Tensor, fmt: int, group: int, pow2_scales: bool):
     s = amax / qmax
     if fmt == 4:
         s = g.abs().mean(-1, keepdim=True).clamp(min=1e-30) * 1.0    # ternary: scale = mean |w| (threshold at half of it)
-    if pow2_scales:
+    if given_scales is not None:
+        s = given_scales.reshape(Np, Kp // group, 1).float().clamp(min=1e-30)
+    elif pow2_scales:
         s = torch.exp2(torch.ceil(torch.log2(s)))
     s = s.to(torch.bfloat16).float()                                  # the kernel sees bf16 scales
     x = g / s
@@ -77,7 +81,9 @@ def _quantise(w: torch.Tensor, fmt: int, group: int, pow2_scales: bool):
     return codes.view(Np, Kp), s.view(Np, Kp // group), deq.reshape(Np, Kp)
 
 
-def pack_weight(w: torch.Tensor, fmt="int8", group: int = 64, pow2_scales: Optional[bool] = None) -> PackedWeight:
+def pack_weight(w: torch.Tensor, fmt="int8", group: int = 64, pow2_scales: Optional[bool] = None,
+                row_scales: Optional[torch.Tensor] = None) -> PackedWeight:
+    """``row_scales`` [N]: one scale per row, used for every group of that row instead of scales derived from the data."""
     f = FORMATS[fmt] if isinstance(fmt, str) else int(fmt)
     assert group in (32, 64)
     if pow2_scales is None:
@@ -86,7 +92,11 @@ def pack_weight(w: torch.Tensor, fmt="int8", group: int = 64, pow2_scales: Optio
     Np, Kp = (N + 127) // 128 * 128, (K + 63) // 64 * 64
     wp = torch.zeros((Np, Kp), dtype=torch.float32, device=w.device)
     wp[:N, :K] = w.float()
-    codes, scales, _ = _quantise(wp, f, group, pow2_scales)
+    given = None
+    if row_scales is not None:
+        given = torch.ones((Np, Kp // group), dtype=torch.float32, device=w.device)
+        given[:N] = row_scales.float().reshape(N, 1)
+    codes, scales, _ = _quantise(wp, f, group, pow2_scales, given)
     # pack codes along k
     # order inside a 32-bit word (see gemm_wq.cu): 4-bit: nibble j = element 2j, nibble j + 4 = element 2j + 1 (j < 4);
     # 2-bit: field j = element 2j, field j + 8 = element 2j + 1 (j < 8)
