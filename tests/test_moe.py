@@ -209,3 +209,51 @@ def test_structural_and_quantised_output_variants():
     # wherever it does not already sit on a level (small mixtures may all snap to the same level at initialisation)
     for name in ("PRODUCT_KEY", "ATTENTION_MOE", "LOWRANK_MOE", "DOMAIN_MOE", "Q1_MOE", "Q8_MOE"):
         assert ces[name] != ces["SPARSE_TOPK"], (name, ces)
+
+
+def test_cross_layer_multi_gate_and_state_variants():
+    """CROSS_LAYER: every layer routes into one shared pool of experts (routers cycle over num_shared_layers); MMOE: the
+    gate of the selected task routes; MAMBA_MOE: a tiled state projection is added in front of router and experts."""
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.moe import MoEAllConfig, create_moe_variant
+    base = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=3, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(1))
+    lab = torch.roll(ids, -1, 1)
+
+    def make(name, **kw):
+        return create_moe_variant(name, base, MoEAllConfig(num_experts=8, top_k=2, expert_hidden=32, **kw), device="cpu",
+                                  dtype=torch.float32, seed=0)
+    plain = make("SPARSE_TOPK")
+    cross = make("CROSS_LAYER", num_shared_layers=2)
+    assert cross.layers[1].gate_up is cross.layers[0].gate_up and cross.layers[2].down is cross.layers[0].down
+    assert cross.layers[2].router is cross.layers[0].router and cross.layers[1].router is not cross.layers[0].router
+    n_plain = sum(p.numel() for p in plain.parameters())
+    n_cross = sum(p.numel() for p in cross.parameters())
+    assert n_cross < n_plain - 2 * cross.layers[0].gate_up.numel()            # two layers' experts (and one router) are gone
+    cross.flatten()
+    loss, _, _ = cross.loss(ids, lab)
+    loss.backward()
+    assert torch.isfinite(loss) and float(cross.layers[0].gate_up.main_grad.abs().sum()) > 0
+    assert len([n for n, _ in cross.named_tensors() if "expert.0.gate_proj" in n]) == 3   # the file still lists every layer
+
+    mm = make("MMOE", num_tasks=3)
+    mm.flatten()
+    outs = []
+    for tid in (0, 1):
+        for blk in mm.layers:
+            blk.task_id = tid
+        outs.append(mm(ids).detach())
+    assert not torch.allclose(outs[0], outs[1])                               # another task, another gate
+    loss, _, _ = mm.loss(ids, lab)
+    loss.backward()
+    g = mm.layers[0].task_gates.grad.view(3, 8, -1).abs().sum((1, 2))
+    assert float(g[1]) > 0 and float(g[0]) == 0 and float(g[2]) == 0          # only the selected task's gate learns
+
+    mb = make("MAMBA_MOE")
+    mb.flatten()
+    loss, ce, _ = mb.loss(ids, lab)
+    loss.backward()
+    assert torch.isfinite(loss) and mb.layers[0].ssm_proj.grad is not None and float(mb.layers[0].ssm_proj.grad.abs().sum()) > 0
+    _, ce_plain, _ = plain.loss(ids, lab)
+    assert float(ce.detach()) != float(ce_plain.detach())

@@ -134,7 +134,16 @@ class MoEBlock(nn.Module):
         self.ep = None            # parallel.ep.ExpertParallel when experts are sharded across ranks
         # variant-specific parameters (reference: src/model/moe_variants.cpp:990-1150)
         variant = cfg.variant.upper()
-        self.router_k = self.lowrank_down = self.lowrank_up = self.domain_classifier = None
+        self.router_k = self.lowrank_down = self.lowrank_up = self.domain_classifier = self.task_gates = self.ssm_proj = None
+        self.task_id = 0                          # MMOE: which task's gate routes (set by the caller per batch)
+        if variant == "MMOE":                     # one gate per task over the shared experts
+            self.num_tasks = max(1, getattr(cfg, "num_tasks", 0) or 2)
+            self.task_gates = nn.Parameter(torch.empty(self.num_tasks * E, H, **kw))
+        elif variant == "MAMBA_MOE":              # a state projection, tiled back over the hidden dimension, is added to x
+            st = 64 if H % 64 == 0 else max(8, H // 8 // 8 * 8)
+            while H % st:
+                st -= 8
+            self.ssm_proj = nn.Parameter(torch.empty(max(st, 8), H, **kw))
         if variant == "ATTENTION_MOE":            # routing score = (x Wq) * (x Wk) * sqrt(H), element-wise per expert
             self.router_k = nn.Parameter(torch.empty(E, H, **kw))
         elif variant == "LOWRANK_MOE":            # router and experts see x pushed through a rank-r bottleneck
@@ -238,6 +247,13 @@ class MoEBlock(nn.Module):
             if variant == "LOWRANK_MOE":
                 xin = _LinearAG.apply(_LinearAG.apply(f, self.lowrank_down), self.lowrank_up)
                 logits = _LinearAG.apply(xin, self.router).float()
+            elif variant == "MAMBA_MOE":
+                st = self.ssm_proj.shape[0]
+                xin = f + _LinearAG.apply(f, self.ssm_proj).repeat(1, cfg.hidden_size // st)   # state j feeds dims d with d % st == j
+                logits = _LinearAG.apply(xin, self.router).float()
+            elif variant == "MMOE":
+                tid = self.task_id if 0 <= self.task_id < self.num_tasks else 0
+                logits = _LinearAG.apply(f, self.task_gates[tid * E:(tid + 1) * E]).float()
             y, aux, idx = experts(xin, logits, 0, E, min(k, 8))
         if covered is not None:
             y = y * covered[:, None].to(y.dtype)               # tokens that no expert serves contribute nothing
@@ -290,6 +306,15 @@ class MoEModel(DenseModel):
         self.tok_embeddings = nn.Parameter(torch.empty(V, H, **kw))
         self.pos_embeddings = None
         self.layers = nn.ModuleList([MoEBlock(cfg, device, dtype) for _ in range(cfg.num_layers)])
+        if cfg.variant.upper() == "CROSS_LAYER":
+            # one pool of experts serves every layer; the routers cycle over num_shared_layers layers
+            # (reference: CrossLayerMoE, src/model/moe_variants.cpp:579-614)
+            nsl = max(1, getattr(cfg, "num_shared_layers", 0) or cfg.num_layers)
+            for i, blk in enumerate(self.layers):
+                if i > 0:
+                    blk.gate_up, blk.down = self.layers[0].gate_up, self.layers[0].down
+                if i >= nsl:
+                    blk.router = self.layers[i % nsl].router
         self.norm = nn.Parameter(torch.ones(H, **kw))
         self.norm_bias = None
         self.lm_head = self.tok_embeddings if cfg.tie_embeddings else nn.Parameter(torch.empty(V, H, **kw))
@@ -362,7 +387,7 @@ class MoEModel(DenseModel):
                 ep = pre + f"moe.expert.{e}."
                 out += [(ep + "gate_proj.weight", l.gate_up.data[e, :Fe]), (ep + "up_proj.weight", l.gate_up.data[e, Fe:]),
                         (ep + "down_proj.weight", l.down.data[e])]
-            for nm in ("router_k", "lowrank_down", "lowrank_up", "domain_classifier"):
+            for nm in ("router_k", "lowrank_down", "lowrank_up", "domain_classifier", "task_gates", "ssm_proj"):
                 if getattr(l, nm, None) is not None:
                     out.append((pre + f"moe.{nm}.weight", getattr(l, nm).data))
             if l.shared_gate_up is not None:
@@ -395,6 +420,8 @@ class MoEAllConfig:
     num_shared_experts: int = 0
     num_groups: int = 0                     # HIERARCHICAL / MOMOE: 0 = about sqrt(num_experts)
     num_domains: int = 4                    # DOMAIN_MOE: expert groups mixed by the domain classifier
+    num_tasks: int = 2                      # MMOE: gates (one per task) over the shared experts
+    num_shared_layers: int = 0              # CROSS_LAYER: routers cycle over this many layers (0 = one per layer)
     top_groups: int = 0                     # 0 = top_k
     top_experts_per_group: int = 1
 
@@ -414,5 +441,5 @@ def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfi
                     load_balance_weight=m.load_balance_weight, router_z_weight=m.router_z_weight, capacity_factor=m.capacity_factor,
                     capacity_policy=m.capacity_policy, variant=name)
     cfg.num_groups, cfg.top_groups, cfg.top_experts_per_group = m.num_groups, m.top_groups, m.top_experts_per_group
-    cfg.num_domains = m.num_domains
+    cfg.num_domains, cfg.num_tasks, cfg.num_shared_layers = m.num_domains, m.num_tasks, m.num_shared_layers
     return MoEModel(cfg, **model_kw)
