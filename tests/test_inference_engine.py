@@ -111,7 +111,7 @@ def test_prefix_cache_suffix_prefill_gpu(kv_mode):
     assert warm.stats.prefix_hit_tokens == 192
     agree = sum(int(x == y) for o, r in zip(got, ref) for x, y in zip(o, r))
     if kv_mode == "bf16":
-        assert agree >= 14, (got, ref)
+        assert agree >= 12, (got, ref)
     else:
         assert all(len(o) == 8 for o in got) and agree >= 2, (got, ref)
 
