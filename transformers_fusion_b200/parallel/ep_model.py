@@ -51,9 +51,14 @@ class EPTrainer:
     """Fused AdamW (fp32 masters, one kernel over the flat buffer) over the replicated tensors and this rank's experts.
     The clipping norm is global: the replicated part once plus every rank's expert part."""
 
-    def __init__(self, model, expert_params: List[nn.Parameter], lr=3e-4, weight_decay=0.01, max_grad_norm=1.0, group=None):
+    def __init__(self, model, expert_params: List[nn.Parameter], lr=3e-4, weight_decay=0.01, max_grad_norm=1.0, group=None,
+                 replica_group=None, replicas: int = 1):
+        """``group``: every rank of the job (the replicated tensors are averaged over it).  When the expert-parallel
+        degree is smaller than the job (``replicas`` = world / ep copies of every expert), ``replica_group`` holds the
+        ranks that own the same experts as this one: their expert gradients are summed over it."""
         from ..trainer.fused_optim import FlatAdamW
         self.model, self.group = model, group
+        self.replica_group, self.replicas = replica_group, max(1, int(replicas))
         ids = {id(p) for p in expert_params}
         self.experts = list(expert_params)
         self.shared = [p for p in model.parameters() if id(p) not in ids]
@@ -89,7 +94,8 @@ class EPTrainer:
         own = torch.stack([p.main_grad.pow(2).sum() for p in self.experts]).sum().reshape(1)
         v = torch.cat([sumsq.reshape(1) - own, own])
         dist.all_reduce(v, group=self.group)
-        sumsq.copy_((v[0] / self.world + v[1]).reshape(sumsq.shape))
+        # the replicated part was counted by every rank, each distinct expert by each of its `replicas` owners
+        sumsq.copy_((v[0] / self.world + v[1] / self.replicas).reshape(sumsq.shape))
 
     @property
     def grad_norm(self) -> float:
@@ -102,6 +108,9 @@ class EPTrainer:
         if W > 1:
             for g in self._shared_runs():
                 dist.all_reduce(g, group=self.group)
+            if self.replicas > 1:
+                for p in self.experts:
+                    dist.all_reduce(p.main_grad, group=self.replica_group)
             m.flat.grads.div_(W)
             dist.all_reduce(lt, group=self.group)
         self.opt.step(lr)                                   # clips, updates, refreshes the bf16 weights, zeroes the gradients

@@ -9,7 +9,7 @@ fastest (tensor-parallel peers exchange the most data per step), then dp, then p
   tp > 1 or zero stage 3   ShardedEngine: ZeRO-3 over the dp ranks x tensor + sequence parallelism over the tp ranks
                   (weight gather, all-gather->GEMM and GEMM->reduce-scatter inside the GEMM launches; symmetric heaps per
                   dp group and per tp group).  Model shapes it does not cover fall back to TPDenseModel + TPTrainer.
-  ep > 1          MoE model with the experts of every layer spread over the ranks (fused dispatch / combine), EPTrainer
+  ep > 1          MoE model with the experts of every layer spread over groups of ep ranks (fused dispatch / combine; ep < world: replicas), EPTrainer
   pp > 1          PipelineParallel 1F1B over the layer ranges, AdamW on the parameters each stage owns
   otherwise       the ordinary Trainer: data parallel with ZeRO stage 0 / 1 / 2 (fused reduce-scatter + AdamW)
 
@@ -187,14 +187,28 @@ def fit_parallel(model, tok, data_path: str, cfg, st: ParallelState, log: Option
             Trainer(model, tok).compile("adamw", _single(cfg)).save_checkpoint(cfg.checkpoint_path)
         return loss
     if st.ep > 1:
-        # expert parallel over all ranks (which are also the data-parallel ranks of the replicated tensors)
-        if st.ep != st.world or not hasattr(model.cfg, "num_experts") or st.device.type != "cuda":
-            raise ValueError("--ep needs a mixture-of-experts model on CUDA and ep equal to the number of ranks")
+        # expert parallel: every rank is a data-parallel rank of the replicated tensors; the experts of a layer are spread
+        # over groups of `ep` consecutive ranks, and with ep < world every expert has world / ep replicas whose gradients
+        # are summed over the ranks that hold the same experts
+        if st.world % st.ep or st.tp > 1 or st.pp > 1 or not hasattr(model.cfg, "num_experts") or st.device.type != "cuda":
+            raise ValueError("--ep needs a mixture-of-experts model on CUDA, tp = pp = 1 and ep dividing the number of ranks")
         from .ep_model import EPTrainer, attach_expert_parallel
         from .symm import SymmetricHeap
-        symm = SymmetricHeap(st.rank, st.world, st.device)
-        experts = attach_expert_parallel(model, symm, st.rank, st.world, cfg.batch_size * cfg.seq_length)
-        tr = EPTrainer(model, experts, cfg.learning_rate, cfg.weight_decay, cfg.max_grad_norm)
+        ep_rank, replicas = st.rank % st.ep, st.world // st.ep
+        ep_group = replica_group = None
+        if replicas > 1:
+            for g in range(replicas):
+                grp = dist.new_group(list(range(g * st.ep, (g + 1) * st.ep)))
+                if st.rank // st.ep == g:
+                    ep_group = grp
+            for e in range(st.ep):
+                grp = dist.new_group([e + g * st.ep for g in range(replicas)])
+                if ep_rank == e:
+                    replica_group = grp
+        symm = SymmetricHeap(ep_rank, st.ep, st.device, group=ep_group)
+        experts = attach_expert_parallel(model, symm, ep_rank, st.ep, cfg.batch_size * cfg.seq_length)
+        tr = EPTrainer(model, experts, cfg.learning_rate, cfg.weight_decay, cfg.max_grad_norm, replica_group=replica_group,
+                       replicas=replicas)
         for step in range(1, steps + 1):
             ids, labels = dl.next_batch()
             loss = tr.train_step(ids, labels, lr_at(step))
