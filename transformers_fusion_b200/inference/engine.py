@@ -22,6 +22,7 @@ import heapq
 import itertools
 import math
 import time
+import weakref
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional
 
@@ -121,6 +122,29 @@ class PrefixCache:
         self.table.clear()
 
 
+class _TokenBuffers(list):
+    """A claimed pair of pinned buffers; when the engine that holds it goes away the pair is free for the next engine."""
+
+
+_PINNED_TOKENS: Dict[int, list] = {}        # device index -> [(weak reference to the claiming _TokenBuffers, [buf, buf])]
+
+
+def _pinned_token_buffers(dev, n: int) -> _TokenBuffers:
+    """Two pinned int64 buffers of at least n entries for the device -> host copy of a step's sampled ids.  The memory is
+    kept for the life of the process and handed from engine to engine instead of being freed: a pinned block pending
+    release makes the host allocator record and query events, and such calls disturb a stream capture in progress."""
+    pool = _PINNED_TOKENS.setdefault(dev.index if dev.index is not None else torch.cuda.current_device(), [])
+    for i, (owner, bufs) in enumerate(pool):
+        if owner() is None and bufs[0].numel() >= n:
+            break
+    else:
+        i, bufs = len(pool), [torch.empty(max(n, 64), dtype=torch.int64).pin_memory() for _ in range(2)]
+        pool.append(None)
+    held = _TokenBuffers(bufs)
+    pool[i] = (weakref.ref(held), bufs)
+    return held
+
+
 class _DecodeGraph:
     """One captured decode step (all layers + final norm + LM head) for a fixed batch-size bucket.  Inputs live in static
     device buffers that the scheduler fills before each replay; rows past the live batch carry slot -1 (no KV write)
@@ -145,7 +169,10 @@ class _DecodeGraph:
         self._last_n = -1
         self.eng = eng
         self.token = eng._graph_capture_begin()
-        with torch.cuda.graph(self.graph):
+        # "relaxed": API calls that a capture in the default (global) mode forbids process-wide - an event query or a free by
+        # the pinned-memory allocator on any thread, for instance, once pinned buffers of an earlier engine are pending
+        # release - would invalidate the capture; nothing captured here depends on them
+        with torch.cuda.graph(self.graph, capture_error_mode="relaxed"):
             self.logits = run()
             eng._graph_capture_end(self.token)
 
@@ -517,7 +544,7 @@ class InferenceEngine:
                 host = ev = None
                 if dev.type == "cuda":
                     if self._tok_host is None:
-                        self._tok_host = [torch.empty(self.cfg.max_batch, dtype=torch.int64).pin_memory() for _ in range(2)]
+                        self._tok_host = _pinned_token_buffers(dev, self.cfg.max_batch)
                     self._tok_flip = getattr(self, "_tok_flip", 0) ^ 1  # never the buffer the previous step is still read from
                     host = self._tok_host[self._tok_flip][:len(reqs)]
                     host.copy_(toks_dev, non_blocking=True)
