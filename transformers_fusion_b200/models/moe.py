@@ -283,7 +283,7 @@ class MoEBlock(nn.Module):
             gu = _LinearAG.apply(f, self.shared_gate_up)
             Fh = gu.shape[1] // 2
             y = y + _LinearAG.apply((TF.silu(gu[:, :Fh].float()) * gu[:, Fh:].float()).to(f.dtype), self.shared_down)
-        self.last_idx = idx
+        self.last_idx, self.last_logits, self.last_covered = idx, logits.detach(), covered
         return y, aux
 
     def forward(self, h, B, S, rope):
