@@ -56,3 +56,106 @@ def test_offload_and_checkpointing_helpers():
     ac = ActivationCheckpointing(m).enable()
     assert m.activation_checkpointing and ac.memory_saved_bytes(2, 16) > 0
     assert FullyShardedDataParallel.auto_wrap(m, 1000) == ["layers.0", "layers.1", "layers.2"]
+
+
+def test_facade_two_call_form_precision_helpers_and_shard_optimizer(capsys):
+    """forward(); backward() equals train_step's gradients; flat shard view, memory print, per-block accounting, the
+    explicit save_input / recompute form and the per-shard optimizer (plain and with an fp32 master)."""
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.parallel.collectives import DistributedContext
+    from transformers_fusion_b200.parallel.fsdp import (ActivationCheckpointing, FSDPBlock, FSDPConfig,
+                                                       FullyShardedDataParallel, ZeROOptimizer)
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, ffn_hidden_size=64, max_seq_len=16)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(1))
+    lab = torch.roll(ids, -1, 1)
+
+    def make():
+        f = FullyShardedDataParallel(DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0),
+                                     FSDPConfig(lr=1e-2, weight_decay=0.0), DistributedContext(0, 1))
+        f.engine.mesh.world_group = None
+        return f
+    a, b = make(), make()
+    logits = a.forward(ids, lab)
+    assert logits.shape == (2, 16, 64)
+    la = a.backward()
+    a.optimizer_step()
+    lb = b.train_step(ids, lab)
+    assert float(la) == pytest.approx(float(lb), abs=1e-6)
+    assert torch.allclose(a.flatten_and_shard(), b.flatten_and_shard(), atol=1e-6)
+    with pytest.raises(RuntimeError):
+        a.backward()                                                   # the batch was consumed
+    assert a.stage() == 3 and a.world_size() == 1 and a.world_rank() == 0 and a.is_mixed_precision()
+    assert a.to_fp32(a.to_fp16(torch.ones(3))).dtype == torch.float32
+    a.unflatten_params()
+    text = a.print_memory_profile()
+    assert "optimizer state" in text and "unsharded total" in capsys.readouterr().out
+    blk = FSDPBlock(a, 0)
+    assert blk.memory_usage() > 0 and len(blk.sync_gradients()) == len(blk.weights)
+    # explicit activation checkpointing: the recomputed output carries gradients back to the saved input
+    lin = torch.nn.Linear(8, 8)
+    ac = ActivationCheckpointing()
+    x = torch.randn(4, 8)
+    ac.save_input(3, x)
+    assert ac.saved_memory() == x.numel() * 4
+    y = ac.recompute(lin, 3)
+    y.sum().backward()
+    assert torch.allclose(y, lin(x)) and lin.weight.grad is not None
+    ac.clear()
+    assert ac.saved_memory() == 0
+    # per-shard optimizer: both forms descend on a quadratic; the mixed form keeps the master exact and the shard rounded
+    opt = ZeROOptimizer(lr=5e-2, weight_decay=0.0)
+    w = torch.randn(16, 8, generator=torch.Generator().manual_seed(2))
+    target = torch.zeros_like(w)
+    w_lp, master = w.to(torch.bfloat16), w.clone()
+    start = float(w.pow(2).sum())
+    for t in range(1, 60):
+        opt.step(w, 2 * (w - target), t)
+        opt.step_mixed(w_lp, master, 2 * (master - target), t)
+    assert float(w.pow(2).sum()) < 0.2 * start and float(master.pow(2).sum()) < 0.2 * start
+    assert torch.equal(w_lp, master.to(torch.bfloat16))
+    opt.set_param_count(128)
+    assert opt.param_count() == 128
+
+
+def test_zero_optimizer_stage3_verbs_single_process():
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.parallel.fsdp import ZeroOptimizer
+    m = DenseModel(TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=16),
+                   device="cpu", dtype=torch.float32, seed=0)
+    z = ZeroOptimizer(m, 0, 1, lr=1e-2, stage=2)
+    z.set_grad_clip_norm(0.5)
+    ids = torch.randint(0, 64, (2, 16))
+    m.forward_backward(ids, torch.roll(ids, -1, 1))
+    n = z.clip_grad_norm()
+    assert n > 0.5 and float(m.flat.grads.norm()) == pytest.approx(0.5, rel=1e-4)
+    assert z.reduce_scatter_grads().numel() == z.num_owned() and z.all_gather_params() is m.flat.params
+    assert z.state_bytes_owned() == z.state_bytes_full() and z.world_size() == 1
+
+
+def test_activation_checkpoint_regions_measure_and_place():
+    from transformers_fusion_b200.parallel.fsdp import ActivationCheckpoint, MemoryBudget
+    ac = ActivationCheckpoint()
+    blocks = [torch.nn.Sequential(torch.nn.Linear(32, w), torch.nn.GELU(), torch.nn.Linear(w, 32)) for w in (64, 256, 128)]
+    x = torch.randn(16, 32, requires_grad=True)
+    h = x
+    for i, blk in enumerate(blocks):
+        with ac.region(f"block{i}") as info:
+            h = blk(h)
+        assert not ac.in_checkpoint_region()
+    sizes = [r.forward_activations_bytes for r in ac.regions()]
+    # each block saves its input [16, 32], the pre-activation and the activation [16, w]: 4 bytes each
+    assert sizes == [16 * (32 + 2 * w) * 4 for w in (64, 256, 128)]
+    assert ac.auto_place_checkpoints() == []                           # no budget: nothing to do
+    total = sum(sizes)
+    ac.set_budget(MemoryBudget(total_bytes=total + 1000, param_bytes=600, grad_bytes=300, opt_state_bytes=100 + sizes[1] - 10))
+    assert ac.auto_place_checkpoints() == ["block1"]                   # dropping the largest region is enough
+    assert ac.estimated_savings_all() == sizes[1] and ac.budget.activation_bytes == total - sizes[1]
+    ac.begin_region("declared", "FULL", activation_bytes=4096, recompute_flops=8192)
+    assert ac.in_checkpoint_region()
+    ac.end_region()
+    assert ac.total_activations_saved() == sizes[1] + 4096 and ac.compute_overhead() == pytest.approx((1 + 8192) / (sizes[1] + 4096))
+    assert ActivationCheckpoint.estimate_layer_activations(2, 128, 64, 256) == 2 * 128 * (512 + 768) * 2
+    ac.reset()
+    assert ac.regions() == [] and ac.compute_overhead() == 0.0

@@ -49,6 +49,10 @@ class DistributedContext:
     def is_distributed(self):
         return self.world_size > 1 and dist.is_initialized()
 
+    @property
+    def world_rank(self) -> int:
+        return self.rank
+
     def all_reduce(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
         if self.is_distributed:
             dist.all_reduce(t, op=_TORCH_OPS[op], group=self.group)

@@ -88,11 +88,26 @@ class FullyShardedDataParallel:
         block's backward is complete (reduce_scatter_grads of the reference, fsdp.cpp:508-543)."""
         return self.engine.forward_backward(ids, labels)
 
-    def forward(self, ids):
-        """Logits [B, S, V] of the current weights (gathers the whole model into ``self.model``: evaluation helper)."""
+    def forward(self, ids, labels=None):
+        """Logits [B, S, V] of the current weights (gathers the whole model into ``self.model``: evaluation helper).  The
+        batch is remembered, so that the reference's two-call form ``forward(ids); backward()`` works (fsdp.h:46-52)."""
+        self._pending = (ids, labels)
         self.consolidate()
         with torch.no_grad():
             return self.model.forward(ids)
+
+    def backward(self, loss_value=None, labels=None):
+        """Gradients of the batch last given to ``forward`` (labels: those given there or here, else the ids shifted left
+        by one).  The engine's step is one fused forward + backward with the per-unit reduce-scatter issued as backward
+        proceeds, so this runs that step; ``loss_value`` is accepted for signature parity and not needed.  Returns the loss."""
+        ids, lab = getattr(self, "_pending", (None, None))
+        if ids is None:
+            raise RuntimeError("backward() needs a batch: call forward(ids) first")
+        lab = labels if labels is not None else lab
+        if lab is None:
+            lab = torch.cat([ids[:, 1:], torch.full_like(ids[:, :1], -100)], 1)
+        self._pending = (None, None)
+        return self.forward_backward(ids, lab)
 
     def optimizer_step(self, lr: Optional[float] = None):
         self.step_count += 1
@@ -130,6 +145,40 @@ class FullyShardedDataParallel:
         mp.total = mp_["total"]
         return mp
 
+    def print_memory_profile(self, file=None):
+        mp = self.profile_memory()
+        un = self.engine.memory_profile()["unsharded_total"]
+        rows = [("parameters (+ gather buffers)", mp.parameters), ("gradients", mp.gradients),
+                ("optimizer state", mp.optimizer_state), ("total", mp.total), ("unsharded total", un)]
+        lines = [f"FSDP memory, rank {self.rank} of {self.world} (stage {self.cfg.stage}):"]
+        lines += [f"  {k:<32}{v / 2**20:12.1f} MiB" for k, v in rows]
+        text = "\n".join(lines)
+        print(text, file=file)
+        return text
+
+    # ---- mixed precision / flat views ----------------------------------------------------------------------------
+    def stage(self) -> int: return self.cfg.stage
+    def is_mixed_precision(self) -> bool: return self.cfg.mixed_precision
+    def world_size(self) -> int: return self.world
+    def world_rank(self) -> int: return self.rank
+
+    def to_fp16(self, t: torch.Tensor) -> torch.Tensor:
+        """The compute-precision copy of a tensor: the dtype of the engine's weight shards (bf16 on the GPU path; the
+        reference's name is kept, fsdp.h:64)."""
+        return t.to(self.engine.shard_lp.dtype) if self.cfg.mixed_precision else t
+
+    def to_fp32(self, t: torch.Tensor) -> torch.Tensor:
+        return t.float()
+
+    def flatten_and_shard(self) -> torch.Tensor:
+        """This rank's flat fp32 master shard of every sharded matrix (one contiguous buffer: the engine flattens and
+        shards at construction; this hands out the view, fsdp.h:75)."""
+        return self.engine.master
+
+    def unflatten_params(self):
+        """Write the full, unflattened weights back into the wrapped model (every rank ends with the whole model)."""
+        return self.consolidate()
+
     def memory_savings_ratio(self) -> float:
         """Fraction of the parameter + optimizer-state bytes this rank does not hold."""
         e = self.engine
@@ -165,16 +214,48 @@ class FSDPBlock:
         e = self.fsdp.engine
         return [e.gshard[p.shard_off:p.shard_off + p.per * p.cols].view(p.per, p.cols) for p in self.weights]
 
+    def sync_gradients(self):
+        """The block's gradients are reduce-scattered by the engine as soon as the block's backward is done; this returns
+        the reduced shards (nothing is left to synchronise afterwards)."""
+        return self.shard_gradients()
+
+    def memory_usage(self) -> int:
+        """Bytes this rank holds for the block: weight shards, fp32 master + two Adam moments, reduced gradient shards."""
+        e = self.fsdp.engine
+        n = sum(p.per * p.cols for p in self.weights)
+        return n * (e.shard_lp.element_size() + 12 + 4)
+
 
 class ActivationCheckpointing:
     """Switch recomputation of block activations in the backward pass on or off for a model."""
 
-    def __init__(self, model):
+    def __init__(self, model=None):
         self.model = model
+        self._saved: Dict[int, torch.Tensor] = {}
 
     def enable(self, on: bool = True):
         self.model.activation_checkpointing = bool(on)
         return self
+
+    # ---- explicit form (reference: fsdp.h:204-231): keep only a layer's input, run the layer again when needed
+    def save_input(self, layer_idx: int, x: torch.Tensor):
+        if not hasattr(self, "_saved"):
+            self._saved = {}
+        self._saved[int(layer_idx)] = x.detach()
+
+    def recompute(self, block, layer_idx: int, *args, **kw):
+        """Run ``block`` again from the input saved for ``layer_idx`` (with autograd on, so that the caller can
+        back-propagate through the recomputed activations); extra arguments are passed to the block."""
+        x = self._saved[int(layer_idx)].requires_grad_(True)
+        with torch.enable_grad():
+            return block(x, *args, **kw)
+
+    def clear(self):
+        self._saved = {}
+
+    def saved_memory(self) -> int:
+        """Bytes held by the saved inputs."""
+        return sum(t.numel() * t.element_size() for t in getattr(self, "_saved", {}).values())
 
     def memory_saved_bytes(self, batch, seq):
         cfg = self.model.cfg
@@ -235,6 +316,93 @@ class ZeroOptimizer:
 
     def zero_grad(self):
         self.model.flat.zero_grad()
+
+    # ---- the stage-3 verbs of the reference (zero_optimizer.h:48-52) over the flat buffers --------------------------
+    def rank_(self) -> int: return self.rank
+    def world_size(self) -> int: return self.world
+    def step_count(self) -> int: return int(getattr(self.engine, "steps", 0))
+
+    def all_gather_params(self):
+        """Every rank receives every owner's slice of the flat parameter buffer (after a sharded update the engine does
+        this inside its fused step; the call is for callers that changed their shard themselves)."""
+        if self.world > 1 and dist.is_initialized():
+            flat = self.model.flat.params
+            n = flat.numel()
+            per = -(-n // self.world)
+            pad = torch.zeros(per * self.world, dtype=flat.dtype, device=flat.device)
+            pad[:n].copy_(flat)
+            mine = pad[self.rank * per:(self.rank + 1) * per].clone()
+            dist.all_gather_into_tensor(pad, mine) if pad.is_cuda else dist.all_gather(list(pad.view(self.world, per).unbind(0)), mine)
+            flat.copy_(pad[:n])
+        return self.model.flat.params
+
+    def reduce_scatter_grads(self):
+        """Average the flat gradient over the ranks and return this rank's slice of it."""
+        g = self.model.flat.grads
+        lo, hi = self.engine.shard
+        if self.world > 1 and dist.is_initialized():
+            dist.all_reduce(g)
+            g.div_(self.world)
+        return g[lo:hi]
+
+    def clip_grad_norm(self) -> float:
+        """Scale the gradients so that their global norm does not exceed the configured threshold; returns the norm."""
+        g = self.model.flat.grads
+        norm = float(g.norm())
+        mx = float(getattr(self.engine.opt, "max_grad_norm", 0.0) or 0.0)
+        if mx > 0 and norm > mx:
+            g.mul_(mx / (norm + 1e-6))
+        return norm
+
+    def state_bytes_owned(self) -> int: return self.num_owned() * 12
+    def state_bytes_full(self) -> int: return self.model.flat.params.numel() * 12
+
+
+class ShardOptimizer:
+    """Optimizer for one rank's parameter shards, called shard by shard (the reference's ``ZeROOptimizer``,
+    fsdp.h:233-268: Adafactor with a persistent factored state per shard buffer).  ``step`` updates a shard in place;
+    ``step_mixed`` updates an fp32 master and writes its rounded value into the lower-precision shard."""
+
+    def __init__(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-2, world_size=1, world_rank=0):
+        self.lr, self.beta1, self.beta2, self.eps, self.wd = lr, beta1, beta2, eps, weight_decay
+        self.world_size, self.world_rank = world_size, world_rank
+        self._state: Dict[int, dict] = {}
+        self._count = 0
+
+    def param_count(self) -> int: return self._count
+    def set_param_count(self, n: int): self._count = int(n)
+
+    def _update(self, key: int, w32: torch.Tensor, g: torch.Tensor, step_num: int) -> torch.Tensor:
+        g = g.float()
+        st = self._state.setdefault(key, {})
+        rho = min(self.beta2, 1.0 - (max(1, step_num)) ** -0.8)       # Adafactor's increasing decay
+        g2 = g * g + 1e-30
+        if g.dim() == 2 and min(g.shape) > 1:                           # factored second moment: row and column means
+            r = st.setdefault("r", torch.zeros(g.shape[0], device=g.device))
+            c = st.setdefault("c", torch.zeros(g.shape[1], device=g.device))
+            r.mul_(rho).add_(g2.mean(1), alpha=1 - rho)
+            c.mul_(rho).add_(g2.mean(0), alpha=1 - rho)
+            v = torch.outer(r, c) / r.mean().clamp(min=1e-30)
+        else:
+            v = st.setdefault("v", torch.zeros_like(g))
+            v.mul_(rho).add_(g2, alpha=1 - rho)
+        u = g / (v.sqrt() + self.eps)
+        u = u / max(1.0, float(u.pow(2).mean().sqrt()))                 # update clipping at RMS 1
+        if self.wd:
+            w32.mul_(1.0 - self.lr * self.wd)
+        return w32.add_(u, alpha=-self.lr)
+
+    @torch.no_grad()
+    def step(self, param_shard: torch.Tensor, grad_shard: torch.Tensor, step_num: int):
+        w = self._update(param_shard.data_ptr(), param_shard.float(), grad_shard, step_num)
+        param_shard.copy_(w.to(param_shard.dtype))
+        return param_shard
+
+    @torch.no_grad()
+    def step_mixed(self, param_shard: torch.Tensor, fp32_master: torch.Tensor, grad_shard: torch.Tensor, step_num: int):
+        self._update(fp32_master.data_ptr(), fp32_master, grad_shard, step_num)
+        param_shard.copy_(fp32_master.to(param_shard.dtype))
+        return param_shard
 
 
 class CPUOffloadEngine:
@@ -312,7 +480,7 @@ class ZeROOffloadManager:
         return r
 
 
-ZeROOptimizer = ZeroOptimizer
+ZeROOptimizer = ShardOptimizer
 
 
 class GradientCheckpointManager:
@@ -352,3 +520,136 @@ class GradientCheckpointManager:
         if hasattr(model, "activation_checkpointing"):
             model.activation_checkpointing = all(self.checkpointed) and bool(self.checkpointed)
         return list(self.checkpointed)
+
+
+@dataclass
+class MemoryBudget:
+    total_bytes: int = 0              # 0 = unlimited
+    activation_bytes: int = 0
+    param_bytes: int = 0
+    grad_bytes: int = 0
+    opt_state_bytes: int = 0
+
+    def usage_ratio(self) -> float:
+        return (self.activation_bytes + self.param_bytes + self.grad_bytes + self.opt_state_bytes) / max(1, self.total_bytes)
+
+
+@dataclass
+class RegionInfo:
+    name: str
+    forward_activations_bytes: int = 0
+    recompute_cost_flops: int = 0
+    is_checkpointed: bool = False
+    mode: str = "NONE"                # NONE | FULL | PARTIAL | BALANCED
+
+
+class ActivationCheckpoint:
+    """Named regions of the forward pass with the bytes each keeps for backward, and a placement rule that marks regions
+    for recomputation until the activations fit what the budget leaves after parameters, gradients and optimizer state
+    (largest regions first).  Reference counterpart: ActivationCheckpoint, include/quant/zero_optimizer.h:356-437 and
+    src/trainer/zero_optimizer_mem.cpp:580-705.
+
+    A region is either declared (``begin_region(name, mode, activation_bytes=, recompute_flops=)`` ... ``end_region()``)
+    or measured: ``with ac.region(name): y = block(x)`` counts the bytes autograd saves inside the block."""
+
+    MODES = ("NONE", "FULL", "PARTIAL", "BALANCED")
+
+    def __init__(self, budget: Optional[MemoryBudget] = None):
+        self.budget = budget or MemoryBudget()
+        self.reset()
+
+    def reset(self):
+        self._regions: List[RegionInfo] = []
+        self._stack: List[RegionInfo] = []
+        self.total_saved = self.total_recomputed = 0
+
+    def set_budget(self, b: MemoryBudget): self.budget = b
+    def regions(self) -> List[RegionInfo]: return list(self._regions)
+    def total_activations_saved(self) -> int: return self.total_saved
+    def total_activations_recomputed(self) -> int: return self.total_recomputed
+
+    def begin_region(self, name: str, mode: str = "FULL", activation_bytes: int = 0, recompute_flops: int = 0):
+        mode = mode.upper()
+        assert mode in self.MODES, mode
+        self._stack.append(RegionInfo(name, int(activation_bytes), int(recompute_flops), mode != "NONE", mode))
+
+    def end_region(self):
+        if not self._stack:
+            return
+        r = self._stack.pop()
+        r.forward_activations_bytes = max(r.forward_activations_bytes, 1024)
+        r.recompute_cost_flops = max(r.recompute_cost_flops, 1)
+        self._regions.append(r)
+        if r.is_checkpointed:
+            self.total_saved += r.forward_activations_bytes
+            self.total_recomputed += r.recompute_cost_flops
+
+    def in_checkpoint_region(self) -> bool:
+        return bool(self._stack) and self._stack[-1].is_checkpointed
+
+    def region(self, name: str, mode: str = "NONE", recompute_flops: int = 0):
+        """Context manager: the region's activation bytes are what autograd saves for backward inside it (each distinct
+        storage counted once; parameters and views of parameters are not activations)."""
+        ac = self
+
+        class _Region:
+            def __enter__(self_):
+                ac.begin_region(name, mode, 0, recompute_flops)
+                info, seen = ac._stack[-1], set()
+
+                def pack(t):
+                    key = t.untyped_storage().data_ptr() if t.numel() else None
+                    is_param = isinstance(t, torch.nn.Parameter) or isinstance(getattr(t, "_base", None), torch.nn.Parameter)
+                    if key is not None and key not in seen and not is_param:
+                        seen.add(key)
+                        info.forward_activations_bytes += t.numel() * t.element_size()
+                    return t
+                self_.hooks = torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t)
+                self_.hooks.__enter__()
+                return info
+
+            def __exit__(self_, *exc):
+                self_.hooks.__exit__(*exc)
+                ac.end_region()
+                return False
+        return _Region()
+
+    @staticmethod
+    def estimate_layer_activations(batch: int, seq: int, hidden: int, ffn_hidden: int = 0, bytes_per_value: int = 2) -> int:
+        """Bytes one transformer block keeps for backward when nothing is recomputed: normed inputs, q / k / v and the
+        attention output, the two GLU halves and their product, the two residual streams."""
+        ffn_hidden = ffn_hidden or 4 * hidden
+        return batch * seq * (8 * hidden + 3 * ffn_hidden) * bytes_per_value
+
+    def auto_place_checkpoints(self) -> List[str]:
+        """Mark regions, largest first, until the unmarked ones fit the budget; returns the newly marked names."""
+        b = self.budget
+        if not self._regions or b.total_bytes <= 0:
+            return []
+        target = b.total_bytes - b.param_bytes - b.grad_bytes - b.opt_state_bytes
+        if target <= 0:
+            target = b.total_bytes // 4
+        held = sum(r.forward_activations_bytes for r in self._regions if not r.is_checkpointed)
+        marked = []
+        for r in sorted(self._regions, key=lambda r: -r.forward_activations_bytes):
+            if held <= target:
+                break
+            if r.is_checkpointed:
+                continue
+            r.is_checkpointed, r.mode = True, "BALANCED"
+            held -= r.forward_activations_bytes
+            self.total_saved += r.forward_activations_bytes
+            self.total_recomputed += r.recompute_cost_flops
+            marked.append(r.name)
+        b.activation_bytes = held
+        return marked
+
+    def estimated_savings(self, region: RegionInfo) -> int:
+        return region.forward_activations_bytes if region.is_checkpointed else 0
+
+    def estimated_savings_all(self) -> int:
+        return sum(self.estimated_savings(r) for r in self._regions)
+
+    def compute_overhead(self) -> float:
+        """Recomputed FLOPs per byte saved (the reference's figure of merit)."""
+        return self.total_recomputed / self.total_saved if self.total_saved > 0 else 0.0
