@@ -74,6 +74,19 @@ def main():
         res[f"{sched}_grad_err"] = err
         res[f"{sched}_live"] = pp.max_live_microbatches(sched)
         assert not pp._saved
+    # inference pass through the stages: the last stage's logits equal the single-process model's
+    m = DenseModel(cfg, device="cpu", dtype=torch.float32, seed=1)
+    pp = PipelineParallel(m, ctx.world_size, ctx.rank, ctx, num_microbatches=4)
+    logits = pp.forward(ids)
+    if pp.last:
+        with torch.no_grad():
+            want = ref.forward(ids)
+        res["fwd_logits_err"] = float((logits - want).abs().max())
+        res["fwd_loss_err"] = abs(float(pp.compute_loss(logits, labels)) - ref_loss)
+    else:
+        assert logits is None
+    res["two_call_loss"] = pp.forward_1f1b(ids, labels) is pp.backward_1f1b() and pp.micro_batch_queue_size() == 0
+    res["stage_params"] = pp.model_param_count()
     json.dump(res, open(os.path.join(out_dir, f"rank{ctx.rank}.json"), "w"))
     ctx.barrier()
     dist.destroy_process_group()

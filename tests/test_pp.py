@@ -30,3 +30,5 @@ def test_pipeline_matches_single_process(tmp_path):
     for r in res:
         assert r["tied_norm_err"] < 1e-4
         assert r["tied_grad_err"] < 1e-5 and r["tied_param_err"] < 1e-5
+    assert res[1]["fwd_logits_err"] < 1e-4 and res[1]["fwd_loss_err"] < 1e-4
+    assert all(r["two_call_loss"] and r["stage_params"] > 0 for r in res)

@@ -17,7 +17,7 @@ from typing import List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from ..models.dense import block_backward, block_forward
+from ..models.dense import _norm_fwd, block_backward, block_forward
 from ..ops import functional as F
 from .collectives import DistributedContext
 
@@ -244,7 +244,51 @@ class PipelineParallel:
                     p.main_grad.mul_(max_norm / (norm + 1e-6))
         return norm
 
-    forward_1f1b = run_1f1b
+    def forward_1f1b(self, ids, labels):
+        """The reference splits 1F1B into a forward and a backward call (pipeline.h:42-45); here the schedule interleaves
+        them, so this call runs all of it and ``backward_1f1b`` reports its result."""
+        self._last_loss = self.run_1f1b(ids, labels)
+        return self._last_loss
+
+    def backward_1f1b(self):
+        """Loss of the schedule run by ``forward_1f1b`` (last stage; None elsewhere).  The gradients are already
+        accumulated in ``accumulated_gradient()``."""
+        return getattr(self, "_last_loss", None)
+
+    @torch.no_grad()
+    def forward(self, ids):
+        """Inference pass through the pipeline: every stage runs its layers on the whole batch and hands the hidden state
+        to the next one; the last stage returns the logits [B, S, V] (the other stages return None)."""
+        m, cfg = self.model, self.model.cfg
+        B, S = ids.shape
+        h = m.embed(ids) if self.first else self._exchange(recv_prev=self._hidden_spec(ids))[1]
+        rope = m.rope(m.tok_embeddings.device)
+        for i in range(self.lo, self.hi):
+            h, _ = block_forward(cfg, m.layers[i], h, B, S, rope, save=False)
+        if not self.last:
+            self._exchange(send_next=h)
+            return None
+        f, _ = _norm_fwd(cfg, h, m.norm, m.norm_bias)
+        return F.gemm(f, m.lm_head.data).view(B, S, -1)
+
+    @staticmethod
+    def compute_loss(logits, labels, ignore_index: int = -100):
+        """Mean cross entropy of logits [B, S, V] (or [T, V]) against labels."""
+        return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), labels.reshape(-1),
+                                                 ignore_index=ignore_index)
+
+    def num_micro_batches(self) -> int: return self.num_microbatches
+    def micro_batch_queue_size(self) -> int: return len(self._saved)
+    def balance_weights(self): return list(self.balance) if self.balance else []
+
+    def model_param_count(self) -> int:
+        """Parameters this stage owns (a tied embedding is counted on both end stages, which both hold a copy)."""
+        seen, n = set(), 0
+        for p in self.owned_parameters():
+            if id(p) not in seen:
+                seen.add(id(p))
+                n += p.numel()
+        return n
 
     def max_live_microbatches(self, schedule="1f1b"):
         """Activations a stage holds at once: GPipe M, 1F1B min(M, stages - stage_id)."""
