@@ -116,3 +116,75 @@ def test_pipeline_scheduler_chains_stages_and_micro_batches():
     assert torch.equal(sch.get_stage(2).output_buffer, torch.full((1, 4), 111.0))
     sch.reset()
     assert sch.get_stage(0).input_buffer is None and sch.current_step == 0
+
+
+def test_manager_forward_over_local_experts_sums_to_the_dense_mixture():
+    """Two managers that hold half of the experts each: their partial outputs add up to the dense top-k mixture, stats
+    are counted, a failure moves the experts, and real managers can be chained by the pipeline scheduler."""
+    from transformers_fusion_b200.parallel.fault import NodeInfo
+    E, H, F_, T = 4, 16, 24, 12
+    g = torch.Generator().manual_seed(0)
+    experts = {e: (torch.randn(2 * F_, H, generator=g) * 0.2, torch.randn(H, F_, generator=g) * 0.2) for e in range(E)}
+    x = torch.randn(T, H, generator=g)
+    router = torch.randn(E, H, generator=g)
+    mgrs = []
+    for node in (0, 1):
+        m = X.ExpertParallelManager(ClusterConfig(), E, hidden_size=H, top_k=2)
+        m.node_id, m.router = node, router
+        m.restore_nodes([NodeInfo(0, "127.0.0.1", 1), NodeInfo(1, "127.0.0.1", 2)])
+        mgrs.append(m)
+    assert mgrs[0].local_experts() == [0, 1] and mgrs[1].local_experts() == [2, 3] and mgrs[0].num_nodes() == 2
+    outs = [m.forward_expert_parallel(x, {e: experts[e] for e in m.local_experts()}) for m in mgrs]
+    # dense statement of the same layer
+    probs = torch.softmax(x @ router.t(), -1)
+    w, idx = probs.topk(2, -1)
+    w = w / w.sum(-1, keepdim=True)
+    want = torch.zeros(T, H)
+    for t in range(T):
+        for k in range(2):
+            want[t] += w[t, k] * X._run_expert(experts[int(idx[t, k])], x[t:t + 1])[0]
+    assert torch.allclose(outs[0].output + outs[1].output, want, atol=1e-5)
+    assert torch.equal(outs[0].expert_indices, idx) and outs[0].load_balance_loss >= 1.0 - 1e-4 and outs[0].z_loss > 0
+    st = mgrs[0].get_stats()
+    assert st.total_tokens_routed == T and 1 <= st.total_expert_forward_calls <= 2 and st.max_load_imbalance >= 1.0
+    assert st.total_comm_bytes > 0 and torch.equal(mgrs[0].expert_parallel_mlp(x, experts), outs[0].output)
+    # node 1 fails: its experts move to node 0, which then computes the whole mixture
+    moves = mgrs[0].redistribute_experts_after_failure(1)
+    assert sorted(e for e, _, _ in moves) == [2, 3] and mgrs[0].local_experts() == [0, 1, 2, 3]
+    assert torch.allclose(mgrs[0].forward_expert_parallel(x, experts).output, want, atol=1e-5)
+    assert mgrs[0].get_stats().expert_redistributions == 1
+    mgrs[0].reset_stats()
+    assert mgrs[0].get_stats().total_tokens_routed == 0
+    # dispatcher bookkeeping
+    d = X.ExpertDispatcher(8, 2, 0)
+    assert d.get_all_assignments() == [0, 0, 0, 0, 1, 1, 1, 1]
+    d.assign_experts_to_nodes(4)
+    assert d.get_expert_assignment(7) == 3 and d.get_all_assignments() == [0, 0, 1, 1, 2, 2, 3, 3]
+    # scheduler over real managers: stage 2 consumes stage 1's mixture
+    sch = X.PipelineScheduler(2, micro_batch_size=T)
+    sch.schedule_forward(x, 0)
+    y = sch.execute_pipeline([mgrs[0], mgrs[0]], [experts, experts])
+    assert torch.allclose(y, mgrs[0].forward_expert_parallel(want, experts).output, atol=1e-4)
+
+
+def test_fault_manager_heartbeat_thread_reports_failure_and_recovery():
+    from transformers_fusion_b200.parallel.fault import FaultToleranceManager, NodeInfo
+    ft = FaultToleranceManager(ClusterConfig())
+    for i in range(3):
+        ft.add_node(NodeInfo(i, "127.0.0.1", 1000 + i))
+    seen = []
+    ft.failure_cbs.append(lambda i: seen.append(("down", i)))
+    ft.recovery_cbs.append(lambda i: seen.append(("up", i)))
+    health = {0: True, 1: True, 2: True}
+    ft.start_heartbeat(10, probe=lambda i: health[i])
+    assert ft.heartbeat_running()
+    health[2] = False
+    deadline = time.time() + 3.0
+    while ("down", 2) not in seen and time.time() < deadline:
+        time.sleep(0.01)
+    assert seen == [("down", 2)] and ft.get_failed_nodes() == [2] and not ft.check_node_health(2)
+    health[2] = True
+    while ("up", 2) not in seen and time.time() < deadline:
+        time.sleep(0.01)
+    ft.stop_heartbeat()
+    assert seen == [("down", 2), ("up", 2)] and ft.get_failed_nodes() == [] and not ft.heartbeat_running()

@@ -115,3 +115,155 @@ class EPTrainer:
             dist.all_reduce(lt, group=self.group)
         self.opt.step(lr)                                   # clips, updates, refreshes the bf16 weights, zeroes the gradients
         return float(lt) / W
+
+
+# =====================================================================================================================
+# Replicated-token expert parallelism: the reference's algorithm, on library collectives
+# =====================================================================================================================
+class _SumOverRanks(torch.autograd.Function):
+    """y = sum over ranks of the partial outputs.  Every rank holds the same tokens and computes the same loss from the
+    same y, so the gradient of each partial output is the gradient of y itself."""
+
+    @staticmethod
+    def forward(ctx, y, group):
+        y = y.contiguous().clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
+class _GradSumOverRanks(torch.autograd.Function):
+    """Identity whose gradient is summed over the ranks: the input feeds every rank's partial mixture."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dx):
+        dx = dx.contiguous().clone()
+        dist.all_reduce(dx, group=ctx.group)
+        return dx, None
+
+
+class _ReplicatedTokenFFN:
+    """Stand-in for the device dispatch / combine object of a block (``blk.ep``): every rank routes ALL tokens, runs the
+    experts it holds on the rows routed to them and the partial mixtures are summed over the ranks."""
+
+    def __init__(self, rank: int, world: int, num_experts: int, group=None):
+        self.rank, self.world, self.E, self.group = rank, world, num_experts, group
+        self.El = num_experts // world
+
+    def moe_ffn(self, x, logits, gate_up, down, k, renorm, act, lb_weight, z_weight):
+        from ..ops import moe as M
+        T, H = x.shape
+        E, lo = self.E, self.rank * self.El
+        idx, w, probs, counts, lse, prob_sums, lse_sq = M.router_topk_stats(logits.detach(), k, renorm)
+        multi = self.world > 1 and dist.is_initialized()
+        p = torch.softmax(logits.float(), -1)                  # for the auxiliary losses: replicated, not summed
+        # the expert path: x and the mixture weights feed every rank's partial output, so their gradients are summed
+        lg_e = _GradSumOverRanks.apply(logits, self.group) if multi and logits.requires_grad else logits
+        x = _GradSumOverRanks.apply(x, self.group) if multi and x.requires_grad else x
+        wsel = torch.softmax(lg_e.float(), -1).gather(1, idx.long())
+        if renorm:
+            wsel = wsel / wsel.sum(-1, keepdim=True)
+        holds_all = gate_up.shape[0] == E                      # un-cut model: use this rank's block of the full tensors
+        y = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+        for j in range(self.El):
+            e = lo + j
+            tok, slot = (idx == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            wg, wd = (gate_up[e], down[e]) if holds_all else (gate_up[j], down[j])
+            gu = x[tok].float() @ wg.float().t()
+            Fh = gu.shape[1] // 2
+            g = gu[:, :Fh]
+            a = {"gelu": torch.nn.functional.gelu(g, approximate="tanh"), "relu": torch.relu(g)}.get(str(act), torch.nn.functional.silu(g)) * gu[:, Fh:]
+            y = y.index_add(0, tok, (a @ wd.float().t()) * wsel[tok, slot][:, None])
+        if multi:
+            y = _SumOverRanks.apply(y, self.group)
+        f = counts.float() / float(T * k)
+        aux = lb_weight * E * (f * p.mean(0)).sum() + z_weight * torch.logsumexp(logits.float(), -1).pow(2).mean()
+        return y.to(x.dtype), aux, idx
+
+
+class ModelExpertParallel:
+    """Model-level expert parallelism with the reference's interface (``ExpertParallel`` of include/quant/moe_model.h:
+    96-120; algorithm of src/model/moe_model.cpp:537-665): tokens are replicated, every rank runs the experts it holds,
+    the partial mixtures meet in one all-reduce per layer, and ``sync_gradients`` averages what is replicated.  It runs
+    on any ``torch.distributed`` backend, CPU included; the NVLink dispatch / combine path (``attach_expert_parallel`` +
+    ``EPTrainer``) is the fast form of the same layer on GPUs and is tested against this one."""
+
+    def __init__(self, num_experts: int, num_ranks: int = 1, rank: int = 0, ctx=None):
+        if num_experts % max(1, num_ranks):
+            raise ValueError("the number of experts must divide by the number of ranks")
+        self._E, self._W, self._rank = num_experts, max(1, num_ranks), rank
+        self.group = getattr(ctx, "group", None)
+
+    def num_experts(self) -> int: return self._E
+    def num_ranks(self) -> int: return self._W
+    def rank(self) -> int: return self._rank
+    def num_local_experts(self) -> int: return self._E // self._W
+
+    def local_experts(self) -> List[int]:
+        per = self._E // self._W
+        return list(range(self._rank * per, (self._rank + 1) * per))
+
+    def alltoall_experts(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Every rank's rows, concatenated in rank order (the reference's exchange is an all-gather: tokens are
+        replicated, nothing is routed at this point)."""
+        if self._W == 1 or not dist.is_initialized():
+            res = x.clone()
+        else:
+            parts = [torch.empty_like(x) for _ in range(self._W)]
+            dist.all_gather(parts, x.contiguous(), group=self.group)
+            res = torch.cat(parts, 0)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    def attach(self, model):
+        for blk in model.layers:
+            if hasattr(blk, "router"):
+                blk.ep = _ReplicatedTokenFFN(self._rank, self._W, self._E, self.group)
+        return model
+
+    def detach(self, model):
+        for blk in model.layers:
+            if isinstance(getattr(blk, "ep", None), _ReplicatedTokenFFN):
+                blk.ep = None
+        return model
+
+    def forward_with_parallel(self, model, ids: torch.Tensor) -> torch.Tensor:
+        """Logits of ``model`` with every MoE layer computed across the ranks (all ranks pass the same ``ids``)."""
+        self.attach(model)
+        try:
+            return model.forward(ids)
+        finally:
+            self.detach(model)
+
+    def forward_backward(self, model, ids, labels):
+        """Training form of ``forward_with_parallel``: loss and gradients (in ``main_grad``), expert layers across ranks."""
+        self.attach(model)
+        try:
+            return model.forward_backward(ids, labels)
+        finally:
+            self.detach(model)
+
+    def sync_gradients(self, model):
+        """After ``forward_backward`` on replicated tokens: the replicated tensors already hold identical gradients on
+        every rank and an expert's gradient lives on its owner only, so the owners' expert gradients are summed into every
+        rank's copy (each rank then holds the full model's gradient).  With a model cut to its local experts there is
+        nothing to exchange."""
+        if self._W == 1 or not dist.is_initialized():
+            return
+        for blk in model.layers:
+            if hasattr(blk, "router") and blk.gate_up.shape[0] == self._E:
+                for p in (blk.gate_up, blk.down):
+                    if getattr(p, "main_grad", None) is not None:
+                        dist.all_reduce(p.main_grad, group=self.group)

@@ -66,6 +66,21 @@ class ExpertDispatcher:
             for e in es:
                 self.owner[e] = n
 
+    def assign_experts_to_nodes(self, num_nodes: int):
+        """Contiguous blocks over ``num_nodes`` nodes (replaces the current assignment)."""
+        self.nodes = max(1, int(num_nodes))
+        self.assignment = assign_experts_to_nodes(self.E, self.nodes)
+        self._refresh()
+        return self.assignment
+
+    def get_expert_assignment(self, expert: int) -> int:
+        """Node that holds ``expert``."""
+        return int(self.owner[expert])
+
+    def get_all_assignments(self) -> List[int]:
+        """Owner node of every expert, by expert id."""
+        return self.owner.tolist()
+
     def redistribute_expert(self, expert: int, to_node: int):
         for es in self.assignment:
             if expert in es:
@@ -270,16 +285,142 @@ class TCPCommBackend:
             self.server.close()
 
 
+@dataclass
+class ExpertParallelStats:
+    total_tokens_routed: int = 0
+    total_tokens_dropped: int = 0
+    total_comm_bytes: int = 0
+    total_expert_forward_calls: int = 0
+    avg_load_imbalance: float = 0.0
+    max_load_imbalance: float = 0.0
+    node_failures_handled: int = 0
+    expert_redistributions: int = 0
+    total_forward_time_ms: float = 0.0
+    total_comm_time_ms: float = 0.0
+
+
+@dataclass
+class MoEOutput:
+    output: torch.Tensor                       # [T, H]: the weighted sum over the experts THIS node holds
+    router_logits: torch.Tensor
+    expert_weights: torch.Tensor
+    expert_indices: torch.Tensor
+    load_balance_loss: float = 0.0
+    z_loss: float = 0.0
+    tokens_dropped: int = 0
+
+
+def _run_expert(expert, x: torch.Tensor) -> torch.Tensor:
+    """``expert``: a callable, or (gate_up [2F, H], down [H, F]) weights of a SwiGLU expert."""
+    if callable(expert):
+        return expert(x)
+    gate_up, down = expert
+    gu = x.float() @ gate_up.float().t()
+    F_ = gu.shape[1] // 2
+    return ((torch.nn.functional.silu(gu[:, :F_]) * gu[:, F_:]) @ down.float().t()).to(x.dtype)
+
+
 class ExpertParallelManager:
-    def __init__(self, cfg: Optional[ClusterConfig] = None, num_experts: int = 0):
+    def __init__(self, cfg: Optional[ClusterConfig] = None, num_experts: int = 0, hidden_size: int = 0, top_k: int = 2):
         self.cfg = cfg or ClusterConfig(num_experts=num_experts)
         self.E = num_experts or self.cfg.num_experts
+        self.hidden, self.top_k = hidden_size, top_k
         self.ft = FaultToleranceManager(self.cfg)
         self.comm: Optional[TCPCommBackend] = None
         self.node_id = 0
         self.assignment: Dict[int, List[int]] = {}
         self.last_seen: Dict[int, float] = {}
         self.ft.failure_cbs.append(self._on_failure)
+        self.stats = ExpertParallelStats()
+        self.router: Optional[torch.Tensor] = None       # [E, H]; made on first use (or set by the caller)
+        self._imbalance_n = 0
+
+    # ---- accessors of the reference's manager (include/quant/expert_parallel.h:150-158)
+    def is_cluster_active(self) -> bool: return self.comm is not None and self.comm.server is not None
+    def local_node_id(self) -> int: return self.node_id
+    def num_nodes(self) -> int: return max(1, len(self.ft.alive_nodes()))
+    def get_nodes(self) -> List[NodeInfo]: return sorted(self.ft.nodes.values(), key=lambda n: n.id)
+    def get_stats(self) -> ExpertParallelStats: return self.stats
+    def reset_stats(self): self.stats = ExpertParallelStats(); self._imbalance_n = 0
+
+    def restore_nodes(self, nodes: List[NodeInfo]):
+        self.ft.nodes = {n.id: n for n in nodes}
+        self.ft.failed = [n.id for n in nodes if not n.alive]
+        self._reassign()
+
+    def restore_stats(self, stats: ExpertParallelStats): self.stats = stats
+
+    # ---- forward over the experts this node holds
+    def forward_expert_parallel(self, x: torch.Tensor, local_experts, training: bool = True) -> MoEOutput:
+        """Route all T tokens over all experts, run those routed to an expert of THIS node and return their weighted sum
+        (the sum of the nodes' outputs is the layer's output).  ``local_experts``: {expert id: expert} or a list indexed
+        by expert id; an expert is a callable or a (gate_up, down) pair.  Reference:
+        src/model/expert_parallel.cpp:683-758 (which walks token by token; here each expert runs once on its rows)."""
+        t0 = time.perf_counter()
+        T, H = x.shape[0], x.shape[-1]
+        xf = x.reshape(T, H)
+        if self.router is None:
+            g = torch.Generator().manual_seed(1234)
+            self.router = (torch.randn(self.E, H, generator=g) * H ** -0.5).to(xf.device)
+        logits = xf.float() @ self.router.float().t()
+        nodes = sorted(self.ft.alive_nodes()) or [self.node_id]
+        disp = ExpertDispatcher(self.E, 1, 0, self.top_k, H)
+        r = disp.route_tokens(logits, self.top_k)
+        mine = set(self.local_experts()) if self.assignment else set(range(self.E))
+        experts = local_experts if isinstance(local_experts, dict) else dict(enumerate(local_experts or []))
+        out = torch.zeros((T, H), dtype=torch.float32, device=xf.device)
+        calls = 0
+        for e in sorted(mine):
+            if e not in experts:
+                continue
+            tok, slot = (r.expert_indices == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            y = _run_expert(experts[e], xf[tok])
+            out.index_add_(0, tok, y.float() * r.expert_weights[tok, slot].float()[:, None])
+            calls += 1
+        lb, z = disp.compute_load_balance(r)
+        st = self.stats
+        st.total_tokens_routed += T
+        st.total_expert_forward_calls += calls
+        st.total_forward_time_ms += (time.perf_counter() - t0) * 1e3
+        remote = sum(int(c) for e, c in enumerate(r.tokens_per_expert.tolist()) if e not in mine)
+        st.total_comm_bytes += remote * H * xf.element_size() * (2 if len(nodes) > 1 else 0)
+        cnt = r.tokens_per_expert.float()
+        imb = float(cnt.max() / cnt.mean().clamp(min=1e-9))            # busiest expert against the mean load
+        self._imbalance_n += 1
+        st.avg_load_imbalance += (imb - st.avg_load_imbalance) / self._imbalance_n
+        st.max_load_imbalance = max(st.max_load_imbalance, imb)
+        return MoEOutput(out.to(x.dtype).reshape(x.shape), logits, r.expert_weights, r.expert_indices, lb, z, 0)
+
+    def expert_parallel_mlp(self, x: torch.Tensor, local_experts) -> torch.Tensor:
+        """The output tensor of ``forward_expert_parallel`` alone."""
+        return self.forward_expert_parallel(x, local_experts, training=False).output
+
+    def rebalance_experts(self):
+        """Contiguous reassignment over the nodes that are alive now."""
+        self._reassign()
+        self.stats.expert_redistributions += 1
+        return self.assignment
+
+    def redistribute_experts_after_failure(self, failed_node: int):
+        """Experts of ``failed_node`` go to the surviving nodes; returns the moves [(expert, from, to)]."""
+        n = self.ft.nodes.get(failed_node)
+        if n is not None and n.alive:
+            self.ft.on_node_failure(failed_node)          # triggers _reassign through the failure callback
+        else:
+            self._reassign()
+        self.stats.expert_redistributions += 1
+        return list(getattr(self, "last_moves", []))
+
+    def all_reduce_gradients(self, grad: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
+        """Average ``grad`` over the alive nodes through the control plane, in place (small tensors only; bulk gradients
+        travel over NVLink through the fused collectives).  Reference: src/model/expert_parallel.cpp:777-806."""
+        t0 = time.perf_counter()
+        avg = self._average_over_nodes(grad, timeout_s)
+        grad.copy_(avg.to(grad.dtype))
+        self.stats.total_comm_time_ms += (time.perf_counter() - t0) * 1e3
+        return grad
 
     # ---- membership
     def init_cluster(self, node_id: int, port: int = 0) -> int:
@@ -352,6 +493,7 @@ class ExpertParallelManager:
 
     def handle_node_failure(self, node_id: int):
         self.ft.on_node_failure(node_id)
+        self.stats.node_failures_handled += 1
 
     def _on_failure(self, node_id):
         self._reassign()
@@ -370,11 +512,21 @@ class ExpertParallelManager:
         return st["experts"]
 
     # ---- small-tensor gradient averaging over the control plane
-    def sync_gradients(self, grads: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
+    def sync_gradients(self, grads, timeout_s: float = 5.0):
+        """A tensor: its average over the nodes.  A mapping / list of tensors (the gradients of the local experts): each
+        is averaged in place, as the reference's ``sync_gradients(local_experts)`` does."""
+        if isinstance(grads, dict):
+            return {k: self.all_reduce_gradients(g, timeout_s) for k, g in grads.items()}
+        if isinstance(grads, (list, tuple)):
+            return [self.all_reduce_gradients(g, timeout_s) for g in grads]
+        return self._average_over_nodes(grads, timeout_s)
+
+    def _average_over_nodes(self, grads: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
         peers = [n for n in self.ft.nodes.values() if n.id != self.node_id and n.alive]
         payload = grads.detach().float().cpu().numpy().tobytes()
         for n in peers:
             self.comm.send((n.addr, n.port), MSG_GRADIENT_SYNC, payload, n.id)
+            self.stats.total_comm_bytes += len(payload)
         acc, got = grads.detach().float().cpu().clone(), 1
         for _ in peers:
             m = self.comm.recv(MSG_GRADIENT_SYNC, timeout_s)

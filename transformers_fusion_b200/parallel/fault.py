@@ -161,6 +161,45 @@ class FaultToleranceManager:
     def alive_nodes(self) -> List[int]:
         return sorted(i for i, n in self.nodes.items() if n.alive)
 
+    def get_failed_nodes(self) -> List[int]:
+        return list(self.failed)
+
+    # ---- periodic health check (reference: FaultToleranceManager::start_heartbeat, include/quant/expert_parallel.h:240)
+    def start_heartbeat(self, interval_ms: int, probe: Optional[Callable[[int], bool]] = None):
+        """Every ``interval_ms`` a daemon thread asks ``probe(node_id)`` (default: the node's ``alive`` flag as last set
+        by the transport) about every known node; a node whose probe fails is reported through ``on_node_failure``, one
+        that answers again through ``on_node_recovery``."""
+        self.stop_heartbeat()
+        self._hb_stop = threading.Event()
+        self._hb_probe = probe
+
+        def loop():
+            while not self._hb_stop.wait(max(1, interval_ms) / 1e3):
+                self.heartbeat_once()
+        self._hb_thread = threading.Thread(target=loop, name="tfb-fault-heartbeat", daemon=True)
+        self._hb_thread.start()
+
+    def heartbeat_once(self):
+        """One round of the health check (what the heartbeat thread runs; callable directly from tests)."""
+        probe = getattr(self, "_hb_probe", None)
+        for i in list(self.nodes):
+            ok = probe(i) if probe is not None else self.nodes[i].alive
+            if not ok and i not in self.failed:
+                self.on_node_failure(i)
+            elif ok and i in self.failed:
+                self.on_node_recovery(i)
+
+    def stop_heartbeat(self):
+        t = getattr(self, "_hb_thread", None)
+        if t is not None:
+            self._hb_stop.set()
+            t.join(timeout=2.0)
+            self._hb_thread = None
+
+    def heartbeat_running(self) -> bool:
+        t = getattr(self, "_hb_thread", None)
+        return t is not None and t.is_alive()
+
     def check_node_health(self, node_id: int) -> bool:
         n = self.nodes.get(node_id)
         return bool(n and n.alive)
