@@ -145,3 +145,46 @@ def test_config_binary_roundtrip():
               "activation", "num_kv_heads", "use_parallel_residual", "mtp_num_heads", "rope_scaling_mode"):
         assert getattr(back, k) == getattr(cfg, k), k
     assert abs(back.rope_scaling_factor - 4.0) < 1e-6 and abs(back.mtp_loss_weight - 0.3) < 1e-6
+
+
+def test_multi_token_prediction_heads_train_and_files_roundtrip(tmp_path):
+    """The fused step with extra prediction heads equals the autograd statement (main CE + weight x mean of the heads' CE
+    on labels shifted further left), and save / save_quantized / load keep the heads."""
+    from transformers_fusion_b200.models.dense import _LinearFn
+    cfg = TransformerConfig(**CASES["llama_gqa"], init_std=0.2, mtp_num_heads=2, mtp_loss_weight=0.3)
+    model = DenseModel(cfg, dtype=torch.float32, seed=4)
+    model.flatten()
+    B, S = 2, 8
+    ids = torch.randint(0, cfg.vocab_size, (B, S))
+    labels = torch.randint(0, cfg.vocab_size, (B, S))
+    labels[1, 2] = -100
+    loss = model.forward_backward(ids, labels)
+    g1 = model.flat.grads.clone()
+    assert all(h.main_grad.abs().sum() > 0 for h in model.mtp_heads)
+    model.flat.zero_grad()
+    f = model.hidden_states(ids)
+    want = TF.cross_entropy(_LinearFn.apply(f, model.lm_head).float(), labels.view(-1), ignore_index=-100)
+    shifted = model.mtp_shifted_labels(labels)
+    assert shifted[0].view(B, S)[0, :-1].tolist() == labels[0, 1:].tolist() and shifted[1].view(B, S)[0, -2:].tolist() == [-100, -100]
+    for w, lab in zip(model.mtp_heads, shifted):
+        want = want + 0.3 / 2 * TF.cross_entropy(_LinearFn.apply(f, w).float(), lab, ignore_index=-100)
+    want.backward()
+    assert abs(want.item() - loss.item()) < 1e-4
+    assert torch.allclose(model.flat.grads, g1, atol=1e-4, rtol=1e-3)
+    # without the weight the heads are left alone
+    model.flat.zero_grad()
+    model.mtp_loss_weight = 0.0
+    model.forward_backward(ids, labels)
+    assert all(float(h.main_grad.abs().sum()) == 0 for h in model.mtp_heads)
+    # files
+    path = model.save(str(tmp_path / "m.quant"))
+    back = DenseModel.load(path)
+    assert len(back.mtp_heads) == 2 and torch.equal(back.mtp_heads[1].data, model.mtp_heads[1].data)
+    with torch.no_grad():
+        a, b = model.mtp_forward(ids), back.mtp_forward(ids)
+    assert len(a) == 2 and a[0].shape == (B, S, cfg.vocab_size) and torch.allclose(a[1], b[1], atol=1e-6)
+    q = DenseModel.load(model.save_quantized(str(tmp_path / "m8.quant"), "Q_8"))
+    with torch.no_grad():
+        full = model(ids)
+        err = (q(ids) - full).abs().max()
+    assert 0 < float(err) < 0.05 * float(full.abs().max())

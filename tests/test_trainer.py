@@ -123,3 +123,120 @@ def test_engine_gradient_accumulation_matches_full_batch():
     eb.step(ids[2:], labels[2:])
     assert eb.opt.step_count == 1
     assert (a.flat.params - b.flat.params).abs().max() < 1e-5
+
+
+def _tiny_trainer(opt="sgd", **cfgkw):
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.trainer.trainer import TrainConfig, Trainer
+    m = DenseModel(TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=16,
+                                     init_std=0.1, **cfgkw.pop("model", {})), device="cpu", dtype=torch.float32, seed=0)
+    kw = dict(batch_size=4, seq_length=16, learning_rate=5e-2, warmup_steps=0, lr_schedule="CONSTANT", max_grad_norm=0.0, zero_stage=0)
+    kw.update(cfgkw)
+    return Trainer(m).compile(opt, TrainConfig(**kw))
+
+
+def test_qat_straight_through_absmax_and_lsq():
+    import torch as T
+    g = T.Generator().manual_seed(0)
+    ids = T.randint(0, 64, (4, 16), generator=g)
+    lab = T.roll(ids, -1, 1)
+    t = _tiny_trainer(qat_bits=4)                                 # the configuration switch turns it on
+    assert t.qat_enabled()
+    w0 = t.model.flat.params.clone()
+    l0 = t.train_step(ids, lab)
+    # the weights stay unquantised (many distinct values), yet the loss was computed on 4-bit weights
+    mat = t.model.layers[0].qkv.data
+    assert mat.unique().numel() > 100 and not T.equal(t.model.flat.params, w0)
+    q = t.qat_fake_quantize(mat)
+    assert q.unique().numel() <= 15 and (q - mat).abs().max() <= mat.abs().max() / 7 / 2 + 1e-6
+    plain = _tiny_trainer()
+    assert abs(plain.train_step(ids, lab) - l0) > 1e-6            # the quantised forward really differs
+    losses = [t.train_step(ids, lab) for _ in range(30)]
+    assert losses[-1] < l0 - 0.3
+    t.disable_qat()
+    assert not t.qat_enabled()
+    # learned step sizes: one per matrix, they move and stay positive
+    t2 = _tiny_trainer()
+    t2.enable_qat(4, True, use_lsq=True)
+    t2.train_step(ids, lab)
+    first = {i: float(s) for i, s in t2._qat_steps.items()}
+    for _ in range(5):
+        t2.train_step(ids, lab)
+    assert first and all(float(s) > 0 for s in t2._qat_steps.values())
+    assert any(abs(float(t2._qat_steps[i]) - v) > 0 for i, v in first.items())
+    step = T.nn.Parameter(T.tensor([0.05]))
+    y = t2.qat_fake_quantize_lsq(mat.clone().requires_grad_(True), step)
+    y.sum().backward()
+    assert step.grad is not None and y.unique().numel() <= 16
+
+
+def test_continual_learning_consolidation_and_replay():
+    import torch as T
+    from transformers_fusion_b200.trainer.continual import ContinualEngineConfig
+    from transformers_fusion_b200.trainer.trainer import DataLoader
+    g = T.Generator().manual_seed(1)
+    task_a = T.randint(0, 32, (16,), generator=g).repeat(60)
+    task_b = T.randint(32, 64, (16,), generator=g).repeat(60)
+
+    def run(continual):
+        t = _tiny_trainer(learning_rate=0.1)
+        if continual:
+            t.enable_continual(ContinualEngineConfig(ecc_lambda=50.0, ecc_alpha=0.1, replay_capacity=64))
+            t.set_replay_ratio(0.25)
+            assert t.continual_enabled() and t.continual_engine() is t.continual
+        dl_a, dl_b = DataLoader(tokens=task_a, batch_size=4, seq_length=16), DataLoader(tokens=task_b, batch_size=4, seq_length=16)
+        for _ in range(25):
+            t.train_step(*dl_a.next_batch())
+        base = t.eval_loss(DataLoader(tokens=task_a, batch_size=4, seq_length=16), 2)
+        got = t.on_task_boundary(1, DataLoader(tokens=task_a, batch_size=4, seq_length=16), 2)
+        if continual:
+            assert got == pytest.approx(base) and t._ewc_anchored and len(t._replay) > 0
+        for _ in range(25):
+            t.train_step(*dl_b.next_batch())
+        return base, t.eval_loss(DataLoader(tokens=task_a, batch_size=4, seq_length=16), 2), t
+    base_p, after_p, _ = run(False)
+    base_c, after_c, tc = run(True)
+    assert after_p > base_p + 0.5                                   # plain training forgets task A
+    assert after_c - base_c < 0.5 * (after_p - base_p)              # consolidation + replay keep most of it
+    assert any(r[2] == 0 for r in tc._replay) and tc.current_task == 1
+    tc.set_ewc_lambda(3.0)
+    assert tc.continual.cfg.ecc_lambda == 3.0
+    tc.disable_continual()
+    assert not tc.continual_enabled()
+
+
+def test_loss_helpers_and_scale_rule():
+    import torch as T
+    from transformers_fusion_b200.trainer.trainer import Trainer
+    g = T.Generator().manual_seed(2)
+    logits = T.randn(2, 5, 11, generator=g)
+    labels = T.randint(0, 11, (2, 5), generator=g)
+    ls = Trainer.label_smoothing_loss(logits, labels, 0.1)
+    want = T.nn.functional.cross_entropy(logits.view(-1, 11), labels.view(-1), label_smoothing=0.1, reduction="none").view(2, 5)
+    assert T.allclose(ls, want, atol=1e-5)
+    bad = labels.clone()
+    bad[0, 0] = 99
+    assert float(Trainer.label_smoothing_loss(logits, bad, 0.1)[0, 0]) == 0.0
+    heads = [T.randn(2, 5, 11, generator=g) for _ in range(2)]
+    m = Trainer.mtp_loss(heads, labels)
+    w0 = T.nn.functional.cross_entropy(heads[0][:, :-1].reshape(-1, 11), labels[:, 1:].reshape(-1))
+    w1 = T.nn.functional.cross_entropy(heads[1][:, :-2].reshape(-1, 11), labels[:, 2:].reshape(-1))
+    assert m == pytest.approx(float(w0 + w1) / 2, rel=1e-5) and Trainer.mtp_loss([], labels) == 0.0
+    t = _tiny_trainer(model=dict(mtp_num_heads=1), mtp_loss_weight=0.5)
+    assert t.model.mtp_loss_weight == 0.5
+    ids = T.randint(0, 64, (4, 16), generator=g)
+    lab = T.roll(ids, -1, 1)
+    ce = float(T.nn.functional.cross_entropy(t.model(ids).detach().view(-1, 64), lab.view(-1)))
+    assert t.rdrop_loss(ids, lab, 5.0) == pytest.approx(ce, abs=1e-5)          # deterministic model: the KL term vanishes
+    t.train_step(ids, lab)
+    assert t.model.mtp_heads[0].main_grad is not None
+    t.loss_scale, t.cfg.loss_scale_interval = 64.0, 2
+    assert t.dynamic_loss_scale(5.0, 1.0) == 32.0 and t.dynamic_loss_scale(0.5, 1.0) == 32.0 and t.dynamic_loss_scale(0.5, 1.0) == 64.0
+    t.loss_scale = 1.0
+    assert t.dynamic_loss_scale(1e9, 1.0) == 1.0
+    t.ema_init(0.5)
+    t.train_step(ids, lab)
+    avg = t.ema.shadow.clone()
+    t.ema_apply()
+    assert T.equal(t.model.flat.params, avg) and T.equal(t.ema.shadow, avg) and t.ema_enabled()

@@ -322,6 +322,45 @@ class DenseModel(nn.Module):
             out.append((f"mtp_heads.{i}.weight", m.data))
         return out
 
+    # ------------------------------------------------------------------ multi-token prediction heads
+    def mtp_shifted_labels(self, labels, ignore_index: int = -100):
+        """Targets of the extra heads: head k (0-based) sees labels moved k + 1 further to the left; the tail of every
+        sequence, which has no such token, is ignored.  Returns one flattened [B * S] vector per head."""
+        out = []
+        for k in range(len(self.mtp_heads)):
+            sh = torch.full_like(labels, ignore_index)
+            if labels.shape[1] > k + 1:
+                sh[:, :-(k + 1)] = labels[:, k + 1:]
+            out.append(sh.reshape(-1))
+        return out
+
+    def mtp_forward(self, ids):
+        """Logits of the extra prediction heads, one [B, S, V] tensor per head (reference: DenseModel::mtp_forward,
+        src/model/model.cpp).  Empty when the model has no such heads."""
+        B, S = ids.shape
+        f = self.hidden_states(ids)
+        return [_LinearFn.apply(f, w).view(B, S, -1) for w in self.mtp_heads]
+
+    # ------------------------------------------------------------------ files (reference: DenseModel::save / save_quantized / load)
+    def save(self, path, fmt="Q_32"):
+        """Write the model as a ``.quant`` container (raw fp32 blocks by default)."""
+        from ..quant import codec
+        codec.save_model(self, path, fmt)
+        return path
+
+    def save_quantized(self, path, fmt="Q_8", per_layer=None):
+        """Write the model with its matrices in a block format (``Q_8`` / ``Q_4`` / ``Q_2`` in the reference, any registry
+        name here); ``per_layer`` maps tensor-name prefixes to formats."""
+        from ..quant import codec
+        codec.save_model(self, path, fmt, per_layer)
+        return path
+
+    @classmethod
+    def load(cls, path, device="cpu", dtype=torch.float32, strict=True):
+        """Read a ``.quant`` container into a new model of this class."""
+        from ..quant import codec
+        return codec.load_model(path, device=device, dtype=dtype, model_cls=cls, strict=strict)
+
     # ------------------------------------------------------------------ autograd path
     def embed(self, ids):
         B, S = ids.shape
@@ -345,10 +384,11 @@ class DenseModel(nn.Module):
 
     @torch.no_grad()
     def head_loss_backward(self, h, lab_f, loss_scale: float = 1.0, ignore_index: int = -100, label_smoothing: float = 0.0,
-                           n_valid=None):
+                           n_valid=None, mtp_labels=None, mtp_weight: float = 0.0):
         """Final norm + chunked LM head + cross entropy on hidden states h [T, H]; accumulates the head's weight
         gradients and returns (mean loss, d loss / d h).  ``n_valid`` overrides the token count the loss is
-        averaged over (pipeline micro-batches divide by the whole batch's count)."""
+        averaged over (pipeline micro-batches divide by the whole batch's count).  ``mtp_labels`` (one [T] label vector
+        per multi-token-prediction head, already shifted) adds ``mtp_weight`` x the mean of the heads' cross entropies."""
         cfg = self.cfg
         T = h.shape[0]
         f, st = _norm_fwd(cfg, h, self.norm, self.norm_bias)
@@ -367,6 +407,21 @@ class DenseModel(nn.Module):
             F.gemm(logits, W.data, b_mn=True, out=d_f[t0:t1])
             F.gemm(logits, f[t0:t1], a_mn=True, b_mn=True, out=W.main_grad, accumulate=True)
         loss = losses.sum() / n_valid
+        if mtp_labels and mtp_weight > 0:
+            # head k predicts the token k + 2 positions ahead from the same normed hidden state
+            # (reference: Trainer::mtp_loss, src/trainer/trainer_core.cpp:1098-1125; tails are ignored here, not zero-labelled)
+            nh = len(mtp_labels)
+            for Wk, lab_k in zip(self.mtp_heads, mtp_labels):
+                _ensure_main_grad(Wk)
+                nv = (lab_k != ignore_index).sum().clamp(min=1).float()
+                sk = (loss_scale * mtp_weight / nh / nv).reshape(1)
+                for t0 in range(0, T, ck):
+                    t1 = min(T, t0 + ck)
+                    logits = F.gemm(f[t0:t1], Wk.data)
+                    lk = F.cross_entropy_fwd_bwd(logits, lab_k[t0:t1], sk, ignore_index, label_smoothing)
+                    loss = loss + lk.sum() * (mtp_weight / nh) / nv
+                    F.gemm(logits, Wk.data, b_mn=True, out=d_f[t0:t1], accumulate=True)
+                    F.gemm(logits, f[t0:t1], a_mn=True, b_mn=True, out=Wk.main_grad, accumulate=True)
         dh = _norm_bwd(cfg, d_f, h, self.norm, self.norm_bias, st, None)
         return loss, dh
 
@@ -391,7 +446,10 @@ class DenseModel(nn.Module):
             inputs.append(h)
             h, c = block_forward(cfg, blk, h, B, S, rope, save=not ckpt)
             ctxs.append(c)
-        loss, dh = self.head_loss_backward(h, lab_f, loss_scale, ignore_index, label_smoothing)
+        mtp_w = float(getattr(self, "mtp_loss_weight", cfg.mtp_loss_weight) or 0.0)
+        mtp_labels = self.mtp_shifted_labels(labels, ignore_index) if (mtp_w > 0 and len(self.mtp_heads)) else None
+        loss, dh = self.head_loss_backward(h, lab_f, loss_scale, ignore_index, label_smoothing,
+                                           mtp_labels=mtp_labels, mtp_weight=mtp_w)
         for i in range(cfg.num_layers - 1, -1, -1):
             c = ctxs[i]
             if ckpt:

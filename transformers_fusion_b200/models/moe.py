@@ -400,6 +400,42 @@ class MoEModel(DenseModel):
             out.append(("lm_head.weight", self.lm_head.data))
         return out
 
+    @classmethod
+    def load(cls, path, device="cpu", dtype=torch.float32, strict=True, **moe_kw):
+        """Read a ``.quant`` container written by ``save``.  The container's header holds the dense configuration only
+        (as the reference's does, src/model/moe_model.cpp:384-440), so the mixture's shape is read off the tensors: the
+        number of experts and their width from the ``moe.expert.N`` names, shared experts from theirs; what cannot be
+        seen in a file (``top_k``, the variant, loss weights) comes from ``moe_kw`` or the defaults."""
+        import re
+        from dataclasses import fields
+        from ..quant import codec
+        from .config import MoEConfig, TransformerConfig
+        raw, tensors = codec.load_state(path)
+        base = TransformerConfig.from_bytes(raw)
+        experts = {int(m.group(1)) for n in tensors for m in [re.match(r"layers\.0\.moe\.expert\.(\d+)\.gate_proj", n)] if m}
+        if not experts:
+            raise ValueError(f"{path}: no expert tensors (not a mixture-of-experts checkpoint)")
+        kw = {f.name: getattr(base, f.name) for f in fields(TransformerConfig)}
+        kw["tie_embeddings"] = "lm_head.weight" not in tensors
+        fe = tensors["layers.0.moe.expert.0.gate_proj.weight"].numel() // base.hidden_size
+        ns = 0
+        if "layers.0.shared_expert.gate_proj.weight" in tensors:
+            ns = tensors["layers.0.shared_expert.gate_proj.weight"].numel() // base.hidden_size // fe
+        kw.update(num_experts=len(experts), expert_hidden_size=fe, num_shared_experts=ns)
+        kw.update(moe_kw)
+        model = cls(MoEConfig(**kw), device=device, dtype=dtype, seed=None)
+        with torch.no_grad():
+            for name, dst in model.named_tensors():
+                if name not in tensors:
+                    if strict:
+                        raise KeyError(f"{path}: tensor {name} missing")
+                    continue
+                src = tensors[name]
+                if src.numel() != dst.numel():
+                    raise ValueError(f"{name}: {src.numel()} weights in file, {dst.numel()} expected")
+                dst.copy_(src.view(dst.shape).to(dst.dtype))
+        return model
+
     def expert_utilization(self):
         """Fraction of routed (token, k) pairs per expert in the last forward, per layer."""
         E = self.cfg.num_experts

@@ -142,7 +142,9 @@ class ModelEMA:
         self.flat.params.copy_(self.shadow.to(self.flat.params.dtype))
         self.shadow = cur
 
-    apply = swap
+    def apply(self):
+        """Overwrite the parameters with their average (the average is kept)."""
+        self.flat.params.copy_(self.shadow.to(self.flat.params.dtype))
 
 
 class Trainer:
@@ -158,6 +160,13 @@ class Trainer:
         self.loss_scale = 1.0
         self._good_steps = 0
         self.global_step = 0
+        self._qat = None                 # (bits, symmetric, use_lsq) when quantisation-aware training is on
+        self._qat_steps = {}             # LSQ: learned step size per parameter (by position in the flat list)
+        self.continual = None            # trainer.continual.ContinualEngine when continual learning is on
+        self.current_task = 0
+        self.replay_ratio = 0.25
+        self._replay = []                # exact (ids row, labels row, task) samples of earlier steps
+        self._ewc_anchored = False
 
     # ------------------------------------------------------------------ configuration
     def compile(self, optimizer=None, cfg: Optional[TrainConfig] = None, symm=None):
@@ -182,6 +191,10 @@ class Trainer:
         if c.ema_decay > 0:
             self.ema = ModelEMA(self.model.flat, c.ema_decay)
         self.loss_scale = c.loss_scale if c.dynamic_loss_scale else 1.0
+        if c.qat_bits > 0:
+            self.enable_qat(c.qat_bits, c.qat_symmetric)
+        if c.mtp_loss_weight > 0:
+            self.model.mtp_loss_weight = c.mtp_loss_weight
         return self
 
     def set_log_callback(self, cb): self.log_cb = cb
@@ -215,12 +228,20 @@ class Trainer:
         c = self.cfg
         lr = self.lr_at(self.global_step)
         fused = isinstance(self.opt, FlatAdamW)
-        if fused and c.grad_accum_steps == 1 and not c.dynamic_loss_scale and c.grad_noise_eta == 0:
+        plain = self._qat is None and self.continual is None
+        if fused and plain and c.grad_accum_steps == 1 and not c.dynamic_loss_scale and c.grad_noise_eta == 0:
             self.model.loss_label_smoothing = c.label_smoothing
             loss = self.engine.step(ids, labels, lr)
         else:
+            if self.continual is not None:
+                ids, labels = self._mix_replay(ids, labels)
+            shadow = self._qat_quantize_weights() if self._qat is not None else None
             chunks = zip(ids.chunk(c.grad_accum_steps), labels.chunk(c.grad_accum_steps))
             loss = sum(self.micro_step(i, l, self.loss_scale) for i, l in chunks) / c.grad_accum_steps
+            if shadow is not None:
+                self._qat_restore_weights(shadow)          # straight-through: the update is applied to the unquantised weights
+            if self.continual is not None:
+                lr = self._continual_after_backward(lr)
             if c.grad_noise_eta > 0:
                 self.inject_gradient_noise(self.global_step, c.grad_noise_eta, c.grad_noise_gamma)
             if self.loss_scale != 1.0:
@@ -289,6 +310,217 @@ class Trainer:
                 break
         self.save_checkpoint(c.checkpoint_path, dl)
         return self._metrics
+
+    # ------------------------------------------------------------------ loss helpers (reference: trainer.h:265-267)
+    @torch.no_grad()
+    def rdrop_loss(self, ids, labels, alpha: float) -> float:
+        """Cross entropy of one forward pass + alpha x mean KL(p1 || p2) between two forward passes of the same batch.
+        The two passes differ only through stochastic layers (gating dropout of the MoE variants); for a deterministic
+        model the second term is zero.  Reference: Trainer::rdrop_loss, src/trainer/trainer_core.cpp:960-992."""
+        was = self.model.training
+        self.model.train()
+        l1 = self.model(ids).float()
+        l2 = self.model(ids).float()
+        self.model.train(was)
+        V = l1.shape[-1]
+        lp1, lp2 = torch.log_softmax(l1.reshape(-1, V), -1), torch.log_softmax(l2.reshape(-1, V), -1)
+        kl = (lp1.exp() * (lp1 - lp2)).sum(-1).mean()
+        ce = torch.nn.functional.cross_entropy(l1.reshape(-1, V), labels.reshape(-1), ignore_index=-100)
+        return float(ce + alpha * kl)
+
+    @staticmethod
+    def label_smoothing_loss(logits, labels, smoothing: float):
+        """Per-token loss [B, S] against (1 - smoothing) one-hot + smoothing / V uniform targets; tokens whose label is
+        outside the vocabulary get 0.  Reference: src/trainer/trainer_core.cpp:994-1028."""
+        V = logits.shape[-1]
+        lp = torch.log_softmax(logits.float().reshape(-1, V), -1)
+        lab = labels.reshape(-1).long()
+        ok = (lab >= 0) & (lab < V)
+        picked = lp.gather(1, lab.clamp(0, V - 1)[:, None])[:, 0]
+        loss = -(1.0 - smoothing) * picked - (smoothing / V) * lp.sum(-1)
+        return torch.where(ok, loss, torch.zeros_like(loss)).view(labels.shape)
+
+    @staticmethod
+    def mtp_loss(mtp_logits, labels, ignore_index: int = -100) -> float:
+        """Mean over the extra heads of the cross entropy of head k against the labels moved k + 1 further left."""
+        if not mtp_logits:
+            return 0.0
+        tot = 0.0
+        for k, lg in enumerate(mtp_logits):
+            sh = torch.full_like(labels, ignore_index)
+            if labels.shape[1] > k + 1:
+                sh[:, :-(k + 1)] = labels[:, k + 1:]
+            tot += float(torch.nn.functional.cross_entropy(lg.float().reshape(-1, lg.shape[-1]), sh.reshape(-1),
+                                                           ignore_index=ignore_index))
+        return tot / len(mtp_logits)
+
+    def dynamic_loss_scale(self, grad_norm: float, max_grad_norm: float):
+        """The reference's scale rule as a call (src/trainer/trainer_core.cpp:1071-1084): a norm above the threshold
+        halves the scale, ``loss_scale_interval`` quiet steps double it; a scale of 1 means scaling is off."""
+        if self.loss_scale == 1.0:
+            return self.loss_scale
+        if not math.isfinite(grad_norm) or grad_norm > max_grad_norm:
+            self.loss_scale, self._good_steps = max(1.0, self.loss_scale / 2), 0
+        else:
+            self._good_steps += 1
+            if self._good_steps >= self.cfg.loss_scale_interval:
+                self.loss_scale, self._good_steps = min(65536.0, self.loss_scale * 2), 0
+        return self.loss_scale
+
+    def unscale_gradients(self, scale: float):
+        if scale != 1.0:
+            self.model.flat.grads.mul_(1.0 / scale)
+
+    def get_model_params(self): return list(self.model.parameters())
+
+    # ------------------------------------------------------------------ quantisation-aware training (trainer.h:281-288)
+    def enable_qat(self, bits: int = 8, symmetric: bool = True, use_lsq: bool = False, init_scale: float = 0.1):
+        """From the next step on every matrix is replaced by its fake-quantised value for forward and backward and the
+        optimizer updates the unquantised weights (straight-through estimator).  ``use_lsq``: one learned step size per
+        matrix (started from the weights' statistics, or ``init_scale`` for an all-zero matrix) instead of the per-tensor
+        absmax grid; the step sizes learn from the same backward pass."""
+        self._qat = (int(bits), bool(symmetric), bool(use_lsq), float(init_scale))
+        self._qat_steps = {}
+
+    def disable_qat(self):
+        self._qat, self._qat_steps = None, {}
+
+    def qat_enabled(self) -> bool: return self._qat is not None
+
+    def qat_fake_quantize(self, weight):
+        """Per-tensor absmax fake quantisation at the configured width (what the forward pass sees)."""
+        bits, sym = (self._qat[0], self._qat[1]) if self._qat else (8, True)
+        qmax = (1 << (bits - 1)) - 1 if sym else (1 << bits) - 1
+        qmin = -qmax if sym else 0
+        w = weight.float()
+        if sym:
+            sc = w.abs().max().clamp(min=1e-8) / qmax
+            return (torch.round(w / sc).clamp(qmin, qmax) * sc).to(weight.dtype)
+        lo, hi = w.min(), w.max()
+        sc = ((hi - lo) / qmax).clamp(min=1e-8)
+        return ((torch.round((w - lo) / sc).clamp(0, qmax)) * sc + lo).to(weight.dtype)
+
+    def qat_fake_quantize_lsq(self, weight, scale_param):
+        from ..quant.qat import lsq_fake_quantize
+        bits, sym = (self._qat[0], self._qat[1]) if self._qat else (8, True)
+        return lsq_fake_quantize(weight, scale_param, bits, sym)
+
+    @torch.no_grad()
+    def _qat_quantize_weights(self):
+        """Replace the matrices by their quantised values; returns what is needed to undo it."""
+        from ..quant.qat import lsq_init_step
+        bits, sym, lsq, init = self._qat
+        flat = self.model.flat
+        shadow = flat.params.clone()
+        for i, p in enumerate(flat.params_list):
+            if p.dim() < 2 or p.numel() < 64:
+                continue
+            if lsq:
+                st = self._qat_steps.get(i)
+                if st is None:
+                    st = lsq_init_step(p.data.float(), bits, sym)
+                    st = torch.as_tensor(st, dtype=torch.float32, device=p.device).reshape(())
+                    if float(st) <= 0:
+                        st = torch.tensor(init, device=p.device)
+                    self._qat_steps[i] = st
+                qmax = (1 << (bits - 1)) - 1
+                p.data.copy_((torch.round(p.data.float() / st).clamp(-qmax if sym else 0, qmax) * st).to(p.dtype))
+            else:
+                p.data.copy_(self.qat_fake_quantize(p.data))
+        return shadow
+
+    @torch.no_grad()
+    def _qat_restore_weights(self, shadow):
+        bits, sym, lsq, _ = self._qat
+        flat = self.model.flat
+        if lsq:
+            # step-size gradient of LSQ: sum over weights of g * (round(w/s) - w/s inside the range, the bound outside),
+            # scaled by 1 / sqrt(n * qmax); a plain SGD step at the trainer's learning rate keeps the step positive
+            qmax = (1 << (bits - 1)) - 1
+            off = 0
+            for i, (p, o) in enumerate(zip(flat.params_list, flat.offsets)):
+                st = self._qat_steps.get(i)
+                if st is None:
+                    continue
+                w = shadow[o:o + p.numel()].view(p.shape).float()
+                g = p.main_grad.float()
+                v = w / st
+                inside = (v > (-qmax if sym else 0)) & (v < qmax)
+                ds = torch.where(inside, torch.round(v) - v, v.clamp(-qmax if sym else 0, qmax))
+                gs = (g * ds).sum() / math.sqrt(p.numel() * qmax)
+                self._qat_steps[i] = (st - self.lr_at(self.global_step) * gs).clamp(min=1e-8)
+        flat.params.copy_(shadow)
+
+    # ------------------------------------------------------------------ continual learning (trainer.h:290-302)
+    def enable_continual(self, cfg=None):
+        """Elastic weight consolidation (Fisher-weighted pull towards the weights at the last task boundary) + replay of
+        earlier tasks' samples + a forgetting-aware learning rate, driven by ``trainer.continual.ContinualEngine``."""
+        from .continual import ContinualEngine, ContinualEngineConfig
+        self.continual = ContinualEngine(cfg or ContinualEngineConfig())
+        self.current_task = 0
+        self._replay = []
+        self._ewc_anchored = False
+        return self.continual
+
+    def disable_continual(self):
+        self.continual, self._replay = None, []
+
+    def continual_enabled(self) -> bool: return self.continual is not None
+    def continual_engine(self): return self.continual
+
+    def set_ewc_lambda(self, lam: float):
+        if self.continual is not None:
+            self.continual.cfg.ecc_lambda = float(lam)
+
+    def set_replay_ratio(self, r: float):
+        self.replay_ratio = min(1.0, max(0.0, float(r)))
+
+    def on_task_boundary(self, new_task_id: int, eval_dl=None, max_batches: int = 4):
+        """The task that ends becomes the anchor of the consolidation penalty; its loss on ``eval_dl`` (when given) is the
+        baseline later forgetting is measured against."""
+        if self.continual is None:
+            self.current_task = new_task_id
+            return None
+        base = self.eval_loss(eval_dl, max_batches) if eval_dl is not None else None
+        w = self.model.flat.params.detach().float()
+        if not self.continual.ecc.initialized:
+            self.continual.ecc.initialize(w.numel(), w.device)
+        self.continual.on_task_boundary(new_task_id, w, base)
+        self._ewc_anchored = True
+        self.current_task = new_task_id
+        return base
+
+    def _mix_replay(self, ids, labels):
+        """Remember this batch's rows for later tasks and replace ``replay_ratio`` of the rows by rows of earlier tasks."""
+        cap = max(1, self.continual.cfg.replay_capacity)
+        old = [r for r in self._replay if r[2] != self.current_task]
+        n = min(len(old), int(round(self.replay_ratio * ids.shape[0])))
+        new_ids, new_lab = ids, labels
+        if n > 0:
+            g = torch.Generator().manual_seed(self.cfg.seed * 7919 + self.global_step)
+            pick = torch.randperm(len(old), generator=g)[:n].tolist()
+            new_ids, new_lab = ids.clone(), labels.clone()
+            for row, j in enumerate(pick):
+                if old[j][0].numel() == ids.shape[1]:
+                    new_ids[row], new_lab[row] = old[j][0].to(ids.device), old[j][1].to(labels.device)
+        for b in range(ids.shape[0]):
+            self._replay.append((ids[b].detach().cpu(), labels[b].detach().cpu(), self.current_task))
+        while len(self._replay) > cap:                                   # evict from the task that holds the most rows,
+            counts = {}                                                  # so that earlier tasks keep their share
+            for r in self._replay:
+                counts[r[2]] = counts.get(r[2], 0) + 1
+            big = max(counts, key=counts.get)
+            self._replay.pop(next(i for i, r in enumerate(self._replay) if r[2] == big))
+        return new_ids, new_lab
+
+    def _continual_after_backward(self, lr: float) -> float:
+        flat = self.model.flat
+        w = flat.params.detach().float()
+        eng = self.continual
+        lr = eng.on_step(flat.grads, w, lr, self.current_task)            # Fisher update, forgetting-aware rate
+        if eng.cfg.ecc_lambda > 0 and self._ewc_anchored:               # no pull before the first task has ended
+            flat.grads.copy_(eng.regularized_grads(flat.grads, w))
+        return lr
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, path, dl=None):
@@ -373,7 +605,8 @@ class Trainer:
     def ema_init(self, decay=0.999): self.ema = ModelEMA(self.model.flat, decay)
     def ema_step(self): self.ema and self.ema.step()
     def ema_swap(self): self.ema and self.ema.swap()
-    ema_apply = ema_swap
+    def ema_apply(self): self.ema and self.ema.apply()
+    def ema_enabled(self) -> bool: return self.ema is not None
 
 
 KINDS = {"dense": "dense", "pretrain": "dense", "finetune": "finetune", "fine_tune": "finetune", "ft": "finetune",
