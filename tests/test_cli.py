@@ -74,3 +74,36 @@ def test_convert_and_format_list(tmp_path):
     assert (tmp_path / "w.quant").stat().st_size < 4096 * 4 * 0.2
     out, _ = run("quant_format_list")
     assert "Q_G_8_K_M" in out and "Q_32" in out
+
+
+def test_serve_engine_service_swaps_models_between_requests():
+    """The serving bridge of quant_serve: a request runs on the engine that was current when it arrived, a swap waits for
+    the old engine to drain, an unloaded service refuses."""
+    import torch
+    from transformers_fusion_b200.cli.serve import EngineService
+    from transformers_fusion_b200.inference.engine import EngineConfig, InferenceEngine
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+
+    def engine(seed):
+        m = DenseModel(TransformerConfig(vocab_size=260, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=64,
+                                         max_seq_len=64), device="cpu", dtype=torch.float32, seed=seed)
+        return InferenceEngine(m, ByteTokenizer(), EngineConfig(max_batch=2, num_pages=32, max_seq_len=64))
+    a, b = engine(1), engine(2)
+    svc = EngineService(a, {"max_tokens": 8})
+    try:
+        first = "".join(svc.generate("hello", 6, 0.0, 1.0, 0, False))
+        assert svc.last_usage[0] == 5 and svc.last_usage[1] >= 1
+        svc.swap_engine(b)
+        assert svc.engine is b and not a.has_pending()
+        second = "".join(svc.generate("hello", 6, 0.0, 1.0, 0, False))
+        assert isinstance(first, str) and isinstance(second, str)
+        svc.swap_engine(a)
+        assert "".join(svc.generate("hello", 6, 0.0, 1.0, 0, False)) == first       # greedy: the first model answers as before
+        svc.swap_engine(None)
+        import pytest as _pt
+        with _pt.raises(RuntimeError):
+            next(svc.generate("hello", 2, 0.0, 1.0, 0, False))
+    finally:
+        svc.stop()

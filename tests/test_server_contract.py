@@ -124,3 +124,31 @@ def test_live_limits_and_auth(server):
     server.set_rate_limit(0.001, 2)
     codes = [_raw(port, b"GET /health HTTP/1.1\r\nHost: x\r\n\r\n")[0] for _ in range(4)]
     assert codes[:2] == [200, 200] and 429 in codes[2:]
+
+
+def test_model_load_and_unload_routes(server):
+    port = server.port
+    code, _, body = _post(port, "/v1/models/load", {"path": "/models/a.quant"})
+    assert code == 503 and json.loads(body)["error"]["code"] == "no_load_callback"
+    seen = []
+    server.set_load_model_callback(lambda path: seen.append(("load", path)) or path.endswith(".quant"))
+    server.set_unload_model_callback(lambda: seen.append(("unload",)))
+    code, _, body = _post(port, "/v1/models/unload", {})
+    assert code == 200 and json.loads(body)["status"] == "unloaded"
+    code, _, body = _raw(port, b"GET /v1/models HTTP/1.1\r\nHost: x\r\n\r\n")
+    assert code == 200 and json.loads(body)["data"] == []
+    code, _, body = _post(port, "/v1/completions", {"prompt": "hi", "max_tokens": 1})
+    assert code == 503 and json.loads(body)["error"]["code"] == "model_not_loaded"
+    code, _, body = _post(port, "/v1/models/load", {"path": "/models/b.bin"})
+    assert code == 500 and json.loads(body)["error"]["code"] == "load_failed"
+    code, _, body = _post(port, "/v1/models/load", {"name": "x"})
+    assert code == 400
+    code, _, body = _post(port, "/v1/models/load", {"path": "/models/a.quant", "name": "second-model"})
+    assert code == 200 and json.loads(body) == {"status": "loaded", "model": "second-model", "path": "/models/a.quant"}
+    code, _, body = _raw(port, b"GET /v1/models HTTP/1.1\r\nHost: x\r\n\r\n")
+    assert json.loads(body)["data"][0]["id"] == "second-model"
+    code, _, body = _post(port, "/v1/completions", {"prompt": "hi", "max_tokens": 1})
+    assert code == 200 and json.loads(body)["model"] == "second-model"
+    assert seen == [("unload",), ("load", "/models/b.bin"), ("load", "/models/a.quant")]
+    code, _, _ = _raw(port, b"GET /v1/models/load HTTP/1.1\r\nHost: x\r\n\r\n")
+    assert code == 405

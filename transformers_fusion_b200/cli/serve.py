@@ -26,7 +26,7 @@ class EngineService:
     def _loop(self):
         while self.running:
             with self.cv:
-                while self.running and not self.engine.has_pending():
+                while self.running and (self.engine is None or not self.engine.has_pending()):
                     self.cv.wait(0.05)
                 if not self.running:
                     return
@@ -35,8 +35,11 @@ class EngineService:
 
     def generate(self, prompt, max_tokens, temperature, top_p, top_k, stream):
         from ..inference.sampler import SamplerConfig
-        tok = self.engine.tok
-        ids = tok.encode(prompt)[-(self.engine.max_len - 2):] or [tok.bos_id if tok.bos_id >= 0 else 0]
+        eng = self.engine                       # a model swap waits for this request: it is pending on `eng` until it ends
+        if eng is None:
+            raise RuntimeError("no model is loaded")
+        tok = eng.tok
+        ids = tok.encode(prompt)[-(eng.max_len - 2):] or [tok.bos_id if tok.bos_id >= 0 else 0]
         pieces, acc, sent = [], [], [""]
 
         def on_tok(t):
@@ -49,7 +52,11 @@ class EngineService:
                 sent[0] = text
         sc = SamplerConfig(temperature, top_k, top_p)
         with self.cv:
-            r = self.engine.add_request(ids, min(max_tokens, self.defaults["max_tokens"]), sc, on_token=on_tok)
+            if self.engine is not eng:          # swapped between the two lines above
+                eng = self.engine
+                if eng is None:
+                    raise RuntimeError("no model is loaded")
+            r = eng.add_request(ids, min(max_tokens, self.defaults["max_tokens"]), sc, on_token=on_tok)
             self.cv.notify_all()
         emitted = 0
         while True:
@@ -64,6 +71,14 @@ class EngineService:
             if done and emitted >= len(pieces):
                 break
         self.last_usage = (len(ids), len(r.out))
+
+    def swap_engine(self, engine):
+        """Serve from another engine: waits until the current one has nothing in flight, under the loop's lock."""
+        with self.cv:
+            while self.engine is not None and self.engine.has_pending():
+                self.cv.wait(0.05)
+            self.engine = engine
+            self.cv.notify_all()
 
     def stop(self):
         self.running = False
@@ -91,9 +106,11 @@ def main(argv=None):
     from ..quant import codec
     from ..server import HTTPServer
     dev = pick_device(a.device)
-    model = codec.load_model(a.model, device=dev, dtype=model_dtype(dev))
-    tok = load_tokenizer(a.model, a.model_dir)
-    eng = InferenceEngine(model, tok, EngineConfig(max_batch=a.batch_size, kv_mode=a.kv, num_pages=4096, weight_format=a.weights))
+    def build_engine(path):
+        model = codec.load_model(path, device=dev, dtype=model_dtype(dev))
+        tok = load_tokenizer(path, a.model_dir)
+        return InferenceEngine(model, tok, EngineConfig(max_batch=a.batch_size, kv_mode=a.kv, num_pages=4096, weight_format=a.weights))
+    eng = build_engine(a.model)
     svc = EngineService(eng, {"max_tokens": a.max_tokens})
     srv = HTTPServer(a.port)
     srv.set_thread_pool_size(max(a.workers, a.batch_size))
@@ -104,10 +121,23 @@ def main(argv=None):
 
     def embed(text):
         import torch
-        ids = torch.tensor([tok.encode(text)[: eng.max_len] or [0]], device=dev)
+        e = svc.engine
+        if e is None:
+            raise RuntimeError("no model is loaded")
+        ids = torch.tensor([e.tok.encode(text)[: e.max_len] or [0]], device=dev)
         with torch.no_grad():
-            return model.hidden_states(ids).float().mean(0).tolist()
+            return e.model.hidden_states(ids).float().mean(0).tolist()
     srv.set_embeddings_callback(embed)
+
+    def load(path):                                   # POST /v1/models/load: build first, swap when the old engine is idle
+        try:
+            svc.swap_engine(build_engine(path))
+            return True
+        except Exception as e:                        # a bad path or file leaves the current model in service
+            print(f"load {path}: {e}", file=sys.stderr, flush=True)
+            return False
+    srv.set_load_model_callback(load)
+    srv.set_unload_model_callback(lambda: svc.swap_engine(None))
     if not srv.start():
         print(f"Error: cannot bind port {a.port}", file=sys.stderr)
         return 1

@@ -6,7 +6,7 @@
 //   per-IP token-bucket rate limit (429), Bearer auth on /v1/* (401), max_concurrent admission (503),
 //   415 for non-JSON POST bodies, CORS + security headers, OPTIONS -> 204
 //   routes: GET /health, GET /metrics, GET /v1/models, POST /v1/completions, POST /v1/chat/completions,
-//           POST /v1/embeddings;  streaming = "data: {json}\n\n" ... "data: [DONE]\n\n"
+//           POST /v1/embeddings, POST /v1/models/load, POST /v1/models/unload;  streaming = "data: {json}\n\n" ... "data: [DONE]\n\n"
 //   errors: {"error":{"code","message","type"}}
 // Generation and embeddings are callbacks (C function pointers) so the engine can live in Python or C++.
 //
@@ -46,6 +46,8 @@ typedef int (*tfb_generate_fn)(void* user, const char* prompt, int max_tokens, f
                                int stream, tfb_emit_fn emit, void* emit_ctx, int* prompt_tokens, int* completion_tokens);
 // writes up to cap floats, returns the embedding dimension (<= 0 on error)
 typedef int (*tfb_embed_fn)(void* user, const char* text, float* out, int cap);
+typedef int (*tfb_load_model_fn)(void* user, const char* path);   // non-zero = the model at `path` is now the served one
+typedef void (*tfb_unload_model_fn)(void* user);
 }
 
 namespace {
@@ -203,6 +205,11 @@ struct Server {
   void* gen_user = nullptr;
   tfb_embed_fn emb = nullptr;
   void* emb_user = nullptr;
+  tfb_load_model_fn load_model = nullptr;      // POST /v1/models/load {"path": ..., "name": ...}
+  tfb_unload_model_fn unload_model = nullptr;  // POST /v1/models/unload
+  void* model_user = nullptr;
+  std::mutex model_mu;                         // one load / unload at a time
+  std::atomic<bool> model_loaded{true};
   std::atomic<bool> running{false};
   std::atomic<int> current{0};
   std::atomic<long long> total{0}, errors{0}, tokens_out{0};
@@ -348,6 +355,7 @@ std::string chat_prompt(const Json& messages) {
 }
 
 void handle_generate(Server& s, int fd, const Request& rq, bool chat) {
+  if (!s.model_loaded) return respond_err(s, fd, 503, "no model is loaded", "server_error", "model_not_loaded");
   JsonParser jp(rq.body);
   Json j = jp.parse();
   if (!jp.ok || j.t != Json::OBJ) return respond_err(s, fd, 400, "request body is not valid JSON", "invalid_request_error", "invalid_json");
@@ -451,6 +459,30 @@ void handle_embeddings(Server& s, int fd, const Request& rq) {
                                            ",\"usage\":{\"prompt_tokens\":" + std::to_string(toks) + ",\"total_tokens\":" + std::to_string(toks) + "}}");
 }
 
+// POST /v1/models/load and /v1/models/unload: hand the request to the registered callbacks (the engine lives behind them);
+// the served model name follows a successful load.
+void handle_model_admin(Server& s, int fd, const Request& rq, bool load) {
+  if (load) {
+    JsonParser jp(rq.body);
+    Json j = jp.parse();
+    if (!jp.ok || j.t != Json::OBJ) return respond_err(s, fd, 400, "request body is not valid JSON", "invalid_request_error", "invalid_json");
+    const Json& pth = j.at("path");
+    if (pth.t != Json::STR || pth.s.empty()) return respond_err(s, fd, 400, "'path' must be a non-empty string", "invalid_request_error", "missing_path");
+    if (!s.load_model) return respond_err(s, fd, 503, "No model-load callback registered", "server_error", "no_load_callback");
+    std::lock_guard<std::mutex> l(s.model_mu);
+    if (!s.load_model(s.model_user, pth.s.c_str())) return respond_err(s, fd, 500, "model could not be loaded from " + pth.s, "server_error", "load_failed");
+    const Json& nm = j.at("name");
+    if (nm.t == Json::STR && !nm.s.empty()) s.model_name = nm.s;
+    s.model_loaded = true;
+    return respond(fd, 200, "application/json", "{\"status\":\"loaded\",\"model\":" + jstr(s.model_name) + ",\"path\":" + jstr(pth.s) + "}");
+  }
+  if (!s.unload_model) return respond_err(s, fd, 503, "No model-unload callback registered", "server_error", "no_unload_callback");
+  std::lock_guard<std::mutex> l(s.model_mu);
+  s.unload_model(s.model_user);
+  s.model_loaded = false;
+  respond(fd, 200, "application/json", "{\"status\":\"unloaded\"}");
+}
+
 void handle(Server& s, int fd, const std::string& ip) {
   timeval tv{s.timeout_s, 0};
   setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof tv);
@@ -492,8 +524,10 @@ void handle(Server& s, int fd, const std::string& ip) {
       << "\ntfb_ttft_ms{quantile=\"0.5\"} " << s.ttft.pct(0.5) << "\ntfb_ttft_ms{quantile=\"0.99\"} " << s.ttft.pct(0.99) << "\n";
     return respond(fd, 200, "text/plain; version=0.0.4", m.str());
   }
-  if (rq.method == "GET" && rq.path == "/v1/models")
+  if (rq.method == "GET" && rq.path == "/v1/models") {
+    if (!s.model_loaded) return respond(fd, 200, "application/json", "{\"object\":\"list\",\"data\":[]}");
     return respond(fd, 200, "application/json", "{\"object\":\"list\",\"data\":[{\"id\":" + jstr(s.model_name) + ",\"object\":\"model\",\"owned_by\":\"tfb\"}]}");
+  }
   if (rq.method == "POST") {
     auto ct = rq.headers.find("content-type");
     if (ct == rq.headers.end() || ct->second.find("application/json") == std::string::npos)
@@ -501,8 +535,10 @@ void handle(Server& s, int fd, const std::string& ip) {
     if (rq.path == "/v1/completions") { handle_generate(s, fd, rq, false); s.latency.add((now_s() - t0) * 1e3); return; }
     if (rq.path == "/v1/chat/completions") { handle_generate(s, fd, rq, true); s.latency.add((now_s() - t0) * 1e3); return; }
     if (rq.path == "/v1/embeddings") { handle_embeddings(s, fd, rq); s.latency.add((now_s() - t0) * 1e3); return; }
+    if (rq.path == "/v1/models/load") return handle_model_admin(s, fd, rq, true);
+    if (rq.path == "/v1/models/unload") return handle_model_admin(s, fd, rq, false);
   }
-  if (rq.path == "/health" || rq.path == "/v1/models" || rq.path == "/v1/completions" || rq.path == "/v1/chat/completions" || rq.path == "/v1/embeddings")
+  if (rq.path == "/v1/models/load" || rq.path == "/v1/models/unload" || rq.path == "/health" || rq.path == "/v1/models" || rq.path == "/v1/completions" || rq.path == "/v1/chat/completions" || rq.path == "/v1/embeddings")
     return respond_err(s, fd, 405, "method not allowed", "invalid_request_error", "method_not_allowed");
   respond_err(s, fd, 404, "unknown route " + rq.path, "invalid_request_error", "not_found");
 }
@@ -561,6 +597,10 @@ TFB_EXPORT void tfb_server_set_auth_token(void* h, const char* t) { static_cast<
 TFB_EXPORT void tfb_server_set_model_name(void* h, const char* n) { static_cast<Server*>(h)->model_name = n ? n : ""; }
 TFB_EXPORT void tfb_server_set_generate(void* h, tfb_generate_fn fn, void* user) { Server* s = static_cast<Server*>(h); s->gen = fn; s->gen_user = user; }
 TFB_EXPORT void tfb_server_set_embeddings(void* h, tfb_embed_fn fn, void* user) { Server* s = static_cast<Server*>(h); s->emb = fn; s->emb_user = user; }
+TFB_EXPORT void tfb_server_set_model_callbacks(void* h, tfb_load_model_fn load, tfb_unload_model_fn unload, void* user) {
+  Server* s = static_cast<Server*>(h);
+  s->load_model = load; s->unload_model = unload; s->model_user = user;
+}
 TFB_EXPORT int tfb_server_is_running(void* h) { return static_cast<Server*>(h)->running ? 1 : 0; }
 TFB_EXPORT int tfb_server_current_requests(void* h) { return static_cast<Server*>(h)->current.load(); }
 TFB_EXPORT int tfb_server_port(void* h) { return static_cast<Server*>(h)->bound_port; }

@@ -15,6 +15,8 @@ _EMIT = C.CFUNCTYPE(None, C.c_void_p, C.c_char_p)
 _GEN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_char_p, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int, _EMIT, C.c_void_p,
                    C.POINTER(C.c_int), C.POINTER(C.c_int))
 _EMB = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_char_p, C.POINTER(C.c_float), C.c_int)
+_LOAD = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_char_p)
+_UNLOAD = C.CFUNCTYPE(None, C.c_void_p)
 
 
 def _lib():
@@ -43,6 +45,8 @@ def _lib():
         L.tfb_server_set_model_name.argtypes = [C.c_void_p, C.c_char_p]
         L.tfb_server_set_generate.argtypes = [C.c_void_p, _GEN, C.c_void_p]
         L.tfb_server_set_embeddings.argtypes = [C.c_void_p, _EMB, C.c_void_p]
+        L.tfb_server_set_model_callbacks.argtypes = [C.c_void_p, _LOAD, _UNLOAD, C.c_void_p]
+        L.tfb_server_set_model_callbacks.restype = None
         L.tfb_server_latency_pct.restype = C.c_double
         L.tfb_server_latency_pct.argtypes = [C.c_void_p, C.c_double]
         L.tfb_server_ttft_pct.restype = C.c_double
@@ -130,6 +134,36 @@ class HTTPServer:
         cb = _GEN(tramp)
         self._keep.append(cb)
         _lib().tfb_server_set_generate(self._h, cb, None)
+
+    def set_load_model_callback(self, fn):
+        """``fn(path) -> bool``: called by ``POST /v1/models/load {"path": ..., "name": ...}``; a true result makes the
+        model at ``path`` the served one (reference: HTTPServer::set_load_model_callback, include/quant/http_server.h:125)."""
+        self._load_fn = fn
+        self._install_model_callbacks()
+
+    def set_unload_model_callback(self, fn):
+        """``fn()``: called by ``POST /v1/models/unload``; until the next load, generation answers 503."""
+        self._unload_fn = fn
+        self._install_model_callbacks()
+
+    def _install_model_callbacks(self):
+        load_fn, unload_fn = getattr(self, "_load_fn", None), getattr(self, "_unload_fn", None)
+
+        def load_tramp(_u, path):
+            try:
+                return 1 if load_fn(path.decode("utf-8", "replace")) else 0
+            except Exception:
+                return 0
+
+        def unload_tramp(_u):
+            try:
+                unload_fn()
+            except Exception:
+                pass
+        lcb = _LOAD(load_tramp) if load_fn else C.cast(None, _LOAD)
+        ucb = _UNLOAD(unload_tramp) if unload_fn else C.cast(None, _UNLOAD)
+        self._keep += [lcb, ucb]
+        _lib().tfb_server_set_model_callbacks(self._h, lcb, ucb, None)
 
     def set_embeddings_callback(self, fn):
         def tramp(_u, text, out, cap):
