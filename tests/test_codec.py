@@ -168,3 +168,51 @@ def test_foreign_stream_guard(tmp_path):
     assert not flags & 0x40000000
     r = codec.QuantReader(tmp_path / "a.quant")
     assert r.read_tensor("x").shape == (1024,) and torch.equal(r.read_tensor("y"), t)
+
+
+def test_block_level_reader_and_streaming_writer(tmp_path):
+    """Blocks copied from one container into another with the streaming verbs, without decoding them, read back to the
+    same weights; the block-level reader reports the tables as stored."""
+    import numpy as np
+    import torch
+    from transformers_fusion_b200.quant import codec
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(700, generator=g), torch.randn(300, generator=g)
+    src = tmp_path / "src.quant"
+    w = codec.QuantWriter(src, b"cfg-bytes")
+    w.add_tensor("a", a, codec.parse_format("Q_8"))
+    w.add_tensor("b", b, codec.Q_32)
+    w.close()
+    r = codec.QuantReader(src)
+    assert r.valid() and r.header() == {"magic": "QUA1", "version": 1, "flags": r.header()["flags"], "config_size": 9}
+    assert r.tensor_blocks("a") == (0, 3) and r.tensor_blocks("b") == (3, 1)
+    assert r.tensor_formats("a") == [codec.parse_format("Q_8")] * 3 and r.block_sizes(0)[0] == 256 and r.block_sizes(2)[0] == 188
+    table = r.read_format_table()
+    assert [t[0] for t in table] == [0, 1, 2, 3] and table[3][1] == codec.Q_32
+    blk = r.read_block(1)
+    assert blk.num_weights == 256 and len(blk.indices) == r.block_sizes(1)[2] and blk.codebook == b""
+    assert np.array_equal(blk.decode(), r.decode_block(1)) and np.array_equal(r.decode_block(1), r.read_tensor("a").numpy()[256:512])
+    with pytest.raises(IndexError):
+        r.read_block(4)
+    with pytest.raises(KeyError):
+        r.tensor_blocks("nope")
+    # copy tensor "a" (blocks as stored) and a freshly encoded tensor "c" into a new file
+    c = torch.randn(256, generator=g)
+    blocks = [r.read_block(i) for i in range(3)] + [codec.BlockData.encode("Q_4", c.numpy())]
+    out = tmp_path / "dst.quant"
+    sw = codec.QuantWriter(out)
+    sw.write_header(1, r.header()["flags"], r.config_bytes())
+    sw.write_format_table([(i, blk.format, len(blk.codebook)) for i, blk in enumerate(blocks)])
+    sw.write_tensor_table([(0, 3), (3, 1)], ["a", "c"])
+    for blk in blocks:
+        sw.write_block(blk)
+    with pytest.raises(RuntimeError):
+        sw.add_tensor("x", a)
+    sw.close()
+    r2 = codec.QuantReader(out)
+    assert r2.tensor_names() == ["a", "c"] and r2.config_bytes() == b"cfg-bytes" and codec.verify_index(str(out))
+    assert torch.equal(r2.read_tensor("a"), r.read_tensor("a"))
+    assert torch.allclose(r2.read_tensor("c"), torch.from_numpy(blocks[3].decode())) and (r2.read_tensor("c") - c).abs().max() < 0.5
+    store = codec.DedupStore(str(tmp_path / "dedup"))
+    k1, k2 = sw.write_dedup(b"payload", store), sw.write_dedup(b"payload", store)
+    assert k1 == k2 and store.read(k1) == b"payload"

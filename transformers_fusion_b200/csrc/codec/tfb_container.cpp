@@ -181,6 +181,47 @@ TFB_EXPORT long tfb_reader_tensor_block_formats(const tfb_reader* r, const char*
   for (uint32_t b = 0; b < t.count && long(b) < cap; ++b) out[b] = r->fmts[t.start + b].fmt;
   return long(t.count);
 }
+// ---- block-level access (reference: QUANTReader::read_block / tensor_blocks / block_sizes, include/quant/quant_format.h:90-140)
+// First block and block count of a tensor; returns 0, or -1 for an unknown name.
+TFB_EXPORT int tfb_reader_tensor_range(const tfb_reader* r, const char* name, uint32_t* start, uint32_t* count) {
+  auto it = r->by_name.find(name);
+  if (!r->valid || it == r->by_name.end()) return -1;
+  *start = r->tensors[it->second].start;
+  *count = r->tensors[it->second].count;
+  return 0;
+}
+// Table entry and payload sizes of block b: {table id, format byte, table codebook bytes, weights, codebook bytes, index bytes}.
+TFB_EXPORT int tfb_reader_block_info(const tfb_reader* r, uint32_t b, uint32_t out[6]) {
+  if (!r->valid || b >= r->fmts.size()) return -1;
+  const uint8_t* p = r->data.data() + r->block_off[b];
+  uint32_t nw, cb, ib;
+  memcpy(&nw, p, 4);
+  memcpy(&cb, p + 4, 4);
+  memcpy(&ib, p + 8 + cb, 4);
+  out[0] = r->fmts[b].id; out[1] = r->fmts[b].fmt; out[2] = r->fmts[b].cb; out[3] = nw; out[4] = cb; out[5] = ib;
+  return 0;
+}
+// Copies the codebook and index bytes of block b (either pointer may be null); returns 0 or -1.
+TFB_EXPORT int tfb_reader_block_payload(const tfb_reader* r, uint32_t b, uint8_t* codebook, uint8_t* indices) {
+  uint32_t info[6];
+  if (tfb_reader_block_info(r, b, info) != 0) return -1;
+  const uint8_t* p = r->data.data() + r->block_off[b];
+  if (codebook && info[4]) memcpy(codebook, p + 8, info[4]);
+  if (indices && info[5]) memcpy(indices, p + 8 + info[4] + 4, info[5]);
+  return 0;
+}
+// Decodes block b alone into out[nw]; returns the weight count, -1 on a bad id, -2 for a foreign stream (see read_tensor).
+TFB_EXPORT long long tfb_reader_decode_block(const tfb_reader* r, uint32_t b, float* out, long long cap) {
+  uint32_t info[6];
+  if (tfb_reader_block_info(r, b, info) != 0 || (long long)info[3] > cap) return -1;
+  int fmt = info[1];
+  if (fmt >= TFB_FORMAT_COUNT) fmt = TFB_FMT_Q32;
+  if (!tfb_format_is_wire_exact(fmt) && !(r->flags & TFB_FLAG_OWN_STREAMS)) return -2;
+  const uint8_t* p = r->data.data() + r->block_off[b];
+  tfb_dequantize_block(fmt, p + 8 + info[4] + 4, info[5], p + 8, info[4], info[3], out);
+  return info[3];
+}
+
 TFB_EXPORT long long tfb_reader_read_tensor(const tfb_reader* r, const char* name, float* out, long long cap) {
   const long long numel = tfb_reader_tensor_numel(r, name);
   if (numel < 0 || numel > cap) return -1;

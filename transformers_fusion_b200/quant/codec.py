@@ -56,6 +56,11 @@ def lib():
         L.tfb_writer_close.argtypes = [C.c_void_p, C.c_int]
         L.tfb_writer_add_tensor_mixed.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_uint32,
                                                   C.c_uint32]
+        L.tfb_reader_tensor_range.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_void_p]
+        L.tfb_reader_block_info.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
+        L.tfb_reader_block_payload.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.tfb_reader_decode_block.restype = C.c_longlong
+        L.tfb_reader_decode_block.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_longlong]
         L.tfb_reader_tensor_block_formats.restype = C.c_long
         L.tfb_reader_tensor_block_formats.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_long]
         _LIB = L
@@ -163,6 +168,57 @@ class QuantReader:
         lib().tfb_reader_tensor_block_formats(self._h, name.encode(), out.ctypes.data, n)
         return out[:n]
 
+    # ---- block-level verbs of the reference reader (include/quant/quant_format.h:90-140)
+    def valid(self) -> bool:
+        return bool(self._h) and bool(lib().tfb_reader_valid(self._h))
+
+    def header(self) -> dict:
+        """{magic, version, flags, config_size} of the 16-byte file header."""
+        return {"magic": "QUA1", "version": int(self.version), "flags": int(lib().tfb_reader_flags(self._h)),
+                "config_size": int(lib().tfb_reader_config(self._h, None, 0))}
+
+    def _block_info(self, b: int):
+        info = (C.c_uint32 * 6)()
+        if lib().tfb_reader_block_info(self._h, int(b), info) != 0:
+            raise IndexError(f"block {b} of {self.num_blocks()}")
+        return [int(v) for v in info]
+
+    def read_format_table(self):
+        """[(block_id, format byte, codebook bytes)] as stored in the table, one entry per block."""
+        return [tuple(self._block_info(b)[:3]) for b in range(self.num_blocks())]
+
+    def block_sizes(self, b: int):
+        """(num_weights, codebook bytes, index bytes) of block ``b``."""
+        i = self._block_info(b)
+        return i[3], i[4], i[5]
+
+    def read_block(self, b: int) -> "BlockData":
+        """Block ``b`` as stored: its format, weight count and the raw codebook / index bytes."""
+        i = self._block_info(b)
+        cb, ib = (C.c_uint8 * max(1, i[4]))(), (C.c_uint8 * max(1, i[5]))()
+        lib().tfb_reader_block_payload(self._h, int(b), cb, ib)
+        return BlockData(i[1], i[3], bytes(ib[:i[5]]), bytes(cb[:i[4]]))
+
+    def decode_block(self, b: int) -> np.ndarray:
+        """The weights of block ``b`` alone."""
+        n = self._block_info(b)[3]
+        out = np.empty(max(1, n), dtype=np.float32)
+        got = lib().tfb_reader_decode_block(self._h, int(b), out.ctypes.data, n)
+        if got != n:
+            raise ValueError(f"block {b}: cannot be decoded ({got})")
+        return out[:n]
+
+    def tensor_blocks(self, name: str):
+        """(first block, number of blocks) of a tensor."""
+        s, c = C.c_uint32(), C.c_uint32()
+        if lib().tfb_reader_tensor_range(self._h, name.encode(), C.byref(s), C.byref(c)) != 0:
+            raise KeyError(name)
+        return int(s.value), int(c.value)
+
+    def tensor_formats(self, name: str):
+        """Format byte of every block of a tensor (the reference's name for ``block_formats``)."""
+        return self.block_formats(name).tolist()
+
     def read_tensor(self, name) -> torch.Tensor:
         n = lib().tfb_reader_tensor_numel(self._h, name.encode())
         if n < 0:
@@ -178,25 +234,116 @@ class QuantReader:
         return torch.from_numpy(out)
 
 
+class BlockData:
+    """One stored block: format byte, number of weights, index bytes (the block stream) and codebook bytes."""
+
+    def __init__(self, format: int, num_weights: int, indices: bytes = b"", codebook: bytes = b""):
+        self.format, self.num_weights, self.indices, self.codebook = int(format), int(num_weights), bytes(indices), bytes(codebook)
+
+    @classmethod
+    def encode(cls, fmt, weights) -> "BlockData":
+        """Quantise a block of weights into ``fmt``."""
+        f = parse_format(fmt) if isinstance(fmt, str) else int(fmt)
+        a = np.ascontiguousarray(np.asarray(weights, dtype=np.float32).reshape(-1))
+        return cls(f, a.size, quantize_block(f, a))
+
+    def decode(self) -> np.ndarray:
+        return dequantize_block(self.format, self.indices, self.num_weights)
+
+
 class QuantWriter:
+    """Two ways to write a container.  ``add_tensor`` / ``add_tensor_mixed`` + ``close`` encode tensors and lay the file
+    out themselves.  The streaming verbs ``write_header`` / ``write_format_table`` / ``write_tensor_table`` /
+    ``write_block`` / ``write_raw`` (reference: QUANTWriter, include/quant/quant_format.h:34-88) append to the file in the
+    order they are called, for callers that build the tables themselves or copy blocks between files without decoding;
+    a file is readable when the order is header, format table, tensor table, blocks."""
+
     def __init__(self, path, config: bytes = b"", version: int = 1, flags: int = 0):
-        self._h = lib().tfb_writer_open(str(path).encode(), version, flags, config, len(config))
+        self.path = str(path)
+        self._stream = None
+        self._cfg = (config, version, flags)
+        self._h = None
+
+    def _handle(self):
+        if self._stream is not None:
+            raise RuntimeError("this writer is in streaming mode (write_header was called)")
+        if self._h is None:
+            config, version, flags = self._cfg
+            self._h = lib().tfb_writer_open(self.path.encode(), version, flags, config, len(config))
+        return self._h
+
+    # ---- streaming verbs
+    def _file(self):
+        if self._h is not None:
+            raise RuntimeError("this writer already holds encoded tensors (add_tensor was called)")
+        if self._stream is None:
+            self._stream = open(self.path, "wb")
+            self._names = []
+        return self._stream
+
+    def write_header(self, version: int = 1, flags: int = 0, config: bytes = b""):
+        import struct
+        self._file().write(b"QUA1" + struct.pack("<III", version, flags, len(config)) + bytes(config))
+
+    def write_format_table(self, entries):
+        """``entries``: (block_id, format byte, codebook bytes) per block."""
+        import struct
+        f = self._file()
+        f.write(struct.pack("<I", len(entries)))
+        for bid, fmt, cb in entries:
+            f.write(struct.pack("<IBI", bid, fmt, cb))
+
+    def write_tensor_table(self, entries, names):
+        """``entries``: (first block, number of blocks) per tensor, ``names`` in the same order."""
+        import struct
+        f = self._file()
+        f.write(struct.pack("<I", len(entries)))
+        for (start, count), name in zip(entries, names):
+            nb = name.encode()
+            f.write(struct.pack("<H", len(nb)) + nb + struct.pack("<II", start, count))
+        self._names = list(names)
+
+    def write_block(self, block: "BlockData"):
+        import struct
+        self._file().write(struct.pack("<II", block.num_weights, len(block.codebook)) + block.codebook +
+                           struct.pack("<I", len(block.indices)) + block.indices)
+
+    def write_raw(self, data: bytes):
+        self._file().write(bytes(data))
+
+    def write_dedup(self, payload: bytes, store: "DedupStore") -> str:
+        """Put ``payload`` into a content-addressed store next to the file and return its key (identical payloads are
+        stored once)."""
+        return store.write_dedup(payload)
 
     def add_tensor(self, name: str, t: torch.Tensor, fmt: int = Q_32, block: int | None = None):
         a = t.detach().float().cpu().contiguous().numpy().reshape(-1)
         if block is None:
             block = 32768 if fmt == Q_32 else 256
-        if lib().tfb_writer_add_tensor(self._h, name.encode(), a.ctypes.data, a.size, fmt, block) != 0:
+        if lib().tfb_writer_add_tensor(self._handle(), name.encode(), a.ctypes.data, a.size, fmt, block) != 0:
             raise ValueError(f"add_tensor({name}) failed")
 
     def add_tensor_mixed(self, name: str, t: torch.Tensor, fmts, block: int = 256):
         """One format per ``block`` weights (a FormatPlan's assignment)."""
         a = t.detach().float().cpu().contiguous().numpy().reshape(-1)
         f = np.ascontiguousarray(np.asarray(fmts, dtype=np.uint8))
-        if lib().tfb_writer_add_tensor_mixed(self._h, name.encode(), a.ctypes.data, a.size, f.ctypes.data, f.size, block) != 0:
+        if lib().tfb_writer_add_tensor_mixed(self._handle(), name.encode(), a.ctypes.data, a.size, f.ctypes.data, f.size, block) != 0:
             raise ValueError(f"add_tensor_mixed({name}) failed")
 
     def close(self, write_idx=True):
+        if self._stream is not None:
+            self._stream.close()
+            self._stream = None
+            if write_idx and self._names:
+                import struct
+                with open(self.path + ".idx", "wb") as g:
+                    g.write(IDX_MAGICS[0] + struct.pack("<II", 1, len(self._names)))
+                    for name in self._names:
+                        nb = name.encode()
+                        g.write(struct.pack("<H", len(nb)) + nb + sha256(nb))
+            return
+        if self._h is None and self._cfg is not None:
+            self._handle()                     # a writer closed without tensors still writes a valid, empty container
         h, self._h = self._h, None
         if h and lib().tfb_writer_close(h, int(write_idx)) != 0:
             raise IOError("writing .quant failed")
