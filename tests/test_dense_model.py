@@ -188,3 +188,15 @@ def test_multi_token_prediction_heads_train_and_files_roundtrip(tmp_path):
         full = model(ids)
         err = (q(ids) - full).abs().max()
     assert 0 < float(err) < 0.05 * float(full.abs().max())
+
+
+def test_rotary_embedding_object_rotates_and_inverts():
+    from transformers_fusion_b200.models.dense import RotaryEmbedding
+    cfg = TransformerConfig(**CASES["llama_gqa"])
+    r = RotaryEmbedding.from_config(cfg)
+    x = torch.randn(2 * 12, cfg.num_heads * cfg.head_dim)
+    y = r(x, cfg.num_heads, 12)
+    assert (y - x).abs().max() > 0 and torch.allclose(y.view(24, cfg.num_heads, -1).norm(dim=-1), x.view(24, cfg.num_heads, -1).norm(dim=-1), atol=1e-5)
+    assert torch.allclose(r.apply_(y.clone(), cfg.num_heads, 12, inverse=True), x, atol=1e-5)
+    lin = RotaryEmbedding(cfg.head_dim, 32, scaling_mode="linear", scaling_factor=2.0)
+    assert torch.allclose(lin.cos[2], r.cos[1], atol=1e-6)            # positions are divided by the factor

@@ -97,3 +97,74 @@ def test_reward_model_and_rollout_worker():
     out = w.drain()
     assert [o.seq for o in out] == [0, 1, 2, 3] and out[0].prompt == [3, 4, 5]
     assert len(pipe.run_round([[9, 10, 11]])) == 1
+
+
+def tiny_bytes(seed=0):
+    cfg = TransformerConfig(vocab_size=260, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=48, max_seq_len=64,
+                            init_std=0.1)
+    return DenseModel(cfg, dtype=torch.float32, seed=seed)
+
+
+def test_reference_named_helpers():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(2, 5, 7, generator=g)
+    ids = torch.randint(0, 7, (2, 5), generator=g)
+    lp = rl.GRPOTrainer.compute_log_probs(logits, ids)
+    want = torch.log_softmax(logits[:, :-1], -1).gather(-1, ids[:, 1:, None])[..., 0]
+    assert torch.allclose(lp, want) and rl.PPOTrainer.compute_kl_divergence(logits, logits) == 0.0
+    assert rl.PPOTrainer.compute_kl_divergence(logits, torch.zeros_like(logits)) > 0
+    adv = rl.PPOTrainer.compute_gae(torch.tensor([0.0, 0.0, 1.0]), torch.zeros(3))
+    assert abs(float(adv[0]) - (0.99 * 0.95) ** 2) < 1e-6
+    ret = rl.RLHFPipeline.compute_returns_discounted(torch.tensor([1.0, 0.0, 2.0]), 0.5)
+    assert ret.tolist() == [1.5, 1.0, 2.0]
+    acts = torch.randint(0, 7, (2, 5), generator=g)
+    assert rl.RLHFPipeline.compute_kl_between_policies(logits, logits, acts) == 0.0
+    m = tiny(5)
+    t = rl.PPOTrainer(m, lr=1e-3)
+    assert t.critic_forward(torch.zeros(2, 3, 32)).shape == (2, 3) and len(t.critic_parameters()) == 2
+    t.train_step(torch.randint(0, 64, (2, 8)), torch.ones(2, 8), torch.tensor([1.0, -1.0]))
+    assert t.last_kl() == t.last_kl() and t.kl_alpha() > 0 and t.optimizer() is t.opt
+    d = rl.DPOTrainer(tiny(6), beta=0.2)
+    d.set_beta(0.3)
+    assert d.beta == 0.3 and d.last_loss() == 0.0
+    gr = rl.GRPOTrainer(tiny(7), group_size=4)
+    gr.set_beta(0.1)
+    assert gr.group_size() == 4 and gr.beta == 0.1 and gr.last_loss() == 0.0
+
+
+def test_rlvr_text_form_and_verifier():
+    tok = ByteTokenizer()
+    t = rl.RLVRTrainer(tiny_bytes(1), tok, group_size=3, max_new_tokens=4, lr=1e-3)
+    assert t.verify("the answer is 42", "42") and not t.verify("nothing", "42") and not t.verify("x", " ")
+    loss = t.train_step("2+2=", "4")
+    assert loss == loss and 0.0 <= t.last_reward() <= 1.0
+    seen = []
+    t.verifier = lambda completion, answer: seen.append(answer) or float(len(seen) % 2)
+    t.train_step(prompt="q", answer="a")
+    assert seen == ["a"] * 3 and t.last_reward() == (1 + 0 + 1) / 3
+
+
+def test_rlhf_pipeline_stages_end_to_end():
+    tok = ByteTokenizer()
+    m = tiny_bytes(2)
+    pipe = rl.RLHFPipeline(rl.GRPOTrainer(m, tok, group_size=2, max_new_tokens=3, lr=1e-4), rl.RewardModel(m))
+    prompts = ["hi", "yo", "ok", "no", "go"]
+    pipe.generate_comparisons(prompts[:3], max_new_tokens=3)
+    cs = pipe.comparisons()
+    assert len(cs) == 3 and all(c.reward_chosen >= c.reward_rejected and c.chosen_ids[:2] == tok.encode(c.prompt) for c in cs)
+    # a synthetic preference the reward head can learn: chosen sequences end in low ids, rejected in high ids
+    data = [rl.Comparison("", [5, 6, 7, 8 + i], [5, 6, 7, 200 + i]) for i in range(8)]
+    acc0 = pipe.compute_reward_accuracy(data)
+    acc = pipe.train_reward_model_epoch_with_accuracy(data, None, epochs=40, batch_size=8)
+    assert acc >= 0.75 and acc >= acc0 and pipe.metrics().reward_loss < 0.69
+    w0 = m.flat.params.clone()
+    out = pipe.ppo_finetune(prompts[:2], n_ppo_steps=2, ppo_batch_size=2, max_new_tokens=3)
+    assert len(out) == 3 and not torch.equal(m.flat.params, w0)
+    assert pipe._ppo.opt is pipe.policy.opt                          # one optimizer state for the policy
+    assert pipe.dpo_finetune(data, n_steps=2, batch_size=4) == pipe.metrics().dpo_loss > 0
+    assert pipe.grpo_finetune(prompts[:2], n_steps=2, max_new_tokens=3) == pipe.metrics().grpo_loss
+    pipe.rlvf_finetune([("2+2=", "4")], n_steps=1, max_new_tokens=3)
+    logs = []
+    pipe.set_log_callback(lambda mt: logs.append(mt.step))
+    mt = pipe.run(n_rounds=2, n_ppo_steps=1, prompts=prompts, max_new_tokens=3)
+    assert logs == [0, 1] and 0.0 <= mt.reward_accuracy <= 1.0 and len(pipe.comparisons()) >= 3 + 2 * 4

@@ -27,6 +27,32 @@ from .config import TransformerConfig
 # =================================================================================================
 # flat parameter storage
 # =================================================================================================
+class RotaryEmbedding:
+    """Rotary position embedding as an object: the cos / sin tables of a head size (with the linear, NTK and YaRN context
+    scalings) and their application to [T, heads * head_dim] rows, in place, through the RoPE kernel.  The models keep
+    their tables themselves (``DenseModel.rope``); this class is the stand-alone form (reference: RotaryEmbedding,
+    src/model/transformer.cpp:124-270)."""
+
+    def __init__(self, head_dim: int, max_seq_len: int, theta: float = 10000.0, scaling_mode: str = "none",
+                 scaling_factor: float = 1.0, original_max_seq_len: int = 0, device="cpu", **yarn):
+        self.head_dim, self.max_seq_len = head_dim, max_seq_len
+        self.cos, self.sin = F.rope_tables(head_dim, max_seq_len, theta, scaling_mode, scaling_factor, original_max_seq_len,
+                                           device=device, **yarn)
+
+    @classmethod
+    def from_config(cls, cfg: TransformerConfig, device="cpu"):
+        return cls(cfg.head_dim, cfg.max_seq_len, cfg.rope_theta, cfg.rope_scaling_mode, cfg.rope_scaling_factor,
+                   cfg.rope_original_max_seq_len, device=device, yarn_attn_factor=cfg.yarn_attn_factor,
+                   yarn_beta_fast=cfg.yarn_beta_fast, yarn_beta_slow=cfg.yarn_beta_slow)
+
+    def apply_(self, x, n_heads: int, seq_len: int, pos_offset: int = 0, positions=None, inverse: bool = False):
+        """Rotate the first ``n_heads`` heads of every row of x [T, ld] in place (``inverse`` undoes it: the backward)."""
+        return F.rope_(x, self.cos, self.sin, n_heads, self.head_dim, seq_len, pos_offset, positions, backward=inverse)
+
+    def __call__(self, x, n_heads: int, seq_len: int, pos_offset: int = 0):
+        return self.apply_(x.clone(), n_heads, seq_len, pos_offset)
+
+
 class FlatBuffers:
     """Contiguous parameter / gradient storage.
 

@@ -58,6 +58,26 @@ class _RLBase:
         self.opt.step()
         self.steps += 1
 
+    # ---- reference-named helpers (include/quant/trainer.h:347-465)
+    def set_optimizer(self, opt):
+        """Use another flat optimizer (anything with ``step()`` over this model's flat buffers)."""
+        self.opt = opt
+
+    def optimizer(self):
+        return self.opt
+
+    @staticmethod
+    def compute_log_probs(logits, ids):
+        """log p of the tokens that follow: logits [B, S, V], ids [B, S] -> [B, S-1] (position t scores ids[:, t+1])."""
+        lp = torch.log_softmax(logits.float()[:, :-1], -1)
+        return lp.gather(-1, ids[:, 1:].unsqueeze(-1)).squeeze(-1)
+
+    @staticmethod
+    def compute_kl_divergence(logits_a, logits_b) -> float:
+        """Mean over positions of KL(softmax(a) || softmax(b))."""
+        la, lb = torch.log_softmax(logits_a.float(), -1), torch.log_softmax(logits_b.float(), -1)
+        return float((la.exp() * (la - lb)).sum(-1).mean())
+
     def generate(self, prompt_ids: List[int], n: int, max_new: int, temperature=1.0, top_k=0, top_p=1.0, seed=0):
         """n sampled completions of one prompt through the inference engine."""
         from ..inference.engine import EngineConfig, InferenceEngine
@@ -87,6 +107,11 @@ class GRPOTrainer(_RLBase):
         self.max_new = max_new_tokens
         self.ref_model = copy.deepcopy(model).eval() if kl_coef > 0 else None
         self.last_advantages = None
+        self._last_loss = 0.0
+
+    def set_beta(self, b: float): self.beta = float(b)
+    def group_size(self) -> int: return self.G
+    def last_loss(self) -> float: return self._last_loss
 
     @staticmethod
     def advantages(rewards: torch.Tensor) -> torch.Tensor:
@@ -131,7 +156,8 @@ class GRPOTrainer(_RLBase):
             kl = (torch.exp(ref_lp - lp) - (ref_lp - lp) - 1) * m
             loss = loss + self.kl_coef * (kl.sum(-1) / denom).mean()
         self._backward_and_step(loss, grad_scale=1.0 - 0.01 * self.beta)
-        return float(loss.detach())
+        self._last_loss = float(loss.detach())
+        return self._last_loss
 
 
 # ------------------------------------------------------------------------------------------------
@@ -158,6 +184,24 @@ class PPOTrainer(_RLBase):
         dev, dt = model.tok_embeddings.device, torch.float32
         self.value_head = torch.nn.Linear(H, 1).to(dev, dt)
         self.value_opt = torch.optim.Adam(self.value_head.parameters(), lr=1e-3)
+
+    def critic_forward(self, hidden):
+        """Value of every position from final hidden states [..., H]."""
+        return self.value_head(hidden.float()).squeeze(-1)
+
+    def critic_parameters(self):
+        return list(self.value_head.parameters())
+
+    @staticmethod
+    def compute_gae(rewards, values, gamma=0.99, lam=0.95):
+        """Advantages of one trajectory: rewards [T], values [T] or [T + 1] (a missing bootstrap value counts as 0)."""
+        r, v = torch.as_tensor(rewards).float().cpu(), torch.as_tensor(values).float().cpu()
+        if v.numel() == r.numel():
+            v = torch.cat([v, torch.zeros(1)])
+        return gae(r, v, gamma, lam)[0]
+
+    def kl_alpha(self) -> float: return self.kl_coef
+    def last_kl(self) -> float: return getattr(self, "_last_kl", 0.0)
 
     def values(self, ids):
         B, S = ids.shape
@@ -194,7 +238,7 @@ class PPOTrainer(_RLBase):
         self.value_opt.zero_grad()
         (self.value_coef * vloss).backward()
         self.value_opt.step()
-        kl = float(approx_kl.detach())
+        kl = self._last_kl = float(approx_kl.detach())
         if kl > 1.5 * self.kl_target:                 # adaptive KL coefficient
             self.kl_coef *= 1.5
         elif kl < self.kl_target / 1.5:
@@ -210,6 +254,10 @@ class DPOTrainer(_RLBase):
         super().__init__(model, tokenizer, lr=lr)
         self.beta = beta
         self.ref = (ref_model or copy.deepcopy(model)).eval()
+        self._last_loss = 0.0
+
+    def set_beta(self, b: float): self.beta = float(b)
+    def last_loss(self) -> float: return self._last_loss
 
     def train_step(self, chosen, rejected, chosen_mask, rejected_mask):
         dev = self.model.tok_embeddings.device
@@ -222,7 +270,8 @@ class DPOTrainer(_RLBase):
         margin = self.beta * ((pc - rc) - (pr - rr))
         loss = -TF.logsigmoid(margin).mean()
         self._backward_and_step(loss)
-        return float(loss.detach()), float((margin > 0).float().mean())
+        self._last_loss = float(loss.detach())
+        return self._last_loss, float((margin > 0).float().mean())
 
 
 # ------------------------------------------------------------------------------------------------
@@ -235,10 +284,32 @@ class RLVRTrainer(GRPOTrainer):
         super().__init__(model, tokenizer, **kw)
         self.verifier = verifier or (lambda completion, answer: 1.0 if answer.strip() and answer.strip() in completion else 0.0)
 
+    def verify(self, output: str, answer: str) -> bool:
+        return self.verifier(output, answer) > 0
+
+    def last_reward(self) -> float:
+        return getattr(self, "_last_reward", 0.0)
+
     def train_on_example(self, prompt: str, answer: str):
         p = self.tok.encode(prompt)
-        self.reward_fn = lambda ids: self.verifier(self.tok.decode(ids), answer)
-        return self.train_step(prompt=p)
+        got = []
+
+        def reward(ids):
+            got.append(self.verifier(self.tok.decode(ids), answer))
+            return got[-1]
+        self.reward_fn = reward
+        loss = GRPOTrainer.train_step(self, prompt=p)
+        self._last_reward = sum(got) / max(1, len(got))
+        return loss
+
+    def train_step(self, ids=None, mask=None, rewards=None, prompt=None, answer: Optional[str] = None):
+        """``train_step(prompt_text, answer_text)`` (the reference's verifiable form: sample a group, reward = the
+        verifier's verdict) or the group form of GRPO (ids, mask, rewards)."""
+        if isinstance(ids, str):
+            return self.train_on_example(ids, mask if isinstance(mask, str) else (answer or ""))
+        if isinstance(prompt, str):
+            return self.train_on_example(prompt, answer or "")
+        return GRPOTrainer.train_step(self, ids, mask, rewards, prompt)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -293,12 +364,243 @@ class RolloutWorker:
         return [self.buffer.popleft() for _ in range(n)]
 
 
+@dataclass
+class Comparison:
+    prompt: str = ""
+    chosen_ids: List[int] = field(default_factory=list)
+    rejected_ids: List[int] = field(default_factory=list)
+    reward_chosen: float = 0.0
+    reward_rejected: float = 0.0
+
+
+@dataclass
+class RLHFMetrics:
+    step: int = 0
+    reward_loss: float = 0.0
+    reward_accuracy: float = 0.0
+    ppo_loss: float = 0.0
+    ppo_kl: float = 0.0
+    dpo_loss: float = 0.0
+    grpo_loss: float = 0.0
+    mean_reward: float = 0.0
+
+
+DEFAULT_PROMPTS = ("Explain why the sky is blue.", "Write a short poem about AI.", "What is machine learning?",
+                   "Describe how a computer works.", "Tell me a joke.", "What is the capital of France?")
+
+
 class RLHFPipeline:
-    """reward-model fit -> rollouts -> policy optimisation, one round per ``run_round``."""
+    """Preference alignment loop: sample pairs of completions and rank them -> fit the reward model -> optimise the policy
+    (PPO against the reward model, DPO on the stored pairs, GRPO / verifiable-reward steps) - one round per ``run_round``
+    or the whole schedule with ``run``.  Reference: RLHFPipeline, include/quant/trainer.h:466-521,
+    src/trainer/trainer_rl.cpp:1021-1127, trainer_rl_ops.cpp:28-526 (whose ``generate_comparisons`` stores one greedy
+    sequence as both members of a pair; here the two members are two sampled completions ranked by reward)."""
 
     def __init__(self, policy_trainer: GRPOTrainer, reward_model: Optional[RewardModel] = None):
         self.policy, self.rm = policy_trainer, reward_model
         self.rm_opt = torch.optim.Adam(reward_model.head.parameters(), lr=1e-3) if reward_model is not None else None
+        self._comparisons: List[Comparison] = []
+        self._metrics = RLHFMetrics()
+        self.log_cb = None
+        self.verbose = False
+        self._ppo = self._dpo = None
+
+    # ---- bookkeeping
+    def comparisons(self) -> List[Comparison]: return self._comparisons
+    def metrics(self) -> RLHFMetrics: return self._metrics
+    def set_log_callback(self, cb): self.log_cb = cb
+    def set_verbose(self, v: bool): self.verbose = bool(v)
+
+    def _say(self, text):
+        if self.verbose:
+            print(text)
+
+    def _encode(self, prompt):
+        tok = self.policy.tok
+        if isinstance(prompt, str):
+            ids = tok.encode(prompt) if tok is not None else []
+            V = self.policy.model.cfg.vocab_size
+            return ids or [ord(c) % max(1, V - 5) + 5 for c in prompt]      # the reference's fallback without a tokenizer
+        return list(prompt)
+
+    def _score(self, ids: List[int]) -> float:
+        if self.rm is not None:
+            dev = self.policy.model.tok_embeddings.device
+            with torch.no_grad():
+                return float(self.rm.score(torch.tensor([ids or [0]], device=dev)))
+        return float(self.policy.reward_fn(ids))
+
+    # ---- math helpers with the reference's names
+    compute_gae = staticmethod(lambda rewards, values, gamma=0.99, lam=0.95: PPOTrainer.compute_gae(rewards, values, gamma, lam))
+
+    @staticmethod
+    def compute_returns_discounted(rewards, gamma: float = 0.99):
+        r = torch.as_tensor(rewards).float()
+        out, acc = torch.zeros_like(r), 0.0
+        for t in reversed(range(r.numel())):
+            acc = float(r[t]) + gamma * acc
+            out[t] = acc
+        return out
+
+    @staticmethod
+    def compute_kl_between_policies(logits_pi, logits_ref, actions) -> float:
+        """Mean over positions of log pi(a) - log ref(a) on the taken actions (the sampled-action KL estimate)."""
+        lp = torch.log_softmax(logits_pi.float(), -1).gather(-1, actions.long().unsqueeze(-1)).squeeze(-1)
+        lr_ = torch.log_softmax(logits_ref.float(), -1).gather(-1, actions.long().unsqueeze(-1)).squeeze(-1)
+        return float((lp - lr_).mean())
+
+    # ---- data
+    def generate_comparisons(self, prompts, max_new_tokens: int = 64):
+        """Two sampled completions per prompt, ranked by the reward model (or the policy trainer's reward function)."""
+        for i, p in enumerate(prompts):
+            ids = self._encode(p)
+            a, b = self.policy.generate(ids, 2, max_new_tokens, temperature=1.0, seed=len(self._comparisons))
+            ra, rb = self._score(ids + a), self._score(ids + b)
+            if rb > ra:
+                a, b, ra, rb = b, a, rb, ra
+            self._comparisons.append(Comparison(p if isinstance(p, str) else "", ids + a, ids + b, ra, rb))
+            self._say(f"[RLHF] Comparison {i + 1}/{len(prompts)} | reward_chosen={ra:.4f} reward_rejected={rb:.4f}")
+        return self._comparisons
+
+    def _pair_batch(self, data: Sequence[Comparison]):
+        dev = self.policy.model.tok_embeddings.device
+        S = max(max(len(c.chosen_ids), len(c.rejected_ids)) for c in data)
+
+        def pad(rows):
+            ids = torch.zeros((len(rows), S), dtype=torch.long)
+            mask = torch.zeros((len(rows), S))
+            for i, r in enumerate(rows):
+                ids[i, :len(r)] = torch.tensor(r)
+                mask[i, :len(r)] = 1
+            return ids.to(dev), mask.to(dev)
+        return pad([c.chosen_ids for c in data]), pad([c.rejected_ids for c in data])
+
+    def _rm_scores(self, ids, mask):
+        return self.rm.score(ids, mask.sum(-1).long().clamp(min=1))
+
+    # ---- reward model
+    def compute_reward_accuracy(self, data: Optional[Sequence[Comparison]] = None) -> float:
+        """Fraction of pairs whose chosen member the reward model scores higher."""
+        data = list(data if data is not None else self._comparisons)
+        data = [c for c in data if c.chosen_ids and c.rejected_ids]
+        if not data or self.rm is None:
+            return 0.0
+        (ci, cm), (ri, rm_) = self._pair_batch(data)
+        with torch.no_grad():
+            return float((self._rm_scores(ci, cm) > self._rm_scores(ri, rm_)).float().mean())
+
+    def train_reward_model(self, data: Optional[Sequence[Comparison]] = None, epochs: int = 3, batch_size: int = 8):
+        data = [c for c in (data if data is not None else self._comparisons) if c.chosen_ids and c.rejected_ids]
+        last = 0.0
+        for _ in range(epochs):
+            for o in range(0, len(data), batch_size):
+                (ci, cm), (ri, rm_) = self._pair_batch(data[o:o + batch_size])
+                loss = -TF.logsigmoid(self._rm_scores(ci, cm) - self._rm_scores(ri, rm_)).mean()
+                self.rm_opt.zero_grad()
+                loss.backward()
+                self.rm_opt.step()
+                last = float(loss.detach())
+        self._metrics.reward_loss = last
+        return last
+
+    def train_reward_model_epoch_with_accuracy(self, train_data, val_data, epochs: int = 3, batch_size: int = 8, split_name=None):
+        """Fit on ``train_data`` and report the pairwise accuracy on ``val_data`` after every epoch; returns the last."""
+        acc = 0.0
+        for e in range(epochs):
+            loss = self.train_reward_model(train_data, 1, batch_size)
+            acc = self.compute_reward_accuracy(val_data if val_data else train_data)
+            self._say(f"[{split_name or 'RM'}] epoch {e + 1}/{epochs} loss={loss:.4f} val_acc={acc:.3f}")
+        self._metrics.reward_accuracy = acc
+        return acc
+
+    # ---- policy optimisation stages
+    def _share_optimizer(self, trainer):
+        trainer.flat, trainer.opt = self.policy.flat, self.policy.opt        # one optimizer state per policy
+        return trainer
+
+    def ppo_finetune(self, prompts, n_ppo_steps: int = 100, ppo_batch_size: int = 8, max_new_tokens: int = 64):
+        """PPO steps on sampled completions whose terminal reward is the reward model's score."""
+        if self._ppo is None:
+            self._ppo = self._share_optimizer(PPOTrainer(self.policy.model, self.policy.tok))
+        dev = self.policy.model.tok_embeddings.device
+        out = (0.0, 0.0, 0.0)
+        for step in range(n_ppo_steps):
+            ids_p = self._encode(prompts[step % len(prompts)])
+            outs = self.policy.generate(ids_p, ppo_batch_size, max_new_tokens, temperature=1.0, seed=step)
+            S = len(ids_p) + max(1, max(len(o) for o in outs))
+            ids, mask = torch.zeros((len(outs), S), dtype=torch.long), torch.zeros((len(outs), S))
+            for i, o in enumerate(outs):
+                seq = ids_p + o
+                ids[i, :len(seq)] = torch.tensor(seq)
+                mask[i, len(ids_p):len(seq)] = 1
+            rewards = torch.tensor([self._score(ids_p + o) for o in outs])
+            out = self._ppo.train_step(ids.to(dev), mask.to(dev), rewards)
+            self._metrics.mean_reward = float(rewards.mean())
+        self._metrics.ppo_loss, self._metrics.ppo_kl = out[0], out[2]
+        return out
+
+    def dpo_finetune(self, comparisons: Optional[Sequence[Comparison]] = None, n_steps: int = 10, batch_size: int = 4):
+        data = [c for c in (comparisons if comparisons is not None else self._comparisons) if c.chosen_ids and c.rejected_ids]
+        if not data:
+            return 0.0
+        if self._dpo is None:
+            self._dpo = self._share_optimizer(DPOTrainer(self.policy.model, tokenizer=self.policy.tok))
+        loss = 0.0
+        for step in range(n_steps):
+            o = (step * batch_size) % len(data)
+            (ci, cm), (ri, rm_) = self._pair_batch((data + data)[o:o + batch_size])
+            loss, _ = self._dpo.train_step(ci, ri, cm, rm_)
+        self._metrics.dpo_loss = loss
+        return loss
+
+    def grpo_finetune(self, prompts, n_steps: int = 20, max_new_tokens: int = 32):
+        self.policy.max_new = max_new_tokens
+        if self.rm is not None:
+            self.policy.reward_fn = lambda ids: self._score(ids)
+        loss = 0.0
+        for step in range(n_steps):
+            loss = self.policy.train_step(prompt=self._encode(prompts[step % len(prompts)]))
+        self._metrics.grpo_loss = loss
+        return loss
+
+    def rlvf_finetune(self, qa_pairs, n_steps: int = 20, max_new_tokens: int = 32, verifier=None):
+        """Verifiable-reward steps: the reward of a completion is whether it contains the pair's answer."""
+        verifier = verifier or (lambda completion, answer: 1.0 if answer.strip() and answer.strip() in completion else 0.0)
+        tok = self.policy.tok
+        self.policy.max_new = max_new_tokens
+        loss = 0.0
+        for step in range(n_steps):
+            q, a = qa_pairs[step % len(qa_pairs)]
+            self.policy.reward_fn = lambda ids, a=a: verifier(tok.decode(ids) if tok is not None else "", a)
+            loss = self.policy.train_step(prompt=self._encode(q))
+        self._metrics.grpo_loss = loss
+        return loss
+
+    def run(self, n_rounds: int = 3, n_prompts: int = 50, n_ppo_steps: int = 200, prompts=None, max_new_tokens: int = 32):
+        """Rounds of: new comparisons -> reward model (one more epoch each round, a fifth of the prompts held out) -> PPO
+        -> DPO on everything gathered so far."""
+        prompts = list(prompts) if prompts else [DEFAULT_PROMPTS[i % len(DEFAULT_PROMPTS)] for i in range(n_prompts)]
+        hold = max(1, len(prompts) // 5)
+        train_prompts = prompts[:-hold] or prompts
+        heldout: List[Comparison] = []
+        for rnd in range(n_rounds):
+            self._say(f"=== RLHF Round {rnd + 1}/{n_rounds} ===")
+            self._metrics.step = rnd
+            if not heldout and self.rm is not None:
+                before = len(self._comparisons)
+                self.generate_comparisons(prompts[-hold:], max_new_tokens)
+                heldout, self._comparisons = self._comparisons[before:], self._comparisons[:before]
+            self.generate_comparisons(train_prompts, max_new_tokens)
+            if self.rm is not None:
+                self.train_reward_model_epoch_with_accuracy(self._comparisons, heldout, max(1, 3 + rnd), 8, "RM")
+            self.ppo_finetune(train_prompts, max(1, n_ppo_steps + rnd * 10), 8, max_new_tokens)
+            if len(self._comparisons) > 4:
+                self.dpo_finetune(self._comparisons, max(1, 2 + rnd), 4)
+            if self.rm is not None:
+                self._metrics.reward_accuracy = self.compute_reward_accuracy(self._comparisons)
+            if self.log_cb:
+                self.log_cb(self._metrics)
+        return self._metrics
 
     def fit_reward_model(self, chosen, rejected, steps=10):
         losses = []
@@ -307,7 +609,7 @@ class RLHFPipeline:
             self.rm_opt.zero_grad()
             loss.backward()
             self.rm_opt.step()
-            losses.append(float(loss))
+            losses.append(float(loss.detach()))
         return losses
 
     def run_round(self, prompts: List[List[int]]):
