@@ -94,3 +94,112 @@ def test_batcher_embeddings_lowprec():
     ids = torch.randint(0, 259, (2, 8))
     logits = sh1.forward(sh0.forward(ids, 2, 8), 2, 8)
     assert torch.allclose(logits.view(2, 8, -1), m.forward(ids).detach(), atol=1e-4)
+
+
+def test_reference_named_inference_helpers():
+    """Sampler verbs, tree decoding loop, batched generation, embeddings / reranking scores, speculative counters,
+    prefix-cache verbs, the block pool and the compressed-KV accessors."""
+    import torch
+    from transformers_fusion_b200.inference import generation as G
+    from transformers_fusion_b200.inference.engine import PrefixCache
+    from transformers_fusion_b200.inference.kv_cache import PAGE, PageAllocator
+    from transformers_fusion_b200.inference.kv_extras import CompressedKVCache
+    from transformers_fusion_b200.inference.sampler import Sampler, SamplerConfig
+    from transformers_fusion_b200.inference.speculative_extras import InferenceMemoryPool
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    s = Sampler(SamplerConfig(temperature=1.0, top_k=3, top_p=1.0, repetition_penalty=2.0))
+    z = torch.tensor([4.0, 3.0, -2.0, 1.0, 0.5])
+    assert s.greedy(z) == 0 and torch.allclose(s.apply_temperature(z, 2.0), z / 2)
+    pen = s.apply_repetition_penalty(z, [0, 2], 2.0)
+    assert pen.tolist() == [2.0, 3.0, -4.0, 1.0, 0.5]
+    s.set_seed(7)
+    draws = {s.sample_top_k(z, 2) for _ in range(40)}
+    assert draws <= {0, 1} and len(draws) == 2
+    assert {s.sample_top_p(z, 0.5) for _ in range(20)} == {0}
+    assert s.sample(z, history=[0]) in (0, 1, 3)                    # the penalty demotes token 0 but keeps it in the top 3
+    assert Sampler(SamplerConfig(temperature=0.0, repetition_penalty=4.0)).sample(z, history=[0]) == 1
+    assert SamplerConfig(max_tokens=5000).effective_max_tokens("medium") == 2048 and SamplerConfig().effective_max_tokens() == 512
+    assert G.StreamingConfig(max_tokens=999).effective_max_tokens("low") == 256
+    tok = ByteTokenizer()
+    cfg = TransformerConfig(vocab_size=260, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=64, max_seq_len=64)
+    tgt, drf = DenseModel(cfg, dtype=torch.float32, seed=1), DenseModel(cfg, dtype=torch.float32, seed=1)
+    out = G.TreeDecoder(tgt, drf, branching=2, depth=2).decode(tok.encode("ab"), 5)
+    ids = tok.encode("ab")
+    greedy = []
+    for _ in range(5):
+        with torch.no_grad():
+            greedy.append(int(tgt(torch.tensor([ids + greedy]))[0, -1].argmax()))
+    assert out == greedy                                             # identical draft: every tree step is accepted in full
+    texts = G.DynamicBatcher(max_batch=4, model=tgt, tokenizer=tok).batch_generate(["ab", "hello"], 4)
+    assert len(texts) == 2 and all(isinstance(t, str) for t in texts)
+    ep = G.EmbeddingEndpoint(tgt, tok)
+    assert ep.embed_batch(["a", "bc"]).shape == (2, 32)
+    rr = G.Reranker(ep)
+    sc = rr.score_batch("hello", ["hello", "zzzz"])
+    assert abs(sc[0] - 1.0) < 1e-5 and rr.score("hello", "zzzz") == pytest.approx(sc[1], abs=1e-6) and sc[1] < sc[0]
+    sd = G.SpeculativeDecoder(tgt, drf, gamma=2, adaptive=False)
+    sd.generate(tok.encode("ab"), 6)
+    assert sd.accepted_count() == sd.total_count() > 0 and sd.acceptance_rate() == 1.0 and sd.current_gamma() == 2.0
+    assert not sd.used_uniform_draft_fallback()
+    alloc = PageAllocator(8)
+    pc = PrefixCache(alloc)
+    toks = list(range(2 * PAGE + 3))
+    pages = [alloc.alloc(), alloc.alloc()]
+    pc.store(toks, pages)
+    assert pc.match_prefix(toks) == 2 * PAGE and pc.match_prefix(toks[:PAGE + 1]) == PAGE and pc.match_prefix([9] * 40) == 0
+    assert pc.get_cache(toks) == pages and alloc.refs[pages[0]] == 3
+    pool = InferenceMemoryPool.of_blocks(1024, 2)
+    a, b = pool.alloc(), pool.alloc()
+    assert {a, b} == {0, 1} and pool.alloc() is None and pool.used == 2048
+    pool.free(a)
+    assert pool.alloc() == a
+    with pytest.raises(ValueError):
+        pool.free(b), pool.free(b)
+    kv = CompressedKVCache(2, 32, 8)
+    k, v = torch.randn(3, 2, 32), torch.randn(3, 2, 32)
+    kv.append(k, v)
+    K, V = kv.get()
+    assert torch.equal(kv.get_k(1), K[1]) and torch.equal(kv.get_v(2), V[2]) and kv.size() == 3
+    kv.clear()
+    assert kv.size() == 0
+    with pytest.raises(IndexError):
+        kv.get_k(0)
+
+
+def test_attention_variants_against_plain_statement():
+    import math
+    import torch
+    from transformers_fusion_b200.inference.attention_variants import (ALiBi, GroupedQueryAttention, MultiQueryAttention,
+                                                                     SlidingWindowAttention, compute_logprobs)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 10, 32, generator=g)
+
+    def plain(m, bias=None):
+        B, S, _ = x.shape
+        H, Hkv, D = m.n_heads(), m.n_kv_heads(), m.head_dim
+        q = (x @ m.w_q.t()).view(B, S, H, D).transpose(1, 2)
+        k = (x @ m.w_k.t()).view(B, S, Hkv, D).transpose(1, 2).repeat_interleave(H // Hkv, 1)
+        v = (x @ m.w_v.t()).view(B, S, Hkv, D).transpose(1, 2).repeat_interleave(H // Hkv, 1)
+        s = q @ k.transpose(-1, -2) / math.sqrt(D)
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+        if bias is not None:
+            s = s + bias
+        return (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, H * D) @ m.w_o.t()
+    gqa = GroupedQueryAttention(32, 4, 2, seed=1)
+    assert torch.allclose(gqa(x), plain(gqa), atol=1e-5) and gqa.w_k.shape == (16, 32)
+    mqa = MultiQueryAttention(32, 4, seed=2)
+    assert mqa.n_kv_heads() == 1 and torch.allclose(mqa(x), plain(mqa), atol=1e-5)
+    swa = SlidingWindowAttention(32, 4, window_size=3, seed=3)
+    i, j = torch.arange(10)[:, None], torch.arange(10)[None, :]
+    assert torch.allclose(swa(x), plain(swa, torch.where(i - j >= 3, float("-inf"), 0.0)), atol=1e-5)
+    wide = SlidingWindowAttention(32, 4, window_size=64, seed=3)
+    assert torch.allclose(wide(x), plain(wide), atol=1e-5)          # a window longer than the sequence changes nothing
+    al = ALiBi(4, 32, seed=4)
+    assert al.slopes.tolist() == pytest.approx([0.25, 0.0625, 0.015625, 0.00390625])
+    bias = al.build_alibi_bias(10, 10)
+    assert bias.shape == (4, 10, 10) and float(bias[0, 5, 3]) == -0.5 and float(bias[0, 3, 5]) == 0.0
+    assert torch.allclose(al(x), plain(al, bias), atol=1e-5) and len(ALiBi.compute_slopes(6)) == 6
+    lp = compute_logprobs(torch.randn(3, 7, generator=g), [1, 2, 3])
+    assert len(lp) == 3 and len(lp[0]) == 7 and abs(sum(math.exp(v) for v in lp[0]) - 1.0) < 1e-5

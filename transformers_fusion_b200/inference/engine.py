@@ -121,6 +121,25 @@ class PrefixCache:
             self.alloc.release(p)
         self.table.clear()
 
+    # ---- the reference's verbs (include/quant/inference_opt.h:108-119)
+    def match_prefix(self, tokens) -> int:
+        """Number of leading tokens whose K/V is cached (a multiple of the page size); takes no reference."""
+        n = 0
+        while n + PAGE <= len(tokens) - 1:
+            p = self.table.get(self._key(tokens, n + PAGE))
+            if p is None or self.alloc.refs[p] == 0:
+                break
+            n += PAGE
+        return n
+
+    def store(self, tokens, pages):
+        """Remember the pages that hold the whole-page prefixes of ``tokens`` (same as ``insert``)."""
+        self.insert(tokens, pages)
+
+    def get_cache(self, tokens):
+        """Pages of the longest cached prefix, each with a new reference for the caller (same as ``lookup``)."""
+        return self.lookup(tokens)
+
 
 class _TokenBuffers(list):
     """A claimed pair of pinned buffers; when the engine that holds it goes away the pair is free for the next engine."""

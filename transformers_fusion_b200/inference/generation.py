@@ -80,6 +80,11 @@ class StreamingConfig:
     stop_strings: Sequence[str] = ()
     top_logprobs: int = 0
 
+    def effective_max_tokens(self, budget: Optional[str] = None) -> int:
+        from .sampler import REASONING_BUDGET
+        cap = REASONING_BUDGET.get((budget or "").lower())
+        return min(self.max_tokens, cap) if cap else self.max_tokens
+
 
 class StreamingGenerator:
     START, TOKEN, COMPLETE, ERROR, STOP = "START", "TOKEN", "COMPLETE", "ERROR", "STOP"
@@ -107,6 +112,13 @@ class StreamingGenerator:
 
     def tokens_per_sec(self):
         return self._tps
+
+    def num_tokens_generated(self) -> int:
+        return len(self._out)
+
+    def stopped(self) -> bool:
+        """True when the last generation ended on a stop request or a stop string."""
+        return getattr(self, "_stopped", False)
 
     @torch.no_grad()
     def generate(self, prompt, cfg: Optional[StreamingConfig] = None) -> str:
@@ -146,6 +158,7 @@ class StreamingGenerator:
                     break
             dt = time.perf_counter() - t0
             self._tps = len(self._out) / max(dt, 1e-9)
+            self._stopped = reason == self.STOP
             self.handler(reason, {"text": text, "tokens": len(self._out), "tokens_per_sec": self._tps})
             return text
         except Exception as e:                         # surface the failure as an event, then re-raise
@@ -201,6 +214,13 @@ class SpeculativeDecoder:
         self.gamma, self.adaptive, self.max_gamma = gamma, adaptive, max_gamma
         self.gen = torch.Generator().manual_seed(seed)
         self.stats = SpeculativeStats()
+
+    # ---- counters with the reference's names (include/quant/inference_opt.h:41-49)
+    def acceptance_rate(self) -> float: return self.stats.acceptance_rate
+    def accepted_count(self) -> int: return self.stats.accepted
+    def total_count(self) -> int: return self.stats.proposed
+    def current_gamma(self) -> float: return float(self.gamma)
+    def used_uniform_draft_fallback(self) -> bool: return False      # a draft model is mandatory here
 
     def _probs(self, logits_row, sc: SamplerConfig):
         if sc.temperature <= 0:
@@ -300,15 +320,38 @@ class TreeDecoder:
                 best, best_tok = p[:n], int(lg[base + n].argmax())
         return best + [best_tok]
 
+    def decode(self, prompt: Sequence[int], max_tokens: int, eos_id: int = -1) -> List[int]:
+        """Generate up to ``max_tokens`` tokens, one verified tree step at a time; returns the new tokens."""
+        out: List[int] = []
+        while len(out) < max_tokens:
+            step = self.step(list(prompt) + out)
+            for t in step:
+                out.append(t)
+                if t == eos_id or len(out) >= max_tokens:
+                    return out
+        return out
+
 
 # ================================================================================================ serving helpers
 class DynamicBatcher:
-    """Collects requests for up to ``window_s`` or ``max_batch`` items, then hands them out as one left-padded batch."""
+    """Collects requests for up to ``window_s`` or ``max_batch`` items, then hands them out as one left-padded batch.
+    With a model and tokenizer, ``batch_generate(prompts, max_tokens)`` answers a list of prompts in one continuous batch."""
 
-    def __init__(self, max_batch=8, window_s=0.005, pad_id=0):
+    def __init__(self, max_batch=8, window_s=0.005, pad_id=0, model=None, tokenizer=None):
         self.max_batch, self.window_s, self.pad_id = max_batch, window_s, pad_id
+        self.model, self.tok = model, tokenizer
         self.queue: List = []
         self.lock = threading.Condition()
+
+    def batch_generate(self, prompts: Sequence[str], max_tokens: int, sampling: Optional[SamplerConfig] = None) -> List[str]:
+        if self.model is None or self.tok is None:
+            raise RuntimeError("batch_generate needs the batcher to be built with a model and a tokenizer")
+        eng = InferenceEngine(self.model, self.tok, EngineConfig(max_batch=min(self.max_batch, max(1, len(prompts))),
+                                                                 num_pages=max(64, 16 * len(prompts))))
+        outs = eng.generate_batch([self.tok.encode(p) or [0] for p in prompts], max_tokens,
+                                  sampling or SamplerConfig(temperature=0.0))
+        eos = getattr(self.tok, "eos_id", -1)
+        return [self.tok.decode([t for t in o if t != eos]) for o in outs]
 
     def submit(self, tokens: Sequence[int], tag=None):
         with self.lock:
@@ -350,9 +393,20 @@ class EmbeddingEndpoint:
         return torch.stack(out)
 
 
+    embed_batch = embed
+
+
 class Reranker:
     def __init__(self, endpoint: EmbeddingEndpoint):
         self.ep = endpoint
+
+    def score(self, query: str, document: str) -> float:
+        """Cosine similarity of the two mean-pooled embeddings."""
+        return self.score_batch(query, [document])[0]
+
+    def score_batch(self, query: str, documents: Sequence[str]) -> List[float]:
+        e = torch.nn.functional.normalize(self.ep.embed([query] + list(documents)), dim=-1)
+        return (e[1:] @ e[0]).tolist()
 
     def rerank(self, query: str, docs: Sequence[str], top_k: Optional[int] = None):
         e = self.ep.embed([query] + list(docs))

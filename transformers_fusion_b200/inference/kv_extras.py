@@ -224,6 +224,27 @@ class CompressedKVCache:
     def bytes_per_token(self):
         return 2 * self.H * (self.D / 4 + self.D / 32 * 2)
 
+    def _row(self, i, pos):
+        p = self.codes[i, pos]
+        c = torch.stack([p & 3, (p >> 2) & 3, (p >> 4) & 3, p >> 6], -1).reshape(self.H, self.D).float() - 1
+        return c * self.scales[i, pos].float().repeat_interleave(32, -1)
+
+    def get_k(self, pos: int) -> torch.Tensor:
+        """Decoded keys [heads, dim] of one cached position."""
+        if not 0 <= pos < self.len:
+            raise IndexError(pos)
+        return self._row(0, pos)
+
+    def get_v(self, pos: int) -> torch.Tensor:
+        if not 0 <= pos < self.len:
+            raise IndexError(pos)
+        return self._row(1, pos)
+
+    def size(self) -> int: return self.len
+
+    def clear(self):
+        self.len = 0
+
 
 def flash_decoding(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, splits=4, scale=None):
     """q [H, D], k / v [N, Hkv, D] -> [H, D]; the key range is cut into ``splits`` chunks whose partial (max, sum, output)
@@ -278,6 +299,13 @@ class PagedAttention:
 
     def free_block(self, block_id: int):
         self.cache.allocator.release(block_id)
+
+    def num_blocks(self) -> int:
+        """Pages of the pool (page 0 is the scratch page of padded rows)."""
+        return len(self.cache.allocator.refs)
+
+    def available_blocks(self) -> int:
+        return len(self.cache.allocator.free)
 
     def forward(self, q, block_table, seq_lens, num_q_heads):
         return self.cache.decode(self.layer, q, block_table, seq_lens, num_q_heads)

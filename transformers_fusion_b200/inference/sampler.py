@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -27,6 +28,11 @@ class SamplerConfig:
     max_tokens: int = 512
     seed: int = 42
     reference_rule: bool = False
+
+    def effective_max_tokens(self, budget: Optional[str] = None) -> int:
+        """``max_tokens`` capped by a reasoning budget level ("low" 256 / "medium" 2048 / "high" 8192) when one is given."""
+        cap = REASONING_BUDGET.get((budget or "").lower())
+        return min(self.max_tokens, cap) if cap else self.max_tokens
 
 
 class _Desc(C.Structure):
@@ -117,3 +123,51 @@ class Sampler:
         t, k, p, r = self.params(logits.shape[0], logits.device)
         self.step += 1
         return sample(logits, t, k, p, r, history, self.cfg.seed, self.step)
+
+    # ---- the single-row verbs of the reference's Sampler (include/quant/sampler.h; src/inference/sampler.cpp)
+    def set_seed(self, seed: int):
+        self.cfg.seed, self.step = int(seed), 0
+
+    @staticmethod
+    def apply_temperature(logits: torch.Tensor, temperature: float) -> torch.Tensor:
+        return logits.float() / max(float(temperature), 1e-6)
+
+    @staticmethod
+    def apply_repetition_penalty(logits: torch.Tensor, history, penalty: float) -> torch.Tensor:
+        """Seen tokens: positive logits divided by the penalty, negative ones multiplied by it."""
+        z = logits.float().clone()
+        if penalty != 1.0 and history is not None and len(history):
+            idx = torch.as_tensor(sorted({int(t) for t in history if 0 <= int(t) < z.shape[-1]}), dtype=torch.long, device=z.device)
+            if idx.numel():
+                v = z[..., idx]
+                z[..., idx] = torch.where(v > 0, v / penalty, v * penalty)
+        return z
+
+    @staticmethod
+    def greedy(logits: torch.Tensor) -> int:
+        return int(logits.reshape(-1, logits.shape[-1])[-1].argmax())
+
+    def _draw(self, logits, temperature, top_k, top_p, history=None):
+        row = logits.reshape(-1, logits.shape[-1])[-1:].contiguous()
+        dev = row.device
+        one = lambda v, dt: torch.full((1,), v, dtype=dt, device=dev)
+        hist = None
+        if history is not None and len(history) and self.cfg.repetition_penalty != 1.0:
+            hist = torch.as_tensor([list(history)], dtype=torch.int32 if row.is_cuda else torch.long, device=dev)
+        self.step += 1
+        return int(sample(row, one(temperature, torch.float32), one(top_k, torch.int32), one(top_p, torch.float32),
+                          one(self.cfg.repetition_penalty, torch.float32), hist, self.cfg.seed, self.step)[0])
+
+    def sample_top_k(self, logits, k: int, temperature: Optional[float] = None) -> int:
+        return self._draw(logits, self.cfg.temperature if temperature is None else temperature, k, 1.0)
+
+    def sample_top_p(self, logits, p: float, temperature: Optional[float] = None) -> int:
+        return self._draw(logits, self.cfg.temperature if temperature is None else temperature, 0, p)
+
+    def sample(self, logits, history=None) -> int:
+        """One token for one row of logits under the configuration (``reference_rule``: top-p when p < 1, else top-k)."""
+        c = self.cfg
+        if c.temperature <= 0:
+            return self.greedy(self.apply_repetition_penalty(logits.reshape(-1, logits.shape[-1])[-1], history, c.repetition_penalty))
+        k = 0 if (c.reference_rule and c.top_p < 1.0) else c.top_k
+        return self._draw(logits, c.temperature, k, c.top_p, history)

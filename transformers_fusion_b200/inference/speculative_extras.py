@@ -8,6 +8,8 @@ MemoryEfficientAttention forward / forward_block_sparse, max_context_tokens 4M (
 MultiGPUManager detect / allocate_on / transfer (src/backend/gpu_extras.cpp:154-455)."""
 from __future__ import annotations
 
+import threading
+
 import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -104,6 +106,7 @@ class InferenceMemoryPool:
         self.capacity, self.used = int(capacity_bytes), 0
         self._by_owner: Dict[object, int] = {}
         self.peak = 0
+        self._lock = threading.Lock()
 
     def reserve(self, owner, nbytes: int) -> bool:
         if nbytes < 0 or self.used + nbytes > self.capacity:
@@ -117,6 +120,31 @@ class InferenceMemoryPool:
         n = self._by_owner.pop(owner, 0)
         self.used -= n
         return n
+
+    # ---- fixed-size block form (reference: InferenceMemoryPool(block_size, num_blocks), include/quant/inference_opt.h:188-201)
+    @classmethod
+    def of_blocks(cls, block_size: int, num_blocks: int) -> "InferenceMemoryPool":
+        pool = cls(block_size * num_blocks)
+        pool.block_size, pool._free_blocks = block_size, list(range(num_blocks - 1, -1, -1))
+        return pool
+
+    def alloc(self):
+        """Handle (block index) of a free block, or None when the pool is exhausted."""
+        free = getattr(self, "_free_blocks", None)
+        if free is None:
+            raise RuntimeError("alloc() needs a pool made with InferenceMemoryPool.of_blocks")
+        with self._lock:
+            if not free:
+                return None
+            self.used += self.block_size
+            return free.pop()
+
+    def free(self, handle: int):
+        with self._lock:
+            if handle in self._free_blocks:
+                raise ValueError(f"block {handle} is already free")
+            self._free_blocks.append(handle)
+            self.used -= self.block_size
 
     def available(self) -> int: return self.capacity - self.used
     def utilization(self) -> float: return self.used / self.capacity if self.capacity else 0.0
