@@ -98,3 +98,155 @@ def test_telemetry(capsys):
     assert torch.equal(kq.quantize(x, "fp"), x) and (kq.quantize(x, "q4") - x).abs().max() < 0.5 and len(torch.unique(kq.quantize(x, "ternary")[0, :32].abs())) <= 2
     line = T.TelemetryPrinter.print_training_step(3, 2.0, 1e-3, 1234.5, 0.7, m)
     assert line.startswith("Step 3 | loss: 2 | ppl: 7.38906 | lr: 0.001 | tok/s: 1234.5") and "Step 3" in capsys.readouterr().out
+
+
+def test_reference_dataset_verbs(tmp_path):
+    import numpy as np
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    tok = ByteTokenizer()
+    (tmp_path / "a.txt").write_text("hello world, this is a text file with enough characters in it")
+    (tmp_path / "b.txt").write_text("second file of the directory, also long enough to cut windows")
+    ds = D.InMemoryDataset.from_text_file(str(tmp_path / "a.txt"), tok, 8, stride=4, max_samples=5)
+    assert ds.size() == 5 and ds.get(1)[0].tolist() == tok.encode("o world,")[:8] and torch.equal(ds.get(0)[0][1:], ds.get(0)[1][:-1])
+    assert len(ds.inputs()) == len(ds.targets()) == 5
+    both = D.InMemoryDataset.from_directory(str(tmp_path), ".txt", tok, 8)
+    assert both.size() == D.InMemoryDataset.from_text_file(str(tmp_path / "a.txt"), tok, 8).size() + \
+        D.InMemoryDataset.from_text_file(str(tmp_path / "b.txt"), tok, 8).size()
+    np.arange(100, dtype=np.int64).tofile(tmp_path / "t.bin")
+    tk = D.InMemoryDataset.from_tokenized_file(str(tmp_path / "t.bin"), 9, max_samples=3)
+    assert tk.size() == 3 and tk.get(2)[0].tolist() == list(range(18, 27)) and tk.get(2)[1][-1] == 27
+    ds.add_sample(torch.zeros(8), torch.ones(8))
+    assert ds.size() == 6
+    ds.clear()
+    assert ds.size() == 0
+    m = D.MapDataset(tk, lambda x, y: (x + 1, y))
+    assert m.get(0)[0][0] == 1
+    m.set_map_fn(lambda pair: pair[1])
+    assert m.get(0).tolist() == list(range(1, 10))
+    f = D.FilterDataset(tk, lambda x, y: int(x[0]) >= 9)
+    assert f.filtered_indices() == [1, 2] and f.size() == 2
+    c = D.ConcatDataset()
+    c.add_dataset(tk), c.add_dataset(f)
+    assert c.num_datasets() == 2 and c.size() == 5 and c.get(3)[0][0] == 9
+    sh = D.ShuffleDataset(D.InMemoryDataset(list(range(20))), seed=1, buffer_size=5)
+    p = sh.permutation()
+    assert sorted(p) == list(range(20)) and all(i // 5 == v // 5 for i, v in enumerate(p))
+    sh.reshuffle()
+    assert sh.permutation() != p and sorted(sh.permutation()) == list(range(20))
+    ch = D.ChunkedDataset(str(tmp_path / "t.bin"), 10, overlap=5)
+    assert ch.num_chunks() == 19 and list(ch.get(1)) == list(range(5, 15))
+    ch.set_overlap(0)
+    assert ch.num_chunks() == 10
+    # token shards: whitespace-separated ids, read through a small buffer
+    (tmp_path / "s0.tok").write_text(" ".join(map(str, range(0, 50))))
+    (tmp_path / "s1.tok").write_text("\n".join(map(str, range(50, 80))) + "\n")
+    st = D.StreamingDataset(str(tmp_path / "s*.tok"), seq_len=8, buffer_size=16)
+    assert st.has_next() and st.next_chunk(5) == [0, 1, 2, 3, 4]
+    x, y = st.get(0)
+    assert x.tolist() == list(range(5, 13)) and y.tolist() == list(range(6, 14))
+    assert st.get(1)[0].tolist() == list(range(13, 21))          # windows continue where the last one ended
+    rest = st.next_chunk(1000)
+    assert rest[0] == 21 and rest[-1] == 79 and not st.has_next() and st.num_chunks() > 0
+    st.reset()
+    assert st.next_chunk(2) == [0, 1]
+    st.shuffle()
+    assert sorted(st.next_chunk(1000)) == list(range(80))
+
+
+def test_text_preprocessor_passes_and_pipeline_stages(tmp_path):
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    p = D.TextPreprocessor()
+    p.set_html_stripping(True), p.set_url_removal(True), p.set_email_removal(True), p.set_accent_removal(True), p.set_lowercase(True)
+    out = p.process("<p>Visit https://example.com/x?y=1 or mail Bob@Example.org — Café   déjà</p><script>evil()</script>")
+    assert out == "visit or mail — cafe deja"
+    q = D.TextPreprocessor()
+    q.set_pii_removal(True)
+    red = q.process("SSN 123-45-6789, card 4111 1111 1111 1111, call +1 (555) 123-4567, host 10.0.0.12, a@b.io")
+    assert "123-45-6789" not in red and "4111" not in red and "555" not in red and "10.0.0.12" not in red and "[EMAIL]" in red
+    assert "SSN" in red and "call" in red
+    q2 = D.TextPreprocessor()
+    q2.set_min_length(10), q2.set_max_length(12)
+    assert q2.process("short") == "" and q2.process("a much longer sentence") == "a much longe"
+    d = D.TextPreprocessor()
+    d.set_deduplication(True), d.set_fuzzy_dedup_threshold(0.8)
+    texts = ["the quick brown fox jumps over the lazy dog", "the quick brown fox jumps over the lazy dog",
+             "the quick brown fox jumps over the lazy dog!", "completely different sentence about kernels"]
+    assert d.process_batch(texts) == [texts[0], texts[3]]
+    assert d.fuzzy_similarity("abcdef", "abcdef") == 1.0 and d.fuzzy_similarity("abcdef", "uvwxyz") == 0.0
+    assert [D.TextPreprocessor.detect_language(t) for t in ("the model is in the loop", "el modelo es de los datos y que",
+            "это модель", "这是模型", "これはモデルです", "모델입니다", "12345")] == ["en", "es", "ru", "zh", "ja", "ko", "unknown"]
+    outs, langs, lens = d.process_with_metadata(["the cat is in the hat", "  "])
+    assert outs == ["the cat is in the hat"] and langs == ["en"] and lens == [21]
+    pipe = D.DataPipeline()
+    bt = ByteTokenizer()
+    pipe.set_tokenizer(bt), pipe.set_seq_length(8), pipe.set_batch_size(2), pipe.set_num_workers(2)
+    pipe.add_stage("upper", lambda ts: [t.upper() for t in ts])
+    batches = pipe.process_texts(["hello world, twelve", "and another line here"])
+    assert batches[0].shape == (2, 8) and bt.decode(batches[0][0].tolist()) == "HELLO WO" and pipe.total_processed() == 2
+    pipe.clear_pipeline()
+    (tmp_path / "f.txt").write_text("first line of text\n\nsecond line of text\n")
+    b2 = pipe.process_file(str(tmp_path / "f.txt"))
+    assert bt.decode(b2[0][0].tolist()) == "first li" and pipe.run_stage2(["ab"]) == [bt.encode("ab")]
+
+
+def test_task_generators_curriculum_and_tokenizer_report(tmp_path):
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    g = D.DataGenerator(3)
+    for s in g.generate_arithmetic(20, "+-*"):
+        lhs, rhs = s.split(" = ")
+        assert eval(lhs) == int(rhs)
+    assert all(s.split(" -> ")[0].split(": ")[1] == s.split(" -> ")[1] for s in g.generate_copy_tasks(5, 9))
+    assert all(s.split(" -> ")[0].split(": ")[1][::-1] == s.split(" -> ")[1] for s in g.generate_reverse_tasks(5, 9))
+    for s in g.generate_sorting_tasks(5, 6):
+        a, b = s[6:].split(" -> ")
+        assert sorted(map(int, a.split())) == list(map(int, b.split()))
+    for s in g.generate_masked_prediction(5, 6):
+        a, b = s.split(" -> ")
+        assert a.count("[MASK]") == 1 and b in D.DataGenerator._WORDS
+    for s in g.generate_next_token_prediction(5, 6):
+        xs, nxt = s.split(" -> ")
+        xs = list(map(int, xs.split()))
+        assert int(nxt) - xs[-1] == xs[1] - xs[0]
+    for s in g.generate_pattern_recognition(3, 4):
+        a, b = s.split(" -> ")
+        assert a.split()[:4] == b.split() and len(a.split()) == 12
+    assert all(len(a.split()) == len(b.split()) for a, b in (s.split(" -> ") for s in g.generate_token_recovery(4, 7)))
+    assert len(g.generate_random_text(4, 10, 20)) == 4 and len(g.generate_ngram_text(3, 12, 3)[0].split()) == 14
+    only_sort = g.generate_mixed(6, [0, 0, 0, 0, 0, 1.0])
+    assert all(s.startswith("sort: ") for s in only_sort) and len(g.generate_mixed(7)) == 7
+    assert D.DataGenerator(3).generate_copy_tasks(3) == D.DataGenerator(3).generate_copy_tasks(3)
+    cur = D.CurriculumGenerator()
+    seen = []
+    cur.set_progress_fn(lambda name, diff, acc: seen.append((name, diff)))
+    cur.add_stage("hard", 2, lambda n: ["h"] * n, max_samples=100, accuracy_threshold=0.8)
+    cur.add_stage("easy", 1, lambda n: ["e"] * n, max_samples=5, accuracy_threshold=0.9)
+    assert cur.current_stage_name() == "easy" and cur.generate_next_batch(3) == ["e"] * 3
+    cur.report_accuracy(0.5)
+    assert cur.current_stage_name() == "easy" and seen == [("easy", 1)]
+    cur.generate_next_batch(3)                                   # 6 samples: the stage's budget is used up
+    assert cur.current_stage_name() == "hard" and cur.current_difficulty() == 2
+    cur.report_accuracy(0.95)
+    assert cur.is_complete() and cur.generate_next_batch(2) == []
+    ev = D.TokenizerEvaluator(ByteTokenizer())
+    rep = ev.evaluate("héllo wörld")
+    assert rep["total_tokens"] == 13 and rep["corpus_size_bytes"] == 13 and rep["reconstruction_fidelity"] == 1.0
+    assert rep["re_encoding_accuracy"] == 1.0 and rep["oov_count"] == 0 and rep["compression_ratio"] == 1.0
+    assert ev.character_error_rate("kitten", "sitting") == pytest.approx(3 / 6)
+    # memory-mapped loader verbs and the Parquet reader
+    D.MmapDataLoader.write_tokens(str(tmp_path / "m.bin"), list(range(64)) * 8 + list(range(500, 756)))
+    ml = D.MmapDataLoader(str(tmp_path / "m.bin"), 2, 16)
+    x, y = ml.next_batch_with_labels()
+    assert x.shape == (2, 16) and ml.has_next() and ml.num_batches() == len(ml)
+    assert ml.dedup(window=64) == [1, 2, 3, 4, 5, 6, 7]            # seven repeats of the first 64-token span
+    ml.reset(seed=5)
+    ml.close()
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    pq.write_table(pa.table({"text": ["abc", None, "defgh"]}), str(tmp_path / "d.parquet"))
+    r = D.ParquetReader()
+    assert not r.open(str(tmp_path / "missing.parquet")) and r.open(str(tmp_path / "d.parquet"))
+    assert r.next_batch(4) == list(b"abcd") and r.next_batch(10) == list(b"efgh") and r.next_batch(10) == []
+    assert r.rows_read() == 2 and r.total_tokens() == 8
+    r.reset()
+    assert r.next_batch(2) == list(b"ab")
+    r.close()
