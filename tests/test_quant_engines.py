@@ -118,3 +118,50 @@ def test_ternary_lut_streams():
     pw = tl.to_packed_weight(tl.pack(t), 64, scale)
     from transformers_fusion_b200.quant import wq
     assert torch.allclose(wq.dequant(pw)[:128, :64], t.float() * scale[:, None], rtol=1e-2, atol=1e-3)
+
+
+def test_engine_verbs_shared_by_all_widths():
+    import torch
+    from transformers_fusion_b200.quant import engines as E
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(16, 64, generator=g)
+    a = torch.randn(4, 64, generator=g)
+    for cls, tol in ((E.Q8Engine, 0.05), (E.Q4Engine, 0.35), (E.Q2Engine, 0.9)):
+        e = cls(block_size=64).train_codebook_per_block(w)
+        assert e.codebook().numel() == 2 ** e.bits
+        idx, sc = e.quantize_per_block(w, 32)
+        assert sc.numel() == 32 and idx.numel() == w.numel()
+        back = e.dequantize_per_block(idx, sc, w.numel(), 32).view_as(w)
+        assert e.quant_error(w, back) < tol and e.quant_snr(w, back) > 0
+        qt = e.quantize_tensor(w)
+        assert torch.allclose(e.quant_gemm(a, qt, 4, 16, 64), a @ e.dequant_tensor(qt).view(16, 64).t(), atol=1e-5)
+        i2, s2 = e.quantize(w)
+        assert torch.allclose(e.quant_gemm(a, i2, 4, 16, 64, scales=s2), a @ e.dequantize(i2, s2, w.numel()).view(16, 64).t(), atol=1e-5)
+        qc, scs = e.quantize_per_channel(w, 0)
+        assert qc.shape == w.shape and scs.shape == (16,)
+        assert e.quant_error(w, e.dequantize_per_channel(qc, scs, 0)) < tol
+        qc1, scs1 = e.quantize_per_channel(w, 1)
+        assert scs1.shape == (64,) and e.dequantize_per_channel(qc1, scs1, 1).shape == w.shape
+        e.enable_stochastic_rounding(True, 0.5)
+        assert e.stochastic and e.stoch_temperature == 0.5
+    for cls, exact in ((E.Q32Engine, True), (E.Q16Engine, False)):
+        e = cls()
+        q = e.quantize_batch(w)
+        assert torch.equal(e.dequantize_batch(q), w) == exact and e.quant_error(w, e.dequantize(q)) < 1e-3
+        assert torch.allclose(e.quant_gemm(a, q, 4, 16, 64), a @ w.t(), atol=1e-2)
+        qc, sc = e.quantize_per_channel(w, 0)
+        assert torch.allclose(e.dequantize_per_channel(qc, sc, 0), w, atol=1e-3)
+    q1 = E.Q1Engine()
+    packed = q1.quantize_batch(w)
+    assert torch.equal(q1.dequantize_batch(packed)[: w.numel()].sign(), torch.where(w.reshape(-1) >= 0, 1.0, -1.0))
+    qc, sc = q1.quantize_per_channel(w, 0)
+    assert torch.equal(q1.dequantize_per_channel(qc, sc, 0).sign(), torch.where(w >= 0, 1.0, -1.0))
+    # fp8 by name: exact values of the encodings
+    assert E.fp8_e4m3_dequantize(E.fp8_e4m3_quantize(1.0)) == 1.0 and E.fp8_e4m3_dequantize(E.fp8_e4m3_quantize(1e6)) == 448.0
+    assert E.fp8_e5m2_dequantize(E.fp8_e5m2_quantize(-1e9)) == -57344.0 and E.fp8_e5m2_quantize(0.0) == 0
+    bits = E.fp8_e4m3_quantize_tensor(w)
+    assert bits.dtype == torch.uint8 and E.fp8_e4m3_quant_error(w, E.fp8_e4m3_dequant_tensor(bits)) < 0.08
+    assert torch.allclose(E.fp8_e4m3_quant_gemm(a, bits, 4, 16, 64), a @ E.fp8_e4m3_dequant_tensor(bits).t(), atol=1e-5)
+    qch, sch = E.fp8_e5m2_quantize_per_channel(w, 0)
+    assert qch.dtype == torch.uint8 and E.fp8_e5m2_quant_snr(w, E.fp8_e5m2_dequantize_per_channel(qch, sch, 0)) > 15
+    assert E.compute_quant_mse(w, w) == 0.0 and E.compute_quant_error(w, w) == 0.0

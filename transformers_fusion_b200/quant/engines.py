@@ -197,6 +197,60 @@ class _CodebookEngine:
         i, s = self.quantize(w)
         return self.dequantize(i, s, w.numel()).view(w.shape)
 
+    # ---- the reference's verbs (include/quant/quant_engines.h: Q8Engine / Q4Engine / Q2Engine)
+    def codebook(self) -> torch.Tensor:
+        return self.cb.centroids
+
+    def enable_stochastic_rounding(self, enable: bool, temperature: float = 1.0):
+        self.stochastic, self.stoch_temperature = bool(enable), float(temperature)
+
+    def quantize_per_block(self, data, block_size: Optional[int] = None):
+        """(indices, per-block absmax scales) with blocks of ``block_size`` (default: the engine's block)."""
+        old, self.block = self.block, block_size or self.block
+        try:
+            return self.quantize(data)
+        finally:
+            self.block = old
+
+    def dequantize_per_block(self, indices, scales, n: Optional[int] = None, block_size: Optional[int] = None):
+        old, self.block = self.block, block_size or self.block
+        try:
+            return self.dequantize(indices, scales, n)
+        finally:
+            self.block = old
+
+    def quantize_tensor(self, data) -> torch.Tensor:
+        """Codebook indices of a tensor scaled by its own absmax (one scale for the whole tensor, kept in
+        ``last_tensor_scale``): the plain, block-free form."""
+        x = data.detach().float().reshape(-1)
+        self.last_tensor_scale = float(x.abs().max().clamp(min=1e-30))
+        return self.cb.quantize(x / self.last_tensor_scale).to(torch.uint8)
+
+    def dequant_tensor(self, indices, n: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
+        v = self.cb.dequantize(indices.long()) * (self.last_tensor_scale if scale is None else scale)
+        return v[: n or v.numel()]
+
+    def quant_gemm(self, a, b_idx, M: int, N: int, K: int, scales=None) -> torch.Tensor:
+        """a [M, K] @ W^T where W [N, K] is given by its codebook indices: per-block scales when ``scales`` is passed
+        (the output of ``quantize``), else the tensor-wide scale of ``quantize_tensor``."""
+        w = self.dequantize(b_idx, scales, N * K) if scales is not None else self.dequant_tensor(b_idx, N * K)
+        return a.float().reshape(M, K) @ w.view(N, K).t()
+
+    def quantize_per_channel(self, t, channel_dim: int = 0):
+        """(indices shaped like ``t``, one absmax scale per slice along ``channel_dim``)."""
+        x = t.detach().float().movedim(channel_dim, 0)
+        s = x.reshape(x.shape[0], -1).abs().amax(1).clamp(min=1e-30)
+        q = self.cb.quantize((x / s.view([-1] + [1] * (x.dim() - 1))).reshape(-1)).view(x.shape).to(torch.uint8)
+        return q.movedim(0, channel_dim), s
+
+    def dequantize_per_channel(self, q, scales, channel_dim: int = 0):
+        shp = [1] * q.dim()
+        shp[channel_dim] = -1
+        return self.cb.dequantize(q.long().reshape(-1)).view(q.shape) * scales.view(shp)
+
+    quant_error = staticmethod(quant_error)
+    quant_snr = staticmethod(quant_snr)
+
 
 class Q8Engine(_CodebookEngine):
     bits = 8
@@ -343,24 +397,59 @@ class Q1Engine:
         s = x.reshape(x.shape[0], -1).abs().mean(1)
         return torch.where(x >= 0, 1, -1).to(torch.int8).transpose(0, channel_dim), s
 
+    def dequantize_per_channel(self, q, scales, channel_dim=0):
+        shp = [1] * q.dim()
+        shp[channel_dim] = -1
+        return q.float() * scales.view(shp)
+
+    quantize_batch = quantize
+
+    def dequantize_batch(self, q):
+        """``q``: the (packed, scale) pair of ``quantize``; every bit of the packed bytes is decoded."""
+        return self.dequantize(q[0], q[1], q[0].numel() * 8)
+
     quant_error = staticmethod(quant_error)
     quant_snr = staticmethod(quant_snr)
 
 
-class Q16Engine:
-    def quantize(self, w):
-        return w.detach().to(torch.float16)
+class _FloatEngine:
+    """Engines whose "quantisation" is a cast: the same verbs as the integer engines, for code written against them."""
+    dtype = torch.float32
 
-    def dequantize(self, q):
+    def quantize(self, w):
+        return w.detach().to(self.dtype).clone()
+
+    def dequantize(self, q, n: Optional[int] = None):
+        v = q.float()
+        return v.reshape(-1)[:n] if n else v
+
+    quantize_batch = quantize
+
+    def dequantize_batch(self, q):
         return q.float()
 
+    def quant_gemm(self, a, b_packed, M: int, N: int, K: int):
+        return a.float().reshape(M, K) @ b_packed.float().reshape(N, K).t()
 
-class Q32Engine:
-    def quantize(self, w):
-        return w.detach().float().clone()
+    def quantize_per_channel(self, t, channel_dim: int = 0):
+        """(cast tensor, unit scales): a cast needs no scale; the scales exist so that callers can treat all engines alike."""
+        return self.quantize(t), torch.ones(t.shape[channel_dim], device=t.device)
 
-    def dequantize(self, q):
-        return q
+    def dequantize_per_channel(self, q, scales, channel_dim: int = 0):
+        shp = [1] * q.dim()
+        shp[channel_dim] = -1
+        return q.float() * scales.view(shp)
+
+    quant_error = staticmethod(quant_error)
+    quant_snr = staticmethod(quant_snr)
+
+
+class Q16Engine(_FloatEngine):
+    dtype = torch.float16
+
+
+class Q32Engine(_FloatEngine):
+    dtype = torch.float32
 
 
 _FP8 = {"e4m3": (torch.float8_e4m3fn, 448.0), "e5m2": (torch.float8_e5m2, 57344.0)}
@@ -404,3 +493,49 @@ def quant8_quantize_tensor(t: torch.Tensor, symmetric=False):
 
 def quant8_dequantize_tensor(q, scale, zero_point=0):
     return (q.float() - zero_point) * scale
+
+
+# ---- the reference's fp8 function names (include/quant/quant_engines.h:9-26), both encodings ------------------------------
+def _fp8_family(kind):
+    dt, mx = _FP8[kind]
+
+    def quantize(val: float) -> int:
+        """Bits of one value rounded to the format (saturating at its largest finite value)."""
+        return int(torch.tensor([max(-mx, min(mx, float(val)))]).to(dt).view(torch.uint8)[0])
+
+    def dequantize(bits: int) -> float:
+        return float(torch.tensor([bits], dtype=torch.uint8).view(dt).float()[0])
+
+    def quantize_tensor(data) -> torch.Tensor:
+        return torch.as_tensor(data).float().clamp(-mx, mx).to(dt).view(torch.uint8)
+
+    def dequant_tensor(bits: torch.Tensor, n: Optional[int] = None) -> torch.Tensor:
+        v = bits.view(dt).float()
+        return v.reshape(-1)[:n] if n else v
+
+    def quant_gemm(a, b_q: torch.Tensor, M: int, N: int, K: int) -> torch.Tensor:
+        return a.float().reshape(M, K) @ dequant_tensor(b_q).reshape(N, K).t()
+
+    def quantize_per_channel(t, channel_dim: int = 0):
+        q, s = fp8_quantize(t, kind, channel_dim)
+        return q.view(torch.uint8), s
+
+    def dequantize_per_channel(q, scales, channel_dim: int = 0):
+        return q.view(dt).float() * scales
+
+    return dict(quantize=quantize, dequantize=dequantize, quantize_tensor=quantize_tensor, dequant_tensor=dequant_tensor,
+                quant_gemm=quant_gemm, quantize_per_channel=quantize_per_channel, dequantize_per_channel=dequantize_per_channel,
+                quant_error=quant_error, quant_snr=quant_snr)
+
+
+for _kind in ("e4m3", "e5m2"):
+    for _name, _fn in _fp8_family(_kind).items():
+        globals()[f"fp8_{_kind}_{_name}"] = _fn
+
+
+def compute_quant_mse(original, reconstructed) -> float:
+    return float((original.float() - reconstructed.float()).pow(2).mean())
+
+
+compute_quant_error = quant_error
+compute_quant_snr = quant_snr
