@@ -114,3 +114,73 @@ def test_plugins_and_zoo(tmp_path):
     assert zoo.get("tiny") is m2 and m2.cfg.hidden_size == 32
     zoo.unload("tiny")
     assert "tiny" not in zoo.loaded
+
+
+def test_model_server_load_unload_and_named_helpers(tmp_path):
+    from transformers_fusion_b200.quant import codec
+    from transformers_fusion_b200.utils.logging import AppConfig, Logger
+    m, eng = engine()
+    other = DenseModel(m.cfg, device="cpu", dtype=torch.float32, seed=9)
+    codec.save_model(other, str(tmp_path / "other.quant"))
+    want = InferenceEngine(other, ByteTokenizer(), EngineConfig(num_pages=64)).generate_batch([[5, 6, 7]], 5, SamplerConfig(0.0))[0]
+    ms = P.ModelServer(eng).start()
+    try:
+        assert ms.is_running() and ms.is_model_loaded()
+        ms.set_batch_size(3), ms.set_queue_wait_ms(2)
+        assert eng.cfg.max_batch == 3 and ms.queue_wait_s == 0.002
+        first = ms.generate([5, 6, 7], 5, SamplerConfig(0.0))
+        assert not ms.load_model(str(tmp_path / "missing.quant")) and ms.is_model_loaded()      # a bad path changes nothing
+        assert ms.load_model(str(tmp_path / "other.quant"))
+        assert ms.generate([5, 6, 7], 5, SamplerConfig(0.0)) == want != first
+        ms.unload_model()
+        assert not ms.is_model_loaded() and ms.submit([1], 1).error == "no model is loaded"
+        assert ms.metrics.avg_latency_ms() > 0 and ms.metrics.requests_per_sec() > 0
+        h = ms.metrics.latency
+        assert h.p50() <= h.p95() <= h.p99()
+    finally:
+        ms.stop()
+    assert not ms.is_running()
+    # process-wide logger with a file, numeric levels
+    log = Logger.instance()
+    assert Logger.instance() is log
+    old_stream, log.stream = log.stream, None
+    log.set_file(str(tmp_path / "app.log"))
+    log.set_level(2)
+    log.log(1, "quiet"), log.log(Logger.ERROR, "loud"), log.log(3, "numeric")
+    log.set_file(None)
+    log.stream = old_stream
+    log.set_level("info")
+    text = (tmp_path / "app.log").read_text()
+    assert "quiet" not in text and "[ERROR] loud" in text and "[ERROR] numeric" in text
+    cfg = AppConfig()
+    cfg.set("server.port", "8080"), cfg.set("server.rate", "2.5"), cfg.set("server.debug", "true"), cfg.set("name", "tfb")
+    assert cfg.get_int("server.port") == 8080 and cfg.get_float("server.rate") == 2.5 and cfg.get("server.debug") is True
+    assert cfg.get_string("name") == "tfb" and cfg.get_string("server.debug") == "true" and cfg.get_int("nope", 7) == 7
+    assert cfg.get_int("name", 3) == 3 and json.loads(cfg.to_json())["server"]["port"] == 8080
+    # plugin hooks: objects registered directly and Python files
+    (tmp_path / "plug.py").write_text("seen = []\ndef on_generate_start(p): seen.append(('start', p))\ndef on_token_generated(t): seen.append(('tok', t))\n")
+    pm = P.PluginManager()
+    name = pm.load(str(tmp_path / "plug.py"))
+
+    class Direct:
+        def __init__(self):
+            self.ends = []
+
+        def name(self): return "direct"
+        def on_generate_end(self, out): self.ends.append(out)
+        def on_token_generated(self, t): raise RuntimeError("faulty plugin")
+    d = Direct()
+    pm.register_plugin(d)
+    pm.on_generate_start("hi"), pm.on_token_generated(5), pm.on_generate_end("done")
+    assert pm.direct_plugin_count() == 1 and d.ends == ["done"]
+    assert pm.plugins[name]["module"].seen == [("start", "hi"), ("tok", 5)]
+    (tmp_path / "plug.py").write_text("seen = ['fresh']\n")
+    assert pm.hot_reload(str(tmp_path / "plug.py")) and pm.plugins[name]["module"].seen == ["fresh"]
+    assert not pm.hot_reload(str(tmp_path / "missing.py"))
+    pm.unload_all()
+    assert pm.names() == [] and pm.direct_plugin_count() == 0
+    zoo = P.ModelZoo()
+    zoo.scan(str(tmp_path))
+    info = zoo.list_models()
+    assert info[0]["name"] == "other" and info[0]["params"] == sum(p.numel() for p in other.parameters()) and info[0]["format"] == "Q_32"
+    assert zoo.load("other") is zoo.get("other")

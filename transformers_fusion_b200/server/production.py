@@ -43,6 +43,10 @@ class LatencyHistogram:
                 return 0.0
             return self.samples[min(len(self.samples) - 1, int(p / 100.0 * len(self.samples)))]
 
+    def p50(self) -> float: return self.percentile(50.0)
+    def p95(self) -> float: return self.percentile(95.0)
+    def p99(self) -> float: return self.percentile(99.0)
+
     def summary(self):
         return {"count": self.count, "mean_ms": self.total / max(1, self.count), "p50_ms": self.percentile(50),
                 "p95_ms": self.percentile(95), "p99_ms": self.percentile(99)}
@@ -58,6 +62,12 @@ class ServerMetrics:
     started_at: float = field(default_factory=time.time)
     latency: LatencyHistogram = field(default_factory=LatencyHistogram)
     ttft: LatencyHistogram = field(default_factory=LatencyHistogram)
+
+    def avg_latency_ms(self) -> float:
+        return self.latency.total / max(1, self.latency.count)
+
+    def requests_per_sec(self) -> float:
+        return self.requests_total / max(1e-9, time.time() - self.started_at)
 
     def to_json(self) -> str:
         up = time.time() - self.started_at
@@ -103,9 +113,60 @@ class ModelServer:
         if self.thread:
             self.thread.join(timeout=5)
 
+    def is_running(self) -> bool:
+        return self.running and self.thread is not None and self.thread.is_alive()
+
+    def is_model_loaded(self) -> bool:
+        return self.engine is not None
+
+    def set_batch_size(self, n: int):
+        """Upper bound on the sequences the engine decodes together (takes effect for requests admitted from now on)."""
+        if self.engine is not None:
+            self.engine.cfg.max_batch = max(1, int(n))
+
+    def set_queue_wait_ms(self, ms: int):
+        """How long the loop sleeps when it has nothing to do before it looks at the queue again."""
+        self.queue_wait_s = max(0.0, ms / 1e3)
+
+    def unload_model(self):
+        """Stop admitting work, wait for what is in flight and drop the engine; queued tickets fail with "no model"."""
+        with self.cv:
+            while self.inflight:
+                self.cv.wait(0.05)
+            for t in self.pending:
+                t.error = "no model is loaded"
+                t.done.set()
+            self.pending, self.engine = [], None
+            self.metrics.queue_depth = 0
+
+    def load_model(self, path: str, tokenizer=None, engine_cfg=None) -> bool:
+        """Build an engine for the checkpoint at ``path`` and serve from it (the previous engine is drained first)."""
+        try:
+            from ..inference.engine import EngineConfig, InferenceEngine
+            from ..quant import codec
+            import torch
+            old = self.engine
+            dev = old.device if old is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+            model = codec.load_model(path, device=dev, dtype=torch.bfloat16 if str(dev).startswith("cuda") else torch.float32)
+            eng = InferenceEngine(model, tokenizer or (old.tok if old is not None else None), engine_cfg or (old.cfg if old is not None else EngineConfig()))
+        except Exception as e:
+            self.last_error = str(e)
+            return False
+        if self.engine is not None:
+            self.unload_model()
+        with self.cv:
+            self.engine = eng
+            self.cv.notify_all()
+        return True
+
     def submit(self, prompt_ids, max_tokens=64, sampling=None, priority=0, on_token=None) -> _Ticket:
         t = _Ticket(list(prompt_ids), max_tokens, sampling, priority, on_token)
         with self.cv:
+            if self.engine is None:
+                t.error = "no model is loaded"
+                t.done.set()
+                self.metrics.requests_failed += 1
+                return t
             if len(self.pending) >= self.max_queue:
                 t.error = "queue full"
                 t.done.set()
@@ -126,11 +187,12 @@ class ModelServer:
         return t.tokens
 
     def _loop(self):
-        eng = self.engine
         while self.running:
             with self.cv:
-                while self.running and not self.pending and not eng.has_pending():
-                    self.cv.wait(0.05)
+                eng = self.engine
+                while self.running and (eng is None or (not self.pending and not eng.has_pending())):
+                    self.cv.wait(getattr(self, "queue_wait_s", 0.05) or 0.001)
+                    eng = self.engine
                 if not self.running:
                     return
                 batch, self.pending = self.pending, []
@@ -160,13 +222,16 @@ class ModelServer:
                 self.metrics.requests_failed += len(self.inflight)
                 self.inflight.clear()
                 continue
-            self.metrics.active = len(self.inflight)
             for r in finished:
                 t = self.inflight.pop(r.id, None)
                 if t is not None:
                     self.metrics.tokens_generated += len(t.tokens)
                     self.metrics.latency.record((time.perf_counter() - t.t_submit) * 1e3)
                     t.done.set()
+            self.metrics.active = len(self.inflight)
+            if finished:
+                with self.cv:
+                    self.cv.notify_all()                   # a model swap may be waiting for the engine to drain
 
     def health_json(self) -> str:
         return json.dumps({"status": "ok" if self.running else "stopped", "queue_depth": self.metrics.queue_depth,
@@ -200,6 +265,11 @@ class ModelHTTPServer:
     def stop(self):
         self.http.stop()
         self.ms.stop()
+
+    def is_running(self) -> bool: return self.http.is_running()
+    def set_thread_pool_size(self, n: int): self.http.set_thread_pool_size(n)
+    def set_timeout_seconds(self, s: int): self.http.set_timeout_seconds(s)
+    def set_max_body_size(self, n: int): self.http.set_max_body_size(n)
 
     @property
     def port(self):
@@ -381,6 +451,52 @@ class PluginManager:
     def call(self, name, fn, *args):
         return getattr(self.plugins[name]["module"], fn)(*args)
 
+    # ---- in-process plugins and the generation hooks (reference: Plugin / PluginManager, include/quant/production.h)
+    def register_plugin(self, plugin):
+        """An object with ``name()`` (or ``name``) and any of on_generate_start / on_token_generated / on_generate_end."""
+        if not hasattr(self, "direct"):
+            self.direct = []
+        self.direct.append(plugin)
+
+    def direct_plugin_count(self) -> int:
+        return len(getattr(self, "direct", []))
+
+    def unload_all(self):
+        for name in list(self.plugins):
+            self.unload(name)
+        self.direct = []
+
+    def hot_reload(self, path: str) -> bool:
+        """Load ``path`` again in place of the plugin that came from it (or load it for the first time)."""
+        for name, p in list(self.plugins.items()):
+            if os.path.abspath(p["path"]) == os.path.abspath(path):
+                ctx = p["ctx"]
+                self.unload(name)
+                try:
+                    self.load(path, ctx)
+                    return True
+                except Exception:
+                    return False
+        try:
+            self.load(path)
+            return True
+        except Exception:
+            return False
+
+    def _fire(self, hook: str, arg):
+        targets = list(getattr(self, "direct", [])) + [p["module"] for p in self.plugins.values() if p["kind"] == "python"]
+        for t in targets:
+            fn = getattr(t, hook, None)
+            if callable(fn):
+                try:
+                    fn(arg)
+                except Exception:                          # a faulty plugin must not break generation
+                    pass
+
+    def on_generate_start(self, prompt: str): self._fire("on_generate_start", prompt)
+    def on_token_generated(self, token: int): self._fire("on_token_generated", token)
+    def on_generate_end(self, output: str): self._fire("on_generate_end", output)
+
     def names(self):
         return sorted(self.plugins)
 
@@ -408,6 +524,26 @@ class ModelZoo:
 
     def unload(self, name):
         self.loaded.pop(name, None)
+
+    def list_models(self):
+        """[{name, path, params, format}] of the registered checkpoints (parameter count and block format read from the
+        file's tables, without decoding the weights)."""
+        from ..quant import codec
+        out = []
+        for name in self.list():
+            info = {"name": name, "path": self.paths[name], "params": 0, "format": ""}
+            try:
+                with codec.QuantReader(self.paths[name]) as r:
+                    info["params"] = sum(r.block_sizes(b)[0] for b in range(r.num_blocks()))
+                    names = r.tensor_names()
+                    big = max(names, key=lambda n: r.tensor_blocks(n)[1]) if names else None
+                    info["format"] = codec.format_name(r.tensor_format(big)) if big else ""
+            except Exception:
+                pass
+            out.append(info)
+        return out
+
+    load = get
 
     def scan(self, directory):
         for f in sorted(os.listdir(directory)):

@@ -23,10 +23,33 @@ class Logger:
         self.file = open(path, "a") if path else None
         self.stream, self.lock = stream, threading.Lock()
 
+    DEBUG, INFO, WARN, ERROR = "debug", "info", "warn", "error"
+    _instance: Optional["Logger"] = None
+
+    @classmethod
+    def instance(cls) -> "Logger":
+        """The process-wide logger (created on first use at level info, writing to stderr)."""
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    def set_file(self, path: Optional[str]):
+        """Also append every line to ``path`` (None stops writing to a file)."""
+        with self.lock:
+            if self.file:
+                self.file.close()
+            self.file = open(path, "a") if path else None
+
     def set_level(self, level):
-        self.level = self.LEVELS[level]
+        self.level = self.LEVELS[self._name(level)]
+
+    @staticmethod
+    def _name(level):
+        """Level names, or the reference's numeric levels 0..3 (include/quant/production.h: Logger::Level)."""
+        return ("debug", "info", "warn", "error")[level] if isinstance(level, int) else str(level).lower()
 
     def log(self, level, msg):
+        level = self._name(level)
         if self.LEVELS[level] < self.level:
             return
         line = f"{time.strftime('%Y-%m-%d %H:%M:%S')} [{level.upper()}] {msg}\n"
@@ -221,7 +244,41 @@ class AppConfig:
             cur = cur[part]
         return cur
 
+    # ---- typed getters of the reference (include/quant/production.h: AppConfig)
+    def get_int(self, key: str, default: int = 0) -> int:
+        v = self.get(key)
+        try:
+            return int(v) if v is not None and not isinstance(v, (dict, list)) else default
+        except (TypeError, ValueError):
+            return default
+
+    def get_float(self, key: str, default: float = 0.0) -> float:
+        v = self.get(key)
+        try:
+            return float(v) if v is not None and not isinstance(v, (dict, list, bool)) else default
+        except (TypeError, ValueError):
+            return default
+
+    def get_string(self, key: str, default: str = "") -> str:
+        v = self.get(key)
+        return default if v is None or isinstance(v, (dict, list)) else (str(v).lower() if isinstance(v, bool) else str(v))
+
+    def to_json(self, indent: int = 2) -> str:
+        return json.dumps(self.data, indent=indent, sort_keys=True)
+
     def set(self, dotted: str, value):
+        if isinstance(value, str):                       # text from a command line becomes the value it spells
+            low = value.strip().lower()
+            if low in ("true", "false"):
+                value = low == "true"
+            else:
+                try:
+                    value = int(value)
+                except ValueError:
+                    try:
+                        value = float(value)
+                    except ValueError:
+                        pass
         cur = self.data
         parts = dotted.split(".")
         for part in parts[:-1]:
