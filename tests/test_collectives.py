@@ -60,3 +60,54 @@ def test_parameter_server():
     a.flush()
     a.stop()
     assert a.pull("k")[0].min() < -2
+
+
+def test_first_generation_wrappers_and_parameter_server_on_gloo(tmp_path):
+    import json
+    import subprocess
+    import sys as _sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    port = 29870 + (os.getpid() % 50)
+    cmd = [_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "_mp_wrappers_worker.py"), str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = [json.load(open(os.path.join(tmp_path, f"rank{i}.json"))) for i in range(2)]
+    assert [x["is_main"] for x in res] == [True, False] and res[0]["mode0"] == "DDP"
+    for i, x in enumerate(res):
+        assert x["tp_err"] < 1e-4 and x["tp_mode"] == "TENSOR_PARALLEL"
+        assert x["split"] == ([0.0, 1.0, 2.0, 3.0] if i == 0 else [4.0, 5.0, 6.0, 7.0])
+        assert x["ps_avg"] == [0.5] * 4 and x["ring"] == [i, 2]
+        assert x["ddp"] == [1, 2, i, 2, True] and x["ddp_reset"] == 0 and x["wrapper_ctx"]
+    assert res[0]["pp_err"] is None and res[1]["pp_err"] < 1e-4
+    assert res[0]["ps_node"] == [True, 0, 1] and res[1]["ps_node"] == [False, -1, 1]
+
+
+def test_parameter_server_management_verbs():
+    import torch
+    from transformers_fusion_b200.parallel.collectives import ParameterServer
+    ps = ParameterServer(num_shards=3, lr=0.1)
+    f = ps.push_async("a", torch.ones(3))
+    f.result(5)
+    ps.push("b", torch.full((2,), 2.0))
+    assert ps.list_params() == ["a", "b"] and ps.owns_param("a") and not ps.owns_param("zz") and ps.get_param("zz") is None
+    assert ps.get_version("a") == 1 and ps.get_version("zz") == -1
+    assert 0 <= ParameterServer.shard_for("a", 3) < 3 and ParameterServer.shard_for("a", 3) == ParameterServer.shard_for("a", 3)
+    t, v = ps.pull_async("a").result(5)
+    assert v == 1 and ps.update_gradient_async("a", torch.ones(3), v).result(5)
+    assert torch.allclose(ps.get_param("a"), torch.full((3,), 0.9))
+    ps.apply_weight_decay(0.5)
+    assert torch.allclose(ps.get_param("b"), torch.ones(2))
+    ps.accumulate_gradient("b", torch.ones(2)), ps.accumulate_gradient("b", torch.ones(2))
+    ps.apply_momentum(0.9, 0.1)
+    assert torch.allclose(ps.get_param("b"), torch.full((2,), 0.8))
+    ps.accumulate_gradient("b", torch.zeros(2))
+    ps.apply_momentum(0.9, 0.1)                                   # the velocity carries on: v = 0.9 * 2
+    assert torch.allclose(ps.get_param("b"), torch.full((2,), 0.8 - 0.18))
+    ps.set_max_stale_gradients(0)
+    assert not ps.update_gradient("a", torch.ones(3), 0)          # computed against version 0, now 2: too stale
+    ps.remove_param("a")
+    assert ps.list_params() == ["b"]
+    ps.clear_params()
+    assert ps.list_params() == []
+    ps.barrier(), ps.shutdown()

@@ -53,6 +53,12 @@ class DistributedContext:
     def world_rank(self) -> int:
         return self.rank
 
+    #: how the ranks of this context cooperate ("DDP", "TENSOR_PARALLEL", "PIPELINE_PARALLEL"); informational
+    mode: str = "DDP"
+
+    def is_main(self) -> bool:
+        return self.rank == 0
+
     def all_reduce(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
         if self.is_distributed:
             dist.all_reduce(t, op=_TORCH_OPS[op], group=self.group)
@@ -292,6 +298,10 @@ class RingAllReduce:
         return self.sc is not None and t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) and \
             t.numel() * t.element_size() <= self.sc.capacity - 16 * self.sc.world
 
+    def world_size(self) -> int: return self.ctx.world_size
+    def rank(self) -> int: return self.ctx.rank
+    def barrier(self): self.ctx.barrier()
+
     def allreduce(self, t, op="sum"):
         return self.sc.all_reduce(t.contiguous(), op) if self._dev(t) else self.ctx.all_reduce(t, op)
 
@@ -397,6 +407,115 @@ class ParameterServer:
             with self.lock:
                 if not self.queue:
                     return
+
+    # ---- the reference's surface (include/quant/distributed.h: ParameterServer) ----------------------------------
+    def configure_world(self, world_size: int, world_rank: int, num_ps_nodes: Optional[int] = None):
+        """Describe the job this store is part of: the first ``num_ps_nodes`` ranks hold the shards."""
+        self._world = (int(world_size), int(world_rank), int(num_ps_nodes or self.num_shards))
+        return self
+
+    def world_size(self) -> int: return getattr(self, "_world", (1, 0, self.num_shards))[0]
+    def world_rank(self) -> int: return getattr(self, "_world", (1, 0, self.num_shards))[1]
+    def num_ps_nodes(self) -> int: return getattr(self, "_world", (1, 0, self.num_shards))[2]
+    def ps_node_id(self) -> int: return self.world_rank() if self.is_ps_node() else -1
+    def is_ps_node(self) -> bool: return self.world_rank() < self.num_ps_nodes()
+
+    @staticmethod
+    def shard_for(name: str, num_ps_nodes: int) -> int:
+        import zlib
+        return zlib.crc32(name.encode()) % max(1, num_ps_nodes)
+
+    def owns_param(self, name: str) -> bool:
+        return name in self._shard(name)
+
+    def get_param(self, name: str):
+        with self.lock:
+            t = self._shard(name).get(name)
+            return None if t is None else t.clone()
+
+    def list_params(self) -> List[str]:
+        with self.lock:
+            return sorted(k for sh in self.shards for k in sh)
+
+    def remove_param(self, name: str):
+        with self.lock:
+            self._shard(name).pop(name, None)
+            self.versions.pop(name, None)
+
+    def clear_params(self):
+        with self.lock:
+            for sh in self.shards:
+                sh.clear()
+            self.versions.clear()
+
+    def get_version(self, name: str) -> int:
+        return self.versions.get(name, -1)
+
+    def set_max_stale_gradients(self, n: int):
+        self.max_staleness = int(n)
+
+    def apply_weight_decay(self, decay_rate: float):
+        with self.lock:
+            for sh in self.shards:
+                for t in sh.values():
+                    t.mul_(1.0 - decay_rate)
+
+    def average_parameters(self, weight: float = 1.0, ctx: Optional["DistributedContext"] = None):
+        """Blend every stored tensor towards its mean over the ranks of ``ctx``: p <- (1 - weight) p + weight mean(p)."""
+        if ctx is None or not ctx.is_distributed:
+            return
+        with self.lock:
+            for sh in self.shards:
+                for t in sh.values():
+                    mean = ctx.all_reduce(t.clone(), "avg")
+                    t.mul_(1.0 - weight).add_(mean, alpha=weight)
+
+    def apply_momentum(self, momentum: float, lr: float):
+        """One heavy-ball step from the gradients accumulated by ``accumulate_gradient``: v <- momentum v + g; p -= lr v."""
+        with self.lock:
+            vel = self.__dict__.setdefault("_velocity", {})
+            for name, g in self.__dict__.setdefault("_grad_acc", {}).items():
+                p = self._shard(name).get(name)
+                if p is None:
+                    continue
+                v = vel.setdefault(name, torch.zeros_like(p))
+                v.mul_(momentum).add_(g)
+                p.add_(v, alpha=-lr)
+                self.versions[name] += 1
+            self._grad_acc = {}
+
+    def accumulate_gradient(self, name: str, grad: torch.Tensor):
+        with self.lock:
+            acc = self.__dict__.setdefault("_grad_acc", {})
+            acc[name] = acc[name] + grad if name in acc else grad.detach().clone()
+
+    def push_async(self, key, t):
+        """Queue a ``push``; returns at once (a ``concurrent.futures.Future`` carries completion)."""
+        return self._pool().submit(self.push, key, t)
+
+    def pull_async(self, key):
+        return self._pool().submit(self.pull, key)
+
+    def update_gradient_async(self, key, grad, version):
+        return self._pool().submit(self.update_gradient, key, grad, version)
+
+    def _pool(self):
+        if getattr(self, "_executor", None) is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._executor = ThreadPoolExecutor(max_workers=2, thread_name_prefix="tfb-ps")
+        return self._executor
+
+    def barrier(self, ctx: Optional["DistributedContext"] = None):
+        """Wait until queued work of this store is applied (and, with ``ctx``, until every rank got here)."""
+        self.flush()
+        if ctx is not None:
+            ctx.barrier()
+
+    def shutdown(self):
+        self.stop()
+        if getattr(self, "_executor", None) is not None:
+            self._executor.shutdown(wait=True)
+            self._executor = None
 
     def stop(self):
         self._stop = True

@@ -56,6 +56,13 @@ class DistributedDataParallel:
     def set_grad_accumulation_steps(self, n: int):
         self.accum_steps = max(1, int(n))
 
+    def grad_accumulation_steps(self) -> int: return self.accum_steps
+    def grad_accum_count(self) -> int: return self._micro % self.accum_steps
+    def reset_grad_accum_count(self): self._micro = 0
+    def context(self) -> DistributedContext: return self.ctx
+    def world_size(self) -> int: return self.ctx.world_size
+    def rank(self) -> int: return self.ctx.rank
+
     # ---- forward / gradient path
     def forward(self, ids):
         return self.model.forward(ids)
@@ -171,3 +178,56 @@ class DDPWrapper:
     def sync_gradients(self):
         for p in self.model.parameters():
             self.ctx.all_reduce(p.main_grad, "avg")
+
+    def context(self) -> DistributedContext: return self.ctx
+
+
+class TensorParallelWrapper:
+    """The reference's first tensor-parallel wrapper (include/quant/distributed.h: TensorParallelWrapper): a model whose
+    linear layers are split over the ranks of ``ctx``.  The work is done by ``parallel.tp_model.TPDenseModel``; this class
+    keeps the small surface: ``forward(ids)``, ``context()``, ``split_linear(weight, dim)``."""
+
+    def __init__(self, model, ctx: Optional[DistributedContext] = None):
+        self.ctx = ctx or DistributedContext.init()
+        self.ctx.mode = "TENSOR_PARALLEL"
+        self.full = model
+        self._tp = None
+
+    def context(self) -> DistributedContext: return self.ctx
+
+    def split_linear(self, weight: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        """This rank's slice of a weight: dim 0 = output rows (column-parallel layer), dim 1 = input columns (row-parallel)."""
+        n = weight.shape[dim] // self.ctx.world_size
+        return weight.narrow(dim, self.ctx.rank * n, n).contiguous()
+
+    def forward(self, ids):
+        if self.ctx.world_size == 1:
+            return self.full.forward(ids)
+        from .tp_model import TPDenseModel, TPGroup, _HeadFn, _RMSNormFn
+        if self._tp is None:
+            self._tp = TPDenseModel(self.full, TPGroup(self.ctx.rank, self.ctx.world_size, self.ctx.group))
+        tp = self._tp
+        B, S = ids.shape
+        with torch.no_grad():
+            h = torch.nn.functional.embedding(tp._shard_rows(ids.reshape(-1)), tp.tok_embeddings)
+            rope = self.full.rope(ids.device)
+            for blk in tp.layers:
+                h = blk(h, B, S, rope)
+            logits = _HeadFn.apply(_RMSNormFn.apply(h, tp.norm, tp.cfg.norm_eps), tp.lm_head)
+            return tp.tp.all_gather_rows(logits.contiguous()).view(B, S, -1)
+
+
+class PipelineParallelWrapper:
+    """The reference's first pipeline wrapper (include/quant/distributed.h: PipelineParallelWrapper): rank r runs the
+    r-th contiguous range of layers; ``forward(ids)`` returns the logits on the last rank (None elsewhere)."""
+
+    def __init__(self, model, ctx: Optional[DistributedContext] = None):
+        from .pp import PipelineParallel
+        self.ctx = ctx or DistributedContext.init()
+        self.ctx.mode = "PIPELINE_PARALLEL"
+        self.pp = PipelineParallel(model, self.ctx.world_size, self.ctx.rank, self.ctx, num_microbatches=1)
+
+    def context(self) -> DistributedContext: return self.ctx
+
+    def forward(self, ids):
+        return self.pp.forward(ids)
