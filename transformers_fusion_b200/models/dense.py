@@ -367,6 +367,29 @@ class DenseModel(nn.Module):
         f = self.hidden_states(ids)
         return [_LinearFn.apply(f, w).view(B, S, -1) for w in self.mtp_heads]
 
+    # ------------------------------------------------------------------ accessors (reference: include/quant/model.h:28-65)
+    def get_parameters(self):
+        return list(self.parameters())
+
+    def param_count(self) -> int:
+        """Distinct parameters (a tied embedding / head counts once)."""
+        return sum(p.numel() for p in self.parameters())
+
+    def vocab_size(self) -> int:
+        return self.cfg.vocab_size
+
+    def mtp_loss(self, ids, labels, ignore_index: int = -100) -> float:
+        """Mean over the extra heads of the cross entropy against the labels moved further left (evaluation; the training
+        step folds the same term into its loss when ``mtp_loss_weight`` > 0)."""
+        with torch.no_grad():
+            heads = self.mtp_forward(ids)
+        if not heads:
+            return 0.0
+        tot = 0.0
+        for lg, lab in zip(heads, self.mtp_shifted_labels(labels, ignore_index)):
+            tot += float(torch.nn.functional.cross_entropy(lg.float().reshape(-1, lg.shape[-1]), lab, ignore_index=ignore_index))
+        return tot / len(heads)
+
     # ------------------------------------------------------------------ files (reference: DenseModel::save / save_quantized / load)
     def save(self, path, fmt="Q_32"):
         """Write the model as a ``.quant`` container (raw fp32 blocks by default)."""

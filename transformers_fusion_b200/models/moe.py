@@ -286,6 +286,19 @@ class MoEBlock(nn.Module):
         self.last_idx, self.last_logits, self.last_covered = idx, logits.detach(), covered
         return y, aux
 
+    # ---- sizes (reference: MoEBlock, include/quant/moe_model.h)
+    def num_stored_experts(self) -> int:
+        return self.gate_up.shape[0]
+
+    def param_count(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def activated_param_count(self) -> int:
+        """Parameters one token touches: everything but the experts it is not routed to."""
+        experts = self.gate_up.numel() + self.down.numel()
+        k = min(self.cfg.top_k, self.cfg.num_experts)
+        return self.param_count() - experts + experts * k // max(1, self.gate_up.shape[0])
+
     def forward(self, h, B, S, rope):
         h = AttentionBlockFn.apply(h, self, B, S, rope, self.attention_norm, self.qkv, self.o)
         f = _RMSNormFn.apply(h, self.ffn_norm, self.cfg.norm_eps)
@@ -435,6 +448,41 @@ class MoEModel(DenseModel):
                     raise ValueError(f"{name}: {src.numel()} weights in file, {dst.numel()} expected")
                 dst.copy_(src.view(dst.shape).to(dst.dtype))
         return model
+
+    # ---- sizes and the expert prefetcher (reference: MoEModel, include/quant/moe_model.h)
+    def stored_param_count(self) -> int:
+        seen, n = set(), 0
+        for p in self.parameters():
+            if id(p) not in seen:
+                seen.add(id(p))
+                n += p.numel()
+        return n
+
+    def param_count(self) -> int:
+        """Parameters active per token (all experts count in ``stored_param_count``)."""
+        inactive = 0
+        for l in self.layers:
+            experts = l.gate_up.numel() + l.down.numel()
+            inactive += experts - experts * min(self.cfg.top_k, self.cfg.num_experts) // max(1, l.gate_up.shape[0])
+        return self.stored_param_count() - inactive
+
+    def vocab_size(self) -> int:
+        return self.cfg.vocab_size
+
+    def init_prefetcher(self, directory: str, host_slots: int = 8, device_slots: int = 2):
+        """An expert prefetcher (disk -> pinned host -> device tiers) sized for this model; ``wire_prefetcher_sources``
+        fills its disk tier."""
+        from .moe_extras import ExpertPrefetcher
+        dev = self.tok_embeddings.device
+        self.prefetcher = ExpertPrefetcher(directory, dev, host_slots, device_slots).initialize(self.cfg.num_experts, len(self.layers))
+        return self.prefetcher
+
+    def wire_prefetcher_sources(self):
+        """Write every expert of every layer to the prefetcher's disk tier."""
+        for li, l in enumerate(self.layers):
+            for e in range(l.gate_up.shape[0]):
+                self.prefetcher.set_expert_segments(li, e, [("gate_up", l.gate_up.data[e]), ("down", l.down.data[e])])
+        return self.prefetcher
 
     def expert_utilization(self):
         """Fraction of routed (token, k) pairs per expert in the last forward, per layer."""

@@ -46,6 +46,11 @@ class DenseToMoEPruner:
             dn[e] = down[:, idx]
         return gu, dn, cent.to(gate_up.dtype), assign
 
+    def prune_ffn(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor):
+        """The reference's call shape (include/quant/moe_enhance.h: DenseToMoEPruner::prune_ffn): separate gate [F, H] and
+        up [F, H] matrices and down [H, F] of a dense FFN -> (expert gate_up, expert down, router initialisation)."""
+        return self.convert(torch.cat([gate, up], 0), down)
+
     @staticmethod
     def _balanced_assign(score: torch.Tensor, per: int) -> torch.Tensor:
         """Greedy capacity-constrained assignment: most confident units choose first."""
@@ -85,6 +90,14 @@ class SwitchV2Router:
         return idx, w * kept, kept, aux
 
 
+    def forward(self, logits: torch.Tensor, tokens: Optional[int] = None) -> torch.Tensor:
+        """Dispatch matrix [T, E]: the routing weight where a token was kept by its expert, 0 elsewhere (evaluation mode)."""
+        idx, w, kept, _ = self.route(logits, training=False)
+        out = torch.zeros(logits.shape, dtype=torch.float32, device=logits.device)
+        out[torch.arange(logits.shape[0], device=logits.device), idx] = w
+        return out
+
+
 class ExpertChoiceV2:
     """Experts pick tokens: every expert takes its ``capacity`` highest-scoring tokens, so the load is perfectly balanced;
     a token may be served by several experts or by none."""
@@ -104,6 +117,12 @@ class ExpertChoiceV2:
         for e in range(self.E):
             y.index_add_(0, tok[e], expert_fn(e, x[tok[e]]).float() * w[e][:, None])
         return y.to(x.dtype)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, expert_fn=None) -> torch.Tensor:
+        """Route and combine in one call; without ``expert_fn`` every expert is the identity (the weighted tokens come
+        back, which shows who was served and how strongly)."""
+        tok, w = self.route(logits)
+        return self.combine(x, tok, w, expert_fn or (lambda e, rows: rows))
 
 
 class ExpertMerger:
@@ -146,6 +165,31 @@ class DynamicExpertPool:
     def num_experts(self):
         return self.gu.shape[0]
 
+    def count(self) -> int:
+        return self.num_experts
+
+    def add_expert(self, gate_up: torch.Tensor, down: Optional[torch.Tensor] = None, router_row: Optional[torch.Tensor] = None) -> int:
+        """Append an expert (its router row defaults to the mean of the existing rows); returns its index, or -1 when the
+        pool is full."""
+        if self.num_experts >= self.max:
+            return -1
+        down = down if down is not None else self.dn.float().mean(0).to(self.dn.dtype)
+        row = router_row if router_row is not None else self.router.float().mean(0).to(self.router.dtype)
+        self.gu = torch.cat([self.gu, gate_up.reshape(1, *self.gu.shape[1:]).to(self.gu.dtype)])
+        self.dn = torch.cat([self.dn, down.reshape(1, *self.dn.shape[1:]).to(self.dn.dtype)])
+        self.router = torch.cat([self.router, row.reshape(1, -1)])
+        new_share = 1.0 / (self.num_experts)
+        self.share = torch.cat([self.share * (1 - new_share), torch.tensor([new_share])])
+        return self.num_experts - 1
+
+    def remove_expert(self, idx: int) -> bool:
+        if not 0 <= idx < self.num_experts or self.num_experts <= self.min:
+            return False
+        keep = [i for i in range(self.num_experts) if i != idx]
+        self.gu, self.dn, self.router, self.share = self.gu[keep], self.dn[keep], self.router[keep], self.share[keep]
+        self.share = self.share / self.share.sum().clamp(min=1e-12)
+        return True
+
     def observe(self, expert_indices):
         c = torch.bincount(expert_indices.reshape(-1).cpu(), minlength=self.num_experts).float()
         self.share = self.mom * self.share + (1 - self.mom) * c / c.sum().clamp(min=1)
@@ -181,6 +225,17 @@ class ExpertDropout:
 
     def __init__(self, p=0.1, keep_min=2):
         self.p, self.keep_min = p, keep_min
+
+    def get_active_count(self, total: int) -> int:
+        """Experts expected to stay active out of ``total`` (never fewer than ``keep_min``)."""
+        return max(min(self.keep_min, total), int(round(total * (1.0 - self.p))))
+
+    def get_mask(self, total: int, generator=None) -> List[bool]:
+        """One draw of the keep-mask over ``total`` experts (True = active)."""
+        drop = torch.rand(total, generator=generator) < self.p
+        if int((~drop).sum()) < min(self.keep_min, total):
+            drop[torch.randperm(total, generator=generator)[: self.keep_min]] = False
+        return (~drop).tolist()
 
     def __call__(self, logits: torch.Tensor, training=True, generator=None):
         if not training or self.p <= 0:
@@ -256,6 +311,50 @@ class ExpertPrefetcher:
     def prefetch(self, experts):
         for e in experts:
             self.q.put(int(e))
+
+    # ---- per-layer form of the reference (include/quant/expert_prefetch.h:73-105): experts are addressed by (layer, expert)
+    def initialize(self, num_experts: int = 0, num_layers: int = 1):
+        self.num_experts_per_layer, self.num_layers = int(num_experts), int(num_layers)
+        self.wait_ms_total, self.waits, self.misses, self.evictions = 0.0, 0, 0, 0
+        return self
+
+    def _key(self, layer_id: int, expert_id: int) -> int:
+        return int(layer_id) * max(1, getattr(self, "num_experts_per_layer", 0) or 1 << 16) + int(expert_id)
+
+    def set_expert_source(self, layer_id: int, expert_id: int, tensors):
+        """Register where an expert's weights come from: a dict of tensors (or one packed tensor), written to the disk tier."""
+        self.store(self._key(layer_id, expert_id), tensors if isinstance(tensors, dict) else {"packed": tensors})
+
+    def set_expert_segments(self, layer_id: int, expert_id: int, segments):
+        """Several separately stored pieces (gate, up, down) of one expert: a list of tensors or (name, tensor) pairs."""
+        named = {(s[0] if isinstance(s, tuple) else f"segment{i}"): (s[1] if isinstance(s, tuple) else s) for i, s in enumerate(segments)}
+        self.store(self._key(layer_id, expert_id), named)
+
+    def schedule_prefetch(self, layer_id: int, expert_ids):
+        self.prefetch(self._key(layer_id, e) for e in expert_ids)
+
+    def get_expert_weights(self, layer_id: int, expert_id: int, timeout_s: float = 5.0):
+        k = self._key(layer_id, expert_id)
+        with self.cv:
+            hit = k in self.dev
+        t0 = time.perf_counter()
+        out = self.get(k, timeout_s)
+        if not hit and hasattr(self, "waits"):
+            self.misses += 1
+            self.waits += 1
+            self.wait_ms_total += (time.perf_counter() - t0) * 1e3
+        return out
+
+    def release_expert(self, layer_id: int, expert_id: int):
+        """Drop an expert from the device tier (it stays in the host tier until that fills up)."""
+        with self.cv:
+            if self.dev.pop(self._key(layer_id, expert_id), None) is not None and hasattr(self, "evictions"):
+                self.evictions += 1
+
+    def get_stats(self) -> Dict[str, float]:
+        return {"prefetch_hits": self.stats["device_hits"], "prefetch_misses": getattr(self, "misses", 0),
+                "evictions": getattr(self, "evictions", 0), "disk_loads": self.stats["disk_loads"],
+                "avg_wait_ms": getattr(self, "wait_ms_total", 0.0) / max(1, getattr(self, "waits", 0))}
 
     def get(self, e: int, timeout_s=5.0) -> Dict[str, torch.Tensor]:
         with self.cv:
