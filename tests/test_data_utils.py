@@ -250,3 +250,42 @@ def test_task_generators_curriculum_and_tokenizer_report(tmp_path):
     r.reset()
     assert r.next_batch(2) == list(b"ab")
     r.close()
+
+
+def test_telemetry_reference_verbs(capsys):
+    c = T.CacheHitLogger.instance()
+    assert T.CacheHitLogger.instance() is c
+    c.reset()
+    c.record_sequential(1 << 20, 8, 64)
+    c.record_access(1 << 40, 64)
+    st = c.stats()
+    assert st["total_accesses"] == 9 and st["sequential_reads"] == 7 and st["ram_fetches"] == 2 and st["l1_hits"] == 7
+    assert "HBM" in c.print_report()
+    m = T.MemoryTracker.instance()
+    m.reset()
+    m.track_weights("w", 1000), m.track_weights("w", 500), m.track_gradients("g", 2000), m.track_optimizer("o", 2000, 2000)
+    m.track_activations("a", 100), m.track_kv_cache(50), m.track_offload("cpu", 7000)
+    bd = m.breakdown()
+    assert bd["weights_bytes"] == 500 and bd["optimizer_bytes"] == 4000 and bd["total_device_bytes"] == 6650 and bd["total_bytes"] == 13650
+    assert m.bpw(1000) == 4.0 and m.verify_bpw(1000, 4.2, 0.1) and not m.verify_bpw(1000, 8.0)
+    assert m.update() == 6650 and "bits per weight" in m.print_report(1000, 4.0)
+    h = T.RoutingHistogram(3)
+    h.record_with_modalities(torch.tensor([[0, 1], [0, 2], [0, 1]]), ["text", "image", "text"])
+    e = h.entries()
+    assert [x["tokens_routed"] for x in e] == [3, 2, 1] and e[0]["modality_name"] == "text" and e[2]["modality_name"] == "image"
+    assert "load-balance loss" in h.print_with_loss(1.5) and "expert" in h.print()
+    h.reset()
+    assert sum(x["tokens_routed"] for x in h.entries()) == 0
+    q = T.KVCacheQuantizer(recent=4, middle=8)
+    k, v = torch.randn(20, 2, 32), torch.randn(20, 2, 32)
+    k0 = k.clone()
+    saved = q.quantize_old_states(k, v, 20)
+    assert saved > 0 and torch.equal(k[16:], k0[16:]) and not torch.equal(k[:8], k0[:8]) and k[:8].unique().numel() < 200
+    assert q.bytes_saved() == saved and q.compression_ratio() > 1.5 and 0 < q.estimated_quality_loss() < 0.1
+    assert torch.equal(q.restore_for_attention(k, 2, 6), k[2:6].float()) and q.config()["quant4_window"] == 8
+    T.TelemetryPrinter.routing, T.TelemetryPrinter.kv = h, q
+    T.TelemetryPrinter.print_all_header(), T.TelemetryPrinter.print_cache_report(), T.TelemetryPrinter.print_memory_report(1000, 4.0)
+    T.TelemetryPrinter.print_routing_report(0.5), T.TelemetryPrinter.print_kv_quant_report(), T.TelemetryPrinter.print_all_footer()
+    out = capsys.readouterr().out
+    assert "telemetry" in out and "kv cache: saved" in out and "memory:" in out
+    T.TelemetryPrinter.routing = T.TelemetryPrinter.kv = None
