@@ -40,3 +40,23 @@ def test_tp_model_matches_dense_gpu(tmp_path):
     res = _run(tmp_path, 2, "cuda", {"NCCL_NVLS_ENABLE": "0"})
     assert all(r["status"] == 0 for r in res)
     _check(res, 4e-2)
+
+
+def test_head_partitioner_and_parallel_linear_accessors():
+    import torch
+    from transformers_fusion_b200.parallel.tp import ColumnParallelLinear, HeadPartitioner, RowParallelLinear, SequenceParallel, TensorParallelManager
+    hp = HeadPartitioner(8, 2, 4, rank=2, head_dim=4)
+    assert (hp.head_start(), hp.head_end(), hp.heads_per_rank()) == (4, 6, 2) and hp.q_heads(2) == [4, 5] and hp.kv_heads(2) == [1]
+    x = torch.arange(2 * 32.0).view(2, 32)
+    loc = hp.partition_heads(x)
+    assert loc.shape == (2, 8) and loc[0].tolist() == list(range(16, 24))
+    one = HeadPartitioner(8, 8, 1, head_dim=4)
+    assert torch.equal(one.merge_heads(one.partition_heads(x)), x) and one.sync_output(x.clone()).equal(x)
+    w = torch.randn(12, 8)
+    col, row = ColumnParallelLinear(w, 1, 2), RowParallelLinear(w, 1, 2)
+    assert col.local_out_features() == 6 and torch.equal(col.local_weight().data, w[6:]) and col.local_bias() is None
+    assert row.local_in_features() == 4 and torch.equal(row.local_weight().data, w[:, 4:])
+    sp = SequenceParallel(1, 2)
+    assert sp.world_size() == 2 and sp.world_rank() == 1 and sp.allreduce(x) is x
+    m = TensorParallelManager(None, 4, 3)
+    assert m.world_size() == 4 and m.world_rank() == 3

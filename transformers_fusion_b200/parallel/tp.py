@@ -172,6 +172,10 @@ class ColumnParallelLinear(torch.nn.Module):
         self.weight = torch.nn.Parameter(column_parallel_split(weight_full, world, rank))
         self.rank, self.world, self.ctx, self.group = rank, world, ctx, group
 
+    def local_weight(self): return self.weight
+    def local_bias(self): return None                      # the dense blocks carry their biases outside the TP products
+    def local_out_features(self) -> int: return self.weight.shape[0]
+
     def forward(self, x_shard):
         if self.world == 1:
             return F.gemm(x_shard, self.weight.data)
@@ -187,6 +191,10 @@ class RowParallelLinear(torch.nn.Module):
         super().__init__()
         self.weight = torch.nn.Parameter(row_parallel_split(weight_full, world, rank))
         self.rank, self.world, self.ctx, self.group = rank, world, ctx, group
+
+    def local_weight(self): return self.weight
+    def local_bias(self): return None
+    def local_in_features(self) -> int: return self.weight.shape[1]
 
     def forward(self, x, residual_shard=None):
         if self.world == 1:
@@ -206,9 +214,34 @@ class RowParallelLinear(torch.nn.Module):
 class HeadPartitioner:
     """Attention heads per rank (query heads and, for grouped-query attention, the kv heads they share)."""
 
-    def __init__(self, num_heads, num_kv_heads, world):
+    def __init__(self, num_heads, num_kv_heads, world, rank: int = 0, head_dim: int = 0, group=None):
         assert num_heads % world == 0, "query heads must divide over the ranks"
         self.h, self.kv, self.world = num_heads, num_kv_heads, world
+        self.rank, self.head_dim, self.group = rank, head_dim, group
+
+    # ---- this rank's range and the tensor forms (reference: HeadPartitioner, include/quant/tensor_parallelism.h:141-171)
+    def heads_per_rank(self) -> int: return self.h // self.world
+    def head_start(self) -> int: return self.rank * self.heads_per_rank()
+    def head_end(self) -> int: return self.head_start() + self.heads_per_rank()
+
+    def partition_heads(self, x: torch.Tensor, seq_len: int = 0) -> torch.Tensor:
+        """This rank's heads of a [..., num_heads * head_dim] tensor."""
+        d = self.head_dim or x.shape[-1] // self.h
+        return x[..., self.head_start() * d:self.head_end() * d].contiguous()
+
+    def merge_heads(self, local: torch.Tensor, seq_len: int = 0) -> torch.Tensor:
+        """Inverse of ``partition_heads``: every rank's heads side by side (an all-gather over the ranks)."""
+        if self.world == 1 or not dist.is_initialized():
+            return local
+        parts = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(parts, local.contiguous(), group=self.group)
+        return torch.cat(parts, -1)
+
+    def sync_output(self, output: torch.Tensor) -> torch.Tensor:
+        """Sum the ranks' partial outputs of the projection that follows the heads (in place)."""
+        if self.world > 1 and dist.is_initialized():
+            dist.all_reduce(output, group=self.group)
+        return output
 
     def q_heads(self, rank):
         return partition_heads(self.h, self.world, rank)
@@ -242,6 +275,14 @@ class SequenceParallel:
             dist.all_reduce(x, group=self.group)
         return self.scatter(x, seq_dim)
 
+    def allreduce(self, x):
+        if self.world > 1 and dist.is_initialized():
+            dist.all_reduce(x, group=self.group)
+        return x
+
+    def world_size(self) -> int: return self.world
+    def world_rank(self) -> int: return self.rank
+
 
 class TensorParallelManager:
     """The reference's manager API on top of the fused kernels: weight splitting, column / row parallel products,
@@ -255,6 +296,9 @@ class TensorParallelManager:
     row_parallel_split = staticmethod(row_parallel_split)
     reconstruct_weight = staticmethod(reconstruct_weight)
     communication_volume = staticmethod(communication_volume)
+
+    def world_size(self) -> int: return self.world
+    def world_rank(self) -> int: return self.rank
 
     def partition_heads(self, num_heads):
         return partition_heads(num_heads, self.world, self.rank)
