@@ -113,3 +113,31 @@ def test_knowledge_slots(tmp_path):
     k2 = KnowledgeExpansionEngine(m)
     assert k2.load(tmp_path / "s.kexp") and k2.slot_count() == 1
     assert torch.allclose(k2.forward_with_slots(ids), k.forward_with_slots(ids), atol=1e-5)
+
+
+def test_fine_tuner_configure_run_and_block_selection(tmp_path):
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    from transformers_fusion_b200.trainer.finetune import FineTuner
+    m = DenseModel(TransformerConfig(vocab_size=260, hidden_size=32, num_layers=1, num_heads=4, ffn_hidden_size=64, max_seq_len=32),
+                   device="cpu", dtype=torch.float32, seed=0)
+    (tmp_path / "d.txt").write_text("abcabcabc " * 60)
+    logs = []
+    ft = FineTuner(m, lr=1e-3, fmt="q16").configure(learning_rate=5e-3, num_epochs=2, batch_size=2, seq_length=16, log_interval=1,
+                                                     save_interval=3, output_path=str(tmp_path / "ft.quant"), tokenizer=ByteTokenizer(),
+                                                     log=lambda step, loss: logs.append(loss))
+    last = ft.fine_tune(str(tmp_path / "d.txt"))
+    assert len(logs) >= 8 and last < logs[0] and (tmp_path / "ft.quant").exists()
+    back = DenseModel.load(str(tmp_path / "ft.quant"))
+    assert torch.allclose(back.tok_embeddings.data, m.tok_embeddings.data)
+    g = torch.zeros(1024)
+    g[256:512] = 1e-3
+    g[700] = 1.0
+    assert FineTuner.find_trainable_blocks(g, 1e-4) == [1, 2] and FineTuner.find_trainable_blocks(g, 1e-2) == []
+    w = torch.randn(512)
+    w0 = w.clone()
+    ft.apply_quant_update(torch.ones(512), w, "q16", lr=0.5)
+    from transformers_fusion_b200.quant.qat import ste_roundtrip_
+    assert torch.allclose(w, w0 - 0.5, atol=2e-3) and torch.equal(ste_roundtrip_(w.clone(), "q16"), w)     # already on the format's grid

@@ -1,6 +1,7 @@
 """RL trainers on a tiny model: GRPO semantics (advantage-weighted updates widen the gap between
 rewarded and penalised sequences; zero-variance rewards are a no-op; MoE parameters are collected),
 DPO prefers the chosen sequence, PPO runs with adaptive KL, reward model, rollout buffer ordering."""
+import pytest
 import torch
 
 from transformers_fusion_b200.models.config import MoEConfig, TransformerConfig
@@ -168,3 +169,46 @@ def test_rlhf_pipeline_stages_end_to_end():
     pipe.set_log_callback(lambda mt: logs.append(mt.step))
     mt = pipe.run(n_rounds=2, n_ppo_steps=1, prompts=prompts, max_new_tokens=3)
     assert logs == [0, 1] and 0.0 <= mt.reward_accuracy <= 1.0 and len(pipe.comparisons()) >= 3 + 2 * 4
+
+
+def test_reward_model_verbs_rollout_buffer_and_text_worker(tmp_path):
+    import threading
+    m = tiny_bytes(3)
+    rm = rl.RewardModel(m)
+    assert rm.hidden_size() == 32 and rm.num_layers() == 2 and rm.last_loss() == 0.0
+    g = torch.Generator().manual_seed(0)
+    c, r = torch.randint(5, 60, (8, 6), generator=g), torch.randint(150, 250, (8, 6), generator=g)
+    seen = []
+    rm.set_log_callback(lambda loss, acc: seen.append((loss, acc)))
+    first = rm.train_step(c, r)
+    for _ in range(40):
+        last = rm.train_step(c, r, loss_scale=4.0)
+    sc, sr = rm.score_pair(c, r)
+    assert last < first and rm.last_loss() == last and seen[-1][1] == 1.0 and bool((sc > sr).all())
+    assert float(rl.RewardModel.reward_loss(torch.tensor([2.0]), torch.tensor([2.0]))) == pytest.approx(0.6931, abs=1e-3)
+    assert rm.compute_abstention_reward("I don't know.", 0.1) > 0 > rm.compute_abstention_reward("I don't know.", 0.95)
+    assert rm.compute_abstention_reward("The answer is 4.", 0.9) == pytest.approx(0.4)
+    rm.save(str(tmp_path / "rm.pt"))
+    fresh = rl.RewardModel(tiny_bytes(3)).load(str(tmp_path / "rm.pt"))
+    assert torch.allclose(fresh.score(c), rm.score(c))
+    buf = rl.AsyncRolloutBuffer(2)
+    assert buf.push(rl.Trajectory(tokens=[1])) and buf.push(rl.Trajectory(tokens=[2])) and buf.size() == 2
+    assert not buf.push(rl.Trajectory(tokens=[3]), timeout_s=0.05)                 # full
+    got = []
+    t = threading.Thread(target=lambda: got.append(buf.push(rl.Trajectory(tokens=[3]), timeout_s=5)))
+    t.start()
+    assert buf.pop().tokens == [1]                                                 # frees a slot: the blocked push completes
+    t.join()
+    assert got == [True] and [buf.pop().seq, buf.try_pop().seq] == [1, 2] and buf.try_pop() is None
+    assert [x.tokens for x in buf.replay()] == [[1], [2], [3]] and buf.capacity() == 2 and buf.deterministic_replay()
+    buf.close()
+    assert buf.closed() and not buf.push(rl.Trajectory()) and buf.pop(timeout_s=0.05) is None
+    tok = ByteTokenizer()
+    w = rl.RolloutWorker(rl.GRPOTrainer(m, tok, group_size=2, max_new_tokens=3), lambda ids: float(len(ids)), max_new=3)
+    seq = w.generate("hi")
+    assert seq[:2] == tok.encode("hi") and 2 < len(seq) <= 5 and len(w.generate_batch(["a", "b"])) == 2
+    tr = w.generate_trajectory("hi")
+    assert tr.reward == float(len(tr.tokens) - 2) and w.generate_trajectory("hi", reward=7.0).reward == 7.0
+    out = rl.AsyncRolloutBuffer(8)
+    assert w.produce_to(out, ["a", "b", "c"]) == 3 and [t.seq for t in out.replay()] == [0, 1, 2]
+    assert w.param_count() == sum(p.numel() for p in m.parameters())

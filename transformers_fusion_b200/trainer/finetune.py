@@ -17,6 +17,8 @@ Reference counterparts: include/quant/fine_tuning.h:43-242, src/trainer/fine_tun
 .nrad :816-890), src/trainer/finetune.cpp."""
 from __future__ import annotations
 
+import os
+
 import math
 import struct
 from dataclasses import dataclass
@@ -467,3 +469,54 @@ class FineTuner:
                 if p.dim() >= 2 and p.numel() >= 1024:
                     ste_roundtrip_(p.data, self.fmt)
         return float(loss)
+
+    # ---- the reference's surface (include/quant/finetune.h: FineTuneConfig / FineTuner) -----------------------------------
+    def configure(self, learning_rate: Optional[float] = None, num_epochs: int = 1, batch_size: int = 4, seq_length: int = 512,
+                  log_interval: int = 10, save_interval: int = 100, grad_threshold: float = 1e-6, max_grad_norm: float = 1.0,
+                  output_path: str = "finetuned.quant", tokenizer=None, log=None):
+        if learning_rate is not None:
+            self.lr = learning_rate
+        self.opt.max_grad_norm = max_grad_norm
+        self.cfg = dict(num_epochs=num_epochs, batch_size=batch_size, seq_length=seq_length, log_interval=log_interval,
+                        save_interval=save_interval, grad_threshold=grad_threshold, output_path=output_path)
+        self.tok, self.log = tokenizer, log
+        return self
+
+    def fine_tune(self, data):
+        """``data``: a text file (tokenised with the configured tokenizer) or a loader with ``next_batch()`` / ``len``.
+        Runs the configured epochs, saves at the save interval and at the end; returns the last loss."""
+        from .trainer import DataLoader
+        c = getattr(self, "cfg", None) or self.configure().cfg
+        dl = DataLoader(self.tok, data, c["batch_size"], c["seq_length"]) if isinstance(data, (str, os.PathLike)) else data
+        dev = self.model.tok_embeddings.device
+        loss = 0.0
+        for _ in range(c["num_epochs"]):
+            dl.reset()
+            for _ in range(len(dl)):
+                ids, labels = dl.next_batch()
+                loss = self.train_step(ids.to(dev), labels.to(dev))
+                if self.log and c["log_interval"] and self.steps % c["log_interval"] == 0:
+                    self.log(self.steps, loss)
+                if c["save_interval"] and self.steps % c["save_interval"] == 0:
+                    self.save(c["output_path"])
+        self.save(c["output_path"])
+        return loss
+
+    @staticmethod
+    def find_trainable_blocks(gradients: torch.Tensor, threshold: float = 1e-6, block: int = 256) -> List[int]:
+        """Indices of the ``block``-weight blocks whose mean |gradient| exceeds the threshold: the blocks worth updating."""
+        g = gradients.detach().float().reshape(-1)
+        pad = (-g.numel()) % block
+        if pad:
+            g = torch.cat([g, torch.zeros(pad, device=g.device)])
+        return (g.view(-1, block).abs().mean(1) > threshold).nonzero().reshape(-1).tolist()
+
+    def apply_quant_update(self, fp32_grad: torch.Tensor, quant_weight: torch.Tensor, fmt=None, lr: Optional[float] = None):
+        """Straight-through step on a weight that is stored in a block format: w <- roundtrip_fmt(w - lr * grad), in place."""
+        quant_weight.add_(fp32_grad.to(quant_weight.dtype), alpha=-(self.lr if lr is None else lr))
+        return ste_roundtrip_(quant_weight, fmt or self.fmt or "q16")
+
+    def save(self, path: str):
+        from ..quant import codec
+        codec.save_model(self.model, path)
+        return path

@@ -335,6 +335,60 @@ class RewardModel(torch.nn.Module):
     def pairwise_loss(self, chosen, rejected):
         return -TF.logsigmoid(self.score(chosen) - self.score(rejected)).mean()
 
+    # ---- the reference's surface (include/quant/reward.h:18-52)
+    def hidden_size(self) -> int: return self.backbone.cfg.hidden_size
+    def num_layers(self) -> int: return sum(1 for m in self.head if isinstance(m, torch.nn.Linear))
+    def last_loss(self) -> float: return getattr(self, "_last_loss", 0.0)
+    def set_log_callback(self, cb): self.log_cb = cb
+
+    def score_pair(self, chosen, rejected):
+        """(score of chosen, score of rejected), each [B]."""
+        return self.score(chosen), self.score(rejected)
+
+    @staticmethod
+    def reward_loss(chosen_rewards, rejected_rewards):
+        """Bradley-Terry: -log sigmoid(r_chosen - r_rejected), mean over the pairs."""
+        return -TF.logsigmoid(chosen_rewards - rejected_rewards).mean()
+
+    def train_step(self, chosen, rejected, opt=None, loss_scale: float = 1.0) -> float:
+        """One optimizer step on the head from a batch of pairs; reports (loss, pair accuracy) to the log callback."""
+        if opt is None:
+            opt = self.__dict__.setdefault("_opt", torch.optim.Adam(self.head.parameters(), lr=1e-3))
+        rc, rr = self.score_pair(chosen, rejected)
+        loss = self.reward_loss(rc, rr)
+        opt.zero_grad()
+        (loss * loss_scale).backward()
+        if loss_scale != 1.0:
+            for p in self.head.parameters():
+                if p.grad is not None:
+                    p.grad.div_(loss_scale)
+        opt.step()
+        self._last_loss = float(loss.detach())
+        if getattr(self, "log_cb", None):
+            self.log_cb(self._last_loss, float((rc > rr).float().mean()))
+        return self._last_loss
+
+    @staticmethod
+    def compute_abstention_reward(output: str, confidence: float) -> float:
+        """Reward shaping for "I don't know"-style answers: abstaining is worth a small positive reward when the model is
+        unsure (confidence < 0.5) and is penalised when it was confident; a committed answer earns its confidence."""
+        text = output.lower()
+        abstains = any(k in text for k in ("i don't know", "i do not know", "not sure", "cannot answer", "unsure", "no idea"))
+        c = min(1.0, max(0.0, float(confidence)))
+        if abstains:
+            return 0.3 * (1.0 - c) - 0.5 * max(0.0, c - 0.5)
+        return c - 0.5
+
+    def save(self, path: str):
+        torch.save({"head": self.head.state_dict(), "hidden": self.hidden_size()}, path)
+
+    def load(self, path: str):
+        st = torch.load(path, map_location="cpu", weights_only=True)
+        if st["hidden"] != self.hidden_size():
+            raise ValueError(f"{path}: head for hidden size {st['hidden']}, this backbone has {self.hidden_size()}")
+        self.head.load_state_dict(st["head"])
+        return self
+
 
 @dataclass
 class Rollout:
@@ -342,6 +396,73 @@ class Rollout:
     prompt: List[int]
     completion: List[int]
     reward: float
+
+
+@dataclass
+class Trajectory:
+    seq: int = 0                     # global push order: the deterministic replay key
+    tokens: List[int] = field(default_factory=list)      # prompt + generated tokens
+    reward: float = 0.0
+    done: bool = True
+
+
+class AsyncRolloutBuffer:
+    """Bounded hand-over between rollout producers and the trainer.  Trajectories are numbered in push order and popped in
+    that order, so a run can be replayed exactly; ``push`` blocks while the buffer is full, ``pop`` while it is empty (both
+    give up on ``close``).  Reference: AsyncRolloutBuffer, include/quant/rollout_worker.h:36-62."""
+
+    def __init__(self, capacity: int = 64):
+        import threading
+        self._cap, self._items, self._next, self._closed = int(capacity), {}, 0, False
+        self._det, self._log = True, []
+        self._cv = threading.Condition()
+
+    def set_deterministic_replay(self, v: bool): self._det = bool(v)
+    def deterministic_replay(self) -> bool: return self._det
+    def capacity(self) -> int: return self._cap
+    def closed(self) -> bool: return self._closed
+
+    def size(self) -> int:
+        with self._cv:
+            return len(self._items)
+
+    def push(self, t: Trajectory, timeout_s: Optional[float] = None) -> bool:
+        with self._cv:
+            if not self._cv.wait_for(lambda: self._closed or len(self._items) < self._cap, timeout_s) or self._closed:
+                return False
+            t.seq = self._next
+            self._next += 1
+            self._items[t.seq] = t
+            if self._det:
+                self._log.append(Trajectory(t.seq, list(t.tokens), t.reward, t.done))
+            self._cv.notify_all()
+            return True
+
+    def _take(self):
+        k = min(self._items)
+        t = self._items.pop(k)
+        self._cv.notify_all()
+        return t
+
+    def pop(self, timeout_s: Optional[float] = None) -> Optional[Trajectory]:
+        with self._cv:
+            if not self._cv.wait_for(lambda: self._closed or self._items, timeout_s):
+                return None
+            return self._take() if self._items else None
+
+    def try_pop(self) -> Optional[Trajectory]:
+        with self._cv:
+            return self._take() if self._items else None
+
+    def close(self):
+        with self._cv:
+            self._closed = True
+            self._cv.notify_all()
+
+    def replay(self) -> List[Trajectory]:
+        """Every trajectory pushed so far, in push order (kept only under deterministic replay)."""
+        with self._cv:
+            return list(self._log)
 
 
 class RolloutWorker:
@@ -362,6 +483,39 @@ class RolloutWorker:
     def drain(self, n=None):
         n = len(self.buffer) if n is None else min(n, len(self.buffer))
         return [self.buffer.popleft() for _ in range(n)]
+
+    # ---- text-prompt form of the reference (include/quant/rollout_worker.h:64-80)
+    def _ids(self, prompt):
+        tok = self.tr.tok
+        return list(prompt) if not isinstance(prompt, str) else (tok.encode(prompt) if tok is not None else [ord(c) % 250 + 5 for c in prompt])
+
+    def generate(self, prompt) -> List[int]:
+        """Prompt ids followed by one sampled completion."""
+        ids = self._ids(prompt)
+        out = self.tr.generate(ids, 1, self.max_new, self.temperature, seed=self.next_seq)[0]
+        self.next_seq += 1
+        return ids + out
+
+    def generate_batch(self, prompts) -> List[List[int]]:
+        return [self.generate(p) for p in prompts]
+
+    def generate_trajectory(self, prompt, reward: Optional[float] = None) -> Trajectory:
+        ids = self._ids(prompt)
+        toks = self.generate(ids)
+        r = float(self.reward_fn(toks[len(ids):])) if reward is None else float(reward)
+        return Trajectory(0, toks, r, True)
+
+    def produce_to(self, buf: AsyncRolloutBuffer, prompts) -> int:
+        """Push one trajectory per prompt; stops early when the buffer is closed.  Returns how many were pushed."""
+        n = 0
+        for p in prompts:
+            if not buf.push(self.generate_trajectory(p)):
+                break
+            n += 1
+        return n
+
+    def param_count(self) -> int:
+        return sum(p.numel() for p in self.tr.model.parameters())
 
 
 @dataclass
@@ -615,5 +769,5 @@ class RLHFPipeline:
     def run_round(self, prompts: List[List[int]]):
         if self.rm is not None:
             dev = self.policy.model.tok_embeddings.device
-            self.policy.reward_fn = lambda ids: float(self.rm.score(torch.tensor([ids or [0]], device=dev)))
+            self.policy.reward_fn = lambda ids: float(self.rm.score(torch.tensor([ids or [0]], device=dev)).detach())
         return [self.policy.train_step(prompt=p) for p in prompts]
