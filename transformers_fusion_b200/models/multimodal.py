@@ -107,7 +107,40 @@ class PatchEmbedding(nn.Module):
         return self.proj(x)
 
 
-class VisionTransformer(nn.Module):
+class _TowerAPI:
+    """The reference's encoder verbs on every tower (include/quant/{vision,audio,video,text}.h): ``init`` (re-)draws the
+    weights, ``is_initialized`` says whether weights exist, ``encode`` returns pooled features, ``hidden_size`` their width."""
+
+    def init(self, seed: int = 0):
+        g = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for p_ in self.parameters():
+                if p_.dim() >= 2:
+                    p_.copy_((torch.randn(p_.shape, generator=g) * (1.0 / math.sqrt(p_.shape[-1]))).to(p_.dtype))
+        self._initialized = True
+        return self
+
+    def is_initialized(self) -> bool:
+        return getattr(self, "_initialized", True) and any(True for _ in self.parameters())
+
+    def hidden_size(self) -> int:
+        c = getattr(self, "cfg", None)
+        for name in ("hidden_dim", "shared_hidden", "hidden"):
+            if c is not None and hasattr(c, name):
+                return int(getattr(c, name))
+        return int(getattr(self, "dim", 0))
+
+    d_model = hidden_size
+
+    @torch.no_grad()
+    def encode(self, x, *args, **kw):
+        """Pooled features [B, hidden] of a batch (a single unbatched item gets a batch dimension)."""
+        out = self(x, *args, **kw)
+        out = out[0] if isinstance(out, tuple) else out
+        return out if out.dim() == 2 else out.mean(1)
+
+
+class VisionTransformer(_TowerAPI, nn.Module):
     def __init__(self, cfg: Optional[ViTConfig] = None):
         super().__init__()
         self.cfg = cfg = cfg or ViTConfig()
@@ -125,6 +158,14 @@ class VisionTransformer(nn.Module):
             x = b(x)
         x = self.norm(x)
         return x if return_tokens else x[:, 0]
+
+    def config(self) -> ViTConfig: return self.cfg
+    def patch_embed(self, img): return self.patch(img)
+
+    @torch.no_grad()
+    def get_patch_features(self, img):
+        """Per-patch features [B, patches, hidden] (the class token is left out)."""
+        return self(img, return_tokens=True)[:, 1:]
 
 
 @dataclass
@@ -150,7 +191,7 @@ class Conv1DExtractor(nn.Module):
         return TF.gelu(self.c2(y)).transpose(1, 2).to(x.dtype)
 
 
-class AudioTransformer(nn.Module):
+class AudioTransformer(_TowerAPI, nn.Module):
     def __init__(self, cfg: Optional[AudioEncoderConfig] = None):
         super().__init__()
         self.cfg = cfg = cfg or AudioEncoderConfig()
@@ -172,6 +213,10 @@ class AudioTransformer(nn.Module):
             x = b(x)
         x = self.norm(x)
         return x if return_tokens else x.mean(1)
+
+    def config(self) -> AudioEncoderConfig: return self.cfg
+    def n_mels(self) -> int: return self.cfg.input_dim
+    def sample_rate(self) -> int: return int(getattr(self.cfg, "sample_rate", 16000))
 
 
 @dataclass
@@ -209,6 +254,10 @@ class CrossAttentionBlock(nn.Module):
         x = x + self.o(a)
         return x + self.down(TF.gelu(self.up(self.nm(x)), approximate="tanh"))
 
+    def forward_self_attn(self, x, mask=None):
+        """The block applied to a sequence that attends to itself."""
+        return self.forward(x, x, mask)
+
 
 @dataclass
 class MultimodalEncoderConfig:
@@ -236,10 +285,10 @@ class MultimodalEncoderConfig:
     modality_dropout: float = 0.1
 
 
-class TextEncoder(nn.Module):
+class TextEncoder(_TowerAPI, nn.Module):
     def __init__(self, vocab, dim, layers, heads, max_len=2048, causal=False):
         super().__init__()
-        self.emb = nn.Embedding(vocab, dim)
+        self.emb, self.dim = nn.Embedding(vocab, dim), dim
         self.pos = nn.Parameter(torch.randn(1, max_len, dim) * 0.02)
         self.blocks = nn.ModuleList(EncoderBlock(dim, heads, 4 * dim) for _ in range(layers))
         self.norm, self.causal = RMSNorm(dim), causal
@@ -259,6 +308,9 @@ class ModalityProjection(nn.Module):
 
     def forward(self, x):
         return self.norm(self.proj(x))
+
+    project = forward
+    project_vision = project_audio = project_text = forward      # one projection per instance: the names say what it is used for
 
 
 class ModalityFusionEncoder(nn.Module):
@@ -293,6 +345,36 @@ class ModalityFusionEncoder(nn.Module):
             x = b(x)
         return self.norm(x), spans
 
+    # ---- named fusion modes (reference: ModalityFusionEncoder, include/quant/multimodal_cross_attn.h)
+    def fuse(self, image=None, audio=None, text=None):
+        """Fused token sequence [B, tokens, hidden] (early fusion, the module's forward)."""
+        return self(image, audio, text)[0]
+
+    fuse_early = fuse
+
+    def fuse_late(self, image=None, audio=None, text=None):
+        """Late fusion: every modality runs through the shared transformer on its own and the pooled results are
+        averaged -> [B, hidden]."""
+        pooled = []
+        for name, t in (("image", image), ("audio", audio), ("text", text)):
+            if t is not None:
+                pooled.append(self(**{name: t})[0].mean(1))
+        return torch.stack(pooled).mean(0)
+
+    def get_per_modality_features(self, image=None, audio=None, text=None):
+        """{modality: pooled features [B, hidden]} read from the early-fused sequence."""
+        x, spans = self(image, audio, text)
+        return {m: x[:, a:b].mean(1) for m, (a, b) in spans.items()}
+
+    def apply_modality_dropout(self, feats: dict, p: Optional[float] = None, generator=None) -> dict:
+        """Drop whole modalities with probability ``p`` (at least one always survives): {name: tensor or None}."""
+        p = self.cfg.modality_dropout if p is None else p
+        names = [m for m, t in feats.items() if t is not None]
+        keep = [m for m in names if float(torch.rand((), generator=generator)) >= p]
+        if not keep and names:
+            keep = [names[int(torch.randint(len(names), (), generator=generator))]]
+        return {m: (t if m in keep else None) for m, t in feats.items()}
+
 
 class ContrastiveAlignmentHead(nn.Module):
     """CLIP-style symmetric InfoNCE between two pooled embeddings with a learned temperature."""
@@ -313,6 +395,27 @@ class ContrastiveAlignmentHead(nn.Module):
         s = self.similarity(a, b)
         t = torch.arange(s.shape[0], device=s.device)
         return 0.5 * (TF.cross_entropy(s, t) + TF.cross_entropy(s.t(), t))
+
+    # ---- the reference's names (include/quant/multimodal_cross_attn.h: ContrastiveAlignmentHead)
+    def project(self, x, which: str = "a"):
+        return TF.normalize((self.pa if which == "a" else self.pb)(x).float(), dim=-1)
+
+    def align_features(self, a, b):
+        return self.embed(a, b)
+
+    compute_clip_loss = forward
+
+    def compute_infonce_loss(self, a, b):
+        """One-directional InfoNCE: each row of ``a`` must pick its own row of ``b``."""
+        s = self.similarity(a, b)
+        return TF.cross_entropy(s, torch.arange(s.shape[0], device=s.device))
+
+    def get_temperature(self) -> float:
+        return float(1.0 / self.logit_scale.exp())
+
+    def set_temperature(self, t: float):
+        with torch.no_grad():
+            self.logit_scale.fill_(math.log(1.0 / max(float(t), 1e-4)))
 
 
 class MultimodalCrossAttention(nn.Module):
@@ -345,6 +448,94 @@ class MultimodalCrossAttention(nn.Module):
         if av is not None and tv is not None:
             out["loss_audio_text"] = self.align_at(av.mean(1), tv.mean(1))
         return out
+
+
+def _mmca_api():
+    """High-level verbs of the joint model (reference: MultimodalCrossAttention, include/quant/multimodal_cross_attn.h)."""
+    M = MultimodalCrossAttention
+
+    def config(self): return self.cfg
+    def vision_encoder(self): return self.vision
+    def audio_encoder(self): return self.audio
+    def text_embedding(self): return self.text
+    def contrastive_head(self, pair: str = "image_text"): return self.align_it if pair == "image_text" else self.align_at
+
+    @torch.no_grad()
+    def encode_image(self, image): return self.vision(image, return_tokens=False)
+
+    @torch.no_grad()
+    def encode_audio(self, mel): return self.audio(mel, return_tokens=False)
+
+    @torch.no_grad()
+    def encode_text(self, text_ids): return self.text(text_ids, return_tokens=False)
+
+    def forward_text_image(self, text_ids, image):
+        """Text tokens grounded in the image: [B, text tokens, shared hidden]."""
+        return self(image=image, text_ids=text_ids)["text_grounded"]
+
+    def forward_text_audio(self, text_ids, mel):
+        return self(mel=mel, text_ids=text_ids)["text_grounded"]
+
+    def add_image_tokens(self, image):
+        """Shared-width tokens of an image, tagged as image tokens (what the fusion encoder concatenates)."""
+        return self.fusion.proj["image"](self.vision(image, return_tokens=True)) + self.fusion.tag["image"]
+
+    def add_audio_tokens(self, mel):
+        return self.fusion.proj["audio"](self.audio(mel)) + self.fusion.tag["audio"]
+
+    def add_text_tokens(self, text_ids):
+        return self.fusion.proj["text"](self.text(text_ids)) + self.fusion.tag["text"]
+
+    @torch.no_grad()
+    def retrieve_images(self, text_ids, images, top_k: int = 5):
+        """Indices and similarities of the images that match one text best (alignment-head similarity)."""
+        sim = self.align_it.similarity(self.encode_image(images), self.encode_text(text_ids))[:, 0]
+        v, i = sim.topk(min(top_k, sim.numel()))
+        return i.tolist(), v.tolist()
+
+    @torch.no_grad()
+    def retrieve_text(self, image, texts_ids, top_k: int = 5):
+        sim = self.align_it.similarity(self.encode_image(image), self.encode_text(texts_ids))[0]
+        v, i = sim.topk(min(top_k, sim.numel()))
+        return i.tolist(), v.tolist()
+
+    def _vocab_logits(self, grounded):
+        """Grounded text states scored against the text tower's embedding table (tied read-out through the fusion's text
+        projection): [B, T, vocab]."""
+        table = self.fusion.proj["text"](self.text.emb.weight[None])[0]
+        return grounded @ table.t()
+
+    @torch.no_grad()
+    def generate_caption(self, image, bos: int = 1, eos: int = 2, max_tokens: int = 16):
+        """Greedy caption ids for ONE image [1, C, H, W]: the next token is read from the last grounded text state."""
+        ids = [bos]
+        for _ in range(max_tokens):
+            g = self.forward_text_image(torch.tensor([ids], device=image.device), image)
+            nxt = int(self._vocab_logits(g)[0, -1].argmax())
+            ids.append(nxt)
+            if nxt == eos:
+                break
+        return ids[1:]
+
+    @torch.no_grad()
+    def visual_question_answer(self, image, question_ids, max_tokens: int = 8, eos: int = 2):
+        """Greedy answer ids that continue the question, grounded in the image."""
+        ids = list(question_ids[0].tolist() if torch.is_tensor(question_ids) else question_ids)
+        out = []
+        for _ in range(max_tokens):
+            g = self.forward_text_image(torch.tensor([ids + out], device=image.device), image)
+            nxt = int(self._vocab_logits(g)[0, -1].argmax())
+            out.append(nxt)
+            if nxt == eos:
+                break
+        return out
+
+    for name, fn in list(locals().items()):
+        if callable(fn) and name not in ("M",):
+            setattr(M, name, fn)
+
+
+_mmca_api()
 
 
 class CrossModalAttention(CrossAttentionBlock):
@@ -390,6 +581,20 @@ class MelSpectrogram:
             fb[i] = torch.clamp(torch.minimum((bins - l) / (c - l), (r - bins) / (r - c)), min=0)
         return fb
 
+    def init(self, sample_rate: Optional[int] = None, n_mels: Optional[int] = None):
+        """Rebuild the filter bank for another sample rate / number of bands."""
+        self.sr, self.n_mels = sample_rate or self.sr, n_mels or self.n_mels
+        self.fb = self.mel_filterbank(self.n_mels, self.n_fft, self.sr)
+        return self
+
+    def is_initialized(self) -> bool: return self.fb is not None
+    def feature_length(self, num_samples: int) -> int: return 1 + num_samples // self.hop
+
+    def extract(self, waveform):
+        """The reference's name for ``compute``; a 1-D waveform is treated as one channel."""
+        w = torch.as_tensor(waveform)
+        return self.compute(w[None] if w.dim() == 1 else w)
+
     def compute(self, waveform):
         """waveform [channels, samples] -> [channels, frames, n_mels]."""
         w = waveform.float()
@@ -407,6 +612,12 @@ class AudioFeatureExtractor:
     @torch.no_grad()
     def extract(self, audio):
         return self.encoder(self.mel.compute(audio), return_tokens=False)
+
+    def init(self, sample_rate: Optional[int] = None):
+        self.mel.init(sample_rate, self.encoder.cfg.input_dim)
+        return self
+
+    def is_initialized(self) -> bool: return self.mel.is_initialized() and self.encoder.is_initialized()
 
 
 class AudioSynthesizer:
@@ -527,6 +738,43 @@ class MultimodalFusion(nn.Module):
         return self.cat(both)
 
 
+def _fusion_api():
+    """Named fusions (reference: MultimodalFusion, include/quant/multimodal.h): pairs, all three, weighted."""
+    Fz = MultimodalFusion
+
+    def fuse_vision_text(self, vision, text): return self(text, vision)        # text queries the image
+    def fuse_audio_text(self, audio, text): return self(text, audio)
+    def fuse_vision_audio(self, vision, audio): return self(vision, audio)
+
+    def compute_fusion_weights(self, *streams):
+        """Soft-max over the streams of their mean activation energy: the louder stream gets the larger weight."""
+        e = torch.stack([s_.float().pow(2).mean() for s_ in streams])
+        return torch.softmax(e / e.mean().clamp(min=1e-12), 0)
+
+    def fuse_weighted(self, streams, weights=None):
+        """Weighted sum of pooled streams -> [B, hidden]."""
+        w = self.compute_fusion_weights(*streams) if weights is None else torch.as_tensor(weights, dtype=torch.float32)
+        return sum(wi * s_.mean(1).float() for wi, s_ in zip(w, streams))
+
+    def fuse_all(self, vision, audio, text):
+        """Text grounded first in the image, then in the audio: [B, text tokens, hidden]."""
+        return self(self(text, vision), audio)
+
+    def fuse_all_multistream(self, vision, audio, text):
+        """Every stream grounded in the two others; returns the three grounded streams."""
+        va = torch.cat([vision, audio], 1)
+        return self(vision, torch.cat([audio, text], 1)), self(audio, torch.cat([vision, text], 1)), self(text, va)
+
+    def param_count(self): return sum(p_.numel() for p_ in self.parameters())
+
+    for name, fn in list(locals().items()):
+        if callable(fn) and name != "Fz":
+            setattr(Fz, name, fn)
+
+
+_fusion_api()
+
+
 class CrossModalAlignment(ContrastiveAlignmentHead):
     def contrastive_loss(self, a, b):
         return self.forward(a, b)
@@ -567,6 +815,31 @@ class MultiModalTokenizer:
             ids += [self.BOA] + [self.audio_base + int(c) for c in audio_codes] + [self.EOA]
         return ids
 
+    def image_token_id(self, code: int = 0) -> int: return self.image_base + int(code)
+    def audio_token_id(self, code: int = 0) -> int: return self.audio_base + int(code)
+
+    def encode_image(self, image, grid: int = 8, levels: Optional[int] = None) -> List[int]:
+        """Discrete codes of an image without a learned codebook: the mean brightness of each cell of a ``grid`` x ``grid``
+        partition, quantised to the image-code range, bracketed by the image markers."""
+        img = image.data if isinstance(image, Image) else torch.as_tensor(image).float()
+        img = img.mean(0, keepdim=True) if img.dim() == 3 else img[None]
+        cells = TF.adaptive_avg_pool2d(img[None], grid)[0, 0].reshape(-1)
+        n = levels or (self.audio_base - self.image_base)
+        lo, hi = float(cells.min()), float(cells.max())
+        codes = ((cells - lo) / max(hi - lo, 1e-12) * (n - 1)).round().long().tolist()
+        return self.encode("", image_codes=codes)
+
+    def encode_audio(self, mel_or_wave, frames: int = 16) -> List[int]:
+        """Discrete codes of a log-mel spectrogram [frames, mels] (or a waveform): the mean energy of ``frames`` equal
+        time slices, quantised to the audio-code range."""
+        x = torch.as_tensor(mel_or_wave).float()
+        x = x.abs()[:, None] if x.dim() == 1 else x
+        sl = TF.adaptive_avg_pool1d(x.mean(1)[None, None], frames)[0, 0]
+        n = self.vocab_size - self.audio_base
+        lo, hi = float(sl.min()), float(sl.max())
+        codes = ((sl - lo) / max(hi - lo, 1e-12) * (n - 1)).round().long().tolist()
+        return self.encode("", audio_codes=codes)
+
     def decode(self, ids):
         text = self.text.decode([i for i in ids if i < self.tv])
         img = [i - self.image_base for i in ids if self.image_base <= i < self.audio_base]
@@ -588,6 +861,14 @@ class ImageNetClassifier(nn.Module):
         p = torch.softmax(self.forward(img).float(), -1)
         v, i = p.topk(top_k, -1)
         return [[(int(a), float(b)) for a, b in zip(ii, vv)] for ii, vv in zip(i, v)]
+
+    @torch.no_grad()
+    def evaluate(self, images, labels, top_k: int = 5) -> dict:
+        """{top1, top5 (top-``top_k``) accuracy} on a labelled batch."""
+        lg = self.forward(images).float()
+        lab = torch.as_tensor(labels, device=lg.device)
+        top = lg.topk(min(top_k, lg.shape[-1]), -1).indices
+        return {"top1": float((top[:, 0] == lab).float().mean()), f"top{top_k}": float((top == lab[:, None]).any(-1).float().mean())}
 
 
 ImageClassifier = ImageNetClassifier
@@ -631,7 +912,7 @@ class OCRBox:
     confidence: float = 0.0
 
 
-class OCREngine(nn.Module):
+class OCREngine(_TowerAPI, nn.Module):
     """Line recogniser: the image is cut into column strips (patch columns), encoded, and decoded with CTC."""
 
     def __init__(self, vit: VisionTransformer, vocab_size, blank=0):
@@ -656,13 +937,13 @@ class OCREngine(nn.Module):
 OCRPipeline = OCREngine
 
 
-class VideoEncoder(nn.Module):
+class VideoEncoder(_TowerAPI, nn.Module):
     """Frames through the image tower, then a temporal transformer over the per-frame features."""
 
     def __init__(self, vit: VisionTransformer, temporal_layers=2):
         super().__init__()
         d = vit.cfg.hidden_dim
-        self.vit = vit
+        self.vit, self.dim = vit, d
         self.temporal = nn.ModuleList(EncoderBlock(d, vit.cfg.num_heads, 4 * d) for _ in range(temporal_layers))
 
     def forward(self, video):
@@ -680,6 +961,14 @@ class VideoUnderstanding(nn.Module):
 
     def forward(self, video):
         return self.head(self.enc(video).mean(1))
+
+    @torch.no_grad()
+    def describe(self, video, class_names: Optional[Sequence[str]] = None, top_k: int = 3) -> str:
+        """One line per clip naming the most likely classes with their probabilities."""
+        p = torch.softmax(self.forward(video).float(), -1)
+        v, i = p.topk(min(top_k, p.shape[-1]), -1)
+        name = lambda c: class_names[c] if class_names else f"class {c}"
+        return "\n".join(", ".join(f"{name(int(c))} ({float(q):.2f})" for c, q in zip(ii, vv)) for ii, vv in zip(i, v))
 
 
 class ImageCaptioning(nn.Module):
@@ -724,6 +1013,12 @@ class VisualQA(nn.Module):
         v = self.pv(self.vit(img, return_tokens=True))
         q = self.pt(self.text(question_ids))
         return self.head(self.fuse(q, v).mean(1))
+
+    @torch.no_grad()
+    def answer(self, img, question_ids, answers: Optional[Sequence[str]] = None):
+        """The most likely answer per example: its index, or its text when ``answers`` names the classes."""
+        best = self.forward(img, question_ids).argmax(-1).tolist()
+        return [answers[b] for b in best] if answers else best
 
 
 class TextToImage(nn.Module):
@@ -794,6 +1089,18 @@ class Image:
         w = torch.tensor([0.299, 0.587, 0.114])[:, None, None]
         return Image((self.data[:3] * w).sum(0, keepdim=True))
 
+    # ---- accessors and file verbs of the reference (include/quant/image.h)
+    def channels(self) -> int: return self.data.shape[0]
+    def height(self) -> int: return self.data.shape[1]
+    def width(self) -> int: return self.data.shape[2]
+    def numel(self) -> int: return self.data.numel()
+    def to_tensor(self) -> torch.Tensor: return self.data
+
+    def save(self, path): return self.save_ppm(path)
+
+    @classmethod
+    def load(cls, path): return cls.load_ppm(path)
+
     def save_ppm(self, path):
         d = (self.data.clamp(0, 1) * 255).to(torch.uint8)
         if d.shape[0] == 1:
@@ -821,6 +1128,25 @@ class Video:
     def duration(self):
         return self.frames.shape[0] / self.fps
 
+    # ---- accessors and file verbs of the reference (include/quant/video.h)
+    def num_frames(self) -> int: return self.frames.shape[0]
+    def height(self) -> int: return self.frames.shape[2]
+    def width(self) -> int: return self.frames.shape[3]
+    def frame(self, i: int) -> Image: return Image(self.frames[i])
+
+    @classmethod
+    def load(cls, directory: str, fps: float = 30.0) -> "Video":
+        """Frames from a directory of PPM files (sorted by name)."""
+        import os
+        names = sorted(n for n in os.listdir(directory) if n.lower().endswith(".ppm"))
+        return cls(torch.stack([Image.load_ppm(os.path.join(directory, n)).data for n in names]), fps)
+
+    def save(self, directory: str):
+        import os
+        os.makedirs(directory, exist_ok=True)
+        for i in range(self.num_frames()):
+            self.frame(i).save_ppm(os.path.join(directory, f"frame_{i:06d}.ppm"))
+
 
 VisionEncoder = VisionTransformer
 AudioEncoder = AudioTransformer
@@ -833,6 +1159,18 @@ class TextDecoder(TextEncoder):
 
     def forward(self, ids):
         return self.head(super().forward(ids))
+
+    @torch.no_grad()
+    def decode(self, ids, max_tokens: int = 16, eos: int = -1):
+        """Greedy continuation of a prompt [1, S] -> the new ids."""
+        ids = list(ids[0].tolist() if torch.is_tensor(ids) else ids)
+        out = []
+        for _ in range(max_tokens):
+            nxt = int(self(torch.tensor([ids + out]))[0, -1].argmax())
+            out.append(nxt)
+            if nxt == eos:
+                break
+        return out
 
 
 class SentenceEmbedder:
@@ -851,3 +1189,8 @@ class SentenceEmbedder:
     def similarity(self, a: str, b: str) -> float:
         e = self.embed([a, b])
         return float(e[0] @ e[1])
+
+    forward = embed
+
+    def hidden_size(self) -> int: return self.text.hidden_size()
+    def output_size(self) -> int: return self.text.hidden_size()
