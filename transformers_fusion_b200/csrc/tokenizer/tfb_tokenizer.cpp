@@ -539,6 +539,41 @@ TFB_EXPORT int tfb_tok_load(void* h, const char* path) {
   if (t->kind == 1) return t->uni.load_tsv(path) ? 0 : -1;
   return t->hf.load(path) ? 0 : -1;
 }
+// Text of piece `id` (Unigram pieces / BPE vocabulary / byte-level BPE tokens); returns its byte length or -1.
+TFB_EXPORT long long tfb_tok_id_to_token(void* h, int id, char* out, long long cap) {
+  Tok* t = static_cast<Tok*>(h);
+  const std::vector<std::string>& v = t->kind == 0 ? t->bpe.vocab : t->kind == 1 ? t->uni.pieces : t->hf.id2tok;
+  if (id < 0 || size_t(id) >= v.size()) return -1;
+  memcpy(out, v[size_t(id)].data(), size_t(std::min<long long>(cap, (long long)v[size_t(id)].size())));
+  return (long long)v[size_t(id)].size();
+}
+// Log-probability of a Unigram piece (0 for the other kinds).
+TFB_EXPORT double tfb_tok_piece_score(void* h, int id) {
+  Tok* t = static_cast<Tok*>(h);
+  return (t->kind == 1 && id >= 0 && size_t(id) < t->uni.logp.size()) ? t->uni.logp[size_t(id)] : 0.0;
+}
+// Unigram special ids: which = 0 unknown, 1 begin, 2 end.
+TFB_EXPORT void tfb_tok_set_special(void* h, int which, int id) {
+  Tok* t = static_cast<Tok*>(h);
+  if (t->kind != 1) return;
+  (which == 0 ? t->uni.unk : which == 1 ? t->uni.bos : t->uni.eos) = id;
+}
+// Encode with the per-piece log-probabilities of the best segmentation (Unigram only; others get zeros).
+TFB_EXPORT long long tfb_tok_encode_scores(void* h, const char* text, long long n, int* out, double* scores, long long cap) {
+  Tok* t = static_cast<Tok*>(h);
+  if (t->kind != 1) return -1;
+  std::vector<double> lp;
+  const std::vector<int> ids = t->uni.viterbi(Unigram::normalize(std::string(text, size_t(n))), &lp);
+  for (long long i = 0; i < (long long)ids.size() && i < cap; ++i) { out[i] = ids[size_t(i)]; scores[i] = lp[size_t(i)]; }
+  return (long long)ids.size();
+}
+// 1 when `id` is one of the byte-level tokenizer's added special tokens.
+TFB_EXPORT int tfb_tok_is_special(void* h, int id) {
+  Tok* t = static_cast<Tok*>(h);
+  if (t->kind != 2) return id >= 0 && id <= 2;
+  for (const auto& sp : t->hf.specials) if (sp.second == id) return 1;
+  return 0;
+}
 TFB_EXPORT int tfb_tok_token_to_id(void* h, const char* tok) {
   Tok* t = static_cast<Tok*>(h);
   if (t->kind == 2) { auto it = t->hf.tok2id.find(tok); return it == t->hf.tok2id.end() ? -1 : it->second; }
