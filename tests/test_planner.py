@@ -71,3 +71,24 @@ def test_mixed_tensor_roundtrip(tmp_path):
     back = r.read_tensor("w")
     # Q_6 is a 64-level normal-quantile codebook: outliers beyond its top level clip, so the check is on the energy of the error
     assert back.shape == w.shape and float(((back - w) ** 2).sum() / (w ** 2).sum()) < 5e-3
+
+
+def test_registry_quantize_results():
+    import numpy as np
+    from transformers_fusion_b200.quant.planner import FormatRegistry as R
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal(1000).astype(np.float32)
+    q8 = R.quantize_q8(w)
+    back = R.dequantize(q8)
+    assert back.shape == (1000,) and R.measure_mse(w, back) < 1e-3 and len(q8.blocks) == 4
+    assert 8.0 <= R.actual_bpw(q8) < 9.5 and R.serialized_size_bytes(q8) == sum(map(len, q8.blocks)) + 48
+    errs = [R.measure_mse(w, R.dequantize(f(w))) for f in (R.quantize_q1, R.quantize_q2, R.quantize_q4, R.quantize_q8)]
+    assert errs == sorted(errs, reverse=True)
+    one = R.quantize_block(w[:100], R.parse_format_name("Q_4"))
+    assert len(one.blocks) == 1 and R.dequantize(one).shape == (100,)
+    scaled = np.concatenate([w[:256] * 10, w[256:512] * 0.1, w[512:768] * 5, w[768:] * 0.2])
+    mix = R.quantize_q_twi_mix_1_5(scaled, 256)
+    assert [R.parse_format_name("Q_2").id == m.format for m in mix] == [True, False, True, False]
+    sp = R.quantize_q_sparse(w, 0.1)
+    dense = R.dequantize_sparse(sp)
+    assert sp["indices"].size == 100 and (dense != 0).sum() == 100 and abs(dense).max() == pytest.approx(abs(w).max(), rel=1e-3)

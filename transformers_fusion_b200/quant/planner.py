@@ -82,6 +82,15 @@ class FormatPlan:
         return h
 
 
+@dataclass
+class QuantResult:
+    """Blocks of one array encoded in one format."""
+    format: int
+    n: int
+    block: int
+    blocks: List[bytes]
+
+
 class FormatRegistry:
     _singles = None
     _twi = None
@@ -154,6 +163,73 @@ class FormatRegistry:
         for o in range(0, data.size, block):
             seg = data[o:o + block]
             out[o:o + block] = codec.dequantize_block(fmt, codec.quantize_block(fmt, seg), seg.size)
+        return out
+
+    # ---- quantise / dequantise with a result record (reference: FormatRegistry::quantize ... actual_bpw,
+    # include/quant/format_registry.h:121-147)
+    @classmethod
+    def quantize(cls, data, fmt, block: int = 256) -> "QuantResult":
+        """Encode a flat array block by block into ``fmt`` (a descriptor, a format id or a name)."""
+        f = fmt.id if isinstance(fmt, FormatDescriptor) else (_fmt(fmt) if isinstance(fmt, str) else int(fmt))
+        a = np.ascontiguousarray(np.asarray(data, dtype=np.float32).reshape(-1))
+        blocks = [codec.quantize_block(f, a[o:o + block]) for o in range(0, a.size, block)]
+        return QuantResult(f, a.size, block, blocks)
+
+    @classmethod
+    def quantize_block(cls, block_data, fmt) -> "QuantResult":
+        a = np.asarray(block_data, dtype=np.float32).reshape(-1)
+        return cls.quantize(a, fmt, block=max(1, a.size))
+
+    @staticmethod
+    def dequantize(qr: "QuantResult", n: Optional[int] = None) -> np.ndarray:
+        out = np.concatenate([codec.dequantize_block(qr.format, payload, min(qr.block, qr.n - i * qr.block))
+                              for i, payload in enumerate(qr.blocks)]) if qr.blocks else np.zeros(0, np.float32)
+        return out[: n or qr.n]
+
+    @staticmethod
+    def serialized_size_bytes(qr: "QuantResult") -> int:
+        """Payload bytes plus the container's per-block framing (weight count, codebook size, index size: 12 bytes)."""
+        return sum(len(b) for b in qr.blocks) + 12 * len(qr.blocks)
+
+    @staticmethod
+    def actual_bpw(qr: "QuantResult") -> float:
+        return 8.0 * sum(len(b) for b in qr.blocks) / max(1, qr.n)
+
+    @classmethod
+    def quantize_q1(cls, data): return cls.quantize(data, "Q_1")
+
+    @classmethod
+    def quantize_q2(cls, data): return cls.quantize(data, "Q_2")
+
+    @classmethod
+    def quantize_q4(cls, data): return cls.quantize(data, "Q_4")
+
+    @classmethod
+    def quantize_q8(cls, data): return cls.quantize(data, "Q_8")
+
+    @classmethod
+    def quantize_q_twi_mix_1_5(cls, data, block_size: int = 256) -> List["QuantResult"]:
+        """The 1.5-bit two-format mix: the half of the blocks with the larger energy in Q_2, the rest in Q_1; one result
+        per block, in order."""
+        a = np.ascontiguousarray(np.asarray(data, dtype=np.float32).reshape(-1))
+        spans = [a[o:o + block_size] for o in range(0, a.size, block_size)]
+        energy = np.array([float((sp ** 2).mean()) for sp in spans])
+        hi = set(np.argsort(-energy)[: len(spans) // 2].tolist())
+        return [cls.quantize(sp, "Q_2" if i in hi else "Q_1", block_size) for i, sp in enumerate(spans)]
+
+    @classmethod
+    def quantize_q_sparse(cls, data, keep: float = 0.1) -> dict:
+        """Sparse form: the largest ``keep`` fraction of the weights (by magnitude) as (index, fp16 value) pairs, the rest
+        zero.  Returns {"n", "indices" int32, "values" float16}; ``dequantize_sparse`` restores the dense array."""
+        a = np.asarray(data, dtype=np.float32).reshape(-1)
+        k = max(1, int(round(keep * a.size)))
+        idx = np.sort(np.argpartition(-np.abs(a), k - 1)[:k]).astype(np.int32)
+        return {"n": a.size, "indices": idx, "values": a[idx].astype(np.float16)}
+
+    @staticmethod
+    def dequantize_sparse(sp: dict) -> np.ndarray:
+        out = np.zeros(sp["n"], dtype=np.float32)
+        out[sp["indices"]] = sp["values"].astype(np.float32)
         return out
 
     @classmethod
