@@ -98,3 +98,69 @@ def test_training_utils():
     pt = U.ProgressTracker(10)
     pt.update(5)
     assert pt.fraction() == 0.5 and pt.render(10).startswith("[#####.....]")
+
+
+def test_training_utils_reference_verbs(tmp_path):
+    s = U.MixedPrecisionScaler(64.0, interval=1)
+    loss = torch.tensor(2.0)
+    assert float(s.scale_loss(loss)) == 128.0 and s.current_scale() == 64.0
+    good, bad = torch.nn.Parameter(torch.ones(2)), torch.nn.Parameter(torch.ones(2))
+    good.grad, bad.grad = torch.ones(2), torch.tensor([1.0, float("nan")])
+    assert not s.check_gradients([good]) and s.check_gradients([good, bad]) and s.check_gradients([torch.tensor([float("inf")])])
+    s.update_scale(False)
+    assert s.current_scale() == 128.0 and s.good_steps() == 0
+    s.reset()
+    assert s.current_scale() == 64.0
+    w = torch.nn.Parameter(torch.tensor([1.0001, 2.0], dtype=torch.bfloat16))
+    mp = U.MixedPrecisionManager(enabled=True, init_loss_scale=8.0, growth_interval=1)
+    mp.create_master_weights([w])
+    mp.master[0][0] = 1.0001
+    assert mp.is_enabled() and mp.current_loss_scale() == 8.0 and mp.to_fp16(w).dtype == torch.bfloat16 and mp.to_fp32(mp.to_fp16(w)).dtype == torch.float32
+    mp.sync_weights_to_model()
+    assert float(w.data[0]) == 1.0                                       # rounded to the compute precision
+    w.grad = torch.tensor([8.0, 16.0], dtype=torch.bfloat16)
+    mp.cast_gradients_to_fp32()
+    mp.unscale_gradients()
+    assert w.grad is None and w.main_grad.dtype == torch.float32 and w.main_grad.tolist() == [1.0, 2.0] and not mp.check_gradients()
+    assert mp.update_loss_scale(True) == 4.0 and float(mp.scale_loss(torch.tensor(1.0))) == 4.0
+    w.data.fill_(5.0)
+    mp.sync_weights_from_model()
+    assert mp.master[0].tolist() == [5.0, 5.0]
+    off = U.MixedPrecisionManager(enabled=False)
+    assert float(off.scale_loss(torch.tensor(3.0))) == 3.0 and off.update_loss_scale(True) == 1.0
+    p = torch.nn.Parameter(torch.ones(3))
+    ema = U.EMAWeightAveraging(0.5).init([p])
+    p.data.fill_(3.0)
+    ema.update([p])
+    ema.copy_to_model([p])
+    assert p.data.tolist() == [2.0] * 3
+    pt = U.ProgressTracker(4, log_interval=2)
+    assert [pt.step() for _ in range(4)] == [False, True, False, True] and pt.is_done() and pt.current_step() == 4 and pt.total_steps() == 4
+    assert pt.progress() == 1.0 and pt.elapsed_sec() >= 0 and pt.eta_sec() == 0
+    pt.reset()
+    assert pt.current_step() == 0
+    mt = U.MetricTracker(0.5, True)
+    assert mt.update(4.0) == 4.0 and mt.improved() and mt.update(2.0) == 3.0 and mt.improved() and mt.update(9.0) == 6.0 and not mt.improved()
+    assert mt.best() == 3.0 and mt.value() == 6.0 and mt.steps() == 3 and mt.alpha() == 0.5
+    es = U.EarlyStopping(patience=2, min_delta=0.0)
+    for v in (1.0, 0.5, 0.6, 0.7):
+        es.step(v)
+    assert es.stopped() and es.best_epoch() == 1 and es.best_metric() == 0.5
+    es.reset()
+    assert not es.stopped() and es.best_metric() is None
+    lw = U.LearningRateWarmup(2.0, 4)
+    assert lw.get_lr(1) == 1.0 and lw.warmup_steps() == 4 and lw.target_lr() == 2.0
+    a, b = torch.nn.Parameter(torch.zeros(2)), torch.nn.Parameter(torch.zeros(2))
+    acc = U.GradientAccumulator(2)
+    opt = torch.optim.SGD([a, b], lr=1.0)
+    a.grad, b.grad = torch.tensor([1.0, 1.0]), torch.tensor([2.0, 2.0])
+    assert not acc.accumulate([a, b])
+    a.grad, b.grad = torch.tensor([3.0, 3.0]), torch.tensor([4.0, 4.0])
+    assert acc.accumulate([a, b]) and acc.ready() and acc.current_step() == 2 and acc.accumulation_steps() == 2
+    acc.apply_grads([a, b], opt)
+    assert a.data.tolist() == [-2.0, -2.0] and b.data.tolist() == [-3.0, -3.0] and acc.current_step() == 0
+    snap = U.ModelSnapshot(str(tmp_path / "snap.pt"))
+    assert snap.load(opt, [a, b]) is None
+    snap.save(opt, 7, 0.25, [a, b])
+    a.data.zero_()
+    assert snap.load(opt, [a, b]) == (7, 0.25) and a.data.tolist() == [-2.0, -2.0] and snap.path().endswith("snap.pt")
