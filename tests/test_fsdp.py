@@ -159,3 +159,53 @@ def test_activation_checkpoint_regions_measure_and_place():
     assert ActivationCheckpoint.estimate_layer_activations(2, 128, 64, 256) == 2 * 128 * (512 + 768) * 2
     ac.reset()
     assert ac.regions() == [] and ac.compute_overhead() == 0.0
+
+
+def test_offload_engine_and_manager_reference_verbs():
+    from transformers_fusion_b200.parallel.fsdp import CPUOffloadEngine, GradientCheckpointManager, ZeROOffloadManager
+    eng = CPUOffloadEngine(pool_bytes=1 << 20, device="cpu")
+    a, b = torch.arange(8.0), torch.arange(4.0) + 10
+    eng.offload_params([a, b])
+    keep = a.clone()
+    a.zero_()
+    eng.prefetch_params([0])
+    assert torch.equal(a, keep) and eng.bytes_offloaded() == 48 and eng.bytes_prefetched() == 32
+    b.zero_()
+    eng.prefetch_all()
+    assert b.tolist() == [10.0, 11.0, 12.0, 13.0]
+    dst = torch.zeros(4)
+    eng.async_transfer(dst, torch.ones(4))
+    eng.synchronize()
+    assert dst.sum() == 4 and not eng.is_busy() and eng.pending_transfers() == 0
+    comp, tr = torch.zeros(2), torch.zeros(2)
+    comp, tr = eng.double_buffer_transfer(comp, tr, torch.tensor([5.0, 6.0]))
+    assert comp.tolist() == [5.0, 6.0] and eng.pin_memory(a) is a and CPUOffloadEngine.unpin_memory(a) is a
+    eng.reset_stats(), eng.clear()
+    assert eng.bytes_offloaded() == 0 and eng.used == 0
+
+    class Opt:
+        m, v = torch.ones(6), torch.full((6,), 2.0)
+    mgr = ZeROOffloadManager(Opt(), CPUOffloadEngine(1 << 20, "cpu"))
+    assert mgr.bytes_on_device() == 48 and mgr.offload_ratio() == 0.0
+    m, v = torch.ones(3), torch.full((3,), 4.0)
+    mgr.offload_optimizer_state(m, v, 7)
+    m.zero_(), v.zero_()
+    assert mgr.bytes_offloaded() == 24 and 0 < mgr.offload_ratio() < 1
+    mgr.reload_optimizer_state(m, v, 7)
+    assert m.tolist() == [1.0] * 3 and v.tolist() == [4.0] * 3
+    g = torch.arange(10.0)
+    parts = [ZeROOffloadManager.shard_gradient(g, r, 4) for r in range(4)]
+    assert [p.tolist() for p in parts] == [[0, 1, 2], [3, 4, 5], [6, 7, 8], [9, 0, 0]]
+    full = sum(ZeROOffloadManager.unshard_gradient(p, r, 4, 10) for r, p in enumerate(parts))
+    assert torch.equal(full, g)
+    mgr.reset_stats()
+    G = GradientCheckpointManager
+    G.reset_stats()
+    G.begin_checkpoint(1000)
+    assert G.in_checkpoint()
+    G.end_checkpoint()
+    G.begin_checkpoint(500), G.end_checkpoint(recomputed=False)
+    assert not G.in_checkpoint() and G.activations_saved() == 2 and G.activations_recomputed() == 1
+    assert G.memory_saved_bytes() == 1500 and G.compute_overhead() == 0.5
+    G.reset_stats()
+    assert G.activations_saved() == 0

@@ -451,6 +451,72 @@ class CPUOffloadEngine:
         if t is not None:
             self.used -= t.numel() * t.element_size()
 
+    # ---- the reference's verbs (include/quant/zero_optimizer.h: CPUOffloadEngine): parameters addressed by id, counters
+    def offload_single(self, param_id: int, t: torch.Tensor):
+        self.offload(f"param{int(param_id)}", t)
+        self._count("off", t)
+        self.__dict__.setdefault("_devs", {})[int(param_id)] = t
+
+    def offload_params(self, params):
+        """Copy every tensor of ``params`` (a list, ids = positions) to the host pool."""
+        for i, t in enumerate(params):
+            self.offload_single(i, t)
+
+    def prefetch_params(self, param_ids):
+        """Start bringing the listed parameters back into the tensors they were offloaded from."""
+        devs = self.__dict__.setdefault("_devs", {})
+        for i in param_ids:
+            self.fetch(f"param{int(i)}", devs.get(int(i)))
+            self._count("pre", self.host[f"param{int(i)}"])
+
+    def prefetch_all(self):
+        self.prefetch_params(sorted(self.__dict__.setdefault("_devs", {})))
+
+    def async_transfer(self, dst: torch.Tensor, src: torch.Tensor, param_id: int = -1):
+        """One copy on the transfer stream (either direction: host <-> device); ``synchronize`` makes it visible."""
+        if self.stream is not None:
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.stream):
+                dst.copy_(src, non_blocking=True)
+            self._pending = getattr(self, "_pending", 0) + 1
+        else:
+            dst.copy_(src)
+        self._count("off" if not dst.is_cuda else "pre", src)
+
+    def double_buffer_transfer(self, compute_buf: torch.Tensor, transfer_buf: torch.Tensor, src: torch.Tensor):
+        """Fill ``transfer_buf`` from ``src`` on the transfer stream while the caller computes on ``compute_buf``; returns
+        the pair swapped, ready for the next round (call ``synchronize`` before using the new compute buffer)."""
+        self.async_transfer(transfer_buf, src)
+        return transfer_buf, compute_buf
+
+    def pin_memory(self, t: torch.Tensor) -> torch.Tensor:
+        return t.pin_memory() if self.device.type == "cuda" and not t.is_pinned() else t
+
+    @staticmethod
+    def unpin_memory(t: torch.Tensor) -> torch.Tensor:
+        return t.clone() if t.is_pinned() else t               # an unpinned copy; the pinned block returns to the allocator
+
+    def _count(self, which: str, t: torch.Tensor):
+        k = "_bytes_off" if which == "off" else "_bytes_pre"
+        setattr(self, k, getattr(self, k, 0) + t.numel() * t.element_size())
+
+    def bytes_offloaded(self) -> int: return getattr(self, "_bytes_off", 0)
+    def bytes_prefetched(self) -> int: return getattr(self, "_bytes_pre", 0)
+
+    def pending_transfers(self) -> int:
+        if self.stream is not None and self.stream.query():
+            self._pending = 0
+        return getattr(self, "_pending", 0)
+
+    def is_busy(self) -> bool: return self.pending_transfers() > 0
+
+    def clear(self):
+        self.synchronize()
+        self.host, self.used, self._devs = {}, 0, {}
+
+    def reset_stats(self):
+        self._bytes_off = self._bytes_pre = 0
+
 
 class ZeROOffloadManager:
     """Keeps Adam's m and v of a flat optimizer on the host between steps."""
@@ -478,6 +544,57 @@ class ZeROOffloadManager:
         r = fn()
         self.to_host()
         return r
+
+    # ---- per-parameter form and gradient sharding (reference: ZeROOffloadManager, include/quant/zero_offload.h)
+    def offload_optimizer_state(self, m: torch.Tensor, v: torch.Tensor, param_idx: int):
+        self.engine.offload(f"m{param_idx}", m)
+        self.engine.offload(f"v{param_idx}", v)
+        self.engine.synchronize()
+        self._off = getattr(self, "_off", 0) + (m.numel() + v.numel()) * m.element_size()
+        self.__dict__.setdefault("_idx", set()).add(param_idx)
+
+    def reload_optimizer_state(self, m: torch.Tensor, v: torch.Tensor, param_idx: int):
+        self.engine.fetch(f"m{param_idx}", m)
+        self.engine.fetch(f"v{param_idx}", v)
+        self.engine.synchronize()
+        self.__dict__.setdefault("_idx", set()).discard(param_idx)
+
+    @staticmethod
+    def shard_gradient(grad: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+        """This rank's contiguous slice of a flattened gradient (zero-padded so that it divides evenly)."""
+        flat = grad.reshape(-1)
+        per = -(-flat.numel() // world_size)
+        lo = rank * per
+        out = torch.zeros(per, dtype=flat.dtype, device=flat.device)
+        n = max(0, min(per, flat.numel() - lo))
+        out[:n] = flat[lo:lo + n]
+        return out
+
+    @staticmethod
+    def unshard_gradient(local_grad: torch.Tensor, rank: int, world_size: int, numel: Optional[int] = None, group=None) -> torch.Tensor:
+        """All ranks' slices put back together (an all-gather when a process group is up; alone, the slice in its place)."""
+        if world_size > 1 and dist.is_initialized():
+            parts = [torch.empty_like(local_grad) for _ in range(world_size)]
+            dist.all_gather(parts, local_grad.contiguous(), group=group)
+            full = torch.cat(parts)
+        else:
+            full = torch.zeros(local_grad.numel() * world_size, dtype=local_grad.dtype, device=local_grad.device)
+            full[rank * local_grad.numel():(rank + 1) * local_grad.numel()] = local_grad
+        return full[:numel] if numel else full
+
+    def bytes_offloaded(self) -> int: return getattr(self, "_off", 0) if getattr(self, "_idx", None) else (self.engine.used if self.on_host else 0)
+
+    def bytes_on_device(self) -> int:
+        o = self.opt
+        tot = sum(t.numel() * t.element_size() for t in (getattr(o, "m", None), getattr(o, "v", None)) if t is not None)
+        return 0 if self.on_host else tot
+
+    def offload_ratio(self) -> float:
+        off, dev = self.bytes_offloaded(), self.bytes_on_device()
+        return off / max(1, off + dev)
+
+    def reset_stats(self):
+        self._off, self._idx = 0, set()
 
 
 ZeROOptimizer = ShardOptimizer
@@ -513,6 +630,43 @@ class GradientCheckpointManager:
         """Extra forward FLOPs as a fraction of one forward pass."""
         tot = sum(self.flops)
         return sum(f for f, c in zip(self.flops, self.checkpointed) if c) / tot if tot else 0.0
+
+    # ---- run-time accounting (reference: GradientCheckpointManager statics, include/quant/zero_offload.h:11-22)
+    _depth, _saved, _recomputed, _bytes = 0, 0, 0, 0
+
+    @classmethod
+    def begin_checkpoint(cls, activation_bytes: int = 0):
+        """A checkpointed region starts: its activations (``activation_bytes``) are dropped and recomputed in backward."""
+        cls._depth += 1
+        cls._saved += 1
+        cls._bytes += int(activation_bytes)
+
+    @classmethod
+    def end_checkpoint(cls, recomputed: bool = True):
+        if cls._depth > 0:
+            cls._depth -= 1
+            cls._recomputed += 1 if recomputed else 0
+
+    @classmethod
+    def in_checkpoint(cls) -> bool: return cls._depth > 0
+
+    @classmethod
+    def activations_saved(cls) -> int: return cls._saved
+
+    @classmethod
+    def activations_recomputed(cls) -> int: return cls._recomputed
+
+    @classmethod
+    def memory_saved_bytes(cls) -> int: return cls._bytes
+
+    @classmethod
+    def compute_overhead(cls) -> float:
+        """Extra forward passes per region entered."""
+        return cls._recomputed / cls._saved if cls._saved else 0.0
+
+    @classmethod
+    def reset_stats(cls):
+        cls._depth = cls._saved = cls._recomputed = cls._bytes = 0
 
     def apply(self, model):
         """Sets the per-model switch when every layer is marked (the dense model recomputes all layers or none) and
