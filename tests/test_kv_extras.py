@@ -112,3 +112,35 @@ def test_q4_kv_cache_lloyd_max_codebooks():
     assert c.max_seq_len() == 128 and c.get_all(0)[0].shape[2] == 13
     c.clear()
     assert c.context_len() == 0
+
+
+def test_memory_efficient_attention_backward_and_stats():
+    import math
+    import torch
+    from transformers_fusion_b200.inference.speculative_extras import MemoryEfficientAttention
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(2, 3, 20, 8, generator=g) for _ in range(3))
+    mea = MemoryEfficientAttention(block_q=8, block_k=4)
+    with torch.no_grad():
+        out = mea.forward(q, k, v)
+    st = mea.last_softmax_stats()
+    assert st["num_blocks"] > 0 and st["sum_val"] >= 1.0 and math.isfinite(st["max_val"])
+    qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+    s = (qd @ kd.transpose(-1, -2)) / math.sqrt(8)
+    s = s.masked_fill(torch.ones(20, 20, dtype=torch.bool).triu(1), float("-inf"))
+    ref = torch.softmax(s, -1) @ vd
+    assert torch.allclose(out, ref, atol=1e-5)
+    go = torch.randn(ref.shape, generator=g)
+    ref.backward(go)
+    dq, dk, dv = mea.backward(go, q, k, v)
+    assert torch.allclose(dq, qd.grad, atol=1e-4) and torch.allclose(dk, kd.grad, atol=1e-4) and torch.allclose(dv, vd.grad, atol=1e-4)
+    # one tile of the running soft-max, twice, equals the soft-max over both key blocks
+    sc = torch.randn(5, 6, generator=g)
+    vv = torch.randn(6, 4, generator=g)
+    m, l, o = torch.full((5,), -float("inf")), torch.zeros(5), torch.zeros(5, 4)
+    for a in (0, 3):
+        m, l, o = MemoryEfficientAttention.online_softmax_tile(sc[:, a:a + 3], m, l, o, vv[a:a + 3])
+    assert torch.allclose(o / l[:, None], torch.softmax(sc, -1) @ vv, atol=1e-6)
+    mea.set_config(block_size_q=16, max_context_tokens=1 << 10)
+    assert mea.config() == {"block_size_q": 16, "block_size_kv": 4, "max_context_tokens": 1024}
+    assert mea.forward_memory_bytes(1, 8, 4096, 64) < 4096 * 4096 * 4 * 8 and mea.backward_memory_bytes(1, 8, 4096, 64) > mea.forward_memory_bytes(1, 8, 4096, 64) / 4

@@ -162,6 +162,8 @@ class MemoryEfficientAttention:
 
     def _run(self, q, k, v, causal, window, n_global, mask):
         S, Sk, d = q.shape[-2], k.shape[-2], q.shape[-1]
+        if not torch.is_grad_enabled():
+            self._stats = {"max_val": -float("inf"), "sum_val": 0.0, "num_blocks": 0}
         if max(S, Sk) > self.max_context_tokens:
             raise ValueError(f"context of {max(S, Sk)} tokens exceeds the limit of {self.max_context_tokens}")
         scale = 1.0 / math.sqrt(d)
@@ -200,6 +202,11 @@ class MemoryEfficientAttention:
                     acc = acc * corr[..., None] + p @ v[..., k0:k1, :].float()
                     m = m_new
             out[..., q0:q0 + self.bq, :] = acc / l.clamp(min=1e-30)[..., None]
+            if not torch.is_grad_enabled():
+                st = self.__dict__.setdefault("_stats", {"max_val": -float("inf"), "sum_val": 0.0, "num_blocks": 0})
+                st["max_val"] = max(st["max_val"], float(m[torch.isfinite(m)].max()) if torch.isfinite(m).any() else st["max_val"])
+                st["sum_val"] = float(l.mean())
+                st["num_blocks"] += sum(-(-(b - a) // self.bk) for a, b in ranges)
         return out.to(q.dtype)
 
     def forward(self, q, k, v, causal: bool = True, mask: Optional[torch.Tensor] = None):
@@ -207,6 +214,43 @@ class MemoryEfficientAttention:
 
     def forward_block_sparse(self, q, k, v, window: int = 1024, n_global: int = 0, causal: bool = True):
         return self._run(q, k, v, causal, window, n_global, None)
+
+    # ---- backward, statistics and estimates (reference: MemoryEfficientAttention, include/quant/zero_optimizer.h:274-350)
+    def config(self) -> dict:
+        return {"block_size_q": self.bq, "block_size_kv": self.bk, "max_context_tokens": self.max_context_tokens}
+
+    def set_config(self, block_size_q: Optional[int] = None, block_size_kv: Optional[int] = None, max_context_tokens: Optional[int] = None):
+        self.bq, self.bk = block_size_q or self.bq, block_size_kv or self.bk
+        self.max_context_tokens = max_context_tokens or self.max_context_tokens
+
+    def backward(self, grad_output, q, k, v, causal: bool = True, mask: Optional[torch.Tensor] = None):
+        """(dq, dk, dv) by recomputation: the forward is run again tile by tile under autograd (nothing of the first
+        forward pass is kept), so the memory stays O(S * d)."""
+        qd, kd, vd = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        with torch.enable_grad():
+            out = self._run(qd, kd, vd, causal, 0, 0, mask)
+        dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), grad_output.float())
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+    @staticmethod
+    def online_softmax_tile(scores, row_max, row_sum, output, v_tile):
+        """One tile of the running soft-max: ``scores`` [rows, keys] of a key block and its values ``v_tile`` [keys, d]
+        are folded into the running (row_max, row_sum, unnormalised output); returns the three updated tensors."""
+        m_new = torch.maximum(row_max, scores.amax(-1))
+        p = torch.exp(scores - m_new[..., None])
+        corr = torch.exp(row_max - m_new)
+        return m_new, row_sum * corr + p.sum(-1), output * corr[..., None] + p @ v_tile
+
+    def last_softmax_stats(self) -> dict:
+        """{max_val, sum_val, num_blocks} of the most recent forward (largest row maximum, mean row sum, key tiles visited)."""
+        return dict(getattr(self, "_stats", {"max_val": 0.0, "sum_val": 0.0, "num_blocks": 0}))
+
+    def forward_memory_bytes(self, B: int, H: int, N: int, D: int, dtype_bytes: int = 2) -> int:
+        return B * self.memory_bytes(N, H, D, dtype_bytes)["tiled"]
+
+    def backward_memory_bytes(self, B: int, H: int, N: int, D: int, dtype_bytes: int = 2) -> int:
+        """Recomputation keeps the inputs, their gradients and one tile's intermediates twice (forward + its adjoint)."""
+        return B * H * (6 * N * D * max(dtype_bytes, 4) + 2 * (self.bq * self.bk * 4 + self.bq * D * 4))
 
     def memory_bytes(self, seq: int, heads: int, dim: int, dtype_bytes: int = 2) -> Dict[str, int]:
         """Working set of the tiled form against the naive score matrix."""
