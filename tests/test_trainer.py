@@ -240,3 +240,50 @@ def test_loss_helpers_and_scale_rule():
     avg = t.ema.shadow.clone()
     t.ema_apply()
     assert T.equal(t.model.flat.params, avg) and T.equal(t.ema.shadow, avg) and t.ema_enabled()
+
+
+def test_dataloader_shuffle_augmentation_curriculum_and_streaming(tmp_path):
+    import torch as T
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    from transformers_fusion_b200.trainer.trainer import DataLoader, ModelEMA
+    from transformers_fusion_b200.utils.data import StreamingDataLoader
+    dl = DataLoader(tokens=T.arange(2 * 8 * 10 + 1), batch_size=2, seq_length=8)
+    assert dl.num_batches() == 10 and dl.batch_size() == 2 and dl.seq_length() == 8 and dl.has_next()
+    plain = [int(dl.next_batch()[0][0, 0]) for _ in range(10)]
+    assert plain == list(range(0, 160, 16)) and not dl.has_next()
+    dl.shuffle(epoch=1)
+    shuffled = [int(dl.next_batch_with_labels()[0][0, 0]) for _ in range(10)]
+    assert sorted(shuffled) == plain and shuffled != plain
+    dl.shuffle(epoch=1)
+    assert [int(dl.next_batch()[0][0, 0]) for _ in range(10)] == shuffled                # same epoch, same order
+    dl = DataLoader(tokens=T.arange(2 * 8 * 10 + 1), batch_size=2, seq_length=8)
+    dl.set_augmentation(mask_prob=0.5, replace_prob=0.25, mask_id=999, vocab_size=50, seed=3)
+    ids, lab = dl.next_batch()
+    assert (ids == 999).any() and (ids != 999).any() and T.equal(lab[0], T.arange(1, 9))  # labels are untouched
+    dl.set_augmentation()
+    dl.set_curriculum(total_epochs=4, min_seq_length=2)
+    assert dl.effective_seq_length() == 2
+    _, lab = dl.next_batch()
+    assert (lab[:, 2:] == -100).all() and (lab[:, :2] >= 0).all()
+    dl.curriculum_step(2)
+    assert dl.effective_seq_length() == 5
+    dl.curriculum_step(9)
+    assert dl.effective_seq_length() == 8 and (dl.next_batch()[1] >= 0).all()
+    (tmp_path / "s.txt").write_text("hello streaming loader\n" * 40)
+    sl = StreamingDataLoader(ByteTokenizer(), [str(tmp_path / "s.txt")], 2, 8, prefetch=2)
+    first = sl.next_batch()
+    assert first[0].shape == (2, 8) and sl.batch_size() == 2 and sl.seq_length() == 8 and sl.num_batches() >= 1
+    n = 1
+    while sl.next_batch() is not None:
+        n += 1
+    assert n > 3 and sl.next_batch() is None
+    sl.reset()
+    again = sl.next_batch()
+    assert T.equal(again[0], first[0])
+    sl.close()
+    t = _tiny_trainer()
+    ema = ModelEMA(t.model.flat, 0.5)
+    t.model.flat.params.add_(1.0)
+    ema.update()
+    ema.set_decay(0.9)
+    assert ema.decay == 0.9 and T.allclose(ema.shadow, t.model.flat.params.float() - 0.5)

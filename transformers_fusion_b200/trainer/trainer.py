@@ -101,13 +101,73 @@ class DataLoader:
     def reset(self):
         self.offset = 0
 
+    # ---- the reference's verbs (include/quant/trainer.h:78-159)
+    def num_batches(self) -> int: return len(self)
+    def batch_size(self) -> int: return self.B
+    def seq_length(self) -> int: return self.S
+    def has_next(self) -> bool: return self.offset < len(self)
+
+    def shuffle(self, epoch: int = 0):
+        """Visit the batches of this epoch in a permuted order (the same order for the same epoch on every rank)."""
+        n = len(self)
+        if self.tokens is not None and n > 0:
+            self._order = torch.randperm(n, generator=torch.Generator().manual_seed(1000003 * (epoch + 1))).tolist()
+        self.offset = 0
+
+    def set_augmentation(self, mask_prob: float = 0.0, replace_prob: float = 0.0, mask_id: int = 0, vocab_size: int = 0, seed: int = 0):
+        """Token-level augmentation of the inputs: each position is masked with ``mask_prob`` (its label is kept, so the
+        model must recover it) or replaced by a random id with ``replace_prob``."""
+        self._aug = dict(mask_prob=mask_prob, replace_prob=replace_prob, mask_id=mask_id, vocab_size=vocab_size)
+        self._aug_gen = torch.Generator().manual_seed(seed)
+
+    def apply_augmentation(self, ids, labels):
+        a = getattr(self, "_aug", None)
+        if not a or (a["mask_prob"] <= 0 and a["replace_prob"] <= 0):
+            return ids, labels
+        r = torch.rand(ids.shape, generator=self._aug_gen).to(ids.device)
+        out = ids.clone()
+        out[r < a["mask_prob"]] = a["mask_id"]
+        rep = (r >= a["mask_prob"]) & (r < a["mask_prob"] + a["replace_prob"])
+        if a["vocab_size"] > 0 and bool(rep.any()):
+            out[rep] = torch.randint(0, a["vocab_size"], (int(rep.sum()),), generator=self._aug_gen).to(ids.device)
+        return out, labels
+
+    def set_curriculum(self, total_epochs: int, min_seq_length: int = 64):
+        """Sequence-length curriculum: batches start at ``min_seq_length`` tokens and grow linearly to the full length
+        over ``total_epochs`` (the batch keeps its shape; positions past the current length get label -100)."""
+        self._cur = dict(total=max(1, total_epochs), epoch=0, min_len=min_seq_length)
+
+    def curriculum_step(self, epoch: int):
+        if getattr(self, "_cur", None):
+            self._cur["epoch"] = epoch
+
+    def effective_seq_length(self) -> int:
+        c = getattr(self, "_cur", None)
+        if not c:
+            return self.S
+        t = min(1.0, c["epoch"] / c["total"])
+        return int(min(self.S, max(c["min_len"], round(c["min_len"] + t * (self.S - c["min_len"])))))
+
     def next_batch(self):
+        ids, labels = self._next_batch()
+        if getattr(self, "_cur", None) and self.effective_seq_length() < self.S:
+            labels = labels.clone()
+            labels[:, self.effective_seq_length():] = -100
+        if getattr(self, "_aug", None):
+            ids, labels = self.apply_augmentation(ids, labels)
+        return ids, labels
+
+    next_batch_with_labels = next_batch
+
+    def _next_batch(self):
         B, S = self.B, self.S
         if self.tokens is None:
             ids = torch.randint(0, self.synthetic[0], (B, S + 1), generator=self._gen)
         else:
             n = B * S
-            start = (self.offset * self.world + self.rank) * n
+            order = getattr(self, "_order", None)
+            slot = order[self.offset % len(order)] if order and self.offset < len(order) else self.offset
+            start = (slot * self.world + self.rank) * n
             if start + n + 1 > self.tokens.numel():
                 self.offset = 0
                 start = self.rank * n
@@ -136,6 +196,11 @@ class ModelEMA:
 
     def step(self):
         self.shadow.mul_(self.decay).add_(self.flat.params.float(), alpha=1 - self.decay)
+
+    update = step
+
+    def set_decay(self, d: float):
+        self.decay = float(d)
 
     def swap(self):
         cur = self.flat.params.float().clone()

@@ -549,6 +549,34 @@ class StreamingDataLoader:
                 return
             yield item[0].to(self.device, non_blocking=True), item[1].to(self.device, non_blocking=True)
 
+    # ---- the reference's verbs (include/quant/trainer.h:160-238)
+    def batch_size(self) -> int: return self.B
+    def seq_length(self) -> int: return self.S
+
+    def next_batch(self):
+        """The next (ids, labels) pair, or None when the stream has ended."""
+        if getattr(self, "_ended", False):
+            return None
+        item = self.q.get()
+        if item is None:
+            self._ended = True
+            return None
+        return item[0].to(self.device, non_blocking=True), item[1].to(self.device, non_blocking=True)
+
+    def num_batches(self) -> int:
+        """Estimate from the files' sizes (about one token per 4 bytes of text)."""
+        import os
+        return sum(os.path.getsize(p) for p in self.paths) // 4 // max(1, self.B * (self.S + 1))
+
+    def reset(self):
+        """Start the stream over: the worker is stopped and a new one reads the files from the beginning."""
+        self.close()
+        self.thread.join(timeout=5)
+        self.q = queue.Queue(maxsize=self.q.maxsize)
+        self._stop, self._ended = False, False
+        self.thread = threading.Thread(target=self._work, daemon=True)
+        self.thread.start()
+
     def close(self):
         self._stop = True
         while not self.q.empty():
