@@ -165,3 +165,35 @@ def test_inferno():
     with pytest.raises(ZeroDivisionError):
         bad.result(5)
     q.stop()
+
+
+def test_world_model_reference_verbs():
+    from transformers_fusion_b200.agi.world_model import Transition, WorldModel
+    wm = WorldModel(discount=0.9)
+    wm.train_on_transitions([Transition("a", "go", "b", 1.0), Transition("b", "go", "c", 5.0), Transition("a", "stay", "a", 0.1),
+                             Transition("b", "stay", "b", 0.0), Transition("a", "go", "b", 1.0)])
+    assert wm.simulate_step("a", "go") == "b" and wm.predict_reward("a", "go") == 1.0 and len(wm.get_transition_buffer()) == 5
+    traj = wm.simulate_trajectory("a", ["go", "go", "go"])
+    assert [t.next_state for t in traj] == ["b", "c"] and traj[1].reward == 5.0
+    plan = wm.beam_search_plan("a", 2, beam_width=4)
+    assert plan.actions == ["go", "go"] and abs(plan.expected_return - (1.0 + 0.9 * 5.0)) < 1e-9 and wm.plan_actions("a", 2) == ["go", "go"]
+    mpc = wm.model_predictive_control("a", 2, n_samples=40)
+    assert mpc.actions == ["go", "go"]
+    wm.set_current_state("a")
+    assert wm.get_current_state() == "a" and wm.plan(2) == ["a", "b", "c"]
+    pr, unc = wm.predict_with_uncertainty("a", "go")
+    assert pr.next_state == "b" and unc.epistemic_uncertainty < wm.estimate_uncertainty("zz", "go").epistemic_uncertainty
+    assert unc.ensemble_size == 5 and unc.disagreement_magnitude == 0.0
+    assert wm.compute_ensemble_disagreement(["x", "x", "y", "z"]) == 0.5 and wm.compute_ensemble_disagreement([]) == 0.0
+    cf = wm.counterfactual_analysis("a", "stay", "go")
+    assert cf.difference == pytest.approx(0.9) and len(wm.batch_counterfactual("a", "stay", ["go", "stay"])) == 2
+    wm.store_state({"room": 1}, importance=0.2, key="room/kitchen", vector=[1.0, 0.0])
+    wm.store_state({"room": 2}, importance=0.9, key="room/garden", vector=[0.0, 1.0])
+    wm.store_state({"room": 3}, importance=0.1, key="hall", vector=[0.7, 0.7])
+    assert wm.retrieve_most_relevant("room/gar")["room"] == 2 and wm.retrieve_most_relevant([0.9, 0.1])["room"] == 1
+    wm.consolidate_memory(2)
+    assert len(wm.get_memory()) == 2 and all(e["state"]["room"] != 3 for e in wm.get_memory())
+    st = wm.get_stats()
+    assert st["total_transitions"] == 5 and st["planning_calls"] >= 3 and st["memory_entries"] == 2 and st["total_predictions"] >= 2
+    wm.reset_stats()
+    assert wm.get_stats()["planning_calls"] == 0
