@@ -197,3 +197,51 @@ def test_world_model_reference_verbs():
     assert st["total_transitions"] == 5 and st["planning_calls"] >= 3 and st["memory_entries"] == 2 and st["total_predictions"] >= 2
     wm.reset_stats()
     assert wm.get_stats()["planning_calls"] == 0
+
+
+def test_multi_agent_reference_verbs():
+    from transformers_fusion_b200.agi.multi_agent import AgentMessage, MultiAgentSystem
+    mas = MultiAgentSystem()
+    flaky_calls = []
+
+    def flaky(task):
+        flaky_calls.append(task)
+        raise RuntimeError("tool down")
+    a0 = mas.add_agent("supervisor", lambda t: f"ok:{t}")
+    a1 = mas.add_agent("worker", flaky)
+    a2 = mas.add_agent("worker", lambda t: f"done:{t}")
+    mas.configure("STAR")
+    assert mas.agent_count() == 3 and mas.get_agent(a1).role == "worker"
+    assert mas.communicate_direct(a0, a2, "hello") and not mas.communicate_direct(a1, a2, "side channel")      # spokes only reach the hub
+    mas.set_max_queue_size(2)
+    for i in range(4):
+        mas.send_message(AgentMessage(a0, a2, "t", f"m{i}"))
+    got = mas.receive_messages(a2)
+    assert [m.content for m in got] == ["m2", "m3"] and mas.receive_messages(a2) == [] and len(mas.get_histories()) == 5
+    mas.configure("RING")
+    assert mas.communicate_direct(a1, a2, "neighbour")
+    plan = mas.create_plan("load the data; clean it, then train the model. evaluate", 4)
+    assert plan.high_level_steps == ["load the data", "clean it", "train the model", "evaluate"] and len(mas.get_ready_subtasks()) == 1
+    assert mas.get_task_status(plan.subtask_ids[0]) == "pending" and mas.get_task_status(99) == "unknown"
+    mas.assign_subtask(plan.subtask_ids[0], a1)                        # the flaky agent gets the first step
+    assert mas.get_task_status(plan.subtask_ids[0]) == "assigned"
+    assert mas.execute_plan(plan, max_rounds=12) and plan.completed and mas.get_plan_progress(plan) == 1.0
+    assert flaky_calls and mas.get_metrics(a1).tasks_failed >= 1 and mas.subtasks[plan.subtask_ids[0]].result.startswith(("ok:", "done:"))
+    assert len(mas.search_blackboard("subtask/")) == 4 and mas.read_blackboard("subtask/0") != "" and mas.read_blackboard("nope") == ""
+    mas.write_blackboard("note", "v1", a0), mas.write_blackboard("note", "v2", a2)
+    assert mas.supervisor_resolve_conflicts() == ["note"]
+    mas.cleanup_blackboard()
+    assert all(k.startswith("plan/") for k in mas.blackboard)
+    mas.submit_vote(a0, "ship", True, 0.9, "tests pass"), mas.submit_vote(a1, "ship", False, 0.2), mas.submit_vote(a2, "ship", True, 0.8)
+    assert mas.check_consensus(0.6) and len(mas.get_votes()) == 3
+    mas.reset_votes()
+    assert not mas.check_consensus()
+    t = mas.assign_task_to_role("worker", "extra job")
+    assert mas.subtasks[t].assigned_to in (a1, a2) and mas.run_episode(3) >= 1 and mas.get_task_status(t) == "done"
+    mas.update_metrics(a2)
+    assert not mas.get_agent(a2).busy and "agent 2 (worker)" in mas.metrics_summary() and len(mas.get_all_metrics()) == 3
+    mas.supervisor_escalate("budget exceeded")
+    assert mas.escalations == ["budget exceeded"] and mas.search_blackboard("escalation/")
+    t2 = mas.assign_task(a2, "last job")
+    mas.remove_agent(a2)
+    assert mas.agent_count() == 2 and mas.subtasks[t2].assigned_to == -1 and mas.run_round(3)
