@@ -245,3 +245,36 @@ def test_multi_agent_reference_verbs():
     t2 = mas.assign_task(a2, "last job")
     mas.remove_agent(a2)
     assert mas.agent_count() == 2 and mas.subtasks[t2].assigned_to == -1 and mas.run_round(3)
+
+
+def test_self_eval_suite_reference_verbs():
+    import re
+    from transformers_fusion_b200.agi.self_eval import SelfEvalSuite
+
+    def solver(prompt):                                   # answers the generated benchmarks exactly
+        nums = list(map(int, re.findall(r"\d+", prompt.split("(A)")[0] if "(A)" in prompt else prompt)))
+        if "(A)" not in prompt:
+            return str(sum(nums[:2])) if len(nums) >= 2 else "0"
+        a, b = nums[:2]
+        right = a * b if "times" in prompt.lower() else (a + b if "plus" in prompt.lower() else max(a, b))
+        opts = dict(re.findall(r"\((\w)\) (\d+)", prompt))
+        return next((f"({l})" for l, v in opts.items() if int(v) == right), "(A)")
+    s = SelfEvalSuite(solver, confidence=lambda p, o: 0.95)
+    for fn in (s.run_accuracy_benchmark_mmlu, s.run_accuracy_benchmark_arc, s.run_accuracy_benchmark_gsm8k):
+        r = fn(12)
+        assert r["n_total"] == 12 and r["accuracy"] >= 0.9, r
+    cal = s.run_calibration_benchmark(20)
+    assert cal["bins"][9]["count"] == 20 and cal["ece"] == pytest.approx(abs(cal["bins"][9]["accuracy"] - 0.95))
+    assert SelfEvalSuite.compute_expected_calibration_error([{"count": 10, "accuracy": 0.5, "confidence": 0.9}, {"count": 0, "accuracy": 0, "confidence": 0}]) == pytest.approx(0.4)
+    c = s.run_consistency_benchmark("Ann has 3 apples and buys 4 more.", 4)
+    assert c["agreement"] == 1.0 and c["majority_answer"] == "7" and len(s.run_consistency_suite(3, 2)) == 3
+    rb = s.run_robustness_suite(3, 4)
+    assert len(rb) == 3 and all(0.0 <= r["stability"] <= 1.0 for r in rb)
+    assert s.run_speed_benchmark(5)["ops_per_sec"] > 0 and s.run_memory_benchmark(2)["peak_bytes"] > 0
+    assert s.run_pass_at_k("gsm8k", 2, 4)["pass_at_k"] == 1.0 and [r["k"] for r in s.run_pass_at_k_suite(5, n_problems=2)] == [1, 2, 5]
+    s.register_benchmark("mine", [("What is 1 plus 1? (A) 2 (B) 3", "(A)")])
+    assert s.run_accuracy_benchmark("mine", 5)["n_total"] == 1
+    rep = s.generate_report("v1", n_samples=6)
+    assert rep["version_id"] == "v1" and 0.8 < rep["overall_score"] <= 1.0 and s.get_latest_report() is rep and len(s.get_report_history()) == 1
+    weak = SelfEvalSuite(lambda p: "no idea")
+    assert weak.run_accuracy_benchmark_gsm8k(5)["accuracy"] == 0.0
