@@ -278,3 +278,42 @@ def test_self_eval_suite_reference_verbs():
     assert rep["version_id"] == "v1" and 0.8 < rep["overall_score"] <= 1.0 and s.get_latest_report() is rep and len(s.get_report_history()) == 1
     weak = SelfEvalSuite(lambda p: "no idea")
     assert weak.run_accuracy_benchmark_gsm8k(5)["accuracy"] == 0.0
+
+
+def test_meta_cognition_reference_verbs():
+    from transformers_fusion_b200.agi.meta import FeedbackEntry, MetaCognitionEngine
+    m = MetaCognitionEngine()
+    chain = m.analyze_reasoning("What is the value of x?", "We set x = 3. Maybe the value matters. Then x = 4. So the answer is four.")
+    assert len(chain.steps) == 4 and chain.steps[1].confidence < chain.steps[0].confidence        # hedged step
+    assert m.find_first_error_step(chain) == 2 and "contradicts step 0" in m.diagnose_error(chain, 2)
+    assert m.calculate_chain_consistency(chain) < 1.0 and m.diagnose_error(chain, 9) == "no error step"
+    from transformers_fusion_b200.agi.meta import ReasoningStep
+    assert not m.check_step_consistency(ReasoningStep(0, "the sky is blue"), ReasoningStep(1, "the sky is not blue"))
+    assert m.check_step_consistency(ReasoningStep(0, "the sky is blue"), ReasoningStep(1, "grass is green"))
+    for i in range(20):
+        m.record_confidence(0.9, i % 2 == 0, "math")
+    assert m.get_expected_calibration_error() == pytest.approx(0.4) and len(m.get_calibration_bins(5)) == 5
+    assert m.get_current_confidence() == pytest.approx(0.5) and len(m.get_confidence_history()) == 20      # calibrated down from 0.9
+    d = m.decompose("collect the logs; parse them, then write the report", 5)
+    assert len(d.subgoals) == 3 and m.get_ready_subgoals(d) == [d.subgoals[0]] and not m.check_subgoal_completion(d)
+    m.complete(d.subgoals[0])
+    assert m.get_ready_subgoals(d) == [d.subgoals[1]]
+    for g in d.subgoals[1:]:
+        m.complete(g)
+    assert m.check_subgoal_completion(d) and m.goals[d.root].done
+    assert m.select_strategy("solve 12 * 7", 0.3) == "CHAIN_OF_THOUGHT" and m.select_strategy("solve 12 * 7", 0.6) == "VERIFY_THEN_ANSWER"
+    assert m.select_strategy("say hello", 0.1) == "DIRECT" and m.select_strategy("anything", 0.9) == "DECOMPOSE"
+    for ok in (False, False, True):
+        m.record_feedback(FeedbackEntry("calculate 3 + 4", "DIRECT", 1.0 if ok else 0.0, ok, "" if ok else "arithmetic slip"))
+    m.record_feedback(FeedbackEntry("solve 9 - 2", "VERIFY_THEN_ANSWER", 0.9, True))
+    assert m.get_best_strategy_for_task_type("math") == "VERIFY_THEN_ANSWER" and m.select_strategy("solve 1 + 1", 0.1) == "VERIFY_THEN_ANSWER"
+    pats = m.extract_improvement_patterns()
+    assert "recurring failure: arithmetic slip (x2)" in pats and any("DIRECT fails" in p for p in pats)
+    assert "4 tasks, 2 succeeded" in m.generate_feedback_summary() and len(m.get_recent_feedback(2)) == 2
+    a = m.assess_self(10)
+    assert a.overconfidence == pytest.approx(0.4) and any("recurring" in i for i in a.insights)
+    ins = m.generate_insight("why is the sky blue", "Because of scattering. It is blue = 1. It is blue = 2.")
+    assert ins["task_type"] == "explanation" and ins["first_error_step"] == 2 and ins["consistency"] < 1
+    assert len(m.get_history()) >= 2
+    m.reset()
+    assert m.get_history() == [] and m.generate_feedback_summary() == "no feedback recorded"
