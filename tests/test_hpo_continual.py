@@ -98,3 +98,45 @@ def test_projection_watchdog_entropy():
     for i in range(5):
         rb.add(i, -i)
     assert rb.size() == 3 and rb.should_replay(4) and not rb.should_replay(3) and len(rb.sample_batch(2)[0]) == 2
+
+
+def test_nas_engine_reference_verbs(tmp_path):
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.trainer.hpo_nas import Architecture, HardwareConstraints, NASConfig, NASEngine
+    target = 24 * 1024 * 1024
+    fit = lambda a: -abs(math.log(a.param_count / target))                # best: about 24 M parameters
+    nas = NASEngine(fit, seed=3)
+    nas.set_search_config(NASConfig(population=10, generations=6))
+    nas.set_hardware_constraints(HardwareConstraints(enabled=True, max_params=10**9, target_memory_bytes=10**10, target_latency_ms=1e6))
+
+    class M:
+        cfg = TransformerConfig(vocab_size=1000, hidden_size=256, num_layers=4, num_heads=4, ffn_hidden_size=512, max_seq_len=64)
+    nas.set_model(M())
+    pop = nas.initialize_population(5)
+    assert len(pop) == 5 and (pop[0].hidden_size, pop[0].num_layers) == (256, 4)
+    a = pop[0]
+    assert nas.mutate_add_layer(a).num_layers == 5 and nas.mutate_remove_layer(a).num_layers == 3 and nas.mutate_change_ffn(a).ffn_size != 512
+    assert nas.mutate_change_width(a).hidden_size != 256 and nas.mutate_change_heads(a).num_heads != 4 and nas.mutate_change_dropout(a).dropout != a.dropout
+    child = nas.crossover(pop[0], pop[1])
+    assert child.num_layers in (pop[0].num_layers, pop[1].num_layers) and child.hidden_size % child.num_heads == 0
+    for x in pop:
+        nas.evaluate(x)
+    assert nas.tournament_select(pop, 5) is max(pop, key=lambda x: x.score)
+    best = nas.search(population=10, generations=6)
+    assert best is nas.get_best_architecture() and abs(math.log(best.param_count / target)) < abs(math.log(pop[0].param_count / target))
+    front = nas.get_pareto_front()
+    assert front and front[0].score == best.score and all(f.score >= -10 for f in front)
+    assert nas.save_architectures(str(tmp_path / "a.json"), 3)
+    loaded = NASEngine.load_architectures(str(tmp_path / "a.json"))
+    assert len(loaded) == 3 and loaded[0].score == best.score and isinstance(loaded[0], Architecture)
+    assert nas.estimate_memory(4, 256, 512, 1000) == pop[0].memory_bytes and nas.estimate_latency_cycles(4, 256, 4) > 0
+    small, huge = nas.hardware_aware_score(pop[0]), None
+    nas.set_hardware_constraints(HardwareConstraints(enabled=True, max_params=1000, target_memory_bytes=10**10, target_latency_ms=1e6))
+    assert nas.hardware_aware_score(pop[0]) < small
+    nas2 = NASEngine(fit, seed=5)
+    d = nas2.darts_search(30)
+    first = nas2.history[0]
+    assert d.score >= first.score and nas2.darts_migrate(first, 1.0).num_layers == d.num_layers
+    n = len(nas2.history)
+    nas2.record_architecture(first)
+    assert len(nas2.history) == n + 1

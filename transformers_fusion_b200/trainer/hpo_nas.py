@@ -12,7 +12,7 @@ import json
 import math
 import random
 from dataclasses import asdict, dataclass, field
-from typing import Callable, List, Optional, Tuple
+from typing import Callable, List, Optional, Sequence, Tuple
 
 
 @dataclass
@@ -394,9 +394,11 @@ class NASEngine:
         self.history.append(a)
         return a.score
 
-    def search(self) -> Architecture:
+    def search(self, population: Optional[int] = None, generations: Optional[int] = None) -> Architecture:
         c = self.cfg
-        pop = [self.random_architecture() for _ in range(c.population)]
+        if population or generations:
+            c = NASConfig(**{**asdict(c), "population": population or c.population, "generations": generations or c.generations})
+        pop = self.initialize_population(c.population)
         for a in pop:
             self.score(a)
         for _ in range(c.generations):
@@ -409,6 +411,112 @@ class NASEngine:
                 children.append(child)
             pop = elite + children
         return max(pop, key=lambda a: a.score)
+
+    # ---- the reference's verbs (include/quant/hpo_nas.h: NASEngine) ------------------------------------------------
+    def set_search_config(self, cfg: NASConfig): self.cfg = cfg
+    def set_hardware_constraints(self, hw: HardwareConstraints): self.hw = hw
+
+    def set_model(self, model):
+        """Start the search around an existing model: its shape becomes the first member of every population."""
+        c = model.cfg
+        self.seed_arch = self.estimate(Architecture(id=-1, num_layers=c.num_layers, hidden_size=c.hidden_size, num_heads=c.num_heads,
+                                                    ffn_size=c.ffn_hidden_size, vocab_size=c.vocab_size), self.cfg.tflops, self.cfg.tokens)
+
+    def initialize_population(self, n: int) -> List[Architecture]:
+        seed = [Architecture(**asdict(self.seed_arch))] if getattr(self, "seed_arch", None) is not None else []
+        return seed + [self.random_architecture() for _ in range(n - len(seed))]
+
+    def mutate_add_layer(self, a): return self.mutate(a, NASMutateOp.ADD_LAYER)
+    def mutate_remove_layer(self, a): return self.mutate(a, NASMutateOp.REMOVE_LAYER)
+    def mutate_change_width(self, a): return self.mutate(a, NASMutateOp.CHANGE_WIDTH)
+    def mutate_change_heads(self, a): return self.mutate(a, NASMutateOp.CHANGE_HEADS)
+    def mutate_change_ffn(self, a): return self.mutate(a, NASMutateOp.CHANGE_FFN)
+    def mutate_change_dropout(self, a): return self.mutate(a, NASMutateOp.CHANGE_DROPOUT)
+
+    def crossover(self, a: Architecture, b: Architecture) -> Architecture:
+        """Each gene from one of the parents; the width is re-aligned to the chosen head count."""
+        pick = lambda x, y: x if self.rng.random() < 0.5 else y
+        heads = pick(a.num_heads, b.num_heads)
+        hd = max(16, pick(a.hidden_size // a.num_heads, b.hidden_size // b.num_heads))
+        c = Architecture(id=self._next, num_layers=pick(a.num_layers, b.num_layers), hidden_size=hd * heads, num_heads=heads,
+                         ffn_size=pick(a.ffn_size, b.ffn_size), dropout=pick(a.dropout, b.dropout), vocab_size=pick(a.vocab_size, b.vocab_size))
+        self._next += 1
+        return self.estimate(c, self.cfg.tflops, self.cfg.tokens)
+
+    def evaluate(self, a: Architecture) -> float:
+        return self.score(a)
+
+    def tournament_select(self, pop: Sequence[Architecture], k: int = 3) -> Architecture:
+        return max(self.rng.sample(list(pop), min(k, len(pop))), key=lambda x: x.score)
+
+    def hardware_aware_score(self, a: Architecture) -> float:
+        """Quality proxy minus the hardware penalty, without calling the (expensive) evaluation function: larger models
+        score higher with diminishing returns until a limit is crossed."""
+        self.estimate(a, self.cfg.tflops, self.cfg.tokens)
+        return math.log10(max(10.0, a.param_count)) - self.penalty(a)
+
+    def estimate_latency_cycles(self, depth: int, width: int, num_heads: int, clock_ghz: float = 1.9) -> int:
+        a = self.estimate(Architecture(id=-1, num_layers=depth, hidden_size=width, num_heads=num_heads, ffn_size=4 * width),
+                          self.cfg.tflops, self.cfg.tokens)
+        return int(a.latency_ms * 1e-3 * clock_ghz * 1e9)
+
+    def estimate_memory(self, depth: int, width: int, ffn_size: int, vocab_size: int = 32000) -> int:
+        return self.estimate(Architecture(id=-1, num_layers=depth, hidden_size=width, num_heads=max(1, width // 64), ffn_size=ffn_size,
+                                          vocab_size=vocab_size)).memory_bytes
+
+    def record_architecture(self, a: Architecture):
+        self.history.append(a)
+
+    def get_best_architecture(self) -> Optional[Architecture]:
+        return max(self.history, key=lambda a: a.score) if self.history else None
+
+    def get_pareto_front(self) -> List[Architecture]:
+        """Architectures not dominated in (score up, parameters down, latency down)."""
+        hist = list({a.id: a for a in self.history}.values())
+        dom = lambda x, y: x.score >= y.score and x.param_count <= y.param_count and x.latency_ms <= y.latency_ms and \
+            (x.score > y.score or x.param_count < y.param_count or x.latency_ms < y.latency_ms)
+        return sorted((a for a in hist if not any(dom(b, a) for b in hist)), key=lambda a: -a.score)
+
+    def save_architectures(self, path, top_k: int = 10) -> bool:
+        try:
+            best = sorted({a.id: a for a in self.history}.values(), key=lambda a: -a.score)[:top_k]
+            with open(path, "w") as f:
+                json.dump([asdict(a) for a in best], f, indent=1)
+            return True
+        except OSError:
+            return False
+
+    @staticmethod
+    def load_architectures(path) -> List[Architecture]:
+        with open(path) as f:
+            return [Architecture(**d) for d in json.load(f)]
+
+    # ---- differentiable-search flavour: a continuous relaxation over the same genes
+    def darts_evaluate(self, a: Architecture) -> float:
+        return self.score(a)
+
+    def darts_migrate(self, a: Architecture, alpha: float = 0.1) -> Architecture:
+        """One relaxed step: every gene moves by the fraction ``alpha`` towards the best architecture seen so far (then
+        snaps back to valid sizes)."""
+        best = self.get_best_architecture() or a
+        mix = lambda x, y: x + alpha * (y - x)
+        heads = max(1, int(round(mix(a.num_heads, best.num_heads))))
+        hd = max(16, int(round(mix(a.hidden_size / a.num_heads, best.hidden_size / best.num_heads) / 16)) * 16)
+        b = Architecture(id=self._next, num_layers=max(1, int(round(mix(a.num_layers, best.num_layers)))), hidden_size=hd * heads,
+                         num_heads=heads, ffn_size=max(64, int(round(mix(a.ffn_size, best.ffn_size) / 64)) * 64),
+                         dropout=mix(a.dropout, best.dropout), vocab_size=a.vocab_size)
+        self._next += 1
+        return self.estimate(b, self.cfg.tflops, self.cfg.tokens)
+
+    def darts_search(self, n_iterations: int = 50, alpha: float = 0.3) -> Architecture:
+        """Alternate a relaxed move towards the incumbent with a random mutation; keep whichever scores better."""
+        cur = self.initialize_population(1)[0]
+        self.darts_evaluate(cur)
+        for _ in range(n_iterations):
+            cand = self.mutate(self.darts_migrate(cur, alpha))
+            if self.darts_evaluate(cand) > cur.score:
+                cur = cand
+        return self.get_best_architecture()
 
     def to_transformer_config(self, a: Architecture):
         from ..models.config import TransformerConfig
