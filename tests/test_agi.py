@@ -317,3 +317,86 @@ def test_meta_cognition_reference_verbs():
     assert len(m.get_history()) >= 2
     m.reset()
     assert m.get_history() == [] and m.generate_feedback_summary() == "no feedback recorded"
+
+
+def test_core_classes_reference_verbs():
+    import torch
+    from transformers_fusion_b200.agi import core as A
+    rs = A.RollingStats()
+    for v in (1.0, 1.1, 0.9, 1.0, 1.05, 0.95, 1.0, 1.0, 1.02):
+        rs.update(v)
+    assert rs.is_anomalous(5.0) and not rs.is_anomalous(1.01) and rs.z_score(1.0) == pytest.approx(rs.zscore(1.0))
+    mon = A.SelfMonitor()
+    assert mon.get_confidence_stats() is mon.confidence_stats and mon.get_uncertainty_stats() is mon.uncertainty_stats
+    mc = A.MetaCognition()
+    mc.self_model_update("q", 0.9, True), mc.self_model_update("q", 0.9, False)
+    assert mc.get_self_model_accuracy() == 0.5
+    g = A.SafetyGuardrails()
+    g.set_paused(True)
+    assert g.is_paused()
+    h = A.HITL(lambda a: True)
+    h.request_approval("deploy"), h.pause()
+    assert h.is_paused() and not h.request_approval("again") and len(h.get_approval_history()) == 2
+    pe = A.PlanningEngine()
+    plan = pe.plan("read the file; parse it")
+    pe.execute(plan)
+    assert len(pe.get_execution_history()) == len(plan) >= 2
+    # self-improver knobs: the evaluation prefers a learning rate near 2e-4 and some dropout
+    score = lambda s: -abs(math.log(s["learning_rate"] / 2e-4)) - abs(s["dropout"] - 0.05)
+    imp = A.RecursiveSelfImprover(score)
+    assert imp.self_modify("training is slow and has reached a plateau") and imp.settings["learning_rate"] == pytest.approx(1.5e-4)
+    assert imp.self_modify("add dropout") and imp.settings["dropout"] == 0.05
+    assert not imp.self_modify("nothing to change here")
+    kept = dict(imp.settings)
+    assert not imp.self_modify("loss is unstable and diverging") and imp.settings == kept          # halving the rate scores worse: rolled back
+    imp.apply_pruning(0.02), imp.apply_perturbation(0.03)
+    assert imp.settings["prune_threshold"] == 0.02 and imp.settings["perturbation"] == 0.03
+    assert imp.adjust_format("memory bandwidth bound") == "q4" and imp.adjust_format("accuracy degraded") == "q8"
+    assert imp.evaluate_candidate({**imp.settings, "learning_rate": 2e-4}) > imp.evaluate_candidate(imp.settings)
+    sv = A.SelfVerifier()
+    assert sv.verify("what is 12 * 7", "12 * 7 = 84") and not sv.verify("what is 12 * 7", "12 * 7 = 85") and not sv.verify("x", "  ")
+    assert sv.verify("write code", "```python\nprint(sum(range(4)))\n```") and not sv.verify("write code", "```python\nraise SystemExit(3)\n```")
+    ec = sv.find_edge_cases("sort the list and divide by 10")
+    assert {"division by zero", "already sorted", "9", "10", "11", "empty input"} <= set(ec)
+    ex = A.CuriosityDrivenExplorer()
+    visits = ex.explore(12, ["a", "b", "c"], outcome=lambda k: {"a": 0.0, "b": 0.0, "c": 5.0}[k])
+    assert len(visits) == 12 and visits.count(2) > visits.count(0) and ex.intrinsic_reward("c") > ex.intrinsic_reward("a")
+    assert ex.intrinsic_reward(torch.ones(3)) > 0
+    learn_log = []
+    cl = A.ContinuousLearner(lambda b: learn_log.append(b) or 0.0, buffer_size=4)
+    cl.update("b1"), cl.update("b2")
+    skill = iter([1.0, 0.99, 0.5])
+    assert cl.prevent_forgetting(0.95, lambda: next(skill)) and cl.prevent_forgetting(0.95, lambda: next(skill))
+    n = len(learn_log)
+    assert not cl.prevent_forgetting(0.95, lambda: next(skill)) and len(learn_log) == n + 2        # the buffer was replayed
+    kd = A.KnowledgeDistillation(2.0, 0.5)
+    teacher, student = torch.nn.Linear(4, 3), torch.nn.Linear(4, 3)
+    data = [(torch.randn(8, 4), torch.randint(0, 3, (8,))) for _ in range(30)]
+    first = float(kd.loss(student(data[0][0]), teacher(data[0][0]).detach(), data[0][1]).detach())
+    assert kd.distill(data, 30, student, teacher) < first
+    po = A.PromptOptimizer(lambda p: float(len(p)))
+    assert po.evaluate("abc", "de") == 5.0
+    cot = A.ChainOfThought(lambda p: "therefore the answer is 4" if "Step" in p and "Final" not in p else "4")
+    assert cot.reason("2+2?", 5) == "4" and cot.get_chain() == ["therefore the answer is 4"]
+    tu = A.ToolUse()
+    tu.register("upper", lambda s: s.upper())
+    assert tu.call_tool("upper", "abc") == "ABC" and tu.call_tool("nope").startswith("error") and tu.get_available_tools() == ["upper"]
+    ms = A.MemorySystem(short_capacity=4)
+    ms.store("the cat sat on the mat"), ms.store("the cat sat on the mat!"), ms.store("kernels run on the gpu")
+    ms.consolidate()
+    assert len(ms.long) == 2 and ms.short == [] and ms.retrieve("gpu kernels", 1) == ["kernels run on the gpu"]
+    ms.store(torch.tensor([1.0, 0.0]), "east"), ms.store(torch.tensor([0.0, 1.0]), "north")
+    assert ms.retrieve(torch.tensor([0.9, 0.1]), 1) == ["east"]
+    eh = A.EvaluationHarness(lambda p: "4" if "2+2" in p else "?")
+    eh.register("tiny", [("2+2", "4"), ("3+3", "6")])
+    assert eh.evaluate("tiny")["accuracy"] == 0.5 and [r["benchmark"] for r in eh.evaluate_all()] == ["tiny"]
+    fw = A.Flywheel(eh, lambda failures: None)
+    fw.run([("2+2", "4"), ("3+3", "6")], max_iterations=3)
+    assert len(fw.get_history()) == 3 and fw.get_no_improvement_count() == 2 and fw.get_log_path() == ""
+    assert fw.self_play_for_test().startswith("iteration 0: accuracy")
+    cg = A.CodeGenSelfImprover()
+    assert cg.generate_kernel("no_such_op", 4) == "" and not cg.compile_and_test("") and not cg.replace_kernel("x", "")
+    ok_src = "__global__ void k(float* x) { x[threadIdx.x] += 1.0f; }\n"
+    assert cg.compile_and_test(ok_src) and not cg.compile_and_test("__global__ void k( {") and cg.replace_kernel("inc", ok_src)
+    assert cg.candidates["inc"] == ok_src
+    assert hasattr(A.HPOptimizer(), "population_based_training") and hasattr(A.NeuralArchitectureSearch(), "search")

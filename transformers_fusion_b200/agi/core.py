@@ -815,3 +815,304 @@ class NeuralArchitectureSearch:
 def _accepts(cls, name: str) -> bool:
     import inspect
     return name in inspect.signature(cls.__init__).parameters
+
+
+# =====================================================================================================================
+# The reference's verb names on the classes above (include/quant/agi.h)
+# =====================================================================================================================
+def _agi_api():
+    import difflib
+
+    def put(cls, **fns):
+        for name, fn in fns.items():
+            setattr(cls, name, fn)
+
+    # ---- RollingStats
+    put(RollingStats, update=RollingStats.add, z_score=RollingStats.zscore,
+        is_anomalous=lambda self, value, threshold=3.0: len(self.values) >= 8 and abs(self.zscore(value)) > threshold)
+
+    # ---- SelfMonitor / MetaCognition / guardrails / planning / human in the loop: accessors
+    put(SelfMonitor, get_confidence_stats=lambda self: self.confidence_stats, get_uncertainty_stats=lambda self: self.uncertainty_stats)
+    put(MetaCognition, get_self_model_accuracy=lambda self: self.self_model_accuracy)
+    put(SafetyGuardrails, set_paused=lambda self, p: setattr(self, "paused", bool(p)), is_paused=lambda self: getattr(self, "paused", False))
+    put(PlanningEngine, get_execution_history=lambda self: list(self.execution_history))
+    put(HITL, get_approval_history=lambda self: list(self.approval_history), is_paused=lambda self: self.paused)
+
+    # ---- RecursiveSelfImprover: the individual knobs
+    def adjust_lr(self, weakness: str = ""):
+        """Unstable / diverging -> halve the rate; slow / plateau -> raise it by half."""
+        w = weakness.lower()
+        f = 0.5 if any(k in w for k in ("unstable", "diverg", "nan", "spike", "overfit")) else (1.5 if any(k in w for k in ("slow", "plateau", "underfit")) else 1.0)
+        self.settings["learning_rate"] *= f
+        return self.settings["learning_rate"]
+
+    def apply_perturbation(self, magnitude: float = 0.01):
+        self.settings["perturbation"] = float(magnitude)
+
+    def apply_dropout(self, rate: float = 0.1):
+        self.settings["dropout"] = min(0.9, max(0.0, float(rate)))
+
+    def apply_pruning(self, threshold: float = 0.01):
+        self.settings["prune_threshold"] = max(0.0, float(threshold))
+
+    def adjust_format(self, analysis: str = ""):
+        """Pick the weight format the analysis calls for: memory-bound -> fewer bits, accuracy loss -> more bits."""
+        a = analysis.lower()
+        order = ["q2", "q4", "q8", "q16"]
+        cur = order.index(self.settings.get("format", "q8"))
+        if any(k in a for k in ("memory", "size", "bandwidth", "slow")):
+            cur = max(0, cur - 1)
+        elif any(k in a for k in ("accuracy", "quality", "precision", "degrad")):
+            cur = min(len(order) - 1, cur + 1)
+        self.settings["format"] = order[cur]
+        return order[cur]
+
+    def evaluate_candidate(self, candidate) -> float:
+        return float(self.evaluate(candidate if isinstance(candidate, dict) else self.settings))
+
+    def self_modify(self, analysis: str) -> bool:
+        """Apply the change an analysis in words asks for, keep it only when the evaluation improves (and the guard lets
+        the modification through); returns whether it was kept."""
+        before, base = dict(self.settings), self.evaluate(self.settings)
+        a = analysis.lower()
+        if "dropout" in a or "overfit" in a:
+            self.apply_dropout(min(0.5, self.settings["dropout"] + 0.05))
+        if "prun" in a or "sparse" in a:
+            self.apply_pruning(0.01)
+        if any(k in a for k in ("learning rate", "unstable", "diverg", "slow", "plateau")):
+            self.adjust_lr(analysis)
+        if "format" in a or "bits" in a or "memory" in a:
+            self.adjust_format(analysis)
+        if self.settings == before:
+            return False
+        score = self.evaluate(self.settings)
+        if score > base and self.guard.check_modification("training settings", str(self.settings)):
+            self.history.append({"score": score, **self.settings})
+            return True
+        self.settings = before
+        return False
+    put(RecursiveSelfImprover, adjust_lr=adjust_lr, apply_perturbation=apply_perturbation, apply_dropout=apply_dropout,
+        apply_pruning=apply_pruning, adjust_format=adjust_format, evaluate_candidate=evaluate_candidate, self_modify=self_modify)
+
+    # ---- CodeGenSelfImprover
+    def generate_kernel(self, op: str, M: int, N: int = 1, K: int = 1) -> str:
+        """CUDA source of a shape-specialised kernel for ``op`` from the kernel source generator ("" when the generator has
+        no template for it)."""
+        from ..trainer.code_gen import KernelType
+        name = op.upper()
+        if name not in KernelType.__members__:
+            return ""
+        try:
+            cands = self.gen.auto_optimize(KernelType[name], max(1, M * N), 1)
+        except ValueError:
+            return ""
+        return getattr(cands[0], "source", "") if cands else ""
+
+    def compile_and_test(self, code: str) -> bool:
+        """Does the source compile for sm_100a?  (nvcc -c into a scratch directory; no GPU is needed, nothing is run.)"""
+        import shutil
+        import subprocess
+        import tempfile
+        if not code.strip() or shutil.which("nvcc") is None:
+            return False
+        with tempfile.TemporaryDirectory() as d:
+            src = os.path.join(d, "k.cu")
+            open(src, "w").write(code)
+            r = subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-c", src, "-o", os.path.join(d, "k.o")],
+                               capture_output=True, text=True, timeout=300)
+            self.last_compile_log = r.stderr[-2000:]
+            return r.returncode == 0
+
+    def replace_kernel(self, op: str, new_code: str) -> bool:
+        """Register a candidate source for ``op`` (kept in memory; the framework's own kernels are built from the source
+        tree and are never overwritten by generated code)."""
+        if not self.compile_and_test(new_code):
+            return False
+        self.__dict__.setdefault("candidates", {})[op] = new_code
+        return True
+    put(CodeGenSelfImprover, generate_kernel=generate_kernel, compile_and_test=compile_and_test, replace_kernel=replace_kernel)
+
+    # ---- SelfVerifier
+    def verify(self, problem: str, solution: str) -> bool:
+        """Arithmetic claims ("12 * 7 = 84") are recomputed; code blocks must run in the sandbox; anything else passes only
+        when it is non-empty and does not contradict a number asked for in the problem."""
+        claims = re.findall(r"([-+*/().\d\s]+?)\s*=\s*(-?\d+(?:\.\d+)?)", solution)
+        checked = False
+        for expr, val in claims:
+            if re.search(r"\d\s*[-+*/]\s*\d", expr):
+                checked = True
+                try:
+                    if not self.verify_arithmetic(expr.strip(), float(val), 1e-6):
+                        return False
+                except (SyntaxError, ZeroDivisionError, ValueError):
+                    return False
+        m = re.search(r"```(?:python)?\n(.*?)```", solution, re.S)
+        if m:
+            checked = True
+            r_ = self.sandbox.compile_and_test(m.group(1))
+            if not (r_.compiled and r_.exit_code == 0):
+                return False
+        return checked or bool(solution.strip())
+
+    def find_edge_cases(self, solution: str) -> List[str]:
+        """Inputs worth trying against a solution, read off its text: boundaries of the numbers it mentions, empty / zero /
+        negative inputs, and the usual suspects of the constructs it uses."""
+        cases = ["empty input", "zero", "negative value"]
+        for n in sorted({int(x) for x in re.findall(r"\b\d{1,9}\b", solution)})[:4]:
+            cases += [f"{n - 1}", f"{n}", f"{n + 1}"]
+        if re.search(r"/|divide|ratio", solution, re.I):
+            cases.append("division by zero")
+        if re.search(r"\[|index|list|array", solution, re.I):
+            cases += ["single element", "index out of range"]
+        if re.search(r"sort|order|max|min", solution, re.I):
+            cases += ["all elements equal", "already sorted", "reverse sorted"]
+        if re.search(r"str|text|char", solution, re.I):
+            cases += ["non-ASCII text", "very long string"]
+        return list(dict.fromkeys(cases))
+    put(SelfVerifier, verify=verify, find_edge_cases=find_edge_cases)
+
+    # ---- CuriosityDrivenExplorer
+    def intrinsic_reward(self, state) -> float:
+        """Novelty of a state (a key, or a tensor / sequence hashed by its rounded content)."""
+        key = state if isinstance(state, str) else repr([round(float(v), 2) for v in torch.as_tensor(state).reshape(-1)[:16].tolist()])
+        return self.novelty(key)
+
+    def explore(self, n_steps: int, keys: Optional[Sequence] = None, outcome: Optional[Callable] = None) -> List[int]:
+        """Visit ``n_steps`` times the index of the most novel candidate among ``keys`` (default: the keys seen so far);
+        ``outcome(key)`` gives the observed value, the running mean of which is the prediction."""
+        keys = list(keys) if keys is not None else sorted(self.err)
+        if not keys:
+            return []
+        mean: Dict = {}
+        out = []
+        for _ in range(n_steps):
+            k = self.select(keys)
+            y = float(outcome(k)) if outcome else 0.0
+            self.observe(k, mean.get(k, 0.0), y)
+            mean[k] = 0.5 * mean.get(k, 0.0) + 0.5 * y
+            out.append(keys.index(k))
+        return out
+    put(CuriosityDrivenExplorer, intrinsic_reward=intrinsic_reward, explore=explore)
+
+    # ---- facades over the search engines
+    put(NeuralArchitectureSearch, search=lambda self, population=50, generations=20: self.engine.search(population, generations))
+
+    put(HPOptimizer, population_based_training=lambda self, n_population=8, n_generations=10:
+        self.engine.population_based_training(n_population, n_generations))
+
+    # ---- ContinuousLearner
+    def cl_update(self, new_data):
+        return self.learn(new_data)
+
+    def prevent_forgetting(self, threshold: float = 0.95, evaluate: Optional[Callable] = None) -> bool:
+        """True while the retained skill is at least ``threshold`` of its best value so far; when it drops below, the whole
+        replay buffer is trained on once.  ``evaluate()`` returns the skill (higher is better)."""
+        if evaluate is None:
+            return True
+        s = float(evaluate())
+        self.best_skill = max(getattr(self, "best_skill", s), s)
+        if s >= threshold * self.best_skill:
+            return True
+        for b in self.buffer:
+            self.train_step(b)
+        return False
+    put(ContinuousLearner, update=cl_update, prevent_forgetting=prevent_forgetting)
+
+    # ---- KnowledgeDistillation
+    def distill(self, data, steps: int, student=None, teacher=None, opt=None):
+        """``steps`` optimizer steps of the student on the distillation loss against the teacher's logits.  ``data``:
+        a loader with ``next_batch()`` or an iterable of (ids, labels); models map ids -> logits."""
+        student, teacher = student or self.student, teacher or self.teacher
+        opt = opt or torch.optim.Adam([p for p in student.parameters() if p.requires_grad], lr=1e-3)
+        it = iter(data) if not hasattr(data, "next_batch") else None
+        last = 0.0
+        for _ in range(steps):
+            ids, labels = data.next_batch() if it is None else next(it)
+            with torch.no_grad():
+                t_logits = teacher(ids)
+            loss = self.loss(student(ids), t_logits, labels)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            last = float(loss.detach())
+        return last
+    put(KnowledgeDistillation, distill=distill, student=None, teacher=None)
+
+    # ---- PromptOptimizer / ChainOfThought / ToolUse / MemorySystem / EvaluationHarness / Flywheel
+    def po_evaluate(self, prompt: str, task: str = "") -> float:
+        return float(self.score(prompt + task))
+    put(PromptOptimizer, evaluate=po_evaluate)
+
+    def reason(self, problem: str, max_steps: int = 10) -> str:
+        self.chain, answer = self.solve(problem, max_steps)
+        return answer
+    put(ChainOfThought, reason=reason, get_chain=lambda self: list(getattr(self, "chain", [])))
+
+    def call_tool(self, tool_name: str, args: str = "") -> str:
+        if tool_name not in self.tools:
+            return f"error: unknown tool {tool_name}"
+        try:
+            return str(self.tools[tool_name](args))
+        except Exception as e:
+            return f"error: {e}"
+    put(ToolUse, call_tool=call_tool, get_available_tools=lambda self: sorted(self.tools))
+
+    def mem_store(self, key, value=None):
+        """Text form: ``store(text)``.  Vector form: ``store(key_vector, value)`` for retrieval by similarity."""
+        if value is None:
+            return self.remember(str(key))
+        self.__dict__.setdefault("vectors", []).append((torch.as_tensor(key).float().reshape(-1), value))
+
+    def mem_retrieve(self, query, k: int = 5):
+        if isinstance(query, str):
+            return self.recall(query, k)
+        q = torch.as_tensor(query).float().reshape(-1)
+        vs = self.__dict__.get("vectors", [])
+        sims = [float(torch.nn.functional.cosine_similarity(q, kv, dim=0)) for kv, _ in vs]
+        return [vs[i][1] for i in sorted(range(len(vs)), key=lambda i: -sims[i])[:k]]
+
+    def consolidate(self, max_long: int = 1000):
+        """Short-term entries move to the long-term store; near-duplicates (difflib ratio > 0.9) are merged."""
+        self.long += self.short
+        self.short = []
+        kept: List[str] = []
+        for t in self.long:
+            if not any(difflib.SequenceMatcher(None, t, u).ratio() > 0.9 for u in kept[-50:]):
+                kept.append(t)
+        self.long = kept[-max_long:]
+    put(MemorySystem, store=mem_store, retrieve=mem_retrieve, consolidate=consolidate)
+
+    def eh_evaluate(self, benchmark_name: str, n_samples: int = 100) -> dict:
+        """Accuracy on a named benchmark: case sets registered with ``register(name, cases)``, else the generated stand-ins
+        of the self-evaluation suite."""
+        from .self_eval import _builtin_benchmark
+        cases = self.__dict__.get("benchmarks", {}).get(benchmark_name) or _builtin_benchmark(benchmark_name, n_samples)
+        rep = self.run(cases[:n_samples])
+        return {"benchmark": benchmark_name, "accuracy": rep["accuracy"], "samples": len(cases[:n_samples]), "failures": rep["failures"]}
+
+    def eh_register(self, name: str, cases):
+        self.__dict__.setdefault("benchmarks", {})[name] = list(cases)
+
+    def evaluate_all(self, n_samples: int = 20):
+        names = sorted(self.__dict__.get("benchmarks", {})) or ["mmlu", "arc", "hellaswag", "gsm8k"]
+        return [self.evaluate(n, n_samples) for n in names]
+    put(EvaluationHarness, evaluate=eh_evaluate, register=eh_register, evaluate_all=evaluate_all)
+
+    def get_no_improvement_count(self) -> int:
+        """Iterations at the end of the record whose accuracy did not beat the best before them."""
+        n, best = 0, -1.0
+        for it in self.iterations:
+            n = 0 if it["accuracy"] > best else n + 1
+            best = max(best, it["accuracy"])
+        return n
+
+    def self_play_for_test(self, cases=None) -> str:
+        """One evaluate-and-improve round on a tiny built-in case set; returns a one-line summary."""
+        cases = cases or [("2+2", "4"), ("3+5", "8")]
+        it = self.run(cases, max_iterations=1)
+        return f"iteration {it[-1]['iteration']}: accuracy {it[-1]['accuracy']:.2f}, failures {it[-1]['failures']}" if it else "no iteration ran"
+    put(Flywheel, get_history=lambda self: list(self.iterations), get_no_improvement_count=get_no_improvement_count,
+        get_log_path=lambda self: getattr(self, "log_path", ""), self_play_for_test=self_play_for_test)
+
+
+_agi_api()
