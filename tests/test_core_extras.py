@@ -171,3 +171,34 @@ def test_mapped_file_json_value_rate_limiter_and_aliases(tmp_path):
     from transformers_fusion_b200.agi.core import CodeGenSelfImprover, HPOptimizer, NeuralArchitectureSearch
     assert HPOptimizer().engine is not None and NeuralArchitectureSearch().engine is not None
     assert CodeGenSelfImprover().improve({"attention": 5.0}) is None     # hand-written kernels are not generated
+
+
+def test_json_node_accessors_and_inferno_units():
+    from transformers_fusion_b200.utils import core as C
+    from transformers_fusion_b200.utils.inferno import InfernoCounter
+    j = C.JsonValue.parse('{"n": 3, "f": 2.5, "s": "x", "b": true, "a": [1, "two", null], "o": {"k": 1}}')
+    assert j["n"].as_int_checked() == 3 and j["f"].as_float() == 2.5 and j["n"].as_float() == 3.0 and j["s"].as_string_checked() == "x"
+    assert j["b"].as_bool_checked() is True and j["missing"].is_null() and j.has("o") and not j.has("zz") and j["o"]["k"].int_val == 1
+    assert [v.type for v in j["a"].arr] == [C.JsonValue.INT, C.JsonValue.STRING, C.JsonValue.NUL] and j["a"][1].str_val == "two"
+    assert j["a"].at_or_null(9).is_null() and j["o"].obj["k"].as_int() == 1 and j["s"].is_string() and j["f"].is_number() and j["b"].is_bool()
+    with pytest.raises(IndexError):
+        j["a"][5]
+    with pytest.raises(TypeError):
+        j["s"].as_int_checked()
+    with pytest.raises(TypeError):
+        j["f"].as_int_checked()
+    assert j["s"].as_int() == 0 and j["n"].as_string() == "" and C.JsonValue.parse(j.to_string())["a"][0].as_int() == 1
+    bad, err = C.JsonValue.try_parse("{oops")
+    assert bad.is_null() and err and C.json_escape_string('a"b\n') == 'a\\"b\\n'
+    c = InfernoCounter()
+    c.record("Q_4", 1000), c.record(9, 1000), c.record_mix("Q_MX_8_5", 1000), c.record(99, 5), c.record_iw(2.0, 1000)
+    assert c.mean_info_weight() == pytest.approx((8.0 + 1.0 + 32.0 / 8.5 + 2.0) / 4) and c.ops == 8000
+    c.ns = int(1e6)                                          # one millisecond
+    assert c.elapsed_sec() == 1e-3 and c.gflops() == pytest.approx(8000 / 1e-3 / 1e9) == c.effective_gflops()
+    raw = c.raw_ops_per_sec()
+    assert c.minferno() == pytest.approx(raw / 1e6) and c.uinferno() == pytest.approx(raw / 1e9) and c.ninferno() == pytest.approx(raw / 1e12)
+    assert c.pinferno() == pytest.approx(raw / 1e15) and c.best_unit() == "fInferno" and c.best_value() == pytest.approx(raw / 1e21 * 1e12)
+    c.ops, c.ns = int(4e24), int(1e9)
+    assert c.best_unit() == "Inferno" and c.best_value() >= 1.0
+    c.reset()
+    assert c.ops == 0 and c.mean_info_weight() == 1.0

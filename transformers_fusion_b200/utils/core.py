@@ -336,6 +336,79 @@ class JsonValue:
     def is_object(self): return isinstance(self.value, dict)
     def is_array(self): return isinstance(self.value, list)
 
+    # ---- node-level accessors of the reference (include/quant/json_parser.h): a JsonValue wraps ONE node
+    NUL, BOOL, INT, FLOAT, STRING, ARRAY, OBJECT = range(7)
+
+    @property
+    def type(self) -> int:
+        v = self.value
+        return (self.NUL if v is None else self.BOOL if isinstance(v, bool) else self.INT if isinstance(v, int) else
+                self.FLOAT if isinstance(v, float) else self.STRING if isinstance(v, str) else self.ARRAY if isinstance(v, list) else self.OBJECT)
+
+    def is_null(self): return self.value is None
+    def is_bool(self): return isinstance(self.value, bool)
+    def is_number(self): return isinstance(self.value, (int, float)) and not isinstance(self.value, bool)
+    def is_string(self): return isinstance(self.value, str)
+
+    def as_bool(self) -> bool: return self.value if isinstance(self.value, bool) else False
+    def as_int(self) -> int: return int(self.value) if self.is_number() else 0
+    def as_float(self) -> float: return float(self.value) if self.is_number() else 0.0
+    def as_string(self) -> str: return self.value if isinstance(self.value, str) else ""
+
+    def _checked(self, ok: bool, what: str):
+        if not ok:
+            raise TypeError(f"JsonValue: not {what}")
+        return self.value
+
+    def as_bool_checked(self) -> bool: return self._checked(self.is_bool(), "a bool")
+    def as_int_checked(self) -> int: return self._checked(self.type == self.INT, "an int")
+    def as_float_checked(self) -> float: return float(self._checked(self.is_number(), "a number"))
+    def as_string_checked(self) -> str: return self._checked(self.is_string(), "a string")
+
+    @property
+    def bool_val(self): return self.as_bool()
+    @property
+    def int_val(self): return self.as_int()
+    @property
+    def float_val(self): return self.as_float()
+    @property
+    def str_val(self): return self.as_string()
+    @property
+    def arr(self): return [JsonValue(v) for v in self.value] if isinstance(self.value, list) else []
+    @property
+    def obj(self): return {k: JsonValue(v) for k, v in self.value.items()} if isinstance(self.value, dict) else {}
+    arr_val, obj_val = arr, obj
+
+    def has(self, key: str) -> bool: return isinstance(self.value, dict) and key in self.value
+
+    def __getitem__(self, key) -> "JsonValue":
+        """Object member (a null node when absent) or array element (IndexError when out of range)."""
+        if isinstance(key, str):
+            return JsonValue(self.value.get(key) if isinstance(self.value, dict) else None)
+        if not isinstance(self.value, list) or not -len(self.value) <= key < len(self.value):
+            raise IndexError("JsonValue: array index out of range")
+        return JsonValue(self.value[key])
+
+    def at_or_null(self, index: int) -> "JsonValue":
+        return JsonValue(self.value[index] if isinstance(self.value, list) and 0 <= index < len(self.value) else None)
+
+    def to_string(self) -> str: return self.dump()
+
     def dump(self) -> str:
         import json
         return json.dumps(self.value, separators=(",", ":"))
+
+    @staticmethod
+    def try_parse(text: str):
+        """(value, error): a null node and the parser's message instead of an exception."""
+        import json
+        try:
+            return JsonValue(json.loads(text)), ""
+        except json.JSONDecodeError as e:
+            return JsonValue(None), str(e)
+
+
+def json_escape_string(s: str) -> str:
+    """The JSON spelling of a string without its quotes."""
+    import json
+    return json.dumps(s)[1:-1]
