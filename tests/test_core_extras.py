@@ -202,3 +202,39 @@ def test_json_node_accessors_and_inferno_units():
     assert c.best_unit() == "Inferno" and c.best_value() >= 1.0
     c.reset()
     assert c.ops == 0 and c.mean_info_weight() == 1.0
+
+
+def test_small_accessors_locks_counters_shapes_verifier_and_json_helpers():
+    from transformers_fusion_b200.utils import core as C
+    from transformers_fusion_b200.utils.hf_streamer import SimpleJSON
+    from transformers_fusion_b200.inference import speculative_extras as SX
+    from transformers_fusion_b200.server.production import RateLimiter
+    m = C.SharedMutex()
+    assert m.try_lock_shared() and m.try_lock_shared() and not m.try_lock()
+    m.unlock_shared(), m.unlock_shared()
+    assert m.try_lock() and not m.try_lock_shared() and not m.try_lock()
+    m.unlock()
+    assert m.try_lock_shared()
+    c = C.ThreadSafeCounter()
+    c.add(3), c.add(2, "x"), c.increment("x")
+    assert c.total() == 6 and c.get("x") == 3 and C.Shape(2, 3, 4).to_string() == "[2, 3, 4]" and C.Shape().to_string() == "[]"
+    doc = '{"a": {"id": 7, "name": "inner"}, "list": [{"name": "second"}], "tags": ["x", 1, "y"]}'
+    assert SimpleJSON.find_string(doc, "name") == "inner" and SimpleJSON.find_string(doc, "id") == "" and SimpleJSON.find_string("{bad", "a") == ""
+    assert SimpleJSON.find_all_strings_in_array('["x", 1, "y"]') == ["x", "y"] == SimpleJSON.find_all_strings_in_array(SimpleJSON.find_array(doc, "tags"))
+    v = SX.SmallBatchVerifier(4)
+    d = torch.eye(4)
+    r8 = v.verify(d, d)
+    v.set_format_index(3)                                         # Q_4: twice the information weight of Q_8
+    r4 = v.verify(d, d)
+    assert r8.total_accepted == 4 and r8.verify_inferno == pytest.approx(r8.verify_flops * 4 / 2) and r4.verify_inferno == pytest.approx(2 * r8.verify_inferno)
+    g = SX.MultiGPUManager()
+    assert g.detect_devices() == g.device_count() and not g.init_device(99) and g.device_name(99) == "cpu"
+    t = torch.ones(8)
+    g.free_on(0, t)
+    assert t.numel() == 0
+    now = [0.0]
+    rl = RateLimiter(1.0, 3.0, clock=lambda: now[0])
+    assert [rl.allow("a") for _ in range(4)] == [True, True, True, False]
+    rl.set_limits(10.0, 1.0)
+    now[0] += 1.0
+    assert rl.max_requests_per_sec() == 10.0 and rl.burst_size() == 1.0 and [rl.allow("a") for _ in range(2)] == [True, False]

@@ -289,3 +289,14 @@ def test_telemetry_reference_verbs(capsys):
     out = capsys.readouterr().out
     assert "telemetry" in out and "kv cache: saved" in out and "memory:" in out
     T.TelemetryPrinter.routing = T.TelemetryPrinter.kv = None
+
+
+def test_tokenizer_evaluator_comparison_and_report():
+    from transformers_fusion_b200.tokenizer import ByteTokenizer
+    from transformers_fusion_b200.utils.data import TokenizerEvaluator
+    docs = ["hello world", "second line"]
+    reps = TokenizerEvaluator.compare_tokenizers([ByteTokenizer(), ByteTokenizer()], docs)
+    assert len(reps) == 2 and reps[0]["tokenizer"] == "ByteTokenizer" and reps[0]["reconstruction_fidelity"] == 1.0
+    assert reps[0]["corpus_size_bytes"] == len("hello world\nsecond line")
+    text = TokenizerEvaluator.report_string(reps[0])
+    assert "compression_ratio" in text and "total_tokens" in text and len(text.splitlines()) == len(reps[0])

@@ -188,3 +188,22 @@ def test_fault_manager_heartbeat_thread_reports_failure_and_recovery():
         time.sleep(0.01)
     ft.stop_heartbeat()
     assert seen == [("down", 2), ("up", 2)] and ft.get_failed_nodes() == [] and not ft.heartbeat_running()
+
+
+def test_tcp_backend_node_addressing_async_and_byte_counters():
+    s = X.TCPCommBackend(0, timeout_s=1.0)
+    port = s.listen()
+    c = X.TCPCommBackend(1, timeout_s=1.0)
+    try:
+        assert not c.is_connected(0) and not c.send(0, X.MSG_TOKEN_DATA, b"x") and c.connect("127.0.0.1", port, node_id=0) and c.is_connected(0)
+        waiter = s.recv_async(X.MSG_TOKEN_DATA, 2.0)
+        sends = [c.send_async(0, X.MSG_TOKEN_DATA, b"a" * 1000) for _ in range(3)]
+        c.wait_all(), s.wait_all()
+        assert all(t.ok for t in sends) and waiter.message is not None and waiter.message[1] == 1 and len(waiter.message[3]) == 1000
+        assert s.recv(X.MSG_TOKEN_DATA, 1.0) is not None and s.recv(X.MSG_TOKEN_DATA, 1.0) is not None
+        assert c.bytes_sent(0) == 3 * (1000 + 64) == s.bytes_received(1) and c.bytes_sent(7) == 0
+        c.disconnect(0)
+        assert not c.is_connected(0) and not c.send(0, X.MSG_TOKEN_DATA, b"x")
+        assert not c.connect("127.0.0.1", 1, node_id=5)          # nothing listens on port 1
+    finally:
+        c.shutdown(), s.shutdown()

@@ -92,6 +92,23 @@ def test_facade_two_call_form_precision_helpers_and_shard_optimizer(capsys):
     assert "optimizer state" in text and "unsharded total" in capsys.readouterr().out
     blk = FSDPBlock(a, 0)
     assert blk.memory_usage() > 0 and len(blk.sync_gradients()) == len(blk.weights)
+    # the block alone: forward keeps what backward needs; backward returns the input gradient and refreshes the shards
+    h = torch.randn(32, 32)
+    eng = a.engine
+    ref_out, ref_ctx = eng._block_fwd(0, h, 2, 16)
+    out = blk.forward(h, 2, 16)
+    assert torch.equal(out, ref_out)
+    dy = torch.randn_like(out)
+    eng.gshard.zero_()
+    dh = blk.backward(dy)
+    hp = h.clone().requires_grad_(True)
+    assert dh.shape == h.shape and any(float(g.abs().sum()) > 0 for g in blk.shard_gradients())
+    eps = 1e-3
+    d = torch.randn_like(h)
+    num = float(((eng._block_fwd(0, h + eps * d, 2, 16)[0] - eng._block_fwd(0, h - eps * d, 2, 16)[0]) * dy).sum()) / (2 * eps)
+    assert num == pytest.approx(float((dh * d).sum()), rel=2e-2, abs=1e-3)
+    with pytest.raises(RuntimeError):
+        blk.backward(dy)
     # explicit activation checkpointing: the recomputed output carries gradients back to the saved input
     lin = torch.nn.Linear(8, 8)
     ac = ActivationCheckpointing()

@@ -203,3 +203,26 @@ def test_attention_variants_against_plain_statement():
     assert torch.allclose(al(x), plain(al, bias), atol=1e-5) and len(ALiBi.compute_slopes(6)) == 6
     lp = compute_logprobs(torch.randn(3, 7, generator=g), [1, 2, 3])
     assert len(lp) == 3 and len(lp[0]) == 7 and abs(sum(math.exp(v) for v in lp[0]) - 1.0) < 1e-5
+
+
+def test_fp8_two_stage_forward_reduces_activation_rounding_error():
+    from transformers_fusion_b200.inference.generation import FP8Inference
+    from transformers_fusion_b200.quant import fp8
+    torch.manual_seed(0)
+    w, x = torch.randn(128, 256), torch.randn(16, 256)
+    lin = FP8Inference(w)
+    ref = x @ fp8.dequant(lin.qw, lin.sw, 128).t()               # exact activations, the same quantised weights
+    e1 = (lin.forward(x).float() - ref).abs().mean()
+    e2 = (lin.forward_two_stage(x).float() - ref).abs().mean()
+    assert e2 < e1
+
+
+def test_model_evaluator_run_all_on_cpu():
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.utils.metrics import ModelEvaluator
+    m = DenseModel(TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=64, max_seq_len=32), device="cpu",
+                   dtype=torch.float32, seed=0)
+    ev = ModelEvaluator(m, batch_size=2)
+    res = ev.run_all([int(i) % 64 for i in range(100)])
+    assert [r.name for r in res] == ["perplexity", "accuracy"] and res[0].perplexity > 1.0 and 0.0 <= res[1].accuracy <= 1.0 and ev.results == res

@@ -140,3 +140,18 @@ def test_nas_engine_reference_verbs(tmp_path):
     n = len(nas2.history)
     nas2.record_architecture(first)
     assert len(nas2.history) == n + 1
+
+
+def test_forgetting_benchmark_task_registry_and_transfer():
+    from transformers_fusion_b200.trainer.continual import ForgettingBenchmark
+    fb = ForgettingBenchmark()
+    a = fb.register_task([1.0, 2.0, 3.0], [2.0, 4.0, 6.0], 2)
+    b = fb.register_task([5.0], [6.0])
+    assert (a, b) == (0, 1) and fb.num_tasks() == 2 and fb.eval_set(0) == ([1.0, 2.0], [2.0, 4.0])
+    fb.record_current(1, 3.0)                        # task 1 measured before it was trained: the untrained loss
+    fb.record_baseline(0, 1.0), fb.record_baseline(1, 1.5)
+    fb.record_current(0, 1.4), fb.record_current(1, 1.5)
+    assert fb.forgetting(0) == pytest.approx(0.4) and fb.forgetting(1) == 0.0 and fb.forgetting(9) == 0.0
+    assert fb.backward_transfer() == pytest.approx(-0.2) and fb.forward_transfer() == pytest.approx((0.0 + 1.5) / 2)
+    m = fb.compute()
+    assert m.num_tasks == 2 and m.max_forgetting == pytest.approx(0.4) and m.avg_forgetting == pytest.approx(0.2)

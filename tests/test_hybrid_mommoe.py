@@ -84,3 +84,18 @@ def test_native_quant_moe_model_steps():
     assert mets[-1].quant8 + mets[-1].quant + mets[-1].quant1 > 0 and 0 < mets[-1].active_params < mets[-1].total_params
     rep = nm.memory_report()
     assert rep["bytes"] < rep["fp32_bytes"] and rep["stored_bits_per_weight"] < 16
+
+
+def test_modality_router_stand_alone_losses_and_accessors():
+    torch.manual_seed(0)
+    cfg = MM.MoMMoEConfig(hidden_size=32, num_heads=2, ffn_hidden=48, num_layers=1, num_experts=8, top_k=2, vocab_size=50)
+    model = MM.MoMMoE(cfg)
+    assert model.config() is cfg
+    r = model.layers[0].router if hasattr(model.layers[0], "router") else next(m for m in model.modules() if isinstance(m, MM.TopKRouter))
+    x = torch.randn(24, 32)
+    out = r(x)
+    assert r.num_experts() == 8 and r.top_k() == 2 and r.gate_weight().shape == (8, 32) and r.modality_head_weight().shape[1] == 32
+    assert float(r.load_balance_loss(out.gates, out.indices)) == pytest.approx(float(out.load_balance_loss), rel=1e-5)
+    logits = torch.randn(5, 8)
+    assert float(r.z_loss(logits)) == pytest.approx(float((torch.logsumexp(logits, -1) ** 2).mean()))
+    assert r.classify_modality(x) == out.dominant_modality

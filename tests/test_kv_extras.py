@@ -144,3 +144,13 @@ def test_memory_efficient_attention_backward_and_stats():
     mea.set_config(block_size_q=16, max_context_tokens=1 << 10)
     assert mea.config() == {"block_size_q": 16, "block_size_kv": 4, "max_context_tokens": 1024}
     assert mea.forward_memory_bytes(1, 8, 4096, 64) < 4096 * 4096 * 4 * 8 and mea.backward_memory_bytes(1, 8, 4096, 64) > mea.forward_memory_bytes(1, 8, 4096, 64) / 4
+
+
+def test_cache_init_forms_and_capacity():
+    from transformers_fusion_b200.inference.kv_cache import PAGE, PagedKVCache
+    from transformers_fusion_b200.inference.kv_extras import Q4KVCache
+    c = PagedKVCache.init(2, 100, 2, 32, mode="bf16", device="cpu", sequences=3)
+    pages = (100 + PAGE - 1) // PAGE
+    assert c.num_pages == 3 * pages and c.logical_capacity() == 3 * pages * PAGE == c.max_seq_len()
+    q = Q4KVCache(1, 8, 2, 32, block_size=32)
+    assert q.init(2, 16, 2, 32, 64) is q and q.num_layers == 2 and q.k_idx[0].shape == (16 * 1, 32) and q.pos == [0, 0]

@@ -83,6 +83,14 @@ def test_websocket_roundtrip():
             got.append(fr[1].decode())
             buf = buf[fr[2]:]
         assert got == ["A", "B", "C"]
+        assert ws.is_running() and ws.broadcast("tok") == 1
+        while True:
+            fr = P.ws_decode_frame(buf)
+            if fr is not None:
+                break
+            buf += c.recv(1024)
+        assert fr[1] == b"tok"
+        buf = buf[fr[2]:]
         c.sendall(P.ws_encode_frame(b"", 8, mask=b"abcd"))
         c.close()
         bad = socket.create_connection(("127.0.0.1", port))
@@ -91,6 +99,7 @@ def test_websocket_roundtrip():
         bad.close()
     finally:
         ws.stop()
+    assert not ws.is_running()
 
 
 def test_plugins_and_zoo(tmp_path):

@@ -165,3 +165,52 @@ def test_engine_verbs_shared_by_all_widths():
     qch, sch = E.fp8_e5m2_quantize_per_channel(w, 0)
     assert qch.dtype == torch.uint8 and E.fp8_e5m2_quant_snr(w, E.fp8_e5m2_dequantize_per_channel(qch, sch, 0)) > 15
     assert E.compute_quant_mse(w, w) == 0.0 and E.compute_quant_error(w, w) == 0.0
+
+
+def test_vector_quantizer_online_updates_and_usage_statistics():
+    torch.manual_seed(0)
+    centres = torch.tensor([[4.0, 4.0], [-4.0, 4.0], [4.0, -4.0], [-4.0, -4.0]])
+    x = (centres[torch.randint(0, 4, (2, 256))] + 0.1 * torch.randn(2, 256, 2))
+    vq = E.VectorQuantizer(E.VQConfig(codebook_size=4, embedding_dim=2, ema_decay=0.5, codebook_init_std=4.0), seed=1)
+    assert vq.config().codebook_size == 4 and vq.codebook().shape == (4, 2) and vq.perplexity() == 0.0
+    first = vq.quantize(x)
+    assert first.quantized.shape == x.shape and first.indices.shape == (2, 256) and first.codebook_loss == 0.0
+    for _ in range(30):
+        r = vq.quantize(x)
+        vq.update_ema(x, r.indices)
+    last = vq.quantize(x)
+    assert last.commitment_loss < 0.6 * first.commitment_loss         # k-means can still leave one code serving two clusters
+    used = int((vq._hits > 0).sum())
+    assert vq.usage_rate() == used / 4 and 1.0 <= vq.perplexity() <= used + 1e-4
+    g = torch.randn(2, 256, 2)
+    assert vq.backward(g) is g
+    # the gradient form: a step against the gradient of ||q - x||^2 / 2 moves every used code toward its members
+    vg = E.VectorQuantizer(E.VQConfig(codebook_size=4, embedding_dim=2, use_ema=False, codebook_init_std=4.0), seed=1)
+    r0 = vg.quantize(x)
+    assert r0.codebook_loss == r0.commitment_loss
+    for _ in range(50):
+        r = vg.quantize(x)
+        n = torch.bincount(r.indices.reshape(-1), minlength=4).clamp(min=1)[r.indices.reshape(-1)]
+        vg.update_codebook_grad(((r.quantized - x).reshape(-1, 2) / n[:, None]), r.indices, lr=0.5)
+    assert vg.quantize(x).commitment_loss < r0.commitment_loss
+
+
+def test_min_max_observer_interface():
+    from transformers_fusion_b200.quant import qat as Q
+    o = Q.MinMaxObserver()
+    assert not o.has_data() and o.calc_qparams(8, True).scale == 1.0 and o.type() == "MinMax" and o.min_val() == 0.0
+    o.observe(torch.tensor([-1.0, 0.5])), o.observe(torch.tensor([0.25, 3.0]))
+    assert o.min_val() == -1.0 and o.max_val() == 3.0
+    sp = o.calc_qparams(8, True)
+    assert sp.zero_point == 0 and sp.qmax == 127 and sp.scale == pytest.approx(3.0 / 127)
+    ap = o.calc_qparams(8, False)
+    x = torch.tensor([-1.0, 0.0, 1.7, 3.0])
+    assert ap.qmin == 0 and ap.qmax == 255 and float(ap.dequantize(ap.quantize(torch.zeros(1)))) == 0.0
+    assert (ap.dequantize(ap.quantize(x)) - x).abs().max() <= ap.scale / 2 + 1e-6
+    o.reset()
+    assert not o.has_data()
+    m = Q.MovingAverageObserver(0.5)
+    m.observe(torch.tensor([0.0, 2.0])), m.observe(torch.tensor([0.0, 4.0]))
+    assert m.max_val() == 3.0 and m.type() == "MovingAverage"
+    m.reset(), m.observe(torch.tensor([0.0, 8.0]))
+    assert m.max_val() == 8.0

@@ -152,3 +152,5 @@ def test_model_load_and_unload_routes(server):
     assert seen == [("unload",), ("load", "/models/b.bin"), ("load", "/models/a.quant")]
     code, _, _ = _raw(port, b"GET /v1/models/load HTTP/1.1\r\nHost: x\r\n\r\n")
     assert code == 405
+    assert server.model_name() == "second-model" and server.total_requests() >= 10 and server.total_errors() >= 4
+    assert server.total_tokens() >= 1

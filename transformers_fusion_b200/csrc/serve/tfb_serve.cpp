@@ -603,6 +603,14 @@ TFB_EXPORT void tfb_server_set_model_callbacks(void* h, tfb_load_model_fn load, 
 }
 TFB_EXPORT int tfb_server_is_running(void* h) { return static_cast<Server*>(h)->running ? 1 : 0; }
 TFB_EXPORT int tfb_server_current_requests(void* h) { return static_cast<Server*>(h)->current.load(); }
+TFB_EXPORT long long tfb_server_total_requests(void* h) { return static_cast<Server*>(h)->total.load(); }
+TFB_EXPORT long long tfb_server_total_errors(void* h) { return static_cast<Server*>(h)->errors.load(); }
+TFB_EXPORT long long tfb_server_total_tokens(void* h) { return static_cast<Server*>(h)->tokens_out.load(); }
+TFB_EXPORT int tfb_server_model_name(void* h, char* out, int cap) {
+  const std::string& n = static_cast<Server*>(h)->model_name;
+  if (out && cap > 0) { int k = (int)n.size() < cap - 1 ? (int)n.size() : cap - 1; memcpy(out, n.data(), k); out[k] = 0; }
+  return (int)n.size();
+}
 TFB_EXPORT int tfb_server_port(void* h) { return static_cast<Server*>(h)->bound_port; }
 TFB_EXPORT double tfb_server_latency_pct(void* h, double p) { return static_cast<Server*>(h)->latency.pct(p); }
 TFB_EXPORT double tfb_server_ttft_pct(void* h, double p) { return static_cast<Server*>(h)->ttft.pct(p); }

@@ -206,6 +206,14 @@ class SpeculativeStats:
         return self.generated / max(1, self.target_passes)
 
 
+@dataclass
+class SpeculativeStepResult:
+    tokens_accepted: List[int]
+    tokens_rejected: int = 0
+    total_proposed: int = 0
+    acceptance_rate: float = 0.0
+
+
 class SpeculativeDecoder:
     def __init__(self, target, draft, gamma: int = 4, adaptive: bool = True, max_gamma: int = 8, seed: int = 0, kv_mode="bf16"):
         pages = lambda m: max(64, 4 * m.cfg.max_seq_len // PAGE)
@@ -221,6 +229,61 @@ class SpeculativeDecoder:
     def total_count(self) -> int: return self.stats.proposed
     def current_gamma(self) -> float: return float(self.gamma)
     def used_uniform_draft_fallback(self) -> bool: return False      # a draft model is mandatory here
+
+    # ---- step-wise form (reference: include/quant/speculative_decoder.h:80-98)
+    def current_draft_k(self) -> int: return self.gamma
+    def total_accepted(self) -> int: return self.stats.accepted
+    def total_proposed(self) -> int: return self.stats.proposed
+
+    def update_draft_k(self, new_k: int):
+        """Set the number of drafted tokens per round, clamped to [1, max]."""
+        self.gamma = max(1, min(int(new_k), self.max_gamma))
+
+    @torch.no_grad()
+    def decode_step(self, context: List[int], sampling: Optional[SamplerConfig] = None) -> "SpeculativeStepResult":
+        """One draft-and-verify round on ``context`` (extended in place by the accepted tokens and the target's own token).  Both
+        caches are rebuilt from the context, so a caller that wants them kept across rounds uses ``generate``."""
+        sc = sampling or SamplerConfig(temperature=0.0)
+        g = self.gamma
+        total = min(len(context) + g + 2, min(self.te.max_len, self.de.max_len))
+        if not context or len(context) + g + 1 > total:
+            return SpeculativeStepResult([], 0, 0, self.acceptance_rate())
+        T, D = _Seq(self.te, total), _Seq(self.de, total)
+        try:
+            if len(context) > 1:
+                T.extend(context[:-1])
+            q_list, prop, cur = [], [], list(context)
+            for _ in range(g):
+                q = self._probs(D.extend(cur)[-1], sc)
+                t = int(torch.multinomial(q.cpu(), 1, generator=self.gen))
+                q_list.append(q), prop.append(t), cur.append(t)
+            lt = T.extend(cur, all_positions=True)
+            self.stats.target_passes += 1
+            self.stats.proposed += g
+            n_acc, bonus = 0, None
+            for i in range(g):
+                p, q, t = self._probs(lt[i], sc), q_list[i], prop[i]
+                if float(torch.rand((), generator=self.gen)) < min(1.0, float(p[t]) / max(float(q[t]), 1e-30)):
+                    n_acc += 1
+                    continue
+                resid = (p - q.to(p.device)).clamp(min=0)
+                bonus = int(torch.multinomial((resid / resid.sum().clamp(min=1e-30)).cpu(), 1, generator=self.gen)) \
+                    if float(resid.sum()) > 0 else int(p.argmax())
+                break
+            if bonus is None:
+                bonus = int(torch.multinomial(self._probs(lt[g], sc).cpu(), 1, generator=self.gen))
+            self.stats.accepted += n_acc
+            new = prop[:n_acc] + [bonus]
+            self.stats.generated += len(new)
+            context.extend(new)
+            if self.adaptive:
+                if n_acc == g:
+                    self.update_draft_k(self.gamma + 1)
+                elif n_acc < g // 2:
+                    self.update_draft_k(self.gamma - 1)
+            return SpeculativeStepResult(new, g - n_acc, g, self.acceptance_rate())
+        finally:
+            T.free(), D.free()
 
     def _probs(self, logits_row, sc: SamplerConfig):
         if sc.temperature <= 0:
@@ -637,6 +700,18 @@ class FP8Inference:
     def forward(self, x):
         qa, sa = self.fp8.quant_act_1x128(x.contiguous())
         return self.fp8.gemm_fp8(qa, sa, self.qw, self.sw)
+
+    def forward_two_stage(self, x):
+        """Two-stage residual accumulation: what the 8-bit activations lost (x minus their dequantised value) is quantised
+        again with its own, much smaller scales and sent through a second GEMM, so the activation rounding error drops by
+        about the fp8 step (1/16) at twice the tensor-core work.  Meant for long contexts, where that error accumulates.
+        Reference counterpart: FP8Inference::forward_two_stage (include/quant/inference_opt.h:151-158)."""
+        x = x.contiguous()
+        qa, sa = self.fp8.quant_act_1x128(x)
+        resid = (x.float() - self.fp8.dequant(qa, sa, 1)).to(x.dtype)
+        qr, sr = self.fp8.quant_act_1x128(resid.contiguous())
+        y = self.fp8.gemm_fp8(qa, sa, self.qw, self.sw)
+        return y + self.fp8.gemm_fp8(qr, sr, self.qw, self.sw)
 
 
 class ModelShard:

@@ -117,6 +117,19 @@ class PagedKVCache:
         self.allocator = PageAllocator(num_pages)
         self._ws = {}
 
+    @classmethod
+    def init(cls, num_layers: int, max_seq_len: int, num_heads: int, head_dim: int, mode="bf16", device="cuda", sequences: int = 1):
+        """A cache with room for ``sequences`` sequences of ``max_seq_len`` tokens (rounded up to whole pages)."""
+        return cls(num_layers, sequences * ((max_seq_len + PAGE - 1) // PAGE), num_heads, head_dim, mode, device)
+
+    def logical_capacity(self) -> int:
+        """Tokens the pools can hold over all sequences."""
+        return self.num_pages * PAGE
+
+    def max_seq_len(self) -> int:
+        """The longest single sequence: one that owns every page."""
+        return self.num_pages * PAGE
+
     def bytes_per_token(self) -> float:
         per = {"bf16": 2.0, "fp8": 1.0 + 4.0 / self.D, "q4": 0.5 + 2.0 / 32}[self.mode]
         return 2 * self.L * self.Hkv * self.D * per

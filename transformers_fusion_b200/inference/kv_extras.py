@@ -373,6 +373,11 @@ class Q4KVCache:
         self.k_cb, self.v_cb = [mk_c() for _ in range(num_layers)], [mk_c() for _ in range(num_layers)]
         self.pos = [0] * num_layers
 
+    def init(self, num_layers: int, max_seq_len: int, num_heads: int, head_dim: int, block_size: int = 64):
+        """Re-create the store with new dimensions; everything cached is dropped."""
+        self.__init__(num_layers, max_seq_len, num_heads, head_dim, block_size, self.device)
+        return self
+
     # ---- block codec (batched over blocks)
     @staticmethod
     def quantize_blocks(x: torch.Tensor, iters: int = 20):

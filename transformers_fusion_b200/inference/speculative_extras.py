@@ -46,6 +46,7 @@ class VerificationResult:
     first_rejection_pos: int = -1
     total_accepted: int = 0
     verify_flops: float = 0.0
+    verify_inferno: float = 0.0          # the comparison work weighted by the information weight of the weight format
 
 
 class SmallBatchVerifier:
@@ -54,6 +55,12 @@ class SmallBatchVerifier:
 
     def __init__(self, max_batch: int = 8):
         self.max_batch = max_batch
+        self.format_index = 5            # Q_8 in the throughput counter's format table
+
+    def set_format_index(self, idx: int):
+        """Which weight format the verified model runs in (index into ``InfernoCounter.FORMATS``): it sets the information
+        weight applied to ``verify_flops`` in the result's ``verify_inferno``."""
+        self.format_index = int(idx)
 
     def verify(self, draft_logits: torch.Tensor, target_logits: torch.Tensor, temperature: float = 1.0) -> VerificationResult:
         n = min(self.max_batch, draft_logits.shape[0], target_logits.shape[0])
@@ -61,6 +68,9 @@ class SmallBatchVerifier:
         if n == 0 or draft_logits.shape[-1] != target_logits.shape[-1]:
             res.first_rejection_pos = 0 if n else -1
             return res
+        from ..utils.inferno import InfernoCounter
+        if 0 <= self.format_index < len(InfernoCounter.FORMATS):
+            res.verify_inferno = res.verify_flops * (32.0 / InfernoCounter.FORMATS[self.format_index][1]) / 2.0
         same = (draft_logits[:n].argmax(-1) == target_logits[:n].argmax(-1)).tolist()
         for i, ok in enumerate(same):
             if not ok:
@@ -293,6 +303,32 @@ class MultiGPUManager:
     def transfer(self, t: torch.Tensor, index: int, non_blocking: bool = True) -> torch.Tensor:
         dev = torch.device("cuda", index) if self.device_count() else torch.device("cpu")
         return t.to(dev, non_blocking=non_blocking)
+
+    # ---- the reference's verbs (include/quant/gpu_extras.h:63-77)
+    def detect_devices(self) -> int:
+        self._devices = self.detect()
+        return len(self._devices)
+
+    def init_device(self, index: int) -> bool:
+        """Create the CUDA context of a device (a 1-element allocation does it); False for an index that does not exist."""
+        if not 0 <= index < self.device_count():
+            return False
+        torch.empty(1, device=torch.device("cuda", index))
+        if not hasattr(self, "_ready"):
+            self._ready = set()
+        self._ready.add(index)
+        return True
+
+    def device_name(self, index: int) -> str:
+        return torch.cuda.get_device_properties(index).name if 0 <= index < self.device_count() else "cpu"
+
+    def free_on(self, index: int, t: Optional[torch.Tensor] = None):
+        """Drop a tensor's storage and hand cached blocks of that device back to the driver."""
+        if t is not None:
+            t.set_(torch.empty(0, dtype=t.dtype, device=t.device).untyped_storage(), 0, (0,))
+        if 0 <= index < self.device_count():
+            with torch.cuda.device(index):
+                torch.cuda.empty_cache()
 
     def can_access_peer(self, a: int, b: int) -> bool:
         return self.device_count() > max(a, b) and (a == b or torch.cuda.can_device_access_peer(a, b))

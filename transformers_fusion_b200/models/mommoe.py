@@ -76,6 +76,31 @@ class TopKRouter(nn.Module):
         return RouterOutput(gates, idx, w, mp, dom, lb, z, int((f > 0).sum()))
 
 
+def _router_api():
+    """The reference's stand-alone pieces of the router (include/quant/mommoe_block.h:88-106): the two auxiliary losses as
+    functions of given routing results, the modality classifier, and plain accessors."""
+    def load_balance_loss(self, gates: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        f = torch.bincount(indices.reshape(-1), minlength=self.E).float() / max(1, indices.numel())
+        return self.E * (f * gates.float().reshape(-1, self.E).mean(0)).sum()
+
+    def z_loss(self, logits: torch.Tensor) -> torch.Tensor:
+        return (torch.logsumexp(logits.float(), -1) ** 2).mean()
+
+    def classify_modality(self, hidden: torch.Tensor) -> Modality:
+        """The modality the classifier head gives the highest mean probability over the given tokens."""
+        mp = torch.softmax(self.modality_head(hidden.reshape(-1, hidden.shape[-1])).float(), -1)
+        return Modality(int(mp.mean(0).argmax()))
+
+    TopKRouter.load_balance_loss, TopKRouter.z_loss, TopKRouter.classify_modality = load_balance_loss, z_loss, classify_modality
+    TopKRouter.gate_weight = lambda self: self.gate.weight
+    TopKRouter.modality_head_weight = lambda self: self.modality_head.weight
+    TopKRouter.num_experts = lambda self: self.E
+    TopKRouter.top_k = lambda self: self.k
+
+
+_router_api()
+
+
 class CrossModalAttention(nn.Module):
     """Tokens attend to per-modality summaries of the sequence (mean of the tokens weighted by their modality
     probability): M keys per sequence, so the cost is linear in the sequence length."""
@@ -212,6 +237,8 @@ class MoMMoE(nn.Module):
                 nxt = i.gather(1, torch.multinomial(torch.softmax(v, -1), 1, generator=generator))
             ids = torch.cat([ids, nxt], 1)
         return ids
+
+    def config(self) -> MoMMoEConfig: return self.cfg
 
     def total_parameters(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -190,6 +190,11 @@ class TCPCommBackend:
         self.seq = 0
         self._stop = False
         self.threads: List[threading.Thread] = []
+        self.peers: Dict[int, Tuple[str, int]] = {}             # node id -> address, filled by connect()
+        self._tx: Dict[int, int] = {}
+        self._rx: Dict[int, int] = {}
+        self._pending: List[threading.Thread] = []
+        self._send_lock = threading.Lock()
 
     def listen(self, port: int = 0, host: str = "127.0.0.1") -> int:
         self.server = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
@@ -241,13 +246,26 @@ class TCPCommBackend:
                     return
                 with self.cv:
                     self.inbox.append((typ, src, seq, payload))
+                    self._rx[src] = self._rx.get(src, 0) + _HDR.size + len(payload)
                     self.cv.notify_all()
         except OSError:
             return
         finally:
             c.close()
 
-    def send(self, addr: Tuple[str, int], typ: int, payload: bytes = b"", dst: int = 0) -> bool:
+    def send(self, addr, typ: int, payload: bytes = b"", dst: int = 0) -> bool:
+        """``addr``: an (host, port) pair, or the node id of a peer registered with ``connect``."""
+        if isinstance(addr, int):
+            if addr not in self.peers:
+                return False
+            addr, dst = self.peers[addr], addr
+        with self._send_lock:
+            ok = self._send_locked(addr, typ, payload, dst)
+        if ok:
+            self._tx[dst] = self._tx.get(dst, 0) + _HDR.size + len(payload)
+        return ok
+
+    def _send_locked(self, addr: Tuple[str, int], typ: int, payload: bytes, dst: int) -> bool:
         try:
             c = self.conns.get(addr)
             if c is None:
@@ -274,8 +292,67 @@ class TCPCommBackend:
                     return None
                 self.cv.wait(rest)
 
+    # ---- node-id addressed form (reference: TCPCommBackend, include/quant/expert_parallel.h:91-111)
+    def connect(self, address: str, port: int, node_id: Optional[int] = None) -> bool:
+        """Open the connection to a peer now and remember it under ``node_id`` (default: the next free id)."""
+        nid = node_id if node_id is not None else (max(self.peers) + 1 if self.peers else 0)
+        addr = (address, int(port))
+        try:
+            if addr not in self.conns:
+                self.conns[addr] = socket.create_connection(addr, timeout=self.timeout)
+        except OSError:
+            return False
+        self.peers[nid] = addr
+        return True
+
+    def disconnect(self, node_id: int):
+        addr = self.peers.pop(node_id, None)
+        c = self.conns.pop(addr, None) if addr else None
+        if c is not None:
+            try:
+                c.close()
+            except OSError:
+                pass
+
+    def is_connected(self, node_id: int) -> bool:
+        return node_id in self.peers and self.peers[node_id] in self.conns
+
+    def bytes_sent(self, node_id: int) -> int: return self._tx.get(node_id, 0)
+    def bytes_received(self, node_id: int) -> int: return self._rx.get(node_id, 0)
+
+    def send_async(self, node_id, typ: int, payload: bytes = b"") -> "threading.Thread":
+        """Send on a helper thread; ``wait_all`` joins every outstanding one.  The thread's ``ok`` attribute holds the result."""
+        def run():
+            t.ok = self.send(node_id, typ, payload)
+        t = threading.Thread(target=run, daemon=True)
+        t.ok = None
+        t.start()
+        self._pending.append(t)
+        return t
+
+    def recv_async(self, typ: Optional[int] = None, timeout_s: Optional[float] = None) -> "threading.Thread":
+        """Wait for a message on a helper thread; after ``wait_all`` (or ``join``) its ``message`` attribute holds it (None on
+        time-out)."""
+        def run():
+            t.message = self.recv(typ, timeout_s)
+        t = threading.Thread(target=run, daemon=True)
+        t.message = None
+        t.start()
+        self._pending.append(t)
+        return t
+
+    def wait_all(self):
+        pend, self._pending = self._pending, []
+        for t in pend:
+            t.join()
+
+    def shutdown(self):
+        self.wait_all()
+        self.close()
+
     def close(self):
         self._stop = True
+        self.peers.clear()
         for c in self.conns.values():
             try:
                 c.close()

@@ -214,6 +214,26 @@ class FSDPBlock:
         e = self.fsdp.engine
         return [e.gshard[p.shard_off:p.shard_off + p.per * p.cols].view(p.per, p.cols) for p in self.weights]
 
+    @torch.no_grad()
+    def forward(self, h: torch.Tensor, batch: int, seq_len: int) -> torch.Tensor:
+        """The block alone: its weights are gathered (or read inside the GEMMs), ``h`` [tokens / tp, hidden] goes through
+        attention and the feed-forward, and the activations the backward needs are kept on the block."""
+        e = self.fsdp.engine
+        out, self._ctx = e._block_fwd(self.unit - 1, h, batch, seq_len)
+        self._bs = (batch, seq_len)
+        return out
+
+    @torch.no_grad()
+    def backward(self, grad_output: torch.Tensor) -> torch.Tensor:
+        """Gradient of the block's input; the weight gradients are reduce-scattered into this rank's shards on the way."""
+        if getattr(self, "_ctx", None) is None:
+            raise RuntimeError("FSDPBlock.backward needs a forward first")
+        e = self.fsdp.engine
+        dh = e._block_bwd(self.unit - 1, self._ctx, grad_output, *self._bs)
+        self._ctx = None
+        e._unit_done(self.unit)
+        return dh
+
     def sync_gradients(self):
         """The block's gradients are reduce-scattered by the engine as soon as the block's backward is done; this returns
         the reduced shards (nothing is left to synchronise afterwards)."""

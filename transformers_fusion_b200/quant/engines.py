@@ -22,6 +22,7 @@ import struct
 from typing import Optional, Tuple
 
 import torch
+from dataclasses import dataclass
 
 
 def quant_error(a, b) -> float:
@@ -106,11 +107,90 @@ def CodebookQ8(device="cpu"): return Codebook(8, device)
 def CodebookQ12(device="cpu"): return Codebook(12, device)
 
 
+@dataclass
+class VQConfig:
+    codebook_size: int = 256
+    embedding_dim: int = 64
+    commitment_weight: float = 0.25
+    ema_decay: float = 0.99
+    codebook_init_std: float = 1.0
+    use_ema: bool = True
+
+
+@dataclass
+class VQResult:
+    quantized: torch.Tensor
+    indices: torch.Tensor
+    commitment_loss: float
+    codebook_loss: float
+
+
 class VectorQuantizer:
-    def __init__(self, num_codes: int, dim: int, device="cpu", seed=0):
+    """Learned vector codebook (reference: include/quant/vector_quantizer.h:36-80).  ``train`` fits it with Lloyd iterations;
+    ``update_ema`` / ``update_codebook_grad`` are the two online updates used while the encoder that feeds it is training."""
+
+    def __init__(self, num_codes=256, dim: int = 64, device="cpu", seed=0):
+        if isinstance(num_codes, VQConfig):
+            self.cfg = num_codes
+        else:
+            self.cfg = VQConfig(codebook_size=num_codes, embedding_dim=dim)
         g = torch.Generator().manual_seed(seed)
-        self.codes = torch.randn(num_codes, dim, generator=g).to(device)
-        self.dim = dim
+        self.codes = (torch.randn(self.cfg.codebook_size, self.cfg.embedding_dim, generator=g) * self.cfg.codebook_init_std).to(device)
+        self.dim = self.cfg.embedding_dim
+        self._counts = torch.zeros(self.cfg.codebook_size, device=device)       # EMA cluster sizes
+        self._sums = self.codes.clone() * 0                                    # EMA cluster sums
+        self._hits = torch.zeros(self.cfg.codebook_size, device=device)        # raw assignment counts, for the usage statistics
+        self._last_idx = None
+
+    def config(self) -> VQConfig: return self.cfg
+    def codebook(self) -> torch.Tensor: return self.codes
+
+    def quantize(self, embeddings: torch.Tensor) -> VQResult:
+        """The reference's forward: nearest code per vector plus the two losses (the codebook loss is 0 under EMA updates)."""
+        x = embeddings.detach().float()
+        idx = self.encode(x)
+        q = self.decode(idx, x.shape)
+        self._last_idx = idx
+        self._hits.index_add_(0, idx.to(self._hits.device), torch.ones(idx.numel(), device=self._hits.device))
+        mse = float(((q - x) ** 2).mean())
+        return VQResult(q.to(embeddings.dtype), idx.reshape(embeddings.shape[:-1]), mse, 0.0 if self.cfg.use_ema else mse)
+
+    def backward(self, grad_output: torch.Tensor) -> torch.Tensor:
+        """Straight-through: the encoder receives the gradient of the quantised output unchanged."""
+        return grad_output
+
+    def update_ema(self, embeddings: torch.Tensor, indices: torch.Tensor):
+        x = embeddings.detach().float().reshape(-1, self.dim).to(self.codes.device)
+        idx = indices.reshape(-1).long().to(self.codes.device)
+        d = self.cfg.ema_decay
+        n = torch.zeros_like(self._counts).index_add_(0, idx, torch.ones(idx.numel(), device=x.device))
+        s = torch.zeros_like(self._sums).index_add_(0, idx, x)
+        self._counts.mul_(d).add_(n, alpha=1 - d)
+        self._sums.mul_(d).add_(s, alpha=1 - d)
+        # Laplace smoothing keeps a code that lost all its members from dividing by zero; it stays where it was instead
+        tot = self._counts.sum()
+        K = self._counts.numel()
+        sm = (self._counts + 1e-5) / (tot + K * 1e-5) * tot
+        live = self._counts > 1e-8
+        self.codes = torch.where(live[:, None], self._sums / sm[:, None].clamp(min=1e-12), self.codes)
+
+    def update_codebook_grad(self, grad_quantized: torch.Tensor, indices: torch.Tensor, lr: float = 1.0):
+        """Gradient form (``use_ema`` off): every code moves against the summed gradient of the positions assigned to it."""
+        g = grad_quantized.detach().float().reshape(-1, self.dim).to(self.codes.device)
+        idx = indices.reshape(-1).long().to(self.codes.device)
+        self.codes = self.codes - lr * torch.zeros_like(self.codes).index_add_(0, idx, g)
+
+    def usage_rate(self) -> float:
+        """Fraction of the codes that have been chosen at least once since construction."""
+        return float((self._hits > 0).float().mean())
+
+    def perplexity(self) -> float:
+        """exp(entropy) of the assignment distribution: the effective number of codes in use."""
+        tot = self._hits.sum()
+        if tot <= 0:
+            return 0.0
+        p = self._hits / tot
+        return float(torch.exp(-(p[p > 0] * p[p > 0].log()).sum()))
 
     def train(self, data: torch.Tensor, iters=20):
         x = data.detach().float().reshape(-1, self.dim)

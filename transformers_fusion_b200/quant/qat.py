@@ -8,6 +8,8 @@ from __future__ import annotations
 import math
 
 import numpy as np
+from dataclasses import dataclass
+
 import torch
 
 from ..ops import _lib
@@ -113,6 +115,20 @@ def lsq_init_step(x, bits=8, symmetric=True):
     return (2.0 * x.float().abs().mean() / math.sqrt(qp)).reshape(1).clone()
 
 
+@dataclass
+class QuantParams:
+    scale: float = 1.0
+    zero_point: int = 0
+    qmin: int = -127
+    qmax: int = 127
+
+    def quantize(self, x: torch.Tensor) -> torch.Tensor:
+        return (x.float() / self.scale + self.zero_point).round().clamp(self.qmin, self.qmax)
+
+    def dequantize(self, q: torch.Tensor) -> torch.Tensor:
+        return (q.float() - self.zero_point) * self.scale
+
+
 class MinMaxObserver:
     def __init__(self):
         self.lo, self.hi = float("inf"), float("-inf")
@@ -125,6 +141,31 @@ class MinMaxObserver:
             return max(abs(self.lo), abs(self.hi)) / ((1 << (bits - 1)) - 1) or 1.0, 0.0
         s = (self.hi - self.lo) / ((1 << bits) - 1) or 1.0
         return s, self.lo
+
+    # ---- the reference's observer interface (include/quant/qat.h:120-145)
+    def has_data(self) -> bool: return self.lo <= self.hi
+    def min_val(self) -> float: return self.lo if self.has_data() else 0.0
+    def max_val(self) -> float: return self.hi if self.has_data() else 0.0
+    def type(self) -> str: return {"MinMaxObserver": "MinMax", "MovingAverageObserver": "MovingAverage", "PercentileObserver": "Percentile"}.get(type(self).__name__, type(self).__name__)
+
+    def reset(self):
+        self.lo, self.hi = float("inf"), float("-inf")
+        if hasattr(self, "init"):
+            self.init = False
+
+    def calc_qparams(self, bits=8, symmetric=True) -> "QuantParams":
+        """Scale, integer zero point and integer range for the observed values; scale 1 before anything was observed."""
+        if symmetric:
+            qmin, qmax = -(1 << (bits - 1)) + 1, (1 << (bits - 1)) - 1
+        else:
+            qmin, qmax = 0, (1 << bits) - 1
+        if not self.has_data():
+            return QuantParams(1.0, 0, qmin, qmax)
+        if symmetric:
+            return QuantParams(max(abs(self.lo), abs(self.hi)) / qmax or 1.0, 0, qmin, qmax)
+        lo, hi = min(self.lo, 0.0), max(self.hi, 0.0)            # the range must contain 0 so that 0 is exactly representable
+        s = (hi - lo) / (qmax - qmin) or 1.0
+        return QuantParams(s, int(min(max(round(qmin - lo / s), qmin), qmax)), qmin, qmax)
 
 
 class MovingAverageObserver(MinMaxObserver):

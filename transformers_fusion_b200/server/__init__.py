@@ -39,6 +39,10 @@ def _lib():
                   "tfb_server_set_max_concurrent"):
             getattr(L, n).argtypes = [C.c_void_p, C.c_int]
             getattr(L, n).restype = None
+        for n in ("tfb_server_total_requests", "tfb_server_total_errors", "tfb_server_total_tokens"):
+            getattr(L, n).argtypes = [C.c_void_p]
+            getattr(L, n).restype = C.c_longlong
+        L.tfb_server_model_name.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         L.tfb_server_set_max_body.argtypes = [C.c_void_p, C.c_longlong]
         L.tfb_server_set_rate_limit.argtypes = [C.c_void_p, C.c_double, C.c_double]
         L.tfb_server_set_auth_token.argtypes = [C.c_void_p, C.c_char_p]
@@ -81,6 +85,16 @@ class HTTPServer:
 
     def current_requests(self) -> int:
         return _lib().tfb_server_current_requests(self._h)
+
+    def total_requests(self) -> int: return _lib().tfb_server_total_requests(self._h)
+    def total_errors(self) -> int: return _lib().tfb_server_total_errors(self._h)
+    def total_tokens(self) -> int: return _lib().tfb_server_total_tokens(self._h)
+
+    def model_name(self) -> str:
+        """The name the server reports, including one set by a ``/v1/models/load`` request."""
+        buf = C.create_string_buffer(512)
+        _lib().tfb_server_model_name(self._h, buf, 512)
+        return buf.value.decode("utf-8", "replace")
 
     def __del__(self):
         if getattr(self, "_h", None):

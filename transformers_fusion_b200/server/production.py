@@ -339,6 +339,28 @@ class WebSocketHandler:
         self.sock: Optional[socket.socket] = None
         self._stop = False
         self.clients = 0
+        self._socks: List[socket.socket] = []
+        self._socks_lock = threading.Lock()
+
+    def is_running(self) -> bool:
+        return self.sock is not None and not self._stop
+
+    def broadcast(self, text: str) -> int:
+        """Send one text frame to every connected client; returns how many received it (a client whose socket fails is
+        dropped)."""
+        frame = ws_encode_frame(text.encode())
+        with self._socks_lock:
+            socks = list(self._socks)
+        n = 0
+        for c in socks:
+            try:
+                c.sendall(frame)
+                n += 1
+            except OSError:
+                with self._socks_lock:
+                    if c in self._socks:
+                        self._socks.remove(c)
+        return n
 
     def start(self):
         self.sock = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
@@ -384,6 +406,8 @@ class WebSocketHandler:
             c.sendall(("HTTP/1.1 101 Switching Protocols\r\nUpgrade: websocket\r\nConnection: Upgrade\r\n"
                        f"Sec-WebSocket-Accept: {websocket_accept_key(key)}\r\n\r\n").encode())
             self.clients += 1
+            with self._socks_lock:
+                self._socks.append(c)
             send = lambda text: c.sendall(ws_encode_frame(text.encode()))
             buf = rest
             while not self._stop:
@@ -406,6 +430,9 @@ class WebSocketHandler:
         except (OSError, ValueError):
             return
         finally:
+            with self._socks_lock:
+                if c in self._socks:
+                    self._socks.remove(c)
             c.close()
 
 
@@ -580,3 +607,12 @@ class RateLimiter:
         with self._lock:
             tokens, last = self._b.get(key, (self.burst, self._clock()))
         return max(0.0, (cost - tokens) / self.rate) if self.rate > 0 else float("inf")
+
+    def set_limits(self, max_requests_per_sec: float, burst: float):
+        """New rate and burst for every client; buckets holding more than the new burst are cut down to it."""
+        with self._lock:
+            self.rate, self.burst = float(max_requests_per_sec), float(burst)
+            self._b = {k: (min(t, self.burst), last) for k, (t, last) in self._b.items()}
+
+    def max_requests_per_sec(self) -> float: return self.rate
+    def burst_size(self) -> float: return self.burst

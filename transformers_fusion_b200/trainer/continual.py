@@ -150,6 +150,39 @@ class ForgettingBenchmark:
     def update(self, task_id, loss):
         self.current[task_id] = loss
 
+    # ---- the reference's spelling (include/quant/continual_engine.h:124-144): tasks are numbered in registration order and
+    # keep their held-out evaluation set, so a caller can re-measure them after every later task
+    def register_task(self, eval_inputs, eval_targets, elem_count: Optional[int] = None) -> int:
+        if not hasattr(self, "tasks"):
+            self.tasks = []
+        n = elem_count if elem_count is not None else len(eval_inputs)
+        self.tasks.append((eval_inputs[:n], eval_targets[:n]))
+        return len(self.tasks) - 1
+
+    def eval_set(self, task_id: int):
+        return self.tasks[task_id]
+
+    def record_baseline(self, task_id: int, loss: float):
+        """Loss on the task right after training on it; the first value ever recorded for a task (normally before training) is
+        kept as the untrained loss that forward transfer is measured from."""
+        self.first_seen.setdefault(task_id, float(loss))
+        self.baseline[task_id] = float(loss)
+
+    def record_current(self, task_id: int, loss: float):
+        self.first_seen.setdefault(task_id, float(loss))
+        self.current[task_id] = float(loss)
+
+    def forgetting(self, task_id: int) -> float:
+        if task_id not in self.baseline or task_id not in self.current:
+            return 0.0
+        return max(0.0, self.current[task_id] - self.baseline[task_id])
+
+    def backward_transfer(self) -> float: return self.compute().backward_transfer
+    def forward_transfer(self) -> float: return self.compute().forward_transfer
+
+    def num_tasks(self) -> int:
+        return max(len(getattr(self, "tasks", ())), len(self.baseline))
+
     def compute(self) -> ForgettingMetrics:
         ts = [t for t in self.baseline if t in self.current]
         if not ts:

@@ -55,6 +55,9 @@ class Shape(tuple):
     @property
     def rank(self) -> int: return len(self)
 
+    def to_string(self) -> str:
+        return "[" + ", ".join(str(d) for d in self) + "]"
+
     def numel(self) -> int:
         n = 1
         for d in self:
@@ -162,6 +165,21 @@ class SharedMutex:
             self._writer = False
             self._cv.notify_all()
 
+    def try_lock(self) -> bool:
+        """Take the exclusive lock only if nobody holds the lock in either mode; never waits."""
+        with self._cv:
+            if self._writer or self._readers:
+                return False
+            self._writer = True
+            return True
+
+    def try_lock_shared(self) -> bool:
+        with self._cv:
+            if self._writer or self._waiting_writers:
+                return False
+            self._readers += 1
+            return True
+
     def shared(self):
         return _Guard(self.lock_shared, self.unlock_shared)
 
@@ -258,6 +276,13 @@ class ThreadSafeCounter:
     def snapshot(self) -> dict:
         with self._l:
             return dict(self._c)
+
+    def add(self, n: int = 1, name: str = "") -> int:
+        return self.increment(name, n)
+
+    def total(self) -> int:
+        with self._l:
+            return sum(self._c.values())
 
 
 # ------------------------------------------------------------------------------------------------ files and JSON values

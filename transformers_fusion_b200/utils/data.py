@@ -966,7 +966,27 @@ class TokenizerEvaluator:
         bits = max(1, (v - 1).bit_length())
         return len(self.tok.encode(text)) * bits / max(1, 8 * len(text.encode("utf-8")))
 
+    @staticmethod
+    def report_string(report: dict) -> str:
+        """One aligned ``name: value`` line per figure of an ``evaluate`` result."""
+        w = max((len(k) for k in report), default=0)
+        return "\n".join(f"{k:<{w}} : {v:.4f}" if isinstance(v, float) else f"{k:<{w}} : {v}" for k, v in report.items())
+
+    @staticmethod
+    def compare_tokenizers(tokenizers, corpus) -> List[dict]:
+        """The ``evaluate`` report of every tokenizer on the same corpus (a string, or documents that are joined by newlines),
+        each with the tokenizer's class name under ``"tokenizer"``."""
+        text = corpus if isinstance(corpus, str) else "\n".join(corpus)
+        out = []
+        for t in tokenizers:
+            r = TokenizerEvaluator(t).evaluate(text)
+            r["tokenizer"] = type(t).__name__
+            out.append(r)
+        return out
+
     def evaluate(self, corpus: str) -> dict:
+        if not isinstance(corpus, str):
+            corpus = "\n".join(corpus)
         ids = self.tok.encode(corpus)
         back = self.tok.decode(ids)
         return {"compression_ratio": self.compression_ratio(corpus), "re_encoding_accuracy": self.re_encoding_accuracy(corpus),

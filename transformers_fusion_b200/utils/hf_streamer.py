@@ -66,6 +66,38 @@ class SimpleJSON:
         return v if isinstance(v, list) else []
 
     @staticmethod
+    def find_string(doc: str, key: str) -> str:
+        """The first string value stored under ``key`` anywhere in the document (depth first, in document order); "" if none."""
+        def walk(v):
+            if isinstance(v, dict):
+                if isinstance(v.get(key), str):
+                    return v[key]
+                for c in v.values():
+                    r = walk(c)
+                    if r is not None:
+                        return r
+            elif isinstance(v, list):
+                for c in v:
+                    r = walk(c)
+                    if r is not None:
+                        return r
+            return None
+        try:
+            return walk(json.loads(doc)) or ""
+        except ValueError:
+            return ""
+
+    @staticmethod
+    def find_all_strings_in_array(arr) -> List[str]:
+        """The string elements of a JSON array, given as text or as an already parsed list."""
+        if isinstance(arr, str):
+            try:
+                arr = json.loads(arr)
+            except ValueError:
+                return []
+        return [x for x in arr if isinstance(x, str)] if isinstance(arr, list) else []
+
+    @staticmethod
     def find_object(doc: str, key: str) -> dict:
         v = json.loads(doc).get(key, {})
         return v if isinstance(v, dict) else {}

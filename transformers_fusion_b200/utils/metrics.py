@@ -11,7 +11,7 @@ import math
 import time
 from collections import Counter
 from dataclasses import dataclass, field
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -223,6 +223,15 @@ class ModelEvaluator:
         r = EvalResult(name, accuracy=ok / max(1, n), correct=ok, total=n, total_tokens=n)
         self.results.append(r)
         return r
+
+    def run_all(self, eval_tokens, context: int = 512, generation: Optional[bool] = None) -> List[EvalResult]:
+        """Perplexity and next-token accuracy on ``eval_tokens`` and, where the model can be served (a CUDA device), the
+        generation-speed measurement; returns the results in that order."""
+        ctx = min(context, self.model.cfg.max_seq_len)
+        out = [self.evaluate_perplexity(eval_tokens, context=ctx), self.evaluate_accuracy(eval_tokens, context=ctx)]
+        if generation if generation is not None else self._device().type == "cuda":
+            out.append(self.evaluate_generation(prompt_len=min(32, max(1, self.model.cfg.max_seq_len // 4))))
+        return out
 
     def evaluate_generation(self, prompt_len=32, new_tokens=128, name="generation") -> EvalResult:
         from ..inference.engine import EngineConfig, InferenceEngine
