@@ -141,3 +141,29 @@ def test_fine_tuner_configure_run_and_block_selection(tmp_path):
     ft.apply_quant_update(torch.ones(512), w, "q16", lr=0.5)
     from transformers_fusion_b200.quant.qat import ste_roundtrip_
     assert torch.allclose(w, w0 - 0.5, atol=2e-3) and torch.allclose(ste_roundtrip_(w.clone(), "q16"), w, atol=1e-3) and not torch.equal(w, w0 - 0.5)
+
+
+def test_engine_step_counters_fisher_views_and_dora_magnitude_step():
+    m = tiny()
+    ids, lab = batch()
+    eng = RankAdapterEngine(m, RankAdapterConfig(rank=4, use_dora=True, learning_rate=1e-3, warmup_steps=1))
+    assert eng.step() == 0
+    eng.train_step(ids, lab)
+    assert eng.step() == 1
+    a = eng.adapters[0]
+    # autograd statement of the same thing: W' = m * V / |V| with V detached
+    V = (a.W0 + a.B @ a.A).detach()
+    mag = a.magnitude.detach().clone().requires_grad_(True)
+    G = torch.randn(a.out_dim, a.in_dim)
+    ((mag / V.norm(dim=1))[:, None] * V * G).sum().backward()
+    before = a.magnitude.detach().clone()
+    assert eng.magnitude_step([G] + [None] * (len(eng.adapters) - 1), 0.1) == 1
+    assert torch.allclose(a.magnitude.detach(), before - 0.1 * mag.grad, atol=1e-6)
+    assert eng.magnitude_step([torch.zeros(2, 2)], 0.1) == 0
+    plain = RankAdapterEngine(m, RankAdapterConfig(rank=4, use_dora=False))
+    assert plain.magnitude_step([G], 0.1) == 0
+    st = SelectiveFineTuner(m)
+    st.accumulate_fisher(ids, lab), st.accumulate_fisher(ids, lab)
+    f = st.fisher_diag()
+    assert len(f) == len(m.flat.params_list) and all(x.shape == p.shape for x, p in zip(f, m.flat.params_list))
+    assert float(sum(x.sum() for x in f)) == pytest.approx(float(st.fisher.sum()) / 2, rel=1e-5)

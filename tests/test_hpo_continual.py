@@ -155,3 +155,25 @@ def test_forgetting_benchmark_task_registry_and_transfer():
     assert fb.backward_transfer() == pytest.approx(-0.2) and fb.forward_transfer() == pytest.approx((0.0 + 1.5) / 2)
     m = fb.compute()
     assert m.num_tasks == 2 and m.max_forgetting == pytest.approx(0.4) and m.avg_forgetting == pytest.approx(0.2)
+
+
+def test_hpo_built_in_training_objective_restores_the_trainer():
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.trainer.hpo_nas import HPConfig, HPOEngine
+    from transformers_fusion_b200.trainer.trainer import DataLoader, TrainConfig, Trainer
+    m = DenseModel(TransformerConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=2, ffn_hidden_size=48, max_seq_len=32, init_std=0.1),
+                   dtype=torch.float32, seed=0)
+    t = Trainer(m).compile("adamw", TrainConfig(batch_size=4, seq_length=16, learning_rate=1e-3, warmup_steps=0, lr_schedule="CONSTANT", zero_stage=0))
+    base = torch.randint(0, 64, (16,), generator=torch.Generator().manual_seed(0))
+    dl = DataLoader(tokens=base.repeat(100), batch_size=4, seq_length=16)
+    h = HPOEngine(seed=0)
+    h.set_model(m)
+    h.set_trainer(t, dl, steps_per_budget=10)
+    w0 = m.flat.params.clone()
+    good = h._train_objective(HPConfig(id=0, lr=1e-2, weight_decay=0.0, warmup_steps=0), 2.0)
+    idle = h._train_objective(HPConfig(id=1, lr=1e-9, weight_decay=0.0, warmup_steps=0), 2.0)
+    assert good > idle                                            # a useful learning rate reaches a lower loss in 20 steps
+    assert torch.equal(m.flat.params, w0) and t.global_step == 0 and t.cfg.learning_rate == 1e-3 and t.opt.step_count == 0
+    assert h.evaluate_fn == h._train_objective

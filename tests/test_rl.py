@@ -70,10 +70,13 @@ def test_dpo_prefers_chosen():
     g = torch.Generator().manual_seed(3)
     c, r = torch.randint(0, 64, (4, 10), generator=g), torch.randint(0, 64, (4, 10), generator=g)
     mk = torch.ones(4, 10)
+    seen = []
+    t.set_log_callback(lambda loss, kl: seen.append((loss, kl)))
     l0, _ = t.train_step(c, r, mk, mk)
     for _ in range(25):
         l1, acc = t.train_step(c, r, mk, mk)
     assert l1 < l0 and acc == 1.0
+    assert len(seen) == 26 and seen[0] == (pytest.approx(l0), pytest.approx(0.0, abs=1e-5)) and seen[-1][1] > 0   # chosen answers got likelier
 
 
 def test_ppo_step_and_gae():
@@ -82,8 +85,11 @@ def test_ppo_step_and_gae():
     m = tiny(3)
     t = rl.PPOTrainer(m, lr=1e-3)
     ids = torch.randint(0, 64, (3, 10))
+    seen = []
+    t.set_log_callback(lambda pl, vl, ent, k: seen.append((pl, vl, ent, k)))
     loss, vloss, kl = t.train_step(ids, torch.ones(3, 10), torch.tensor([1.0, 0.0, -1.0]))
     assert loss == loss and vloss >= 0
+    assert seen == [(pytest.approx(loss), pytest.approx(vloss), seen[0][2], pytest.approx(kl))] and seen[0][2] > 0
 
 
 def test_reward_model_and_rollout_worker():

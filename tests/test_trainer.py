@@ -287,3 +287,53 @@ def test_dataloader_shuffle_augmentation_curriculum_and_streaming(tmp_path):
     ema.update()
     ema.set_decay(0.9)
     assert ema.decay == 0.9 and T.allclose(ema.shadow, t.model.flat.params.float() - 0.5)
+
+
+def test_adamw_built_in_schedule_reset_and_scheduler_get_lr():
+    from transformers_fusion_b200.trainer.optimizers import AdamW
+    m = tiny()
+    flat = m.flatten()
+    opt = AdamW(flat, lr=1e-2, weight_decay=0.0)
+    with pytest.raises(ValueError):
+        opt.set_schedule("triangle")
+    opt.set_schedule("warmup_cosine", warmup_steps=10, total_steps=110)
+    assert opt.scheduler_step(5) == pytest.approx(5e-3) and opt.scheduler_step(10) == pytest.approx(1e-2)
+    assert opt.scheduler_step(60) == pytest.approx(5e-3) and opt.scheduler_step(110) == pytest.approx(0.0, abs=1e-9)
+    opt.set_schedule("linear", total_steps=100)
+    assert opt.adjusted_lr(25) == pytest.approx(7.5e-3)
+    opt.set_schedule("cosine_restart", total_steps=100, restart_period=20)
+    assert opt.adjusted_lr(0) == pytest.approx(1e-2) and opt.adjusted_lr(20) == pytest.approx(5e-3) and opt.adjusted_lr(30) == pytest.approx(2.5e-3)
+    # the scheduled rate is the one the next step uses: rate 0 leaves the weights where they are
+    opt.set_schedule("linear", total_steps=10)
+    opt.scheduler_step(10)
+    before = flat.params.clone()
+    flat.grads.fill_(1.0)
+    opt.step()
+    assert torch.equal(flat.params, before) and opt.step_count == 1
+    opt.scheduler_step(0)
+    flat.grads.fill_(1.0)
+    opt.step()
+    assert not torch.equal(flat.params, before) and "m" in opt.state
+    opt.reset()
+    assert opt.state == {} and opt.step_count == 0 and opt.current_lr is None and torch.equal(opt.master, flat.params.float()) and opt.get_lr() == 1e-2
+    sch = S.LinearWarmupDecay(1.0, 10, 110)
+    assert sch.get_last_lr() == 1.0 and sch.get_lr(5) == pytest.approx(sch(5)) and sch.get_last_lr() == pytest.approx(sch(5))
+    assert S.CosineWarmupRestart(1.0, 0, 10).get_lr(5) == pytest.approx(S.CosineWarmupRestart(1.0, 0, 10)(5))
+
+
+def test_unified_trainer_inner_and_mixed_precision_restart():
+    m = tiny()
+    u = UnifiedTrainer(m)
+    assert u.inner() is None
+    with pytest.raises(RuntimeError):
+        u.set_log_callback(print)
+    u.configure(UnifiedTrainArgs(kind="dense", optimizer="adamw", batch_size=2, seq_length=16, lr=1e-3))
+    t = u.inner()
+    assert isinstance(t, Trainer)
+    cb = lambda *a: None
+    u.set_log_callback(cb)
+    assert t.log_cb is cb
+    m.flat.params.add_(1.0)                                    # weights changed behind the optimizer's back
+    assert t.init_mixed_precision() == 1.0 and torch.equal(t.opt.master, m.flat.params[t.opt.lo:t.opt.hi].float())
+    t.cfg.dynamic_loss_scale, t.loss_scale = True, 4.0
+    assert t.init_mixed_precision() == t.cfg.loss_scale

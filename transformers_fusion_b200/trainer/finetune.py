@@ -137,6 +137,26 @@ class RankAdapterEngine:
         self.opt.zero_grad(set_to_none=True)
         self.model.flat.zero_grad()
 
+    def step(self) -> int:
+        """Training steps taken so far."""
+        return self.step_count
+
+    @torch.no_grad()
+    def magnitude_step(self, dL_dW, lr: float) -> int:
+        """Plain gradient step on the DoRA magnitudes alone, from given gradients of the MERGED weights (one tensor per
+        adapter, shaped like the adapted matrix [out, in]; None or a wrong shape skips that adapter).  With the direction
+        V = W0 + B A held fixed, W' = m * V / |V| row by row, so dL/dm[o] = sum_k dL/dW'[o, k] V[o, k] / |V[o, :]|.
+        Returns how many adapters were stepped.  Reference counterpart: RankAdapterEngine::magnitude_step
+        (include/quant/fine_tuning.h:189-197)."""
+        n = 0
+        for a, g in zip(self.adapters, dL_dW):
+            if a.magnitude is None or g is None or tuple(g.shape) != (a.out_dim, a.in_dim):
+                continue
+            V = a.W0 + a.B @ a.A
+            a.magnitude.sub_(lr * (g.float().to(V.device) * V).sum(1) / V.norm(dim=1).clamp(min=1e-12))
+            n += 1
+        return n
+
     @torch.no_grad()
     def merge_into_base(self):
         self._materialise()
@@ -321,6 +341,12 @@ class SelectiveFineTuner:
         for _ in range(max_batches):
             self.fine_tune(*dl.next_batch())
 
+    def fisher_diag(self) -> List[torch.Tensor]:
+        """The accumulated Fisher diagonal (mean squared gradient over the anchor batches), one tensor per model parameter
+        in the flat buffer's order and shape."""
+        f = self.fisher / max(1, self.fisher_batches)
+        return [f[off:off + p.numel()].view(p.shape) for p, off in zip(self.flat.params_list, self.flat.offsets)]
+
     def freeze_all(self, freeze):
         self.frozen = freeze
 
@@ -420,6 +446,9 @@ class KnowledgeExpansionEngine:
     def clear_grads(self):
         if self.opt:
             self.opt.zero_grad(set_to_none=True)
+
+    def step(self) -> int:
+        return self.step_count
 
     def save(self, path=None):
         w = codec.QuantWriter(path or self.cfg.output_path, struct.pack("<II", len(self.slots), self.model.cfg.hidden_size), flags=2)

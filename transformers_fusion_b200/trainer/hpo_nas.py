@@ -111,6 +111,51 @@ class HPOEngine:
     def set_search_space(self, s):
         self.space = s
 
+    # ---- a ready-made objective: short training runs of a given trainer (reference: HPOEngine::set_trainer / set_model,
+    # include/quant/hpo_nas.h:146-147)
+    def set_model(self, model):
+        self.model = model
+
+    def set_trainer(self, trainer, loader=None, steps_per_budget: int = 8):
+        """Score a configuration by training ``trainer``'s model from its CURRENT weights for ``budget x steps_per_budget``
+        steps with the configuration's learning rate, weight decay and warm-up, and returning minus the mean loss of the last
+        quarter of the steps.  Weights, optimizer state and step counter are put back after every trial, so trials are
+        comparable.  Used when no ``evaluate`` callable was given."""
+        self.trainer, self.loader, self.steps_per_budget = trainer, loader, steps_per_budget
+        self.model = getattr(trainer, "model", getattr(self, "model", None))
+        if self.evaluate_fn is None:
+            self.evaluate_fn = self._train_objective
+
+    def _train_objective(self, c: HPConfig, budget: float) -> float:
+        import torch
+        t, dl = self.trainer, self.loader
+        if dl is None:
+            raise RuntimeError("set_trainer needs a data loader for the built-in objective")
+        flat = t.model.flat
+        w0 = flat.params.clone()
+        opt_sd = {k: (v.clone() if torch.is_tensor(v) else ({a: b.clone() for a, b in v.items()} if isinstance(v, dict) else v))
+                  for k, v in t.opt.state_dict().items()} if hasattr(t.opt, "state_dict") else None
+        cfg0 = (t.cfg.learning_rate, t.cfg.weight_decay, t.cfg.warmup_steps, t.global_step)
+        t.cfg.learning_rate, t.cfg.weight_decay, t.cfg.warmup_steps, t.global_step = c.lr, c.weight_decay, c.warmup_steps, 0
+        for o in (t.opt, getattr(t, "engine", None) and getattr(t.engine, "opt", None)):
+            if o is not None and hasattr(o, "wd"):
+                o.wd = c.weight_decay
+        n = max(1, int(round(budget * self.steps_per_budget)))
+        losses = []
+        try:
+            for _ in range(n):
+                if hasattr(dl, "has_next") and not dl.has_next():
+                    dl.reset()
+                losses.append(float(t.train_step(*dl.next_batch())))
+        finally:
+            flat.params.copy_(w0)
+            if opt_sd is not None:
+                t.opt.load_state_dict(opt_sd)
+            t.cfg.learning_rate, t.cfg.weight_decay, t.cfg.warmup_steps, t.global_step = cfg0
+        tail = losses[-max(1, n // 4):]
+        c.val_loss = sum(tail) / len(tail)
+        return -c.val_loss if math.isfinite(c.val_loss) else -1e30
+
     def get_search_space(self):
         return self.space
 

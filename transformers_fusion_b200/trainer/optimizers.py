@@ -78,6 +78,17 @@ class FlatOptimizer:
     def zero_grad(self):
         self.flat.grads.zero_()
 
+    def reset(self):
+        """Forget the optimizer state (moments, step count, a built-in schedule's position); the weights stay as they are."""
+        self.state.clear()
+        self.step_count = 0
+        self.master.copy_(self.flat.params[self.lo:self.hi].float())
+        if hasattr(self, "current_lr"):
+            self.current_lr = None
+
+    def get_lr(self) -> float: return self.lr
+    def set_lr(self, lr: float): self.lr = float(lr)
+
     def state_dict(self):
         return {"step": self.step_count, "lr": self.lr, "master": self.master, "state": self.state}
 
@@ -122,8 +133,43 @@ class Adam(FlatOptimizer):
 
 
 class AdamW(Adam):
+    """Decoupled weight decay.  It can carry its own learning-rate schedule (reference: AdamW::set_schedule /
+    scheduler_step, include/quant/optimizer.h:60-63, src/trainer/optimizer.cpp:54-90): after ``scheduler_step(s)`` the next
+    ``step()`` without an explicit rate uses the scheduled one."""
     name = "adamw"
     decoupled = True
+    SCHEDULES = ("constant", "cosine", "linear", "warmup_cosine", "cosine_restart")
+    current_lr = None
+
+    def set_schedule(self, schedule: str, warmup_steps: int = 0, total_steps: int = 0, restart_period: int = 0):
+        schedule = schedule.lower()
+        if schedule not in self.SCHEDULES:
+            raise ValueError(f"unknown schedule {schedule!r}; one of {self.SCHEDULES}")
+        self._sched = (schedule, int(warmup_steps), int(total_steps), int(restart_period))
+
+    def adjusted_lr(self, step: int) -> float:
+        kind, warm, total, period = getattr(self, "_sched", ("constant", 0, 0, 0))
+        if total <= 0 or kind == "constant":
+            return self.lr
+        ratio = min(1.0, step / total)
+        if kind == "cosine":
+            return self.lr * 0.5 * (1.0 + math.cos(math.pi * ratio))
+        if kind == "linear":
+            return self.lr * (1.0 - ratio)
+        if kind == "warmup_cosine":
+            if step < warm:
+                return self.lr * step / warm
+            r = min(1.0, (step - warm) / max(1, total - warm))
+            return self.lr * 0.5 * (1.0 + math.cos(math.pi * r))
+        p = period if period > 0 else max(1, total // 4)            # cosine with restarts; every cycle starts at half the last peak
+        return self.lr * 0.5 ** (step // p) * 0.5 * (1.0 + math.cos(math.pi * (step % p) / p))
+
+    def scheduler_step(self, step: int) -> float:
+        self.current_lr = self.adjusted_lr(step)
+        return self.current_lr
+
+    def step(self, lr: Optional[float] = None):
+        super().step(self.current_lr if lr is None and self.current_lr is not None else lr)
 
 
 class Adamax(FlatOptimizer):

@@ -175,6 +175,11 @@ def gae(rewards, values, gamma=0.99, lam=0.95):
     return adv, adv + values[:T]
 
 
+def _set_log_callback(self, cb):
+    """``cb`` is called at the end of every train_step (PPO: policy loss, value loss, entropy, KL; DPO: loss, KL)."""
+    self.log_cb = cb
+
+
 class PPOTrainer(_RLBase):
     def __init__(self, model, tokenizer=None, clip=0.2, gamma=0.99, lam=0.95, kl_target=0.01, kl_coef=0.1, lr=1e-5,
                  value_coef=0.5):
@@ -239,6 +244,10 @@ class PPOTrainer(_RLBase):
         (self.value_coef * vloss).backward()
         self.value_opt.step()
         kl = self._last_kl = float(approx_kl.detach())
+        if getattr(self, "log_cb", None):
+            # policy loss, value loss, mean entropy estimate of the action tokens (-log-prob of the taken actions), KL to the old policy
+            ent = float((-(lp.detach()) * m).sum() / m.sum().clamp(min=1))
+            self.log_cb(float(loss.detach()), float(vloss.detach()), ent, kl)
         if kl > 1.5 * self.kl_target:                 # adaptive KL coefficient
             self.kl_coef *= 1.5
         elif kl < self.kl_target / 1.5:
@@ -271,12 +280,19 @@ class DPOTrainer(_RLBase):
         loss = -TF.logsigmoid(margin).mean()
         self._backward_and_step(loss)
         self._last_loss = float(loss.detach())
+        if getattr(self, "log_cb", None):
+            # loss and the sequence-level KL estimate to the frozen reference on the chosen answers
+            self.log_cb(self._last_loss, float((pc.detach() - rc).mean()))
         return self._last_loss, float((margin > 0).float().mean())
 
 
 # ------------------------------------------------------------------------------------------------
 # RLVR: verifiable rewards
 # ------------------------------------------------------------------------------------------------
+PPOTrainer.set_log_callback = _set_log_callback
+DPOTrainer.set_log_callback = _set_log_callback
+
+
 class RLVRTrainer(GRPOTrainer):
     """GRPO whose reward is a verifier: 1 when the expected answer appears in the completion, else 0."""
 

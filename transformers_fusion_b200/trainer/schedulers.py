@@ -42,6 +42,14 @@ class Scheduler:
     def __init__(self, base_lr: float):
         self.base_lr = base_lr
 
+    def get_lr(self, step: int) -> float:
+        """The reference's spelling of a call (include/quant/scheduler.h:11); the value is remembered as ``last_lr``."""
+        self.last_lr = float(self(step))
+        return self.last_lr
+
+    def get_last_lr(self) -> float:
+        return getattr(self, "last_lr", self.base_lr)
+
     def __call__(self, step: int) -> float:
         raise NotImplementedError
 

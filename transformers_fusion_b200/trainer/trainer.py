@@ -262,6 +262,20 @@ class Trainer:
             self.model.mtp_loss_weight = c.mtp_loss_weight
         return self
 
+    def init_mixed_precision(self) -> float:
+        """(Re)start mixed-precision training: the optimizer's fp32 master weights are re-read from the model's
+        compute-dtype weights, and for an fp16 model dynamic loss scaling is switched on at the configured scale (bf16 and
+        fp32 have fp32's exponent range and train unscaled).  Returns the loss scale in effect."""
+        c = self.cfg
+        if self.opt is not None and hasattr(self.opt, "master"):
+            lo, hi = getattr(self.opt, "lo", 0), getattr(self.opt, "hi", self.model.flat.numel)
+            self.opt.master.copy_(self.model.flat.params[lo:hi].float())
+        if self.model.flat.params.dtype == torch.float16:
+            c.dynamic_loss_scale = True
+        self.loss_scale = c.loss_scale if c.dynamic_loss_scale else 1.0
+        self._good_steps = 0
+        return self.loss_scale
+
     def set_log_callback(self, cb): self.log_cb = cb
     def set_epoch_callback(self, cb): self.epoch_cb = cb
     def set_step_callback(self, cb): self.step_cb = cb
@@ -735,6 +749,15 @@ class UnifiedTrainer:
 
     def train_step_once(self, ids, labels) -> float:
         return self.trainer.train_step(ids, labels)
+
+    def inner(self) -> Optional["Trainer"]:
+        """The trainer built by ``configure`` (None before it)."""
+        return self.trainer
+
+    def set_log_callback(self, cb):
+        if self.trainer is None:
+            raise RuntimeError("configure() first")
+        self.trainer.set_log_callback(cb)
 
     def save_checkpoint(self, path): self.trainer.save_checkpoint(path)
     def load_checkpoint(self, path): self.trainer.load_checkpoint(path)
