@@ -238,3 +238,36 @@ def test_small_accessors_locks_counters_shapes_verifier_and_json_helpers():
     rl.set_limits(10.0, 1.0)
     now[0] += 1.0
     assert rl.max_requests_per_sec() == 10.0 and rl.burst_size() == 1.0 and [rl.allow("a") for _ in range(2)] == [True, False]
+
+
+def test_status_rotary_object_replay_entry_and_loader_config(tmp_path):
+    from transformers_fusion_b200.utils import core as C
+    from transformers_fusion_b200.models.dense import RotaryEmbedding
+    from transformers_fusion_b200.trainer.continual import CompressedReplayBuffer
+    from transformers_fusion_b200.trainer.trainer import DataLoader, DataLoaderConfig
+    assert C.Status.success() and C.Status.success().msg == "" and C.Status.error("bad").msg == "bad" and not C.Status.error("bad")
+    r = RotaryEmbedding(8, 32)
+    x = torch.randn(2, 3, 5, 8)
+    ref = x.clone()
+    half = 4
+    pos = torch.arange(4, 9).float()
+    inv = 10000.0 ** (-torch.arange(half).float() * 2 / 8)
+    ang = pos[:, None] * inv[None]
+    want = torch.cat([ref[..., :half] * ang.cos() - ref[..., half:] * ang.sin(), ref[..., half:] * ang.cos() + ref[..., :half] * ang.sin()], -1)
+    assert r.apply(x, 4, 5) is x and torch.allclose(x, want, atol=1e-5) and r.attn_scale_mult() == 1.0
+    y = RotaryEmbedding(8, 64, scaling_mode="yarn", scaling_factor=4.0, original_max_seq_len=16, yarn_attn_factor=1.0)
+    assert y.attn_scale_mult() == pytest.approx(0.1 * math.log(4.0) + 1.0, rel=1e-6)
+    b = CompressedReplayBuffer(8)
+    b.insert(torch.arange(4.0), torch.ones(4), task_id=3)
+    assert b.at(0).task_id == 3
+    with pytest.raises(IndexError):
+        b.at(1)
+    p = tmp_path / "c.txt"
+    p.write_text("abcdefghij" * 40)
+    cfg = DataLoaderConfig(data_path=str(p), batch_size=2, seq_length=8, world_size=2, rank=1, seed=7)
+    dl = DataLoader.from_config(cfg)
+    assert dl.config() is cfg and dl.num_batches() == (400 - 1) // (2 * 8 * 2)
+    ids, lab = dl.next_batch_with_labels()
+    assert ids.shape == (2, 8) and torch.equal(ids[:, 1:], lab[:, :-1])
+    plain = DataLoader(tokens=torch.arange(100), batch_size=2, seq_length=4)
+    assert plain.config().batch_size == 2 and plain.config().seq_length == 4 and plain.config().shuffle_buffer == 0

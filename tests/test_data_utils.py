@@ -300,3 +300,42 @@ def test_tokenizer_evaluator_comparison_and_report():
     assert reps[0]["corpus_size_bytes"] == len("hello world\nsecond line")
     text = TokenizerEvaluator.report_string(reps[0])
     assert "compression_ratio" in text and "total_tokens" in text and len(text.splitlines()) == len(reps[0])
+
+
+def test_streaming_batches_over_token_and_parquet_shards(tmp_path):
+    a, b = tmp_path / "a.tok", tmp_path / "b.tok"
+    a.write_text(" ".join(str(i) for i in range(0, 20)))
+    b.write_text(" ".join(str(i) for i in range(100, 120)))
+    ds = D.StreamingDataset([str(a)], seq_len=4)
+    ds.add_shard(str(b))
+    assert ds.shards_loaded() == 2 and ds.epochs_completed() == 0 and ds.total_tokens() == 0
+    x, y = ds.next_batch(3)
+    assert x.tolist() == [[0, 1, 2, 3], [5, 6, 7, 8], [10, 11, 12, 13]] and torch.equal(y, x + 1) and ds.total_tokens() == 12
+    seen = [x]
+    for _ in range(2):
+        seen.append(ds.next_batch(3)[0])
+    assert seen[1].tolist()[0] == [15, 16, 17, 18] and seen[1].tolist()[1] == [100, 101, 102, 103]
+    assert ds.epochs_completed() == 1 and seen[2][-1].tolist() == [0, 1, 2, 3]        # wrapped around to the first shard
+    assert D.StreamingDataset([str(a)], seq_len=64).next_batch(1) is None           # less than one window in the shards
+    ds.shuffle_shards()
+    assert ds.next_batch(1)[0][0, 0].item() in (0, 100)
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    for k in range(2):
+        pq.write_table(pa.table({"text": ["abcdefgh" * 4, None, "ijklmnop" * 4][: 3 - k]}), tmp_path / f"s{k}.parquet")
+    pds = D.ParquetStreamingDataset(str(tmp_path), vocab_size=64)
+    assert pds.shards_loaded() == 2 and pds.size() == 5
+    x, y = pds.next_batch(2, 8)
+    want = [c % 64 for c in ("abcdefgh" * 4).encode()]
+    assert x[0].tolist() == want[:8] and y[0].tolist() == want[1:9] and x[1].tolist() == want[9:17] and int(x.max()) < 64
+    n = 0
+    while pds.epochs_completed() == 0:
+        pds.next_batch(2, 8)
+        n += 1
+    assert n >= 2 and pds.total_tokens() == (n + 1) * 16
+    with pytest.raises(ValueError):
+        pds.add_shard(str(a))
+    empty = D.ParquetStreamingDataset("", 64, seq_len=8)
+    assert empty.shards_loaded() == 0 and empty.next_batch(1) is None
+    empty.add_shard(str(tmp_path / "s1.parquet"))
+    assert empty.next_batch(1)[0].shape == (1, 8)

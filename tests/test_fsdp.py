@@ -226,3 +226,16 @@ def test_offload_engine_and_manager_reference_verbs():
     assert G.memory_saved_bytes() == 1500 and G.compute_overhead() == 0.5
     G.reset_stats()
     assert G.activations_saved() == 0
+
+
+def test_zero_optimizer_parameter_counts_and_checkpoint_budget_access():
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.parallel.fsdp import ActivationCheckpoint, ZeroOptimizer
+    m = DenseModel(TransformerConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, ffn_hidden_size=64, max_seq_len=16), device="cpu",
+                   dtype=torch.float32, seed=0)
+    z = ZeroOptimizer(m, 0, 1, stage=1)
+    assert z.total_params() == len(m.flat.params_list) == z.owned_params() and z.register_model_params() == z.total_params()
+    ac = ActivationCheckpoint()
+    ac.mutable_budget().total_bytes = 12345
+    assert ac.budget.total_bytes == 12345

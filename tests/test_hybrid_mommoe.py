@@ -84,6 +84,14 @@ def test_native_quant_moe_model_steps():
     assert mets[-1].quant8 + mets[-1].quant + mets[-1].quant1 > 0 and 0 < mets[-1].active_params < mets[-1].total_params
     rep = nm.memory_report()
     assert rep["bytes"] < rep["fp32_bytes"] and rep["stored_bits_per_weight"] < 16
+    # the step in its parts gives the same result as step()
+    a, b = NativeQUANTMoEModel(cfg, seed=1), NativeQUANTMoEModel(cfg, seed=1)
+    met = a.step(ids, labels, 1e-3, 5e-2)
+    loss = b.backward(ids, labels)
+    frozen = b.apply_update(1e-3, 5e-2)
+    assert loss == pytest.approx(met.loss) and 100.0 * frozen == pytest.approx(met.frozen_pct)
+    assert all(torch.equal(pa, pb) for pa, pb in zip(a.model.parameters(), b.model.parameters()))
+    assert "x smaller" in b.print_memory_report()
 
 
 def test_modality_router_stand_alone_losses_and_accessors():

@@ -25,6 +25,12 @@ def test_store_allocation_and_roundtrip():
     assert set(torch.unique(st.indices.view(-1, 128)[5]).tolist()) <= {0, 1, 2}
     assert 2.0 < st.bits_per_weight() < 3.0
     assert st.get_weight(3) == pytest.approx(float(d[3]))
+    assert st.block_size() == 128 and st.get_format(0) == Q8 and st.get_format(5 * 128 + 3) == int(st.formats[5])
+    i = 5 * 128 + 3
+    assert st.get_index(i) == int(st.indices[i]) and st.get_scale(i) == float(st.scales[5])
+    assert st.indices_data() is st.indices and st.block_scales_data() is st.scales and st.formats_data() is st.formats
+    assert NativeQWeightStore.global_codebook().numel() == 256 and NativeQWeightStore.global_quant4_codebook().numel() == 16
+    assert torch.equal(NativeQWeightStore.global_codebook(), st.cb8)
 
 
 def test_quant_update_moves_toward_target():
@@ -59,6 +65,12 @@ def test_native_trainer_runs_through_transition(tmp_path):
     t2 = NativeQUANTTrainer(m2, tr.cfg)
     t2.load_checkpoint(str(tmp_path / "n.pt"))
     assert torch.equal(m2.flat.params, m.flat.params) and t2.native
+    # the warm-up as one call: stops after warmup_steps batches and switches to the quantised store
+    t3 = NativeQUANTTrainer(DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0), tr.config())
+    assert t3.config() is tr.cfg and math.isfinite(t3.warmup_phase([(ids, labels)] * 25)) and t3.native and t3.step_count == 10
+    t4 = NativeQUANTTrainer(DenseModel(cfg, device="cpu", dtype=torch.float32, seed=0), tr.config())
+    t4.warmup_phase([(ids, labels)] * 3)
+    assert t4.native and t4.step_count == 3                    # fewer batches than warm-up steps: still ends in the store
 
 
 def test_training_utils():

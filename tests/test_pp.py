@@ -32,3 +32,16 @@ def test_pipeline_matches_single_process(tmp_path):
         assert r["tied_grad_err"] < 1e-5 and r["tied_param_err"] < 1e-5
     assert res[1]["fwd_logits_err"] < 1e-4 and res[1]["fwd_loss_err"] < 1e-4
     assert all(r["two_call_loss"] and r["stage_params"] > 0 for r in res)
+
+
+def test_stage_and_context_accessors():
+    import torch
+    from transformers_fusion_b200.models.config import TransformerConfig
+    from transformers_fusion_b200.models.dense import DenseModel
+    from transformers_fusion_b200.parallel.pp import PipelineParallel, PipelineStage
+    m = DenseModel(TransformerConfig(vocab_size=32, hidden_size=16, num_layers=4, num_heads=2, ffn_hidden_size=32, max_seq_len=16), device="cpu",
+                   dtype=torch.float32, seed=0)
+    pp = PipelineParallel(m, 2, 1)
+    st = pp.stage()
+    assert isinstance(st, PipelineStage) and (st.layer_start, st.layer_end, st.device_id) == (2, 4, 0) and st.model_segment is m
+    assert pp.context() is pp.ctx and pp.context().rank == 1

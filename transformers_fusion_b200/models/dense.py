@@ -52,6 +52,23 @@ class RotaryEmbedding:
     def __call__(self, x, n_heads: int, seq_len: int, pos_offset: int = 0):
         return self.apply_(x.clone(), n_heads, seq_len, pos_offset)
 
+    def apply(self, x: torch.Tensor, seq_start: int, seq_len: int) -> torch.Tensor:
+        """The reference's form (include/quant/transformer.h:93): x [batch, heads, seq_len, head_dim] (or [heads, seq_len,
+        head_dim]) is rotated in place for positions seq_start .. seq_start + seq_len - 1 and returned."""
+        D = self.head_dim
+        lead = x.shape[:-2]
+        assert x.shape[-1] == D and x.shape[-2] == seq_len
+        flat = x.reshape(-1, seq_len, D)                                   # [B * heads, S, D]: one "head" per row block
+        rows = flat.reshape(-1, D).contiguous()                            # [(B * heads) * S, D], positions cycle every S rows
+        F.rope_(rows, self.cos, self.sin, 1, D, seq_len, seq_start)
+        x.copy_(rows.view(*lead, seq_len, D))
+        return x
+
+    def attn_scale_mult(self) -> float:
+        """The factor YaRN scaling puts on the attention logits' inputs (it is already folded into the cos / sin tables
+        here, so q and k each carry it once); 1 for the other modes."""
+        return float(self.cos[0, 0])                                       # cos(0) * mscale
+
 
 class FlatBuffers:
     """Contiguous parameter / gradient storage.

@@ -300,6 +300,16 @@ class ZeroOptimizer:
         lo, hi = self.engine.shard
         return hi - lo
 
+    def total_params(self) -> int:
+        """Parameter tensors registered with the optimizer."""
+        return len(self.model.flat.params_list)
+
+    def owned_params(self) -> int:
+        """Parameter tensors of which this rank's contiguous shard holds at least one element."""
+        lo, hi = self.engine.shard
+        flat = self.model.flat
+        return sum(1 for p, off in zip(flat.params_list, flat.offsets) if off < hi and off + p.numel() > lo)
+
     def get_shard(self, i=0):
         lo, hi = self.engine.shard
         return self.model.flat.params[lo:hi]
@@ -738,6 +748,7 @@ class ActivationCheckpoint:
         self.total_saved = self.total_recomputed = 0
 
     def set_budget(self, b: MemoryBudget): self.budget = b
+    def mutable_budget(self) -> MemoryBudget: return self.budget
     def regions(self) -> List[RegionInfo]: return list(self._regions)
     def total_activations_saved(self) -> int: return self.total_saved
     def total_activations_recomputed(self) -> int: return self.total_recomputed

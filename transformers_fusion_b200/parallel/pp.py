@@ -12,6 +12,7 @@ GPipe :150-240, 1F1B :250-420, send/recv via ctx.broadcast :301-341), DualPipe :
 from __future__ import annotations
 
 import time
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch
@@ -37,6 +38,14 @@ def split_model(num_layers: int, num_stages: int, balance_weights: Optional[Sequ
     return [(min(num_layers, s * per), min(num_layers, (s + 1) * per)) for s in range(num_stages)]
 
 
+@dataclass
+class PipelineStage:
+    device_id: int
+    layer_start: int
+    layer_end: int
+    model_segment: object
+
+
 class PipelineParallel:
     def __init__(self, model, num_stages: int, stage_id: int, ctx: Optional[DistributedContext] = None,
                  num_microbatches: int = 4, balance_weights=None, stage_ranks: Optional[Sequence[int]] = None):
@@ -56,6 +65,14 @@ class PipelineParallel:
         self.loss_sum = None
 
     # ---- configuration
+    def context(self) -> DistributedContext:
+        return self.ctx
+
+    def stage(self) -> "PipelineStage":
+        """What this rank owns: its device, the half-open layer range and the model (whose other layers are never run)."""
+        dev = self.model.tok_embeddings.device
+        return PipelineStage(dev.index if dev.type == "cuda" and dev.index is not None else 0, self.lo, self.hi, self.model)
+
     def set_num_microbatches(self, m):
         self.num_microbatches = max(1, int(m))
 

@@ -51,6 +51,12 @@ class CompressedReplayBuffer:
         if len(self.entries) > self.capacity:
             self.compact()
 
+    def at(self, idx: int) -> "CompressedReplayEntry":
+        """The stored entry at a position (IndexError outside the buffer)."""
+        if not 0 <= idx < len(self.entries):
+            raise IndexError(f"replay entry {idx} of {len(self.entries)}")
+        return self.entries[idx]
+
     def compact(self):
         """Drop the least important entries down to ``spill_threshold`` of the capacity."""
         keep = int(self.capacity * self.spill)

@@ -199,6 +199,24 @@ class NativeQWeightStore:
         b = i // self.bs
         return float(self._cb(int(self.formats[b]))[int(self.indices[i])] * self.scales[b])
 
+    # ---- element / buffer access (reference: NativeQWeightStore, include/quant/native_weight.h:127-143)
+    def block_size(self) -> int: return self.bs
+    def get_index(self, i: int) -> int: return int(self.indices[i])
+    def get_scale(self, i: int) -> float: return float(self.scales[i // self.bs])
+    def get_format(self, i: int) -> int: return int(self.formats[i // self.bs])
+    def indices_data(self) -> torch.Tensor: return self.indices          # uint8 [num_blocks * block_size], writable
+    def block_scales_data(self) -> torch.Tensor: return self.scales      # fp32 [num_blocks], writable
+    def formats_data(self) -> torch.Tensor: return self.formats          # uint8 [num_blocks]
+
+    @staticmethod
+    def global_codebook() -> torch.Tensor:
+        """The shared 256-entry codebook of the 8-bit blocks (every store uses the same table)."""
+        return _codebook(256)
+
+    @staticmethod
+    def global_quant4_codebook() -> torch.Tensor:
+        return _codebook(16)
+
     def bits_per_weight(self):
         c = self.counts()
         return (8 * c[Q8] + 2 * c[Q1] + 4 * c[Q4]) / max(1, self.nb) + 32.0 / self.bs
@@ -226,6 +244,22 @@ class NativeQUANTTrainer:
 
     def weight_store(self):
         return self.store
+
+    def config(self) -> NativeTrainConfig:
+        return self.cfg
+
+    def warmup_phase(self, batches) -> float:
+        """The floating-point warm-up as one call: a warm-up step on every (ids, labels) batch until ``warmup_steps`` steps
+        have been taken or the batches run out, then the transition to the quantised store.  Returns the last loss."""
+        loss = 0.0
+        for ids, labels in batches:
+            if self.native or self.step_count >= self.cfg.warmup_steps:
+                break
+            self.step_count += 1
+            loss = self.warmup_step(ids, labels)
+        if not self.native:
+            self.transition()
+        return loss
 
     def _update_sensitivity(self):
         a = 1.0 / self.cfg.sens_window
@@ -392,7 +426,7 @@ class NativeQUANTMoEModel:
         m.flat.zero_grad()
         loss = float(m.forward_backward(ids, labels))
         met = NativeMoEMetrics(loss=loss, total_params=self.total_params_)
-        met.lb_loss = float(m.last_aux) if m.last_aux is not None else 0.0
+        met.lb_loss = float(m.last_aux.detach()) if m.last_aux is not None else 0.0
         met.grad_norm = float(m.flat.grads.norm())
         stored = {id(p) for p, _ in self.stores}
         frozen = []
@@ -411,6 +445,36 @@ class NativeQUANTMoEModel:
         per_expert = (m.layers[0].gate_up.numel() + m.layers[0].down.numel()) // self.cfg.num_experts
         met.active_params = self.total_params_ - self.cfg.num_layers * (self.cfg.num_experts - self.cfg.top_k) * per_expert
         return met
+
+    # ---- the step in its three parts (reference: forward / backward / apply_update, include/quant/native_quant_moe.h:44-46)
+    def backward(self, ids, labels) -> float:
+        """Forward and backward through the fused training path: gradients land in the model's flat gradient buffer (the
+        stores are created from the current weights on first use).  Returns the loss."""
+        if not self.stores:
+            self.init_from_fp32()
+        self.model.flat.zero_grad()
+        return float(self.model.forward_backward(ids, labels))
+
+    def apply_update(self, lr_scale: float, lr_weight: float) -> float:
+        """Take the gradients left by ``backward``: quantised update of every stored tensor, plain SGD on the rest, then the
+        stores are expanded into the model again.  Returns the mean fraction of weights whose index did not move."""
+        m = self.model
+        stored = {id(p) for p, _ in self.stores}
+        frozen = [st.apply_quant_update(p.main_grad.reshape(-1).float(), lr_scale, lr_weight) for p, st in self.stores]
+        with torch.no_grad():
+            for p in m.parameters():
+                if id(p) not in stored and getattr(p, "main_grad", None) is not None:
+                    p.data.add_(p.main_grad.to(p.dtype), alpha=-lr_weight)
+        self.push_weights()
+        return sum(frozen) / max(1, len(frozen))
+
+    def print_memory_report(self) -> str:
+        r = self.memory_report()
+        text = (f"native-quant MoE memory: {r['stored_params']:,} stored weights at {r['stored_bits_per_weight']:.2f} bits, "
+                f"{r['float_params']:,} floating-point weights; {r['bytes'] / 1e6:.2f} MB vs {r['fp32_bytes'] / 1e6:.2f} MB in fp32 "
+                f"({r['fp32_bytes'] / max(1.0, r['bytes']):.1f}x smaller)")
+        print(text)
+        return text
 
     def memory_report(self) -> dict:
         bits = sum(st.bits_per_weight() * st.size() for _, st in self.stores)

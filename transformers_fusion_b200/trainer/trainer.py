@@ -73,6 +73,21 @@ class TrainMetrics:
     epoch: int = 0
 
 
+@dataclass
+class DataLoaderConfig:
+    """The reference's loader description (include/quant/dataloader.h:16-27)."""
+    data_path: str = ""
+    batch_size: int = 8
+    seq_length: int = 2048
+    shuffle_buffer: int = 10000
+    num_epochs: int = 1
+    num_workers: int = 1
+    seed: int = 42
+    drop_last: bool = True
+    world_size: int = 1
+    rank: int = 0
+
+
 class DataLoader:
     """Token stream -> (ids, labels) batches of [batch, seq]; labels are ids shifted left by one.
     Source: a text file tokenised with ``tokenizer`` (reference DataLoader, include/quant/trainer.h:78-159),
@@ -100,6 +115,28 @@ class DataLoader:
 
     def reset(self):
         self.offset = 0
+
+    @classmethod
+    def from_config(cls, cfg: DataLoaderConfig, tokenizer=None, device="cpu") -> "DataLoader":
+        """A loader described by a ``DataLoaderConfig``: the text file at ``data_path`` tokenised with ``tokenizer`` (bytes
+        when none is given), this rank's share of every global batch, shuffled per epoch when ``shuffle_buffer`` > 0."""
+        if tokenizer is None:
+            from ..tokenizer import ByteTokenizer
+            tokenizer = ByteTokenizer()
+        dl = cls(tokenizer, cfg.data_path, cfg.batch_size, cfg.seq_length, device=device, rank=cfg.rank, world=cfg.world_size)
+        dl._config = cfg
+        if cfg.shuffle_buffer > 0:
+            dl._order = torch.randperm(max(len(dl), 1), generator=torch.Generator().manual_seed(cfg.seed)).tolist()
+        return dl
+
+    def config(self) -> DataLoaderConfig:
+        """The loader's description; for a loader built directly it is filled in from the constructor's arguments."""
+        if getattr(self, "_config", None) is None:
+            self._config = DataLoaderConfig(batch_size=self.B, seq_length=self.S, shuffle_buffer=0, world_size=self.world, rank=self.rank)
+        return self._config
+
+    def next_batch_with_labels(self):
+        return self.next_batch()
 
     # ---- the reference's verbs (include/quant/trainer.h:78-159)
     def num_batches(self) -> int: return len(self)

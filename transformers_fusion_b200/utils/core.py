@@ -83,6 +83,12 @@ class Status:
     @staticmethod
     def error(msg: str) -> "Status": return Status(False, msg)
 
+    @staticmethod
+    def success() -> "Status": return Status(True, "")
+
+    @property
+    def msg(self) -> str: return self.message
+
     def __bool__(self) -> bool: return self.ok
 
 

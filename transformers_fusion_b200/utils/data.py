@@ -294,6 +294,39 @@ class StreamingDataset:
     def num_chunks(self) -> int:
         return self.size() // max(1, self.seq_len or 1)
 
+    # ---- batch form (reference: StreamingDataset, include/quant/parquet_streamer.h:36-63)
+    def add_shard(self, path: str):
+        self.paths.append(str(path))
+        self._order.append(len(self.paths) - 1)
+        self._done = False
+
+    def shuffle_shards(self): self.shuffle()
+    def shards_loaded(self) -> int: return len(self.paths)
+    def epochs_completed(self) -> int: return getattr(self, "_epochs", 0)
+    def total_tokens(self) -> int: return getattr(self, "_served", 0)
+
+    def next_batch(self, batch_size: int, seq_len: Optional[int] = None):
+        """(input_ids, labels), both int64 [batch_size, seq_len], cut from the stream as consecutive windows of seq_len + 1
+        ids.  When the shards run out before the batch is full the stream starts over (one more epoch completed) and the
+        batch is filled from the start; None when the shards hold less than one window."""
+        S = seq_len or self.seq_len
+        rows: List[List[int]] = []
+        wrapped = False
+        while len(rows) < batch_size:
+            ids = self.next_chunk(S + 1)
+            if len(ids) < S + 1:
+                if wrapped:
+                    return None
+                self._epochs = self.epochs_completed() + 1
+                self.reset()
+                wrapped = True
+                continue
+            rows.append(ids)
+            wrapped = False
+        t = torch.tensor(rows, dtype=torch.long)
+        self._served = self.total_tokens() + batch_size * S
+        return t[:, :-1].contiguous(), t[:, 1:].contiguous()
+
     def __iter__(self) -> Iterator[str]:
         for p in self.paths:
             with open(p, "r", encoding="utf-8", errors="ignore") as f:
@@ -834,6 +867,46 @@ class ParquetReader:
             for v in self.pf.read_row_group(g, columns=[self.column]).column(0).to_pylist():
                 if v is not None:
                     yield v
+
+
+class ParquetStreamingDataset(StreamingDataset):
+    """The same batch interface over Parquet shards: the text column of every shard is tokenised on the fly (UTF-8 bytes
+    folded into the vocabulary when no tokenizer is given) and served as (input, label) windows.  ``data_dir`` may be a
+    directory (every ``*.parquet`` in it, sorted), a glob or empty (shards are then added one by one).
+    Reference counterpart: StreamingDataset (include/quant/parquet_streamer.h:36-63)."""
+
+    def __init__(self, data_dir: str = "", vocab_size: int = 256, tokenizer=None, column: str = "text", seq_len: Optional[int] = None, seed: int = 42):
+        import glob
+        paths: List[str] = []
+        if data_dir:
+            paths = sorted(glob.glob(os.path.join(data_dir, "*.parquet"))) if os.path.isdir(data_dir) else sorted(glob.glob(data_dir))
+        self.vocab_size, self.tokenizer, self.column = vocab_size, tokenizer, column
+        super().__init__(paths, seq_len=seq_len, seed=seed)
+
+    def add_shard(self, path: str):
+        if not ParquetReader().open(path):
+            raise ValueError(f"not a Parquet file: {path}")
+        super().add_shard(path)
+
+    def reset(self):
+        super().reset()
+        self._reader = None
+
+    def _refill(self, want: int):
+        while len(self._buf) < want and not self._done:
+            if self._reader is None:
+                if self._shard >= len(self._order):
+                    self._done = True
+                    break
+                self._reader = ParquetReader(self.paths[self._order[self._shard]], self.column)
+            ids = self._reader.next_batch(max(want - len(self._buf), 4096), self.tokenizer)
+            if not ids:
+                self._reader, self._shard = None, self._shard + 1
+                continue
+            self._buf += ids if self.tokenizer is not None else [i % self.vocab_size for i in ids]
+
+    def size(self) -> int:
+        return sum(ParquetReader(p, self.column).num_rows() for p in self.paths)
 
 
 class DataPipeline:
