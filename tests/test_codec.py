@@ -196,6 +196,14 @@ def test_block_level_reader_and_streaming_writer(tmp_path):
         r.read_block(4)
     with pytest.raises(KeyError):
         r.tensor_blocks("nope")
+    # fail-closed addressing: sentinels instead of exceptions for ids a crafted file could name
+    raw = open(src, "rb").read()
+    rec = r.block_ptr(1)
+    off = r.block_offset(1)
+    assert off > 0 and raw[off:off + len(rec)] == rec and r.block_offset(0) < off < r.block_offset(2)
+    assert r.block_offset(4) == -1 and r.block_offset(-1) == -1 and r.block_ptr(4) is None
+    assert r.format_entry(3) == table[3] and r.format_entry(9)[1] == codec.QuantReader.INVALID_FORMAT
+    assert r.range_ok(0, 4) and not r.range_ok(1, 4) and not r.range_ok(-1, 1) and r.read_config() == b"cfg-bytes"
     # copy tensor "a" (blocks as stored) and a freshly encoded tensor "c" into a new file
     c = torch.randn(256, generator=g)
     blocks = [r.read_block(i) for i in range(3)] + [codec.BlockData.encode("Q_4", c.numpy())]

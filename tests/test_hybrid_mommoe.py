@@ -107,3 +107,27 @@ def test_modality_router_stand_alone_losses_and_accessors():
     logits = torch.randn(5, 8)
     assert float(r.z_loss(logits)) == pytest.approx(float((torch.logsumexp(logits, -1) ** 2).mean()))
     assert r.classify_modality(x) == out.dominant_modality
+
+
+def test_modality_block_projection_views_and_self_attention():
+    torch.manual_seed(0)
+    blk = MM.MoMBlock(32, 2, 48, 8, 2, MM.MoMMoEConfig(num_experts=8).expert_modality())
+    ex = blk.experts[5]
+    x = torch.randn(6, 32)
+    want = (torch.nn.functional.silu(x @ ex.gate_proj().t()) * (x @ ex.up_proj().t())) @ ex.down_proj().t()
+    assert torch.allclose(ex(x), want, atol=1e-5) and ex.specialization() == MM.Modality.AUDIO
+    ca = blk.cross_modal_attn
+    assert ca.q_proj().shape == ca.k_proj().shape == ca.v_proj().shape == ca.o_proj().shape == (32, 32)
+    with torch.no_grad():
+        ca.k_proj().zero_()
+    assert float(ca.kv.weight[:32].abs().sum()) == 0.0 and float(ca.kv.weight[32:].abs().sum()) > 0      # a view: writes go through
+    h = torch.randn(2, 5, 32)
+    out = blk(h)
+    # the first sub-layer of the block is exactly self_attention on the normalised input
+    a = blk.self_attention(blk.attention_norm(h))
+    assert a.shape == h.shape
+    h2 = h.clone()
+    h2[:, -1] += 1.0
+    a2 = blk.self_attention(blk.attention_norm(h2))
+    assert torch.allclose(a[:, :-1], a2[:, :-1], atol=1e-6) and not torch.allclose(a[:, -1], a2[:, -1])   # causal
+    assert out.hidden.shape == h.shape

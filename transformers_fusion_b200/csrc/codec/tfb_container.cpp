@@ -201,6 +201,11 @@ TFB_EXPORT int tfb_reader_block_info(const tfb_reader* r, uint32_t b, uint32_t o
   out[0] = r->fmts[b].id; out[1] = r->fmts[b].fmt; out[2] = r->fmts[b].cb; out[3] = nw; out[4] = cb; out[5] = ib;
   return 0;
 }
+// Byte offset of block b's record from the start of the file; -1 for a block that does not exist.
+TFB_EXPORT long long tfb_reader_block_offset(const tfb_reader* r, uint32_t b) {
+  if (!r->valid || b >= r->block_off.size()) return -1;
+  return (long long)r->block_off[b];
+}
 // Copies the codebook and index bytes of block b (either pointer may be null); returns 0 or -1.
 TFB_EXPORT int tfb_reader_block_payload(const tfb_reader* r, uint32_t b, uint8_t* codebook, uint8_t* indices) {
   uint32_t info[6];

@@ -133,6 +133,22 @@ class ModalityExpertFFN(nn.Module):
         return self.down(TF.silu(g) * u)
 
 
+def _projection_views():
+    """The reference names the projections one by one (include/quant/mommoe_block.h:140-180); here gate / up and key / value
+    are stored fused for one GEMM each, so these return views of the fused weights (writes go through)."""
+    ModalityExpertFFN.gate_proj = lambda self: self.gate_up.weight[: self.gate_up.out_features // 2]
+    ModalityExpertFFN.up_proj = lambda self: self.gate_up.weight[self.gate_up.out_features // 2:]
+    ModalityExpertFFN.down_proj = lambda self: self.down.weight
+    ModalityExpertFFN.specialization = lambda self: self.modality
+    CrossModalAttention.q_proj = lambda self: self.q.weight
+    CrossModalAttention.k_proj = lambda self: self.kv.weight[: self.kv.out_features // 2]
+    CrossModalAttention.v_proj = lambda self: self.kv.weight[self.kv.out_features // 2:]
+    CrossModalAttention.o_proj = lambda self: self.o.weight
+
+
+_projection_views()
+
+
 class _RMS(nn.Module):
     def __init__(self, d, eps=1e-5):
         super().__init__()
@@ -160,11 +176,16 @@ class MoMBlock(nn.Module):
         self.router = TopKRouter(hidden, num_experts, top_k, expert_modality, num_modalities)
         self.experts = nn.ModuleList(ModalityExpertFFN(hidden, ffn_hidden, Modality(m)) for m in expert_modality)
 
+    def self_attention(self, a: torch.Tensor) -> torch.Tensor:
+        """Causal multi-head self-attention of already normalised states [B, S, H] (the block's first sub-layer, without
+        the residual)."""
+        B, S, H = a.shape
+        q, k, v = self.qkv(a).view(B, S, 3, self.h, H // self.h).permute(2, 0, 3, 1, 4)
+        return self.o(TF.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, H))
+
     def forward(self, x, modality_hints=None) -> MoMOutput:
         B, S, H = x.shape
-        a = self.attention_norm(x)
-        q, k, v = self.qkv(a).view(B, S, 3, self.h, H // self.h).permute(2, 0, 3, 1, 4)
-        x = x + self.o(TF.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, H))
+        x = x + self.self_attention(self.attention_norm(x))
         f = self.moe_norm(x)
         r = self.router(f.reshape(B * S, H), modality_hints)
         cross = self.cross_modal_attn(f, r.modality_probs)

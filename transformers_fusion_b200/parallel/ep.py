@@ -63,6 +63,15 @@ class ExpertParallel:
     def local_experts(self):
         return assign_experts(self.E, self.world)[self.rank]
 
+    def num_experts(self) -> int: return self.E
+    def num_local_experts(self) -> int: return self.El
+    def num_ranks(self) -> int: return self.world
+
+    def forward(self, x, logits, gate_up_local, down_local, k, renorm=True, act=0, lb_weight=0.0, z_weight=0.0):
+        """``moe_ffn`` under the name the reference's wrappers use (include/quant/moe_enhance.h:94-98; the model-level
+        wrapper with attach / forward_with_parallel / sync_gradients is ``parallel.ep_model.ModelExpertParallel``)."""
+        return self.moe_ffn(x, logits, gate_up_local, down_local, k, renorm, act, lb_weight, z_weight)
+
     def moe_ffn(self, x, logits, gate_up_local, down_local, k, renorm, act, lb_weight, z_weight):
         """Same contract as ops.moe.moe_ffn, with gate_up_local / down_local holding only this rank's experts."""
         return _EpFFN.apply(x, logits, gate_up_local, down_local, self, k, renorm, act, lb_weight, z_weight)

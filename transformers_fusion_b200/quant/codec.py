@@ -61,6 +61,8 @@ def lib():
         L.tfb_reader_block_payload.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.tfb_reader_decode_block.restype = C.c_longlong
         L.tfb_reader_decode_block.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_longlong]
+        L.tfb_reader_block_offset.restype = C.c_longlong
+        L.tfb_reader_block_offset.argtypes = [C.c_void_p, C.c_uint32]
         L.tfb_reader_tensor_block_formats.restype = C.c_long
         L.tfb_reader_tensor_block_formats.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_long]
         _LIB = L
@@ -182,6 +184,37 @@ class QuantReader:
         if lib().tfb_reader_block_info(self._h, int(b), info) != 0:
             raise IndexError(f"block {b} of {self.num_blocks()}")
         return [int(v) for v in info]
+
+    # ---- fail-closed block addressing (reference: QUANTReader, include/quant/quant_format.h:85-124): a block id from an
+    # untrusted file never raises here; the caller checks the sentinel
+    INVALID_FORMAT = 0xFF
+
+    def block_offset(self, b: int) -> int:
+        """Byte offset of block ``b``'s record in the file; -1 when there is no such block."""
+        return int(lib().tfb_reader_block_offset(self._h, int(b))) if 0 <= int(b) < (1 << 32) else -1
+
+    def range_ok(self, start: int, count: int) -> bool:
+        """Whether blocks [start, start + count) all exist."""
+        return start >= 0 and count >= 0 and start + count <= self.num_blocks()
+
+    def format_entry(self, b: int):
+        """(block_id, format byte, codebook bytes) of the table entry of block ``b``; the format byte is 0xFF (no format has
+        that code) for a block that does not exist."""
+        if not self.range_ok(int(b), 1):
+            return (int(b), self.INVALID_FORMAT, 0)
+        return tuple(self._block_info(b)[:3])
+
+    def block_ptr(self, b: int):
+        """The whole stored record of block ``b`` (u32 weights, u32 codebook bytes, codebook, u32 index bytes, indices);
+        None when there is no such block."""
+        if not self.range_ok(int(b), 1):
+            return None
+        blk = self.read_block(b)
+        import struct
+        return struct.pack("<II", blk.num_weights, len(blk.codebook)) + blk.codebook + struct.pack("<I", len(blk.indices)) + blk.indices
+
+    def read_config(self) -> bytes:
+        return self.config_bytes()
 
     def read_format_table(self):
         """[(block_id, format byte, codebook bytes)] as stored in the table, one entry per block."""
