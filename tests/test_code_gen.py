@@ -22,7 +22,29 @@ def test_generated_kernels_compile(tmp_path):
     assert full.count("GEN_API int") == len(ks) and g.validate(full).compiles
     assert len(g.get_all_kernels()) == len(ks)
     with pytest.raises(ValueError):
-        g.generate_kernel_for_shape(KernelSpec(KernelType.ATTENTION, M=128, N=64))
+        g.generate_kernel_for_shape(KernelSpec(KernelType.ATTENTION, M=128, N=48, K=2))      # head size not a multiple of 32
+
+
+def test_generated_attention_dispatch_and_vector_statements_compile(tmp_path):
+    g = CodeGenerator(work_dir=str(tmp_path))
+    if g._nvcc() is None:
+        pytest.skip("nvcc not available")
+    att = g.generate_optimized_kernel(KernelSpec(KernelType.ATTENTION, M=96, N=64, K=4))
+    assert att.compiled, att.error_message
+    assert "float qr[2], acc[2]" in att.source_code and g.generate_attention(96, 64, 4, VectorWidth.V8) == att.source_code
+    # format dispatch: one branch per format plus the switch; the whole unit compiles
+    branches = "".join(g.generate_format_branch("expand", f, 4096) for f in ("Q_4", "Q_8"))
+    disp = g.generate_format_dispatch("expand", ["Q_4", "Q_8"])
+    from transformers_fusion_b200.quant import codec
+    assert f"case {codec.parse_format('Q_4')}: return expand_Q_4(" in disp and "default: return -1;" in disp
+    assert g.validate(branches + disp).compiles, g.last_error
+    # vector statement emitters compose into a kernel body
+    body = "\n".join([g.generate_simd_load("a", "x + i", 8), g.generate_simd_load("b", "y + i", 8), "float c[8], d[8];",
+                      g.generate_simd_mul("c", "a", "b", 8), g.generate_simd_add("d", "c", "a", 8), g.generate_simd_fma("d", "a", "b", "d", 8),
+                      g.generate_simd_store("z + i", "d", 8)])
+    kern = ("__global__ void vec_k(const __nv_bfloat16* x, const __nv_bfloat16* y, __nv_bfloat16* z, int n) {\n"
+            "  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;\n  if (i >= n) return;\n" + body + "\n}\n")
+    assert g.validate(kern).compiles, g.last_error
 
 
 def test_validation_rejects_broken_code(tmp_path):

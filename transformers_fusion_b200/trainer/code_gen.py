@@ -263,6 +263,83 @@ class CodeGenerator:
                 f"GEN_API int {fn}(const __nv_bfloat16* x, __nv_bfloat16* y, void* stream) {{\n"
                 f"  {fn}_k<<<{(n // group + 255) // 256}, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y);\n  return int(cudaGetLastError());\n}}\n")
 
+    def _attention(self, fn: str, S: int, D: int, H: int) -> str:
+        """Causal self-attention for one fixed (sequence, head size, heads): a warp per (head, query), the head dimension
+        spread over the lanes, keys visited in order with the running-maximum softmax so nothing of size S is stored."""
+        if D % 32 or D > 256:
+            raise ValueError("generated attention needs a head size that is a multiple of 32, at most 256")
+        per = D // 32
+        scale = repr(float(D) ** -0.5) + "f"
+        ld = H * D
+        return (f"// q, k, v, o: [{S}, {H} * {D}] bf16 rows (token-major); causal; softmax scale 1 / sqrt({D})\n"
+                f"__global__ void __launch_bounds__(256) {fn}_k(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ o) {{\n"
+                f"  const int lane = threadIdx.x & 31;\n  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;\n  if (w >= {S * H}) return;\n"
+                f"  const int h = w % {H}, i = w / {H};\n  float qr[{per}], acc[{per}];\n"
+                f"#pragma unroll\n  for (int c = 0; c < {per}; ++c) {{ qr[c] = __bfloat162float(q[(long long)i * {ld} + h * {D} + c * 32 + lane]) * {scale}; acc[c] = 0.f; }}\n"
+                f"  float m = -3.0e38f, l = 0.f;\n  for (int j = 0; j <= i; ++j) {{\n    float s = 0.f;\n"
+                f"#pragma unroll\n    for (int c = 0; c < {per}; ++c) s += qr[c] * __bfloat162float(k[(long long)j * {ld} + h * {D} + c * 32 + lane]);\n"
+                f"    s = gen_warp_sum(s);\n    const float mn = fmaxf(m, s), corr = __expf(m - mn), p = __expf(s - mn);\n    l = l * corr + p;\n"
+                f"#pragma unroll\n    for (int c = 0; c < {per}; ++c) acc[c] = acc[c] * corr + p * __bfloat162float(v[(long long)j * {ld} + h * {D} + c * 32 + lane]);\n"
+                f"    m = mn;\n  }}\n  const float inv = 1.f / l;\n"
+                f"#pragma unroll\n  for (int c = 0; c < {per}; ++c) o[(long long)i * {ld} + h * {D} + c * 32 + lane] = __float2bfloat16(acc[c] * inv);\n}}\n"
+                f"GEN_API int {fn}(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, __nv_bfloat16* o, void* stream) {{\n"
+                f"  {fn}_k<<<{(S * H * 32 + 255) // 256}, 256, 0, static_cast<cudaStream_t>(stream)>>>(q, k, v, o);\n  return int(cudaGetLastError());\n}}\n")
+
+    def generate_attention(self, seq_len: int, head_dim: int, num_heads: int, width=VectorWidth.SCALAR) -> str:
+        """Source of a causal attention kernel for exactly this shape (small and odd shapes; the framework's own flash
+        attention kernels serve the model shapes).  Reference counterpart: CodeGenerator::generate_attention
+        (include/quant/code_gen.h:104)."""
+        return self._gen(KernelSpec(KernelType.ATTENTION, M=seq_len, N=head_dim, K=num_heads, width=width))
+
+    # ---- dispatch over weight formats (reference: generate_format_dispatch / generate_format_branch, code_gen.h:120-121)
+    @staticmethod
+    def _fmt_name(fmt) -> str:
+        if isinstance(fmt, str):
+            return fmt
+        from ..quant import codec
+        return codec.format_name(int(fmt)) if hasattr(codec, "format_name") else f"fmt{int(fmt)}"
+
+    def generate_format_dispatch(self, op_name: str, formats) -> str:
+        """A host function ``<op>_dispatch(format, x, w, y, n, stream)`` that switches on the format id and calls
+        ``<op>_<FORMAT>`` for each of the given formats (-1 for any other id)."""
+        from ..quant import codec
+        cases = ""
+        for f in formats:
+            fid = codec.parse_format(f) if isinstance(f, str) else int(f)
+            cases += f"    case {fid}: return {op_name}_{self._fmt_name(f)}(x, w, y, n, stream);\n"
+        return (f"GEN_API int {op_name}_dispatch(int format, const void* x, const void* w, void* y, long long n, void* stream) {{\n"
+                f"  switch (format) {{\n{cases}    default: return -1;\n  }}\n}}\n")
+
+    def generate_format_branch(self, op_name: str, fmt, dim: int) -> str:
+        """One branch of such a dispatch for plain absmax integer grids (``Q_2`` .. ``Q_8``): a kernel that expands ``dim``
+        stored integers (one int8 each) with a per-32 scale and applies nothing else; ``<op>_<FORMAT>`` is its launcher."""
+        name = self._fmt_name(fmt)
+        return (f"__global__ void __launch_bounds__(256) {op_name}_{name}_k(const int8_t* __restrict__ w, const float* __restrict__ scale, __nv_bfloat16* __restrict__ y) {{\n"
+                f"  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;\n  if (i >= {dim}LL) return;\n"
+                f"  y[i] = __float2bfloat16(float(w[i]) * scale[i >> 5]);\n}}\n"
+                f"GEN_API int {op_name}_{name}(const void* x, const void* w, void* y, long long n, void* stream) {{\n"
+                f"  (void)n;\n  {op_name}_{name}_k<<<{(dim + 255) // 256}, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const int8_t*>(w), static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y));\n"
+                f"  return int(cudaGetLastError());\n}}\n")
+
+    # ---- vector statement emitters (the reference's SIMD emitters, code_gen.h:125-129, for CUDA vector types: a "vector" is
+    # an array of ``width`` floats in registers, loaded and stored through one wide bf16 access)
+    def generate_simd_load(self, var: str, ptr: str, width: int) -> str:
+        return (f"float {var}[{width}]; {{ __align__(16) __nv_bfloat16 t_[{width}]; *reinterpret_cast<{self._vec_ty(width)}*>(t_) = "
+                f"*reinterpret_cast<const {self._vec_ty(width)}*>({ptr});\n#pragma unroll\n for (int j_ = 0; j_ < {width}; ++j_) {var}[j_] = __bfloat162float(t_[j_]); }}")
+
+    def generate_simd_store(self, ptr: str, var: str, width: int) -> str:
+        return (f"{{ __align__(16) __nv_bfloat16 t_[{width}];\n#pragma unroll\n for (int j_ = 0; j_ < {width}; ++j_) t_[j_] = __float2bfloat16({var}[j_]); "
+                f"*reinterpret_cast<{self._vec_ty(width)}*>({ptr}) = *reinterpret_cast<const {self._vec_ty(width)}*>(t_); }}")
+
+    def generate_simd_fma(self, dst: str, a: str, b: str, c: str, width: int = 8) -> str:
+        return f"#pragma unroll\nfor (int j_ = 0; j_ < {width}; ++j_) {dst}[j_] = fmaf({a}[j_], {b}[j_], {c}[j_]);"
+
+    def generate_simd_add(self, dst: str, a: str, b: str, width: int = 8) -> str:
+        return f"#pragma unroll\nfor (int j_ = 0; j_ < {width}; ++j_) {dst}[j_] = {a}[j_] + {b}[j_];"
+
+    def generate_simd_mul(self, dst: str, a: str, b: str, width: int = 8) -> str:
+        return f"#pragma unroll\nfor (int j_ = 0; j_ < {width}; ++j_) {dst}[j_] = {a}[j_] * {b}[j_];"
+
     def generate_kernel_for_shape(self, spec: KernelSpec) -> str:
         fn, t = self.make_function_name(spec), spec.type
         if t in _UNARY:
@@ -283,6 +360,8 @@ class CodeGenerator:
             return self._embedding(fn, spec.M, spec.N, spec.width)
         if t == KernelType.QUANTIZE_DEQUANTIZE:
             return self._qdq(fn, spec.N, spec.K or 8, spec.M or 32)
+        if t == KernelType.ATTENTION:
+            return self._attention(fn, spec.M, spec.N, spec.K)
         raise ValueError(f"{t.name} kernels are hand-written in this framework and are not generated")
 
     def _gen(self, spec: KernelSpec) -> str:
@@ -374,6 +453,13 @@ class CodeGenerator:
                    KernelType.ADD: x + y, KernelType.MUL: x * y, KernelType.RESIDUAL_ADD: x + y, KernelType.SCALE: x * s.scale}[t]
             args = [ctypes.c_void_p(a.data_ptr())] + ([ctypes.c_void_p(b.data_ptr())] if t in _BINARY else []) + [ctypes.c_void_p(o.data_ptr()), ctypes.c_void_p(st)]
             rc = fn(*args)
+        elif t == KernelType.ATTENTION:
+            S, D, H = s.M, s.N, s.K
+            q, k, v = (torch.randn(S, H * D, device="cuda").bfloat16() for _ in range(3))
+            o = torch.empty_like(q)
+            hm = lambda z: z.float().view(S, H, D).transpose(0, 1)
+            ref = torch.nn.functional.scaled_dot_product_attention(hm(q), hm(k), hm(v), is_causal=True).transpose(0, 1).reshape(S, H * D)
+            rc = fn(*(ctypes.c_void_p(z.data_ptr()) for z in (q, k, v, o)), ctypes.c_void_p(st))
         else:
             return res
         torch.cuda.synchronize()
