@@ -271,3 +271,36 @@ def test_status_rotary_object_replay_entry_and_loader_config(tmp_path):
     assert ids.shape == (2, 8) and torch.equal(ids[:, 1:], lab[:, :-1])
     plain = DataLoader(tokens=torch.arange(100), batch_size=2, seq_length=4)
     assert plain.config().batch_size == 2 and plain.config().seq_length == 4 and plain.config().shuffle_buffer == 0
+
+
+def test_accumulating_metric_objects_and_scheduler_names():
+    from transformers_fusion_b200.utils import metrics as M
+    from transformers_fusion_b200.trainer import schedulers as S
+    logits = torch.tensor([[2.0, 1.0, 0.0], [0.0, 1.0, 2.0], [0.0, 3.0, 1.0], [1.0, 0.0, 2.0]])
+    tgt = torch.tensor([0, 1, 1, 0])
+    a1, a2 = M.Accuracy(1), M.Accuracy(2)
+    assert a1.update(logits, tgt) == 0.5 and a2.update(logits, tgt) == 1.0 and a1.update(torch.tensor([0, 1]), [0, 0]) == pytest.approx(3 / 6)
+    assert (a1.correct(), a1.total(), a2.top_k()) == (3, 6, 2)
+    a1.reset()
+    assert a1.value() == 0.0
+    p = M.Perplexity()
+    p.update(logits[:2], tgt[:2]), p.update(logits[2:], torch.tensor([1, -100]))
+    want = torch.nn.functional.cross_entropy(logits[:3], tgt[:3])
+    assert p.count() == 3 and p.value() == pytest.approx(math.exp(float(want)), rel=1e-5) and M.Perplexity().value() == float("inf")
+    cm = M.ConfusionMatrix(3)
+    cm.update(logits, tgt)                                        # predictions 0, 2, 1, 2 against 0, 1, 1, 0
+    assert cm.at(0, 0) == 1 and cm.at(2, 1) == 1 and cm.at(1, 1) == 1 and cm.at(2, 0) == 1 and cm.total_samples() == 4
+    assert (cm.true_positive(1), cm.false_positive(2), cm.false_negative(0), cm.num_classes(), len(cm.data())) == (1, 2, 1, 3, 9)
+    f = M.F1Score(3)
+    f.update(logits, tgt)
+    assert f.precision(0) == 1.0 and f.recall(0) == 0.5 and f.f1(0) == pytest.approx(2 / 3) and f.f1(2) == 0.0
+    assert f.macro_f1() == pytest.approx((2 / 3 + 2 / 3 + 0) / 3) and f.weighted_f1() == pytest.approx(2 / 3)
+    assert M.BLEUScore(2).compute(torch.tensor([1, 2, 3, 4]), [1, 2, 3, 4]) == pytest.approx(1.0) and M.BLEUScore().max_n() == 4
+    assert M.ROUGELScore().compute([1, 2, 3, 4], [1, 3, 4, 5]) == pytest.approx(0.75)
+    mp = M.MeanAveragePrecision()
+    assert mp.compute(torch.tensor([0.9, 0.1, 0.8]), torch.tensor([1, 0, 0])) == 1.0 and mp.compute([0.1, 0.9], [1, 0]) == 0.5 and mp.value() == 0.75
+    assert S.CosineDecayScheduler is S.CosineDecay and issubclass(S.OneCycleScheduler, S.LRScheduler)
+    assert S.ConstantScheduler(0.3).get_lr(99) == 0.3 and S.LambdaScheduler(lambda s: 1.0 / (1 + s)).get_lr(3) == 0.25
+    for n in ("LinearDecayScheduler", "ExponentialDecayScheduler", "StepDecayScheduler", "MultiStepDecay", "PolyScheduler", "WarmupScheduler", "CyclicLR",
+              "ReduceLROnPlateauScheduler", "SequentialScheduler", "ChainedScheduler"):
+        assert issubclass(getattr(S, n), S.Scheduler)

@@ -1,3 +1,4 @@
+import math
 import pytest
 import torch
 
@@ -214,3 +215,47 @@ def test_min_max_observer_interface():
     assert m.max_val() == 3.0 and m.type() == "MovingAverage"
     m.reset(), m.observe(torch.tensor([0.0, 8.0]))
     assert m.max_val() == 8.0
+
+
+def test_qat_objects_lsq_quantizer_kl_observer_and_context():
+    from transformers_fusion_b200.quant import qat as Q
+    assert Q.get_qrange(8) == (-128, 127) and Q.get_qrange(8, True, True) == (-127, 127) and Q.get_qrange(4, False) == (0, 15)
+    assert Q.get_qrange(Q.QATConfig(bits=4, narrow_range=True)) == (-7, 7)
+    x = torch.randn(4096)
+    xg = x.clone().requires_grad_(True)
+    y = Q.fake_quantize_per_tensor(xg, 0.05, 8)
+    y.sum().backward()
+    assert torch.equal(xg.grad, torch.ones_like(x)) and float((y.detach() - x).abs().max()) <= 0.025 + 1e-6
+    assert torch.unique(torch.round(y.detach() / 0.05)).numel() <= 256
+    # LSQ quantiser: trainable step; its explicit gradient equals autograd's
+    lq = Q.LSQQuantizer(Q.QATConfig(bits=4, use_lsq=True)).init_from(x)
+    assert lq.qmin() == -8 and lq.qmax() == 7 and lq.scale() == pytest.approx(float(2 * x.abs().mean() / math.sqrt(7)), rel=1e-5)
+    out = lq(x)
+    g = torch.randn_like(x)
+    (out * g).sum().backward()
+    assert float(lq.scale_param_tensor().grad) == pytest.approx(lq.compute_scale_grad(x, g), rel=1e-4)
+    assert lq.quant_params().qmax == 7
+    lq.set_scale(-1.0)
+    assert lq.scale() == pytest.approx(1e-6)
+    # KL calibration ignores a lone outlier that min / max calibration spends its range on
+    data = torch.cat([torch.randn(20000), torch.tensor([40.0])])
+    mm, kl = Q.MinMaxObserver(), Q.KLDivergenceObserver(bins=512)
+    mm.observe(data), kl.observe(data[:10000]), kl.observe(data[10000:])
+    assert kl.type() == "KLDivergence" and kl.calc_qparams(8).scale < 0.5 * mm.calc_qparams(8).scale
+    bulk = data[:20000]
+    err = lambda qp: float((qp.dequantize(qp.quantize(bulk)) - bulk).pow(2).mean())
+    assert err(kl.calc_qparams(8)) < err(mm.calc_qparams(8))
+    kl.reset()
+    assert not kl.has_data() and float(kl.hist.sum()) == 0 and kl.calc_qparams(8).scale == 1.0
+    assert Q.MovingAverageMinMaxObserver is Q.MovingAverageObserver
+    ctx = Q.QATContext(Q.QATConfig(bits=4))
+    assert ctx.maybe_quantize(x) is x and not ctx.enabled()
+    ctx.enable()
+    q = ctx.maybe_quantize(x)
+    assert torch.unique(q).numel() <= 16 and torch.unique(ctx.maybe_quantize(x, Q.MinMaxObserver())).numel() <= 16
+    asym = Q.fake_quantize_with_observer(x.abs().requires_grad_(True), Q.MinMaxObserver(), 4, False)
+    assert torch.unique(asym.detach()).numel() <= 16 and asym.requires_grad
+    step = torch.nn.Parameter(torch.tensor([0.2]))
+    assert torch.unique(ctx.maybe_lsq_quantize(x, step).detach()).numel() <= 16
+    ctx.disable()
+    assert ctx.maybe_lsq_quantize(x, step) is x

@@ -9,6 +9,7 @@ import math
 
 import numpy as np
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -194,6 +195,194 @@ class PercentileObserver(MinMaxObserver):
         k = max(1, int(f.numel() * (1 - self.pct / 100.0)))
         self.hi = max(self.hi, float(f.topk(k).values[-1]))
         self.lo = min(self.lo, float((-f).topk(k).values[-1] * -1))
+
+
+MovingAverageMinMaxObserver = MovingAverageObserver
+Observer = MinMaxObserver          # the interface every observer follows: observe / calc_qparams / reset / type
+
+
+class KLDivergenceObserver(MinMaxObserver):
+    """Histogram calibration: the clipping threshold is the one whose quantised histogram is closest (Kullback-Leibler) to
+    the observed one, which ignores rare outliers that a min / max range would spend its levels on.  Falls back to the
+    observed range when the histogram is degenerate.  Reference counterpart: KLDivergenceObserver
+    (include/quant/qat.h:164-183)."""
+
+    def __init__(self, bins: int = 2048, quantized_bins: int = 128):
+        super().__init__()
+        self.bins, self.qbins = bins, quantized_bins
+        self.hist = torch.zeros(bins, dtype=torch.float64)
+        self.hmax = 0.0
+
+    def type(self) -> str: return "KLDivergence"
+
+    def reset(self):
+        super().reset()
+        self.hist.zero_()
+        self.hmax = 0.0
+
+    def observe(self, x):
+        f = x.detach().float().reshape(-1).cpu()
+        super().observe(f)
+        amax = float(f.abs().max())
+        if amax > self.hmax:                                       # widen the histogram: re-bin what is already there
+            if self.hmax > 0 and float(self.hist.sum()) > 0:
+                centres = (torch.arange(self.bins, dtype=torch.float64) + 0.5) * (self.hmax / self.bins)
+                idx = (centres / amax * self.bins).long().clamp(max=self.bins - 1)
+                self.hist = torch.zeros_like(self.hist).index_add_(0, idx, self.hist)
+            self.hmax = amax
+        if self.hmax > 0:
+            self.hist += torch.histc(f.abs(), self.bins, 0.0, self.hmax).double()
+
+    def compute_kl_threshold(self, bits: int = 8) -> float:
+        levels = min(self.qbins, 1 << (bits - 1))
+        total = float(self.hist.sum())
+        if total <= 0 or self.hmax <= 0:
+            return 0.0
+        best, best_t = float("inf"), self.hmax
+        for i in range(levels, self.bins + 1, max(1, self.bins // 256)):
+            p = self.hist[:i].clone()
+            p[-1] += self.hist[i:].sum()                           # clipped mass lands in the last kept bin
+            edges = torch.linspace(0, i, levels + 1).long()
+            q = torch.zeros(i, dtype=torch.float64)
+            for a, b in zip(edges[:-1].tolist(), edges[1:].tolist()):
+                seg = self.hist[a:b]
+                nz = seg > 0
+                if nz.any():
+                    q[a:b][nz] = seg.sum() / nz.sum()
+            pn, qn = p / p.sum(), q / q.sum().clamp(min=1e-30)
+            m = pn > 0
+            kl = float((pn[m] * (pn[m] / qn[m].clamp(min=1e-30)).log()).sum())
+            if kl < best:
+                best, best_t = kl, (i / self.bins) * self.hmax
+        return best_t
+
+    def calc_qparams(self, bits=8, symmetric=True) -> QuantParams:
+        t = self.compute_kl_threshold(bits)
+        if t <= 0:
+            return super().calc_qparams(bits, symmetric)
+        lo, hi = self.lo, self.hi
+        self.lo, self.hi = max(lo, -t), min(hi, t)
+        try:
+            return super().calc_qparams(bits, symmetric)
+        finally:
+            self.lo, self.hi = lo, hi
+
+
+@dataclass
+class QATConfig:
+    bits: int = 8
+    symmetric: bool = True
+    per_channel: bool = False
+    narrow_range: bool = False
+    init_scale: float = 1.0
+    use_lsq: bool = False
+    lsq_grad_scale: float = 1.0
+
+
+def get_qrange(cfg_or_bits, symmetric: bool = True, narrow: bool = False):
+    """(qmin, qmax) of a configuration (or of bits / symmetric / narrow given one by one)."""
+    if isinstance(cfg_or_bits, QATConfig):
+        cfg_or_bits, symmetric, narrow = cfg_or_bits.bits, cfg_or_bits.symmetric, cfg_or_bits.narrow_range
+    b = int(cfg_or_bits)
+    if not symmetric:
+        return 0, (1 << b) - 1
+    return -(1 << (b - 1)) + (1 if narrow else 0), (1 << (b - 1)) - 1
+
+
+class _PerTensorSTE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, qmin, qmax):
+        s = max(float(scale), 1e-12)
+        return (torch.clamp(torch.round(x.float() / s), qmin, qmax) * s).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None, None, None
+
+
+def ste_fake_quantize(x, scale: float, qmin: int, qmax: int):
+    """clamp(round(x / scale), qmin, qmax) * scale with one scale for the whole tensor; the gradient passes unchanged."""
+    return _PerTensorSTE.apply(x, scale, qmin, qmax)
+
+
+def fake_quantize_per_tensor(x, scale: float, bits: int = 8, symmetric: bool = True):
+    return ste_fake_quantize(x, scale, *get_qrange(bits, symmetric))
+
+
+def fake_quantize_with_observer(x, obs, bits: int = 8, symmetric: bool = True):
+    """Feed ``x`` to the observer, then quantise it with the observer's current parameters (zero point included)."""
+    obs.observe(x.detach())
+    qp = obs.calc_qparams(bits, symmetric)
+    if qp.zero_point == 0:
+        return ste_fake_quantize(x, qp.scale, qp.qmin, qp.qmax)
+    return x + (qp.dequantize(qp.quantize(x.detach())).to(x.dtype) - x).detach()
+
+
+class LSQQuantizer:
+    """Per-tensor fake quantisation whose step size is a trainable parameter (``scale_param_tensor()`` goes to the
+    optimizer).  Reference counterpart: LSQQuantizer (include/quant/qat.h:84-109)."""
+
+    def __init__(self, cfg: Optional[QATConfig] = None):
+        self.cfg = cfg or QATConfig(use_lsq=True)
+        self._qmin, self._qmax = get_qrange(self.cfg)
+        self._step = torch.nn.Parameter(torch.tensor([max(self.cfg.init_scale, 1e-6)], dtype=torch.float32))
+
+    def config(self) -> QATConfig: return self.cfg
+    def qmin(self) -> int: return self._qmin
+    def qmax(self) -> int: return self._qmax
+    def scale(self) -> float: return float(self._step.detach())
+    def scale_param_tensor(self) -> torch.nn.Parameter: return self._step
+    def quant_params(self) -> QuantParams: return QuantParams(self.scale(), 0, self._qmin, self._qmax)
+
+    def set_scale(self, s: float):
+        with torch.no_grad():
+            self._step.fill_(max(float(s), 1e-6))
+
+    def init_from(self, x: torch.Tensor):
+        """The usual LSQ start: 2 mean|x| / sqrt(qmax)."""
+        self.set_scale(float(lsq_init_step(x, self.cfg.bits, self.cfg.symmetric)))
+        return self
+
+    def forward(self, x: torch.Tensor, scale_param: Optional[torch.Tensor] = None) -> torch.Tensor:
+        step = self._step if scale_param is None else scale_param
+        return lsq_fake_quantize(x, step.to(x.device), self.cfg.bits, self.cfg.symmetric)
+
+    __call__ = forward
+
+    def compute_scale_grad(self, x: torch.Tensor, grad_output: torch.Tensor) -> float:
+        """dL/dstep for given dL/dy, by the LSQ rule (the rounding residual inside the range, the clip level outside),
+        scaled by ``lsq_grad_scale`` / sqrt(numel * qmax)."""
+        s = max(self.scale(), 1e-12)
+        r = x.detach().float() / s
+        qn, qp = float(get_qrange(self.cfg.bits, self.cfg.symmetric)[0]), float(self._qmax)
+        d = torch.where(r <= qn, torch.full_like(r, qn), torch.where(r >= qp, torch.full_like(r, qp), torch.round(r) - r))
+        return float((grad_output.detach().float() * d).sum()) * self.cfg.lsq_grad_scale / math.sqrt(max(1.0, x.numel() * qp))
+
+
+class QATContext:
+    """A switch the training loop consults: ``maybe_quantize`` is the identity while disabled.  Reference counterpart:
+    QATContext (include/quant/qat.h:214-232)."""
+
+    def __init__(self, cfg: Optional[QATConfig] = None):
+        self.cfg, self._on = cfg or QATConfig(), False
+
+    def enable(self): self._on = True
+    def disable(self): self._on = False
+    def enabled(self) -> bool: return self._on
+    def config(self) -> QATConfig: return self.cfg
+    def set_config(self, c: QATConfig): self.cfg = c
+
+    def maybe_quantize(self, x, obs=None):
+        if not self._on:
+            return x
+        if obs is not None:
+            return fake_quantize_with_observer(x, obs, self.cfg.bits, self.cfg.symmetric)
+        qmin, qmax = get_qrange(self.cfg)
+        amax = float(x.detach().abs().max())
+        return ste_fake_quantize(x, (amax / qmax) if amax > 0 else self.cfg.init_scale, qmin, qmax)
+
+    def maybe_lsq_quantize(self, x, scale_param):
+        return lsq_fake_quantize(x, scale_param, self.cfg.bits, self.cfg.symmetric) if self._on else x
 
 
 @torch.no_grad()

@@ -225,3 +225,37 @@ class Chained(Scheduler):
 
 ALL = {c.__name__: c for c in (LinearDecay, CosineDecay, Exponential, Step, ReduceLROnPlateau, OneCycle, Warmup,
                                Sequential, Chained, CosineWarmupRestart, Poly, MultiStep, LinearWarmupDecay, Cyclic)}
+
+
+class Constant(Scheduler):
+    def __call__(self, step):
+        return self.base_lr
+
+
+class Lambda(Scheduler):
+    """``fn(step)`` is the rate (not a multiplier), as in the reference's LambdaScheduler (include/quant/scheduler.h:120-128)."""
+
+    def __init__(self, fn, base_lr: float = 0.0):
+        super().__init__(base_lr)
+        self.fn = fn
+
+    def __call__(self, step):
+        return float(self.fn(step))
+
+
+# the reference's class names (include/quant/scheduler.h)
+LRScheduler = Scheduler
+ConstantScheduler = Constant
+LambdaScheduler = Lambda
+LinearDecayScheduler = LinearDecay
+CosineDecayScheduler = CosineDecay
+ExponentialDecayScheduler = Exponential
+StepDecayScheduler = Step
+MultiStepDecay = MultiStep
+PolyScheduler = Poly
+WarmupScheduler = Warmup
+OneCycleScheduler = OneCycle
+CyclicLR = Cyclic
+ReduceLROnPlateauScheduler = ReduceLROnPlateau
+SequentialScheduler = Sequential
+ChainedScheduler = Chained

@@ -137,6 +137,146 @@ def rouge_l(candidate, reference):
     return {"precision": p, "recall": r, "f1": 2 * p * r / (p + r) if p + r else 0.0}
 
 
+# ---- accumulating metric objects (reference: include/quant/metrics.h): ``update`` takes tensors of one batch and the
+# object keeps running totals, so a metric can be fed batch by batch on the device and read at the end
+def _ids(t) -> torch.Tensor:
+    return t.reshape(-1).long() if torch.is_tensor(t) else torch.tensor(list(t), dtype=torch.long)
+
+
+class Accuracy:
+    """Top-k accuracy.  ``predictions``: class scores [N, C] (or class ids [N] for k = 1)."""
+
+    def __init__(self, top_k: int = 1):
+        self._k = top_k
+        self.reset()
+
+    def reset(self): self._correct = self._total = 0
+    def correct(self) -> int: return self._correct
+    def total(self) -> int: return self._total
+    def top_k(self) -> int: return self._k
+    def value(self) -> float: return self._correct / self._total if self._total else 0.0
+
+    def update(self, predictions: torch.Tensor, targets) -> float:
+        t = _ids(targets).to(predictions.device)
+        if predictions.dim() == 1:
+            hit = predictions.long() == t
+        else:
+            p = predictions.reshape(-1, predictions.shape[-1])
+            hit = (p.topk(min(self._k, p.shape[-1]), -1).indices == t[:, None]).any(-1)
+        self._correct += int(hit.sum())
+        self._total += t.numel()
+        return self.value()
+
+
+class Perplexity:
+    """exp(mean negative log-likelihood) over everything fed so far; targets equal to ``ignore_index`` are skipped."""
+
+    def __init__(self, ignore_index: int = -100):
+        self.ignore_index = ignore_index
+        self.reset()
+
+    def reset(self): self._nll, self._count = 0.0, 0
+    def nll(self) -> float: return self._nll
+    def count(self) -> int: return self._count
+    def value(self) -> float: return perplexity(self._nll / self._count) if self._count else float("inf")
+
+    def update(self, logits: torch.Tensor, targets) -> float:
+        t = _ids(targets).to(logits.device)
+        lp = torch.log_softmax(logits.reshape(-1, logits.shape[-1]).float(), -1)
+        keep = t != self.ignore_index
+        self._nll += float(-lp[keep].gather(1, t[keep][:, None]).sum())
+        self._count += int(keep.sum())
+        return self.value()
+
+
+class ConfusionMatrix:
+    """``at(pred, true)`` counts; rows are predictions."""
+
+    def __init__(self, num_classes: int):
+        self._n = num_classes
+        self.reset()
+
+    def reset(self): self.matrix = torch.zeros(self._n, self._n, dtype=torch.long)
+
+    def update(self, predictions: torch.Tensor, targets, from_logits: Optional[bool] = None):
+        if from_logits or (from_logits is None and torch.is_tensor(predictions) and predictions.dim() > 1):
+            predictions = predictions.reshape(-1, predictions.shape[-1]).argmax(-1)
+        p, t = _ids(predictions).cpu(), _ids(targets).cpu()
+        ok = (p >= 0) & (p < self._n) & (t >= 0) & (t < self._n)
+        self.matrix += torch.bincount(p[ok] * self._n + t[ok], minlength=self._n * self._n).view(self._n, self._n)
+
+    def at(self, pred_class: int, true_class: int) -> int: return int(self.matrix[pred_class, true_class])
+    def true_positive(self, c: int) -> int: return int(self.matrix[c, c])
+    def false_positive(self, c: int) -> int: return int(self.matrix[c].sum() - self.matrix[c, c])
+    def false_negative(self, c: int) -> int: return int(self.matrix[:, c].sum() - self.matrix[c, c])
+    def total_samples(self) -> int: return int(self.matrix.sum())
+    def num_classes(self) -> int: return self._n
+    def data(self) -> List[int]: return self.matrix.reshape(-1).tolist()
+
+
+class F1Score:
+    """Per-class, macro and support-weighted precision / recall / F1 (``class_idx`` -1: the macro average)."""
+
+    def __init__(self, num_classes: int = 2):
+        self.cm = ConfusionMatrix(num_classes)
+
+    def reset(self): self.cm.reset()
+    def num_classes(self) -> int: return self.cm.num_classes()
+    def update(self, predictions, targets): self.cm.update(predictions, targets)
+
+    def _one(self, c: int):
+        tp, fp, fn = self.cm.true_positive(c), self.cm.false_positive(c), self.cm.false_negative(c)
+        p = tp / (tp + fp) if tp + fp else 0.0
+        r = tp / (tp + fn) if tp + fn else 0.0
+        return p, r, (2 * p * r / (p + r) if p + r else 0.0)
+
+    def _avg(self, k: int, c: int) -> float:
+        if c >= 0:
+            return self._one(c)[k]
+        return sum(self._one(i)[k] for i in range(self.num_classes())) / max(1, self.num_classes())
+
+    def precision(self, class_idx: int = -1) -> float: return self._avg(0, class_idx)
+    def recall(self, class_idx: int = -1) -> float: return self._avg(1, class_idx)
+    def f1(self, class_idx: int = -1) -> float: return self._avg(2, class_idx)
+    def macro_f1(self) -> float: return self._avg(2, -1)
+
+    def weighted_f1(self) -> float:
+        sup = self.cm.matrix.sum(0).tolist()
+        return sum(self._one(i)[2] * sup[i] for i in range(self.num_classes())) / max(1, sum(sup))
+
+
+class BLEUScore:
+    def __init__(self, max_n: int = 4, smooth: bool = True):
+        self._n, self.smooth = max_n, smooth
+
+    def max_n(self) -> int: return self._n
+
+    def compute(self, candidate, reference) -> float:
+        return bleu(_ids(candidate).tolist(), [_ids(reference).tolist()], self._n, self.smooth)
+
+
+class ROUGELScore:
+    def compute(self, candidate, reference) -> float:
+        """The F-measure of the longest common subsequence."""
+        return rouge_l(_ids(candidate).tolist(), _ids(reference).tolist())["f1"]
+
+
+class MeanAveragePrecision:
+    """``compute(scores, labels)`` adds one query (scores of its candidates, 0 / 1 relevance labels) and returns its average
+    precision; ``value`` is the mean over the queries so far."""
+
+    def __init__(self): self.reset()
+    def reset(self): self.ap_scores: List[float] = []
+    def value(self) -> float: return sum(self.ap_scores) / len(self.ap_scores) if self.ap_scores else 0.0
+
+    def compute(self, scores, labels) -> float:
+        sc = scores.reshape(-1).tolist() if torch.is_tensor(scores) else list(scores)
+        lb = _ids(labels).tolist()
+        ap = average_precision(sc, [int(r > 0) for r in lb])
+        self.ap_scores.append(ap)
+        return ap
+
+
 def load_eval_tokens(path, max_tokens=0, tokenizer=None) -> List[int]:
     """Whitespace-separated integer ids, or text run through ``tokenizer`` when the file is not numeric."""
     text = open(path, "r", encoding="utf-8", errors="ignore").read()
