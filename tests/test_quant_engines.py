@@ -259,3 +259,54 @@ def test_qat_objects_lsq_quantizer_kl_observer_and_context():
     assert torch.unique(ctx.maybe_lsq_quantize(x, step).detach()).numel() <= 16
     ctx.disable()
     assert ctx.maybe_lsq_quantize(x, step) is x
+
+
+def test_scalar_vq_family_residual_audio_codebook_and_ste_quantizer():
+    from transformers_fusion_b200.quant import codec, qat as Q
+    torch.manual_seed(0)
+    w = torch.randn(1001).clamp(-1, 1)
+    q8 = E.Q8VectorQuantizer()
+    i8 = q8.quantize(w)
+    assert i8.dtype == torch.uint8 and i8.numel() == 1001 and float((q8.dequantize(i8) - w).abs().max()) <= 1.0 / 255 + 1e-6
+    assert q8.find_nearest(-1.0) == 0 and q8.find_nearest(1.0) == 255
+    q4 = E.Q4VectorQuantizer()
+    p4 = q4.quantize(w)
+    assert p4.numel() == 501 and q4.dequantize(p4, 1001).shape == (1001,)
+    e0 = float((q4.dequantize(p4, 1001) - w).pow(2).mean())
+    assert int(p4[0]) & 0xF == q4.find_nearest(float(w[0])) and int(p4[0]) >> 4 == q4.find_nearest(float(w[1]))
+    for _ in range(40):                                            # EMA moves the 16 entries to the data's cluster means
+        q4.update_ema(w, q4.quantize(w), 1001)
+    assert float((q4.dequantize(q4.quantize(w), 1001) - w).pow(2).mean()) < e0 and q4.codebook().dtype == torch.float16
+    assert E.Q4VectorQuantizer.fp16_to_float(E.Q4VectorQuantizer.float_to_fp16(0.5)) == 0.5 and E.Q4VectorQuantizer.float_to_fp16(1.0) == 0x3C00
+    with pytest.raises(ValueError):
+        E.Q8VectorQuantizer([0.0, 1.0])
+    # residual VQ: every added layer lowers the reconstruction error
+    feats = torch.randn(2, 64, 8)
+    ac = E.AudioCodebook(E.AudioCodebookConfig(num_quantizers=3, codebook_size=16, embedding_dim=8)).fit(feats, iters=5)
+    idx = ac.encode(feats)
+    assert idx.shape == (3, 2, 64) and len(ac.quantizers()) == 3 and ac.total_commitment_loss() > 0 and ac.total_codebook_loss() == 0.0
+    errs = [float((ac.decode(idx[:k]) - feats).pow(2).mean()) for k in (1, 2, 3)]
+    assert errs[0] > errs[1] > errs[2] and ac.decode(idx).shape == feats.shape
+    ac.encode(feats, update=True)
+    # straight-through quantisation to container formats
+    st = Q.STEQuantizer("Q_4")
+    assert st.target_format() == codec.parse_format("Q_4") and st.bits_for_format() == 4
+    x = torch.randn(512, requires_grad=True)
+    y = st(x)
+    y.sum().backward()
+    assert torch.equal(x.grad, torch.ones(512)) and not torch.equal(y.detach(), x.detach())
+    assert torch.allclose(y.detach(), Q.ste_roundtrip_(x.detach().clone(), "Q_4"))
+    mixed = st.forward_mixed(x.detach(), ["Q_8", "Q_32"], 256)
+    assert torch.equal(mixed[256:], x.detach()[256:]) and not torch.equal(mixed[:256], x.detach()[:256])
+    with pytest.raises(ValueError):
+        st.forward_mixed(x.detach(), ["Q_8"], 256)
+    codes, sc = st.quantize_Q1(x.detach())
+    assert set(torch.unique(codes).tolist()) <= {0, 1, 2} and sc > 0
+    c4, s4 = st.quantize_quant(x.detach())
+    assert int(c4.max()) <= 15 and float((((c4.float() - 8) * s4) - x.detach()).abs().max()) <= s4 / 2 + 1e-6
+    cb = E.CodebookQ4()
+    snapped = st.quantize_with_codebook(x.detach(), cb)
+    assert torch.unique(snapped).numel() <= 16 and cb.trained
+    assert torch.unique(st.fake_quantize_qat(x.detach())).numel() <= 15
+    assert torch.unique(st.lsq_quantize(x.detach(), torch.tensor([0.3]))).numel() <= 16
+    assert torch.unique(st.fake_quantize_with_observer(x.detach(), Q.MinMaxObserver())).numel() <= 16

@@ -224,6 +224,145 @@ class VectorQuantizer:
         return x + (q - x).detach(), idx, ((q.detach() - x) ** 2).mean()
 
 
+class _ScalarVQ:
+    """Scalar codebook quantiser with online (EMA) centroid updates: the form used for the few most sensitive weights
+    (reference: Q8VectorQuantizer / Q4VectorQuantizer, include/quant/vector_quantizer.h:84-140)."""
+    SIZE = 256
+    DTYPE = torch.float32
+
+    def __init__(self, initial_codebook=None, ema_decay: float = 0.99):
+        if initial_codebook is None:
+            cb = torch.linspace(-1.0, 1.0, self.SIZE)
+        else:
+            cb = torch.as_tensor(initial_codebook)
+            cb = cb.view(torch.float16).float() if cb.dtype in (torch.uint16, torch.int16) else cb.float()
+            if cb.numel() != self.SIZE:
+                raise ValueError(f"the codebook needs {self.SIZE} entries")
+        self._cb = cb.to(self.DTYPE).clone()
+        self.decay = ema_decay
+        self._sum = torch.zeros(self.SIZE)
+        self._cnt = torch.zeros(self.SIZE)
+
+    def codebook(self) -> torch.Tensor: return self._cb
+
+    def find_nearest(self, value: float) -> int:
+        return int((self._cb.float() - float(value)).abs().argmin())
+
+    def _nearest(self, w: torch.Tensor) -> torch.Tensor:
+        c, order = self._cb.float().sort()
+        x = w.detach().float().reshape(-1)
+        pos = torch.bucketize(x.contiguous(), (c[1:] + c[:-1]) / 2)
+        return order[pos]
+
+    def _indices(self, stored: torch.Tensor, n: int) -> torch.Tensor:
+        return stored.reshape(-1)[:n].long()
+
+    def quantize(self, weights: torch.Tensor) -> torch.Tensor:
+        return self._nearest(weights).to(torch.uint8)
+
+    def dequantize(self, indices: torch.Tensor, n: Optional[int] = None) -> torch.Tensor:
+        n = indices.numel() if n is None else n
+        return self._cb.float()[self._indices(indices, n)]
+
+    def update_ema(self, weights: torch.Tensor, indices: torch.Tensor, n: Optional[int] = None):
+        x = weights.detach().float().reshape(-1)
+        idx = self._indices(indices, x.numel() if n is None else n)
+        x = x[: idx.numel()]
+        d = self.decay
+        self._cnt.mul_(d).add_(torch.zeros(self.SIZE).index_add_(0, idx, torch.ones(idx.numel())), alpha=1 - d)
+        self._sum.mul_(d).add_(torch.zeros(self.SIZE).index_add_(0, idx, x), alpha=1 - d)
+        live = self._cnt > 1e-8
+        self._cb = torch.where(live, self._sum / self._cnt.clamp(min=1e-12), self._cb.float()).to(self.DTYPE)
+
+
+class Q8VectorQuantizer(_ScalarVQ):
+    """256 fp32 entries; one byte per weight."""
+
+
+class Q4VectorQuantizer(_ScalarVQ):
+    """16 fp16 entries; two indices per byte, the even position in the low nibble."""
+    SIZE = 16
+    DTYPE = torch.float16
+
+    def quantize(self, weights: torch.Tensor) -> torch.Tensor:
+        idx = self._nearest(weights).to(torch.uint8)
+        if idx.numel() % 2:
+            idx = torch.cat([idx, idx.new_zeros(1)])
+        return idx[0::2] | (idx[1::2] << 4)
+
+    def _indices(self, stored: torch.Tensor, n: int) -> torch.Tensor:
+        p = stored.reshape(-1)
+        return torch.stack([p & 0xF, p >> 4], 1).reshape(-1)[:n].long()
+
+    def dequantize(self, packed: torch.Tensor, n: Optional[int] = None) -> torch.Tensor:
+        return super().dequantize(packed, 2 * packed.numel() if n is None else n)
+
+    @staticmethod
+    def fp16_to_float(h: int) -> float:
+        return float(torch.tensor([h], dtype=torch.int32).to(torch.int16).view(torch.float16)[0])
+
+    @staticmethod
+    def float_to_fp16(f: float) -> int:
+        return int(torch.tensor([f], dtype=torch.float16).view(torch.int16)[0]) & 0xFFFF
+
+
+@dataclass
+class AudioCodebookConfig:
+    num_quantizers: int = 8
+    codebook_size: int = 1024
+    embedding_dim: int = 128
+    commitment_weight: float = 0.25
+    ema_decay: float = 0.99
+
+
+class AudioCodebook:
+    """Residual vector quantisation (EnCodec / DAC style): each layer quantises what the layers before it left over, so the
+    sum of the chosen entries approaches the input as layers are added.  Reference counterpart: AudioCodebook
+    (include/quant/vector_quantizer.h:150-190)."""
+
+    def __init__(self, cfg: Optional[AudioCodebookConfig] = None, seed: int = 0):
+        self.cfg = cfg or AudioCodebookConfig()
+        c = self.cfg
+        self._q = [VectorQuantizer(VQConfig(c.codebook_size, c.embedding_dim, c.commitment_weight, c.ema_decay), seed=seed + i)
+                   for i in range(c.num_quantizers)]
+        self._commit = self._cbloss = 0.0
+
+    def quantizers(self) -> list: return self._q
+    def total_commitment_loss(self) -> float: return self._commit
+    def total_codebook_loss(self) -> float: return self._cbloss
+
+    def fit(self, features: torch.Tensor, iters: int = 10):
+        """Lloyd-fit every layer on the residual the earlier layers leave."""
+        r = features.detach().float().reshape(-1, self.cfg.embedding_dim)
+        for q in self._q:
+            q.train(r, iters)
+            r = r - q.decode(q.encode(r))
+        return self
+
+    def encode(self, features: torch.Tensor, update: bool = False) -> torch.Tensor:
+        """features [batch, seq, dim] -> indices [num_quantizers, batch, seq]; ``update`` also moves every layer's codebook
+        toward its inputs (EMA)."""
+        lead = features.shape[:-1]
+        r = features.detach().float().reshape(-1, self.cfg.embedding_dim)
+        out, self._commit, self._cbloss = [], 0.0, 0.0
+        for q in self._q:
+            res = q.quantize(r)
+            if update:
+                q.update_ema(r, res.indices)
+            self._commit += self.cfg.commitment_weight * res.commitment_loss
+            self._cbloss += res.codebook_loss
+            out.append(res.indices.reshape(lead))
+            r = r - res.quantized.float()
+        return torch.stack(out)
+
+    def decode(self, indices: torch.Tensor) -> torch.Tensor:
+        """indices [num_quantizers (or fewer: a coarser reconstruction), batch, seq] -> features [batch, seq, dim]."""
+        y = 0
+        for q, idx in zip(self._q, indices):
+            y = y + q.decode(idx.reshape(-1).long()).float()
+        return y.view(*indices.shape[1:], self.cfg.embedding_dim)
+
+
 class _CodebookEngine:
     bits = 8
 

@@ -415,3 +415,83 @@ class QATState:
         for p in model.parameters():
             if p.dim() >= 2 and p.numel() >= self.min_numel:
                 fake_quant_block(p.data, self.bits, self.block, self.symmetric, out=p.data)
+
+
+class STEQuantizer:
+    """Straight-through quantisation of weights to one of the container's formats: forward returns exactly what a saved
+    checkpoint in that format would decode to, backward passes the gradient unchanged.  Reference counterpart: STEQuantizer
+    (include/quant/ste_quantizer.h:10-58)."""
+
+    def __init__(self, target_format="Q_1"):
+        self.set_target_format(target_format)
+
+    def set_target_format(self, fmt):
+        self._fmt = codec.parse_format(fmt) if isinstance(fmt, str) else int(fmt)
+
+    def target_format(self) -> int: return self._fmt
+
+    def bits_for_format(self, fmt=None) -> int:
+        return max(1, int(math.ceil(codec.format_bpw(self._fmt if fmt is None else fmt) - 1e-9)))
+
+    def forward(self, w: torch.Tensor, block: int = 256) -> torch.Tensor:
+        q = ste_roundtrip_(w.detach().clone(), self._fmt, block)
+        return w + (q - w).detach()
+
+    __call__ = forward
+
+    def forward_mixed(self, w: torch.Tensor, per_block_formats, block_size: int = 256) -> torch.Tensor:
+        """A different format for every block of ``block_size`` consecutive weights (the last block may be shorter)."""
+        flat = w.detach().float().reshape(-1).cpu().contiguous().numpy()
+        nb = (flat.size + block_size - 1) // block_size
+        if len(per_block_formats) != nb:
+            raise ValueError(f"{nb} blocks need {nb} formats, got {len(per_block_formats)}")
+        out = flat.copy()
+        for b, f in enumerate(per_block_formats):
+            f = codec.parse_format(f) if isinstance(f, str) else int(f)
+            seg = flat[b * block_size:(b + 1) * block_size]
+            out[b * block_size:(b + 1) * block_size] = codec.dequantize_block(f, codec.quantize_block(f, seg), seg.size)
+        q = torch.from_numpy(out).view(w.shape).to(w.dtype).to(w.device)
+        return w + (q - w).detach()
+
+    def quantize_with_codebook(self, w: torch.Tensor, codebook) -> torch.Tensor:
+        """Snap to the nearest entry of a scalar codebook (after scaling by the tensor's absmax); an untrained codebook is
+        trained on ``w`` first.  ``codebook``: an object with ``centroids`` and ``train`` (quant.engines.Codebook)."""
+        amax = w.detach().abs().max().clamp(min=1e-30)
+        u = (w.detach().float() / amax).reshape(-1)
+        if not getattr(codebook, "trained", False):
+            codebook.train(u)
+            codebook.trained = True
+        c = codebook.centroids.to(u.device)
+        q = (c[torch.bucketize(u.contiguous(), (c[1:] + c[:-1]) / 2)] * amax).view(w.shape).to(w.dtype)
+        return w + (q - w).detach()
+
+    @staticmethod
+    def find_scale(x: torch.Tensor) -> float:
+        return float(x.detach().abs().max())
+
+    def quantize_Q1(self, src: torch.Tensor):
+        """(codes uint8 in {0, 1, 2} for -1 / 0 / +1, scale): ternary with the mean magnitude of the kept weights as scale."""
+        x = src.detach().float().reshape(-1)
+        thr = 0.7 * x.abs().mean()
+        sign = torch.where(x.abs() > thr, x.sign(), torch.zeros_like(x))
+        kept = sign != 0
+        scale = float(x[kept].abs().mean()) if bool(kept.any()) else 1.0
+        return (sign + 1).to(torch.uint8), scale
+
+    def quantize_quant(self, src: torch.Tensor):
+        """(4-bit codes uint8 in 0 .. 15, scale) on the symmetric absmax grid with levels -7 .. 7 (code 8 is zero)."""
+        x = src.detach().float().reshape(-1)
+        scale = self.find_scale(x) / 7.0 or 1.0
+        return (torch.clamp(torch.round(x / scale), -7, 7) + 8).to(torch.uint8), scale
+
+    def fake_quantize_qat(self, w: torch.Tensor, scale_override: float = 0.0) -> torch.Tensor:
+        bits = min(16, max(2, self.bits_for_format()))
+        qmin, qmax = get_qrange(bits, True, True)
+        scale = scale_override if scale_override > 0 else (self.find_scale(w) / qmax or 1.0)
+        return ste_fake_quantize(w, scale, qmin, qmax)
+
+    def lsq_quantize(self, w: torch.Tensor, scale_param: torch.Tensor) -> torch.Tensor:
+        return lsq_fake_quantize(w, scale_param, min(16, max(2, self.bits_for_format())), True)
+
+    def fake_quantize_with_observer(self, w: torch.Tensor, obs, bits: int = 0) -> torch.Tensor:
+        return fake_quantize_with_observer(w, obs, bits or min(16, max(2, self.bits_for_format())), True)
