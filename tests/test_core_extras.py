@@ -304,3 +304,39 @@ def test_accumulating_metric_objects_and_scheduler_names():
     for n in ("LinearDecayScheduler", "ExponentialDecayScheduler", "StepDecayScheduler", "MultiStepDecay", "PolyScheduler", "WarmupScheduler", "CyclicLR",
               "ReduceLROnPlateauScheduler", "SequentialScheduler", "ChainedScheduler"):
         assert issubclass(getattr(S, n), S.Scheduler)
+
+
+def test_tensor_view_never_copies_and_global_seed_manager(monkeypatch):
+    from transformers_fusion_b200.utils import core as C
+    from transformers_fusion_b200.utils.random import GlobalSeedManager as G
+    base = torch.arange(24.0)
+    v = C.TensorView(base, (2, 3, 4))
+    assert v.shape() == (2, 3, 4) and v.strides() == [12, 4, 1] and v.rank() == 3 and v.is_contiguous() and v.data_ptr() == base.data_ptr()
+    s = v.slice(1, 1, 3)
+    assert s.shape() == (2, 2, 4) and s.at(0, 0, 0) == 4.0 and not s.is_contiguous() and s.data_ptr() == base.data_ptr() + 4 * 4
+    t = v.transpose(0, 2)
+    assert t.shape() == (4, 3, 2) and t.at(3, 2, 1) == 23.0
+    with pytest.raises(ValueError):
+        t.reshape(24)
+    assert v.reshape(6, 4).at(5, 3) == 23.0 and v.narrow(2, 1, 2).at(0, 0, 1) == 2.0
+    u = v.unsqueeze(1)
+    assert u.shape() == (2, 1, 3, 4) and u.squeeze(1).shape() == (2, 3, 4)
+    with pytest.raises(ValueError):
+        v.squeeze(0)
+    with pytest.raises(IndexError):
+        v.slice(0, 1, 3)
+    s.data()[0, 0, 0] = -1.0
+    assert base[4] == -1.0                                        # a window, not a copy
+    c = t.contiguous()
+    c[0, 0, 0] = 99.0
+    assert base[0] == 0.0 and C.TensorView(base, (2, 2), (1, 2), offset=8).at(1, 1) == 11.0
+    monkeypatch.setenv("QUANT_SEED", "1234")
+    G.reset()
+    assert G.is_deterministic() and G.get_seed() == 1234 and G.next_seed() == 1235 and G.next_seed() == 1236
+    monkeypatch.delenv("QUANT_SEED")
+    G.reset()
+    a = G.get_seed()
+    assert not G.is_deterministic() and a != 0 and G.get_seed() == a and G.next_seed() == (a + 1) & 0xFFFFFFFFFFFFFFFF
+    monkeypatch.setenv("QUANT_SEED", "0")
+    assert not G.is_deterministic()
+    G.reset()

@@ -443,3 +443,58 @@ def json_escape_string(s: str) -> str:
     """The JSON spelling of a string without its quotes."""
     import json
     return json.dumps(s)[1:-1]
+
+
+class TensorView:
+    """A strided window onto storage that someone else owns: every operation returns another view of the same memory and
+    never copies (``reshape`` refuses a view that is not contiguous rather than copying silently).  A torch tensor already
+    is such a view; this class pins the no-copy contract and keeps the reference's interface (include/quant/tensor_view.h)."""
+
+    def __init__(self, data, shape=None, strides=None, offset: int = 0):
+        import torch
+        base = data.t if isinstance(data, TensorView) else data
+        if shape is None:
+            self.t = base
+        else:
+            shape = tuple(shape)
+            if strides is None:
+                strides, acc = [], 1
+                for d in reversed(shape):
+                    strides.insert(0, acc)
+                    acc *= d
+            self.t = torch.as_strided(base, shape, tuple(strides), base.storage_offset() + offset)
+
+    def shape(self) -> Shape: return Shape(*self.t.shape)
+    def strides(self): return list(self.t.stride())
+    def rank(self) -> int: return self.t.dim()
+    def numel(self) -> int: return self.t.numel()
+    def dtype(self): return self.t.dtype
+    def data(self): return self.t
+    def data_ptr(self) -> int: return self.t.data_ptr()
+    def is_contiguous(self) -> bool: return self.t.is_contiguous()
+
+    def slice(self, dim: int, start: int, end: int) -> "TensorView":
+        if not (0 <= dim < self.t.dim() and 0 <= start <= end <= self.t.shape[dim]):
+            raise IndexError("TensorView.slice out of range")
+        return TensorView(self.t.narrow(dim, start, end - start))
+
+    def narrow(self, dim: int, start: int, size: int) -> "TensorView": return self.slice(dim, start, start + size)
+    def transpose(self, d1: int, d2: int) -> "TensorView": return TensorView(self.t.transpose(d1, d2))
+    def unsqueeze(self, dim: int) -> "TensorView": return TensorView(self.t.unsqueeze(dim))
+
+    def squeeze(self, dim: int) -> "TensorView":
+        if self.t.shape[dim] != 1:
+            raise ValueError("TensorView.squeeze: the dimension is not 1")
+        return TensorView(self.t.squeeze(dim))
+
+    def reshape(self, *shape) -> "TensorView":
+        if not self.t.is_contiguous():
+            raise ValueError("only a contiguous view can be reshaped without a copy")
+        return TensorView(self.t.view(*shape))
+
+    def contiguous(self):
+        """An owning, densely packed copy (a plain tensor)."""
+        return self.t.contiguous().clone() if self.t.is_contiguous() else self.t.contiguous()
+
+    def at(self, *index):
+        return self.t[tuple(index)].item()

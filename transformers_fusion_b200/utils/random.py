@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import math
 import os
+import threading
 
 M64 = 0xFFFFFFFFFFFFFFFF
 
@@ -74,3 +75,48 @@ def resolve_base_seed(cli_seed: int = 0) -> int:
         return int(os.environ.get("QUANT_SEED", "") or 42)
     except ValueError:
         return 42
+
+
+class GlobalSeedManager:
+    """Process-wide base seed: the ``QUANT_SEED`` environment variable when it is set to a non-zero number (runs are then
+    reproducible), otherwise 64 bits of operating-system entropy drawn once.  ``next_seed`` hands every caller (thread,
+    worker, generator) its own offset from the base.  Reference counterpart: GlobalSeedManager (include/quant/random.h:16-25,
+    src/core/random.cpp:13-44)."""
+    _base = 0
+    _counter = 0
+    _lock = threading.Lock()
+
+    @classmethod
+    def get_seed(cls) -> int:
+        with cls._lock:
+            if cls._base == 0:
+                env = os.environ.get("QUANT_SEED", "")
+                try:
+                    v = int(env) if env else 0
+                except ValueError:
+                    v = 0
+                if not env:
+                    v = int.from_bytes(os.urandom(8), "little")
+                cls._base = (v & 0xFFFFFFFFFFFFFFFF) or 1
+            return cls._base
+
+    @classmethod
+    def next_seed(cls) -> int:
+        base = cls.get_seed()
+        with cls._lock:
+            cls._counter += 1
+            return (base + cls._counter) & 0xFFFFFFFFFFFFFFFF
+
+    @staticmethod
+    def is_deterministic() -> bool:
+        env = os.environ.get("QUANT_SEED", "")
+        try:
+            return bool(env) and int(env) != 0
+        except ValueError:
+            return False
+
+    @classmethod
+    def reset(cls):
+        """Forget the cached base seed and the counter (the next ``get_seed`` reads the environment again)."""
+        with cls._lock:
+            cls._base = cls._counter = 0
