@@ -146,3 +146,43 @@ def test_moe_pipeline_from_files_early_stop_and_report(tmp_path):
     assert "Step 1 |" in log and "Early stop" in log
     rep = pipe.status_report()
     assert "MoE Training Report" in rep and "Experts: 4 (top-2)" in rep
+
+
+def test_stand_alone_mixture_layers_under_the_reference_class_names():
+    from transformers_fusion_b200.models import moe as M
+    cfg = M.MoEAllConfig(num_experts=8, top_k=2, expert_hidden=32)
+    x = torch.randn(2, 6, 16)
+    assert len(M.MOE_LAYER_CLASSES) == 25 and set(M.MOE_LAYER_CLASSES) <= set(M.VARIANTS)
+    for variant, cls in M.MOE_LAYER_CLASSES.items():
+        layer = cls(16, cfg)
+        xin = x.clone().requires_grad_(True)
+        out = layer(xin)
+        (out.output.float().sum() + out.aux_loss).backward()
+        assert out.output.shape == x.shape and torch.isfinite(out.output).all() and xin.grad is not None, variant
+        assert all(not n.startswith("block.qkv") for n, _ in layer.named_parameters())       # no attention half
+    sp = M.SparseMoE(16, cfg)
+    o = sp(x, training=False)
+    assert o.expert_indices.shape == (12, 2) and o.router_logits.shape == (12, 8) and sp.router_weight.shape == (8, 16) and len(sp.experts) == 8
+    # the layer is the weighted sum of its chosen experts
+    logits = (x.reshape(-1, 16) @ sp.router_weight.t()).detach()
+    w, idx = torch.softmax(logits.float(), -1).topk(2, -1)
+    w = w / w.sum(-1, keepdim=True) if sp.block.cfg.renormalize_topk else w
+    want = torch.zeros(12, 16)
+    for t in range(12):
+        for j in range(2):
+            gu, dn = sp.experts[int(idx[t, j])]
+            h = x.reshape(-1, 16)[t] @ gu.t()
+            want[t] += w[t, j] * ((torch.nn.functional.silu(h[:32]) * h[32:]) @ dn.t())
+    assert torch.allclose(o.output.reshape(12, 16), want, atol=1e-4)
+    gates = torch.softmax(logits, -1)
+    assert float(sp.load_balance_loss(gates, idx)) > 0 and float(sp.z_loss(logits)) > 0 and sp.compute_capacity(64) >= 64 * 2 // 8
+    blob = sp.export_weights()
+    other = M.SparseMoE(16, cfg, seed=5)
+    assert not torch.allclose(other(x).output, o.output)
+    other.import_weights(blob)
+    assert torch.allclose(other(x, training=False).output, o.output)
+    with pytest.raises(ValueError):
+        other.import_weights(blob[:-4])
+    res = M.ResidualMoE(16, cfg)
+    plain = M.SparseMoE(16, cfg)
+    assert torch.allclose(res(x, False).output, plain(x, False).output + x, atol=1e-5)       # same seed: same experts, plus the input

@@ -527,3 +527,109 @@ def create_moe_variant(variant: str, base: TransformerConfig, mcfg: "MoEAllConfi
     cfg.num_groups, cfg.top_groups, cfg.top_experts_per_group = m.num_groups, m.top_groups, m.top_experts_per_group
     cfg.num_domains, cfg.num_tasks, cfg.num_shared_layers = m.num_domains, m.num_tasks, m.num_shared_layers
     return MoEModel(cfg, **model_kw)
+
+
+# ------------------------------------------------------------------------------------------------
+# Stand-alone mixture layers under the reference's class names (include/quant/moe_variants.h:144-680): the feed-forward
+# half of a block of the named variant, usable inside any other network
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class MoELayerOutput:
+    output: torch.Tensor                    # same shape as the input
+    aux_loss: torch.Tensor                  # weighted load-balance + z loss (add it to the training loss)
+    expert_indices: Optional[torch.Tensor]  # [tokens, k] where the variant routes discretely
+    router_logits: Optional[torch.Tensor]
+
+
+class MoELayer(nn.Module):
+    VARIANT = "SPARSE_TOPK"
+
+    def __init__(self, hidden_size: int, cfg: Optional[MoEAllConfig] = None, device=None, dtype=torch.float32, seed: int = 0):
+        super().__init__()
+        self.config, self.hidden_size = cfg or MoEAllConfig(), hidden_size
+        base = TransformerConfig(vocab_size=8, hidden_size=hidden_size, num_layers=1, num_heads=1, ffn_hidden_size=self.config.expert_hidden,
+                                 max_seq_len=8)
+        host = create_moe_variant(self.VARIANT, base, self.config, device=device, dtype=dtype, seed=seed)
+        self.block = host.layers[0]
+        for n in ("attention_norm", "qkv", "o", "ffn_norm"):          # the attention half is not part of a mixture layer
+            setattr(self.block, n, None)
+
+    @property
+    def router_weight(self) -> torch.Tensor: return self.block.router
+
+    @property
+    def experts(self):
+        """(gate_up [2F, H], down [H, F]) views, one pair per expert."""
+        return [(self.block.gate_up[e], self.block.down[e]) for e in range(self.block.gate_up.shape[0])]
+
+    def forward(self, x: torch.Tensor, training: Optional[bool] = None) -> MoELayerOutput:
+        if training is not None:
+            self.block.train(training)
+        flat = x.reshape(-1, self.hidden_size)
+        y, aux = self.block.moe(flat)
+        if self.VARIANT == "RESIDUAL_MOE":
+            y = y + flat
+        b = self.block
+        return MoELayerOutput(y.view(x.shape), aux, getattr(b, "last_idx", None), getattr(b, "last_logits", None))
+
+    def load_balance_loss(self, gates: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+        E = self.config.num_experts
+        f = torch.bincount(indices.reshape(-1).long(), minlength=E).float() / max(1, indices.numel())
+        return E * (f * gates.float().reshape(-1, E).mean(0)).sum()
+
+    def z_loss(self, logits: torch.Tensor) -> torch.Tensor:
+        return (torch.logsumexp(logits.float(), -1) ** 2).mean()
+
+    def compute_capacity(self, T: int) -> int:
+        from .moe_routing import capacity_limit
+        return capacity_limit(T, self.config.num_experts, self.config.top_k, self.config.capacity_factor)
+
+    def export_weights(self) -> bytes:
+        """Every parameter of the layer as little-endian fp32, in ``named_parameters`` order."""
+        return b"".join(p.detach().float().cpu().contiguous().numpy().tobytes() for _, p in self.named_parameters())
+
+    def import_weights(self, data: bytes):
+        import numpy as np
+        a = np.frombuffer(data, dtype="<f4")
+        need = sum(p.numel() for p in self.parameters())
+        if a.size != need:
+            raise ValueError(f"{a.size} values given, the layer holds {need}")
+        off = 0
+        with torch.no_grad():
+            for _, p in self.named_parameters():
+                p.copy_(torch.from_numpy(a[off:off + p.numel()].copy()).view(p.shape).to(p.dtype))
+                off += p.numel()
+
+
+def _variant_layer(name: str, variant: str, doc: str):
+    return type(name, (MoELayer,), {"VARIANT": variant, "__doc__": doc})
+
+
+SparseMoE = _variant_layer("SparseMoE", "SPARSE_TOPK", "Top-k routing with load-balance and z losses.")
+SoftMoE = _variant_layer("SoftMoE", "SOFT_MIXTURE", "Every expert, soft-max mixing weights.")
+HierarchicalMoE = _variant_layer("HierarchicalMoE", "HIERARCHICAL", "Groups first, experts inside the chosen groups second.")
+MoMoE = _variant_layer("MoMoE", "MOMOE", "Mixture of mixtures: grouped routing with per-group balance.")
+ExpertChoiceMoE = _variant_layer("ExpertChoiceMoE", "EXPERT_CHOICE", "Experts pick their tokens up to a capacity.")
+HashMoE = _variant_layer("HashMoE", "HASH_ROUTED", "Routing by a fixed hash of the token: no learned router.")
+CrossLayerMoE = _variant_layer("CrossLayerMoE", "CROSS_LAYER", "One expert pool shared by several layers.")
+MultiModalMoE = _variant_layer("MultiModalMoE", "MULTIMODAL", "Top-k routing over experts shared by the modalities.")
+MMoE = _variant_layer("MMoE", "MMOE", "Multi-gate: one router per task over shared experts (set ``block.task_id``).")
+DeepSeekMoE = _variant_layer("DeepSeekMoE", "DEEPSEEK_MOE", "Fine-grained experts with a non-learned balancing bias.")
+BaseLayerMoE = _variant_layer("BaseLayerMoE", "BASE_LAYER", "Balanced assignment: every expert gets the same number of tokens.")
+DenseMoE = _variant_layer("DenseMoE", "DENSE_MOE", "All experts for every token.")
+SharedExpertMoE = _variant_layer("SharedExpertMoE", "SHARED_EXPERT", "Routed experts plus one expert every token uses.")
+ResidualMoE = _variant_layer("ResidualMoE", "RESIDUAL_MOE", "The mixture is added to its own input.")
+GatingDropoutMoE = _variant_layer("GatingDropoutMoE", "GATING_DROPOUT", "Router logits are dropped at random while training.")
+DomainMoE = _variant_layer("DomainMoE", "DOMAIN_MOE", "A domain classifier mixes per-domain expert groups.")
+ProductKeyMoE = _variant_layer("ProductKeyMoE", "PRODUCT_KEY", "Expert index from the product of two half-size key sets.")
+AttentionMoE = _variant_layer("AttentionMoE", "ATTENTION_MOE", "Routing scores from a query-key product.")
+LowRankMoE = _variant_layer("LowRankMoE", "LOWRANK_MOE", "Router and experts behind a low-rank bottleneck.")
+MambaMoE = _variant_layer("MambaMoE", "MAMBA_MOE", "A state projection is added to the routed input.")
+QuantizedINT8MoE = _variant_layer("QuantizedINT8MoE", "QUANTIZED_INT8_MOE", "Mixture output on a per-expert 8-bit grid.")
+QuantMoE = _variant_layer("QuantMoE", "QUANT_MOE", "Mixture output snapped to 4-bit levels.")
+Quant1MoE = _variant_layer("Quant1MoE", "Q1_MOE", "Mixture output snapped to ternary levels.")
+Q8MoE = _variant_layer("Q8MoE", "Q8_MOE", "Mixture output snapped to 8-bit levels.")
+Q4MoE = _variant_layer("Q4MoE", "Q4_MOE", "Mixture output snapped to 4-bit codebook levels.")
+MOE_LAYER_CLASSES = {c.VARIANT: c for c in (SparseMoE, SoftMoE, HierarchicalMoE, MoMoE, ExpertChoiceMoE, HashMoE, CrossLayerMoE, MultiModalMoE, MMoE,
+                                            DeepSeekMoE, BaseLayerMoE, DenseMoE, SharedExpertMoE, ResidualMoE, GatingDropoutMoE, DomainMoE,
+                                            ProductKeyMoE, AttentionMoE, LowRankMoE, MambaMoE, QuantizedINT8MoE, QuantMoE, Quant1MoE, Q8MoE, Q4MoE)}
